@@ -1,0 +1,190 @@
+/*
+ * jetfire_b200 -- C ABI of the B200-native JetFire decode hot path.
+ *
+ * Plain pointers and sizes only; no torch or CUDA types.  `stream` arguments are a
+ * `cudaStream_t` passed as `void*` (NULL = the legacy default stream).  Every device
+ * pointer must belong to the CUDA device that is current on the calling thread.
+ * Functions return 0 on success, a negative value for an argument error (nothing was
+ * launched) and a positive value for a runtime error.  Nothing here throws, and no
+ * function allocates device memory: callers hand in a workspace whose size
+ * `jf_decode_workspace_bytes` reports.
+ *
+ * Each entry point names the JetFire interface it replaces (paths inside the JetFire
+ * project).
+ */
+#ifndef JETFIRE_B200_H_
+#define JETFIRE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t jf_status_t;
+typedef void*   jf_stream_t;
+
+enum {
+  JF_OK               = 0,
+  JF_ERR_ARG          = -1, /* null pointer, bad shape, misaligned pointer          */
+  JF_ERR_UNSUPPORTED  = -2, /* valid request outside the built envelope              */
+  JF_ERR_WORKSPACE    = -3, /* workspace missing or too small                        */
+  JF_ERR_CUDA         = 1,  /* a CUDA call failed; see jf_last_cuda_error()          */
+  JF_ERR_TIMEOUT      = 2,  /* a bounded wait ran out (device status word or host)   */
+  JF_ERR_STATE        = 3   /* host-side object used in the wrong state              */
+};
+
+enum { JF_DTYPE_BF16 = 0, JF_DTYPE_FP16 = 1 };
+
+/* Quantisation modes of the release matrix that this library builds
+ * (jetfire_vllm/bench/artifact_performance.py:45): K3V2 = SymInt3K_SymInt2V with
+ * group 64, K4V4 = SymInt4K_SymInt4V with group 128. */
+enum { JF_MODE_K3V2 = 0, JF_MODE_K4V4 = 1 };
+
+#define JF_HEAD_DIM   128
+#define JF_BLOCK_SIZE 16
+#define JF_MAX_TOP_K  2048
+#define JF_MAX_GROUP  8     /* query heads per KV head handled in one pass */
+
+const char* jf_status_string(jf_status_t st);
+int32_t     jf_version(void);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+int32_t     jf_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------
+ * Quantise-on-append.
+ * Replaces the Triton writers fused_quant_write_int{2,3,4}_sym
+ * (jetfire_vllm/kernels/fused_quant_write.py:242, :337, :746) with the arithmetic of
+ * the torch reference quantize_and_pack (jetfire_vllm/kernels/intN_pack.py:60-107):
+ * IEEE divide, round-half-even, scale rounded to bf16 before the divide.
+ *
+ * x_tok      (T, H_kv, 128) bf16/fp16 device, element strides stride_t / stride_h,
+ *            innermost contiguous, rows 8-byte aligned
+ * slots      (T,) int64 device; row t goes to out[h, slots[t]]; negative = skip
+ * out_data   (H_kv, num_slots, 128*nbits/8) uint8 device
+ * out_scales (H_kv, num_slots, 128/group_size) bf16 device
+ * ------------------------------------------------------------------------------- */
+jf_status_t jf_pack_append(const void* x_tok, int32_t dtype, int64_t T, int32_t H_kv,
+                           int64_t stride_t, int64_t stride_h, const int64_t* slots,
+                           uint8_t* out_data, void* out_scales, int64_t num_slots,
+                           int32_t nbits, int32_t group_size, jf_stream_t stream);
+
+/* K and V of the same tokens in one launch (the reference's
+ * fused_quant_write_int4_sym_kv, jetfire_vllm/kernels/fused_quant_write.py:552-617,
+ * generalised to any K/V bit pair). */
+jf_status_t jf_pack_append_kv(const void* key_tok, const void* value_tok, int32_t dtype,
+                              int64_t T, int32_t H_kv,
+                              int64_t k_stride_t, int64_t k_stride_h,
+                              int64_t v_stride_t, int64_t v_stride_h,
+                              const int64_t* slots,
+                              uint8_t* k_data, void* k_scales, uint8_t* v_data, void* v_scales,
+                              int64_t num_slots, int32_t k_bits, int32_t v_bits,
+                              int32_t group_size, jf_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
+ * Fused low-bit decode attention.
+ *
+ * One call of jf_decode_fused does what the reference spreads over Stage A
+ * (int3_qk_scores_topk, jetfire_vllm/csrc/int3_qk_scores.cu:562-633;
+ * int8tc_qk_scores_topk_stats, csrc/int8tc_qk_scores.cu:2426-2482) and Stage B
+ * (int2_softmax_v_with_pre_corr_wvs2, csrc/int2_softmax_v.cu:792-901;
+ * int8tc_softmax_v_with_pre_corr_reg_stats, csrc/int8tc_softmax_v_fused.cu:1591-1734),
+ * in the single-call shape the reference defines for int2_fused_attn_topk
+ * (csrc/int2_fused_attn_topk.cu:404).  The three phases can also be called one by one.
+ * ------------------------------------------------------------------------------- */
+typedef struct jf_decode_args {
+  int32_t mode;          /* JF_MODE_*                                              */
+  int32_t q_dtype;       /* JF_DTYPE_* of q                                        */
+  int32_t B, H_q, H_kv;  /* H_q / H_kv in {1,2,4,8}                                */
+  int32_t max_S;         /* positions [0, min(seq_lens[b], max_S)) are attended    */
+  int32_t block_size;    /* must be 16                                             */
+  int32_t top_k;         /* 1..JF_MAX_TOP_K                                        */
+  int32_t max_blocks;    /* row stride of block_table, >= ceil(max_S / 16)         */
+  int32_t reserved0;
+  float   attn_scale;
+  int32_t reserved1;
+  int64_t num_slots;     /* slots per KV head in the packed cache                  */
+  const void*    q;            /* (B, H_q, 128) contiguous                         */
+  const uint8_t* k_data;       /* (H_kv, num_slots, 48 | 64)                       */
+  const void*    k_scales;     /* (H_kv, num_slots, NG) bf16                       */
+  const uint8_t* v_data;       /* (H_kv, num_slots, 32 | 64)                       */
+  const void*    v_scales;     /* (H_kv, num_slots, NG) bf16                       */
+  const int64_t* block_table;  /* (B, max_blocks)                                  */
+  const int32_t* seq_lens;     /* (B,)                                             */
+  /* outputs */
+  float*   scores;        /* optional (B, H_q, max_S): approximate scores, -inf past the
+                             sequence end; NULL keeps them in the workspace only   */
+  int64_t* topk_idx;      /* (B, H_q, top_k) positions, (score desc, index asc), -1 pad */
+  int64_t* topk_slots;    /* (B, H_q, top_k) physical slots, -1 pad                */
+  float*   o_hat;         /* (B, H_q, 128)                                          */
+  float*   o_old_unnorm;  /* (B, H_q, 128)                                          */
+  float*   W;             /* (B, H_q)                                               */
+  float*   softmax_m;     /* optional (B, H_q) reference point of the softmax       */
+  float*   softmax_inv_z; /* optional (B, H_q) 1 / sum exp(s - m)                   */
+  void*    workspace;     /* >= jf_decode_workspace_bytes(...), 256-byte aligned    */
+  uint64_t workspace_bytes;
+} jf_decode_args;
+
+uint64_t    jf_decode_workspace_bytes(int32_t mode, int32_t B, int32_t H_q, int32_t H_kv,
+                                      int32_t max_S, int32_t top_k);
+/* scan: dequantise, Q.K^T, online softmax, P.V over the packed cache; leaves split
+ * partials and approximate scores in the workspace (and in args->scores if given). */
+jf_status_t jf_decode_scan(const jf_decode_args* args, jf_stream_t stream);
+/* select: exact top-k per query head (csrc/int3_qk_scores.cu:426-554 with a
+ * deterministic order and tie rule) + slot translation (:399-417). */
+jf_status_t jf_topk_select(const jf_decode_args* args, jf_stream_t stream);
+/* finish: merge the split partials into o_hat and the softmax statistics, and compute
+ * the approximate contribution of the selected set (W, o_old_unnorm;
+ * csrc/int2_softmax_v.cu:738-788). */
+jf_status_t jf_decode_finish(const jf_decode_args* args, jf_stream_t stream);
+jf_status_t jf_decode_fused(const jf_decode_args* args, jf_stream_t stream);
+/* Reads back (synchronously, after the stream drained) the device status word of the
+ * workspace: 0, or JF_ERR_TIMEOUT if a bounded wait inside a kernel ran out. */
+jf_status_t jf_decode_status(const jf_decode_args* args, jf_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
+ * Correction merge: out = dtype(o_hat + W * float(o_new) - o_old_unnorm).
+ * Replaces blend_unnorm_into (jetfire_vllm/csrc/blend.cu:229-290).
+ * o_new may be device memory or the device alias of mapped pinned host memory.
+ * ------------------------------------------------------------------------------- */
+jf_status_t jf_merge_correct(const float* o_hat, const float* o_old_unnorm, const float* W,
+                             const void* o_new, void* out, int32_t dtype,
+                             int32_t B, int32_t H_q, jf_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
+ * Host correction: exact attention over the selected rows of the full-precision host
+ * mirror.  Replaces cpu_topk_attn (jetfire_vllm/csrc/cpu_topk_attn.cpp:854-956) and the
+ * worker pool of jetfire_vllm/csrc/jetfire_pool.h:69-334.
+ *
+ * q (B,H_q,128), k_shadow/v_shadow (H_kv,num_slots,128), o_new (B,H_q,128): host memory
+ * of `dtype`; head_map may be NULL (then h_kv = h_q / (H_q / H_kv)); ts_buf (B,H_q,K)
+ * int64 physical slots, invalid (<0 or >= num_slots) entries are skipped.
+ * done_flag, if not NULL, is set to 1 (release + store fence) after o_new is complete.
+ * ------------------------------------------------------------------------------- */
+jf_status_t jf_cpu_topk_attn(const void* q, const void* k_shadow, const void* v_shadow,
+                             const int64_t* head_map, const int64_t* ts_buf, void* o_new,
+                             int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                             int64_t num_slots, int32_t K, float scale, int64_t* done_flag);
+jf_status_t jf_set_cpu_attn_threads(int32_t n);
+int32_t     jf_get_cpu_attn_threads(void);
+
+/* Asynchronous form: submit returns at once, wait blocks up to timeout_ms
+ * (JF_ERR_TIMEOUT if the job is still running; it can be waited on again). */
+jf_status_t jf_pool_init(int32_t n_threads);
+jf_status_t jf_pool_submit(const void* q, const void* k_shadow, const void* v_shadow,
+                           const int64_t* head_map, const int64_t* ts_buf, void* o_new,
+                           int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                           int64_t num_slots, int32_t K, float scale, int64_t* done_flag);
+jf_status_t jf_pool_wait_timeout(int32_t timeout_ms);
+jf_status_t jf_pool_shutdown(void);
+
+/* Pinned host memory mapped into the device address space
+ * (alloc_mapped_pinned_pair, jetfire_vllm/csrc/cpu_topk_attn.cpp:958-1040). */
+jf_status_t jf_alloc_mapped(uint64_t bytes, void** host_ptr, void** device_ptr);
+jf_status_t jf_free_mapped(void* host_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JETFIRE_B200_H_ */

@@ -1,0 +1,419 @@
+// Host top-k correction: exact attention over the selected rows of the full-precision
+// KV mirror kept in host DRAM.
+//
+// Keeps the reference's design (jetfire_vllm/csrc/cpu_topk_attn.cpp:316-479, 602-690,
+// 854-956; pool: csrc/jetfire_pool.h:69-334): persistent workers, (b, h_q) rows split
+// evenly over them, per row: gather K/V rows by slot, s = (q . K) * scale in fp32,
+// softmax with exp, o_new = sum p * V in fp32, rounded to the mirror's 16-bit type;
+// invalid slots score -inf, an all-invalid row or a non-positive / non-finite
+// normaliser gives zeros; a store fence precedes the completion flag so that results
+// written to mapped (write-combined) memory are visible to the GPU.
+//
+// Differences: plain C ABI, no torch types; the AVX-512-BF16 path is selected at run time
+// (function multiversioning) so one binary runs on hosts with and without it; fp16
+// mirrors are supported; workers park on a condition variable after a short spin.
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <condition_variable>
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include <immintrin.h>
+
+#include "../../include/jetfire_b200.h"
+
+namespace {
+
+constexpr int D = JF_HEAD_DIM;
+
+inline float bf16_to_f32(uint16_t b) {
+  uint32_t u = static_cast<uint32_t>(b) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return 0x7FC0;  // NaN
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+inline float fp16_to_f32(uint16_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
+  uint32_t u;
+  if (exp == 0) {
+    if (man == 0) u = sign;
+    else {
+      int e = -1;
+      do { man <<= 1; ++e; } while (!(man & 0x400u));
+      u = sign | ((127 - 15 - e) << 23) | ((man & 0x3FFu) << 13);
+    }
+  } else if (exp == 31) u = sign | 0x7F800000u | (man << 13);
+  else u = sign | ((exp + 112) << 23) | (man << 13);
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+inline uint16_t f32_to_fp16(float f) {  // RNE
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  const uint32_t sign = (u >> 16) & 0x8000u;
+  u &= 0x7FFFFFFFu;
+  if (u >= 0x7F800000u) return static_cast<uint16_t>(sign | (u > 0x7F800000u ? 0x7E00u : 0x7C00u));
+  if (u >= 0x477FF000u) return static_cast<uint16_t>(sign | 0x7C00u);  // rounds to inf
+  if (u < 0x38800000u) {  // subnormal half
+    if (u < 0x33000000u) return static_cast<uint16_t>(sign);
+    const int shift = 126 - static_cast<int>(u >> 23);
+    uint32_t man = (u & 0x7FFFFFu) | 0x800000u;
+    const uint32_t lsb = 1u << shift, half = lsb >> 1;
+    uint32_t r = man >> shift;
+    const uint32_t rem = man & (lsb - 1);
+    if (rem > half || (rem == half && (r & 1u))) ++r;
+    return static_cast<uint16_t>(sign | r);
+  }
+  uint32_t r = u - 0x38000000u;
+  const uint32_t rem = r & 0x1FFFu;
+  r >>= 13;
+  if (rem > 0x1000u || (rem == 0x1000u && (r & 1u))) ++r;
+  return static_cast<uint16_t>(sign | r);
+}
+
+struct Job {
+  const uint16_t* q;
+  const uint16_t* ks;
+  const uint16_t* vs;
+  const int64_t* head_map;
+  const int64_t* ts;
+  uint16_t* o;
+  int dtype, B, H_q, H_kv, K;
+  int64_t num_slots;
+  float scale;
+  int64_t* done_flag;
+};
+
+struct Scratch {
+  std::vector<float> scores;
+  std::vector<float> vrows;  // K x 128 fp32 copies of the gathered V rows
+  std::vector<int64_t> slots;
+};
+
+inline float load_elem(const uint16_t* p, int dtype) { return dtype == JF_DTYPE_BF16 ? bf16_to_f32(*p) : fp16_to_f32(*p); }
+
+// ---- row kernels --------------------------------------------------------------------
+
+void finish_row(const Job& j, Scratch& sc, uint16_t* o_bh, bool any_valid, float max_score) {
+  const int K = j.K;
+  float* scores = sc.scores.data();
+  if (!any_valid) { std::memset(o_bh, 0, D * 2); return; }
+  float denom = 0.f;
+  for (int k = 0; k < K; ++k) {
+    scores[k] = std::exp(scores[k] - max_score);
+    denom += scores[k];
+  }
+  if (!(denom > 0.f) || !std::isfinite(denom)) { std::memset(o_bh, 0, D * 2); return; }
+  const float inv = 1.0f / denom;
+  float out[D];
+  for (int i = 0; i < D; ++i) out[i] = 0.f;
+  const float* vr = sc.vrows.data();
+  for (int k = 0; k < K; ++k) {
+    const float w = scores[k] * inv;
+    if (w == 0.f) continue;
+    const float* v = vr + static_cast<size_t>(k) * D;
+    for (int i = 0; i < D; ++i) out[i] += w * v[i];
+  }
+  if (j.dtype == JF_DTYPE_BF16) for (int i = 0; i < D; ++i) o_bh[i] = f32_to_bf16(out[i]);
+  else for (int i = 0; i < D; ++i) o_bh[i] = f32_to_fp16(out[i]);
+}
+
+// Portable path (any x86-64 / any dtype).
+void row_generic(const Job& j, Scratch& sc, int64_t b, int64_t h) {
+  const int K = j.K;
+  const int64_t bh = b * j.H_q + h;
+  const int G = j.H_q / j.H_kv;
+  float qf[D];
+  for (int i = 0; i < D; ++i) qf[i] = load_elem(j.q + bh * D + i, j.dtype);
+  float* scores = sc.scores.data();
+  float* vr = sc.vrows.data();
+  float max_score = -INFINITY;
+  bool any_valid = false;
+  for (int k = 0; k < K; ++k) {
+    const int64_t slot = j.ts[bh * K + k];
+    const int64_t hk = j.head_map ? j.head_map[bh * K + k] : h / G;
+    if (slot < 0 || slot >= j.num_slots || hk < 0 || hk >= j.H_kv) {
+      scores[k] = -INFINITY;
+      std::memset(vr + static_cast<size_t>(k) * D, 0, D * 4);
+      continue;
+    }
+    any_valid = true;
+    const uint16_t* kr = j.ks + (hk * j.num_slots + slot) * D;
+    const uint16_t* vrow = j.vs + (hk * j.num_slots + slot) * D;
+    float dot = 0.f;
+    for (int i = 0; i < D; ++i) dot += qf[i] * load_elem(kr + i, j.dtype);
+    for (int i = 0; i < D; ++i) vr[static_cast<size_t>(k) * D + i] = load_elem(vrow + i, j.dtype);
+    const float s = dot * j.scale;
+    scores[k] = s;
+    if (s > max_score) max_score = s;
+  }
+  finish_row(j, sc, j.o + bh * D, any_valid, max_score);
+}
+
+// AVX-512 + BF16 dot-product path for bf16 mirrors: vdpbf16ps accumulates pairs of bf16
+// products in fp32, as the reference's SIMD kernel does; rows are prefetched 8 ahead.
+__attribute__((target("avx512f,avx512bw,avx512vl,avx512bf16")))
+void row_avx512bf16(const Job& j, Scratch& sc, int64_t b, int64_t h) {
+  const int K = j.K;
+  const int64_t bh = b * j.H_q + h;
+  const int G = j.H_q / j.H_kv;
+  const uint16_t* q = j.q + bh * D;
+  __m512bh qv[4];
+  for (int i = 0; i < 4; ++i) qv[i] = (__m512bh)_mm512_loadu_si512(q + 32 * i);
+  float* scores = sc.scores.data();
+  float* vr = sc.vrows.data();
+  int64_t* slots = sc.slots.data();
+  // resolve row indices first so that prefetches can run ahead
+  for (int k = 0; k < K; ++k) {
+    const int64_t slot = j.ts[bh * K + k];
+    const int64_t hk = j.head_map ? j.head_map[bh * K + k] : h / G;
+    slots[k] = (slot < 0 || slot >= j.num_slots || hk < 0 || hk >= j.H_kv) ? -1 : hk * j.num_slots + slot;
+  }
+  constexpr int AHEAD = 8;
+  auto pf = [&](int k) {
+    if (k < K && slots[k] >= 0) {
+      const char* a = reinterpret_cast<const char*>(j.ks + slots[k] * D);
+      const char* c = reinterpret_cast<const char*>(j.vs + slots[k] * D);
+      for (int l = 0; l < 4; ++l) { _mm_prefetch(a + 64 * l, _MM_HINT_T0); _mm_prefetch(c + 64 * l, _MM_HINT_T0); }
+    }
+  };
+  for (int k = 0; k < AHEAD; ++k) pf(k);
+  float max_score = -INFINITY;
+  bool any_valid = false;
+  for (int k = 0; k < K; ++k) {
+    pf(k + AHEAD);
+    float* vdst = vr + static_cast<size_t>(k) * D;
+    if (slots[k] < 0) {
+      scores[k] = -INFINITY;
+      std::memset(vdst, 0, D * 4);
+      continue;
+    }
+    any_valid = true;
+    const uint16_t* kr = j.ks + slots[k] * D;
+    const uint16_t* vrow = j.vs + slots[k] * D;
+    __m512 acc = _mm512_setzero_ps();
+    for (int i = 0; i < 4; ++i) acc = _mm512_dpbf16_ps(acc, qv[i], (__m512bh)_mm512_loadu_si512(kr + 32 * i));
+    for (int i = 0; i < 8; ++i) {
+      const __m256i raw = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(vrow + 16 * i));
+      _mm512_storeu_ps(vdst + 16 * i, _mm512_castsi512_ps(_mm512_slli_epi32(_mm512_cvtepu16_epi32(raw), 16)));
+    }
+    const float s = _mm512_reduce_add_ps(acc) * j.scale;
+    scores[k] = s;
+    if (s > max_score) max_score = s;
+  }
+  finish_row(j, sc, j.o + bh * D, any_valid, max_score);
+}
+
+bool have_avx512bf16() {
+  static const bool v = __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") &&
+                        __builtin_cpu_supports("avx512vl") && __builtin_cpu_supports("avx512bf16");
+  return v;
+}
+
+void run_rows(const Job& j, int wid, int n_workers, Scratch& sc) {
+  const int64_t total = static_cast<int64_t>(j.B) * j.H_q;
+  const int64_t start = total * wid / n_workers, end = total * (wid + 1) / n_workers;
+  if (start >= end) return;
+  sc.scores.resize(j.K);
+  sc.vrows.resize(static_cast<size_t>(j.K) * D);
+  sc.slots.resize(j.K);
+  const bool simd = j.dtype == JF_DTYPE_BF16 && have_avx512bf16();
+  for (int64_t i = start; i < end; ++i) {
+    const int64_t b = i / j.H_q, h = i % j.H_q;
+    if (simd) row_avx512bf16(j, sc, b, h);
+    else row_generic(j, sc, b, h);
+  }
+}
+
+// ---- worker pool: one job in flight ----------------------------------------------------
+class Pool {
+ public:
+  ~Pool() { shutdown(); }
+  int size() const { return n_; }
+  bool running() const { return n_ > 0; }
+
+  void start(int n) {
+    shutdown();
+    std::lock_guard<std::mutex> g(api_);
+    n_ = n;
+    stop_ = false;
+    gen_.store(0);
+    pending_.store(0);
+    for (int i = 0; i < n; ++i) workers_.emplace_back([this, i] { loop(i); });
+  }
+  void shutdown() {
+    std::lock_guard<std::mutex> g(api_);
+    if (n_ == 0) return;
+    {
+      std::lock_guard<std::mutex> l(m_);
+      stop_ = true;
+      gen_.fetch_add(1);
+    }
+    cv_.notify_all();
+    for (auto& t : workers_) t.join();
+    workers_.clear();
+    n_ = 0;
+  }
+  // false if a job is still in flight
+  bool submit(const Job& j) {
+    if (pending_.load(std::memory_order_acquire) != 0) return false;
+    {
+      std::lock_guard<std::mutex> l(m_);
+      job_ = j;
+      pending_.store(n_, std::memory_order_release);
+      gen_.fetch_add(1, std::memory_order_release);
+    }
+    cv_.notify_all();
+    return true;
+  }
+  // true when no job is in flight within the timeout
+  bool wait(int timeout_ms) {
+    const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    for (int spin = 0; spin < 20000; ++spin) {
+      if (pending_.load(std::memory_order_acquire) == 0) return true;
+      _mm_pause();
+    }
+    std::unique_lock<std::mutex> l(m_);
+    return done_cv_.wait_until(l, t_end, [this] { return pending_.load(std::memory_order_acquire) == 0; });
+  }
+
+ private:
+  void loop(int wid) {
+    Scratch sc;
+    uint64_t seen = 0;
+    for (;;) {
+      // short spin for back-to-back layers, then park
+      bool got = false;
+      for (int spin = 0; spin < 4000; ++spin) {
+        if (gen_.load(std::memory_order_acquire) != seen) { got = true; break; }
+        _mm_pause();
+      }
+      if (!got) {
+        std::unique_lock<std::mutex> l(m_);
+        cv_.wait(l, [&] { return gen_.load(std::memory_order_acquire) != seen; });
+      }
+      Job j;
+      {
+        std::lock_guard<std::mutex> l(m_);
+        seen = gen_.load(std::memory_order_acquire);
+        if (stop_) return;
+        j = job_;
+      }
+      run_rows(j, wid, n_, sc);
+      _mm_sfence();  // results may sit in write-combined mapped memory
+      if (pending_.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+        if (j.done_flag) {
+          reinterpret_cast<std::atomic<int64_t>*>(j.done_flag)->store(1, std::memory_order_release);
+          _mm_sfence();
+        }
+        std::lock_guard<std::mutex> l(m_);
+        done_cv_.notify_all();
+      }
+    }
+  }
+
+  std::mutex api_, m_;
+  std::condition_variable cv_, done_cv_;
+  std::vector<std::thread> workers_;
+  Job job_{};
+  std::atomic<uint64_t> gen_{0};
+  std::atomic<int> pending_{0};
+  bool stop_ = false;
+  int n_ = 0;
+};
+
+Pool& pool() {
+  static Pool p;
+  return p;
+}
+std::atomic<int> g_threads{0};
+
+int default_threads() {
+  int n = static_cast<int>(std::thread::hardware_concurrency());
+  if (n <= 0) n = 1;
+  return n > 64 ? 64 : n;
+}
+
+jf_status_t make_job(Job& j, const void* q, const void* ks, const void* vs, const int64_t* hm, const int64_t* ts,
+                     void* o, int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots, int32_t K,
+                     float scale, int64_t* done_flag) {
+  if (!q || !ks || !vs || !ts || !o) return JF_ERR_ARG;
+  if (B <= 0 || H_q <= 0 || H_kv <= 0 || K <= 0 || num_slots <= 0 || H_q % H_kv != 0) return JF_ERR_ARG;
+  if (dtype != JF_DTYPE_BF16 && dtype != JF_DTYPE_FP16) return JF_ERR_UNSUPPORTED;
+  j = Job{static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ks), static_cast<const uint16_t*>(vs), hm, ts,
+          static_cast<uint16_t*>(o), dtype, B, H_q, H_kv, K, num_slots, scale, done_flag};
+  return JF_OK;
+}
+
+void ensure_pool() {
+  int want = g_threads.load();
+  if (want <= 0) want = default_threads();
+  if (!pool().running() || pool().size() != want) pool().start(want);
+}
+
+}  // namespace
+
+extern "C" jf_status_t jf_set_cpu_attn_threads(int32_t n) {
+  if (n <= 0 || n > 1024) return JF_ERR_ARG;
+  g_threads.store(n);
+  return JF_OK;
+}
+extern "C" int32_t jf_get_cpu_attn_threads(void) {
+  const int n = g_threads.load();
+  return n > 0 ? n : default_threads();
+}
+
+extern "C" jf_status_t jf_pool_init(int32_t n_threads) {
+  if (n_threads > 0) g_threads.store(n_threads);
+  if (!pool().wait(30000)) return JF_ERR_TIMEOUT;
+  ensure_pool();
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_pool_submit(const void* q, const void* k_shadow, const void* v_shadow,
+                                      const int64_t* head_map, const int64_t* ts_buf, void* o_new, int32_t dtype,
+                                      int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots, int32_t K, float scale,
+                                      int64_t* done_flag) {
+  Job j;
+  jf_status_t st = make_job(j, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                            scale, done_flag);
+  if (st != JF_OK) return st;
+  if (pool().running() && !pool().wait(0)) return JF_ERR_STATE;  // single job in flight
+  ensure_pool();
+  if (done_flag) reinterpret_cast<std::atomic<int64_t>*>(done_flag)->store(0, std::memory_order_release);
+  return pool().submit(j) ? JF_OK : JF_ERR_STATE;
+}
+
+extern "C" jf_status_t jf_pool_wait_timeout(int32_t timeout_ms) {
+  if (!pool().running()) return JF_OK;
+  return pool().wait(timeout_ms < 0 ? 0 : timeout_ms) ? JF_OK : JF_ERR_TIMEOUT;
+}
+
+extern "C" jf_status_t jf_pool_shutdown(void) {
+  if (pool().running() && !pool().wait(30000)) return JF_ERR_TIMEOUT;
+  pool().shutdown();
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_cpu_topk_attn(const void* q, const void* k_shadow, const void* v_shadow,
+                                        const int64_t* head_map, const int64_t* ts_buf, void* o_new, int32_t dtype,
+                                        int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots, int32_t K,
+                                        float scale, int64_t* done_flag) {
+  jf_status_t st = jf_pool_submit(q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                                  scale, done_flag);
+  if (st != JF_OK) return st;
+  return jf_pool_wait_timeout(30000);
+}

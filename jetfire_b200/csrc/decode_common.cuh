@@ -1,0 +1,66 @@
+// Workspace layout and launch geometry shared by the scan, select and finish kernels.
+#pragma once
+
+#include "jf_common.cuh"
+
+namespace jf {
+
+constexpr int kScanWarps = 4;         // consumer warps per scan CTA; each owns whole pages
+constexpr int kHeadsPad = 8;          // query heads of one KV head, padded to the MMA N
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kMinusBig = -1.0e30f; // finite stand-in for "no score seen yet"
+
+struct ModeInfo {
+  int k_bits, v_bits, group_size, ng, k_row, v_row;
+};
+__host__ __device__ inline ModeInfo mode_info(int mode) {
+  if (mode == JF_MODE_K4V4) return ModeInfo{4, 4, 128, 1, 64, 64};
+  return ModeInfo{3, 2, 64, 2, 48, 32};
+}
+
+// How many splits of the page range one (b, h_kv) pair is cut into.  Depends only on
+// (B, H_kv, max_S) so that the workspace query and every launch agree.
+__host__ __device__ inline int scan_splits(int B, int H_kv, int max_S) {
+  const int pages = (max_S + JF_BLOCK_SIZE - 1) / JF_BLOCK_SIZE;
+  const int pairs = B * H_kv;
+  int target = (kNumSMs * 4 + pairs - 1) / pairs;  // about four resident CTAs per SM
+  int cap = pages / 8;                             // at least two pages per warp
+  if (cap < 1) cap = 1;
+  if (target > cap) target = cap;
+  if (target > 512) target = 512;
+  if (target < 1) target = 1;
+  return target;
+}
+
+struct Workspace {
+  int32_t* status;   // [0] = sticky error code written by kernels
+  float* part_o;     // [B][H_kv][splits][8][128]
+  float* part_m;     // [B][H_kv][splits][8]
+  float* part_l;     // [B][H_kv][splits][8]
+  float* part_smax;  // [B][H_kv][splits][2]  largest K group scale seen (per group)
+  float* scores;     // [B][H_q][max_S] approximate scores
+  uint64_t bytes;
+};
+
+__host__ __device__ inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+inline Workspace carve_workspace(void* base, int B, int H_q, int H_kv, int max_S, bool need_scores) {
+  const uint64_t splits = scan_splits(B, H_kv, max_S);
+  const uint64_t pairs = static_cast<uint64_t>(B) * H_kv * splits;
+  uint64_t off = 0;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  Workspace w{};
+  w.status = reinterpret_cast<int32_t*>(p + off);   off = align_up(off + 256, 256);
+  w.part_o = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * JF_HEAD_DIM * 4, 256);
+  w.part_m = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
+  w.part_l = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
+  w.part_smax = reinterpret_cast<float*>(p + off);  off = align_up(off + pairs * 2 * 4, 256);
+  w.scores = reinterpret_cast<float*>(p + off);
+  if (need_scores) off = align_up(off + static_cast<uint64_t>(B) * H_q * max_S * 4, 256);
+  w.bytes = off;
+  return w;
+}
+
+jf_status_t validate_decode_args(const jf_decode_args* a);
+
+}  // namespace jf

@@ -1,0 +1,198 @@
+// finish: merge the scan's split partials (log-sum-exp) into o_hat and the softmax
+// statistics, then compute the approximate contribution of the selected set,
+//   W = sum_{i in T} p_i,   o_old_unnorm[d] = sum_{i in T} (p_i * vscale_i,g(d)) * vcode_i,d
+// with p_i = exp(s_i - m) / Z taken from the same approximate scores the scan used
+// (jetfire_vllm/csrc/int2_softmax_v.cu:738-788; V4: csrc/int4_softmax_v.cu:599-817).
+// merge_correct: out = dtype(o_hat + W * float(o_new) - o_old_unnorm)
+// (jetfire_vllm/csrc/blend.cu:202-226).  The normaliser stays the approximate softmax's:
+// this is mass substitution, not a re-normalised merge.
+#include "decode_common.cuh"
+
+namespace jf {
+
+namespace {
+
+constexpr int kChunk = 128;
+
+struct FinishParams {
+  const float* scores;
+  const float* part_o;
+  const float* part_m;
+  const float* part_l;
+  const uint8_t* v_data;
+  const uint16_t* v_scales;
+  const int64_t* block_table;
+  const int32_t* seq_lens;
+  const int64_t* topk_idx;
+  float* o_hat;
+  float* o_old;
+  float* W;
+  float* softmax_m;
+  float* softmax_inv_z;
+  int64_t num_slots;
+  int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(JF_HEAD_DIM)
+decode_finish_kernel(const FinishParams p) {
+  __shared__ int64_t sm_slot[kChunk];
+  __shared__ float sm_pv[kChunk][2];
+  __shared__ float sm_p[kChunk];
+  __shared__ float sm_w[4];
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int hkv = h / p.G, hi = h - hkv * p.G;
+  const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
+  const int n = min(p.seq_lens[b], p.max_S);
+
+  // ---- merge splits ----
+  const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
+  float M = kMinusBig;
+  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.part_m[(pbase + s) * kHeadsPad + hi]);
+  float Z = 0.f, o = 0.f;
+  for (int s = 0; s < p.splits; ++s) {
+    const float w = ex2((p.part_m[(pbase + s) * kHeadsPad + hi] - M) * kLog2e);
+    Z = fmaf(p.part_l[(pbase + s) * kHeadsPad + hi], w, Z);
+    o = fmaf(p.part_o[((pbase + s) * kHeadsPad + hi) * JF_HEAD_DIM + d], w, o);
+  }
+  const float inv_z = (Z > 0.f && n > 0) ? (1.0f / Z) : 0.f;
+  if (!(Z > 0.f) || n <= 0) M = 0.f;
+  p.o_hat[bh * JF_HEAD_DIM + d] = o * inv_z;
+  if (d == 0) {
+    if (p.softmax_m) p.softmax_m[bh] = M;
+    if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
+  }
+
+  // ---- approximate contribution of the selected set ----
+  const ModeInfo mi = mode_info(MODE);
+  const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
+  const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+  const int64_t* bt = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  const float* srow = p.scores + bh * p.max_S;
+  const int64_t* sel = p.topk_idx + bh * p.top_k;
+  float acc = 0.f, wsum = 0.f;
+  for (int k0 = 0; k0 < p.top_k; k0 += kChunk) {
+    {
+      const int kk = k0 + d;
+      int64_t slot = -1;
+      float pr = 0.f, pv0 = 0.f, pv1 = 0.f;
+      if (kk < p.top_k) {
+        const int64_t pos = sel[kk];
+        if (pos >= 0 && pos < n) {
+          const int64_t blk = bt[pos >> 4];
+          if (blk >= 0 && blk < (p.num_slots >> 4)) {
+            slot = blk * 16 + (pos & 15);
+            pr = ex2((srow[pos] - M) * kLog2e) * inv_z;
+            if (MODE == JF_MODE_K3V2) {
+              const uint32_t sw = __ldg(reinterpret_cast<const uint32_t*>(v_sc + slot * 2));
+              pv0 = pr * __uint_as_float(sw << 16);
+              pv1 = pr * __uint_as_float(sw & 0xFFFF0000u);
+            } else {
+              pv0 = pv1 = pr * bf16_bits_to_f32(__ldg(v_sc + slot));
+            }
+          }
+        }
+      }
+      sm_slot[d] = slot; sm_p[d] = pr; sm_pv[d][0] = pv0; sm_pv[d][1] = pv1;
+    }
+    __syncthreads();
+    const int kend = min(kChunk, p.top_k - k0);
+    for (int j = 0; j < kend; ++j) {
+      const int64_t slot = sm_slot[j];
+      if (slot < 0) continue;
+      int code;
+      if (MODE == JF_MODE_K3V2) {
+        const uint32_t byte = __ldg(v_rows + slot * 32 + (d >> 2));
+        code = static_cast<int>((byte >> ((3 - (d & 3)) * 2)) & 3u) - 2;
+      } else {
+        const uint32_t byte = __ldg(v_rows + slot * 64 + (d >> 1));
+        code = static_cast<int>((d & 1) ? (byte & 15u) : (byte >> 4)) - 8;
+      }
+      acc = fmaf(sm_pv[j][d >> 6], static_cast<float>(code), acc);
+      wsum += sm_p[j];
+    }
+    __syncthreads();
+  }
+  p.o_old[bh * JF_HEAD_DIM + d] = acc;
+  if (d == 0) p.W[bh] = wsum;
+  (void)sm_w;
+}
+
+template <int DT>
+__global__ void merge_correct_kernel(const float* __restrict__ o_hat, const float* __restrict__ o_old,
+                                     const float* __restrict__ W, const uint16_t* __restrict__ o_new,
+                                     uint16_t* __restrict__ out, int total) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float w = W[i / JF_HEAD_DIM];
+  const float v = o_hat[i] + w * Elem<DT>::to_f32(o_new[i]) - o_old[i];
+  out[i] = Elem<DT>::from_f32(v);
+}
+
+}  // namespace
+
+}  // namespace jf
+
+extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t stream_) {
+  using namespace jf;
+  jf_status_t st = validate_decode_args(a);
+  if (st != JF_OK) return st;
+  if (!a->topk_idx || !a->o_hat || !a->o_old_unnorm || !a->W) return JF_ERR_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, true);
+  FinishParams fp{};
+  fp.scores = a->scores ? a->scores : ws.scores;
+  fp.part_o = ws.part_o; fp.part_m = ws.part_m; fp.part_l = ws.part_l;
+  fp.v_data = a->v_data; fp.v_scales = static_cast<const uint16_t*>(a->v_scales);
+  fp.block_table = a->block_table; fp.seq_lens = a->seq_lens; fp.topk_idx = a->topk_idx;
+  fp.o_hat = a->o_hat; fp.o_old = a->o_old_unnorm; fp.W = a->W;
+  fp.softmax_m = a->softmax_m; fp.softmax_inv_z = a->softmax_inv_z;
+  fp.num_slots = a->num_slots;
+  fp.B = a->B; fp.H_q = a->H_q; fp.H_kv = a->H_kv; fp.G = a->H_q / a->H_kv;
+  fp.max_S = a->max_S; fp.max_blocks = a->max_blocks;
+  fp.splits = scan_splits(a->B, a->H_kv, a->max_S);
+  fp.top_k = a->top_k;
+  dim3 grid(a->H_q, a->B);
+  if (a->mode == JF_MODE_K3V2) decode_finish_kernel<JF_MODE_K3V2><<<grid, JF_HEAD_DIM, 0, stream>>>(fp);
+  else decode_finish_kernel<JF_MODE_K4V4><<<grid, JF_HEAD_DIM, 0, stream>>>(fp);
+  JF_CUDA_TRY(cudaGetLastError());
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_decode_fused(const jf_decode_args* a, jf_stream_t stream) {
+  jf_status_t st = jf_decode_scan(a, stream);
+  if (st != JF_OK) return st;
+  st = jf_topk_select(a, stream);
+  if (st != JF_OK) return st;
+  return jf_decode_finish(a, stream);
+}
+
+extern "C" jf_status_t jf_decode_status(const jf_decode_args* a, jf_stream_t stream_) {
+  using namespace jf;
+  if (!a || !a->workspace) return JF_ERR_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int32_t host = 0;
+  JF_CUDA_TRY(cudaMemcpyAsync(&host, a->workspace, sizeof(host), cudaMemcpyDeviceToHost, stream));
+  JF_CUDA_TRY(cudaStreamSynchronize(stream));
+  return host == 0 ? JF_OK : static_cast<jf_status_t>(host);
+}
+
+extern "C" jf_status_t jf_merge_correct(const float* o_hat, const float* o_old_unnorm, const float* W,
+                                        const void* o_new, void* out, int32_t dtype, int32_t B,
+                                        int32_t H_q, jf_stream_t stream_) {
+  using namespace jf;
+  if (!o_hat || !o_old_unnorm || !W || !o_new || !out || B <= 0 || H_q <= 0) return JF_ERR_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int total = B * H_q * JF_HEAD_DIM;
+  const int threads = 256, blocks = (total + threads - 1) / threads;
+  if (dtype == JF_DTYPE_BF16)
+    merge_correct_kernel<JF_DTYPE_BF16><<<blocks, threads, 0, stream>>>(
+        o_hat, o_old_unnorm, W, static_cast<const uint16_t*>(o_new), static_cast<uint16_t*>(out), total);
+  else if (dtype == JF_DTYPE_FP16)
+    merge_correct_kernel<JF_DTYPE_FP16><<<blocks, threads, 0, stream>>>(
+        o_hat, o_old_unnorm, W, static_cast<const uint16_t*>(o_new), static_cast<uint16_t*>(out), total);
+  else
+    return JF_ERR_UNSUPPORTED;
+  JF_CUDA_TRY(cudaGetLastError());
+  return JF_OK;
+}

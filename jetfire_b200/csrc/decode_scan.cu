@@ -1,0 +1,476 @@
+// Fused low-bit decode-attention scan for sm_100a.
+//
+// One pass over the packed KV cache computes, for all query heads of a KV head at once
+// (so every packed byte is read from HBM once per step):
+//   approximate scores  s = attn_scale * sum_g  scale_g * (q . codes_g)       -> scratch
+//   online softmax      p = exp(s - m_ref)                                   (registers)
+//   output partial      O += (p * vscale) . vcodes                           (registers)
+// Replaces the reference's Stage A score kernels (jetfire_vllm/csrc/int3_qk_scores.cu:
+// 103-312, csrc/int8tc_qk_scores.cu:133-488) and Stage B softmax.V kernels
+// (csrc/int2_softmax_v.cu:101-144, 601-789; csrc/int8tc_softmax_v_fused.cu:1017-1401),
+// which materialise scores and weights in HBM and read V once per *query* head.
+//
+// Data movement: a 16-token page of the cache is contiguous per tensor (768 B of INT3 K,
+// 512 B of INT2 V, 64 + 64 B of bf16 scales for K3V2), so each page is fetched with four
+// bulk-async copies (TMA, non-tensor form) into a per-warp ring of shared-memory stages,
+// completion counted on an mbarrier.  A page is exactly one MMA M tile.
+//
+// Compute: tokens sit on the MMA M axis and the (<= 8) query heads on N = 8.  Packed codes
+// are expanded in registers straight into the A fragments of mma.sync.m16n8k16 (the
+// dequantised tile never goes through shared memory): a 3-/2-/4-bit field is OR-ed into
+// the mantissa of an fp16 constant (1024 + code * 2^pos), the bias is subtracted exactly,
+// and the 2^pos factor is undone on the other operand (K: folded into Q) or on the output
+// row (V).  Group scales are applied in fp32 after the K MMA and folded into P before the
+// V MMA, so the integer codes stay exact in fp16.
+#include "decode_common.cuh"
+
+namespace jf {
+
+namespace {
+
+constexpr int kStages = 8;  // pages in flight per warp
+
+template <int MODE> struct Tile;
+template <> struct Tile<JF_MODE_K3V2> {
+  static constexpr int kKRow = 48, kVRow = 32, kNG = 2;
+  static constexpr int kKOff = 0, kVOff = 768, kKsOff = 1280, kVsOff = 1344, kBytes = 1408;
+};
+template <> struct Tile<JF_MODE_K4V4> {
+  static constexpr int kKRow = 64, kVRow = 64, kNG = 1;
+  static constexpr int kKOff = 0, kVOff = 1024, kKsOff = 2048, kVsOff = 2080, kBytes = 2112;
+};
+
+struct ScanParams {
+  const void* q;
+  const uint8_t* k_data;
+  const uint16_t* k_scales;
+  const uint8_t* v_data;
+  const uint16_t* v_scales;
+  const int64_t* block_table;
+  const int32_t* seq_lens;
+  float* scores;
+  float* part_o;
+  float* part_m;
+  float* part_l;
+  float* part_smax;
+  int32_t* status;
+  int64_t num_slots;
+  int B, H_q, H_kv, G, max_S, max_blocks, splits, pages_per_split;
+  float attn_scale;
+};
+
+// bit position at which code x (0..7) of an INT3 group is picked up, see unpack below
+__device__ __forceinline__ constexpr int k3_pos(int x) {
+  return x == 0 ? 3 : x == 1 ? 0 : x == 2 ? 7 : x == 3 ? 4 : x == 4 ? 1 : x == 5 ? 6 : x == 6 ? 3 : 0;
+}
+// bit position of 2-bit field f (0..7, bit offset 2f of a 16-bit half row word)
+__device__ __forceinline__ constexpr int v2_pos(int f) { return f <= 4 ? 2 * f : 2 * f - 10; }
+// head-dim index inside the 8-wide chunk for field f: bytes are little-endian in the
+// 16-bit load, codes MSB-first inside a byte
+__device__ __forceinline__ constexpr int v2_dlocal(int f) { return 4 * (f >> 2) + 3 - (f & 3); }
+
+constexpr uint32_t kMagic = 0x64006400u;  // fp16 1024.0 in both halves
+
+template <int POS>
+__device__ __forceinline__ uint32_t k3_field(uint32_t v) {
+  // ((v & field) | 1024) - (1024 + 4 * 2^POS)  ==  (code - 4) * 2^POS, exact in fp16
+  constexpr uint32_t m = (7u << POS) | (7u << (POS + 16));
+  constexpr uint32_t b = (0x6400u | (4u << POS)) * 0x10001u;
+  return hsub2_u32(and_or(v, m, kMagic), b);
+}
+template <int POS>
+__device__ __forceinline__ uint32_t v2_field(uint32_t v) {
+  constexpr uint32_t m = (3u << POS) | (3u << (POS + 16));
+  constexpr uint32_t b = (0x6400u | (2u << POS)) * 0x10001u;
+  return hsub2_u32(and_or(v, m, kMagic), b);
+}
+
+template <int DT>
+__device__ __forceinline__ float load_q(const void* q, int64_t idx) {
+  return Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(q)[idx]);
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------
+// K3V2
+// ------------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kScanWarps * 32, 4)
+scan_k3v2_kernel(const ScanParams p) {
+  using T = Tile<JF_MODE_K3V2>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+
+  uint8_t* my_stages = smem + warp * (kStages * T::kBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * kStages * T::kBytes) + warp * kStages;
+  int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * kStages * (T::kBytes + 8)) + warp * kStages;
+
+  const int len = min(p.seq_lens[b], p.max_S);
+  const int n_pages = (len + 15) >> 4;
+  const int pg_begin = split * p.pages_per_split;
+  const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
+  // this warp's pages: pg_begin + warp, + 4, ...
+  const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;  // may be <= 0
+
+  if (lane == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+  }
+  fence_barrier_init();
+  __syncwarp();
+
+  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  const int64_t n_blocks_phys = p.num_slots >> 4;
+  const uint8_t* kd_h = p.k_data + static_cast<int64_t>(hkv) * p.num_slots * T::kKRow;
+  const uint8_t* vd_h = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * T::kVRow;
+  const uint16_t* ks_h = p.k_scales + static_cast<int64_t>(hkv) * p.num_slots * T::kNG;
+  const uint16_t* vs_h = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * T::kNG;
+
+  // Lanes 0..3 each issue one of the four copies of a page.
+  auto issue = [&](int it, int64_t blk) {
+    const int st = it % kStages;
+    const int pg = pg_begin + warp + it * kScanWarps;
+    int valid = min(16, len - pg * 16);
+    if (blk < 0 || blk >= n_blocks_phys) { blk = 0; valid = 0; }
+    uint8_t* dst = my_stages + st * T::kBytes;
+    if (lane == 0) {
+      page_valid[st] = valid;
+      mbar_expect_tx(&bars[st], T::kBytes);
+    }
+    __syncwarp();
+    if (lane < 4) {
+      const void* src;
+      uint32_t off, bytes;
+      if (lane == 0)      { src = kd_h + blk * (16 * T::kKRow); off = T::kKOff;  bytes = 16 * T::kKRow; }
+      else if (lane == 1) { src = vd_h + blk * (16 * T::kVRow); off = T::kVOff;  bytes = 16 * T::kVRow; }
+      else if (lane == 2) { src = ks_h + blk * (16 * T::kNG);   off = T::kKsOff; bytes = 32 * T::kNG; }
+      else                { src = vs_h + blk * (16 * T::kNG);   off = T::kVsOff; bytes = 32 * T::kNG; }
+      bulk_g2s(dst + off, src, bytes, &bars[st]);
+    }
+  };
+
+  // prologue
+  {
+    const int pro = min(kStages, my_n);
+    for (int it = 0; it < pro; ++it) issue(it, bt_row[pg_begin + warp + it * kScanWarps]);
+  }
+  int64_t next_blk = 0;
+  if (kStages < my_n) next_blk = bt_row[pg_begin + warp + kStages * kScanWarps];
+
+  // ---- query fragments: B operand of the K MMA, scaled by 2^-pos of the code it meets ----
+  uint32_t qf[8][2];
+  {
+    const int h = hkv * p.G + g;
+    const bool live = g < p.G;
+    const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + h) * JF_HEAD_DIM;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int qh = ks >> 2, s = ks & 3;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int x = 2 * s + half;
+        const int d0 = 64 * qh + 16 * tig + x;  // group j = 0
+        const int d1 = d0 + 8;                  // group j = 1
+        float a = 0.f, c = 0.f;
+        if (live) { a = load_q<DT>(p.q, qbase + d0); c = load_q<DT>(p.q, qbase + d1); }
+        const float sc = 1.0f / static_cast<float>(1 << k3_pos(x));
+        qf[ks][half] = pack_f16x2_sat(a * sc, c * sc);
+      }
+    }
+  }
+
+  float oacc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+  float m_ref0 = kMinusBig, m_ref1 = kMinusBig, l0 = 0.f, l1 = 0.f;
+  float smax0 = 0.f, smax1 = 0.f;
+  bool failed = false;
+
+  const int t0 = (g >> 1) | ((g & 1) << 2);  // token of MMA row g (rows g + 8 -> t0 + 8)
+  const int h0 = hkv * p.G + 2 * tig;
+  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S;
+  const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
+  const float attn = p.attn_scale;
+
+  for (int it = 0; it < my_n; ++it) {
+    const int st = it % kStages;
+    if (!mbar_wait(&bars[st], (it / kStages) & 1)) {
+      // give the copies that were already issued a short, bounded chance to land
+      for (int j = it + 1; j < min(my_n, it + kStages); ++j)
+        mbar_wait(&bars[j % kStages], (j / kStages) & 1, 1000000ull);
+      failed = true;
+      break;
+    }
+    const uint8_t* sp = my_stages + st * T::kBytes;
+    const int valid = page_valid[st];
+    const int pg = pg_begin + warp + it * kScanWarps;
+
+    // ---------------- K: unpack + Q.K^T ----------------
+    float acc[2][4];
+#pragma unroll
+    for (int qh = 0; qh < 2; ++qh) {
+      acc[qh][0] = acc[qh][1] = acc[qh][2] = acc[qh][3] = 0.f;
+      uint32_t R[2][8];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint8_t* row = sp + T::kKOff + (t0 + 8 * r) * T::kKRow + 8 * qh + 2 * tig;
+        const uint32_t H0 = *reinterpret_cast<const uint16_t*>(row);
+        const uint32_t H1 = *reinterpret_cast<const uint16_t*>(row + 16);
+        const uint32_t H2 = *reinterpret_cast<const uint16_t*>(row + 32);
+        const uint32_t V0 = prmt(H2, H1, 0x5140);  // halves: bits 15..0 of the two 24-bit groups
+        const uint32_t V1 = prmt(H1, H0, 0x5140);  // halves: bits 23..8
+        const uint32_t V2 = V1 >> 10;              // halves (low 6 bits): bits 23..18
+        R[r][7] = k3_field<0>(V0);
+        R[r][6] = k3_field<3>(V0);
+        R[r][5] = k3_field<6>(V0);
+        R[r][4] = k3_field<1>(V1);
+        R[r][3] = k3_field<4>(V1);
+        R[r][2] = k3_field<7>(V1);
+        R[r][1] = k3_field<0>(V2);
+        R[r][0] = k3_field<3>(V2);
+      }
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        mma_f16_16816(acc[qh], R[0][2 * s], R[1][2 * s], R[0][2 * s + 1], R[1][2 * s + 1],
+                      qf[qh * 4 + s][0], qf[qh * 4 + s][1]);
+    }
+
+    // ---------------- scores ----------------
+    const uint32_t ksw0 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + t0 * 4);
+    const uint32_t ksw1 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + (t0 + 8) * 4);
+    const uint32_t vsw0 = *reinterpret_cast<const uint32_t*>(sp + T::kVsOff + t0 * 4);
+    const uint32_t vsw1 = *reinterpret_cast<const uint32_t*>(sp + T::kVsOff + (t0 + 8) * 4);
+    float ks00 = __uint_as_float(ksw0 << 16), ks01 = __uint_as_float(ksw0 & 0xFFFF0000u);
+    float ks10 = __uint_as_float(ksw1 << 16), ks11 = __uint_as_float(ksw1 & 0xFFFF0000u);
+    float vs00 = __uint_as_float(vsw0 << 16), vs01 = __uint_as_float(vsw0 & 0xFFFF0000u);
+    float vs10 = __uint_as_float(vsw1 << 16), vs11 = __uint_as_float(vsw1 & 0xFFFF0000u);
+    if (valid < 16) {  // last page of the sequence: neutralise rows past the end
+      if (t0 >= valid) { ks00 = ks01 = vs00 = vs01 = 0.f; }
+      if (t0 + 8 >= valid) { ks10 = ks11 = vs10 = vs11 = 0.f; }
+    }
+    smax0 = fmaxf(smax0, fmaxf(ks00, ks10));
+    smax1 = fmaxf(smax1, fmaxf(ks01, ks11));
+    float s0 = attn * (ks00 * acc[0][0] + ks01 * acc[1][0]);  // row g,   head 2tig
+    float s1 = attn * (ks00 * acc[0][1] + ks01 * acc[1][1]);  // row g,   head 2tig+1
+    float s2 = attn * (ks10 * acc[0][2] + ks11 * acc[1][2]);  // row g+8, head 2tig
+    float s3 = attn * (ks10 * acc[0][3] + ks11 * acc[1][3]);  // row g+8, head 2tig+1
+    if (valid < 16) {
+      if (t0 >= valid) { s0 = s1 = -INFINITY; }
+      if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; }
+    }
+    {
+      float* r0 = score_row0 + pg * 16;
+      if (st0) { if (t0 < valid) r0[t0] = s0; if (t0 + 8 < valid) r0[t0 + 8] = s2; }
+      if (st1) { if (t0 < valid) r0[p.max_S + t0] = s1; if (t0 + 8 < valid) r0[p.max_S + t0 + 8] = s3; }
+    }
+
+    // ---------------- online softmax (reference point may lag the true max by < 4) ----------------
+    {
+      float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+      const bool need = (mx0 > m_ref0 + 4.0f) || (mx1 > m_ref1 + 4.0f);
+      if (__any_sync(0xFFFFFFFFu, need)) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
+        }
+        const float n0 = fmaxf(m_ref0, mx0), n1 = fmaxf(m_ref1, mx1);
+        const float f0 = ex2((m_ref0 - n0) * kLog2e), f1 = ex2((m_ref1 - n1) * kLog2e);
+        l0 *= f0; l1 *= f1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { oacc[i][0] *= f0; oacc[i][1] *= f1; oacc[i][2] *= f0; oacc[i][3] *= f1; }
+        m_ref0 = n0; m_ref1 = n1;
+      }
+    }
+    const float mb0 = m_ref0 * kLog2e, mb1 = m_ref1 * kLog2e;
+    const float p0 = ex2(fmaf(s0, kLog2e, -mb0)), p1 = ex2(fmaf(s1, kLog2e, -mb1));
+    const float p2 = ex2(fmaf(s2, kLog2e, -mb0)), p3 = ex2(fmaf(s3, kLog2e, -mb1));
+    l0 += p0 + p2;
+    l1 += p1 + p3;
+
+    // ---------------- V: unpack + (P * vscale).V ----------------
+#pragma unroll
+    for (int qh = 0; qh < 2; ++qh) {
+      const float va = qh ? vs01 : vs00, vb = qh ? vs11 : vs10;
+      const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * va, p1 * va));  // tokens tig, tig+4
+      const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vb, p3 * vb));  // tokens tig+8, tig+12
+      const uint8_t* vbase = sp + T::kVOff + 16 * qh + 2 * g;
+      const uint32_t Ha = *reinterpret_cast<const uint16_t*>(vbase + (tig)*T::kVRow);
+      const uint32_t Hb = *reinterpret_cast<const uint16_t*>(vbase + (tig + 4) * T::kVRow);
+      const uint32_t Hc = *reinterpret_cast<const uint16_t*>(vbase + (tig + 8) * T::kVRow);
+      const uint32_t Hd = *reinterpret_cast<const uint16_t*>(vbase + (tig + 12) * T::kVRow);
+      const uint32_t XA = prmt(Ha, Hb, 0x5410), XB = prmt(Hc, Hd, 0x5410);
+      const uint32_t XA2 = XA >> 10, XB2 = XB >> 10;
+      // fields 2ml -> output row g, 2ml+1 -> output row g+8
+      mma_f16_16816(oacc[qh * 4 + 0], v2_field<0>(XA), v2_field<2>(XA), v2_field<0>(XB), v2_field<2>(XB), B0, B1);
+      mma_f16_16816(oacc[qh * 4 + 1], v2_field<4>(XA), v2_field<6>(XA), v2_field<4>(XB), v2_field<6>(XB), B0, B1);
+      mma_f16_16816(oacc[qh * 4 + 2], v2_field<8>(XA), v2_field<0>(XA2), v2_field<8>(XB), v2_field<0>(XB2), B0, B1);
+      mma_f16_16816(oacc[qh * 4 + 3], v2_field<2>(XA2), v2_field<4>(XA2), v2_field<2>(XB2), v2_field<4>(XB2), B0, B1);
+    }
+
+    __syncwarp();
+    if (it + kStages < my_n) {
+      issue(it + kStages, next_blk);
+      if (it + kStages + 1 < my_n) next_blk = bt_row[pg_begin + warp + (it + kStages + 1) * kScanWarps];
+    }
+  }
+
+  if (failed && lane == 0) atomicExch(p.status, JF_ERR_TIMEOUT);
+
+  // ---------------- CTA merge: 4 warps -> one partial ----------------
+  __syncthreads();  // every warp is done with its stages (or gave up); smem is reused below
+  float* sm_o = reinterpret_cast<float*>(smem);              // [8][128]
+  float* sm_m = sm_o + kHeadsPad * JF_HEAD_DIM;               // [4][8]
+  float* sm_l = sm_m + kScanWarps * kHeadsPad;                // [4][8]
+  float* sm_s = sm_l + kScanWarps * kHeadsPad;                // [4][2]
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, o);
+    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    smax0 = fmaxf(smax0, __shfl_xor_sync(0xFFFFFFFFu, smax0, o));
+    smax1 = fmaxf(smax1, __shfl_xor_sync(0xFFFFFFFFu, smax1, o));
+  }
+  for (int i = threadIdx.x; i < kHeadsPad * JF_HEAD_DIM; i += blockDim.x) sm_o[i] = 0.f;
+  if (g == 0) {
+    sm_m[warp * 8 + 2 * tig] = m_ref0; sm_m[warp * 8 + 2 * tig + 1] = m_ref1;
+    sm_l[warp * 8 + 2 * tig] = l0;     sm_l[warp * 8 + 2 * tig + 1] = l1;
+  }
+  if (lane == 0) { sm_s[warp * 2] = smax0; sm_s[warp * 2 + 1] = smax1; }
+  __syncthreads();
+  float M0 = kMinusBig, M1 = kMinusBig;
+#pragma unroll
+  for (int w = 0; w < kScanWarps; ++w) {
+    M0 = fmaxf(M0, sm_m[w * 8 + 2 * tig]);
+    M1 = fmaxf(M1, sm_m[w * 8 + 2 * tig + 1]);
+  }
+  {
+    const float f0 = ex2((m_ref0 - M0) * kLog2e), f1 = ex2((m_ref1 - M1) * kLog2e);
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      const int qh = mt >> 2, ml = mt & 3;
+      const int fa = 2 * ml, fb = 2 * ml + 1;
+      const int da = 64 * qh + 8 * g + v2_dlocal(fa), db = 64 * qh + 8 * g + v2_dlocal(fb);
+      const float ua = 1.0f / static_cast<float>(1 << v2_pos(fa)), ub = 1.0f / static_cast<float>(1 << v2_pos(fb));
+      atomicAdd(&sm_o[(2 * tig) * JF_HEAD_DIM + da], oacc[mt][0] * f0 * ua);
+      atomicAdd(&sm_o[(2 * tig + 1) * JF_HEAD_DIM + da], oacc[mt][1] * f1 * ua);
+      atomicAdd(&sm_o[(2 * tig) * JF_HEAD_DIM + db], oacc[mt][2] * f0 * ub);
+      atomicAdd(&sm_o[(2 * tig + 1) * JF_HEAD_DIM + db], oacc[mt][3] * f1 * ub);
+    }
+  }
+  __syncthreads();
+  const int64_t pidx = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits + split;
+  float* po = p.part_o + pidx * (kHeadsPad * JF_HEAD_DIM);
+  for (int i = threadIdx.x; i < kHeadsPad * JF_HEAD_DIM; i += blockDim.x) po[i] = sm_o[i];
+  if (threadIdx.x < kHeadsPad) {
+    const int h = threadIdx.x;
+    float M = kMinusBig;
+    for (int w = 0; w < kScanWarps; ++w) M = fmaxf(M, sm_m[w * 8 + h]);
+    float L = 0.f;
+    for (int w = 0; w < kScanWarps; ++w) L += sm_l[w * 8 + h] * ex2((sm_m[w * 8 + h] - M) * kLog2e);
+    p.part_m[pidx * kHeadsPad + h] = M;
+    p.part_l[pidx * kHeadsPad + h] = L;
+  }
+  if (threadIdx.x < 2) {
+    float s = 0.f;
+    for (int w = 0; w < kScanWarps; ++w) s = fmaxf(s, sm_s[w * 2 + threadIdx.x]);
+    p.part_smax[pidx * 2 + threadIdx.x] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+jf_status_t validate_decode_args(const jf_decode_args* a) {
+  if (!a) return JF_ERR_ARG;
+  if (a->mode != JF_MODE_K3V2 && a->mode != JF_MODE_K4V4) return JF_ERR_UNSUPPORTED;
+  if (a->q_dtype != JF_DTYPE_BF16 && a->q_dtype != JF_DTYPE_FP16) return JF_ERR_UNSUPPORTED;
+  if (a->B <= 0 || a->H_q <= 0 || a->H_kv <= 0 || a->max_S <= 0) return JF_ERR_ARG;
+  if (a->H_q % a->H_kv != 0) return JF_ERR_ARG;
+  const int G = a->H_q / a->H_kv;
+  if (G > JF_MAX_GROUP) return JF_ERR_UNSUPPORTED;
+  if (a->block_size != JF_BLOCK_SIZE) return JF_ERR_UNSUPPORTED;
+  if (a->max_S > 262144) return JF_ERR_UNSUPPORTED;
+  if (a->top_k < 1 || a->top_k > JF_MAX_TOP_K) return JF_ERR_UNSUPPORTED;
+  if (a->max_blocks < (a->max_S + 15) / 16) return JF_ERR_ARG;
+  if (a->num_slots <= 0 || (a->num_slots % 16) != 0) return JF_ERR_ARG;
+  if (!a->q || !a->k_data || !a->k_scales || !a->v_data || !a->v_scales || !a->block_table || !a->seq_lens)
+    return JF_ERR_ARG;
+  if (!aligned(a->k_data, 16) || !aligned(a->v_data, 16) || !aligned(a->k_scales, 16) || !aligned(a->v_scales, 16))
+    return JF_ERR_ARG;
+  if (!a->workspace || !aligned(a->workspace, 256)) return JF_ERR_WORKSPACE;
+  if (a->workspace_bytes < jf_decode_workspace_bytes(a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k))
+    return JF_ERR_WORKSPACE;
+  return JF_OK;
+}
+
+__global__ void fill_neg_inf_tail_kernel(float* scores, const int32_t* seq_lens, int H_q, int max_S) {
+  const int bh = blockIdx.x, b = bh / H_q;
+  const int len = min(seq_lens[b], max_S);
+  float* row = scores + static_cast<int64_t>(bh) * max_S;
+  for (int i = len + threadIdx.x; i < max_S; i += blockDim.x) row[i] = -INFINITY;
+}
+
+}  // namespace jf
+
+extern "C" uint64_t jf_decode_workspace_bytes(int32_t mode, int32_t B, int32_t H_q, int32_t H_kv,
+                                              int32_t max_S, int32_t top_k) {
+  (void)mode; (void)top_k;
+  if (B <= 0 || H_q <= 0 || H_kv <= 0 || max_S <= 0) return 0;
+  return jf::carve_workspace(nullptr, B, H_q, H_kv, max_S, true).bytes;
+}
+
+extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t stream_) {
+  using namespace jf;
+  jf_status_t st = validate_decode_args(a);
+  if (st != JF_OK) return st;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, true);
+  JF_CUDA_TRY(cudaMemsetAsync(ws.status, 0, sizeof(int32_t), stream));
+  ScanParams sp{};
+  sp.q = a->q;
+  sp.k_data = a->k_data;  sp.k_scales = static_cast<const uint16_t*>(a->k_scales);
+  sp.v_data = a->v_data;  sp.v_scales = static_cast<const uint16_t*>(a->v_scales);
+  sp.block_table = a->block_table;  sp.seq_lens = a->seq_lens;
+  sp.scores = a->scores ? a->scores : ws.scores;
+  sp.part_o = ws.part_o; sp.part_m = ws.part_m; sp.part_l = ws.part_l; sp.part_smax = ws.part_smax;
+  sp.status = ws.status;
+  sp.num_slots = a->num_slots;
+  sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = a->H_kv; sp.G = a->H_q / a->H_kv;
+  sp.max_S = a->max_S; sp.max_blocks = a->max_blocks;
+  sp.splits = scan_splits(a->B, a->H_kv, a->max_S);
+  const int pages = (a->max_S + 15) / 16;
+  sp.pages_per_split = (pages + sp.splits - 1) / sp.splits;
+  sp.attn_scale = a->attn_scale;
+  dim3 grid(sp.splits, a->H_kv, a->B);
+  if (a->mode == JF_MODE_K3V2) {
+    using T = Tile<JF_MODE_K3V2>;
+    const size_t smem = kScanWarps * kStages * (T::kBytes + 8 + 4);
+    static_assert(kScanWarps * kStages * T::kBytes >= (kHeadsPad * JF_HEAD_DIM + 3 * kScanWarps * kHeadsPad) * 4, "merge buffer");
+    if (a->q_dtype == JF_DTYPE_BF16) {
+      JF_CUDA_TRY(cudaFuncSetAttribute(scan_k3v2_kernel<JF_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      scan_k3v2_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
+    } else {
+      JF_CUDA_TRY(cudaFuncSetAttribute(scan_k3v2_kernel<JF_DTYPE_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      scan_k3v2_kernel<JF_DTYPE_FP16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
+    }
+    JF_CUDA_TRY(cudaGetLastError());
+  } else {
+    return JF_ERR_UNSUPPORTED;
+  }
+  if (a->scores) {
+    fill_neg_inf_tail_kernel<<<a->B * a->H_q, 256, 0, stream>>>(a->scores, a->seq_lens, a->H_q, a->max_S);
+    JF_CUDA_TRY(cudaGetLastError());
+  }
+  return JF_OK;
+}

@@ -1,0 +1,368 @@
+// Exact, deterministic top-k per query head over the scan's approximate scores.
+//
+// The reference selects with a 4-level radix select on fp32 scores that came out of a
+// tensor-core accumulation (jetfire_vllm/csrc/int3_qk_scores.cu:426-554): which position
+// wins near the k-th score depends on an unspecified summation order, and the output order
+// and the choice among ties depend on atomics.  Here selection is two-tier:
+//   1. a 2048-bin histogram of the approximate scores (bin width 1/64 below an upper bound
+//      of the row maximum) finds the bin T that holds the k-th largest approximate score;
+//   2. every position whose approximate score can still beat it -- bins <= T + ceil(2*delta*64)
+//      + 1, with delta a bound on |approximate - canonical| -- is re-scored in the canonical
+//      arithmetic (reference dequantisation rounding, fp32 fma chain over ascending d), and
+//      the k best by (canonical score desc, position asc) are emitted in that order.
+// The result is reproducible by a CPU and independent of tensor-core internals.  If the
+// band does not fit the sort buffer (massive ties, degenerate scales) a slow exact path
+// radix-selects on the 64-bit key (canonical score, ~position) computed on the fly.
+// Slot translation and -1 padding follow csrc/int3_qk_scores.cu:399-417.
+#include "decode_common.cuh"
+
+namespace jf {
+
+namespace {
+
+constexpr int kTopkThreads = 1024;
+constexpr int kBins = 2048;
+constexpr float kBinsPerUnit = 64.0f;
+
+struct TopkParams {
+  const float* scores;
+  const float* part_m;
+  const float* part_smax;
+  const void* q;
+  const uint8_t* k_data;
+  const uint16_t* k_scales;
+  const int64_t* block_table;
+  const int32_t* seq_lens;
+  int64_t* topk_idx;
+  int64_t* topk_slots;
+  int64_t num_slots;
+  int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
+  float attn_scale;
+};
+
+struct RowCtx {
+  const float* q;         // smem, 128 floats (exact values of the query row)
+  const int8_t* qi;       // smem, K4: quantised query
+  const float* qs;        // smem, K4: per-32-channel query scales
+  const uint8_t* k_rows;  // k_data of this KV head
+  const uint16_t* k_sc;   // k_scales of this KV head
+  const int64_t* bt;      // block-table row
+  int64_t num_slots;
+  float attn;
+};
+
+__device__ __forceinline__ int64_t slot_of(const RowCtx& c, int pos) {
+  const int64_t blk = c.bt[pos >> 4];
+  if (blk < 0 || blk >= (c.num_slots >> 4)) return -1;
+  return blk * 16 + (pos & 15);
+}
+
+// Canonical K3 score: k_hat = bf16(float(code - 4) * float(scale_bf16)) as in
+// csrc/int3_qk_scores.cu:90-100, then acc = fmaf(q[d], k_hat[d], acc) for d ascending.
+__device__ float canon_score_k3(const RowCtx& c, int64_t slot) {
+  const uint4* row = reinterpret_cast<const uint4*>(c.k_rows + slot * 48);
+  const uint4 p0 = __ldg(row), p1 = __ldg(row + 1), p2 = __ldg(row + 2);
+  const uint32_t sw = __ldg(reinterpret_cast<const uint32_t*>(c.k_sc + slot * 2));
+  const float sc0 = __uint_as_float(sw << 16), sc1 = __uint_as_float(sw & 0xFFFF0000u);
+  const uint32_t a0[4] = {p0.x, p0.y, p0.z, p0.w}, a1[4] = {p1.x, p1.y, p1.z, p1.w}, a2[4] = {p2.x, p2.y, p2.z, p2.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int w = i >> 2, sh = 8 * (i & 3);
+    const uint32_t w24 = (((a0[w] >> sh) & 255u) << 16) | (((a1[w] >> sh) & 255u) << 8) | ((a2[w] >> sh) & 255u);
+    const float sc = (i < 8) ? sc0 : sc1;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int code = static_cast<int>((w24 >> (21 - 3 * r)) & 7u) - 4;
+      const float kh = __bfloat162float(__float2bfloat16_rn(__fmul_rn(static_cast<float>(code), sc)));
+      acc = __fmaf_rn(c.q[8 * i + r], kh, acc);
+    }
+  }
+  return __fmul_rn(acc, c.attn);
+}
+
+// Canonical K4/G128 score (csrc/int8tc_qk_scores.cu:445-487): exact int32 dot per 32-channel
+// block against the INT8 query, s = fma(float(acc_c), qs_c, s) for c = 0..3, * k_scale, * attn.
+__device__ float canon_score_k4(const RowCtx& c, int64_t slot) {
+  const uint4* row = reinterpret_cast<const uint4*>(c.k_rows + slot * 64);
+  const float ks = bf16_bits_to_f32(__ldg(c.k_sc + slot));
+  float s = 0.f;
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    const uint4 v = __ldg(row + blk);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    int acc = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t byte = (w[j >> 2] >> (8 * (j & 3))) & 255u;
+      const int d = 32 * blk + 2 * j;
+      acc += (static_cast<int>(byte >> 4) - 8) * c.qi[d] + (static_cast<int>(byte & 15u) - 8) * c.qi[d + 1];
+    }
+    s = __fmaf_rn(static_cast<float>(acc), c.qs[blk], s);
+  }
+  return __fmul_rn(__fmul_rn(s, ks), c.attn);
+}
+
+template <int MODE>
+__device__ __forceinline__ uint64_t canon_key(const RowCtx& c, int pos) {
+  const int64_t slot = slot_of(c, pos);
+  float s = -INFINITY;
+  if (slot >= 0) s = (MODE == JF_MODE_K3V2) ? canon_score_k3(c, slot) : canon_score_k4(c, slot);
+  return (static_cast<uint64_t>(float_order_key(s)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(pos));
+}
+
+__device__ __forceinline__ int score_bin(float top, float s) {
+  const float x = (top - s) * kBinsPerUnit;
+  return (x >= static_cast<float>(kBins - 1)) ? (kBins - 1) : max(0, static_cast<int>(x));
+}
+
+template <int MODE, int DT>
+__global__ void __launch_bounds__(kTopkThreads)
+topk_select_kernel(const TopkParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);                   // [sort_n]
+  int* hist = reinterpret_cast<int*>(keys + p.sort_n);                      // [kBins]
+  float* q_sm = reinterpret_cast<float*>(hist + kBins);                     // [128]
+  float* qs_sm = q_sm + JF_HEAD_DIM;                                        // [4]
+  int8_t* qi_sm = reinterpret_cast<int8_t*>(qs_sm + 4);                     // [128]
+  __shared__ int sh_ncand, sh_last, sh_fallback;
+  __shared__ float sh_red[4];
+  __shared__ unsigned long long sh_prefix;
+  __shared__ int sh_remaining;
+
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int hkv = h / p.G, hi = h - hkv * p.G;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n = min(p.seq_lens[b], p.max_S);
+  const int K = p.top_k;
+  const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
+  int64_t* out_idx = p.topk_idx + bh * K;
+  int64_t* out_slot = p.topk_slots + bh * K;
+  if (n <= 0) {
+    for (int r = tid; r < K; r += kTopkThreads) { out_idx[r] = -1; out_slot[r] = -1; }
+    return;
+  }
+
+  // ---- query row (exact values), per-group L1 norms, INT8 model for K4 ----
+  if (tid < JF_HEAD_DIM) {
+    q_sm[tid] = Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid]);
+  }
+  __syncthreads();
+  if (warp < 4) {  // warp w handles channels 32w..32w+31
+    const float v = q_sm[32 * warp + lane];
+    float a = fabsf(v), s1 = fabsf(v) + 0.001953125f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+      s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, o);
+    }
+    if (MODE == JF_MODE_K4V4) {
+      const float qs = fmaxf(__fdiv_rn(a, 127.0f), 1e-12f);
+      const float inv = __fdiv_rn(1.0f, qs);
+      qi_sm[32 * warp + lane] = static_cast<int8_t>(max(-128, min(127, __float2int_rn(__fmul_rn(v, inv)))));
+      if (lane == 0) qs_sm[warp] = qs;
+    }
+    if (lane == 0) sh_red[warp] = s1;
+  }
+  if (tid == 0) { sh_ncand = 0; sh_fallback = 0; }
+  __syncthreads();
+
+  RowCtx ctx;
+  ctx.q = q_sm; ctx.qi = qi_sm; ctx.qs = qs_sm;
+  const ModeInfo mi = mode_info(MODE);
+  ctx.k_rows = p.k_data + static_cast<int64_t>(hkv) * p.num_slots * mi.k_row;
+  ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+  ctx.bt = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  ctx.num_slots = p.num_slots;
+  ctx.attn = p.attn_scale;
+
+  const float* srow = p.scores + bh * p.max_S;
+  int ncand = 0;
+
+  if (n <= p.sort_n) {
+    // short row: every position is a candidate
+    for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = (i < n) ? canon_key<MODE>(ctx, i) : 0ull;
+    ncand = n;
+  } else {
+    // ---- tier 1: histogram of approximate scores ----
+    float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
+    const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
+    for (int s = 0; s < p.splits; ++s) {
+      top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
+      sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
+      sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
+    }
+    top += 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
+    float delta = 0.f;
+    if (MODE == JF_MODE_K3V2) {
+      // |approx - canonical| <= attn * sum_g scale_g * sum_{d in g} |q_d| * 3 * 2^-9, plus slack
+      const float q1a = sh_red[0] + sh_red[1], q1b = sh_red[2] + sh_red[3];
+      delta = fabsf(p.attn_scale) * (sm0 * q1a + sm1 * q1b) * (3.0f / 512.0f) * 1.02f + 1e-6f;
+    }
+    for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += kTopkThreads) atomicAdd(&hist[score_bin(top, srow[i])], 1);
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins 64l..64l+63
+      int local = 0;
+      for (int j = 0; j < 64; ++j) local += hist[64 * lane + j];
+      int incl = local;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const int excl = incl - local;
+      int tbin = -1;
+      if (excl < K && incl >= K) {
+        int cum = excl;
+        for (int j = 0; j < 64; ++j) {
+          cum += hist[64 * lane + j];
+          if (cum >= K) { tbin = 64 * lane + j; break; }
+        }
+      }
+      const unsigned m = __ballot_sync(0xFFFFFFFFu, tbin >= 0);
+      const int src = __ffs(m) - 1;  // exactly one lane holds it (n > K here)
+      tbin = __shfl_sync(0xFFFFFFFFu, tbin, src < 0 ? 0 : src);
+      float nbf = ceilf(2.0f * delta * kBinsPerUnit) + 1.0f;
+      if (!(nbf < 4096.0f)) nbf = 4096.0f;
+      const int nb = (MODE == JF_MODE_K3V2) ? static_cast<int>(nbf) : 0;
+      const int last = min(tbin + nb, kBins - 1);
+      // candidates = everything in bins <= last
+      int cnt_local = 0;
+      for (int j = 0; j < 64; ++j) if (64 * lane + j <= last) cnt_local += hist[64 * lane + j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cnt_local += __shfl_xor_sync(0xFFFFFFFFu, cnt_local, o);
+      if (lane == 0) {
+        sh_last = last;
+        sh_fallback = (last >= kBins - 1 || cnt_local > p.sort_n || src < 0) ? 1 : 0;
+      }
+    }
+    __syncthreads();
+    if (!sh_fallback) {
+      // ---- tier 2: collect the band, re-score canonically ----
+      const int last = sh_last;
+      for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
+      __syncthreads();
+      for (int i = tid; i < n; i += kTopkThreads) {
+        if (score_bin(top, srow[i]) <= last) {
+          const int pos = atomicAdd(&sh_ncand, 1);
+          if (pos < p.sort_n) keys[pos] = static_cast<uint64_t>(i);  // position, re-scored below
+        }
+      }
+      __syncthreads();
+      ncand = min(sh_ncand, p.sort_n);
+      for (int j = tid; j < ncand; j += kTopkThreads) keys[j] = canon_key<MODE>(ctx, static_cast<int>(keys[j]));
+    } else {
+      // ---- slow exact path: 8-level radix select on the 64-bit canonical key ----
+      if (tid == 0) { sh_prefix = 0ull; sh_remaining = K; }
+      __syncthreads();
+      for (int level = 7; level >= 0; --level) {
+        for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
+        __syncthreads();
+        const unsigned long long prefix = sh_prefix;
+        for (int i = tid; i < n; i += kTopkThreads) {
+          const uint64_t key = canon_key<MODE>(ctx, i);
+          const bool match = (level == 7) || ((key >> (8 * (level + 1))) == prefix);
+          if (match) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+          int cum = 0, rem = sh_remaining, cb = 0;
+          for (int bin = 255; bin >= 0; --bin) {
+            if (cum + hist[bin] >= rem) { cb = bin; break; }
+            cum += hist[bin];
+          }
+          sh_remaining = rem - cum;
+          sh_prefix = (prefix << 8) | static_cast<unsigned long long>(cb);
+        }
+        __syncthreads();
+      }
+      const unsigned long long tkey = sh_prefix;  // key of the k-th best; keys are unique
+      for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
+      __syncthreads();
+      for (int i = tid; i < n; i += kTopkThreads) {
+        const uint64_t key = canon_key<MODE>(ctx, i);
+        if (key >= tkey) {
+          const int pos = atomicAdd(&sh_ncand, 1);
+          if (pos < p.sort_n) keys[pos] = key;
+        }
+      }
+      __syncthreads();
+      ncand = min(sh_ncand, p.sort_n);
+    }
+  }
+  __syncthreads();
+
+  // ---- bitonic sort, descending, sort_n a power of two ----
+  for (int size = 2; size <= p.sort_n; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < (p.sort_n >> 1); i += kTopkThreads) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi2 = lo + stride;
+        const bool desc = ((lo & size) == 0);
+        const uint64_t a = keys[lo], c = keys[hi2];
+        if ((a < c) == desc) { keys[lo] = c; keys[hi2] = a; }
+      }
+      __syncthreads();
+    }
+  }
+
+  const int m = min(ncand, K);
+  for (int r = tid; r < K; r += kTopkThreads) {
+    int64_t idx = -1, slot = -1;
+    if (r < m) {
+      idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
+      slot = slot_of(ctx, static_cast<int>(idx));
+    }
+    out_idx[r] = idx;
+    out_slot[r] = slot;
+  }
+}
+
+int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
+
+}  // namespace
+
+}  // namespace jf
+
+extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t stream_) {
+  using namespace jf;
+  jf_status_t st = validate_decode_args(a);
+  if (st != JF_OK) return st;
+  if (!a->topk_idx || !a->topk_slots) return JF_ERR_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, true);
+  TopkParams tp{};
+  tp.scores = a->scores ? a->scores : ws.scores;
+  tp.part_m = ws.part_m; tp.part_smax = ws.part_smax;
+  tp.q = a->q; tp.k_data = a->k_data; tp.k_scales = static_cast<const uint16_t*>(a->k_scales);
+  tp.block_table = a->block_table; tp.seq_lens = a->seq_lens;
+  tp.topk_idx = a->topk_idx; tp.topk_slots = a->topk_slots;
+  tp.num_slots = a->num_slots;
+  tp.B = a->B; tp.H_q = a->H_q; tp.H_kv = a->H_kv; tp.G = a->H_q / a->H_kv;
+  tp.max_S = a->max_S; tp.max_blocks = a->max_blocks;
+  tp.splits = scan_splits(a->B, a->H_kv, a->max_S);
+  tp.top_k = a->top_k;
+  tp.sort_n = pow2_ceil(2 * a->top_k);
+  if (tp.sort_n < 512) tp.sort_n = 512;
+  tp.q_dtype = a->q_dtype;
+  tp.attn_scale = a->attn_scale;
+  const size_t smem = static_cast<size_t>(tp.sort_n) * 8 + kBins * 4 + JF_HEAD_DIM * 4 + 16 + JF_HEAD_DIM;
+  dim3 grid(a->H_q, a->B);
+#define JF_TOPK(MODE, DT)                                                                              \
+  do {                                                                                                 \
+    JF_CUDA_TRY(cudaFuncSetAttribute(topk_select_kernel<MODE, DT>,                                     \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));         \
+    topk_select_kernel<MODE, DT><<<grid, kTopkThreads, smem, stream>>>(tp);                            \
+  } while (0)
+  if (a->mode == JF_MODE_K3V2) {
+    if (a->q_dtype == JF_DTYPE_BF16) JF_TOPK(JF_MODE_K3V2, JF_DTYPE_BF16); else JF_TOPK(JF_MODE_K3V2, JF_DTYPE_FP16);
+  } else {
+    if (a->q_dtype == JF_DTYPE_BF16) JF_TOPK(JF_MODE_K4V4, JF_DTYPE_BF16); else JF_TOPK(JF_MODE_K4V4, JF_DTYPE_FP16);
+  }
+#undef JF_TOPK
+  JF_CUDA_TRY(cudaGetLastError());
+  return JF_OK;
+}

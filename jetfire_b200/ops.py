@@ -1,0 +1,361 @@
+"""Operator surface of the JetFire decode hot path, on top of the C ABI.
+
+Names, argument order and meaning follow the reference's torch-extension ops and Triton
+writers so that its adapter can call these unchanged; torch is used only for device
+memory and streams.  Each op validates like the reference's ``TORCH_CHECK``s (raising
+``RuntimeError``) and runs on ``torch.cuda.current_stream()``.
+
+Reference interfaces mirrored here (paths inside the JetFire project):
+  * ``fused_quant_write_int{2,3,4}_sym`` -- jetfire_vllm/kernels/fused_quant_write.py:242, :337, :746
+  * ``fused_quant_write_int4_sym_kv``    -- jetfire_vllm/kernels/fused_quant_write.py:552
+  * ``fused_attn_topk``                  -- the single-call form of
+    jetfire_vllm/kernels/int2_fused_attn_topk.py:5-10 generalised to K3V2 / K4V4
+  * ``blend_unnorm_into``                -- jetfire_vllm/csrc/blend.cu:229-290
+  * ``cpu_topk_attn`` and friends        -- jetfire_vllm/csrc/cpu_topk_attn.cpp:854-956, :2509-2663
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import NamedTuple
+
+import torch
+
+from . import _lib
+from ._lib import DecodeArgs, JetFireError, check, lib
+
+MODE_IDS = {"k3v2": _lib.JF_MODE_K3V2, "k4v4": _lib.JF_MODE_K4V4,
+            "SymInt3K_SymInt2V": _lib.JF_MODE_K3V2, "SymInt4K_SymInt4V": _lib.JF_MODE_K4V4}
+MODE_BITS = {_lib.JF_MODE_K3V2: (3, 2, 64), _lib.JF_MODE_K4V4: (4, 4, 128)}
+
+
+def _dtype_id(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.JF_DTYPE_BF16
+    if t.dtype == torch.float16:
+        return _lib.JF_DTYPE_FP16
+    raise RuntimeError(f"expected bfloat16 or float16, got {t.dtype}")
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ---------------------------------------------------------------------------------------
+# quantise-on-append
+# ---------------------------------------------------------------------------------------
+
+def _packed_dim(nbits: int) -> int:
+    return 128 * nbits // 8
+
+
+def _check_side(x_tok, out_data, out_scale, nbits, group_size, name):
+    _require(x_tok.is_cuda and out_data.is_cuda and out_scale.is_cuda, f"{name}: tensors must be CUDA")
+    _require(x_tok.dim() == 3 and x_tok.shape[2] == 128, f"{name}: x_tok must be (T, H_kv, 128)")
+    _require(x_tok.stride(2) == 1, f"{name}: x_tok innermost dim must be contiguous")
+    _require(out_data.dtype == torch.uint8 and out_data.is_contiguous(), f"{name}: out_data must be contiguous uint8")
+    _require(out_scale.dtype == torch.bfloat16 and out_scale.is_contiguous(), f"{name}: out_scale must be contiguous bf16")
+    _require(group_size in (64, 128), f"{name}: group_size must be 64 or 128")
+    h = x_tok.shape[1]
+    _require(out_data.dim() == 3 and out_data.shape[0] == h and out_data.shape[2] == _packed_dim(nbits),
+             f"{name}: out_data must be (H_kv, num_slots, {_packed_dim(nbits)})")
+    _require(out_scale.shape[0] == h and out_scale.shape[1] == out_data.shape[1]
+             and out_scale.numel() == h * out_data.shape[1] * (128 // group_size),
+             f"{name}: out_scale must be (H_kv, num_slots, {128 // group_size})")
+
+
+def _quant_write(x_tok, slot_idx, out_data, out_scale, group_size, nbits, name):
+    _check_side(x_tok, out_data, out_scale, nbits, group_size, name)
+    _require(slot_idx.is_cuda and slot_idx.dtype == torch.int64 and slot_idx.dim() == 1
+             and slot_idx.shape[0] == x_tok.shape[0], f"{name}: slot_idx must be (T,) int64 CUDA")
+    slot_idx = slot_idx.contiguous()
+    st = lib.jf_pack_append(x_tok.data_ptr(), _dtype_id(x_tok), x_tok.shape[0], x_tok.shape[1],
+                            x_tok.stride(0), x_tok.stride(1), slot_idx.data_ptr(),
+                            out_data.data_ptr(), out_scale.data_ptr(), out_data.shape[1],
+                            nbits, group_size, _stream())
+    check(name, st)
+
+
+def fused_quant_write_int2_sym(x_tok, slot_idx, out_data, out_scale, group_size=128):
+    """In place: INT2 rows of ``x_tok`` into ``out_data[h, slot]`` / ``out_scale[h, slot]``."""
+    _quant_write(x_tok, slot_idx, out_data, out_scale, group_size, 2, "fused_quant_write_int2_sym")
+
+
+def fused_quant_write_int3_sym(x_tok, slot_idx, out_data, out_scale, group_size=128):
+    _quant_write(x_tok, slot_idx, out_data, out_scale, group_size, 3, "fused_quant_write_int3_sym")
+
+
+def fused_quant_write_int4_sym(x_tok, slot_idx, out_data, out_scale, group_size=128):
+    _quant_write(x_tok, slot_idx, out_data, out_scale, group_size, 4, "fused_quant_write_int4_sym")
+
+
+def fused_quant_write_kv(key_tok, value_tok, slot_idx, k_data, k_scales, v_data, v_scales,
+                         group_size, k_bits, v_bits):
+    """K and V of the same tokens in one launch, any bit pair."""
+    name = "fused_quant_write_kv"
+    _check_side(key_tok, k_data, k_scales, k_bits, group_size, name)
+    _check_side(value_tok, v_data, v_scales, v_bits, group_size, name)
+    _require(key_tok.shape == value_tok.shape and key_tok.dtype == value_tok.dtype,
+             f"{name}: key/value shape or dtype mismatch")
+    _require(k_data.shape[1] == v_data.shape[1], f"{name}: K and V caches differ in num_slots")
+    _require(slot_idx.is_cuda and slot_idx.dtype == torch.int64 and slot_idx.dim() == 1
+             and slot_idx.shape[0] == key_tok.shape[0], f"{name}: slot_idx must be (T,) int64 CUDA")
+    slot_idx = slot_idx.contiguous()
+    st = lib.jf_pack_append_kv(key_tok.data_ptr(), value_tok.data_ptr(), _dtype_id(key_tok),
+                               key_tok.shape[0], key_tok.shape[1],
+                               key_tok.stride(0), key_tok.stride(1), value_tok.stride(0), value_tok.stride(1),
+                               slot_idx.data_ptr(), k_data.data_ptr(), k_scales.data_ptr(),
+                               v_data.data_ptr(), v_scales.data_ptr(), k_data.shape[1],
+                               k_bits, v_bits, group_size, _stream())
+    check(name, st)
+
+
+def fused_quant_write_int4_sym_kv(key_tok, value_tok, slot_idx, k_data, k_scales, v_data, v_scales,
+                                  group_size=128):
+    fused_quant_write_kv(key_tok, value_tok, slot_idx, k_data, k_scales, v_data, v_scales, group_size, 4, 4)
+
+
+# ---------------------------------------------------------------------------------------
+# fused decode attention
+# ---------------------------------------------------------------------------------------
+
+class FusedAttnOut(NamedTuple):
+    o_hat: torch.Tensor          # (B, H_q, 128) f32
+    topk_slots: torch.Tensor     # (B, H_q, k) i64
+    o_old_unnorm: torch.Tensor   # (B, H_q, 128) f32
+    W: torch.Tensor              # (B, H_q) f32
+    topk_idx: torch.Tensor       # (B, H_q, k) i64
+    softmax_m: torch.Tensor      # (B, H_q) f32
+    softmax_inv_z: torch.Tensor  # (B, H_q) f32
+    scores: torch.Tensor | None  # (B, H_q, max_S) f32 when requested
+
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def decode_workspace_bytes(mode, B, H_q, H_kv, max_S, top_k) -> int:
+    return int(lib.jf_decode_workspace_bytes(MODE_IDS[mode] if isinstance(mode, str) else mode,
+                                             B, H_q, H_kv, max_S, top_k))
+
+
+def get_workspace(nbytes: int, device) -> torch.Tensor:
+    """Cached scratch (grows monotonically per device); one per current stream is the
+    caller's business when streams overlap."""
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream().cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+class DecodeCall:
+    """Argument block for the decode entry points, built once and reusable (pointers are
+    captured; tensors are kept alive here)."""
+
+    def __init__(self, mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
+                 max_S, H_q, H_kv, block_size, top_k, attn_scale, *, workspace=None,
+                 want_scores=False, out=None):
+        name = "fused_attn_topk"
+        mode_id = MODE_IDS[mode] if isinstance(mode, str) else int(mode)
+        k_bits, v_bits, gs = MODE_BITS[mode_id]
+        for t, nm in ((q, "q"), (k_data, "k_data"), (k_scales, "k_scales"), (v_data, "v_data"),
+                      (v_scales, "v_scales"), (block_table, "block_table"), (seq_lens, "seq_lens")):
+            _require(t.is_cuda, f"{name}: {nm} must be CUDA")
+        _require(q.dim() == 3 and q.shape[1] == H_q and q.shape[2] == 128, f"{name}: q must be (B, H_q, 128)")
+        q = q.contiguous()
+        B = q.shape[0]
+        _require(k_data.dtype == torch.uint8 and v_data.dtype == torch.uint8, f"{name}: packed data must be uint8")
+        _require(k_scales.dtype == torch.bfloat16 and v_scales.dtype == torch.bfloat16, f"{name}: scales must be bf16")
+        _require(k_data.is_contiguous() and v_data.is_contiguous() and k_scales.is_contiguous()
+                 and v_scales.is_contiguous(), f"{name}: cache tensors must be contiguous")
+        _require(k_data.shape[0] == H_kv and k_data.shape[2] == _packed_dim(k_bits),
+                 f"{name}: k_data must be (H_kv, num_slots, {_packed_dim(k_bits)})")
+        _require(v_data.shape[0] == H_kv and v_data.shape[2] == _packed_dim(v_bits),
+                 f"{name}: v_data must be (H_kv, num_slots, {_packed_dim(v_bits)})")
+        num_slots = k_data.shape[1]
+        ng = 128 // gs
+        _require(k_scales.numel() == H_kv * num_slots * ng and v_scales.numel() == H_kv * num_slots * ng,
+                 f"{name}: scales must hold {ng} group(s) per slot")
+        _require(block_table.dtype == torch.int64 and block_table.dim() == 2 and block_table.shape[0] == B,
+                 f"{name}: block_table must be (B, max_blocks) int64")
+        _require(seq_lens.dtype == torch.int32 and seq_lens.shape == (B,), f"{name}: seq_lens must be (B,) int32")
+        block_table = block_table.contiguous()
+        seq_lens = seq_lens.contiguous()
+        dev = q.device
+        nbytes = decode_workspace_bytes(mode_id, B, H_q, H_kv, max_S, top_k)
+        _require(nbytes > 0, f"{name}: bad shape")
+        if workspace is None:
+            workspace = get_workspace(nbytes, dev)
+        ws_ptr = (workspace.data_ptr() + 255) // 256 * 256
+        ws_bytes = workspace.numel() - (ws_ptr - workspace.data_ptr())
+        f32 = dict(dtype=torch.float32, device=dev)
+        if out is None:
+            out = dict(
+                o_hat=torch.empty(B, H_q, 128, **f32), o_old_unnorm=torch.empty(B, H_q, 128, **f32),
+                W=torch.empty(B, H_q, **f32), softmax_m=torch.empty(B, H_q, **f32),
+                softmax_inv_z=torch.empty(B, H_q, **f32),
+                topk_idx=torch.empty(B, H_q, top_k, dtype=torch.int64, device=dev),
+                topk_slots=torch.empty(B, H_q, top_k, dtype=torch.int64, device=dev),
+            )
+        scores = torch.empty(B, H_q, max_S, **f32) if want_scores else None
+        self.out = out
+        self.scores = scores
+        self._keep = (q, k_data, k_scales, v_data, v_scales, block_table, seq_lens, workspace)
+        a = DecodeArgs()
+        a.mode, a.q_dtype = mode_id, _dtype_id(q)
+        a.B, a.H_q, a.H_kv = B, H_q, H_kv
+        a.max_S, a.block_size, a.top_k = int(max_S), int(block_size), int(top_k)
+        a.max_blocks = block_table.shape[1]
+        a.attn_scale = float(attn_scale)
+        a.num_slots = num_slots
+        a.q, a.k_data, a.k_scales = q.data_ptr(), k_data.data_ptr(), k_scales.data_ptr()
+        a.v_data, a.v_scales = v_data.data_ptr(), v_scales.data_ptr()
+        a.block_table, a.seq_lens = block_table.data_ptr(), seq_lens.data_ptr()
+        a.scores = scores.data_ptr() if scores is not None else None
+        a.topk_idx, a.topk_slots = out["topk_idx"].data_ptr(), out["topk_slots"].data_ptr()
+        a.o_hat, a.o_old_unnorm, a.W = out["o_hat"].data_ptr(), out["o_old_unnorm"].data_ptr(), out["W"].data_ptr()
+        a.softmax_m, a.softmax_inv_z = out["softmax_m"].data_ptr(), out["softmax_inv_z"].data_ptr()
+        a.workspace, a.workspace_bytes = ws_ptr, ws_bytes
+        self.args = a
+        self._ref = C.byref(a)
+
+    def scan(self):
+        check("jf_decode_scan", lib.jf_decode_scan(self._ref, _stream()))
+
+    def select(self):
+        check("jf_topk_select", lib.jf_topk_select(self._ref, _stream()))
+
+    def finish(self):
+        check("jf_decode_finish", lib.jf_decode_finish(self._ref, _stream()))
+
+    def fused(self):
+        check("jf_decode_fused", lib.jf_decode_fused(self._ref, _stream()))
+
+    def status(self):
+        """Synchronises the stream and raises if a kernel recorded a bounded-wait timeout."""
+        check("jf_decode_status", lib.jf_decode_status(self._ref, _stream()))
+
+    def result(self) -> FusedAttnOut:
+        o = self.out
+        return FusedAttnOut(o["o_hat"], o["topk_slots"], o["o_old_unnorm"], o["W"], o["topk_idx"],
+                            o["softmax_m"], o["softmax_inv_z"], self.scores)
+
+
+def fused_attn_topk(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
+                    max_S, H_q, H_kv, block_size, top_k, attn_scale, *, workspace=None,
+                    want_scores=False) -> FusedAttnOut:
+    """One call: approximate attention over the packed cache, exact top-k, and the
+    selected set's approximate contribution.  Returns ``(o_hat, topk_slots, o_old_unnorm,
+    W, ...)`` -- the first four as the reference's ``int2_fused_attn_topk``."""
+    call = DecodeCall(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
+                      max_S, H_q, H_kv, block_size, top_k, attn_scale, workspace=workspace,
+                      want_scores=want_scores)
+    call.fused()
+    return call.result()
+
+
+# ---------------------------------------------------------------------------------------
+# correction merge
+# ---------------------------------------------------------------------------------------
+
+def blend_unnorm_into(o_hat, o_old_unnorm, W, o_new, out) -> None:
+    """``out = dtype(o_hat + W * o_new - o_old_unnorm)``; ``out`` contiguous bf16/fp16."""
+    name = "blend_unnorm_into"
+    _require(o_hat.is_cuda and o_old_unnorm.is_cuda and W.is_cuda and o_new.is_cuda and out.is_cuda,
+             f"{name}: all tensors must be CUDA")
+    _require(o_hat.dtype == torch.float32 and o_old_unnorm.dtype == torch.float32 and W.dtype == torch.float32,
+             f"{name}: o_hat, o_old_unnorm, W must be float32")
+    _require(o_new.dtype == out.dtype, f"{name}: o_new and out dtypes differ")
+    _require(o_hat.dim() == 3 and o_old_unnorm.dim() == 3 and o_new.dim() == 3 and out.dim() == 3 and W.dim() == 2,
+             f"{name}: tensors must be 3D (W 2D)")
+    _require(out.is_contiguous(), f"{name}: out must be contiguous")
+    _require(o_old_unnorm.shape == o_hat.shape and o_new.shape == o_hat.shape and out.shape == o_hat.shape
+             and W.shape == o_hat.shape[:2] and o_hat.shape[2] == 128, f"{name}: shape mismatch")
+    o_hat, o_old_unnorm, W, o_new = o_hat.contiguous(), o_old_unnorm.contiguous(), W.contiguous(), o_new.contiguous()
+    st = lib.jf_merge_correct(o_hat.data_ptr(), o_old_unnorm.data_ptr(), W.data_ptr(), o_new.data_ptr(),
+                              out.data_ptr(), _dtype_id(out), o_hat.shape[0], o_hat.shape[1], _stream())
+    check(name, st)
+
+
+# ---------------------------------------------------------------------------------------
+# host correction
+# ---------------------------------------------------------------------------------------
+
+def set_cpu_attn_threads(n: int) -> None:
+    check("set_cpu_attn_threads", lib.jf_set_cpu_attn_threads(int(n)))
+
+
+def get_cpu_attn_threads() -> int:
+    return int(lib.jf_get_cpu_attn_threads())
+
+
+def _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag, name):
+    for t, nm in ((q, "q"), (k_shadow, "k_shadow"), (v_shadow, "v_shadow"), (ts_buf, "ts_buf"), (o_new, "o_new")):
+        _require(not t.is_cuda, f"{name}: {nm} must be a CPU tensor")
+        _require(t.is_contiguous(), f"{name}: {nm} must be contiguous")
+    _require(q.dtype == k_shadow.dtype == v_shadow.dtype == o_new.dtype, f"{name}: dtype mismatch")
+    _require(q.dim() == 3 and k_shadow.dim() == 3 and v_shadow.dim() == 3 and ts_buf.dim() == 3 and o_new.dim() == 3,
+             f"{name}: tensors must be 3D")
+    B, H_q, D = q.shape
+    H_kv, num_slots = k_shadow.shape[0], k_shadow.shape[1]
+    _require(D == 128 and k_shadow.shape[2] == 128, f"{name} currently only supports D=128")
+    _require(v_shadow.shape == k_shadow.shape, f"{name}: k/v mirror shape mismatch")
+    _require(ts_buf.dtype == torch.int64 and ts_buf.shape[:2] == (B, H_q), f"{name}: ts_buf must be (B,H_q,K) int64")
+    _require(o_new.shape == q.shape, f"{name}: o_new shape mismatch")
+    hm_ptr = None
+    if head_map is not None:
+        _require(head_map.dtype == torch.int64 and head_map.shape == ts_buf.shape and head_map.is_contiguous()
+                 and not head_map.is_cuda, f"{name}: head_map must match ts_buf (int64, CPU, contiguous)")
+        hm_ptr = head_map.data_ptr()
+    flag_ptr = None
+    if done_flag is not None:
+        _require(done_flag.dtype == torch.int64 and done_flag.numel() == 1 and not done_flag.is_cuda,
+                 f"{name}: done_flag must be a 1-element int64 CPU tensor")
+        flag_ptr = done_flag.data_ptr()
+    return (q.data_ptr(), k_shadow.data_ptr(), v_shadow.data_ptr(), hm_ptr, ts_buf.data_ptr(), o_new.data_ptr(),
+            _dtype_id(q), B, H_q, H_kv, num_slots, ts_buf.shape[2], float(scale), flag_ptr)
+
+
+def cpu_topk_attn(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None) -> None:
+    """Exact attention over the selected mirror rows, blocking."""
+    args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag, "cpu_topk_attn")
+    check("cpu_topk_attn", lib.jf_cpu_topk_attn(*args))
+
+
+def cpu_topk_attn_submit(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None) -> None:
+    args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag, "cpu_topk_attn_submit")
+    check("cpu_topk_attn_submit", lib.jf_pool_submit(*args))
+
+
+def cpu_topk_attn_wait(timeout_ms: int = 30000) -> None:
+    check("cpu_topk_attn_wait", lib.jf_pool_wait_timeout(int(timeout_ms)))
+
+
+def alloc_mapped_pinned_pair(shape, dtype):
+    """``(host_tensor, device_tensor)`` over the same pinned, GPU-mapped bytes."""
+    n = 1
+    for s in shape:
+        n *= int(s)
+    itemsize = torch.empty(0, dtype=dtype).element_size()
+    nbytes = max(n * itemsize, 1)
+    h, d = C.c_void_p(), C.c_void_p()
+    check("alloc_mapped_pinned_pair", lib.jf_alloc_mapped(nbytes, C.byref(h), C.byref(d)))
+    buf = (C.c_uint8 * nbytes).from_address(h.value)
+    host = torch.frombuffer(buf, dtype=dtype, count=n).reshape(*shape)
+    dev_ptr = d.value
+
+    class _DevView:
+        """CUDA array interface over the mapped device alias."""
+        __cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (dev_ptr, False), "version": 2, "strides": None}
+
+    device = torch.as_tensor(_DevView(), device="cuda").view(dtype)[:n].reshape(*shape)
+    host._jf_mapped = (buf, h.value)  # keep the ctypes view alive with the tensor
+    return host, device

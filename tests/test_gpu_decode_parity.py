@@ -1,0 +1,121 @@
+"""Fused decode scan / top-k / finish / merge on the GPU against the CPU oracle.
+
+Gates (stated once): packed bytes and top-k index lists bit-exact; attention outputs
+within 2e-3 max-abs + 1e-3 relative.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import jf_oracle as O
+from jf_testlib import Case, to_bits, f32_values
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-3, 1e-3
+
+
+def _close(got, want, what, atol=ATOL, rtol=RTOL):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = np.abs(got - want)
+    lim = atol + rtol * np.abs(want)
+    assert (err <= lim).all(), f"{what}: max err {err.max():.3e} (limit {lim[np.unravel_index(err.argmax(), err.shape)]:.3e})"
+
+
+def run_gpu(case: Case, top_k: int, want_scores=True):
+    from jetfire_b200 import ops
+    kd, ks, vd, vs = case.device_cache()
+    res = ops.fused_attn_topk(case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(),
+                              case.seq_lens.cuda(), case.ctx, case.H_q, case.H_kv, 16, top_k,
+                              case.attn_scale, want_scores=want_scores)
+    torch.cuda.synchronize()
+    return res, (kd, ks, vd, vs)
+
+
+def check_case(case: Case, top_k: int):
+    from jetfire_b200 import ops
+    res, (kd, ks, vd, vs) = run_gpu(case, top_k)
+    okd, oks, ovd, ovs = case.oracle_cache()
+    # the cache the GPU wrote is the oracle's, byte for byte
+    assert np.array_equal(kd.cpu().numpy(), okd) and np.array_equal(to_bits(ks), oks)
+    assert np.array_equal(vd.cpu().numpy(), ovd) and np.array_equal(to_bits(vs), ovs)
+    ref = case.oracle_step(top_k)
+    # top-k: identical lists (order: score desc, position asc), -1 padded
+    assert np.array_equal(res.topk_idx.cpu().numpy(), ref["topk_idx"]), "top-k positions differ"
+    assert np.array_equal(res.topk_slots.cpu().numpy(), ref["topk_slots"]), "top-k slots differ"
+    # approximate scores stay near the canonical ones; -inf past the sequence end
+    sc = res.scores.cpu().numpy()
+    for b in range(case.B):
+        n = min(int(case.seq_lens[b]), case.ctx)
+        assert np.isneginf(sc[b, :, n:]).all()
+        if n:
+            assert np.abs(sc[b, :, :n] - ref["scores"][b]).max() < 2e-2
+    _close(res.o_hat.cpu().numpy(), ref["o_hat"], "o_hat")
+    _close(res.o_old_unnorm.cpu().numpy(), ref["o_old_unnorm"], "o_old_unnorm")
+    _close(res.W.cpu().numpy(), ref["W"], "W", atol=1e-4, rtol=1e-3)
+    # correction merge with the oracle's o_new, then with the product's host correction
+    o_new = torch.from_numpy(ref["o_new"].view(np.int16).copy()).view(torch.bfloat16)
+    if case.dtype == torch.float16:
+        o_new = o_new.float().half()
+    out = torch.empty(case.B, case.H_q, 128, dtype=case.dtype, device="cuda")
+    ops.blend_unnorm_into(res.o_hat, res.o_old_unnorm, res.W, o_new.cuda(), out)
+    want = O.blend(ref["o_hat"], ref["o_old_unnorm"], ref["W"], O.f32_to_bf16_bits(f32_values(o_new)))
+    _close(out.float().cpu().numpy(), want, "out", atol=ATOL + 4e-3 * 0, rtol=RTOL + 2 ** -8)
+    return res, ref
+
+
+@pytest.mark.parametrize("B,H_q,H_kv,ctx,top_k,seed", [
+    (2, 8, 2, 512, 256, 1),      # the reference's validate_runtime geometry
+    (1, 32, 8, 4096, 256, 2),    # Llama-3.1-8B geometry, histogram path
+    (2, 16, 2, 2048, 128, 3),    # GQA group 8
+    (3, 4, 4, 1024, 64, 4),      # group 1
+    (2, 4, 2, 1536, 512, 5),     # group 2, wide k
+])
+def test_k3v2_matches_oracle(B, H_q, H_kv, ctx, top_k, seed):
+    check_case(Case("k3v2", B, H_q, H_kv, ctx, seed=seed), top_k)
+
+
+def test_k3v2_fp16_inputs():
+    check_case(Case("k3v2", 2, 8, 2, 1024, seed=11, dtype=torch.float16), 128)
+
+
+@pytest.mark.parametrize("ctx,lens,top_k,H_q,H_kv", [
+    (16, [1], 32, 8, 2),
+    (32, [0, 1, 9, 17], 32, 8, 2),
+    (512, [17, 257, 512], 256, 32, 4),
+    (512, [17, 257, 512], 256, 32, 8),
+    (4096, [4096, 4083, 600, 0], 256, 8, 2),
+])
+def test_k3v2_short_and_ragged(ctx, lens, top_k, H_q, H_kv):
+    """Lengths shorter than top_k including 0 and 1 (scripts/validate_runtime_edges.py:229-232):
+    every real position once, -1 elsewhere."""
+    case = Case("k3v2", len(lens), H_q, H_kv, ctx, lens=lens, seed=21 + ctx)
+    res, ref = check_case(case, top_k)
+    idx = res.topk_idx.cpu().numpy()
+    for b, n in enumerate(lens):
+        for h in range(H_q):
+            real = idx[b, h][idx[b, h] >= 0]
+            assert real.size == min(top_k, n) and np.unique(real).size == real.size
+            assert (real < max(n, 1)).all()
+
+
+def test_k3v2_massive_ties_take_lowest_positions():
+    """All-zero keys: every score ties at 0, so the k lowest positions win (slow exact path)."""
+    case = Case("k3v2", 1, 8, 2, 2048, seed=5)
+    case.k_full.zero_()
+    res, ref = check_case(case, 64)
+    assert np.array_equal(res.topk_idx.cpu().numpy()[0, 0], np.arange(64))
+
+
+def test_phases_one_by_one_equal_fused():
+    from jetfire_b200 import ops
+    case = Case("k3v2", 2, 8, 2, 1024, seed=8)
+    kd, ks, vd, vs = case.device_cache()
+    args = (case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+            case.ctx, case.H_q, case.H_kv, 16, 128, case.attn_scale)
+    fused = ops.fused_attn_topk(*args)
+    call = ops.DecodeCall(*args)
+    call.scan(); call.select(); call.finish(); call.status()
+    step = call.result()
+    for a, b in zip(fused[:7], step[:7]):
+        assert torch.equal(a, b)
