@@ -1,8 +1,16 @@
 // finish: merge the scan's split partials (log-sum-exp) into o_hat and the softmax
 // statistics, then compute the approximate contribution of the selected set,
 //   W = sum_{i in T} p_i,   o_old_unnorm[d] = sum_{i in T} (p_i * vscale_i,g(d)) * vcode_i,d
-// with p_i = exp(s_i - m) / Z taken from the same approximate scores the scan used
 // (jetfire_vllm/csrc/int2_softmax_v.cu:738-788; V4: csrc/int4_softmax_v.cu:599-817).
+//
+// Weight swap for the selected set.  The scan's scores skip the reference's bf16 rounding
+// of the dequantised key, so a weight can be off by ~1e-3 relative -- visible only on the
+// few dominant positions, which are exactly the selected ones.  For every selected
+// position the select kernel has the canonical score s_c; here the scan's weight
+// exp(s_f - M) is replaced by exp(s_c - M) in the numerator, the normaliser and the
+// selected-set terms, so that p_i of the selected set follows the reference arithmetic
+// and the remaining (individually small) weights keep their approximate scores.
+//
 // merge_correct: out = dtype(o_hat + W * float(o_new) - o_old_unnorm)
 // (jetfire_vllm/csrc/blend.cu:202-226).  The normaliser stays the approximate softmax's:
 // this is mass substitution, not a re-normalised merge.
@@ -16,6 +24,7 @@ constexpr int kChunk = 128;
 
 struct FinishParams {
   const float* scores;
+  const float* sel_canon;
   const float* part_o;
   const float* part_m;
   const float* part_l;
@@ -37,15 +46,15 @@ template <int MODE>
 __global__ void __launch_bounds__(JF_HEAD_DIM)
 decode_finish_kernel(const FinishParams p) {
   __shared__ int64_t sm_slot[kChunk];
-  __shared__ float sm_pv[kChunk][2];
-  __shared__ float sm_p[kChunk];
-  __shared__ float sm_w[4];
+  __shared__ float sm_wc[kChunk][2];   // canonical weight * v scale (per group)
+  __shared__ float sm_dw[kChunk][2];   // (canonical - scan) weight * v scale
+  __shared__ float sm_w[kChunk][2];    // canonical weight, weight difference
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int hkv = h / p.G, hi = h - hkv * p.G;
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
   const int n = min(p.seq_lens[b], p.max_S);
 
-  // ---- merge splits ----
+  // ---- merge splits (unnormalised) ----
   const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
   float M = kMinusBig;
   for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.part_m[(pbase + s) * kHeadsPad + hi]);
@@ -55,45 +64,43 @@ decode_finish_kernel(const FinishParams p) {
     Z = fmaf(p.part_l[(pbase + s) * kHeadsPad + hi], w, Z);
     o = fmaf(p.part_o[((pbase + s) * kHeadsPad + hi) * JF_HEAD_DIM + d], w, o);
   }
-  const float inv_z = (Z > 0.f && n > 0) ? (1.0f / Z) : 0.f;
-  if (!(Z > 0.f) || n <= 0) M = 0.f;
-  p.o_hat[bh * JF_HEAD_DIM + d] = o * inv_z;
-  if (d == 0) {
-    if (p.softmax_m) p.softmax_m[bh] = M;
-    if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
-  }
 
-  // ---- approximate contribution of the selected set ----
+  // ---- selected set: canonical weights, and their difference to the scan's ----
   const ModeInfo mi = mode_info(MODE);
   const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
   const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
   const int64_t* bt = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
   const float* srow = p.scores + bh * p.max_S;
   const int64_t* sel = p.topk_idx + bh * p.top_k;
-  float acc = 0.f, wsum = 0.f;
+  const float* canon = p.sel_canon + bh * p.top_k;
+  float acc_old = 0.f, acc_dw = 0.f, wsum = 0.f, dz = 0.f;
   for (int k0 = 0; k0 < p.top_k; k0 += kChunk) {
     {
       const int kk = k0 + d;
       int64_t slot = -1;
-      float pr = 0.f, pv0 = 0.f, pv1 = 0.f;
-      if (kk < p.top_k) {
+      float wc = 0.f, dw = 0.f, vs0 = 0.f, vs1 = 0.f;
+      if (kk < p.top_k && n > 0) {
         const int64_t pos = sel[kk];
         if (pos >= 0 && pos < n) {
           const int64_t blk = bt[pos >> 4];
           if (blk >= 0 && blk < (p.num_slots >> 4)) {
             slot = blk * 16 + (pos & 15);
-            pr = ex2((srow[pos] - M) * kLog2e) * inv_z;
+            wc = ex2((canon[kk] - M) * kLog2e);
+            dw = wc - ex2((srow[pos] - M) * kLog2e);
             if (MODE == JF_MODE_K3V2) {
               const uint32_t sw = __ldg(reinterpret_cast<const uint32_t*>(v_sc + slot * 2));
-              pv0 = pr * __uint_as_float(sw << 16);
-              pv1 = pr * __uint_as_float(sw & 0xFFFF0000u);
+              vs0 = __uint_as_float(sw << 16);
+              vs1 = __uint_as_float(sw & 0xFFFF0000u);
             } else {
-              pv0 = pv1 = pr * bf16_bits_to_f32(__ldg(v_sc + slot));
+              vs0 = vs1 = bf16_bits_to_f32(__ldg(v_sc + slot));
             }
           }
         }
       }
-      sm_slot[d] = slot; sm_p[d] = pr; sm_pv[d][0] = pv0; sm_pv[d][1] = pv1;
+      sm_slot[d] = slot;
+      sm_w[d][0] = wc; sm_w[d][1] = dw;
+      sm_wc[d][0] = wc * vs0; sm_wc[d][1] = wc * vs1;
+      sm_dw[d][0] = dw * vs0; sm_dw[d][1] = dw * vs1;
     }
     __syncthreads();
     const int kend = min(kChunk, p.top_k - k0);
@@ -108,14 +115,24 @@ decode_finish_kernel(const FinishParams p) {
         const uint32_t byte = __ldg(v_rows + slot * 64 + (d >> 1));
         code = static_cast<int>((d & 1) ? (byte & 15u) : (byte >> 4)) - 8;
       }
-      acc = fmaf(sm_pv[j][d >> 6], static_cast<float>(code), acc);
-      wsum += sm_p[j];
+      const float cf = static_cast<float>(code);
+      acc_old = fmaf(sm_wc[j][d >> 6], cf, acc_old);
+      acc_dw = fmaf(sm_dw[j][d >> 6], cf, acc_dw);
+      wsum += sm_w[j][0];
+      dz += sm_w[j][1];
     }
     __syncthreads();
   }
-  p.o_old[bh * JF_HEAD_DIM + d] = acc;
-  if (d == 0) p.W[bh] = wsum;
-  (void)sm_w;
+  Z += dz;
+  const bool live = (Z > 0.f) && (n > 0);
+  const float inv_z = live ? (1.0f / Z) : 0.f;
+  p.o_hat[bh * JF_HEAD_DIM + d] = (o + acc_dw) * inv_z;
+  p.o_old[bh * JF_HEAD_DIM + d] = acc_old * inv_z;
+  if (d == 0) {
+    p.W[bh] = wsum * inv_z;
+    if (p.softmax_m) p.softmax_m[bh] = live ? M : 0.f;
+    if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
+  }
 }
 
 template <int DT>
@@ -139,9 +156,10 @@ extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t str
   if (st != JF_OK) return st;
   if (!a->topk_idx || !a->o_hat || !a->o_old_unnorm || !a->W) return JF_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, true);
+  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   FinishParams fp{};
   fp.scores = a->scores ? a->scores : ws.scores;
+  fp.sel_canon = ws.sel_canon;
   fp.part_o = ws.part_o; fp.part_m = ws.part_m; fp.part_l = ws.part_l;
   fp.v_data = a->v_data; fp.v_scales = static_cast<const uint16_t*>(a->v_scales);
   fp.block_table = a->block_table; fp.seq_lens = a->seq_lens; fp.topk_idx = a->topk_idx;

@@ -22,42 +22,11 @@
 // and the 2^pos factor is undone on the other operand (K: folded into Q) or on the output
 // row (V).  Group scales are applied in fp32 after the K MMA and folded into P before the
 // V MMA, so the integer codes stay exact in fp16.
-#include "decode_common.cuh"
+#include "decode_scan.cuh"
 
 namespace jf {
 
 namespace {
-
-constexpr int kStages = 8;  // pages in flight per warp
-
-template <int MODE> struct Tile;
-template <> struct Tile<JF_MODE_K3V2> {
-  static constexpr int kKRow = 48, kVRow = 32, kNG = 2;
-  static constexpr int kKOff = 0, kVOff = 768, kKsOff = 1280, kVsOff = 1344, kBytes = 1408;
-};
-template <> struct Tile<JF_MODE_K4V4> {
-  static constexpr int kKRow = 64, kVRow = 64, kNG = 1;
-  static constexpr int kKOff = 0, kVOff = 1024, kKsOff = 2048, kVsOff = 2080, kBytes = 2112;
-};
-
-struct ScanParams {
-  const void* q;
-  const uint8_t* k_data;
-  const uint16_t* k_scales;
-  const uint8_t* v_data;
-  const uint16_t* v_scales;
-  const int64_t* block_table;
-  const int32_t* seq_lens;
-  float* scores;
-  float* part_o;
-  float* part_m;
-  float* part_l;
-  float* part_smax;
-  int32_t* status;
-  int64_t num_slots;
-  int B, H_q, H_kv, G, max_S, max_blocks, splits, pages_per_split;
-  float attn_scale;
-};
 
 // bit position at which code x (0..7) of an INT3 group is picked up, see unpack below
 __device__ __forceinline__ constexpr int k3_pos(int x) {
@@ -68,8 +37,6 @@ __device__ __forceinline__ constexpr int v2_pos(int f) { return f <= 4 ? 2 * f :
 // head-dim index inside the 8-wide chunk for field f: bytes are little-endian in the
 // 16-bit load, codes MSB-first inside a byte
 __device__ __forceinline__ constexpr int v2_dlocal(int f) { return 4 * (f >> 2) + 3 - (f & 3); }
-
-constexpr uint32_t kMagic = 0x64006400u;  // fp16 1024.0 in both halves
 
 template <int POS>
 __device__ __forceinline__ uint32_t k3_field(uint32_t v) {
@@ -83,17 +50,6 @@ __device__ __forceinline__ uint32_t v2_field(uint32_t v) {
   constexpr uint32_t m = (3u << POS) | (3u << (POS + 16));
   constexpr uint32_t b = (0x6400u | (2u << POS)) * 0x10001u;
   return hsub2_u32(and_or(v, m, kMagic), b);
-}
-
-template <int DT>
-__device__ __forceinline__ float load_q(const void* q, int64_t idx) {
-  return Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(q)[idx]);
-}
-
-__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
-  uint32_t d;
-  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
 }
 
 }  // namespace
@@ -110,9 +66,9 @@ scan_k3v2_kernel(const ScanParams p) {
   const int g = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
 
-  uint8_t* my_stages = smem + warp * (kStages * T::kBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * kStages * T::kBytes) + warp * kStages;
-  int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * kStages * (T::kBytes + 8)) + warp * kStages;
+  uint8_t* my_stages = smem + warp * (T::kStages * T::kBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * T::kStages * T::kBytes) + warp * T::kStages;
+  int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8)) + warp * T::kStages;
 
   const int len = min(p.seq_lens[b], p.max_S);
   const int n_pages = (len + 15) >> 4;
@@ -122,7 +78,7 @@ scan_k3v2_kernel(const ScanParams p) {
   const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;  // may be <= 0
 
   if (lane == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < T::kStages; ++s) mbar_init(&bars[s], 1);
   }
   fence_barrier_init();
   __syncwarp();
@@ -136,7 +92,7 @@ scan_k3v2_kernel(const ScanParams p) {
 
   // Lanes 0..3 each issue one of the four copies of a page.
   auto issue = [&](int it, int64_t blk) {
-    const int st = it % kStages;
+    const int st = it % T::kStages;
     const int pg = pg_begin + warp + it * kScanWarps;
     int valid = min(16, len - pg * 16);
     if (blk < 0 || blk >= n_blocks_phys) { blk = 0; valid = 0; }
@@ -159,11 +115,11 @@ scan_k3v2_kernel(const ScanParams p) {
 
   // prologue
   {
-    const int pro = min(kStages, my_n);
+    const int pro = min(T::kStages, my_n);
     for (int it = 0; it < pro; ++it) issue(it, bt_row[pg_begin + warp + it * kScanWarps]);
   }
   int64_t next_blk = 0;
-  if (kStages < my_n) next_blk = bt_row[pg_begin + warp + kStages * kScanWarps];
+  if (T::kStages < my_n) next_blk = bt_row[pg_begin + warp + T::kStages * kScanWarps];
 
   // ---- query fragments: B operand of the K MMA, scaled by 2^-pos of the code it meets ----
   uint32_t qf[8][2];
@@ -201,11 +157,11 @@ scan_k3v2_kernel(const ScanParams p) {
   const float attn = p.attn_scale;
 
   for (int it = 0; it < my_n; ++it) {
-    const int st = it % kStages;
-    if (!mbar_wait(&bars[st], (it / kStages) & 1)) {
+    const int st = it % T::kStages;
+    if (!mbar_wait(&bars[st], (it / T::kStages) & 1)) {
       // give the copies that were already issued a short, bounded chance to land
-      for (int j = it + 1; j < min(my_n, it + kStages); ++j)
-        mbar_wait(&bars[j % kStages], (j / kStages) & 1, 1000000ull);
+      for (int j = it + 1; j < min(my_n, it + T::kStages); ++j)
+        mbar_wait(&bars[j % T::kStages], (j / T::kStages) & 1, 1000000ull);
       failed = true;
       break;
     }
@@ -272,29 +228,9 @@ scan_k3v2_kernel(const ScanParams p) {
       if (st1) { if (t0 < valid) r0[p.max_S + t0] = s1; if (t0 + 8 < valid) r0[p.max_S + t0 + 8] = s3; }
     }
 
-    // ---------------- online softmax (reference point may lag the true max by < 4) ----------------
-    {
-      float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
-      const bool need = (mx0 > m_ref0 + 4.0f) || (mx1 > m_ref1 + 4.0f);
-      if (__any_sync(0xFFFFFFFFu, need)) {
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
-          mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
-        }
-        const float n0 = fmaxf(m_ref0, mx0), n1 = fmaxf(m_ref1, mx1);
-        const float f0 = ex2((m_ref0 - n0) * kLog2e), f1 = ex2((m_ref1 - n1) * kLog2e);
-        l0 *= f0; l1 *= f1;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { oacc[i][0] *= f0; oacc[i][1] *= f1; oacc[i][2] *= f0; oacc[i][3] *= f1; }
-        m_ref0 = n0; m_ref1 = n1;
-      }
-    }
-    const float mb0 = m_ref0 * kLog2e, mb1 = m_ref1 * kLog2e;
-    const float p0 = ex2(fmaf(s0, kLog2e, -mb0)), p1 = ex2(fmaf(s1, kLog2e, -mb1));
-    const float p2 = ex2(fmaf(s2, kLog2e, -mb0)), p3 = ex2(fmaf(s3, kLog2e, -mb1));
-    l0 += p0 + p2;
-    l1 += p1 + p3;
+    // ---------------- online softmax ----------------
+    float p0, p1, p2, p3;
+    softmax_step(s0, s1, s2, s3, m_ref0, m_ref1, l0, l1, oacc, p0, p1, p2, p3);
 
     // ---------------- V: unpack + (P * vscale).V ----------------
 #pragma unroll
@@ -317,9 +253,9 @@ scan_k3v2_kernel(const ScanParams p) {
     }
 
     __syncwarp();
-    if (it + kStages < my_n) {
-      issue(it + kStages, next_blk);
-      if (it + kStages + 1 < my_n) next_blk = bt_row[pg_begin + warp + (it + kStages + 1) * kScanWarps];
+    if (it + T::kStages < my_n) {
+      issue(it + T::kStages, next_blk);
+      if (it + T::kStages + 1 < my_n) next_blk = bt_row[pg_begin + warp + (it + T::kStages + 1) * kScanWarps];
     }
   }
 
@@ -327,65 +263,21 @@ scan_k3v2_kernel(const ScanParams p) {
 
   // ---------------- CTA merge: 4 warps -> one partial ----------------
   __syncthreads();  // every warp is done with its stages (or gave up); smem is reused below
-  float* sm_o = reinterpret_cast<float*>(smem);              // [8][128]
-  float* sm_m = sm_o + kHeadsPad * JF_HEAD_DIM;               // [4][8]
-  float* sm_l = sm_m + kScanWarps * kHeadsPad;                // [4][8]
-  float* sm_s = sm_l + kScanWarps * kHeadsPad;                // [4][2]
-#pragma unroll
-  for (int o = 4; o < 32; o <<= 1) {
-    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, o);
-    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
-  }
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    smax0 = fmaxf(smax0, __shfl_xor_sync(0xFFFFFFFFu, smax0, o));
-    smax1 = fmaxf(smax1, __shfl_xor_sync(0xFFFFFFFFu, smax1, o));
-  }
-  for (int i = threadIdx.x; i < kHeadsPad * JF_HEAD_DIM; i += blockDim.x) sm_o[i] = 0.f;
-  if (g == 0) {
-    sm_m[warp * 8 + 2 * tig] = m_ref0; sm_m[warp * 8 + 2 * tig + 1] = m_ref1;
-    sm_l[warp * 8 + 2 * tig] = l0;     sm_l[warp * 8 + 2 * tig + 1] = l1;
-  }
-  if (lane == 0) { sm_s[warp * 2] = smax0; sm_s[warp * 2 + 1] = smax1; }
-  __syncthreads();
-  float M0 = kMinusBig, M1 = kMinusBig;
-#pragma unroll
-  for (int w = 0; w < kScanWarps; ++w) {
-    M0 = fmaxf(M0, sm_m[w * 8 + 2 * tig]);
-    M1 = fmaxf(M1, sm_m[w * 8 + 2 * tig + 1]);
-  }
   {
-    const float f0 = ex2((m_ref0 - M0) * kLog2e), f1 = ex2((m_ref1 - M1) * kLog2e);
+    float* wo = reinterpret_cast<float*>(smem) + warp * (kHeadsPad * JF_HEAD_DIM);
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
       const int qh = mt >> 2, ml = mt & 3;
       const int fa = 2 * ml, fb = 2 * ml + 1;
       const int da = 64 * qh + 8 * g + v2_dlocal(fa), db = 64 * qh + 8 * g + v2_dlocal(fb);
       const float ua = 1.0f / static_cast<float>(1 << v2_pos(fa)), ub = 1.0f / static_cast<float>(1 << v2_pos(fb));
-      atomicAdd(&sm_o[(2 * tig) * JF_HEAD_DIM + da], oacc[mt][0] * f0 * ua);
-      atomicAdd(&sm_o[(2 * tig + 1) * JF_HEAD_DIM + da], oacc[mt][1] * f1 * ua);
-      atomicAdd(&sm_o[(2 * tig) * JF_HEAD_DIM + db], oacc[mt][2] * f0 * ub);
-      atomicAdd(&sm_o[(2 * tig + 1) * JF_HEAD_DIM + db], oacc[mt][3] * f1 * ub);
+      wo[(2 * tig) * JF_HEAD_DIM + da] = oacc[mt][0] * ua;
+      wo[(2 * tig + 1) * JF_HEAD_DIM + da] = oacc[mt][1] * ua;
+      wo[(2 * tig) * JF_HEAD_DIM + db] = oacc[mt][2] * ub;
+      wo[(2 * tig + 1) * JF_HEAD_DIM + db] = oacc[mt][3] * ub;
     }
   }
-  __syncthreads();
-  const int64_t pidx = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits + split;
-  float* po = p.part_o + pidx * (kHeadsPad * JF_HEAD_DIM);
-  for (int i = threadIdx.x; i < kHeadsPad * JF_HEAD_DIM; i += blockDim.x) po[i] = sm_o[i];
-  if (threadIdx.x < kHeadsPad) {
-    const int h = threadIdx.x;
-    float M = kMinusBig;
-    for (int w = 0; w < kScanWarps; ++w) M = fmaxf(M, sm_m[w * 8 + h]);
-    float L = 0.f;
-    for (int w = 0; w < kScanWarps; ++w) L += sm_l[w * 8 + h] * ex2((sm_m[w * 8 + h] - M) * kLog2e);
-    p.part_m[pidx * kHeadsPad + h] = M;
-    p.part_l[pidx * kHeadsPad + h] = L;
-  }
-  if (threadIdx.x < 2) {
-    float s = 0.f;
-    for (int w = 0; w < kScanWarps; ++w) s = fmaxf(s, sm_s[w * 2 + threadIdx.x]);
-    p.part_smax[pidx * 2 + threadIdx.x] = s;
-  }
+  cta_merge_store(p, smem, l0, l1, m_ref0, m_ref1, smax0, smax1, split, hkv, b);
 }
 
 // ------------------------------------------------------------------------------------
@@ -425,9 +317,9 @@ __global__ void fill_neg_inf_tail_kernel(float* scores, const int32_t* seq_lens,
 
 extern "C" uint64_t jf_decode_workspace_bytes(int32_t mode, int32_t B, int32_t H_q, int32_t H_kv,
                                               int32_t max_S, int32_t top_k) {
-  (void)mode; (void)top_k;
-  if (B <= 0 || H_q <= 0 || H_kv <= 0 || max_S <= 0) return 0;
-  return jf::carve_workspace(nullptr, B, H_q, H_kv, max_S, true).bytes;
+  (void)mode;
+  if (B <= 0 || H_q <= 0 || H_kv <= 0 || max_S <= 0 || top_k <= 0) return 0;
+  return jf::carve_workspace(nullptr, B, H_q, H_kv, max_S, top_k, true).bytes;
 }
 
 extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t stream_) {
@@ -435,7 +327,7 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   jf_status_t st = validate_decode_args(a);
   if (st != JF_OK) return st;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, true);
+  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   JF_CUDA_TRY(cudaMemsetAsync(ws.status, 0, sizeof(int32_t), stream));
   ScanParams sp{};
   sp.q = a->q;
@@ -455,8 +347,8 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   dim3 grid(sp.splits, a->H_kv, a->B);
   if (a->mode == JF_MODE_K3V2) {
     using T = Tile<JF_MODE_K3V2>;
-    const size_t smem = kScanWarps * kStages * (T::kBytes + 8 + 4);
-    static_assert(kScanWarps * kStages * T::kBytes >= (kHeadsPad * JF_HEAD_DIM + 3 * kScanWarps * kHeadsPad) * 4, "merge buffer");
+    const size_t smem = kScanWarps * T::kStages * (T::kBytes + 8 + 4);
+    static_assert(kScanWarps * T::kStages * T::kBytes >= kMergeBytes, "merge buffer");
     if (a->q_dtype == JF_DTYPE_BF16) {
       JF_CUDA_TRY(cudaFuncSetAttribute(scan_k3v2_kernel<JF_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       scan_k3v2_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
@@ -466,7 +358,8 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
     }
     JF_CUDA_TRY(cudaGetLastError());
   } else {
-    return JF_ERR_UNSUPPORTED;
+    st = launch_scan_k4v4(sp, a->q_dtype, grid, stream);
+    if (st != JF_OK) return st;
   }
   if (a->scores) {
     fill_neg_inf_tail_kernel<<<a->B * a->H_q, 256, 0, stream>>>(a->scores, a->seq_lens, a->H_q, a->max_S);

@@ -1,0 +1,367 @@
+// K4V4 (INT4 K, INT4 V, group 128) flavour of the fused decode scan.
+//
+// Scores follow the reference's INT8 tensor-core arithmetic exactly
+// (jetfire_vllm/csrc/int8tc_qk_scores.cu:272-290, 445-487): the query is quantised to INT8
+// per 32-channel block with qs = max(amax/127, 1e-12) and qi = clamp(rn(q * (1/qs))); per
+// block an exact int32 dot of qi with (code - 8); then s = fma(float(acc_c), qs_c, s) for
+// c = 0..3, * k_scale, * attn_scale.  Integer MMA is exact, so these scores are bit-equal
+// to what a CPU computes in the same order and the selection needs no re-scoring band.
+// The nibbles are fed to mma.sync.m16n8k32 as *unsigned* bytes against the signed query
+// (mixed u8 x s8), the "-8" being folded into the accumulator's start value
+// -8 * sum(qi) per block.
+//
+// P.V runs in fp16 like K3V2 (the reference's INT8 quantisation of P for batch > 1,
+// csrc/int8tc_softmax_v_fused.cu:1203-1311, is less accurate than its own fp32 path and is
+// not reproduced; distances to both are measured in the tests).
+//
+// Pages are 64-byte rows; read straight, eight rows of a fragment would hit only two
+// bank groups.  K and V pages are therefore fetched with tiled tensor copies
+// (cp.async.bulk.tensor.2d) using the 64-byte swizzle, which XORs the 16-byte chunk index
+// with bits 1..2 of the row index -- fragment loads then touch all banks once.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "decode_scan.cuh"
+
+namespace jf {
+
+namespace {
+
+using T4 = Tile<JF_MODE_K4V4>;
+
+// token held by MMA row r (0..7); rows r + 8 hold token + 8.  Chosen so that both the K
+// fragment loads (8 rows) and the V fragment loads (4 tokens x 8 lanes) are conflict-free
+// under the 64-byte swizzle.
+__device__ __forceinline__ constexpr int row_token(int r) {
+  return ((r >> 2) & 1) | (((r >> 1) & 1) << 2) | ((r & 1) << 1);
+}
+
+template <int POS>
+__device__ __forceinline__ uint32_t v4_field(uint32_t v) {
+  // ((v & nibble) | 1024) - (1024 + 8 * 2^POS) == (code - 8) * 2^POS, exact in fp16
+  constexpr uint32_t m = (15u << POS) | (15u << (POS + 16));
+  constexpr uint32_t b = (0x6400u | (8u << POS)) * 0x10001u;
+  return hsub2_u32(and_or(v, m, kMagic), b);
+}
+
+__device__ __forceinline__ void mma_u8s8_cd(int (&d)[4], const int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%11,%12,%13};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+}  // namespace
+
+template <int DT>
+__global__ void __launch_bounds__(kScanWarps * 32, 3)
+scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
+                 const __grid_constant__ CUtensorMap v_map) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // swizzled tiles must sit on 512-byte boundaries: align by hand (1 KB of slack is allocated)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+
+  uint8_t* my_stages = smem + warp * (T4::kStages * T4::kBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * T4::kStages * T4::kBytes) + warp * T4::kStages;
+  int32_t* page_valid =
+      reinterpret_cast<int32_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8)) + warp * T4::kStages;
+
+  const int len = min(p.seq_lens[b], p.max_S);
+  const int n_pages = (len + 15) >> 4;
+  const int pg_begin = split * p.pages_per_split;
+  const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
+  const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;
+
+  if (lane == 0) {
+    for (int s = 0; s < T4::kStages; ++s) mbar_init(&bars[s], 1);
+  }
+  fence_barrier_init();
+  __syncwarp();
+
+  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  const int64_t n_blocks_phys = p.num_slots >> 4;
+  const int64_t row_base = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
+  const uint16_t* ks_h = p.k_scales + row_base;
+  const uint16_t* vs_h = p.v_scales + row_base;
+
+  auto issue = [&](int it, int64_t blk) {
+    const int st = it % T4::kStages;
+    const int pg = pg_begin + warp + it * kScanWarps;
+    int valid = min(16, len - pg * 16);
+    if (blk < 0 || blk >= n_blocks_phys) { blk = 0; valid = 0; }
+    uint8_t* dst = my_stages + st * T4::kBytes;
+    if (lane == 0) {
+      page_valid[st] = valid;
+      mbar_expect_tx(&bars[st], T4::kTxBytes);
+    }
+    __syncwarp();
+    const int y = static_cast<int>(row_base + blk * 16);
+    if (lane == 0) tma_load_2d(dst + T4::kKOff, &k_map, 0, y, &bars[st]);
+    else if (lane == 1) tma_load_2d(dst + T4::kVOff, &v_map, 0, y, &bars[st]);
+    else if (lane == 2) bulk_g2s(dst + T4::kKsOff, ks_h + blk * 16, 32, &bars[st]);
+    else if (lane == 3) bulk_g2s(dst + T4::kVsOff, vs_h + blk * 16, 32, &bars[st]);
+  };
+
+  {
+    const int pro = min(T4::kStages, my_n);
+    for (int it = 0; it < pro; ++it) issue(it, bt_row[pg_begin + warp + it * kScanWarps]);
+  }
+  int64_t next_blk = 0;
+  if (T4::kStages < my_n) next_blk = bt_row[pg_begin + warp + T4::kStages * kScanWarps];
+
+  // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
+  //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones. ----
+  uint32_t qb[4][2];
+  float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
+  int init_h0[4], init_h1[4]; // -8 * sum(qi) per block for those heads
+  {
+    const int h = hkv * p.G + g;
+    const bool live = g < p.G;
+    const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + h) * JF_HEAD_DIM;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[8];
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[j] = live ? load_q<DT>(p.q, qbase + 32 * c + 8 * tig + j) : 0.f;
+        amax = fmaxf(amax, fabsf(v[j]));
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+      const float qs = fmaxf(__fdiv_rn(amax, 127.0f), 1e-12f);
+      const float inv = __fdiv_rn(1.0f, qs);
+      int qi[8], sum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        qi[j] = max(-128, min(127, __float2int_rn(__fmul_rn(v[j], inv))));
+        sum += qi[j];
+      }
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+      qb[c][0] = (qi[0] & 255) | ((qi[2] & 255) << 8) | ((qi[4] & 255) << 16) | ((qi[6] & 255) << 24);
+      qb[c][1] = (qi[1] & 255) | ((qi[3] & 255) << 8) | ((qi[5] & 255) << 16) | ((qi[7] & 255) << 24);
+      qs_h0[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig);
+      qs_h1[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig + 4);
+      init_h0[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig);
+      init_h1[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig + 4);
+    }
+  }
+
+  float oacc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+  float m_ref0 = kMinusBig, m_ref1 = kMinusBig, l0 = 0.f, l1 = 0.f;
+  bool failed = false;
+
+  const int t0 = row_token(g);                 // token of MMA row g (row g + 8 -> t0 + 8)
+  const int ksw = (t0 >> 1) & 3;               // swizzle term of rows t0 and t0 + 8
+  const int tA = row_token(2 * tig), tB = row_token(2 * tig + 1);  // tokens of P.V k-slots
+  const int h0 = hkv * p.G + 2 * tig;
+  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S;
+  const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
+  const float attn = p.attn_scale;
+  // byte offsets of this lane's V words inside a token row, swizzled per token below
+  const int vchunk = g >> 1, vsub = 8 * (g & 1);
+
+  for (int it = 0; it < my_n; ++it) {
+    const int st = it % T4::kStages;
+    if (!mbar_wait(&bars[st], (it / T4::kStages) & 1)) {
+      for (int j = it + 1; j < min(my_n, it + T4::kStages); ++j)
+        mbar_wait(&bars[j % T4::kStages], (j / T4::kStages) & 1, 1000000ull);
+      failed = true;
+      break;
+    }
+    const uint8_t* sp = my_stages + st * T4::kBytes;
+    const int valid = page_valid[st];
+    const int pg = pg_begin + warp + it * kScanWarps;
+
+    // ---------------- K: nibbles -> u8 fragments, exact integer Q.K^T per block ----------------
+    int acc[4][4];
+    {
+      const uint8_t* r0 = sp + T4::kKOff + t0 * 64 + 4 * tig;
+      const uint8_t* r1 = r0 + 512;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int off = (c ^ ksw) << 4;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(r0 + off);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(r1 + off);
+        const int init[4] = {init_h0[c], init_h1[c], init_h0[c], init_h1[c]};
+        mma_u8s8_cd(acc[c], init, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu,
+                    w1 & 0x0F0F0F0Fu, qb[c][0], qb[c][1]);
+      }
+    }
+    float ks0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kKsOff + t0 * 2));
+    float ks1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kKsOff + (t0 + 8) * 2));
+    float vs0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kVsOff + t0 * 2));
+    float vs1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kVsOff + (t0 + 8) * 2));
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s0 = __fmaf_rn(static_cast<float>(acc[c][0]), qs_h0[c], s0);
+      s1 = __fmaf_rn(static_cast<float>(acc[c][1]), qs_h1[c], s1);
+      s2 = __fmaf_rn(static_cast<float>(acc[c][2]), qs_h0[c], s2);
+      s3 = __fmaf_rn(static_cast<float>(acc[c][3]), qs_h1[c], s3);
+    }
+    s0 = __fmul_rn(__fmul_rn(s0, ks0), attn);
+    s1 = __fmul_rn(__fmul_rn(s1, ks0), attn);
+    s2 = __fmul_rn(__fmul_rn(s2, ks1), attn);
+    s3 = __fmul_rn(__fmul_rn(s3, ks1), attn);
+    if (valid < 16) {
+      if (t0 >= valid) { s0 = s1 = -INFINITY; vs0 = 0.f; }
+      if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; vs1 = 0.f; }
+    }
+    {
+      float* r0 = score_row0 + pg * 16;
+      if (st0) { if (t0 < valid) r0[t0] = s0; if (t0 + 8 < valid) r0[t0 + 8] = s2; }
+      if (st1) { if (t0 < valid) r0[p.max_S + t0] = s1; if (t0 + 8 < valid) r0[p.max_S + t0 + 8] = s3; }
+    }
+
+    // ---------------- online softmax ----------------
+    float p0, p1, p2, p3;
+    softmax_step(s0, s1, s2, s3, m_ref0, m_ref1, l0, l1, oacc, p0, p1, p2, p3);
+
+    // ---------------- V: nibbles -> fp16 fragments, (P * vscale).V ----------------
+    {
+      const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * vs0, p1 * vs0));  // tokens tA, tB
+      const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vs1, p3 * vs1));  // tokens tA+8, tB+8
+      const uint8_t* vb = sp + T4::kVOff + vsub;
+      const uint2 Wa = *reinterpret_cast<const uint2*>(vb + tA * 64 + ((vchunk ^ ((tA >> 1) & 3)) << 4));
+      const uint2 Wb = *reinterpret_cast<const uint2*>(vb + tB * 64 + ((vchunk ^ ((tB >> 1) & 3)) << 4));
+      const uint2 Wc = *reinterpret_cast<const uint2*>(vb + 512 + tA * 64 + ((vchunk ^ ((tA >> 1) & 3)) << 4));
+      const uint2 Wd = *reinterpret_cast<const uint2*>(vb + 512 + tB * 64 + ((vchunk ^ ((tB >> 1) & 3)) << 4));
+      const uint32_t wa[2] = {Wa.x, Wa.y}, wb[2] = {Wb.x, Wb.y}, wc[2] = {Wc.x, Wc.y}, wd[2] = {Wd.x, Wd.y};
+#pragma unroll
+      for (int wi = 0; wi < 2; ++wi) {
+#pragma unroll
+        for (int bp = 0; bp < 2; ++bp) {
+          const uint32_t sel = bp ? 0x7632u : 0x5410u;
+          const uint32_t XA = prmt(wa[wi], wb[wi], sel), XB = prmt(wc[wi], wd[wi], sel);
+          const uint32_t XA2 = XA >> 8, XB2 = XB >> 8;
+          const int mt = 4 * wi + 2 * bp;
+          // low nibble -> output row g, high nibble -> output row g + 8
+          mma_f16_16816(oacc[mt], v4_field<0>(XA), v4_field<4>(XA), v4_field<0>(XB), v4_field<4>(XB), B0, B1);
+          mma_f16_16816(oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), B0, B1);
+        }
+      }
+    }
+
+    __syncwarp();
+    if (it + T4::kStages < my_n) {
+      issue(it + T4::kStages, next_blk);
+      if (it + T4::kStages + 1 < my_n) next_blk = bt_row[pg_begin + warp + (it + T4::kStages + 1) * kScanWarps];
+    }
+  }
+
+  if (failed && lane == 0) atomicExch(p.status, JF_ERR_TIMEOUT);
+
+  __syncthreads();
+  {
+    float* wo = reinterpret_cast<float*>(smem) + warp * (kHeadsPad * JF_HEAD_DIM);
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      const int wi = mt >> 2, bp = (mt >> 1) & 1, e = mt & 1;
+      const int dlo = 16 * g + 8 * wi + 4 * bp + 2 * e + 1;  // low nibble of the byte: odd channel
+      const int dhi = dlo - 1;                               // high nibble: even channel
+      wo[(2 * tig) * JF_HEAD_DIM + dlo] = oacc[mt][0];
+      wo[(2 * tig + 1) * JF_HEAD_DIM + dlo] = oacc[mt][1];
+      wo[(2 * tig) * JF_HEAD_DIM + dhi] = oacc[mt][2] * 0.0625f;
+      wo[(2 * tig + 1) * JF_HEAD_DIM + dhi] = oacc[mt][3] * 0.0625f;
+    }
+  }
+  cta_merge_store(p, smem, l0, l1, m_ref0, m_ref1, 0.f, 0.f, split, hkv, b);
+}
+
+// ---- tensor maps -----------------------------------------------------------------------
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeFn>(sym);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  uint64_t rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.base) ^ (std::hash<uint64_t>()(k.rows) * 1000003u);
+  }
+};
+
+// (rows x 64 bytes) view of a packed tensor, box = one 16-row page, 64-byte swizzle.
+jf_status_t page_map(const void* base, uint64_t rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  const MapKey key{base, rows};
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return JF_OK; }
+  EncodeFn fn = encode_fn();
+  if (!fn) return JF_ERR_CUDA;
+  const cuuint64_t dims[2] = {64, rows};
+  const cuuint64_t strides[1] = {64};
+  const cuuint32_t box[2] = {64, 16};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = static_cast<int32_t>(r); return JF_ERR_CUDA; }
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return JF_OK;
+}
+
+}  // namespace
+
+jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaStream_t stream) {
+  const uint64_t rows = static_cast<uint64_t>(sp.H_kv) * static_cast<uint64_t>(sp.num_slots);
+  if (rows > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
+  CUtensorMap k_map, v_map;
+  jf_status_t st = page_map(sp.k_data, rows, &k_map);
+  if (st != JF_OK) return st;
+  st = page_map(sp.v_data, rows, &v_map);
+  if (st != JF_OK) return st;
+  const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + 1024;
+  static_assert(kScanWarps * T4::kStages * T4::kBytes >= kMergeBytes, "merge buffer");
+  if (q_dtype == JF_DTYPE_BF16) {
+    JF_CUDA_TRY(cudaFuncSetAttribute(scan_k4v4_kernel<JF_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    scan_k4v4_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp, k_map, v_map);
+  } else {
+    JF_CUDA_TRY(cudaFuncSetAttribute(scan_k4v4_kernel<JF_DTYPE_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    scan_k4v4_kernel<JF_DTYPE_FP16><<<grid, kScanWarps * 32, smem, stream>>>(sp, k_map, v_map);
+  }
+  JF_CUDA_TRY(cudaGetLastError());
+  return JF_OK;
+}
+
+}  // namespace jf

@@ -35,6 +35,7 @@ struct TopkParams {
   const int32_t* seq_lens;
   int64_t* topk_idx;
   int64_t* topk_slots;
+  float* sel_canon;
   int64_t num_slots;
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
   float attn_scale;
@@ -138,8 +139,9 @@ topk_select_kernel(const TopkParams p) {
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
   int64_t* out_idx = p.topk_idx + bh * K;
   int64_t* out_slot = p.topk_slots + bh * K;
+  float* out_canon = p.sel_canon + bh * K;
   if (n <= 0) {
-    for (int r = tid; r < K; r += kTopkThreads) { out_idx[r] = -1; out_slot[r] = -1; }
+    for (int r = tid; r < K; r += kTopkThreads) { out_idx[r] = -1; out_slot[r] = -1; out_canon[r] = -INFINITY; }
     return;
   }
 
@@ -312,12 +314,15 @@ topk_select_kernel(const TopkParams p) {
   const int m = min(ncand, K);
   for (int r = tid; r < K; r += kTopkThreads) {
     int64_t idx = -1, slot = -1;
+    float canon = -INFINITY;
     if (r < m) {
       idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
       slot = slot_of(ctx, static_cast<int>(idx));
+      canon = float_from_order_key(static_cast<uint32_t>(keys[r] >> 32));
     }
     out_idx[r] = idx;
     out_slot[r] = slot;
+    out_canon[r] = canon;
   }
 }
 
@@ -333,13 +338,13 @@ extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t strea
   if (st != JF_OK) return st;
   if (!a->topk_idx || !a->topk_slots) return JF_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, true);
+  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   TopkParams tp{};
   tp.scores = a->scores ? a->scores : ws.scores;
   tp.part_m = ws.part_m; tp.part_smax = ws.part_smax;
   tp.q = a->q; tp.k_data = a->k_data; tp.k_scales = static_cast<const uint16_t*>(a->k_scales);
   tp.block_table = a->block_table; tp.seq_lens = a->seq_lens;
-  tp.topk_idx = a->topk_idx; tp.topk_slots = a->topk_slots;
+  tp.topk_idx = a->topk_idx; tp.topk_slots = a->topk_slots; tp.sel_canon = ws.sel_canon;
   tp.num_slots = a->num_slots;
   tp.B = a->B; tp.H_q = a->H_q; tp.H_kv = a->H_kv; tp.G = a->H_q / a->H_kv;
   tp.max_S = a->max_S; tp.max_blocks = a->max_blocks;

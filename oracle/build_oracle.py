@@ -1,0 +1,94 @@
+"""Build the oracle's native pieces (test infrastructure, never the product).
+
+* ``oracle/_build/libjf_oracle_c.so`` -- the C restatement in ``oracle/jf_oracle_c.c``.
+* ``oracle/_ref/jetfire_cpu_topk_attn_ref_<isa>.so`` -- the reference's own host
+  correction, ``jetfire_vllm/csrc/cpu_topk_attn.cpp``, compiled UNMODIFIED from where it
+  lies in the read-only reference checkout with the flags of its loader
+  (``jetfire_vllm/kernels/cpu_topk_attn.py:41-52``) except ``-march=native``, which is
+  replaced by explicit ISA sets so that the binary can run on another host: ``avx512bf16``
+  (the reference's SIMD path) and ``avx2`` (its scalar template, auto-vectorised).
+  Built only where the checkout exists; outputs are git-ignored and travel with the tree.
+
+    python -m oracle.build_oracle [reference_root]
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+BUILD = HERE / "_build"
+REF_OUT = HERE / "_ref"
+C_LIB = BUILD / "libjf_oracle_c.so"
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+
+ISA_FLAGS = {
+    "avx512bf16": ["-mavx512f", "-mavx512bw", "-mavx512vl", "-mavx512dq", "-mavx512bf16", "-mavx2", "-mfma",
+                   "-mf16c", "-mbmi2"],
+    "avx2": ["-mavx2", "-mfma", "-mf16c"],
+}
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("command failed: " + " ".join(map(str, cmd)) + "\n" + r.stdout[-4000:])
+
+
+def build_c(force: bool = False) -> Path:
+    src = HERE / "jf_oracle_c.c"
+    if not force and C_LIB.exists() and C_LIB.stat().st_mtime >= src.stat().st_mtime:
+        return C_LIB
+    BUILD.mkdir(exist_ok=True)
+    _run(["gcc", "-O2", "-fopenmp", "-ffp-contract=off", "-fPIC", "-shared", str(src), "-o", str(C_LIB), "-lm"])
+    return C_LIB
+
+
+def ref_module_path(isa: str) -> Path:
+    return REF_OUT / f"jetfire_cpu_topk_attn_ref_{isa}.so"
+
+
+def build_ref(ref_root: str | Path = "/root/reference", force: bool = False) -> list[Path]:
+    src = Path(ref_root) / "jetfire_vllm" / "csrc" / "cpu_topk_attn.cpp"
+    if not src.exists():
+        return [ref_module_path(i) for i in ISA_FLAGS if ref_module_path(i).exists()]
+    from torch.utils.cpp_extension import include_paths, library_paths
+    import torch
+    REF_OUT.mkdir(exist_ok=True)
+    incs = [f"-I{p}" for p in include_paths()] + [f"-I{sysconfig.get_paths()['include']}", f"-I{CUDA_HOME}/include"]
+    libdirs = library_paths() + [str(CUDA_HOME / "lib64"), str(CUDA_HOME / "lib64" / "stubs")]
+    outs, procs = [], []
+    for isa, flags in ISA_FLAGS.items():
+        out = ref_module_path(isa)
+        outs.append(out)
+        if not force and out.exists():
+            continue
+        name = out.name[:-3]
+        cmd = ["g++", "-O3", "-std=c++17", "-fopenmp", "-ffast-math", "-fPIC", "-shared", *flags,
+               f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+               f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+               *incs, str(src), "-o", str(out),
+               *[f"-L{d}" for d in libdirs], *[f"-Wl,-rpath,{d}" for d in libdirs[:-1]],
+               "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+               "-lcudart", "-lcuda", "-fopenmp"]
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for cmd, p in procs:
+        out_text, _ = p.communicate()
+        if p.returncode != 0:
+            raise RuntimeError("reference build failed: " + " ".join(cmd) + "\n" + out_text[-4000:])
+    return outs
+
+
+def build_all() -> None:
+    build_c()
+    build_ref()
+
+
+if __name__ == "__main__":
+    build_c(force=True)
+    print(C_LIB)
+    for p in build_ref(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True):
+        print(p)

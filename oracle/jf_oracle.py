@@ -460,6 +460,9 @@ def decode_step(mode: str, q, k_data, k_scales, v_data, v_scales, block_table, s
         n = int(min(int(seq_lens[b]), max_s))
         sl = slots_of(block_table, b, n)
         sc_b = np.zeros((h_q, n), np.float32)
+        if n == 0:  # padded / inactive row: nothing selected, zero outputs
+            res["scores"].append(sc_b)
+            continue
         for hk in range(h_kv):
             kd, ks = k_data[hk, sl], k_scales[hk, sl]
             vd, vs = v_data[hk, sl], v_scales[hk, sl]

@@ -48,7 +48,10 @@ def check_case(case: Case, top_k: int):
     for b in range(case.B):
         n = min(int(case.seq_lens[b]), case.ctx)
         assert np.isneginf(sc[b, :, n:]).all()
-        if n:
+        if n and case.mode == "k4v4":
+            # integer MMA + a fixed fp32 rescale order: bit-equal to the oracle
+            assert np.array_equal(sc[b, :, :n], ref["scores"][b]), "K4 scores are not bit-exact"
+        elif n:
             assert np.abs(sc[b, :, :n] - ref["scores"][b]).max() < 2e-2
     _close(res.o_hat.cpu().numpy(), ref["o_hat"], "o_hat")
     _close(res.o_old_unnorm.cpu().numpy(), ref["o_old_unnorm"], "o_old_unnorm")
@@ -73,6 +76,29 @@ def check_case(case: Case, top_k: int):
 ])
 def test_k3v2_matches_oracle(B, H_q, H_kv, ctx, top_k, seed):
     check_case(Case("k3v2", B, H_q, H_kv, ctx, seed=seed), top_k)
+
+
+@pytest.mark.parametrize("B,H_q,H_kv,ctx,top_k,seed", [
+    (2, 8, 2, 512, 256, 31),
+    (1, 32, 8, 4096, 256, 32),
+    (4, 16, 2, 2048, 128, 33),
+    (2, 4, 4, 1024, 64, 34),
+])
+def test_k4v4_matches_oracle(B, H_q, H_kv, ctx, top_k, seed):
+    case = Case("k4v4", B, H_q, H_kv, ctx, seed=seed)
+    res, ref = check_case(case, top_k)
+    # distance to the reference's INT8-P Stage B (batch > 1 release plan), for the record
+    ref8 = case.oracle_step(top_k, stage_b="int8p", with_correction=False)
+    d8 = np.abs(res.o_hat.cpu().numpy() - ref8["o_hat"]).max()
+    d32 = np.abs(res.o_hat.cpu().numpy() - ref["o_hat"]).max()
+    print(f"k4v4 o_hat max-abs: vs fp32 oracle {d32:.2e}, vs INT8-P oracle {d8:.2e}")
+    assert d8 < 3e-3 + 1e-9   # the reference's own tolerance between its two Stage B variants
+
+
+def test_k4v4_short_and_ragged():
+    case = Case("k4v4", 4, 8, 2, 512, lens=[0, 1, 17, 512], seed=35)
+    check_case(case, 32)
+    check_case(Case("k4v4", 3, 32, 4, 512, lens=[17, 257, 512], seed=36, dtype=torch.float16), 256)
 
 
 def test_k3v2_fp16_inputs():

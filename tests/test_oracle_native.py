@@ -1,0 +1,87 @@
+"""The oracle's native pieces agree with the numpy restatement, and the host correction
+(product C++ vs the reference's own cpu_topk_attn.cpp compiled unmodified vs numpy)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import jf_oracle as O
+from oracle import native
+from jf_testlib import Case, f32_values
+
+
+@pytest.mark.parametrize("mode,seed", [("k3v2", 3), ("k4v4", 4)])
+def test_c_restatement_equals_numpy(mode, seed):
+    case = Case(mode, 3, 8, 2, 700, lens=[700, 0, 333], seed=seed)
+    ref = case.oracle_step(64, with_correction=False)
+    kd, ks, vd, vs = case.oracle_cache()
+    c = native.c_decode(mode, f32_values(case.q), kd, ks, vd, vs, case.block_table.numpy(),
+                        case.seq_lens.numpy(), case.ctx, 64, case.attn_scale, n_threads=2, want_scores=True)
+    assert np.array_equal(c["topk_idx"], ref["topk_idx"])
+    assert np.array_equal(c["topk_slots"], ref["topk_slots"])
+    for b in range(case.B):
+        n = int(case.seq_lens[b])
+        assert np.array_equal(c["scores"][b][:, :n], ref["scores"][b])
+    np.testing.assert_allclose(c["o_hat"], ref["o_hat"], atol=2e-6)
+    np.testing.assert_allclose(c["o_old_unnorm"], ref["o_old_unnorm"], atol=2e-6)
+    np.testing.assert_allclose(c["W"], ref["W"], atol=2e-6)
+
+
+def _correction_inputs(dtype=torch.bfloat16, K=64):
+    case = Case("k3v2", 2, 8, 2, 512, seed=9, dtype=dtype)
+    g = torch.Generator().manual_seed(1)
+    slots = torch.randint(0, case.num_slots, (2, 8, K), generator=g, dtype=torch.int64)
+    slots[0, 0, 5:] = -1                 # mostly padded row
+    slots[1, 3, :] = -1                  # all invalid -> zeros
+    slots[1, 4, 7] = case.num_slots + 3  # out of range -> skipped
+    return case, slots
+
+
+def test_product_correction_matches_numpy_oracle():
+    from jetfire_b200 import ops
+    for dtype in (torch.bfloat16, torch.float16):
+        case, slots = _correction_inputs(dtype)
+        hm = torch.from_numpy(O.head_map(2, 8, 4, slots.shape[2]))
+        out = torch.full((2, 8, 128), 7.0, dtype=dtype)
+        flag = torch.zeros(1, dtype=torch.int64)
+        ops.set_cpu_attn_threads(3)
+        ops.cpu_topk_attn(case.q, case.k_full, case.v_full, hm, slots, out, case.attn_scale, flag)
+        assert int(flag[0]) == 1, "completion flag was not set"
+        want = O.bf16_bits_to_f32(O.cpu_correction(f32_values(case.q), f32_values(case.k_full),
+                                                   f32_values(case.v_full), hm.numpy(), slots.numpy(),
+                                                   case.attn_scale))
+        # the reference's own gate for this op: atol 2e-3, rtol 6e-3 (scripts/validate_runtime.py:178-191)
+        np.testing.assert_allclose(out.float().numpy(), want, atol=2e-3, rtol=6e-3)
+        assert bool((out[1, 3] == 0).all())
+
+
+def test_reference_correction_pins_oracle_and_product():
+    mod = native.ref_cpu_topk_attn_module()
+    if mod is None:
+        pytest.skip("reference extension not built on this machine")
+    from jetfire_b200 import ops
+    case, slots = _correction_inputs()
+    hm = torch.from_numpy(O.head_map(2, 8, 4, slots.shape[2]))
+    ref_out = torch.empty(2, 8, 128, dtype=torch.bfloat16)
+    mod.set_cpu_attn_threads(2)
+    mod.cpu_topk_attn(case.q, case.k_full, case.v_full, hm, slots, ref_out, case.attn_scale, None)
+    want = O.bf16_bits_to_f32(O.cpu_correction(f32_values(case.q), f32_values(case.k_full),
+                                               f32_values(case.v_full), hm.numpy(), slots.numpy(), case.attn_scale))
+    np.testing.assert_allclose(ref_out.float().numpy(), want, atol=2e-3, rtol=6e-3)
+    mine = torch.empty_like(ref_out)
+    ops.cpu_topk_attn(case.q, case.k_full, case.v_full, hm, slots, mine, case.attn_scale)
+    np.testing.assert_allclose(mine.float().numpy(), ref_out.float().numpy(), atol=2e-3, rtol=6e-3)
+
+
+def test_pool_submit_wait_and_single_flight():
+    from jetfire_b200 import ops, _lib
+    case, slots = _correction_inputs()
+    out = torch.empty(2, 8, 128, dtype=torch.bfloat16)
+    ops.set_cpu_attn_threads(2)
+    ops.cpu_topk_attn_submit(case.q, case.k_full, case.v_full, None, slots, out, case.attn_scale)
+    ops.cpu_topk_attn_wait(30000)
+    again = torch.empty_like(out)
+    ops.cpu_topk_attn(case.q, case.k_full, case.v_full, None, slots, again, case.attn_scale)
+    assert torch.equal(out, again)
+    assert _lib.lib.jf_pool_wait_timeout(0) == 0
+    with pytest.raises(RuntimeError):
+        ops.cpu_topk_attn(case.q.float(), case.k_full, case.v_full, None, slots, out, case.attn_scale)
