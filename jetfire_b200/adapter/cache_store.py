@@ -1,0 +1,70 @@
+"""Per-layer packed KV cache with its full-precision host mirror
+(jetfire_vllm/adapter/cache_store.py:193-359 for the layout, :686-759 for the append).
+
+Layout (unchanged from the reference): ``k_data (H_kv, num_slots, 128*kbits/8) u8``,
+``k_scales (H_kv, num_slots, 128/group) bf16``, the same for V, ``slot_filled (num_slots,)
+bool``; mirror ``k_shadow / v_shadow (H_kv, num_slots, 128)`` in host DRAM in the model's
+16-bit dtype.  ``num_slots = num_blocks * 16``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .config import JetFireConfig
+
+
+class JetFireCacheStore:
+    def __init__(self, *, num_blocks: int, num_kv_heads: int, head_dim: int, cfg: JetFireConfig,
+                 device, dtype=torch.bfloat16, shadow_enabled: bool = True, block_size: int = 16):
+        if head_dim != 128 or block_size != 16:
+            raise ValueError("the decode path is built for head_dim 128 and block_size 16")
+        self.cfg = cfg
+        self.block_size = block_size
+        self.num_blocks = int(num_blocks)
+        self.num_slots = self.num_blocks * block_size
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = head_dim
+        self.group_size = cfg.group_size
+        self.k_nbits, self.v_nbits = cfg.scheme.k_nbits, cfg.scheme.v_nbits
+        self.device = torch.device(device)
+        self.dtype = dtype
+        ng = head_dim // self.group_size
+        dev = dict(device=self.device)
+        self.k_data = torch.zeros(num_kv_heads, self.num_slots, head_dim * self.k_nbits // 8, dtype=torch.uint8, **dev)
+        self.v_data = torch.zeros(num_kv_heads, self.num_slots, head_dim * self.v_nbits // 8, dtype=torch.uint8, **dev)
+        self.k_scales = torch.zeros(num_kv_heads, self.num_slots, ng, dtype=torch.bfloat16, **dev)
+        self.v_scales = torch.zeros(num_kv_heads, self.num_slots, ng, dtype=torch.bfloat16, **dev)
+        self.slot_filled = torch.zeros(self.num_slots, dtype=torch.bool, **dev)
+        self.written_count = 0
+        self.shadow_enabled = bool(shadow_enabled)
+        if self.shadow_enabled:
+            self.k_shadow = torch.zeros(num_kv_heads, self.num_slots, head_dim, dtype=dtype)
+            self.v_shadow = torch.zeros(num_kv_heads, self.num_slots, head_dim, dtype=dtype)
+        else:
+            self.k_shadow = self.v_shadow = None
+
+    def write_slots(self, key_tok: torch.Tensor, value_tok: torch.Tensor, slot_idx: torch.Tensor) -> None:
+        """Append ``key_tok / value_tok (T, H_kv, 128)`` at ``slot_idx (T,)``: quantise into the
+        packed cache on the GPU and copy the rows into the host mirror.  Negative slots are
+        padding and are skipped on both sides (jetfire_vllm/kernels/fused_quant_write.py:150-152)."""
+        if key_tok.shape != value_tok.shape or key_tok.dim() != 3:
+            raise RuntimeError("write_slots: key/value must be (T, H_kv, 128) and match")
+        slot_idx = slot_idx.to(torch.int64)
+        ops.fused_quant_write_kv(key_tok, value_tok, slot_idx, self.k_data, self.k_scales, self.v_data,
+                                 self.v_scales, self.group_size, self.k_nbits, self.v_nbits)
+        valid = slot_idx >= 0
+        self.slot_filled[slot_idx[valid]] = True
+        self.written_count += int(key_tok.shape[0])
+        if self.shadow_enabled:
+            idx_cpu = slot_idx.to("cpu")                       # host sync, as in the reference's eager path
+            keep = idx_cpu >= 0
+            idx_cpu = idx_cpu[keep]
+            k_cpu = key_tok.to("cpu")[keep].transpose(0, 1).to(self.dtype)
+            v_cpu = value_tok.to("cpu")[keep].transpose(0, 1).to(self.dtype)
+            self.k_shadow.index_copy_(1, idx_cpu, k_cpu)
+            self.v_shadow.index_copy_(1, idx_cpu, v_cpu)
+
+    def flush_pending_writes(self) -> None:
+        """Appends are synchronous here; kept for interface parity (cache_store.py:1340-1387)."""
+        return None

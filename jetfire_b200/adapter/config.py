@@ -1,0 +1,104 @@
+"""Resolved configuration of the hot path (jetfire_vllm/adapter/config.py:34-60, 238-390).
+
+Only the two paper modes are registered; one code path, no experiment knobs.  Environment
+variables kept from the reference: ``JETFIRE_MODE``, ``JETFIRE_TOPK``, ``JETFIRE_GROUP_SIZE``,
+``JETFIRE_CPU_ATTN_THREADS``, ``JETFIRE_MAX_BATCH_SIZE``.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class QuantScheme:
+    name: str
+    k_nbits: int
+    v_nbits: int
+    k_asymmetric: bool = False
+    v_asymmetric: bool = False
+
+
+SYM_INT3K_SYM_INT2V = QuantScheme("SymInt3K_SymInt2V", 3, 2)
+SYM_INT4K_SYM_INT4V = QuantScheme("SymInt4K_SymInt4V", 4, 4)
+QUANT_SCHEMES = {s.name: s for s in (SYM_INT3K_SYM_INT2V, SYM_INT4K_SYM_INT4V)}
+
+# paper mode table (jetfire_vllm/bench/artifact_performance.py:45): name -> (scheme, group size)
+PAPER_MODES = {"k3v2": ("SymInt3K_SymInt2V", 64), "k4v4": ("SymInt4K_SymInt4V", 128)}
+SCHEME_TO_KERNEL_MODE = {"SymInt3K_SymInt2V": "k3v2", "SymInt4K_SymInt4V": "k4v4"}
+
+# top-k widths the release matrix offers (jetfire_vllm/adapter/release_policy.py:31-34),
+# limited to what this library builds
+SUPPORTED_TOP_K = (32, 64, 128, 256, 512, 1024, 2048)
+
+
+@dataclass(frozen=True)
+class JetFireConfig:
+    mode: str = "SymInt3K_SymInt2V"      # jetfire_vllm/adapter/config.py:166
+    top_k: int = 256                      # :260
+    group_size: int = 64                  # :261
+    cpu_attn_threads: int = 32            # :179
+    max_batch_size: int = 32
+    enabled: bool = True
+
+    @property
+    def scheme(self) -> QuantScheme:
+        return QUANT_SCHEMES[self.mode]
+
+    @property
+    def kernel_mode(self) -> str:
+        return SCHEME_TO_KERNEL_MODE[self.mode]
+
+
+_CONFIG: JetFireConfig | None = None
+
+
+def _int_env(name: str, default: int) -> int:
+    raw = os.environ.get(name)
+    if raw is None or raw.strip() == "":
+        return default
+    try:
+        return int(raw)
+    except ValueError as exc:
+        raise ValueError(f"{name} must be an integer, got {raw!r}") from exc
+
+
+def get_jetfire_config() -> JetFireConfig:
+    """Environment -> config, cached (jetfire_vllm/adapter/config.py:300-390)."""
+    global _CONFIG
+    if _CONFIG is not None:
+        return _CONFIG
+    mode = os.environ.get("JETFIRE_MODE", "SymInt3K_SymInt2V")
+    group_default = 64
+    if mode in PAPER_MODES:                      # accept the paper's short names too
+        mode, group_default = PAPER_MODES[mode]
+    elif mode == "SymInt4K_SymInt4V":
+        group_default = 128
+    if mode not in QUANT_SCHEMES:
+        raise ValueError(f"JETFIRE_MODE={mode!r} is not built; choose one of {sorted(QUANT_SCHEMES)}")
+    group = _int_env("JETFIRE_GROUP_SIZE", group_default)
+    want = 64 if mode == "SymInt3K_SymInt2V" else 128
+    if group != want:
+        raise ValueError(f"{mode} is built for group size {want}, got JETFIRE_GROUP_SIZE={group}")
+    top_k = _int_env("JETFIRE_TOPK", 256)
+    if top_k not in SUPPORTED_TOP_K:
+        raise ValueError(f"JETFIRE_TOPK={top_k} must be one of {SUPPORTED_TOP_K}")
+    threads = _int_env("JETFIRE_CPU_ATTN_THREADS", 32)
+    if threads <= 0:
+        raise ValueError("JETFIRE_CPU_ATTN_THREADS must be positive")
+    _CONFIG = JetFireConfig(mode=mode, top_k=top_k, group_size=group, cpu_attn_threads=threads,
+                            max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32))
+    return _CONFIG
+
+
+def reset_jetfire_config() -> None:
+    global _CONFIG
+    _CONFIG = None
+
+
+def compute_inflate_ratio(scheme: QuantScheme, group_size: int = 128) -> float:
+    """bf16 KV bytes / packed KV bytes (jetfire_vllm/adapter/config.py:409-425): 5.8x for
+    K3V2 at group 64, 3.9x for K4V4 at group 128."""
+    def bits(n):
+        return n + 16.0 / group_size
+    return 32.0 / (bits(scheme.k_nbits) + bits(scheme.v_nbits))

@@ -1,0 +1,144 @@
+"""Decode orchestrator (jetfire_vllm/adapter/decode_path.py:1156-1182, 400-408, 1667-1712,
+and the op order of ``_decode_batched`` :1712-3237):
+
+    fused scan + top-k + finish (GPU)  ->  D2H of q and the selected slots  ->  host
+    correction over the mirror (C++ worker pool)  ->  o_new to the GPU  ->  merge into the
+    caller's output.
+
+The reference's Stage A / Stage B pair is one fused call here, so nothing is left to overlap
+the host correction with inside a layer; across layers the caller may pipeline.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+
+from .. import ops
+from .cache_store import JetFireCacheStore
+from .config import SUPPORTED_TOP_K, JetFireConfig, get_jetfire_config
+
+_HEAD_MAP_CPU: dict[tuple[int, int, int, int], torch.Tensor] = {}
+
+
+def _get_head_map_cpu(B: int, H_q: int, num_groups: int, K: int) -> torch.Tensor:
+    """(B, H_q, K) int64 head map for the host gather: entry = h_q // num_groups."""
+    key = (B, H_q, num_groups, K)
+    out = _HEAD_MAP_CPU.get(key)
+    if out is None:
+        hm = (torch.arange(H_q, dtype=torch.int64) // num_groups).unsqueeze(1).expand(H_q, K)
+        out = hm.unsqueeze(0).expand(B, H_q, K).contiguous()
+        _HEAD_MAP_CPU[key] = out
+    return out
+
+
+def _select_top_k(config_top_k: int, seq_len: int, supported: tuple[int, ...]) -> int | None:
+    """Largest supported width <= the sequence length (short sequences are padded with -1),
+    else the smallest configured width; None for empty sequences or nothing configured."""
+    requested, length = int(config_top_k), int(seq_len)
+    configured = [k for k in supported if 0 < k <= requested]
+    if not configured or length <= 0:
+        return None
+    candidates = [k for k in configured if k <= length]
+    return max(candidates) if candidates else min(configured)
+
+
+def _decode_unsupported(*, impl, layer, query, attn_metadata, cfg: JetFireConfig, store) -> str | None:
+    """Gate: a reason string on a miss, None on a hit (decode_path.py:1667-1695)."""
+    if not cfg.enabled:
+        return "pool_disabled"
+    if attn_metadata is None:
+        return "profiling_run"
+    if getattr(getattr(impl, "attn_type", None), "name", "DECODER") != "DECODER":
+        return "attn_type"
+    if getattr(attn_metadata, "use_cascade", False):
+        return "cascade"
+    if int(attn_metadata.max_query_len) != 1:
+        return "prefill_or_multi_query"
+    n_seqs = int(attn_metadata.seq_lens.numel())
+    if int(attn_metadata.num_actual_tokens) != n_seqs:
+        return "batch_mismatch"
+    if int(query.shape[0]) < n_seqs:
+        return "empty_query"
+    if store is None:
+        return "layer_config_missing"
+    if int(query.shape[-1]) != store.head_dim:
+        return "head_dim_mismatch"
+    if int(layer.num_heads) % int(layer.num_kv_heads) != 0 or int(layer.num_heads) // int(layer.num_kv_heads) > 8:
+        return "gqa_ratio"
+    return None
+
+
+class _DecodeBuffers:
+    """Pinned staging for one (batch, heads, top_k) shape."""
+
+    def __init__(self, B, H_q, K, dtype):
+        self.q_host = torch.empty(B, H_q, 128, dtype=dtype).pin_memory()
+        self.ts_host = torch.empty(B, H_q, K, dtype=torch.int64).pin_memory()
+        self.o_new_host = torch.empty(B, H_q, 128, dtype=dtype).pin_memory()
+
+
+_BUFFERS: dict[tuple, _DecodeBuffers] = {}
+
+
+def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table: torch.Tensor,
+                   seq_lens: torch.Tensor, max_seq_len: int, num_heads: int, scale: float,
+                   output: torch.Tensor, cfg: JetFireConfig | None = None) -> torch.Tensor | None:
+    """One decode step of one layer.  ``query (B, H_q, 128)``, ``output (B, H_q, 128)`` (a view
+    of the caller's buffer, written in place).  Returns ``output``, or None when the
+    configured top-k cannot be served."""
+    cfg = cfg or get_jetfire_config()
+    B = int(seq_lens.numel())
+    top_k = _select_top_k(cfg.top_k, int(max_seq_len), SUPPORTED_TOP_K)
+    if top_k is None:
+        return None
+    store.flush_pending_writes()
+    q = query[:B].contiguous()
+    bt = block_table if block_table.dtype == torch.int64 else block_table.to(torch.int64)
+    lens = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
+    max_S = min(int(bt.shape[1]) * store.block_size, ((int(max_seq_len) + 15) // 16) * 16)
+    res = ops.fused_attn_topk(cfg.kernel_mode, q, store.k_data, store.k_scales, store.v_data, store.v_scales,
+                              bt, lens, max_S, num_heads, store.num_kv_heads, store.block_size, top_k, scale)
+    key = (B, num_heads, top_k, q.dtype)
+    buf = _BUFFERS.get(key)
+    if buf is None:
+        buf = _BUFFERS[key] = _DecodeBuffers(B, num_heads, top_k, q.dtype)
+    buf.q_host.copy_(q, non_blocking=True)
+    buf.ts_host.copy_(res.topk_slots, non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    ops.set_cpu_attn_threads(cfg.cpu_attn_threads)
+    ops.cpu_topk_attn(buf.q_host, store.k_shadow, store.v_shadow, None, buf.ts_host, buf.o_new_host, scale)
+    o_new = buf.o_new_host.to(q.device, non_blocking=True)
+    out_view = output[:B].view(B, num_heads, 128)
+    if out_view.is_contiguous():
+        ops.blend_unnorm_into(res.o_hat, res.o_old_unnorm, res.W, o_new, out_view)
+    else:
+        tmp = torch.empty(B, num_heads, 128, dtype=q.dtype, device=q.device)
+        ops.blend_unnorm_into(res.o_hat, res.o_old_unnorm, res.W, o_new, tmp)
+        out_view.copy_(tmp)
+    return output
+
+
+def try_jetfire_decode(*, impl, layer, query, attn_metadata, output, store=None, cfg=None,
+                       key=None, value=None):
+    """Decode entry with the reference's calling convention (decode_path.py:1699-1712):
+    returns ``output`` on success, None when a precondition fails (the caller then uses its
+    native attention)."""
+    cfg = cfg or get_jetfire_config()
+    if _decode_unsupported(impl=impl, layer=layer, query=query, attn_metadata=attn_metadata,
+                           cfg=cfg, store=store) is not None:
+        return None
+    n = int(attn_metadata.seq_lens.numel())
+    q = query[:n].view(n, int(layer.num_heads), int(layer.head_size))
+    return decode_batched(store=store, query=q, block_table=attn_metadata.block_table,
+                          seq_lens=attn_metadata.seq_lens, max_seq_len=int(attn_metadata.max_seq_len),
+                          num_heads=int(layer.num_heads), scale=float(impl.scale), output=output, cfg=cfg)
+
+
+def make_decode_metadata(seq_lens: torch.Tensor, block_table: torch.Tensor) -> SimpleNamespace:
+    """Stand-in for vLLM's decode metadata (the reference builds the same kind of object for
+    its sub-batches, decode_path.py:1532-1544)."""
+    n = int(seq_lens.numel())
+    return SimpleNamespace(seq_lens=seq_lens, max_seq_len=int(seq_lens.max().item()) if n else 0,
+                           max_query_len=1, num_actual_tokens=n, block_table=block_table,
+                           use_cascade=False, query_start_loc=torch.arange(n + 1, dtype=torch.int32))

@@ -1,0 +1,77 @@
+"""Attention-backend shim (jetfire_vllm/adapter/jetfire_backend.py:66-229).
+
+vLLM's classes are imported lazily and only here, so the rest of the package works without
+vLLM.  ``JetFireAttentionImplMixin`` holds the routing (decode -> ``try_jetfire_decode``,
+append -> ``JetFireCacheStore.write_slots``); ``make_backend()`` binds it to the vLLM
+FlashAttention classes of the installed version and returns the backend class to register
+as ``CUSTOM`` (``register_backend(AttentionBackendEnum.CUSTOM, ...)``, reference
+jetfire_vllm/adapter/registry.py:19, :61).
+"""
+from __future__ import annotations
+
+from .cache_store import JetFireCacheStore
+from .config import get_jetfire_config
+from .decode_path import try_jetfire_decode
+
+_STORES: dict[str, JetFireCacheStore] = {}
+
+
+def get_layer_store(layer_name: str) -> JetFireCacheStore | None:
+    return _STORES.get(layer_name)
+
+
+def register_layer_store(layer_name: str, store: JetFireCacheStore) -> None:
+    _STORES[layer_name] = store
+
+
+class JetFireAttentionImplMixin:
+    """forward / do_kv_cache_update with the reference's signatures."""
+
+    def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None,
+                output_scale=None, output_block_scale=None):
+        store = get_layer_store(getattr(layer, "layer_name", ""))
+        if output is not None and attn_metadata is not None:
+            done = try_jetfire_decode(impl=self, layer=layer, query=query, attn_metadata=attn_metadata,
+                                      output=output, store=store, cfg=get_jetfire_config())
+            if done is not None:
+                return done
+        return super().forward(layer, query, key, value, kv_cache, attn_metadata, output=output,
+                               output_scale=output_scale, output_block_scale=output_block_scale)
+
+    def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping) -> None:
+        store = get_layer_store(getattr(layer, "layer_name", ""))
+        if store is not None:
+            n = int(slot_mapping.shape[0])
+            store.write_slots(key[:n].view(n, store.num_kv_heads, store.head_dim),
+                              value[:n].view(n, store.num_kv_heads, store.head_dim), slot_mapping)
+        parent = getattr(super(), "do_kv_cache_update", None)
+        if parent is not None:
+            parent(layer, key, value, kv_cache, slot_mapping)
+
+
+def make_backend():
+    """Bind the mixin to the installed vLLM's FlashAttention backend.  Raises ImportError
+    with a clear message when vLLM (or the expected classes) is unavailable."""
+    try:
+        from vllm.v1.attention.backends.flash_attn import (FlashAttentionBackend, FlashAttentionImpl,
+                                                           FlashAttentionMetadataBuilder)
+    except Exception as exc:  # pragma: no cover - depends on the installed vLLM
+        raise ImportError(f"vLLM FlashAttention backend classes not importable: {exc}") from exc
+
+    class JetFireAttentionImpl(JetFireAttentionImplMixin, FlashAttentionImpl):
+        pass
+
+    class JetFireAttentionBackend(FlashAttentionBackend):
+        @staticmethod
+        def get_name() -> str:
+            return "CUSTOM"
+
+        @staticmethod
+        def get_impl_cls():
+            return JetFireAttentionImpl
+
+        @staticmethod
+        def get_builder_cls():
+            return FlashAttentionMetadataBuilder
+
+    return JetFireAttentionBackend

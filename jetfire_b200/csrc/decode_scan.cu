@@ -350,10 +350,10 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
     const size_t smem = kScanWarps * T::kStages * (T::kBytes + 8 + 4);
     static_assert(kScanWarps * T::kStages * T::kBytes >= kMergeBytes, "merge buffer");
     if (a->q_dtype == JF_DTYPE_BF16) {
-      JF_CUDA_TRY(cudaFuncSetAttribute(scan_k3v2_kernel<JF_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_BF16>, smem);
       scan_k3v2_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
     } else {
-      JF_CUDA_TRY(cudaFuncSetAttribute(scan_k3v2_kernel<JF_DTYPE_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_FP16>, smem);
       scan_k3v2_kernel<JF_DTYPE_FP16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
     }
     JF_CUDA_TRY(cudaGetLastError());

@@ -354,10 +354,10 @@ jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaS
   const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + 1024;
   static_assert(kScanWarps * T4::kStages * T4::kBytes >= kMergeBytes, "merge buffer");
   if (q_dtype == JF_DTYPE_BF16) {
-    JF_CUDA_TRY(cudaFuncSetAttribute(scan_k4v4_kernel<JF_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_BF16>, smem);
     scan_k4v4_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp, k_map, v_map);
   } else {
-    JF_CUDA_TRY(cudaFuncSetAttribute(scan_k4v4_kernel<JF_DTYPE_FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_FP16>, smem);
     scan_k4v4_kernel<JF_DTYPE_FP16><<<grid, kScanWarps * 32, smem, stream>>>(sp, k_map, v_map);
   }
   JF_CUDA_TRY(cudaGetLastError());

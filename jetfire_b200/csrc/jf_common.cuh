@@ -6,6 +6,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/jetfire_b200.h"
 
 namespace jf {
@@ -22,6 +24,21 @@ inline jf_status_t cuda_fail(cudaError_t e) {
   do {                                                      \
     cudaError_t e__ = (expr);                               \
     if (e__ != cudaSuccess) return ::jf::cuda_fail(e__);    \
+  } while (0)
+
+// Raise a kernel's dynamic shared-memory limit once per device (not a stream operation,
+// so it is kept out of the steady-state launch path and out of stream captures).
+#define JF_ENSURE_SMEM(kernel, bytes)                                                          \
+  do {                                                                                         \
+    static std::atomic<uint64_t> done__{0};                                                    \
+    int dev__ = 0;                                                                             \
+    JF_CUDA_TRY(cudaGetDevice(&dev__));                                                        \
+    const uint64_t bit__ = 1ull << (dev__ & 63);                                               \
+    if (!(done__.load(std::memory_order_acquire) & bit__)) {                                   \
+      JF_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                       static_cast<int>(bytes)));                              \
+      done__.fetch_or(bit__, std::memory_order_release);                                       \
+    }                                                                                          \
   } while (0)
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -355,11 +355,11 @@ extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t strea
   tp.q_dtype = a->q_dtype;
   tp.attn_scale = a->attn_scale;
   const size_t smem = static_cast<size_t>(tp.sort_n) * 8 + kBins * 4 + JF_HEAD_DIM * 4 + 16 + JF_HEAD_DIM;
+  constexpr size_t kTopkMaxSmem = static_cast<size_t>(2 * JF_MAX_TOP_K) * 8 + kBins * 4 + JF_HEAD_DIM * 4 + 16 + JF_HEAD_DIM;
   dim3 grid(a->H_q, a->B);
 #define JF_TOPK(MODE, DT)                                                                              \
   do {                                                                                                 \
-    JF_CUDA_TRY(cudaFuncSetAttribute(topk_select_kernel<MODE, DT>,                                     \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));         \
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT>), kTopkMaxSmem);                                      \
     topk_select_kernel<MODE, DT><<<grid, kTopkThreads, smem, stream>>>(tp);                            \
   } while (0)
   if (a->mode == JF_MODE_K3V2) {

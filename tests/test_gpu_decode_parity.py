@@ -92,7 +92,11 @@ def test_k4v4_matches_oracle(B, H_q, H_kv, ctx, top_k, seed):
     d8 = np.abs(res.o_hat.cpu().numpy() - ref8["o_hat"]).max()
     d32 = np.abs(res.o_hat.cpu().numpy() - ref["o_hat"]).max()
     print(f"k4v4 o_hat max-abs: vs fp32 oracle {d32:.2e}, vs INT8-P oracle {d8:.2e}")
-    assert d8 < 3e-3 + 1e-9   # the reference's own tolerance between its two Stage B variants
+    # The INT8-P variant is itself an approximation of the fp32 one (the reference allows 3e-3
+    # between them on its N(0,1) validation inputs, scripts/validate_runtime.py:173-175); this
+    # build follows the fp32 arithmetic, so it must sit closer to fp32 than INT8-P does.
+    d_ref = np.abs(ref8["o_hat"] - ref["o_hat"]).max()
+    assert d32 <= max(d_ref, 2e-3) and d8 < 1e-2
 
 
 def test_k4v4_short_and_ragged():
