@@ -18,13 +18,19 @@ __host__ __device__ inline ModeInfo mode_info(int mode) {
   return ModeInfo{3, 2, 64, 2, 48, 32};
 }
 
-// How many splits of the page range one (b, h_kv) pair is cut into.  Depends only on
-// (B, H_kv, max_S) so that the workspace query and every launch agree.
-__host__ __device__ inline int scan_splits(int B, int H_kv, int max_S) {
+// Resident scan CTAs per SM (set by registers / shared memory of the kernel variant).
+__host__ __device__ inline int scan_ctas_per_sm(int mode, int q_dtype) {
+  return (mode == JF_MODE_K4V4 || q_dtype == JF_DTYPE_FP16) ? 3 : 4;
+}
+
+// How many splits of the page range one (b, h_kv) pair is cut into: as many as fit in ONE
+// wave of resident CTAs (a second, partial wave would idle most of the GPU), but at least
+// two pages per warp.  Depends only on its arguments, so every launch agrees.
+__host__ __device__ inline int scan_splits(int mode, int q_dtype, int B, int H_kv, int max_S) {
   const int pages = (max_S + JF_BLOCK_SIZE - 1) / JF_BLOCK_SIZE;
   const int pairs = B * H_kv;
-  int target = (kNumSMs * 4 + pairs - 1) / pairs;  // about four resident CTAs per SM
-  int cap = pages / 8;                             // at least two pages per warp
+  int target = (kNumSMs * scan_ctas_per_sm(mode, q_dtype)) / pairs;
+  int cap = pages / 8;
   if (cap < 1) cap = 1;
   if (target > cap) target = cap;
   if (target > 512) target = 512;
@@ -45,8 +51,9 @@ struct Workspace {
 
 __host__ __device__ inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
-inline Workspace carve_workspace(void* base, int B, int H_q, int H_kv, int max_S, int top_k, bool need_scores) {
-  const uint64_t splits = scan_splits(B, H_kv, max_S);
+// Sized for the variant with the most splits (bf16 query), so one workspace serves both dtypes.
+inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv, int max_S, int top_k, bool need_scores) {
+  const uint64_t splits = scan_splits(mode, JF_DTYPE_BF16, B, H_kv, max_S);
   const uint64_t pairs = static_cast<uint64_t>(B) * H_kv * splits;
   uint64_t off = 0;
   uint8_t* p = static_cast<uint8_t*>(base);

@@ -20,7 +20,9 @@ namespace jf {
 
 namespace {
 
-constexpr int kChunk = 128;
+constexpr int kFinishThreads = 256;
+constexpr int kFinishWarps = kFinishThreads / 32;
+constexpr int kChunk = 256;  // selected entries staged per round
 
 struct FinishParams {
   const float* scores;
@@ -42,27 +44,38 @@ struct FinishParams {
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k;
 };
 
+// One CTA per (query head, batch element).  The split merge is one thread per output
+// channel; the selected set is walked a warp per entry, lane l owning channels 4l..4l+3 so
+// that a V row is one coalesced 32- or 64-byte read.
 template <int MODE>
-__global__ void __launch_bounds__(JF_HEAD_DIM)
+__global__ void __launch_bounds__(kFinishThreads)
 decode_finish_kernel(const FinishParams p) {
   __shared__ int64_t sm_slot[kChunk];
   __shared__ float sm_wc[kChunk][2];   // canonical weight * v scale (per group)
   __shared__ float sm_dw[kChunk][2];   // (canonical - scan) weight * v scale
   __shared__ float sm_w[kChunk][2];    // canonical weight, weight difference
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  __shared__ float sm_red[kFinishWarps][JF_HEAD_DIM][2];
+  __shared__ float sm_sum[kFinishWarps][2];
+  __shared__ float sm_stat[2];         // merged reference point M, normaliser Z of the scan
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
   const int hkv = h / p.G, hi = h - hkv * p.G;
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
   const int n = min(p.seq_lens[b], p.max_S);
 
-  // ---- merge splits (unnormalised) ----
+  // ---- merge splits (unnormalised): thread d < 128 owns channel d ----
   const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
   float M = kMinusBig;
   for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.part_m[(pbase + s) * kHeadsPad + hi]);
-  float Z = 0.f, o = 0.f;
-  for (int s = 0; s < p.splits; ++s) {
-    const float w = ex2((p.part_m[(pbase + s) * kHeadsPad + hi] - M) * kLog2e);
-    Z = fmaf(p.part_l[(pbase + s) * kHeadsPad + hi], w, Z);
-    o = fmaf(p.part_o[((pbase + s) * kHeadsPad + hi) * JF_HEAD_DIM + d], w, o);
+  float o = 0.f;
+  if (tid < JF_HEAD_DIM) {
+    float Z = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float w = ex2((p.part_m[(pbase + s) * kHeadsPad + hi] - M) * kLog2e);
+      Z = fmaf(p.part_l[(pbase + s) * kHeadsPad + hi], w, Z);
+      o = fmaf(p.part_o[((pbase + s) * kHeadsPad + hi) * JF_HEAD_DIM + tid], w, o);
+    }
+    if (tid == 0) { sm_stat[0] = M; sm_stat[1] = Z; }
   }
 
   // ---- selected set: canonical weights, and their difference to the scan's ----
@@ -73,10 +86,12 @@ decode_finish_kernel(const FinishParams p) {
   const float* srow = p.scores + bh * p.max_S;
   const int64_t* sel = p.topk_idx + bh * p.top_k;
   const float* canon = p.sel_canon + bh * p.top_k;
-  float acc_old = 0.f, acc_dw = 0.f, wsum = 0.f, dz = 0.f;
+  float a_old[4] = {0.f, 0.f, 0.f, 0.f}, a_dw[4] = {0.f, 0.f, 0.f, 0.f};
+  float wsum = 0.f, dz = 0.f;
+  const int grp = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
   for (int k0 = 0; k0 < p.top_k; k0 += kChunk) {
     {
-      const int kk = k0 + d;
+      const int kk = k0 + tid;
       int64_t slot = -1;
       float wc = 0.f, dw = 0.f, vs0 = 0.f, vs1 = 0.f;
       if (kk < p.top_k && n > 0) {
@@ -97,41 +112,58 @@ decode_finish_kernel(const FinishParams p) {
           }
         }
       }
-      sm_slot[d] = slot;
-      sm_w[d][0] = wc; sm_w[d][1] = dw;
-      sm_wc[d][0] = wc * vs0; sm_wc[d][1] = wc * vs1;
-      sm_dw[d][0] = dw * vs0; sm_dw[d][1] = dw * vs1;
+      sm_slot[tid] = slot;
+      sm_w[tid][0] = wc; sm_w[tid][1] = dw;
+      sm_wc[tid][0] = wc * vs0; sm_wc[tid][1] = wc * vs1;
+      sm_dw[tid][0] = dw * vs0; sm_dw[tid][1] = dw * vs1;
     }
     __syncthreads();
     const int kend = min(kChunk, p.top_k - k0);
-    for (int j = 0; j < kend; ++j) {
+#pragma unroll 4
+    for (int j = warp; j < kend; j += kFinishWarps) {
       const int64_t slot = sm_slot[j];
-      if (slot < 0) continue;
-      int code;
+      if (slot < 0) continue;  // warp-uniform
+      float c[4];
       if (MODE == JF_MODE_K3V2) {
-        const uint32_t byte = __ldg(v_rows + slot * 32 + (d >> 2));
-        code = static_cast<int>((byte >> ((3 - (d & 3)) * 2)) & 3u) - 2;
+        const uint32_t byte = __ldg(v_rows + slot * 32 + lane);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) c[e] = static_cast<float>(static_cast<int>((byte >> ((3 - e) * 2)) & 3u) - 2);
       } else {
-        const uint32_t byte = __ldg(v_rows + slot * 64 + (d >> 1));
-        code = static_cast<int>((d & 1) ? (byte & 15u) : (byte >> 4)) - 8;
+        const uint32_t two = __ldg(reinterpret_cast<const uint16_t*>(v_rows + slot * 64) + lane);
+        c[0] = static_cast<float>(static_cast<int>((two >> 4) & 15u) - 8);
+        c[1] = static_cast<float>(static_cast<int>(two & 15u) - 8);
+        c[2] = static_cast<float>(static_cast<int>((two >> 12) & 15u) - 8);
+        c[3] = static_cast<float>(static_cast<int>((two >> 8) & 15u) - 8);
       }
-      const float cf = static_cast<float>(code);
-      acc_old = fmaf(sm_wc[j][d >> 6], cf, acc_old);
-      acc_dw = fmaf(sm_dw[j][d >> 6], cf, acc_dw);
+      const float fw = sm_wc[j][grp], fd = sm_dw[j][grp];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { a_old[e] = fmaf(fw, c[e], a_old[e]); a_dw[e] = fmaf(fd, c[e], a_dw[e]); }
       wsum += sm_w[j][0];
       dz += sm_w[j][1];
     }
     __syncthreads();
   }
-  Z += dz;
-  const bool live = (Z > 0.f) && (n > 0);
-  const float inv_z = live ? (1.0f / Z) : 0.f;
-  p.o_hat[bh * JF_HEAD_DIM + d] = (o + acc_dw) * inv_z;
-  p.o_old[bh * JF_HEAD_DIM + d] = acc_old * inv_z;
-  if (d == 0) {
-    p.W[bh] = wsum * inv_z;
-    if (p.softmax_m) p.softmax_m[bh] = live ? M : 0.f;
-    if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { sm_red[warp][4 * lane + e][0] = a_old[e]; sm_red[warp][4 * lane + e][1] = a_dw[e]; }
+  if (lane == 0) { sm_sum[warp][0] = wsum; sm_sum[warp][1] = dz; }
+  __syncthreads();
+  if (tid < JF_HEAD_DIM) {
+    float acc_old = 0.f, acc_dw = 0.f, ws = 0.f, dzs = 0.f;
+#pragma unroll
+    for (int w = 0; w < kFinishWarps; ++w) {
+      acc_old += sm_red[w][tid][0]; acc_dw += sm_red[w][tid][1];
+      ws += sm_sum[w][0]; dzs += sm_sum[w][1];
+    }
+    const float Z = sm_stat[1] + dzs;
+    const bool live = (Z > 0.f) && (n > 0);
+    const float inv_z = live ? (1.0f / Z) : 0.f;
+    p.o_hat[bh * JF_HEAD_DIM + tid] = (o + acc_dw) * inv_z;
+    p.o_old[bh * JF_HEAD_DIM + tid] = acc_old * inv_z;
+    if (tid == 0) {
+      p.W[bh] = ws * inv_z;
+      if (p.softmax_m) p.softmax_m[bh] = live ? M : 0.f;
+      if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
+    }
   }
 }
 
@@ -156,7 +188,7 @@ extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t str
   if (st != JF_OK) return st;
   if (!a->topk_idx || !a->o_hat || !a->o_old_unnorm || !a->W) return JF_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
+  Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   FinishParams fp{};
   fp.scores = a->scores ? a->scores : ws.scores;
   fp.sel_canon = ws.sel_canon;
@@ -168,11 +200,11 @@ extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t str
   fp.num_slots = a->num_slots;
   fp.B = a->B; fp.H_q = a->H_q; fp.H_kv = a->H_kv; fp.G = a->H_q / a->H_kv;
   fp.max_S = a->max_S; fp.max_blocks = a->max_blocks;
-  fp.splits = scan_splits(a->B, a->H_kv, a->max_S);
+  fp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
   fp.top_k = a->top_k;
   dim3 grid(a->H_q, a->B);
-  if (a->mode == JF_MODE_K3V2) decode_finish_kernel<JF_MODE_K3V2><<<grid, JF_HEAD_DIM, 0, stream>>>(fp);
-  else decode_finish_kernel<JF_MODE_K4V4><<<grid, JF_HEAD_DIM, 0, stream>>>(fp);
+  if (a->mode == JF_MODE_K3V2) decode_finish_kernel<JF_MODE_K3V2><<<grid, kFinishThreads, 0, stream>>>(fp);
+  else decode_finish_kernel<JF_MODE_K4V4><<<grid, kFinishThreads, 0, stream>>>(fp);
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
 }

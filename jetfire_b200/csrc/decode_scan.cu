@@ -28,9 +28,10 @@ namespace jf {
 
 namespace {
 
-// bit position at which code x (0..7) of an INT3 group is picked up, see unpack below
+// Bit position at which code x (0..7) of an INT3 group is picked up (see the unpack in the
+// kernel): the 3-bit field has to sit inside the 7-bit bf16 mantissa, i.e. at 0..4.
 __device__ __forceinline__ constexpr int k3_pos(int x) {
-  return x == 0 ? 3 : x == 1 ? 0 : x == 2 ? 7 : x == 3 ? 4 : x == 4 ? 1 : x == 5 ? 6 : x == 6 ? 3 : 0;
+  return x == 0 ? 0 : x == 1 ? 3 : x == 2 ? 0 : x == 3 ? 4 : x == 4 ? 1 : x == 5 ? 0 : x == 6 ? 3 : 0;
 }
 // bit position of 2-bit field f (0..7, bit offset 2f of a 16-bit half row word)
 __device__ __forceinline__ constexpr int v2_pos(int f) { return f <= 4 ? 2 * f : 2 * f - 10; }
@@ -38,13 +39,57 @@ __device__ __forceinline__ constexpr int v2_pos(int f) { return f <= 4 ? 2 * f :
 // 16-bit load, codes MSB-first inside a byte
 __device__ __forceinline__ constexpr int v2_dlocal(int f) { return 4 * (f >> 2) + 3 - (f & 3); }
 
+constexpr uint32_t kMagicBf16 = 0x43004300u;  // bf16 128.0 in both halves
+
+// Dequantised K in the reference's rounding, scaled by 2^POS:
+//   ((v & field) | 128) - (128 + 4 * 2^POS) == (code - 4) * 2^POS        exact in bf16
+//   bf16_rn(that * scale)                   == 2^POS * bf16(float(code - 4) * scale)
+// which is jetfire_vllm/csrc/int3_qk_scores.cu:94-99 (a power of two commutes with the
+// rounding); the 2^POS is undone by the query operand.
 template <int POS>
-__device__ __forceinline__ uint32_t k3_field(uint32_t v) {
-  // ((v & field) | 1024) - (1024 + 4 * 2^POS)  ==  (code - 4) * 2^POS, exact in fp16
+__device__ __forceinline__ uint32_t k3_field(uint32_t v, uint32_t scale2) {
   constexpr uint32_t m = (7u << POS) | (7u << (POS + 16));
-  constexpr uint32_t b = (0x6400u | (4u << POS)) * 0x10001u;
-  return hsub2_u32(and_or(v, m, kMagic), b);
+  constexpr uint32_t b = (0x4300u | (4u << POS)) * 0x10001u;
+  uint32_t t = and_or(v, m, kMagicBf16), d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(t) : "r"(t), "r"(b));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(t), "r"(scale2));
+  return d;
 }
+// One 32-bit word of each byte plane (4 INT3 groups = 32 channels of one row) -> 16 bf16x2
+// registers R[pair][code]: pair p holds groups (2p, 2p+1) in its (low, high) halves.
+__device__ __forceinline__ void k3_unpack_row(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t scale2,
+                                              uint32_t (&R)[2][8]) {
+#pragma unroll
+  for (int pr = 0; pr < 2; ++pr) {
+    const uint32_t sel = pr ? 0x7362u : 0x5140u;
+    const uint32_t lo = prmt(P2, P1, sel);  // halves: bits 15..0 of the two 24-bit groups
+    const uint32_t hi = prmt(P1, P0, sel);  // halves: bits 23..8
+    const uint32_t lo6 = lo >> 6, hi7 = hi >> 7, hi13 = hi >> 13;
+    R[pr][7] = k3_field<0>(lo, scale2);
+    R[pr][6] = k3_field<3>(lo, scale2);
+    R[pr][5] = k3_field<0>(lo6, scale2);
+    R[pr][4] = k3_field<1>(hi, scale2);
+    R[pr][3] = k3_field<4>(hi, scale2);
+    R[pr][2] = k3_field<0>(hi7, scale2);
+    R[pr][1] = k3_field<3>(hi7, scale2);
+    R[pr][0] = k3_field<0>(hi13, scale2);
+  }
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
 template <int POS>
 __device__ __forceinline__ uint32_t v2_field(uint32_t v) {
   constexpr uint32_t m = (3u << POS) | (3u << (POS + 16));
@@ -58,7 +103,7 @@ __device__ __forceinline__ uint32_t v2_field(uint32_t v) {
 // K3V2
 // ------------------------------------------------------------------------------------
 template <int DT>
-__global__ void __launch_bounds__(kScanWarps * 32, 4)
+__global__ void __launch_bounds__(kScanWarps * 32, (DT == JF_DTYPE_FP16) ? 3 : 4)
 scan_k3v2_kernel(const ScanParams p) {
   using T = Tile<JF_MODE_K3V2>;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -121,33 +166,40 @@ scan_k3v2_kernel(const ScanParams p) {
   int64_t next_blk = 0;
   if (T::kStages < my_n) next_blk = bt_row[pg_begin + warp + T::kStages * kScanWarps];
 
-  // ---- query fragments: B operand of the K MMA, scaled by 2^-pos of the code it meets ----
-  uint32_t qf[8][2];
+  // ---- query fragments: B operand of the K MMA, scaled by 2^-pos of the code it meets.
+  //      Lane (head n = g, tig) covers channels 32 tig + 8 j + x (group j, code x); k-step x
+  //      pairs groups (0,1) in b0 and (2,3) in b1.  A bf16 query is used as is; an fp16 query
+  //      (11-bit significand) is split exactly into two bf16 terms, hi + lo. ----
+  constexpr int kQTerms = (DT == JF_DTYPE_FP16) ? 2 : 1;
+  uint32_t qf[kQTerms][8][2];
   {
     const int h = hkv * p.G + g;
     const bool live = g < p.G;
     const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + h) * JF_HEAD_DIM;
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const int qh = ks >> 2, s = ks & 3;
+    for (int x = 0; x < 8; ++x) {
+      const float sc = 1.0f / static_cast<float>(1 << k3_pos(x));
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int x = 2 * s + half;
-        const int d0 = 64 * qh + 16 * tig + x;  // group j = 0
-        const int d1 = d0 + 8;                  // group j = 1
+        const int d0 = 32 * tig + 16 * half + x;  // group j = 2 * half
         float a = 0.f, c = 0.f;
-        if (live) { a = load_q<DT>(p.q, qbase + d0); c = load_q<DT>(p.q, qbase + d1); }
-        const float sc = 1.0f / static_cast<float>(1 << k3_pos(x));
-        qf[ks][half] = pack_f16x2_sat(a * sc, c * sc);
+        if (live) { a = load_q<DT>(p.q, qbase + d0) * sc; c = load_q<DT>(p.q, qbase + d0 + 8) * sc; }
+        const uint32_t hi2 = pack_bf16x2(a, c);
+        qf[0][x][half] = hi2;
+        if (kQTerms == 2) {
+          const float ra = a - __uint_as_float(hi2 << 16), rc = c - __uint_as_float(hi2 & 0xFFFF0000u);
+          qf[kQTerms - 1][x][half] = pack_bf16x2(ra, rc);
+        }
       }
     }
   }
+  const uint32_t ks_sel = (tig >> 1) ? 0x3232u : 0x1010u;  // this lane's K group scale, in both halves
 
   float oacc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
   float m_ref0 = kMinusBig, m_ref1 = kMinusBig, l0 = 0.f, l1 = 0.f;
-  float smax0 = 0.f, smax1 = 0.f;
+  uint32_t smax_bits = 0u;  // largest K group scale seen by this lane (bf16 bits; positive floats order as integers)
   bool failed = false;
 
   const int t0 = (g >> 1) | ((g & 1) << 2);  // token of MMA row g (rows g + 8 -> t0 + 8)
@@ -170,54 +222,37 @@ scan_k3v2_kernel(const ScanParams p) {
     const int pg = pg_begin + warp + it * kScanWarps;
 
     // ---------------- K: unpack + Q.K^T ----------------
-    float acc[2][4];
-#pragma unroll
-    for (int qh = 0; qh < 2; ++qh) {
-      acc[qh][0] = acc[qh][1] = acc[qh][2] = acc[qh][3] = 0.f;
-      uint32_t R[2][8];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const uint8_t* row = sp + T::kKOff + (t0 + 8 * r) * T::kKRow + 8 * qh + 2 * tig;
-        const uint32_t H0 = *reinterpret_cast<const uint16_t*>(row);
-        const uint32_t H1 = *reinterpret_cast<const uint16_t*>(row + 16);
-        const uint32_t H2 = *reinterpret_cast<const uint16_t*>(row + 32);
-        const uint32_t V0 = prmt(H2, H1, 0x5140);  // halves: bits 15..0 of the two 24-bit groups
-        const uint32_t V1 = prmt(H1, H0, 0x5140);  // halves: bits 23..8
-        const uint32_t V2 = V1 >> 10;              // halves (low 6 bits): bits 23..18
-        R[r][7] = k3_field<0>(V0);
-        R[r][6] = k3_field<3>(V0);
-        R[r][5] = k3_field<6>(V0);
-        R[r][4] = k3_field<1>(V1);
-        R[r][3] = k3_field<4>(V1);
-        R[r][2] = k3_field<7>(V1);
-        R[r][1] = k3_field<0>(V2);
-        R[r][0] = k3_field<3>(V2);
-      }
-#pragma unroll
-      for (int s = 0; s < 4; ++s)
-        mma_f16_16816(acc[qh], R[0][2 * s], R[1][2 * s], R[0][2 * s + 1], R[1][2 * s + 1],
-                      qf[qh * 4 + s][0], qf[qh * 4 + s][1]);
-    }
-
-    // ---------------- scores ----------------
-    const uint32_t ksw0 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + t0 * 4);
-    const uint32_t ksw1 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + (t0 + 8) * 4);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t ksw0 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + t0 * 4);
+    uint32_t ksw1 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + (t0 + 8) * 4);
     const uint32_t vsw0 = *reinterpret_cast<const uint32_t*>(sp + T::kVsOff + t0 * 4);
     const uint32_t vsw1 = *reinterpret_cast<const uint32_t*>(sp + T::kVsOff + (t0 + 8) * 4);
-    float ks00 = __uint_as_float(ksw0 << 16), ks01 = __uint_as_float(ksw0 & 0xFFFF0000u);
-    float ks10 = __uint_as_float(ksw1 << 16), ks11 = __uint_as_float(ksw1 & 0xFFFF0000u);
     float vs00 = __uint_as_float(vsw0 << 16), vs01 = __uint_as_float(vsw0 & 0xFFFF0000u);
     float vs10 = __uint_as_float(vsw1 << 16), vs11 = __uint_as_float(vsw1 & 0xFFFF0000u);
     if (valid < 16) {  // last page of the sequence: neutralise rows past the end
-      if (t0 >= valid) { ks00 = ks01 = vs00 = vs01 = 0.f; }
-      if (t0 + 8 >= valid) { ks10 = ks11 = vs10 = vs11 = 0.f; }
+      if (t0 >= valid) { ksw0 = 0u; vs00 = vs01 = 0.f; }
+      if (t0 + 8 >= valid) { ksw1 = 0u; vs10 = vs11 = 0.f; }
     }
-    smax0 = fmaxf(smax0, fmaxf(ks00, ks10));
-    smax1 = fmaxf(smax1, fmaxf(ks01, ks11));
-    float s0 = attn * (ks00 * acc[0][0] + ks01 * acc[1][0]);  // row g,   head 2tig
-    float s1 = attn * (ks00 * acc[0][1] + ks01 * acc[1][1]);  // row g,   head 2tig+1
-    float s2 = attn * (ks10 * acc[0][2] + ks11 * acc[1][2]);  // row g+8, head 2tig
-    float s3 = attn * (ks10 * acc[0][3] + ks11 * acc[1][3]);  // row g+8, head 2tig+1
+    {
+      const uint32_t sc0 = prmt(ksw0, ksw0, ks_sel), sc1 = prmt(ksw1, ksw1, ks_sel);
+      smax_bits = max(smax_bits, max(sc0 & 0x7FFFu, sc1 & 0x7FFFu));
+      const uint32_t* row0 = reinterpret_cast<const uint32_t*>(sp + T::kKOff + t0 * T::kKRow) + tig;
+      const uint32_t* row1 = row0 + 8 * (T::kKRow / 4);
+      uint32_t R0[2][8], R1[2][8];
+      k3_unpack_row(row0[0], row0[4], row0[8], sc0, R0);
+      k3_unpack_row(row1[0], row1[4], row1[8], sc1, R1);
+#pragma unroll
+      for (int t = 0; t < kQTerms; ++t)
+#pragma unroll
+        for (int x = 0; x < 8; ++x)
+          mma_bf16_16816(acc, R0[0][x], R1[0][x], R0[1][x], R1[1][x], qf[t][x][0], qf[t][x][1]);
+    }
+
+    // ---------------- scores ----------------
+    float s0 = acc[0] * attn;  // row g,   head 2tig
+    float s1 = acc[1] * attn;  // row g,   head 2tig+1
+    float s2 = acc[2] * attn;  // row g+8, head 2tig
+    float s3 = acc[3] * attn;  // row g+8, head 2tig+1
     if (valid < 16) {
       if (t0 >= valid) { s0 = s1 = -INFINITY; }
       if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; }
@@ -277,7 +312,8 @@ scan_k3v2_kernel(const ScanParams p) {
       wo[(2 * tig + 1) * JF_HEAD_DIM + db] = oacc[mt][3] * ub;
     }
   }
-  cta_merge_store(p, smem, l0, l1, m_ref0, m_ref1, smax0, smax1, split, hkv, b);
+  const float smax = __uint_as_float(smax_bits << 16);
+  cta_merge_store(p, smem, l0, l1, m_ref0, m_ref1, (tig >> 1) ? 0.f : smax, (tig >> 1) ? smax : 0.f, split, hkv, b);
 }
 
 // ------------------------------------------------------------------------------------
@@ -317,9 +353,8 @@ __global__ void fill_neg_inf_tail_kernel(float* scores, const int32_t* seq_lens,
 
 extern "C" uint64_t jf_decode_workspace_bytes(int32_t mode, int32_t B, int32_t H_q, int32_t H_kv,
                                               int32_t max_S, int32_t top_k) {
-  (void)mode;
   if (B <= 0 || H_q <= 0 || H_kv <= 0 || max_S <= 0 || top_k <= 0) return 0;
-  return jf::carve_workspace(nullptr, B, H_q, H_kv, max_S, top_k, true).bytes;
+  return jf::carve_workspace(nullptr, mode, B, H_q, H_kv, max_S, top_k, true).bytes;
 }
 
 extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t stream_) {
@@ -327,7 +362,7 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   jf_status_t st = validate_decode_args(a);
   if (st != JF_OK) return st;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
+  Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   JF_CUDA_TRY(cudaMemsetAsync(ws.status, 0, sizeof(int32_t), stream));
   ScanParams sp{};
   sp.q = a->q;
@@ -340,7 +375,7 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.num_slots = a->num_slots;
   sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = a->H_kv; sp.G = a->H_q / a->H_kv;
   sp.max_S = a->max_S; sp.max_blocks = a->max_blocks;
-  sp.splits = scan_splits(a->B, a->H_kv, a->max_S);
+  sp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
   const int pages = (a->max_S + 15) / 16;
   sp.pages_per_split = (pages + sp.splits - 1) / sp.splits;
   sp.attn_scale = a->attn_scale;

@@ -7,9 +7,10 @@
 //   1. a 2048-bin histogram of the approximate scores (bin width 1/64 below an upper bound
 //      of the row maximum) finds the bin T that holds the k-th largest approximate score;
 //   2. every position whose approximate score can still beat it -- bins <= T + ceil(2*delta*64)
-//      + 1, with delta a bound on |approximate - canonical| -- is re-scored in the canonical
-//      arithmetic (reference dequantisation rounding, fp32 fma chain over ascending d), and
-//      the k best by (canonical score desc, position asc) are emitted in that order.
+//      + 1, with delta a bound on |approximate - canonical| (fp32 summation-order error only,
+//      the scan dequantises with the reference's rounding) -- is re-scored in the canonical
+//      arithmetic, and the k best by (canonical score desc, position asc) are emitted in
+//      that order.
 // The result is reproducible by a CPU and independent of tensor-core internals.  If the
 // band does not fit the sort buffer (massive ties, degenerate scales) a slow exact path
 // radix-selects on the 64-bit key (canonical score, ~position) computed on the fly.
@@ -58,57 +59,59 @@ __device__ __forceinline__ int64_t slot_of(const RowCtx& c, int pos) {
   return blk * 16 + (pos & 15);
 }
 
-// Canonical K3 score: k_hat = bf16(float(code - 4) * float(scale_bf16)) as in
-// csrc/int3_qk_scores.cu:90-100, then acc = fmaf(q[d], k_hat[d], acc) for d ascending.
-__device__ float canon_score_k3(const RowCtx& c, int64_t slot) {
-  const uint4* row = reinterpret_cast<const uint4*>(c.k_rows + slot * 48);
-  const uint4 p0 = __ldg(row), p1 = __ldg(row + 1), p2 = __ldg(row + 2);
+// Canonical K3 score, one warp per position.  k_hat = bf16(float(code - 4) * float(scale_bf16))
+// as in jetfire_vllm/csrc/int3_qk_scores.cu:90-100.  Products of two 16-bit floats are exact
+// in fp32; the canonical summation order is: lane l accumulates channels l, l+32, l+64, l+96
+// with fma (ascending, from 0), then the 32 partials are added by a butterfly over lane
+// distances 16, 8, 4, 2, 1.  Every lane returns the same value.  (The reference's own order is
+// whatever its tensor-core instruction does; any fixed order stays inside its 2e-5 gate.)
+__device__ __forceinline__ float canon_score_k3(const RowCtx& c, int64_t slot, int lane) {
+  const uint8_t* row = c.k_rows + slot * 48;
   const uint32_t sw = __ldg(reinterpret_cast<const uint32_t*>(c.k_sc + slot * 2));
-  const float sc0 = __uint_as_float(sw << 16), sc1 = __uint_as_float(sw & 0xFFFF0000u);
-  const uint32_t a0[4] = {p0.x, p0.y, p0.z, p0.w}, a1[4] = {p1.x, p1.y, p1.z, p1.w}, a2[4] = {p2.x, p2.y, p2.z, p2.w};
-  float acc = 0.f;
+  const int x = lane & 7;
+  float part = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int w = i >> 2, sh = 8 * (i & 3);
-    const uint32_t w24 = (((a0[w] >> sh) & 255u) << 16) | (((a1[w] >> sh) & 255u) << 8) | ((a2[w] >> sh) & 255u);
-    const float sc = (i < 8) ? sc0 : sc1;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const int code = static_cast<int>((w24 >> (21 - 3 * r)) & 7u) - 4;
-      const float kh = __bfloat162float(__float2bfloat16_rn(__fmul_rn(static_cast<float>(code), sc)));
-      acc = __fmaf_rn(c.q[8 * i + r], kh, acc);
-    }
+  for (int r = 0; r < 4; ++r) {
+    const int i = 4 * r + (lane >> 3);  // INT3 group of channel 32 r + lane
+    const uint32_t w24 = (static_cast<uint32_t>(__ldg(row + i)) << 16) |
+                         (static_cast<uint32_t>(__ldg(row + 16 + i)) << 8) | __ldg(row + 32 + i);
+    const float sc = (r < 2) ? __uint_as_float(sw << 16) : __uint_as_float(sw & 0xFFFF0000u);
+    const int code = static_cast<int>((w24 >> (21 - 3 * x)) & 7u) - 4;
+    const float kh = __bfloat162float(__float2bfloat16_rn(__fmul_rn(static_cast<float>(code), sc)));
+    part = __fmaf_rn(c.q[32 * r + lane], kh, part);
   }
-  return __fmul_rn(acc, c.attn);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xFFFFFFFFu, part, o));
+  return __fmul_rn(part, c.attn);
 }
 
-// Canonical K4/G128 score (csrc/int8tc_qk_scores.cu:445-487): exact int32 dot per 32-channel
-// block against the INT8 query, s = fma(float(acc_c), qs_c, s) for c = 0..3, * k_scale, * attn.
-__device__ float canon_score_k4(const RowCtx& c, int64_t slot) {
-  const uint4* row = reinterpret_cast<const uint4*>(c.k_rows + slot * 64);
+// Canonical K4/G128 score (jetfire_vllm/csrc/int8tc_qk_scores.cu:445-487): exact int32 dot per
+// 32-channel block against the INT8 query, s = fma(float(acc_c), qs_c, s) for c = 0..3,
+// * k_scale, * attn.  Lane l handles channels 4l..4l+3 (block l / 8).
+__device__ __forceinline__ float canon_score_k4(const RowCtx& c, int64_t slot, int lane) {
+  const uint32_t two = __ldg(reinterpret_cast<const uint16_t*>(c.k_rows + slot * 64) + lane);
   const float ks = bf16_bits_to_f32(__ldg(c.k_sc + slot));
+  const int d = 4 * lane;
+  int acc = (static_cast<int>((two >> 4) & 15u) - 8) * c.qi[d] + (static_cast<int>(two & 15u) - 8) * c.qi[d + 1] +
+            (static_cast<int>((two >> 12) & 15u) - 8) * c.qi[d + 2] + (static_cast<int>((two >> 8) & 15u) - 8) * c.qi[d + 3];
+  acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+  acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+  acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 4);
   float s = 0.f;
 #pragma unroll
-  for (int blk = 0; blk < 4; ++blk) {
-    const uint4 v = __ldg(row + blk);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    int acc = 0;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const uint32_t byte = (w[j >> 2] >> (8 * (j & 3))) & 255u;
-      const int d = 32 * blk + 2 * j;
-      acc += (static_cast<int>(byte >> 4) - 8) * c.qi[d] + (static_cast<int>(byte & 15u) - 8) * c.qi[d + 1];
-    }
-    s = __fmaf_rn(static_cast<float>(acc), c.qs[blk], s);
-  }
+  for (int blk = 0; blk < 4; ++blk)
+    s = __fmaf_rn(static_cast<float>(__shfl_sync(0xFFFFFFFFu, acc, 8 * blk)), c.qs[blk], s);
   return __fmul_rn(__fmul_rn(s, ks), c.attn);
 }
 
+// Key of a position, computed by a whole warp (all lanes get it): canonical score in the high
+// word (order-preserving), ~position in the low word, so that larger key = better rank and
+// equal scores prefer the lower position.
 template <int MODE>
-__device__ __forceinline__ uint64_t canon_key(const RowCtx& c, int pos) {
+__device__ __forceinline__ uint64_t canon_key(const RowCtx& c, int pos, int lane) {
   const int64_t slot = slot_of(c, pos);
   float s = -INFINITY;
-  if (slot >= 0) s = (MODE == JF_MODE_K3V2) ? canon_score_k3(c, slot) : canon_score_k4(c, slot);
+  if (slot >= 0) s = (MODE == JF_MODE_K3V2) ? canon_score_k3(c, slot, lane) : canon_score_k4(c, slot, lane);
   return (static_cast<uint64_t>(float_order_key(s)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(pos));
 }
 
@@ -183,7 +186,12 @@ topk_select_kernel(const TopkParams p) {
 
   if (n <= p.sort_n) {
     // short row: every position is a candidate
-    for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = (i < n) ? canon_key<MODE>(ctx, i) : 0ull;
+    for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
+    __syncthreads();
+    for (int i = warp; i < n; i += kTopkThreads / 32) {
+      const uint64_t key = canon_key<MODE>(ctx, i, lane);
+      if (lane == 0) keys[i] = key;
+    }
     ncand = n;
   } else {
     // ---- tier 1: histogram of approximate scores ----
@@ -197,9 +205,14 @@ topk_select_kernel(const TopkParams p) {
     top += 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
     float delta = 0.f;
     if (MODE == JF_MODE_K3V2) {
-      // |approx - canonical| <= attn * sum_g scale_g * sum_{d in g} |q_d| * 3 * 2^-9, plus slack
+      // The scan and the canonical order add the same exact products q_d * k_hat_d in fp32,
+      // in different orders: each stays within (roundings) * 2^-24 * sum|q_d k_hat_d| of the
+      // exact sum (canonical: 9 roundings; tensor core: one per k-step, 8, possibly
+      // truncating).  sum|q_d k_hat_d| <= sum_g 3 * scale_g * sum_{d in g} |q_d|.  A factor 32
+      // covers both paths with slack; the last term covers the final multiply by attn_scale.
       const float q1a = sh_red[0] + sh_red[1], q1b = sh_red[2] + sh_red[3];
-      delta = fabsf(p.attn_scale) * (sm0 * q1a + sm1 * q1b) * (3.0f / 512.0f) * 1.02f + 1e-6f;
+      const float mag = fabsf(p.attn_scale) * (sm0 * q1a + sm1 * q1b) * 3.0f;
+      delta = mag * (32.0f / 16777216.0f) + mag * (4.0f / 16777216.0f) + 1e-7f;
     }
     for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0;
     __syncthreads();
@@ -255,7 +268,11 @@ topk_select_kernel(const TopkParams p) {
       }
       __syncthreads();
       ncand = min(sh_ncand, p.sort_n);
-      for (int j = tid; j < ncand; j += kTopkThreads) keys[j] = canon_key<MODE>(ctx, static_cast<int>(keys[j]));
+      for (int j = warp; j < ncand; j += kTopkThreads / 32) {
+        const uint64_t key = canon_key<MODE>(ctx, static_cast<int>(keys[j]), lane);
+        __syncwarp();
+        if (lane == 0) keys[j] = key;
+      }
     } else {
       // ---- slow exact path: 8-level radix select on the 64-bit canonical key ----
       if (tid == 0) { sh_prefix = 0ull; sh_remaining = K; }
@@ -264,10 +281,10 @@ topk_select_kernel(const TopkParams p) {
         for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
         __syncthreads();
         const unsigned long long prefix = sh_prefix;
-        for (int i = tid; i < n; i += kTopkThreads) {
-          const uint64_t key = canon_key<MODE>(ctx, i);
+        for (int i = warp; i < n; i += kTopkThreads / 32) {
+          const uint64_t key = canon_key<MODE>(ctx, i, lane);
           const bool match = (level == 7) || ((key >> (8 * (level + 1))) == prefix);
-          if (match) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
+          if (match && lane == 0) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
         }
         __syncthreads();
         if (tid == 0) {
@@ -284,9 +301,9 @@ topk_select_kernel(const TopkParams p) {
       const unsigned long long tkey = sh_prefix;  // key of the k-th best; keys are unique
       for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
       __syncthreads();
-      for (int i = tid; i < n; i += kTopkThreads) {
-        const uint64_t key = canon_key<MODE>(ctx, i);
-        if (key >= tkey) {
+      for (int i = warp; i < n; i += kTopkThreads / 32) {
+        const uint64_t key = canon_key<MODE>(ctx, i, lane);
+        if (key >= tkey && lane == 0) {
           const int pos = atomicAdd(&sh_ncand, 1);
           if (pos < p.sort_n) keys[pos] = key;
         }
@@ -297,17 +314,32 @@ topk_select_kernel(const TopkParams p) {
   }
   __syncthreads();
 
-  // ---- bitonic sort, descending, sort_n a power of two ----
-  for (int size = 2; size <= p.sort_n; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < (p.sort_n >> 1); i += kTopkThreads) {
-        const int lo = 2 * i - (i & (stride - 1));
-        const int hi2 = lo + stride;
-        const bool desc = ((lo & size) == 0);
-        const uint64_t a = keys[lo], c = keys[hi2];
-        if ((a < c) == desc) { keys[lo] = c; keys[hi2] = a; }
+  // ---- order the candidates: best first ----
+  uint64_t* ranked = keys;
+  if (p.sort_n <= 1024) {
+    // rank by counting (keys are unique): no barriers, two passes over <= 1024 keys
+    uint64_t mine = 0ull;
+    int rank = 0;
+    if (tid < ncand) {
+      mine = keys[tid];
+      for (int j = 0; j < ncand; ++j) rank += (keys[j] > mine) ? 1 : 0;
+    }
+    __syncthreads();
+    if (tid < ncand) keys[rank] = mine;
+    __syncthreads();
+  } else {
+    // bitonic sort, descending, sort_n a power of two
+    for (int size = 2; size <= p.sort_n; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int i = tid; i < (p.sort_n >> 1); i += kTopkThreads) {
+          const int lo = 2 * i - (i & (stride - 1));
+          const int hi2 = lo + stride;
+          const bool desc = ((lo & size) == 0);
+          const uint64_t a = keys[lo], c = keys[hi2];
+          if ((a < c) == desc) { keys[lo] = c; keys[hi2] = a; }
+        }
+        __syncthreads();
       }
-      __syncthreads();
     }
   }
 
@@ -316,9 +348,9 @@ topk_select_kernel(const TopkParams p) {
     int64_t idx = -1, slot = -1;
     float canon = -INFINITY;
     if (r < m) {
-      idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
+      idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(ranked[r] & 0xFFFFFFFFull));
       slot = slot_of(ctx, static_cast<int>(idx));
-      canon = float_from_order_key(static_cast<uint32_t>(keys[r] >> 32));
+      canon = float_from_order_key(static_cast<uint32_t>(ranked[r] >> 32));
     }
     out_idx[r] = idx;
     out_slot[r] = slot;
@@ -338,7 +370,7 @@ extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t strea
   if (st != JF_OK) return st;
   if (!a->topk_idx || !a->topk_slots) return JF_ERR_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  Workspace ws = carve_workspace(a->workspace, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
+  Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   TopkParams tp{};
   tp.scores = a->scores ? a->scores : ws.scores;
   tp.part_m = ws.part_m; tp.part_smax = ws.part_smax;
@@ -348,7 +380,7 @@ extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t strea
   tp.num_slots = a->num_slots;
   tp.B = a->B; tp.H_q = a->H_q; tp.H_kv = a->H_kv; tp.G = a->H_q / a->H_kv;
   tp.max_S = a->max_S; tp.max_blocks = a->max_blocks;
-  tp.splits = scan_splits(a->B, a->H_kv, a->max_S);
+  tp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
   tp.top_k = a->top_k;
   tp.sort_n = pow2_ceil(2 * a->top_k);
   if (tp.sort_n < 512) tp.sort_n = 512;

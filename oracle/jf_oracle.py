@@ -199,18 +199,25 @@ def canonical_scores_bf16path(q_row, k_hat, attn_scale) -> np.ndarray:
     ``k_hat = bf16(float(code - off) * float(scale))``, products of two 16-bit
     floats are exact in fp32 and are accumulated in fp32, then multiplied by
     ``attn_scale``.  The tensor-core accumulation order is unspecified, so the
-    canonical order is fixed here as ``acc = fmaf(q[d], k_hat[d], acc)`` for
-    d = 0..127 ascending from ``acc = 0``; because each product is exact, a
-    float32 multiply followed by a float32 add reproduces ``fmaf`` bit for bit.
+    canonical order is fixed here (any fixed order stays inside the reference's own
+    2e-5 score gate, scripts/validate_runtime.py:147-148):
+
+      * 32 partial sums: partial ``l`` takes channels ``l, l+32, l+64, l+96`` in that
+        order, ``part = fmaf(q[d], k_hat[d], part)`` from 0 -- each product is exact, so
+        a float32 multiply followed by a float32 add reproduces ``fmaf`` bit for bit;
+      * a butterfly over distances 16, 8, 4, 2, 1: ``part[l] += part[l ^ o]``.
 
     q_row (128,) f32 values, k_hat (n, 128) f32 values (bf16-representable).
     """
     q_row = np.asarray(q_row, dtype=np.float32)
     k_hat = np.asarray(k_hat, dtype=np.float32)
-    acc = np.zeros(k_hat.shape[0], dtype=np.float32)
-    for d in range(k_hat.shape[1]):
-        acc = acc + q_row[d] * k_hat[:, d]
-    return acc * np.float32(attn_scale)
+    part = np.zeros((k_hat.shape[0], 32), dtype=np.float32)
+    for r in range(4):
+        part = part + q_row[None, 32 * r:32 * r + 32] * k_hat[:, 32 * r:32 * r + 32]
+    lanes = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        part = part + part[:, lanes ^ o]
+    return part[:, 0] * np.float32(attn_scale)
 
 
 def quantize_query_int8(q):

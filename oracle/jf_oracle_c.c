@@ -7,7 +7,7 @@
  * The JetFire project has no native CPU implementation of the scan; this follows the
  * arithmetic of its GPU kernels and validation scripts (paths inside that project):
  *   dequantisation   scripts/validate_runtime.py:22-43, csrc/int3_qk_scores.cu:90-100
- *   K3 scores        csrc/int3_qk_scores.cu:284-311 (canonical order: fma over ascending d)
+ *   K3 scores        csrc/int3_qk_scores.cu:284-311 (canonical order: 32 strided partials + butterfly)
  *   K4/G128 scores   csrc/int8tc_qk_scores.cu:272-290, 445-487 (INT8 query)
  *   top-k            csrc/int3_qk_scores.cu:426-554, order (score desc, position asc)
  *   Stage B (fp32)   csrc/int2_softmax_v.cu:120-143, 681-705, 738-788
@@ -107,16 +107,24 @@ int jf_oracle_decode(int mode, const float* q, const uint8_t* k_data, const uint
       const uint16_t* ksc = k_scales + ((int64_t)hk * num_slots + slot) * ng;
       float sc;
       if (!mode) {
-        float acc = 0.f;
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t w = ((uint32_t)kr[i] << 16) | ((uint32_t)kr[16 + i] << 8) | kr[32 + i];
-          const float gsc = bf16f(ksc[i >> 3]);
-          for (int r = 0; r < 8; ++r) {
-            const int code = (int)((w >> (21 - 3 * r)) & 7u) - 4;
-            const float kh = round_bf16((float)code * gsc);
-            acc = fmaf(qr[8 * i + r], kh, acc);
+        /* canonical order: 32 partials (channels l, l+32, l+64, l+96), then a butterfly */
+        float part[32];
+        for (int l = 0; l < 32; ++l) part[l] = 0.f;
+        for (int r = 0; r < 4; ++r) {
+          for (int l = 0; l < 32; ++l) {
+            const int d = 32 * r + l, i = d >> 3, x = d & 7;
+            const uint32_t w = ((uint32_t)kr[i] << 16) | ((uint32_t)kr[16 + i] << 8) | kr[32 + i];
+            const int code = (int)((w >> (21 - 3 * x)) & 7u) - 4;
+            const float kh = round_bf16((float)code * bf16f(ksc[i >> 3]));
+            part[l] = fmaf(qr[d], kh, part[l]);
           }
         }
+        for (int o = 16; o > 0; o >>= 1) {
+          float nxt[32];
+          for (int l = 0; l < 32; ++l) nxt[l] = part[l] + part[l ^ o];
+          for (int l = 0; l < 32; ++l) part[l] = nxt[l];
+        }
+        const float acc = part[0];
         sc = acc * attn_scale;
       } else {
         float t = 0.f;
