@@ -30,6 +30,7 @@ enum {
   JF_ERR_ARG          = -1, /* null pointer, bad shape, misaligned pointer          */
   JF_ERR_UNSUPPORTED  = -2, /* valid request outside the built envelope              */
   JF_ERR_WORKSPACE    = -3, /* workspace missing or too small                        */
+  JF_ERR_STATIC_LIMIT = -4, /* request needs more scratch than the built-in buffer   */
   JF_ERR_CUDA         = 1,  /* a CUDA call failed; see jf_last_cuda_error()          */
   JF_ERR_TIMEOUT      = 2,  /* a bounded wait ran out (device status word or host)   */
   JF_ERR_STATE        = 3   /* host-side object used in the wrong state              */
@@ -142,6 +143,28 @@ jf_status_t jf_decode_fused(const jf_decode_args* args, jf_stream_t stream);
 /* Reads back (synchronously, after the stream drained) the device status word of the
  * workspace: 0, or JF_ERR_TIMEOUT if a bounded wait inside a kernel ran out. */
 jf_status_t jf_decode_status(const jf_decode_args* args, jf_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
+ * jf_decode_fused without a workspace argument.  No counterpart in the reference (its
+ * ops allocate their scratch through torch).
+ *
+ * For callers that cannot allocate device memory themselves -- code living inside a host
+ * application that owns all allocations, code on a path where an allocator call or the
+ * synchronisation it may imply is not tolerable, or a process whose device memory is fully
+ * planned in advance.  Inputs and outputs are still the caller's; `workspace` and
+ * `workspace_bytes` of the argument block are ignored.  The scratch is a fixed
+ * JF_STATIC_SCRATCH_BYTES array inside the library image: each GPU that loads the library
+ * holds it until the process exits.  A request whose jf_decode_workspace_bytes() exceeds it
+ * returns JF_ERR_STATIC_LIMIT (roughly: B * H_q * max_S up to ~15 million score slots, e.g.
+ * batch 4 x 32 heads x 64k context).  Mode K3V2 only; K4V4 returns JF_ERR_UNSUPPORTED
+ * because its launch path keeps a host-side cache that may allocate.
+ * All calls on a GPU share the one array and it keeps the previous call's contents, so
+ * calls must not overlap on the same GPU (they would race); results do not depend on what
+ * was left behind.  The first call on each device resolves the array's address and should
+ * be made before any stream capture begins.  Never calls cudaMalloc / cudaFree.
+ * ------------------------------------------------------------------------------- */
+#define JF_STATIC_SCRATCH_BYTES (64ull << 20)
+jf_status_t jf_decode_fused_static(const jf_decode_args* args, jf_stream_t stream);
 
 /* ---------------------------------------------------------------------------------
  * Correction merge: out = dtype(o_hat + W * float(o_new) - o_old_unnorm).

@@ -11,7 +11,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libjetfire_b200.so"
 
 JF_OK = 0
-JF_ERR_ARG, JF_ERR_UNSUPPORTED, JF_ERR_WORKSPACE = -1, -2, -3
+JF_ERR_ARG, JF_ERR_UNSUPPORTED, JF_ERR_WORKSPACE, JF_ERR_STATIC_LIMIT = -1, -2, -3, -4
 JF_ERR_CUDA, JF_ERR_TIMEOUT, JF_ERR_STATE = 1, 2, 3
 JF_DTYPE_BF16, JF_DTYPE_FP16 = 0, 1
 JF_MODE_K3V2, JF_MODE_K4V4 = 0, 1
@@ -61,6 +61,7 @@ _SIGS = {
     "jf_decode_finish": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_fused": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_status": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "jf_decode_fused_static": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_merge_correct": (C.c_int32, [C.c_void_p] * 5 + [C.c_int32] * 3 + [C.c_void_p]),
     "jf_cpu_topk_attn": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                        C.c_void_p]),

@@ -11,6 +11,7 @@ extern "C" const char* jf_status_string(jf_status_t st) {
     case JF_ERR_ARG: return "invalid argument (null pointer, bad shape or misaligned pointer)";
     case JF_ERR_UNSUPPORTED: return "request outside the supported envelope";
     case JF_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case JF_ERR_STATIC_LIMIT: return "request needs more scratch than the library's built-in static buffer holds";
     case JF_ERR_CUDA: return "CUDA call failed (see jf_last_cuda_error)";
     case JF_ERR_TIMEOUT: return "a bounded wait ran out";
     case JF_ERR_STATE: return "object used in the wrong state";
