@@ -20,7 +20,7 @@ __host__ __device__ inline ModeInfo mode_info(int mode) {
 
 // Resident scan CTAs per SM (set by registers / shared memory of the kernel variant).
 __host__ __device__ inline int scan_ctas_per_sm(int mode, int q_dtype) {
-  return (mode == JF_MODE_K4V4 || q_dtype == JF_DTYPE_FP16) ? 3 : 4;
+  return (mode == JF_MODE_K3V2 && q_dtype == JF_DTYPE_FP16) ? 3 : 4;
 }
 
 // How many splits of the page range one (b, h_kv) pair is cut into: as many as fit in ONE

@@ -20,9 +20,10 @@ namespace jf {
 
 namespace {
 
-constexpr int kFinishThreads = 256;
+constexpr int kFinishThreads = 512;
 constexpr int kFinishWarps = kFinishThreads / 32;
-constexpr int kChunk = 256;  // selected entries staged per round
+constexpr int kSplitGroups = kFinishThreads / JF_HEAD_DIM;  // split partials are summed in 4 strided groups
+constexpr int kChunk = 256;                                  // selected entries staged per round
 
 struct FinishParams {
   const float* scores;
@@ -44,38 +45,54 @@ struct FinishParams {
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k;
 };
 
-// One CTA per (query head, batch element).  The split merge is one thread per output
-// channel; the selected set is walked a warp per entry, lane l owning channels 4l..4l+3 so
-// that a V row is one coalesced 32- or 64-byte read.
+// One CTA per (query head, batch element).  Everything is arranged as a few rounds of
+// independent loads (the kernel is bound by L2 latency, not bandwidth): split statistics,
+// then split partials in four strided groups, then per selected entry its slot / weights,
+// then all V rows of a chunk into shared memory, then a warp per entry with lane l owning
+// channels 4l..4l+3.  Summation orders are fixed (bit-reproducible).
 template <int MODE>
 __global__ void __launch_bounds__(kFinishThreads)
 decode_finish_kernel(const FinishParams p) {
+  constexpr int VW = (MODE == JF_MODE_K3V2) ? 8 : 16;  // 32-bit words per packed V row
   __shared__ int64_t sm_slot[kChunk];
   __shared__ float sm_wc[kChunk][2];   // canonical weight * v scale (per group)
   __shared__ float sm_dw[kChunk][2];   // (canonical - scan) weight * v scale
   __shared__ float sm_w[kChunk][2];    // canonical weight, weight difference
+  __shared__ uint32_t sm_v[kChunk * VW];
   __shared__ float sm_red[kFinishWarps][JF_HEAD_DIM][2];
   __shared__ float sm_sum[kFinishWarps][2];
-  __shared__ float sm_stat[2];         // merged reference point M, normaliser Z of the scan
+  __shared__ float sm_o[kSplitGroups][JF_HEAD_DIM];
+  __shared__ float sm_z[kSplitGroups];
+  __shared__ float sm_m[kFinishWarps];
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int hkv = h / p.G, hi = h - hkv * p.G;
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
   const int n = min(p.seq_lens[b], p.max_S);
 
-  // ---- merge splits (unnormalised): thread d < 128 owns channel d ----
+  // ---- merged reference point: max over the splits ----
   const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
   float M = kMinusBig;
-  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.part_m[(pbase + s) * kHeadsPad + hi]);
-  float o = 0.f;
-  if (tid < JF_HEAD_DIM) {
-    float Z = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
+  for (int s = tid; s < p.splits; s += kFinishThreads) M = fmaxf(M, p.part_m[(pbase + s) * kHeadsPad + hi]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+  if (lane == 0) sm_m[warp] = M;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kFinishWarps; ++w) M = fmaxf(M, sm_m[w]);
+
+  // ---- merge splits (unnormalised): thread (group, d) sums splits group, group + 4, ... ----
+  {
+    const int d = tid & (JF_HEAD_DIM - 1), grp = tid >> 7;
+    float o = 0.f, Z = 0.f;
+#pragma unroll 4
+    for (int s = grp; s < p.splits; s += kSplitGroups) {
       const float w = ex2((p.part_m[(pbase + s) * kHeadsPad + hi] - M) * kLog2e);
       Z = fmaf(p.part_l[(pbase + s) * kHeadsPad + hi], w, Z);
-      o = fmaf(p.part_o[((pbase + s) * kHeadsPad + hi) * JF_HEAD_DIM + tid], w, o);
+      o = fmaf(p.part_o[((pbase + s) * kHeadsPad + hi) * JF_HEAD_DIM + d], w, o);
     }
-    if (tid == 0) { sm_stat[0] = M; sm_stat[1] = Z; }
+    sm_o[grp][d] = o;
+    if (d == 0) sm_z[grp] = Z;
   }
 
   // ---- selected set: canonical weights, and their difference to the scan's ----
@@ -88,9 +105,10 @@ decode_finish_kernel(const FinishParams p) {
   const float* canon = p.sel_canon + bh * p.top_k;
   float a_old[4] = {0.f, 0.f, 0.f, 0.f}, a_dw[4] = {0.f, 0.f, 0.f, 0.f};
   float wsum = 0.f, dz = 0.f;
-  const int grp = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
+  const int qg = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
   for (int k0 = 0; k0 < p.top_k; k0 += kChunk) {
-    {
+    const int kend = min(kChunk, p.top_k - k0);
+    if (tid < kChunk) {
       const int kk = k0 + tid;
       int64_t slot = -1;
       float wc = 0.f, dw = 0.f, vs0 = 0.f, vs1 = 0.f;
@@ -118,24 +136,27 @@ decode_finish_kernel(const FinishParams p) {
       sm_dw[tid][0] = dw * vs0; sm_dw[tid][1] = dw * vs1;
     }
     __syncthreads();
-    const int kend = min(kChunk, p.top_k - k0);
-#pragma unroll 4
+    for (int idx = tid; idx < kend * VW; idx += kFinishThreads) {
+      const int c = idx / VW, w = idx - c * VW;
+      const int64_t slot = sm_slot[c];
+      sm_v[idx] = (slot >= 0) ? __ldg(reinterpret_cast<const uint32_t*>(v_rows + slot * (VW * 4)) + w) : 0u;
+    }
+    __syncthreads();
     for (int j = warp; j < kend; j += kFinishWarps) {
-      const int64_t slot = sm_slot[j];
-      if (slot < 0) continue;  // warp-uniform
+      if (sm_slot[j] < 0) continue;  // warp-uniform
       float c[4];
       if (MODE == JF_MODE_K3V2) {
-        const uint32_t byte = __ldg(v_rows + slot * 32 + lane);
+        const uint32_t byte = reinterpret_cast<const uint8_t*>(sm_v + j * VW)[lane];
 #pragma unroll
         for (int e = 0; e < 4; ++e) c[e] = static_cast<float>(static_cast<int>((byte >> ((3 - e) * 2)) & 3u) - 2);
       } else {
-        const uint32_t two = __ldg(reinterpret_cast<const uint16_t*>(v_rows + slot * 64) + lane);
+        const uint32_t two = reinterpret_cast<const uint16_t*>(sm_v + j * VW)[lane];
         c[0] = static_cast<float>(static_cast<int>((two >> 4) & 15u) - 8);
         c[1] = static_cast<float>(static_cast<int>(two & 15u) - 8);
         c[2] = static_cast<float>(static_cast<int>((two >> 12) & 15u) - 8);
         c[3] = static_cast<float>(static_cast<int>((two >> 8) & 15u) - 8);
       }
-      const float fw = sm_wc[j][grp], fd = sm_dw[j][grp];
+      const float fw = sm_wc[j][qg], fd = sm_dw[j][qg];
 #pragma unroll
       for (int e = 0; e < 4; ++e) { a_old[e] = fmaf(fw, c[e], a_old[e]); a_dw[e] = fmaf(fd, c[e], a_dw[e]); }
       wsum += sm_w[j][0];
@@ -148,13 +169,15 @@ decode_finish_kernel(const FinishParams p) {
   if (lane == 0) { sm_sum[warp][0] = wsum; sm_sum[warp][1] = dz; }
   __syncthreads();
   if (tid < JF_HEAD_DIM) {
-    float acc_old = 0.f, acc_dw = 0.f, ws = 0.f, dzs = 0.f;
+    float acc_old = 0.f, acc_dw = 0.f, ws = 0.f, dzs = 0.f, o = 0.f, Z = 0.f;
 #pragma unroll
     for (int w = 0; w < kFinishWarps; ++w) {
       acc_old += sm_red[w][tid][0]; acc_dw += sm_red[w][tid][1];
       ws += sm_sum[w][0]; dzs += sm_sum[w][1];
     }
-    const float Z = sm_stat[1] + dzs;
+#pragma unroll
+    for (int gI = 0; gI < kSplitGroups; ++gI) { o += sm_o[gI][tid]; Z += sm_z[gI]; }
+    Z += dzs;
     const bool live = (Z > 0.f) && (n > 0);
     const float inv_z = live ? (1.0f / Z) : 0.f;
     p.o_hat[bh * JF_HEAD_DIM + tid] = (o + acc_dw) * inv_z;

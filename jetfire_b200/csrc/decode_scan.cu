@@ -204,7 +204,7 @@ scan_k3v2_kernel(const ScanParams p) {
 
   const int t0 = (g >> 1) | ((g & 1) << 2);  // token of MMA row g (rows g + 8 -> t0 + 8)
   const int h0 = hkv * p.G + 2 * tig;
-  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S;
+  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
 
@@ -258,9 +258,12 @@ scan_k3v2_kernel(const ScanParams p) {
       if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; }
     }
     {
-      float* r0 = score_row0 + pg * 16;
-      if (st0) { if (t0 < valid) r0[t0] = s0; if (t0 + 8 < valid) r0[t0 + 8] = s2; }
-      if (st1) { if (t0 < valid) r0[p.max_S + t0] = s1; if (t0 + 8 < valid) r0[p.max_S + t0 + 8] = s3; }
+      float* r0 = score_row0 + static_cast<int64_t>(pg) * 16;
+      const bool lo = t0 < valid, hi = t0 + 8 < valid;
+      if (st0 && lo) r0[0] = s0;
+      if (st0 && hi) r0[8] = s2;
+      if (st1 && lo) r0[p.max_S] = s1;
+      if (st1 && hi) r0[p.max_S + 8] = s3;
     }
 
     // ---------------- online softmax ----------------

@@ -65,7 +65,7 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 }  // namespace
 
 template <int DT>
-__global__ void __launch_bounds__(kScanWarps * 32, 3)
+__global__ void __launch_bounds__(kScanWarps * 32, 4)
 scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
                  const __grid_constant__ CUtensorMap v_map) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -98,22 +98,23 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const uint16_t* ks_h = p.k_scales + row_base;
   const uint16_t* vs_h = p.v_scales + row_base;
 
+  // Lanes 0/1 issue the K/V tensor copies, lanes 2/3 the two scale copies; what differs
+  // between the lanes of a pair is data (map, offsets), not control flow.
+  const CUtensorMap* my_map = (lane & 1) ? &v_map : &k_map;
+  const uint32_t my_dst_off = (lane < 2) ? (lane ? T4::kVOff : T4::kKOff) : ((lane & 1) ? T4::kVsOff : T4::kKsOff);
+  const uint16_t* my_scales = (lane & 1) ? vs_h : ks_h;
   auto issue = [&](int it, int64_t blk) {
     const int st = it % T4::kStages;
     const int pg = pg_begin + warp + it * kScanWarps;
     int valid = min(16, len - pg * 16);
     if (blk < 0 || blk >= n_blocks_phys) { blk = 0; valid = 0; }
-    uint8_t* dst = my_stages + st * T4::kBytes;
+    uint8_t* dst = my_stages + st * T4::kBytes + my_dst_off;
     if (lane == 0) {
       page_valid[st] = valid;
       mbar_expect_tx(&bars[st], T4::kTxBytes);
     }
-    __syncwarp();
-    const int y = static_cast<int>(row_base + blk * 16);
-    if (lane == 0) tma_load_2d(dst + T4::kKOff, &k_map, 0, y, &bars[st]);
-    else if (lane == 1) tma_load_2d(dst + T4::kVOff, &v_map, 0, y, &bars[st]);
-    else if (lane == 2) bulk_g2s(dst + T4::kKsOff, ks_h + blk * 16, 32, &bars[st]);
-    else if (lane == 3) bulk_g2s(dst + T4::kVsOff, vs_h + blk * 16, 32, &bars[st]);
+    if (lane < 2) tma_load_2d(dst, my_map, 0, static_cast<int>(row_base + blk * 16), &bars[st]);
+    else if (lane < 4) bulk_g2s(dst, my_scales + blk * 16, 32, &bars[st]);
   };
 
   {
@@ -172,7 +173,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int ksw = (t0 >> 1) & 3;               // swizzle term of rows t0 and t0 + 8
   const int tA = row_token(2 * tig), tB = row_token(2 * tig + 1);  // tokens of P.V k-slots
   const int h0 = hkv * p.G + 2 * tig;
-  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S;
+  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
   // byte offsets of this lane's V words inside a token row, swizzled per token below
@@ -226,9 +227,12 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; vs1 = 0.f; }
     }
     {
-      float* r0 = score_row0 + pg * 16;
-      if (st0) { if (t0 < valid) r0[t0] = s0; if (t0 + 8 < valid) r0[t0 + 8] = s2; }
-      if (st1) { if (t0 < valid) r0[p.max_S + t0] = s1; if (t0 + 8 < valid) r0[p.max_S + t0 + 8] = s3; }
+      float* r0 = score_row0 + static_cast<int64_t>(pg) * 16;
+      const bool lo = t0 < valid, hi = t0 + 8 < valid;
+      if (st0 && lo) r0[0] = s0;
+      if (st0 && hi) r0[8] = s2;
+      if (st1 && lo) r0[p.max_S] = s1;
+      if (st1 && hi) r0[p.max_S + 8] = s3;
     }
 
     // ---------------- online softmax ----------------
