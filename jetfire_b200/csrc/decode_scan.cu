@@ -40,20 +40,46 @@ __device__ __forceinline__ constexpr int v2_pos(int f) { return f <= 4 ? 2 * f :
 __device__ __forceinline__ constexpr int v2_dlocal(int f) { return 4 * (f >> 2) + 3 - (f & 3); }
 
 constexpr uint32_t kMagicBf16 = 0x43004300u;  // bf16 128.0 in both halves
+constexpr uint32_t kOneBf16x2 = 0x3F803F80u;
+
+// Shared-memory loads with a 32-bit address and an immediate offset: one instruction each,
+// no 64-bit pointer arithmetic in the loop.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint32_t v;  // a 32-bit destination is zero-extended by the 16-bit load
+  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// lo | (hi << 16) for two 16-bit values, as an integer multiply-add (runs on the FMA pipe,
+// which has twice the throughput of the logic pipe that PRMT/SHL/LOP3 share)
+__device__ __forceinline__ uint32_t join16(uint32_t lo, uint32_t hi) {
+  uint32_t d;
+  asm("mad.lo.u32 %0, %1, 65536, %2;" : "=r"(d) : "r"(hi), "r"(lo));
+  return d;
+}
 
 // Dequantised K in the reference's rounding, scaled by 2^POS:
 //   ((v & field) | 128) - (128 + 4 * 2^POS) == (code - 4) * 2^POS        exact in bf16
 //   bf16_rn(that * scale)                   == 2^POS * bf16(float(code - 4) * scale)
 // which is jetfire_vllm/csrc/int3_qk_scores.cu:94-99 (a power of two commutes with the
-// rounding); the 2^POS is undone by the query operand.
+// rounding); the 2^POS is undone by the query operand.  Both steps are single bf16x2 fmas.
 template <int POS>
 __device__ __forceinline__ uint32_t k3_field(uint32_t v, uint32_t scale2) {
   constexpr uint32_t m = (7u << POS) | (7u << (POS + 16));
-  constexpr uint32_t b = (0x4300u | (4u << POS)) * 0x10001u;
-  uint32_t t = and_or(v, m, kMagicBf16), d;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(t) : "r"(t), "r"(b));
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(t), "r"(scale2));
-  return d;
+  constexpr uint32_t negb = (0xC300u | (4u << POS)) * 0x10001u;  // -(128 + 4 * 2^POS)
+  const uint32_t t = fma_bf16x2(and_or(v, m, kMagicBf16), kOneBf16x2, negb);
+  return fma_bf16x2(t, scale2, 0u);
 }
 // One 32-bit word of each byte plane (4 INT3 groups = 32 channels of one row) -> 16 bf16x2
 // registers R[pair][code]: pair p holds groups (2p, 2p+1) in its (low, high) halves.
@@ -97,6 +123,96 @@ __device__ __forceinline__ uint32_t v2_field(uint32_t v) {
   return hsub2_u32(and_or(v, m, kMagic), b);
 }
 
+// Per-warp state that lives across pages.
+template <int QT>
+struct K3State {
+  uint32_t qf[QT][8][2];   // query fragments (B operand of the K MMA)
+  float oacc[8][4];        // output accumulators, O^T fragments
+  float m_ref0, m_ref1, l0, l1;
+  uint32_t smax_bits;      // largest K group scale seen (bf16 bits; positive floats order as integers)
+  uint32_t ks_sel;         // PRMT selector: this lane's K group scale into both halves
+};
+
+// One 16-token page.  `sb` = shared-memory address of the stage.  kPartial: the last page of
+// a sequence (or a page whose block id was invalid) -- rows at or past `valid` are neutralised;
+// the common full-page instance carries none of that logic.
+template <int QT, bool kPartial>
+__device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t k_addr_off, uint32_t v_addr_off,
+                                          uint32_t s_addr_off, int t0, int valid, float attn, float* sp0,
+                                          float* sp1, bool st0, bool st1) {
+  using T = Tile<JF_MODE_K3V2>;
+  // ---------------- K: unpack + Q.K^T ----------------
+  const uint32_t sa = sb + s_addr_off;
+  uint32_t ksw0 = lds32<0>(sa), ksw1 = lds32<32>(sa);
+  const uint32_t vsw0 = lds32<64>(sa), vsw1 = lds32<96>(sa);
+  float vs00 = __uint_as_float(vsw0 << 16), vs01 = __uint_as_float(vsw0 & 0xFFFF0000u);
+  float vs10 = __uint_as_float(vsw1 << 16), vs11 = __uint_as_float(vsw1 & 0xFFFF0000u);
+  if (kPartial) {
+    if (t0 >= valid) { ksw0 = 0u; vs00 = vs01 = 0.f; }
+    if (t0 + 8 >= valid) { ksw1 = 0u; vs10 = vs11 = 0.f; }
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const uint32_t sc0 = prmt(ksw0, ksw0, st.ks_sel), sc1 = prmt(ksw1, ksw1, st.ks_sel);
+    st.smax_bits = max(st.smax_bits, max(sc0 & 0x7FFFu, sc1 & 0x7FFFu));
+    const uint32_t ka = sb + k_addr_off;
+    uint32_t R0[2][8], R1[2][8];
+    k3_unpack_row(lds32<0>(ka), lds32<16>(ka), lds32<32>(ka), sc0, R0);
+    k3_unpack_row(lds32<8 * T::kKRow>(ka), lds32<8 * T::kKRow + 16>(ka), lds32<8 * T::kKRow + 32>(ka), sc1, R1);
+#pragma unroll
+    for (int t = 0; t < QT; ++t)
+#pragma unroll
+      for (int x = 0; x < 8; ++x)
+        mma_bf16_16816(acc, R0[0][x], R1[0][x], R0[1][x], R1[1][x], st.qf[t][x][0], st.qf[t][x][1]);
+  }
+
+  // ---------------- scores ----------------
+  float s0 = acc[0] * attn;  // row g,   head 2tig
+  float s1 = acc[1] * attn;  // row g,   head 2tig+1
+  float s2 = acc[2] * attn;  // row g+8, head 2tig
+  float s3 = acc[3] * attn;  // row g+8, head 2tig+1
+  if (kPartial) {
+    const bool lo = t0 < valid, hi = t0 + 8 < valid;
+    if (!lo) { s0 = s1 = -INFINITY; }
+    if (!hi) { s2 = s3 = -INFINITY; }
+    if (st0 && lo) sp0[0] = s0;
+    if (st0 && hi) sp0[8] = s2;
+    if (st1 && lo) sp1[0] = s1;
+    if (st1 && hi) sp1[8] = s3;
+  } else {
+    if (st0) { sp0[0] = s0; sp0[8] = s2; }
+    if (st1) { sp1[0] = s1; sp1[8] = s3; }
+  }
+
+  // ---------------- online softmax ----------------
+  float p0, p1, p2, p3;
+  softmax_step(s0, s1, s2, s3, st.m_ref0, st.m_ref1, st.l0, st.l1, st.oacc, p0, p1, p2, p3);
+
+  // ---------------- V: unpack + (P * vscale).V ----------------
+  const uint32_t va_addr = sb + v_addr_off;
+#pragma unroll
+  for (int qh = 0; qh < 2; ++qh) {
+    const float va = qh ? vs01 : vs00, vb = qh ? vs11 : vs10;
+    const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * va, p1 * va));  // tokens tig, tig+4
+    const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vb, p3 * vb));  // tokens tig+8, tig+12
+    uint32_t Ha, Hb, Hc, Hd;
+    if (qh == 0) {
+      Ha = lds16<0>(va_addr); Hb = lds16<4 * T::kVRow>(va_addr);
+      Hc = lds16<8 * T::kVRow>(va_addr); Hd = lds16<12 * T::kVRow>(va_addr);
+    } else {
+      Ha = lds16<16>(va_addr); Hb = lds16<4 * T::kVRow + 16>(va_addr);
+      Hc = lds16<8 * T::kVRow + 16>(va_addr); Hd = lds16<12 * T::kVRow + 16>(va_addr);
+    }
+    const uint32_t XA = join16(Ha, Hb), XB = join16(Hc, Hd);
+    const uint32_t XA2 = XA >> 10, XB2 = XB >> 10;
+    // fields 2ml -> output row g, 2ml+1 -> output row g+8
+    mma_f16_16816(st.oacc[qh * 4 + 0], v2_field<0>(XA), v2_field<2>(XA), v2_field<0>(XB), v2_field<2>(XB), B0, B1);
+    mma_f16_16816(st.oacc[qh * 4 + 1], v2_field<4>(XA), v2_field<6>(XA), v2_field<4>(XB), v2_field<6>(XB), B0, B1);
+    mma_f16_16816(st.oacc[qh * 4 + 2], v2_field<8>(XA), v2_field<0>(XA2), v2_field<8>(XB), v2_field<0>(XB2), B0, B1);
+    mma_f16_16816(st.oacc[qh * 4 + 3], v2_field<2>(XA2), v2_field<4>(XA2), v2_field<2>(XB2), v2_field<4>(XB2), B0, B1);
+  }
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------
@@ -106,13 +222,17 @@ template <int DT>
 __global__ void __launch_bounds__(kScanWarps * 32, (DT == JF_DTYPE_FP16) ? 3 : 4)
 scan_k3v2_kernel(const ScanParams p) {
   using T = Tile<JF_MODE_K3V2>;
+  constexpr int kQTerms = (DT == JF_DTYPE_FP16) ? 2 : 1;
   extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the warp index is the same for all lanes; routing it through a shuffle tells the
+  // compiler so, and lets stage / barrier addresses live in uniform registers
+  const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
 
-  uint8_t* my_stages = smem + warp * (T::kStages * T::kBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * T::kStages * T::kBytes) + warp * T::kStages;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t stages0 = smem_base + warp * (T::kStages * T::kBytes);
+  const uint32_t bars0 = smem_base + kScanWarps * T::kStages * T::kBytes + warp * (T::kStages * 8);
   int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8)) + warp * T::kStages;
 
   const int len = min(p.seq_lens[b], p.max_S);
@@ -123,55 +243,53 @@ scan_k3v2_kernel(const ScanParams p) {
   const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;  // may be <= 0
 
   if (lane == 0) {
-    for (int s = 0; s < T::kStages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < T::kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
   }
   fence_barrier_init();
   __syncwarp();
 
-  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
   const int64_t n_blocks_phys = p.num_slots >> 4;
-  const uint8_t* kd_h = p.k_data + static_cast<int64_t>(hkv) * p.num_slots * T::kKRow;
-  const uint8_t* vd_h = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * T::kVRow;
-  const uint16_t* ks_h = p.k_scales + static_cast<int64_t>(hkv) * p.num_slots * T::kNG;
-  const uint16_t* vs_h = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * T::kNG;
 
-  // Lanes 0..3 each issue one of the four copies of a page.
-  auto issue = [&](int it, int64_t blk) {
-    const int st = it % T::kStages;
+  // One elected lane issues the four bulk copies of a page (K data, V data, K scales, V scales).
+  const int64_t head_rows = static_cast<int64_t>(hkv) * p.num_slots;
+  const uint8_t* kd_h = p.k_data + head_rows * T::kKRow;
+  const uint8_t* vd_h = p.v_data + head_rows * T::kVRow;
+  const uint8_t* ks_h = reinterpret_cast<const uint8_t*>(p.k_scales + head_rows * T::kNG);
+  const uint8_t* vs_h = reinterpret_cast<const uint8_t*>(p.v_scales + head_rows * T::kNG);
+  const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
+  uint32_t slow_mask = 0u;  // stages whose page needs the masked path
+  auto issue = [&](int it, int st_idx, int64_t blk64) {
     const int pg = pg_begin + warp + it * kScanWarps;
-    int valid = min(16, len - pg * 16);
-    if (blk < 0 || blk >= n_blocks_phys) { blk = 0; valid = 0; }
-    uint8_t* dst = my_stages + st * T::kBytes;
-    if (lane == 0) {
-      page_valid[st] = valid;
-      mbar_expect_tx(&bars[st], T::kBytes);
-    }
-    __syncwarp();
-    if (lane < 4) {
-      const void* src;
-      uint32_t off, bytes;
-      if (lane == 0)      { src = kd_h + blk * (16 * T::kKRow); off = T::kKOff;  bytes = 16 * T::kKRow; }
-      else if (lane == 1) { src = vd_h + blk * (16 * T::kVRow); off = T::kVOff;  bytes = 16 * T::kVRow; }
-      else if (lane == 2) { src = ks_h + blk * (16 * T::kNG);   off = T::kKsOff; bytes = 32 * T::kNG; }
-      else                { src = vs_h + blk * (16 * T::kNG);   off = T::kVsOff; bytes = 32 * T::kNG; }
-      bulk_g2s(dst + off, src, bytes, &bars[st]);
+    const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
+    const bool slow = bad || pg == last_pg;
+    slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
+    const int64_t blk = bad ? 0 : blk64;
+    const uint32_t bar = bars0 + st_idx * 8;
+    const uint32_t dst = stages0 + st_idx * T::kBytes;
+    if (elect_one()) {
+      if (slow) page_valid[st_idx] = bad ? 0 : min(16, len - pg * 16);
+      mbar_expect_tx_u32(bar, T::kBytes);
+      bulk_g2s_u32(dst + T::kKOff, kd_h + blk * (16 * T::kKRow), 16 * T::kKRow, bar);
+      bulk_g2s_u32(dst + T::kVOff, vd_h + blk * (16 * T::kVRow), 16 * T::kVRow, bar);
+      bulk_g2s_u32(dst + T::kKsOff, ks_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
+      bulk_g2s_u32(dst + T::kVsOff, vs_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
     }
   };
 
   // prologue
   {
     const int pro = min(T::kStages, my_n);
-    for (int it = 0; it < pro; ++it) issue(it, bt_row[pg_begin + warp + it * kScanWarps]);
+    for (int it = 0; it < pro; ++it) issue(it, it, bt_row[it * kScanWarps]);
   }
   int64_t next_blk = 0;
-  if (T::kStages < my_n) next_blk = bt_row[pg_begin + warp + T::kStages * kScanWarps];
+  if (T::kStages < my_n) next_blk = bt_row[T::kStages * kScanWarps];
 
   // ---- query fragments: B operand of the K MMA, scaled by 2^-pos of the code it meets.
   //      Lane (head n = g, tig) covers channels 32 tig + 8 j + x (group j, code x); k-step x
   //      pairs groups (0,1) in b0 and (2,3) in b1.  A bf16 query is used as is; an fp16 query
   //      (11-bit significand) is split exactly into two bf16 terms, hi + lo. ----
-  constexpr int kQTerms = (DT == JF_DTYPE_FP16) ? 2 : 1;
-  uint32_t qf[kQTerms][8][2];
+  K3State<kQTerms> st;
   {
     const int h = hkv * p.G + g;
     const bool live = g < p.G;
@@ -185,116 +303,55 @@ scan_k3v2_kernel(const ScanParams p) {
         float a = 0.f, c = 0.f;
         if (live) { a = load_q<DT>(p.q, qbase + d0) * sc; c = load_q<DT>(p.q, qbase + d0 + 8) * sc; }
         const uint32_t hi2 = pack_bf16x2(a, c);
-        qf[0][x][half] = hi2;
+        st.qf[0][x][half] = hi2;
         if (kQTerms == 2) {
           const float ra = a - __uint_as_float(hi2 << 16), rc = c - __uint_as_float(hi2 & 0xFFFF0000u);
-          qf[kQTerms - 1][x][half] = pack_bf16x2(ra, rc);
+          st.qf[kQTerms - 1][x][half] = pack_bf16x2(ra, rc);
         }
       }
     }
   }
-  const uint32_t ks_sel = (tig >> 1) ? 0x3232u : 0x1010u;  // this lane's K group scale, in both halves
-
-  float oacc[8][4];
+  st.ks_sel = (tig >> 1) ? 0x3232u : 0x1010u;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
-  float m_ref0 = kMinusBig, m_ref1 = kMinusBig, l0 = 0.f, l1 = 0.f;
-  uint32_t smax_bits = 0u;  // largest K group scale seen by this lane (bf16 bits; positive floats order as integers)
+  for (int i = 0; i < 8; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
+  st.m_ref0 = kMinusBig; st.m_ref1 = kMinusBig; st.l0 = 0.f; st.l1 = 0.f;
+  st.smax_bits = 0u;
   bool failed = false;
 
   const int t0 = (g >> 1) | ((g & 1) << 2);  // token of MMA row g (rows g + 8 -> t0 + 8)
+  const uint32_t k_addr_off = T::kKOff + t0 * T::kKRow + tig * 4;
+  const uint32_t v_addr_off = T::kVOff + tig * T::kVRow + 2 * g;
+  const uint32_t s_addr_off = T::kKsOff + t0 * 4;
   const int h0 = hkv * p.G + 2 * tig;
-  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0;
+  float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0 +
+               static_cast<int64_t>(pg_begin + warp) * 16;
+  float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
 
+  int st_idx = 0;
+  uint32_t parity = 0u;
   for (int it = 0; it < my_n; ++it) {
-    const int st = it % T::kStages;
-    if (!mbar_wait(&bars[st], (it / T::kStages) & 1)) {
+    if (!mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + st_idx, parity)) {
       // give the copies that were already issued a short, bounded chance to land
       for (int j = it + 1; j < min(my_n, it + T::kStages); ++j)
-        mbar_wait(&bars[j % T::kStages], (j / T::kStages) & 1, 1000000ull);
+        mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + (j % T::kStages), (j / T::kStages) & 1, 1000000ull);
       failed = true;
       break;
     }
-    const uint8_t* sp = my_stages + st * T::kBytes;
-    const int valid = page_valid[st];
-    const int pg = pg_begin + warp + it * kScanWarps;
-
-    // ---------------- K: unpack + Q.K^T ----------------
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t ksw0 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + t0 * 4);
-    uint32_t ksw1 = *reinterpret_cast<const uint32_t*>(sp + T::kKsOff + (t0 + 8) * 4);
-    const uint32_t vsw0 = *reinterpret_cast<const uint32_t*>(sp + T::kVsOff + t0 * 4);
-    const uint32_t vsw1 = *reinterpret_cast<const uint32_t*>(sp + T::kVsOff + (t0 + 8) * 4);
-    float vs00 = __uint_as_float(vsw0 << 16), vs01 = __uint_as_float(vsw0 & 0xFFFF0000u);
-    float vs10 = __uint_as_float(vsw1 << 16), vs11 = __uint_as_float(vsw1 & 0xFFFF0000u);
-    if (valid < 16) {  // last page of the sequence: neutralise rows past the end
-      if (t0 >= valid) { ksw0 = 0u; vs00 = vs01 = 0.f; }
-      if (t0 + 8 >= valid) { ksw1 = 0u; vs10 = vs11 = 0.f; }
-    }
-    {
-      const uint32_t sc0 = prmt(ksw0, ksw0, ks_sel), sc1 = prmt(ksw1, ksw1, ks_sel);
-      smax_bits = max(smax_bits, max(sc0 & 0x7FFFu, sc1 & 0x7FFFu));
-      const uint32_t* row0 = reinterpret_cast<const uint32_t*>(sp + T::kKOff + t0 * T::kKRow) + tig;
-      const uint32_t* row1 = row0 + 8 * (T::kKRow / 4);
-      uint32_t R0[2][8], R1[2][8];
-      k3_unpack_row(row0[0], row0[4], row0[8], sc0, R0);
-      k3_unpack_row(row1[0], row1[4], row1[8], sc1, R1);
-#pragma unroll
-      for (int t = 0; t < kQTerms; ++t)
-#pragma unroll
-        for (int x = 0; x < 8; ++x)
-          mma_bf16_16816(acc, R0[0][x], R1[0][x], R0[1][x], R1[1][x], qf[t][x][0], qf[t][x][1]);
-    }
-
-    // ---------------- scores ----------------
-    float s0 = acc[0] * attn;  // row g,   head 2tig
-    float s1 = acc[1] * attn;  // row g,   head 2tig+1
-    float s2 = acc[2] * attn;  // row g+8, head 2tig
-    float s3 = acc[3] * attn;  // row g+8, head 2tig+1
-    if (valid < 16) {
-      if (t0 >= valid) { s0 = s1 = -INFINITY; }
-      if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; }
-    }
-    {
-      float* r0 = score_row0 + static_cast<int64_t>(pg) * 16;
-      const bool lo = t0 < valid, hi = t0 + 8 < valid;
-      if (st0 && lo) r0[0] = s0;
-      if (st0 && hi) r0[8] = s2;
-      if (st1 && lo) r0[p.max_S] = s1;
-      if (st1 && hi) r0[p.max_S + 8] = s3;
-    }
-
-    // ---------------- online softmax ----------------
-    float p0, p1, p2, p3;
-    softmax_step(s0, s1, s2, s3, m_ref0, m_ref1, l0, l1, oacc, p0, p1, p2, p3);
-
-    // ---------------- V: unpack + (P * vscale).V ----------------
-#pragma unroll
-    for (int qh = 0; qh < 2; ++qh) {
-      const float va = qh ? vs01 : vs00, vb = qh ? vs11 : vs10;
-      const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * va, p1 * va));  // tokens tig, tig+4
-      const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vb, p3 * vb));  // tokens tig+8, tig+12
-      const uint8_t* vbase = sp + T::kVOff + 16 * qh + 2 * g;
-      const uint32_t Ha = *reinterpret_cast<const uint16_t*>(vbase + (tig)*T::kVRow);
-      const uint32_t Hb = *reinterpret_cast<const uint16_t*>(vbase + (tig + 4) * T::kVRow);
-      const uint32_t Hc = *reinterpret_cast<const uint16_t*>(vbase + (tig + 8) * T::kVRow);
-      const uint32_t Hd = *reinterpret_cast<const uint16_t*>(vbase + (tig + 12) * T::kVRow);
-      const uint32_t XA = prmt(Ha, Hb, 0x5410), XB = prmt(Hc, Hd, 0x5410);
-      const uint32_t XA2 = XA >> 10, XB2 = XB >> 10;
-      // fields 2ml -> output row g, 2ml+1 -> output row g+8
-      mma_f16_16816(oacc[qh * 4 + 0], v2_field<0>(XA), v2_field<2>(XA), v2_field<0>(XB), v2_field<2>(XB), B0, B1);
-      mma_f16_16816(oacc[qh * 4 + 1], v2_field<4>(XA), v2_field<6>(XA), v2_field<4>(XB), v2_field<6>(XB), B0, B1);
-      mma_f16_16816(oacc[qh * 4 + 2], v2_field<8>(XA), v2_field<0>(XA2), v2_field<8>(XB), v2_field<0>(XB2), B0, B1);
-      mma_f16_16816(oacc[qh * 4 + 3], v2_field<2>(XA2), v2_field<4>(XA2), v2_field<2>(XB2), v2_field<4>(XB2), B0, B1);
-    }
-
+    const uint32_t sb = stages0 + st_idx * T::kBytes;
+    if (slow_mask & (1u << st_idx))
+      k3v2_page<kQTerms, true>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
+    else
+      k3v2_page<kQTerms, false>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, 16, attn, sp0, sp1, st0, st1);
     __syncwarp();
     if (it + T::kStages < my_n) {
-      issue(it + T::kStages, next_blk);
-      if (it + T::kStages + 1 < my_n) next_blk = bt_row[pg_begin + warp + (it + T::kStages + 1) * kScanWarps];
+      issue(it + T::kStages, st_idx, next_blk);
+      if (it + T::kStages + 1 < my_n) next_blk = bt_row[(it + T::kStages + 1) * kScanWarps];
     }
+    sp0 += 16 * kScanWarps;
+    sp1 += 16 * kScanWarps;
+    if (++st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
   if (failed && lane == 0) atomicExch(p.status, JF_ERR_TIMEOUT);
@@ -309,14 +366,15 @@ scan_k3v2_kernel(const ScanParams p) {
       const int fa = 2 * ml, fb = 2 * ml + 1;
       const int da = 64 * qh + 8 * g + v2_dlocal(fa), db = 64 * qh + 8 * g + v2_dlocal(fb);
       const float ua = 1.0f / static_cast<float>(1 << v2_pos(fa)), ub = 1.0f / static_cast<float>(1 << v2_pos(fb));
-      wo[(2 * tig) * JF_HEAD_DIM + da] = oacc[mt][0] * ua;
-      wo[(2 * tig + 1) * JF_HEAD_DIM + da] = oacc[mt][1] * ua;
-      wo[(2 * tig) * JF_HEAD_DIM + db] = oacc[mt][2] * ub;
-      wo[(2 * tig + 1) * JF_HEAD_DIM + db] = oacc[mt][3] * ub;
+      wo[(2 * tig) * JF_HEAD_DIM + da] = st.oacc[mt][0] * ua;
+      wo[(2 * tig + 1) * JF_HEAD_DIM + da] = st.oacc[mt][1] * ua;
+      wo[(2 * tig) * JF_HEAD_DIM + db] = st.oacc[mt][2] * ub;
+      wo[(2 * tig + 1) * JF_HEAD_DIM + db] = st.oacc[mt][3] * ub;
     }
   }
-  const float smax = __uint_as_float(smax_bits << 16);
-  cta_merge_store(p, smem, l0, l1, m_ref0, m_ref1, (tig >> 1) ? 0.f : smax, (tig >> 1) ? smax : 0.f, split, hkv, b);
+  const float smax = __uint_as_float(st.smax_bits << 16);
+  cta_merge_store(p, smem, st.l0, st.l1, st.m_ref0, st.m_ref1, (tig >> 1) ? 0.f : smax, (tig >> 1) ? smax : 0.f,
+                  split, hkv, b);
 }
 
 // ------------------------------------------------------------------------------------

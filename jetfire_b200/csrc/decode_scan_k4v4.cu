@@ -61,6 +61,109 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_u32(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint32_t v;  // a 32-bit destination is zero-extended by the 16-bit load
+  asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+
+struct K4State {
+  uint32_t qb[4][2];          // INT8 query fragments (B operand of the K MMA)
+  float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
+  int init_h0[4], init_h1[4]; // -8 * sum(qi) per block for those heads
+  float oacc[8][4];
+  float m_ref0, m_ref1, l0, l1;
+  uint32_t k_off[4];          // swizzled byte offsets of this lane's K words, per 32-channel block
+  uint32_t v_offA, v_offB;    // swizzled byte offsets of this lane's V words for tokens tA, tB
+  uint32_t s_off;             // byte offset of this lane's scale entries
+};
+
+// One 16-token page; kPartial as in the K3V2 kernel.
+template <bool kPartial>
+__device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int valid, float attn, float* sp0,
+                                          float* sp1, bool st0, bool st1) {
+  // ---------------- K: nibbles -> u8 fragments, exact integer Q.K^T per block ----------------
+  int acc[4][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t a = sb + st.k_off[c];
+    const uint32_t w0 = lds32<0>(a), w1 = lds32<512>(a);
+    const int init[4] = {st.init_h0[c], st.init_h1[c], st.init_h0[c], st.init_h1[c]};
+    mma_u8s8_cd(acc[c], init, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu,
+                st.qb[c][0], st.qb[c][1]);
+  }
+  const uint32_t sa = sb + st.s_off;
+  const float ks0 = __uint_as_float(lds16<0>(sa) << 16), ks1 = __uint_as_float(lds16<16>(sa) << 16);
+  float vs0 = __uint_as_float(lds16<32>(sa) << 16), vs1 = __uint_as_float(lds16<48>(sa) << 16);
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    s0 = __fmaf_rn(static_cast<float>(acc[c][0]), st.qs_h0[c], s0);
+    s1 = __fmaf_rn(static_cast<float>(acc[c][1]), st.qs_h1[c], s1);
+    s2 = __fmaf_rn(static_cast<float>(acc[c][2]), st.qs_h0[c], s2);
+    s3 = __fmaf_rn(static_cast<float>(acc[c][3]), st.qs_h1[c], s3);
+  }
+  s0 = __fmul_rn(__fmul_rn(s0, ks0), attn);
+  s1 = __fmul_rn(__fmul_rn(s1, ks0), attn);
+  s2 = __fmul_rn(__fmul_rn(s2, ks1), attn);
+  s3 = __fmul_rn(__fmul_rn(s3, ks1), attn);
+  if (kPartial) {
+    const bool lo = t0 < valid, hi = t0 + 8 < valid;
+    if (!lo) { s0 = s1 = -INFINITY; vs0 = 0.f; }
+    if (!hi) { s2 = s3 = -INFINITY; vs1 = 0.f; }
+    if (st0 && lo) sp0[0] = s0;
+    if (st0 && hi) sp0[8] = s2;
+    if (st1 && lo) sp1[0] = s1;
+    if (st1 && hi) sp1[8] = s3;
+  } else {
+    if (st0) { sp0[0] = s0; sp0[8] = s2; }
+    if (st1) { sp1[0] = s1; sp1[8] = s3; }
+  }
+
+  // ---------------- online softmax ----------------
+  float p0, p1, p2, p3;
+  softmax_step(s0, s1, s2, s3, st.m_ref0, st.m_ref1, st.l0, st.l1, st.oacc, p0, p1, p2, p3);
+
+  // ---------------- V: nibbles -> fp16 fragments, (P * vscale).V ----------------
+  const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * vs0, p1 * vs0));  // tokens tA, tB
+  const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vs1, p3 * vs1));  // tokens tA+8, tB+8
+  const uint32_t aA = sb + st.v_offA, aB = sb + st.v_offB;
+  const uint2 Wa = lds64<0>(aA), Wb = lds64<0>(aB), Wc = lds64<512>(aA), Wd = lds64<512>(aB);
+  const uint32_t wa[2] = {Wa.x, Wa.y}, wb[2] = {Wb.x, Wb.y}, wc[2] = {Wc.x, Wc.y}, wd[2] = {Wd.x, Wd.y};
+#pragma unroll
+  for (int wi = 0; wi < 2; ++wi) {
+#pragma unroll
+    for (int bp = 0; bp < 2; ++bp) {
+      const uint32_t sel = bp ? 0x7632u : 0x5410u;
+      const uint32_t XA = prmt(wa[wi], wb[wi], sel), XB = prmt(wc[wi], wd[wi], sel);
+      const uint32_t XA2 = XA >> 8, XB2 = XB >> 8;
+      const int mt = 4 * wi + 2 * bp;
+      // low nibble -> output row g, high nibble -> output row g + 8
+      mma_f16_16816(st.oacc[mt], v4_field<0>(XA), v4_field<4>(XA), v4_field<0>(XB), v4_field<4>(XB), B0, B1);
+      mma_f16_16816(st.oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), B0, B1);
+    }
+  }
+}
 
 }  // namespace
 
@@ -71,11 +174,13 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // swizzled tiles must sit on 512-byte boundaries: align by hand (1 KB of slack is allocated)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // uniform by construction
   const int g = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
 
-  uint8_t* my_stages = smem + warp * (T4::kStages * T4::kBytes);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t stages0 = smem_base + warp * (T4::kStages * T4::kBytes);
+  const uint32_t bars0 = smem_base + kScanWarps * T4::kStages * T4::kBytes + warp * (T4::kStages * 8);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * T4::kStages * T4::kBytes) + warp * T4::kStages;
   int32_t* page_valid =
       reinterpret_cast<int32_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8)) + warp * T4::kStages;
@@ -92,43 +197,44 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   fence_barrier_init();
   __syncwarp();
 
-  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
   const int64_t n_blocks_phys = p.num_slots >> 4;
   const int64_t row_base = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
   const uint16_t* ks_h = p.k_scales + row_base;
   const uint16_t* vs_h = p.v_scales + row_base;
+  const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
+  uint32_t slow_mask = 0u;
 
-  // Lanes 0/1 issue the K/V tensor copies, lanes 2/3 the two scale copies; what differs
-  // between the lanes of a pair is data (map, offsets), not control flow.
-  const CUtensorMap* my_map = (lane & 1) ? &v_map : &k_map;
-  const uint32_t my_dst_off = (lane < 2) ? (lane ? T4::kVOff : T4::kKOff) : ((lane & 1) ? T4::kVsOff : T4::kKsOff);
-  const uint16_t* my_scales = (lane & 1) ? vs_h : ks_h;
-  auto issue = [&](int it, int64_t blk) {
-    const int st = it % T4::kStages;
+  // One elected lane issues the page's two tensor copies (K, V) and two scale copies.
+  auto issue = [&](int it, int st_idx, int64_t blk64) {
     const int pg = pg_begin + warp + it * kScanWarps;
-    int valid = min(16, len - pg * 16);
-    if (blk < 0 || blk >= n_blocks_phys) { blk = 0; valid = 0; }
-    uint8_t* dst = my_stages + st * T4::kBytes + my_dst_off;
-    if (lane == 0) {
-      page_valid[st] = valid;
-      mbar_expect_tx(&bars[st], T4::kTxBytes);
+    const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
+    const bool slow = bad || pg == last_pg;
+    slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
+    const int64_t blk = bad ? 0 : blk64;
+    const uint32_t bar = bars0 + st_idx * 8;
+    const uint32_t dst = stages0 + st_idx * T4::kBytes;
+    if (elect_one()) {
+      if (slow) page_valid[st_idx] = bad ? 0 : min(16, len - pg * 16);
+      mbar_expect_tx_u32(bar, T4::kTxBytes);
+      const int y = static_cast<int>(row_base + blk * 16);
+      tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, y, bar);
+      tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, y, bar);
+      bulk_g2s_u32(dst + T4::kKsOff, ks_h + blk * 16, 32, bar);
+      bulk_g2s_u32(dst + T4::kVsOff, vs_h + blk * 16, 32, bar);
     }
-    if (lane < 2) tma_load_2d(dst, my_map, 0, static_cast<int>(row_base + blk * 16), &bars[st]);
-    else if (lane < 4) bulk_g2s(dst, my_scales + blk * 16, 32, &bars[st]);
   };
 
   {
     const int pro = min(T4::kStages, my_n);
-    for (int it = 0; it < pro; ++it) issue(it, bt_row[pg_begin + warp + it * kScanWarps]);
+    for (int it = 0; it < pro; ++it) issue(it, it, bt_row[it * kScanWarps]);
   }
   int64_t next_blk = 0;
-  if (T4::kStages < my_n) next_blk = bt_row[pg_begin + warp + T4::kStages * kScanWarps];
+  if (T4::kStages < my_n) next_blk = bt_row[T4::kStages * kScanWarps];
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
   //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones. ----
-  uint32_t qb[4][2];
-  float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
-  int init_h0[4], init_h1[4]; // -8 * sum(qi) per block for those heads
+  K4State st;
   {
     const int h = hkv * p.G + g;
     const bool live = g < p.G;
@@ -154,121 +260,57 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       }
       sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
       sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-      qb[c][0] = (qi[0] & 255) | ((qi[2] & 255) << 8) | ((qi[4] & 255) << 16) | ((qi[6] & 255) << 24);
-      qb[c][1] = (qi[1] & 255) | ((qi[3] & 255) << 8) | ((qi[5] & 255) << 16) | ((qi[7] & 255) << 24);
-      qs_h0[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig);
-      qs_h1[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig + 4);
-      init_h0[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig);
-      init_h1[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig + 4);
+      st.qb[c][0] = (qi[0] & 255) | ((qi[2] & 255) << 8) | ((qi[4] & 255) << 16) | ((qi[6] & 255) << 24);
+      st.qb[c][1] = (qi[1] & 255) | ((qi[3] & 255) << 8) | ((qi[5] & 255) << 16) | ((qi[7] & 255) << 24);
+      st.qs_h0[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig);
+      st.qs_h1[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig + 4);
+      st.init_h0[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig);
+      st.init_h1[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig + 4);
     }
   }
-
-  float oacc[8][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
-  float m_ref0 = kMinusBig, m_ref1 = kMinusBig, l0 = 0.f, l1 = 0.f;
+  for (int i = 0; i < 8; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
+  st.m_ref0 = kMinusBig; st.m_ref1 = kMinusBig; st.l0 = 0.f; st.l1 = 0.f;
   bool failed = false;
 
   const int t0 = row_token(g);                 // token of MMA row g (row g + 8 -> t0 + 8)
-  const int ksw = (t0 >> 1) & 3;               // swizzle term of rows t0 and t0 + 8
-  const int tA = row_token(2 * tig), tB = row_token(2 * tig + 1);  // tokens of P.V k-slots
+  {
+    const int ksw = (t0 >> 1) & 3;             // swizzle term of rows t0 and t0 + 8
+    const int tA = row_token(2 * tig), tB = row_token(2 * tig + 1);  // tokens of P.V k-slots
+    const int vchunk = g >> 1, vsub = 8 * (g & 1);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st.k_off[c] = T4::kKOff + t0 * 64 + 4 * tig + ((c ^ ksw) << 4);
+    st.v_offA = T4::kVOff + tA * 64 + ((vchunk ^ ((tA >> 1) & 3)) << 4) + vsub;
+    st.v_offB = T4::kVOff + tB * 64 + ((vchunk ^ ((tB >> 1) & 3)) << 4) + vsub;
+    st.s_off = T4::kKsOff + t0 * 2;
+  }
   const int h0 = hkv * p.G + 2 * tig;
-  float* score_row0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0;
+  float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0 +
+               static_cast<int64_t>(pg_begin + warp) * 16;
+  float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
-  // byte offsets of this lane's V words inside a token row, swizzled per token below
-  const int vchunk = g >> 1, vsub = 8 * (g & 1);
 
+  int st_idx = 0;
+  uint32_t parity = 0u;
   for (int it = 0; it < my_n; ++it) {
-    const int st = it % T4::kStages;
-    if (!mbar_wait(&bars[st], (it / T4::kStages) & 1)) {
+    if (!mbar_wait(&bars[st_idx], parity)) {
       for (int j = it + 1; j < min(my_n, it + T4::kStages); ++j)
         mbar_wait(&bars[j % T4::kStages], (j / T4::kStages) & 1, 1000000ull);
       failed = true;
       break;
     }
-    const uint8_t* sp = my_stages + st * T4::kBytes;
-    const int valid = page_valid[st];
-    const int pg = pg_begin + warp + it * kScanWarps;
-
-    // ---------------- K: nibbles -> u8 fragments, exact integer Q.K^T per block ----------------
-    int acc[4][4];
-    {
-      const uint8_t* r0 = sp + T4::kKOff + t0 * 64 + 4 * tig;
-      const uint8_t* r1 = r0 + 512;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int off = (c ^ ksw) << 4;
-        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(r0 + off);
-        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(r1 + off);
-        const int init[4] = {init_h0[c], init_h1[c], init_h0[c], init_h1[c]};
-        mma_u8s8_cd(acc[c], init, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu,
-                    w1 & 0x0F0F0F0Fu, qb[c][0], qb[c][1]);
-      }
-    }
-    float ks0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kKsOff + t0 * 2));
-    float ks1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kKsOff + (t0 + 8) * 2));
-    float vs0 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kVsOff + t0 * 2));
-    float vs1 = bf16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + T4::kVsOff + (t0 + 8) * 2));
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      s0 = __fmaf_rn(static_cast<float>(acc[c][0]), qs_h0[c], s0);
-      s1 = __fmaf_rn(static_cast<float>(acc[c][1]), qs_h1[c], s1);
-      s2 = __fmaf_rn(static_cast<float>(acc[c][2]), qs_h0[c], s2);
-      s3 = __fmaf_rn(static_cast<float>(acc[c][3]), qs_h1[c], s3);
-    }
-    s0 = __fmul_rn(__fmul_rn(s0, ks0), attn);
-    s1 = __fmul_rn(__fmul_rn(s1, ks0), attn);
-    s2 = __fmul_rn(__fmul_rn(s2, ks1), attn);
-    s3 = __fmul_rn(__fmul_rn(s3, ks1), attn);
-    if (valid < 16) {
-      if (t0 >= valid) { s0 = s1 = -INFINITY; vs0 = 0.f; }
-      if (t0 + 8 >= valid) { s2 = s3 = -INFINITY; vs1 = 0.f; }
-    }
-    {
-      float* r0 = score_row0 + static_cast<int64_t>(pg) * 16;
-      const bool lo = t0 < valid, hi = t0 + 8 < valid;
-      if (st0 && lo) r0[0] = s0;
-      if (st0 && hi) r0[8] = s2;
-      if (st1 && lo) r0[p.max_S] = s1;
-      if (st1 && hi) r0[p.max_S + 8] = s3;
-    }
-
-    // ---------------- online softmax ----------------
-    float p0, p1, p2, p3;
-    softmax_step(s0, s1, s2, s3, m_ref0, m_ref1, l0, l1, oacc, p0, p1, p2, p3);
-
-    // ---------------- V: nibbles -> fp16 fragments, (P * vscale).V ----------------
-    {
-      const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * vs0, p1 * vs0));  // tokens tA, tB
-      const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vs1, p3 * vs1));  // tokens tA+8, tB+8
-      const uint8_t* vb = sp + T4::kVOff + vsub;
-      const uint2 Wa = *reinterpret_cast<const uint2*>(vb + tA * 64 + ((vchunk ^ ((tA >> 1) & 3)) << 4));
-      const uint2 Wb = *reinterpret_cast<const uint2*>(vb + tB * 64 + ((vchunk ^ ((tB >> 1) & 3)) << 4));
-      const uint2 Wc = *reinterpret_cast<const uint2*>(vb + 512 + tA * 64 + ((vchunk ^ ((tA >> 1) & 3)) << 4));
-      const uint2 Wd = *reinterpret_cast<const uint2*>(vb + 512 + tB * 64 + ((vchunk ^ ((tB >> 1) & 3)) << 4));
-      const uint32_t wa[2] = {Wa.x, Wa.y}, wb[2] = {Wb.x, Wb.y}, wc[2] = {Wc.x, Wc.y}, wd[2] = {Wd.x, Wd.y};
-#pragma unroll
-      for (int wi = 0; wi < 2; ++wi) {
-#pragma unroll
-        for (int bp = 0; bp < 2; ++bp) {
-          const uint32_t sel = bp ? 0x7632u : 0x5410u;
-          const uint32_t XA = prmt(wa[wi], wb[wi], sel), XB = prmt(wc[wi], wd[wi], sel);
-          const uint32_t XA2 = XA >> 8, XB2 = XB >> 8;
-          const int mt = 4 * wi + 2 * bp;
-          // low nibble -> output row g, high nibble -> output row g + 8
-          mma_f16_16816(oacc[mt], v4_field<0>(XA), v4_field<4>(XA), v4_field<0>(XB), v4_field<4>(XB), B0, B1);
-          mma_f16_16816(oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), B0, B1);
-        }
-      }
-    }
-
+    const uint32_t sb = stages0 + st_idx * T4::kBytes;
+    if (slow_mask & (1u << st_idx)) k4v4_page<true>(st, sb, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
+    else k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
     __syncwarp();
     if (it + T4::kStages < my_n) {
-      issue(it + T4::kStages, next_blk);
-      if (it + T4::kStages + 1 < my_n) next_blk = bt_row[pg_begin + warp + (it + T4::kStages + 1) * kScanWarps];
+      issue(it + T4::kStages, st_idx, next_blk);
+      if (it + T4::kStages + 1 < my_n) next_blk = bt_row[(it + T4::kStages + 1) * kScanWarps];
     }
+    sp0 += 16 * kScanWarps;
+    sp1 += 16 * kScanWarps;
+    if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
   if (failed && lane == 0) atomicExch(p.status, JF_ERR_TIMEOUT);
@@ -281,13 +323,13 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       const int wi = mt >> 2, bp = (mt >> 1) & 1, e = mt & 1;
       const int dlo = 16 * g + 8 * wi + 4 * bp + 2 * e + 1;  // low nibble of the byte: odd channel
       const int dhi = dlo - 1;                               // high nibble: even channel
-      wo[(2 * tig) * JF_HEAD_DIM + dlo] = oacc[mt][0];
-      wo[(2 * tig + 1) * JF_HEAD_DIM + dlo] = oacc[mt][1];
-      wo[(2 * tig) * JF_HEAD_DIM + dhi] = oacc[mt][2] * 0.0625f;
-      wo[(2 * tig + 1) * JF_HEAD_DIM + dhi] = oacc[mt][3] * 0.0625f;
+      wo[(2 * tig) * JF_HEAD_DIM + dlo] = st.oacc[mt][0];
+      wo[(2 * tig + 1) * JF_HEAD_DIM + dlo] = st.oacc[mt][1];
+      wo[(2 * tig) * JF_HEAD_DIM + dhi] = st.oacc[mt][2] * 0.0625f;
+      wo[(2 * tig + 1) * JF_HEAD_DIM + dhi] = st.oacc[mt][3] * 0.0625f;
     }
   }
-  cta_merge_store(p, smem, l0, l1, m_ref0, m_ref1, 0.f, 0.f, split, hkv, b);
+  cta_merge_store(p, smem, st.l0, st.l1, st.m_ref0, st.m_ref1, 0.f, 0.f, split, hkv, b);
 }
 
 // ---- tensor maps -----------------------------------------------------------------------
