@@ -48,6 +48,7 @@ WORKLOADS = {
 }
 BYTES_PER_TOKEN_HEAD = {"k3v2": 88, "k4v4": 132}
 MODE_BITS = {"k3v2": (3, 2, 64), "k4v4": (4, 4, 128)}
+DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 93.4, "k4v4": 142.6}   # measured with ncu, see profiles/
 
 
 def parse_args():
@@ -427,13 +428,10 @@ def main():
                 "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s",
                 "unit": "GB/s", "frac": achieved / peak, "us_per_launch": scan_ms * 1e3,
                 "algorithmic_bytes_per_launch": layer_bytes(w), "traffic": None}
-    try:
-        prof = json.loads((ROOT / "profiles" / "traffic.json").read_text())
-        key = f"scan_{w['mode']}"
-        if key in prof:  # DRAM bytes per (token, kv-head) from an ncu capture, scaled to this launch
-            roofline["traffic"] = prof[key]["dram_bytes_per_token_head"] * w["batch"] * w["H_kv"] * w["ctx"]
-    except Exception:
-        pass
+    # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the scan kernel, per
+    # (token, KV head), scaled to this launch by the units it processes (traffic grows in
+    # proportion); figures and commands: profiles/scan_k4v4_b4_ctx32k.md, scan_k3v2_b4_ctx32k.md
+    roofline["traffic"] = DRAM_BYTES_PER_TOKEN_HEAD[w["mode"]] * w["batch"] * w["H_kv"] * w["ctx"]
 
     # ---- end to end with the host in the loop ----
     e2e = None
