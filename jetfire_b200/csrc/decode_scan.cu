@@ -151,14 +151,23 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
     if (t0 >= valid) { ksw0 = 0u; vs00 = vs01 = 0.f; }
     if (t0 + 8 >= valid) { ksw1 = 0u; vs10 = vs11 = 0.f; }
   }
+  // all shared-memory reads of the page are issued up front (the loads keep their source order)
+  const uint32_t ka = sb + k_addr_off;
+  const uint32_t kw0 = lds32<0>(ka), kw1 = lds32<16>(ka), kw2 = lds32<32>(ka);
+  const uint32_t kw3 = lds32<8 * T::kKRow>(ka), kw4 = lds32<8 * T::kKRow + 16>(ka), kw5 = lds32<8 * T::kKRow + 32>(ka);
+  const uint32_t va_addr = sb + v_addr_off;
+  uint32_t vh[2][4];
+  vh[0][0] = lds16<0>(va_addr); vh[0][1] = lds16<4 * T::kVRow>(va_addr);
+  vh[0][2] = lds16<8 * T::kVRow>(va_addr); vh[0][3] = lds16<12 * T::kVRow>(va_addr);
+  vh[1][0] = lds16<16>(va_addr); vh[1][1] = lds16<4 * T::kVRow + 16>(va_addr);
+  vh[1][2] = lds16<8 * T::kVRow + 16>(va_addr); vh[1][3] = lds16<12 * T::kVRow + 16>(va_addr);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   {
     const uint32_t sc0 = prmt(ksw0, ksw0, st.ks_sel), sc1 = prmt(ksw1, ksw1, st.ks_sel);
     st.smax_bits = max(st.smax_bits, max(sc0 & 0x7FFFu, sc1 & 0x7FFFu));
-    const uint32_t ka = sb + k_addr_off;
     uint32_t R0[2][8], R1[2][8];
-    k3_unpack_row(lds32<0>(ka), lds32<16>(ka), lds32<32>(ka), sc0, R0);
-    k3_unpack_row(lds32<8 * T::kKRow>(ka), lds32<8 * T::kKRow + 16>(ka), lds32<8 * T::kKRow + 32>(ka), sc1, R1);
+    k3_unpack_row(kw0, kw1, kw2, sc0, R0);
+    k3_unpack_row(kw3, kw4, kw5, sc1, R1);
 #pragma unroll
     for (int t = 0; t < QT; ++t)
 #pragma unroll
@@ -189,20 +198,12 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
   softmax_step(s0, s1, s2, s3, st.m_ref0, st.m_ref1, st.l0, st.l1, st.oacc, p0, p1, p2, p3);
 
   // ---------------- V: unpack + (P * vscale).V ----------------
-  const uint32_t va_addr = sb + v_addr_off;
 #pragma unroll
   for (int qh = 0; qh < 2; ++qh) {
     const float va = qh ? vs01 : vs00, vb = qh ? vs11 : vs10;
     const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * va, p1 * va));  // tokens tig, tig+4
     const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vb, p3 * vb));  // tokens tig+8, tig+12
-    uint32_t Ha, Hb, Hc, Hd;
-    if (qh == 0) {
-      Ha = lds16<0>(va_addr); Hb = lds16<4 * T::kVRow>(va_addr);
-      Hc = lds16<8 * T::kVRow>(va_addr); Hd = lds16<12 * T::kVRow>(va_addr);
-    } else {
-      Ha = lds16<16>(va_addr); Hb = lds16<4 * T::kVRow + 16>(va_addr);
-      Hc = lds16<8 * T::kVRow + 16>(va_addr); Hd = lds16<12 * T::kVRow + 16>(va_addr);
-    }
+    const uint32_t Ha = vh[qh][0], Hb = vh[qh][1], Hc = vh[qh][2], Hd = vh[qh][3];
     const uint32_t XA = join16(Ha, Hb), XB = join16(Hc, Hd);
     const uint32_t XA2 = XA >> 10, XB2 = XB >> 10;
     // fields 2ml -> output row g, 2ml+1 -> output row g+8
@@ -294,14 +295,25 @@ scan_k3v2_kernel(const ScanParams p) {
     const int h = hkv * p.G + g;
     const bool live = g < p.G;
     const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + h) * JF_HEAD_DIM;
+    // this lane's 32 channels are contiguous: four 16-byte loads
+    uint32_t qraw[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (live) v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + qbase + 32 * tig) + i);
+      qraw[4 * i] = v.x; qraw[4 * i + 1] = v.y; qraw[4 * i + 2] = v.z; qraw[4 * i + 3] = v.w;
+    }
+    auto qval = [&](int d) {  // channel 32 tig + d of this lane's head
+      const uint32_t w = qraw[d >> 1];
+      return Elem<DT>::to_f32(static_cast<uint16_t>((d & 1) ? (w >> 16) : (w & 0xFFFFu)));
+    };
 #pragma unroll
     for (int x = 0; x < 8; ++x) {
       const float sc = 1.0f / static_cast<float>(1 << k3_pos(x));
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int d0 = 32 * tig + 16 * half + x;  // group j = 2 * half
-        float a = 0.f, c = 0.f;
-        if (live) { a = load_q<DT>(p.q, qbase + d0) * sc; c = load_q<DT>(p.q, qbase + d0 + 8) * sc; }
+        const int d0 = 16 * half + x;  // group j = 2 * half
+        const float a = qval(d0) * sc, c = qval(d0 + 8) * sc;
         const uint32_t hi2 = pack_bf16x2(a, c);
         st.qf[0][x][half] = hi2;
         if (kQTerms == 2) {

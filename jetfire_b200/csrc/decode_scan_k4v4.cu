@@ -103,18 +103,27 @@ template <bool kPartial>
 __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int valid, float attn, float* sp0,
                                           float* sp1, bool st0, bool st1) {
   // ---------------- K: nibbles -> u8 fragments, exact integer Q.K^T per block ----------------
-  int acc[4][4];
+  // all shared-memory reads of the page are issued up front
+  uint32_t kw[4][2];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const uint32_t a = sb + st.k_off[c];
-    const uint32_t w0 = lds32<0>(a), w1 = lds32<512>(a);
+    kw[c][0] = lds32<0>(a); kw[c][1] = lds32<512>(a);
+  }
+  const uint32_t sa = sb + st.s_off;
+  const uint32_t ksb0 = lds16<0>(sa), ksb1 = lds16<16>(sa), vsb0 = lds16<32>(sa), vsb1 = lds16<48>(sa);
+  const uint32_t aA = sb + st.v_offA, aB = sb + st.v_offB;
+  const uint2 Wa = lds64<0>(aA), Wb = lds64<0>(aB), Wc = lds64<512>(aA), Wd = lds64<512>(aB);
+  int acc[4][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t w0 = kw[c][0], w1 = kw[c][1];
     const int init[4] = {st.init_h0[c], st.init_h1[c], st.init_h0[c], st.init_h1[c]};
     mma_u8s8_cd(acc[c], init, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu,
                 st.qb[c][0], st.qb[c][1]);
   }
-  const uint32_t sa = sb + st.s_off;
-  const float ks0 = __uint_as_float(lds16<0>(sa) << 16), ks1 = __uint_as_float(lds16<16>(sa) << 16);
-  float vs0 = __uint_as_float(lds16<32>(sa) << 16), vs1 = __uint_as_float(lds16<48>(sa) << 16);
+  const float ks0 = __uint_as_float(ksb0 << 16), ks1 = __uint_as_float(ksb1 << 16);
+  float vs0 = __uint_as_float(vsb0 << 16), vs1 = __uint_as_float(vsb1 << 16);
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -147,8 +156,6 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
   // ---------------- V: nibbles -> fp16 fragments, (P * vscale).V ----------------
   const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * vs0, p1 * vs0));  // tokens tA, tB
   const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vs1, p3 * vs1));  // tokens tA+8, tB+8
-  const uint32_t aA = sb + st.v_offA, aB = sb + st.v_offB;
-  const uint2 Wa = lds64<0>(aA), Wb = lds64<0>(aB), Wc = lds64<512>(aA), Wd = lds64<512>(aB);
   const uint32_t wa[2] = {Wa.x, Wa.y}, wb[2] = {Wb.x, Wb.y}, wc[2] = {Wc.x, Wc.y}, wd[2] = {Wd.x, Wd.y};
 #pragma unroll
   for (int wi = 0; wi < 2; ++wi) {
@@ -243,9 +250,12 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     for (int c = 0; c < 4; ++c) {
       float v[8];
       float amax = 0.f;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);  // the 8 channels are 16 contiguous bytes
+      if (live) raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + qbase + 32 * c + 8 * tig));
+      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        v[j] = live ? load_q<DT>(p.q, qbase + 32 * c + 8 * tig + j) : 0.f;
+        v[j] = Elem<DT>::to_f32(static_cast<uint16_t>((j & 1) ? (rw[j >> 1] >> 16) : (rw[j >> 1] & 0xFFFFu)));
         amax = fmaxf(amax, fabsf(v[j]));
       }
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));

@@ -122,9 +122,13 @@ __device__ __forceinline__ uint64_t canon_key_global(const RowCtx& c, int pos, i
   return make_key(s, pos);
 }
 
-__device__ __forceinline__ int score_bin(float top, float s) {
-  const float x = (top - s) * kBinsPerUnit;
-  return (x >= static_cast<float>(kBins - 1)) ? (kBins - 1) : max(0, static_cast<int>(x));
+// Bin of a score: floor((top - s) * 64) clamped to [0, kBins - 1]; `top64` = top * 64.
+// float -> int without a conversion instruction: adding 2^23 with round-toward-zero leaves
+// floor(x) in the low mantissa bits (0 <= x < 2^11 here).
+__device__ __forceinline__ float score_binf(float top64, float s) { return fmaf(s, -kBinsPerUnit, top64); }
+__device__ __forceinline__ int score_bin(float top64, float s) {
+  const float x = fminf(fmaxf(score_binf(top64, s), 0.0f), static_cast<float>(kBins - 1));
+  return __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
 }
 
 constexpr int kRowChunk = 512;                 // candidates staged in shared memory per round
@@ -232,6 +236,7 @@ topk_select_kernel(const TopkParams p) {
       top = fmaxf(top, sh_w3[w][0]); sm0 = fmaxf(sm0, sh_w3[w][1]); sm1 = fmaxf(sm1, sh_w3[w][2]);
     }
     top += 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
+    const float top64 = top * kBinsPerUnit;
     float delta = 0.f;
     if (MODE == JF_MODE_K3V2) {
       // The scan and the canonical order add the same exact products q_d * k_hat_d in fp32,
@@ -271,7 +276,7 @@ topk_select_kernel(const TopkParams p) {
       load_chunk(ci);
 #pragma unroll
       for (int e = 0; e < kScoreRegs; ++e)
-        if (pos_of(ci, e) < n) atomicAdd(&hist[score_bin(top, sc[e])], 1);
+        if (pos_of(ci, e) < n) atomicAdd(&hist[score_bin(top64, sc[e])], 1);
     }
     __syncthreads();
     {
@@ -315,13 +320,13 @@ topk_select_kernel(const TopkParams p) {
     __syncthreads();
     if (!sh_fallback) {
       // ---- tier 2: collect the band (positions into keys[]) ----
-      const int last = sh_last;
+      const float xlim = static_cast<float>(sh_last + 1);  // bin <= last  <=>  (top - s) * 64 < last + 1
       for (int ci = 0; ci < n_chunks; ++ci) {
         if (n_chunks > 1) load_chunk(ci);
 #pragma unroll
         for (int e = 0; e < kScoreRegs; ++e) {
           const int pp = pos_of(ci, e);
-          if (pp < n && score_bin(top, sc[e]) <= last) {
+          if (pp < n && score_binf(top64, sc[e]) < xlim) {
             const int slot = atomicAdd(&sh_ncand, 1);
             if (slot < p.sort_n) keys[slot] = static_cast<uint64_t>(pp);
           }
@@ -417,15 +422,20 @@ topk_select_kernel(const TopkParams p) {
   // ---- order the candidates: best first ----
   uint64_t* ranked = keys;
   if (p.sort_n <= 1024) {
-    // rank by counting (keys are unique): no barriers, one pass over <= 1024 keys per thread
+    // rank by counting (keys are unique): thread (c, part) counts the keys above candidate c in
+    // its share of the list; the partial counts of a candidate are added by a shuffle
+    const int parts = (ncand <= kTopkThreads / 4) ? 4 : ((ncand <= kTopkThreads / 2) ? 2 : 1);
+    const int c = tid / parts, part = tid - c * parts;
     uint64_t mine = 0ull;
     int rank = 0;
-    if (tid < ncand) {
-      mine = keys[tid];
-      for (int j = 0; j < ncand; ++j) rank += (keys[j] > mine) ? 1 : 0;
+    if (c < ncand) {
+      mine = keys[c];
+      for (int j = part; j < ncand; j += parts) rank += (keys[j] > mine) ? 1 : 0;
     }
+    if (parts >= 2) rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
+    if (parts == 4) rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
     __syncthreads();
-    if (tid < ncand) keys[rank] = mine;
+    if (c < ncand && part == 0) keys[rank] = mine;
     __syncthreads();
   } else {
     // bitonic sort, descending, sort_n a power of two
