@@ -10,8 +10,9 @@
 // written to mapped (write-combined) memory are visible to the GPU.
 //
 // Differences: plain C ABI, no torch types; the AVX-512-BF16 path is selected at run time
-// (function multiversioning) so one binary runs on hosts with and without it; fp16
-// mirrors are supported; workers park on a condition variable after a short spin.
+// so one binary runs on hosts with and without it; fp16 mirrors are supported; the SIMD
+// path makes two prefetched passes (K rows, then V rows) instead of staging V; workers
+// park on a condition variable after a short spin.
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -163,58 +164,127 @@ void row_generic(const Job& j, Scratch& sc, int64_t b, int64_t h) {
   finish_row(j, sc, j.o + bh * D, any_valid, max_score);
 }
 
-// AVX-512 + BF16 dot-product path for bf16 mirrors: vdpbf16ps accumulates pairs of bf16
-// products in fp32, as the reference's SIMD kernel does; rows are prefetched 8 ahead.
-__attribute__((target("avx512f,avx512bw,avx512vl,avx512bf16")))
-void row_avx512bf16(const Job& j, Scratch& sc, int64_t b, int64_t h) {
+// AVX-512 path (bf16 mirrors use vdpbf16ps, which accumulates pairs of bf16 products in
+// fp32 as the reference's SIMD kernel does; fp16 mirrors convert and use fp32 FMAs).
+// Two passes over the selected rows, each with software prefetch running ahead: pass 1
+// reads the K rows and produces the scores, pass 2 reads the V rows and accumulates
+// sum p * V in eight zmm registers straight from the 16-bit rows, so nothing is staged.
+#define JF_AVX512 __attribute__((target("avx512f,avx512bw,avx512vl,avx512bf16")))
+
+// exp(x) for x <= 0 (x = -inf gives 0): x = n ln2 + r, |r| <= ln2 / 2, degree-7 Taylor
+// polynomial in r (truncation error 5e-9 relative), scaled by 2^n with vscalefps.
+JF_AVX512 inline __m512 exp_nonpos(__m512 x) {
+  const __mmask16 dead = _mm512_cmp_ps_mask(x, _mm512_set1_ps(-104.f), _CMP_LT_OQ);
+  x = _mm512_max_ps(_mm512_set1_ps(-104.f), x);  // keeps a NaN in x
+  const __m512 n = _mm512_roundscale_ps(_mm512_mul_ps(x, _mm512_set1_ps(1.44269504088896341f)),
+                                        _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
+  __m512 r = _mm512_fnmadd_ps(n, _mm512_set1_ps(0.693145751953125f), x);
+  r = _mm512_fnmadd_ps(n, _mm512_set1_ps(1.42860682030941723e-6f), r);
+  __m512 p = _mm512_set1_ps(1.f / 5040.f);
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(1.f / 720.f));
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(1.f / 120.f));
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(1.f / 24.f));
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(1.f / 6.f));
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(0.5f));
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(1.f));
+  p = _mm512_fmadd_ps(p, r, _mm512_set1_ps(1.f));
+  return _mm512_mask_blend_ps(dead, _mm512_scalef_ps(p, n), _mm512_setzero_ps());
+}
+
+template <int DT>
+JF_AVX512 inline __m512 load16(const uint16_t* p) {
+  const __m256i raw = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(p));
+  if (DT == JF_DTYPE_BF16) return _mm512_castsi512_ps(_mm512_slli_epi32(_mm512_cvtepu16_epi32(raw), 16));
+  return _mm512_cvtph_ps(raw);
+}
+
+template <int DT>
+JF_AVX512 void row_avx512(const Job& j, Scratch& sc, int64_t b, int64_t h) {
+  constexpr int kAhead = 8;
   const int K = j.K;
   const int64_t bh = b * j.H_q + h;
   const int G = j.H_q / j.H_kv;
   const uint16_t* q = j.q + bh * D;
-  __m512bh qv[4];
-  for (int i = 0; i < 4; ++i) qv[i] = (__m512bh)_mm512_loadu_si512(q + 32 * i);
-  float* scores = sc.scores.data();
-  float* vr = sc.vrows.data();
+  uint16_t* o_bh = j.o + bh * D;
+  float* scores = sc.scores.data();  // padded to a multiple of 16
   int64_t* slots = sc.slots.data();
   // resolve row indices first so that prefetches can run ahead
+  bool any_valid = false;
   for (int k = 0; k < K; ++k) {
     const int64_t slot = j.ts[bh * K + k];
     const int64_t hk = j.head_map ? j.head_map[bh * K + k] : h / G;
-    slots[k] = (slot < 0 || slot >= j.num_slots || hk < 0 || hk >= j.H_kv) ? -1 : hk * j.num_slots + slot;
+    const bool ok = !(slot < 0 || slot >= j.num_slots || hk < 0 || hk >= j.H_kv);
+    slots[k] = ok ? (hk * j.num_slots + slot) * D : -1;
+    any_valid |= ok;
   }
-  constexpr int AHEAD = 8;
-  auto pf = [&](int k) {
+  if (!any_valid) { std::memset(o_bh, 0, D * 2); return; }
+  auto prefetch_row = [&](const uint16_t* base, int k) {
     if (k < K && slots[k] >= 0) {
-      const char* a = reinterpret_cast<const char*>(j.ks + slots[k] * D);
-      const char* c = reinterpret_cast<const char*>(j.vs + slots[k] * D);
-      for (int l = 0; l < 4; ++l) { _mm_prefetch(a + 64 * l, _MM_HINT_T0); _mm_prefetch(c + 64 * l, _MM_HINT_T0); }
+      const char* a = reinterpret_cast<const char*>(base + slots[k]);
+      for (int l = 0; l < 4; ++l) _mm_prefetch(a + 64 * l, _MM_HINT_T0);
     }
   };
-  for (int k = 0; k < AHEAD; ++k) pf(k);
+
+  // pass 1: scores
+  __m512bh qb[4];
+  __m512 qf[8];
+  if (DT == JF_DTYPE_BF16) for (int i = 0; i < 4; ++i) qb[i] = (__m512bh)_mm512_loadu_si512(q + 32 * i);
+  else for (int i = 0; i < 8; ++i) qf[i] = load16<DT>(q + 16 * i);
+  for (int k = 0; k < kAhead; ++k) prefetch_row(j.ks, k);
   float max_score = -INFINITY;
-  bool any_valid = false;
   for (int k = 0; k < K; ++k) {
-    pf(k + AHEAD);
-    float* vdst = vr + static_cast<size_t>(k) * D;
-    if (slots[k] < 0) {
-      scores[k] = -INFINITY;
-      std::memset(vdst, 0, D * 4);
-      continue;
-    }
-    any_valid = true;
-    const uint16_t* kr = j.ks + slots[k] * D;
-    const uint16_t* vrow = j.vs + slots[k] * D;
+    prefetch_row(j.ks, k + kAhead);
+    if (slots[k] < 0) { scores[k] = -INFINITY; continue; }
+    const uint16_t* kr = j.ks + slots[k];
     __m512 acc = _mm512_setzero_ps();
-    for (int i = 0; i < 4; ++i) acc = _mm512_dpbf16_ps(acc, qv[i], (__m512bh)_mm512_loadu_si512(kr + 32 * i));
-    for (int i = 0; i < 8; ++i) {
-      const __m256i raw = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(vrow + 16 * i));
-      _mm512_storeu_ps(vdst + 16 * i, _mm512_castsi512_ps(_mm512_slli_epi32(_mm512_cvtepu16_epi32(raw), 16)));
+    if (DT == JF_DTYPE_BF16) {
+      for (int i = 0; i < 4; ++i) acc = _mm512_dpbf16_ps(acc, qb[i], (__m512bh)_mm512_loadu_si512(kr + 32 * i));
+    } else {
+      __m512 acc2 = _mm512_setzero_ps();
+      for (int i = 0; i < 8; i += 2) {
+        acc = _mm512_fmadd_ps(qf[i], load16<DT>(kr + 16 * i), acc);
+        acc2 = _mm512_fmadd_ps(qf[i + 1], load16<DT>(kr + 16 * i + 16), acc2);
+      }
+      acc = _mm512_add_ps(acc, acc2);
     }
     const float s = _mm512_reduce_add_ps(acc) * j.scale;
     scores[k] = s;
     if (s > max_score) max_score = s;
   }
-  finish_row(j, sc, j.o + bh * D, any_valid, max_score);
+  for (int k = 0; k < kAhead; ++k) prefetch_row(j.vs, k);  // overlaps the softmax below
+
+  // softmax weights (a NaN or +inf score leaves a non-finite normaliser: zeros, as the
+  // scalar path and the reference give)
+  const int K16 = (K + 15) & ~15;
+  for (int k = K; k < K16; ++k) scores[k] = -INFINITY;
+  const __m512 vmax = _mm512_set1_ps(max_score);
+  __m512 vsum = _mm512_setzero_ps();
+  for (int k = 0; k < K16; k += 16) {
+    const __m512 e = exp_nonpos(_mm512_sub_ps(_mm512_loadu_ps(scores + k), vmax));
+    _mm512_storeu_ps(scores + k, e);
+    vsum = _mm512_add_ps(vsum, e);
+  }
+  const float denom = _mm512_reduce_add_ps(vsum);
+  if (!(denom > 0.f) || !std::isfinite(denom)) { std::memset(o_bh, 0, D * 2); return; }
+  const float inv = 1.0f / denom;
+
+  // pass 2: o = sum p * V
+  __m512 out[8];
+  for (int i = 0; i < 8; ++i) out[i] = _mm512_setzero_ps();
+  for (int k = 0; k < K; ++k) {
+    prefetch_row(j.vs, k + kAhead);
+    const float w = scores[k] * inv;
+    if (slots[k] < 0 || w == 0.f) continue;
+    const uint16_t* vrow = j.vs + slots[k];
+    const __m512 wv = _mm512_set1_ps(w);
+    for (int i = 0; i < 8; ++i) out[i] = _mm512_fmadd_ps(wv, load16<DT>(vrow + 16 * i), out[i]);
+  }
+  for (int i = 0; i < 8; ++i) {
+    __m256i r;
+    if (DT == JF_DTYPE_BF16) r = (__m256i)_mm512_cvtneps_pbh(out[i]);
+    else r = _mm512_cvtps_ph(out[i], _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
+    _mm256_storeu_si256(reinterpret_cast<__m256i*>(o_bh + 16 * i), r);
+  }
 }
 
 bool have_avx512bf16() {
@@ -227,14 +297,15 @@ void run_rows(const Job& j, int wid, int n_workers, Scratch& sc) {
   const int64_t total = static_cast<int64_t>(j.B) * j.H_q;
   const int64_t start = total * wid / n_workers, end = total * (wid + 1) / n_workers;
   if (start >= end) return;
-  sc.scores.resize(j.K);
-  sc.vrows.resize(static_cast<size_t>(j.K) * D);
+  sc.scores.resize(static_cast<size_t>(j.K) + 16);
   sc.slots.resize(j.K);
-  const bool simd = j.dtype == JF_DTYPE_BF16 && have_avx512bf16();
+  const bool simd = have_avx512bf16();
+  if (!simd) sc.vrows.resize(static_cast<size_t>(j.K) * D);
   for (int64_t i = start; i < end; ++i) {
     const int64_t b = i / j.H_q, h = i % j.H_q;
-    if (simd) row_avx512bf16(j, sc, b, h);
-    else row_generic(j, sc, b, h);
+    if (!simd) row_generic(j, sc, b, h);
+    else if (j.dtype == JF_DTYPE_BF16) row_avx512<JF_DTYPE_BF16>(j, sc, b, h);
+    else row_avx512<JF_DTYPE_FP16>(j, sc, b, h);
   }
 }
 

@@ -38,8 +38,8 @@ def _correction_inputs(dtype=torch.bfloat16, K=64):
 
 def test_product_correction_matches_numpy_oracle():
     from jetfire_b200 import ops
-    for dtype in (torch.bfloat16, torch.float16):
-        case, slots = _correction_inputs(dtype)
+    for dtype, K in ((torch.bfloat16, 64), (torch.float16, 64), (torch.bfloat16, 70), (torch.float16, 33)):
+        case, slots = _correction_inputs(dtype, K)
         hm = torch.from_numpy(O.head_map(2, 8, 4, slots.shape[2]))
         out = torch.full((2, 8, 128), 7.0, dtype=dtype)
         flag = torch.zeros(1, dtype=torch.int64)
