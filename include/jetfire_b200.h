@@ -140,8 +140,10 @@ jf_status_t jf_topk_select(const jf_decode_args* args, jf_stream_t stream);
  * csrc/int2_softmax_v.cu:738-788). */
 jf_status_t jf_decode_finish(const jf_decode_args* args, jf_stream_t stream);
 jf_status_t jf_decode_fused(const jf_decode_args* args, jf_stream_t stream);
-/* Reads back (synchronously, after the stream drained) the device status word of the
- * workspace: 0, or JF_ERR_TIMEOUT if a bounded wait inside a kernel ran out. */
+/* Reads back (synchronously, after the stream drained) the status record of the
+ * workspace: 0, or JF_ERR_TIMEOUT if a bounded wait inside a kernel ran out since the
+ * record was last read.  Reading an error clears it.  The workspace needs no
+ * initialisation: only a record that a kernel tagged counts. */
 jf_status_t jf_decode_status(const jf_decode_args* args, jf_stream_t stream);
 
 /* ---------------------------------------------------------------------------------

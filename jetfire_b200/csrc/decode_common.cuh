@@ -39,7 +39,7 @@ __host__ __device__ inline int scan_splits(int mode, int q_dtype, int B, int H_k
 }
 
 struct Workspace {
-  int32_t* status;   // [0] = sticky error code written by kernels
+  int32_t* status;   // status record: 64-bit tag, then the error code (see report_status)
   float* part_o;     // [B][H_kv][splits][8][128]
   float* part_m;     // [B][H_kv][splits][8]
   float* part_l;     // [B][H_kv][splits][8]
@@ -69,6 +69,19 @@ inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv,
   w.bytes = off;
   return w;
 }
+
+// Status record at the start of the workspace.  A kernel whose bounded wait ran out writes
+// the code and then the tag; a record without the tag reads as "no error", so a workspace
+// needs no initialisation and no launch has to clear it.  jf_decode_status reads the record
+// and clears it.
+constexpr unsigned long long kStatusTag = 0x4A46535441545553ull;  // "JFSTATUS"
+#ifdef __CUDACC__
+__device__ __forceinline__ void report_status(int32_t* status, int code) {
+  status[2] = code;
+  __threadfence();
+  *reinterpret_cast<unsigned long long*>(status) = kStatusTag;
+}
+#endif
 
 jf_status_t validate_decode_args(const jf_decode_args* a);
 

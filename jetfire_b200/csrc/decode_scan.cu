@@ -366,7 +366,7 @@ scan_k3v2_kernel(const ScanParams p) {
     if (++st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
-  if (failed && lane == 0) atomicExch(p.status, JF_ERR_TIMEOUT);
+  if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
 
   // ---------------- CTA merge: 4 warps -> one partial ----------------
   __syncthreads();  // every warp is done with its stages (or gave up); smem is reused below
@@ -436,7 +436,6 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   if (st != JF_OK) return st;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
-  JF_CUDA_TRY(cudaMemsetAsync(ws.status, 0, sizeof(int32_t), stream));
   ScanParams sp{};
   sp.q = a->q;
   sp.k_data = a->k_data;  sp.k_scales = static_cast<const uint16_t*>(a->k_scales);

@@ -323,7 +323,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
-  if (failed && lane == 0) atomicExch(p.status, JF_ERR_TIMEOUT);
+  if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
 
   __syncthreads();
   {

@@ -15,7 +15,7 @@
 //
 // Sharing: there is one array per device, used by every call.  It keeps whatever the last
 // call left in it -- that is harmless, because each call rewrites every partial it later
-// reads and clears its status word at the start -- but two calls that overlap on the same
+// reads -- but two calls that overlap on the same
 // GPU (different streams, or different host threads) write the same memory and race.
 // Serialise them.
 //

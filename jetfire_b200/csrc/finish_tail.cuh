@@ -1,0 +1,267 @@
+// Finish stage shared by the fused select+finish kernel and the stand-alone finish kernel:
+// merge the scan's split partials (log-sum-exp) into o_hat and the softmax statistics, and
+// compute the approximate contribution of the selected set,
+//   W = sum_{i in T} p_i,   o_old_unnorm[d] = sum_{i in T} (p_i * vscale_i,g(d)) * vcode_i,d
+// (jetfire_vllm/csrc/int2_softmax_v.cu:738-788; V4: csrc/int4_softmax_v.cu:599-817).
+//
+// Weight swap for the selected set.  The scan's fp32 score of a position can differ from
+// the canonical score in the last bits (summation order), and the reference's Stage B uses
+// the scores its Stage A produced.  For every selected position the select stage has the
+// canonical score s_c; here the scan's weight exp(s_f - M) is replaced by exp(s_c - M) in
+// the numerator, the normaliser and the selected-set terms, so that p_i of the selected
+// set follows the canonical arithmetic and the remaining (individually small) weights keep
+// the scan's scores.
+//
+// Both kernels run this code with the same block size, so their results are bit-equal;
+// every summation order is fixed (no floating-point atomics).
+#pragma once
+
+#include "decode_common.cuh"
+
+// Phase stamps for tuning: compiled out unless JF_PHASE_TIMING is defined; then CTA (0, 0)
+// of the select kernel records clock64() at each JF_PHASE(i) and jf_debug_phase_times
+// (topk_select.cu) copies the stamps out.
+#ifdef JF_PHASE_TIMING
+static __device__ unsigned long long g_phase_t[64];
+#define JF_PHASE(i)                                                                          \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_t[i] = clock64();    \
+  } while (0)
+#else
+#define JF_PHASE(i) do { } while (0)
+#endif
+
+namespace jf {
+
+constexpr int kSelThreads = 1024;
+constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kSplitGroups = kSelThreads / JF_HEAD_DIM;  // split partials are summed in 8 strided groups
+constexpr int kSplitPre = 4;                             // partials per thread fetched ahead of use
+constexpr int kTailChunk = 256;                          // selected entries staged per round
+constexpr int kTailPerWarp = kTailChunk / kSelWarps;
+
+struct TailParams {
+  const float* scores;
+  const float* part_o;
+  const float* part_m;
+  const float* part_l;
+  const uint8_t* v_data;
+  const uint16_t* v_scales;
+  float* o_hat;
+  float* o_old;
+  float* W;
+  float* softmax_m;
+  float* softmax_inv_z;
+  int64_t num_slots;
+  int H_q, H_kv, G, max_S, splits, top_k;
+};
+
+template <int MODE>
+struct TailSmem {
+  static constexpr int VW = (MODE == JF_MODE_K3V2) ? 8 : 16;  // 32-bit words per packed V row
+  uint32_t v[kTailChunk * VW];                                 // first: 16-byte aligned
+  int64_t slot[kTailChunk];
+  float wc[kTailChunk][2];   // canonical weight * v scale (per group)
+  float dw[kTailChunk][2];   // (canonical - scan) weight * v scale
+  float w[kTailChunk][2];    // canonical weight, weight difference
+  float red[kSelWarps][JF_HEAD_DIM][2];
+  float sum[kSelWarps][2];
+  float o[kSplitGroups][JF_HEAD_DIM];
+  float z[kSplitGroups];
+};
+
+// The first kSplitPre split partials of thread (group, d), loaded before they are needed so
+// that their latency hides behind other work.
+struct SplitPre {
+  float m[kSplitPre], l[kSplitPre], o[kSplitPre];
+};
+
+__device__ __forceinline__ void split_preload(const TailParams& p, int64_t pbase, int hi, int tid, SplitPre& r) {
+  const int d = tid & (JF_HEAD_DIM - 1), grp = tid >> 7;
+#pragma unroll
+  for (int i = 0; i < kSplitPre; ++i) {
+    const int s = grp + i * kSplitGroups;
+    r.m[i] = kMinusBig; r.l[i] = 0.f; r.o[i] = 0.f;
+    if (s < p.splits) {
+      const int64_t e = (pbase + s) * kHeadsPad + hi;
+      r.m[i] = p.part_m[e];
+      r.l[i] = p.part_l[e];
+      r.o[i] = p.part_o[e * JF_HEAD_DIM + d];
+    }
+  }
+}
+
+// code - bias as a float without an integer-to-float conversion: 2^23 + code is the float
+// with `code` in its low mantissa bits.
+__device__ __forceinline__ float small_code_to_f32(uint32_t code, float bias) {
+  return __uint_as_float(0x4B000000u | code) - (8388608.0f + bias);
+}
+
+// `src(kk, pos, canon)` yields the kk-th selected entry (rank order): its position and
+// canonical score; false if there is none.  M = max over the splits of the scan's
+// reference points.  n = sequence length.
+template <int MODE, typename Src>
+__device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>& sm, const SplitPre& pre, float M, int n,
+                                            int b, int h, const int64_t* bt, Src src) {
+  constexpr int VW = TailSmem<MODE>::VW;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hkv = h / p.G, hi = h - hkv * p.G;
+  const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
+  const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
+
+  JF_PHASE(20);
+  // ---- merge splits (unnormalised): thread (group, d) sums splits group, group + 8, ... ----
+  {
+    const int d = tid & (JF_HEAD_DIM - 1), grp = tid >> 7;
+    float o = 0.f, Z = 0.f;
+#pragma unroll
+    for (int i = 0; i < kSplitPre; ++i) {
+      if (grp + i * kSplitGroups < p.splits) {
+        const float w = ex2((pre.m[i] - M) * kLog2e);
+        Z = fmaf(pre.l[i], w, Z);
+        o = fmaf(pre.o[i], w, o);
+      }
+    }
+    for (int s = grp + kSplitPre * kSplitGroups; s < p.splits; s += kSplitGroups) {
+      const int64_t e = (pbase + s) * kHeadsPad + hi;
+      const float w = ex2((p.part_m[e] - M) * kLog2e);
+      Z = fmaf(p.part_l[e], w, Z);
+      o = fmaf(p.part_o[e * JF_HEAD_DIM + d], w, o);
+    }
+    sm.o[grp][d] = o;
+    if (d == 0) sm.z[grp] = Z;
+  }
+
+  JF_PHASE(21);
+  // ---- selected set: canonical weights, and their difference to the scan's ----
+  const ModeInfo mi = mode_info(MODE);
+  const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
+  const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+  const float* srow = p.scores + bh * p.max_S;
+  float a_old[4] = {0.f, 0.f, 0.f, 0.f}, a_dw[4] = {0.f, 0.f, 0.f, 0.f};
+  float wsum = 0.f, dz = 0.f;
+  const int qg = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
+  for (int k0 = 0; k0 < p.top_k; k0 += kTailChunk) {
+    const int kend = min(kTailChunk, p.top_k - k0);
+    if (tid < kTailChunk) {
+      int64_t slot = -1;
+      float wc = 0.f, dw = 0.f, vs0 = 0.f, vs1 = 0.f;
+      int pos = -1;
+      float canon = 0.f;
+      if (tid < kend && n > 0 && src(k0 + tid, pos, canon) && pos >= 0 && pos < n) {
+        const int64_t blk = bt[pos >> 4];
+        const float approx = srow[pos];  // independent of the block-table lookup
+        if (blk >= 0 && blk < (p.num_slots >> 4)) {
+          slot = blk * 16 + (pos & 15);
+          uint32_t sw;
+          if (MODE == JF_MODE_K3V2) sw = __ldg(reinterpret_cast<const uint32_t*>(v_sc + slot * 2));
+          else sw = __ldg(v_sc + slot);
+          wc = ex2((canon - M) * kLog2e);
+          dw = wc - ex2((approx - M) * kLog2e);
+          if (MODE == JF_MODE_K3V2) {
+            vs0 = __uint_as_float(sw << 16);
+            vs1 = __uint_as_float(sw & 0xFFFF0000u);
+          } else {
+            vs0 = vs1 = __uint_as_float(sw << 16);
+          }
+        }
+      }
+      sm.slot[tid] = slot;
+      sm.w[tid][0] = wc; sm.w[tid][1] = dw;
+      sm.wc[tid][0] = wc * vs0; sm.wc[tid][1] = wc * vs1;
+      sm.dw[tid][0] = dw * vs0; sm.dw[tid][1] = dw * vs1;
+    }
+    __syncthreads();
+    JF_PHASE(22);
+    // packed V rows, one 16-byte load per thread
+    for (int u = tid; u < kend * (VW / 4); u += kSelThreads) {
+      const int c = u / (VW / 4), part = u - c * (VW / 4);
+      const int64_t slot = sm.slot[c];
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (slot >= 0) v = __ldg(reinterpret_cast<const uint4*>(v_rows + slot * (VW * 4)) + part);
+      reinterpret_cast<uint4*>(sm.v)[u] = v;
+    }
+    __syncthreads();
+    JF_PHASE(23);
+    // warp w takes entries w, w + 32, ...; lane l owns channels 4l..4l+3
+    {
+      uint32_t raw[kTailPerWarp];
+      float fw[kTailPerWarp], fd[kTailPerWarp], w0[kTailPerWarp], w1[kTailPerWarp];
+#pragma unroll
+      for (int i = 0; i < kTailPerWarp; ++i) {
+        const int j = warp + i * kSelWarps;  // < kTailChunk; rows past kend hold zero weights
+        raw[i] = (MODE == JF_MODE_K3V2) ? static_cast<uint32_t>(reinterpret_cast<const uint8_t*>(sm.v + j * VW)[lane])
+                                        : static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(sm.v + j * VW)[lane]);
+        fw[i] = sm.wc[j][qg]; fd[i] = sm.dw[j][qg];
+        w0[i] = sm.w[j][0]; w1[i] = sm.w[j][1];
+      }
+#pragma unroll
+      for (int i = 0; i < kTailPerWarp; ++i) {
+        const int j = warp + i * kSelWarps;
+        if (j >= kend || sm.slot[j] < 0) continue;  // warp-uniform
+        float c[4];
+        if (MODE == JF_MODE_K3V2) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[e] = small_code_to_f32((raw[i] >> ((3 - e) * 2)) & 3u, 2.0f);
+        } else {
+          c[0] = small_code_to_f32((raw[i] >> 4) & 15u, 8.0f);
+          c[1] = small_code_to_f32(raw[i] & 15u, 8.0f);
+          c[2] = small_code_to_f32((raw[i] >> 12) & 15u, 8.0f);
+          c[3] = small_code_to_f32((raw[i] >> 8) & 15u, 8.0f);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { a_old[e] = fmaf(fw[i], c[e], a_old[e]); a_dw[e] = fmaf(fd[i], c[e], a_dw[e]); }
+        wsum += w0[i];
+        dz += w1[i];
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { sm.red[warp][4 * lane + e][0] = a_old[e]; sm.red[warp][4 * lane + e][1] = a_dw[e]; }
+  if (lane == 0) { sm.sum[warp][0] = wsum; sm.sum[warp][1] = dz; }
+  __syncthreads();
+  JF_PHASE(24);
+  if (tid < JF_HEAD_DIM) {
+    float acc_old = 0.f, acc_dw = 0.f, ws = 0.f, dzs = 0.f, o = 0.f, Z = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSelWarps; ++w) {
+      acc_old += sm.red[w][tid][0]; acc_dw += sm.red[w][tid][1];
+      ws += sm.sum[w][0]; dzs += sm.sum[w][1];
+    }
+#pragma unroll
+    for (int gI = 0; gI < kSplitGroups; ++gI) { o += sm.o[gI][tid]; Z += sm.z[gI]; }
+    Z += dzs;
+    const bool live = (Z > 0.f) && (n > 0);
+    const float inv_z = live ? (1.0f / Z) : 0.f;
+    p.o_hat[bh * JF_HEAD_DIM + tid] = (o + acc_dw) * inv_z;
+    p.o_old[bh * JF_HEAD_DIM + tid] = acc_old * inv_z;
+    if (tid == 0) {
+      p.W[bh] = ws * inv_z;
+      if (p.softmax_m) p.softmax_m[bh] = live ? M : 0.f;
+      if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
+    }
+  }
+  JF_PHASE(25);
+}
+
+// Shared by both kernels: the merged reference point M = max over the splits, block-wide.
+// `red` = 32 floats of shared memory.  Ends with a barrier.
+__device__ __forceinline__ float block_max_of_splits(const float* part_m, int64_t pbase, int hi, int splits, float* red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float M = kMinusBig;
+  for (int s = tid; s < splits; s += kSelThreads) M = fmaxf(M, part_m[(pbase + s) * kHeadsPad + hi]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+  if (lane == 0) red[warp] = M;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kSelWarps; ++w) M = fmaxf(M, red[w]);
+  return M;
+}
+
+struct Workspace;
+TailParams make_tail_params(const jf_decode_args* a, const Workspace& ws);
+jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fused);
+
+}  // namespace jf

@@ -15,13 +15,12 @@
 // band does not fit the sort buffer (massive ties, degenerate scales) a slow exact path
 // radix-selects on the 64-bit key (canonical score, ~position) computed on the fly.
 // Slot translation and -1 padding follow csrc/int3_qk_scores.cu:399-417.
-#include "decode_common.cuh"
+#include "finish_tail.cuh"
 
 namespace jf {
 
 namespace {
 
-constexpr int kTopkThreads = 1024;
 constexpr int kBins = 2048;
 constexpr float kBinsPerUnit = 64.0f;
 
@@ -131,52 +130,112 @@ __device__ __forceinline__ int score_bin(float top64, float s) {
   return __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
 }
 
+// Canonical K4/G128 score by ONE thread.  The integer dot products are exact, so any order
+// gives the value of canon_score_k4: byte B of the packed row holds channel 2B in its high
+// nibble and channel 2B + 1 in its low nibble; `qe` / `qo` are the INT8 query's even / odd
+// channels packed four to a word, `qsum8[c]` = 8 * (sum of the query over block c) removes
+// the code offset.
+__device__ __forceinline__ float canon_score_k4_thread(const uint32_t* qe, const uint32_t* qo, const int* qsum8,
+                                                       const float* qs, const uint32_t* row, float ks, float attn) {
+  float s = 0.f;
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    int acc = -qsum8[blk];
+#pragma unroll
+    for (int w = 4 * blk; w < 4 * blk + 4; ++w) {
+      const uint32_t word = row[w];
+      acc = __dp4a(static_cast<int>((word >> 4) & 0x0F0F0F0Fu), static_cast<int>(qe[w]), acc);
+      acc = __dp4a(static_cast<int>(word & 0x0F0F0F0Fu), static_cast<int>(qo[w]), acc);
+    }
+    s = __fmaf_rn(static_cast<float>(acc), qs[blk], s);
+  }
+  return __fmul_rn(__fmul_rn(s, ks), attn);
+}
+
 constexpr int kRowChunk = 512;                 // candidates staged in shared memory per round
 constexpr int kScoreRegs = 32;                 // scores cached per thread (32768 positions per CTA)
-constexpr int kScoreChunk = kScoreRegs * kTopkThreads;
+constexpr int kScoreChunk = kScoreRegs * kSelThreads;
 template <int MODE> struct RowWords { static constexpr int v = (MODE == JF_MODE_K3V2) ? 13 : 17; };
 
-template <int MODE, int DT>
-__global__ void __launch_bounds__(kTopkThreads)
-topk_select_kernel(const TopkParams p) {
+struct SelSmemFixed {
+  int hist[kBins];
+  float q[JF_HEAD_DIM];
+  float qs[4];
+  int qsum8[4];
+  uint32_t qe[16], qo[16];
+  int8_t qi[JF_HEAD_DIM];
+  int64_t cand_slot[kRowChunk];
+  uint32_t rows[kRowChunk * 17];
+  float w3[kSelWarps][3];
+  float red[4];
+  int wsum[kSelWarps];
+  int ncand, last, fallback, tbin, remaining;
+  unsigned long long prefix;
+};
+
+// One CTA per (query head, batch element).  FUSED: the finish stage follows in the same
+// kernel (the selected list never leaves the SM).
+template <int MODE, int DT, bool FUSED>
+__global__ void __launch_bounds__(kSelThreads)
+topk_select_kernel(const TopkParams p, const TailParams tp) {
   constexpr int W = RowWords<MODE>::v;         // 32-bit words staged per candidate: data + scales
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw);                   // [sort_n]
-  int* hist = reinterpret_cast<int*>(keys + p.sort_n);                      // [kBins]
-  float* q_sm = reinterpret_cast<float*>(hist + kBins);                     // [128]
-  float* qs_sm = q_sm + JF_HEAD_DIM;                                        // [4]
-  int8_t* qi_sm = reinterpret_cast<int8_t*>(qs_sm + 4);                     // [128]
-  int64_t* cand_slot = reinterpret_cast<int64_t*>(qi_sm + JF_HEAD_DIM);     // [kRowChunk]
-  uint32_t* rows = reinterpret_cast<uint32_t*>(cand_slot + kRowChunk);      // [kRowChunk][W]
-  __shared__ int sh_ncand, sh_last, sh_fallback, sh_tbin;
-  __shared__ float sh_red[4];
-  __shared__ float sh_w3[32][3];
-  __shared__ int sh_wsum[32];
-  __shared__ unsigned long long sh_prefix;
-  __shared__ int sh_remaining;
+  TailSmem<MODE>& tsm = *reinterpret_cast<TailSmem<MODE>*>(smem_raw);
+  SelSmemFixed& sm = *reinterpret_cast<SelSmemFixed*>(smem_raw + sizeof(TailSmem<MODE>));
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw + sizeof(TailSmem<MODE>) + sizeof(SelSmemFixed));  // [sort_n]
+  int* hist = sm.hist;
 
+  JF_PHASE(0);
   const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / p.G, hi = h - hkv * p.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n = min(p.seq_lens[b], p.max_S);
   const int K = p.top_k;
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
+  const float* srow = p.scores + bh * p.max_S;
+  const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
+
+  // ---- the row's scores go to registers first: nothing else depends on them yet, so their
+  //      latency hides behind the prologue.  Positions past the sequence are masked later;
+  //      the row's allocation covers max_S. ----
+  const bool vec = (p.max_S & 3) == 0;     // rows start on 16-byte boundaries
+  float sc[kScoreRegs];
+  auto pos_of = [&](int ci, int e) {
+    return vec ? ci * kScoreChunk + 4 * ((e >> 2) * kSelThreads + tid) + (e & 3)
+               : ci * kScoreChunk + e * kSelThreads + tid;
+  };
+  auto load_chunk = [&](int ci) {
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < kScoreRegs / 4; ++j) {
+        const int p0 = ci * kScoreChunk + 4 * (j * kSelThreads + tid);
+        float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        if (p0 < p.max_S) v = *reinterpret_cast<const float4*>(srow + p0);  // max_S % 4 == 0: stays inside the row
+        sc[4 * j] = v.x; sc[4 * j + 1] = v.y; sc[4 * j + 2] = v.z; sc[4 * j + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < kScoreRegs; ++e) {
+        const int pp = ci * kScoreChunk + e * kSelThreads + tid;
+        sc[e] = (pp < p.max_S) ? srow[pp] : -INFINITY;
+      }
+    }
+  };
+  load_chunk(0);
+  SplitPre pre;
+  if (FUSED) split_preload(tp, pbase, hi, tid, pre);
+
+  const int n = min(p.seq_lens[b], p.max_S);
   int64_t* out_idx = p.topk_idx + bh * K;
   int64_t* out_slot = p.topk_slots + bh * K;
   float* out_canon = p.sel_canon + bh * K;
-  if (n <= 0) {
-    for (int r = tid; r < K; r += kTopkThreads) { out_idx[r] = -1; out_slot[r] = -1; out_canon[r] = -INFINITY; }
-    return;
-  }
 
   // ---- query row (exact values), per-group L1 norms, INT8 model for K4; split statistics ----
   if (tid < JF_HEAD_DIM) {
-    q_sm[tid] = Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid]);
+    sm.q[tid] = Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid]);
   }
   {
     float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
-    const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
-    for (int s = tid; s < p.splits; s += kTopkThreads) {
+    for (int s = tid; s < p.splits; s += kSelThreads) {
       top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
       sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
       sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
@@ -187,11 +246,11 @@ topk_select_kernel(const TopkParams p) {
       sm0 = fmaxf(sm0, __shfl_xor_sync(0xFFFFFFFFu, sm0, o));
       sm1 = fmaxf(sm1, __shfl_xor_sync(0xFFFFFFFFu, sm1, o));
     }
-    if (lane == 0) { sh_w3[warp][0] = top; sh_w3[warp][1] = sm0; sh_w3[warp][2] = sm1; }
+    if (lane == 0) { sm.w3[warp][0] = top; sm.w3[warp][1] = sm0; sm.w3[warp][2] = sm1; }
   }
   __syncthreads();
   if (warp < 4) {  // warp w handles channels 32w..32w+31
-    const float v = q_sm[32 * warp + lane];
+    const float v = sm.q[32 * warp + lane];
     float a = fabsf(v), s1 = fabsf(v) + 0.001953125f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -201,18 +260,30 @@ topk_select_kernel(const TopkParams p) {
     if (MODE == JF_MODE_K4V4) {
       const float qs = fmaxf(__fdiv_rn(a, 127.0f), 1e-12f);
       const float inv = __fdiv_rn(1.0f, qs);
-      qi_sm[32 * warp + lane] = static_cast<int8_t>(max(-128, min(127, __float2int_rn(__fmul_rn(v, inv)))));
-      if (lane == 0) qs_sm[warp] = qs;
+      const int qv = max(-128, min(127, __float2int_rn(__fmul_rn(v, inv))));
+      sm.qi[32 * warp + lane] = static_cast<int8_t>(qv);
+      int qsum = qv;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, o);
+      // words of four even / four odd channels: lanes 8k..8k+7 make word 4 * warp + k
+      const uint32_t byte = static_cast<uint32_t>(qv) & 0xFFu;
+      const uint32_t b2 = __shfl_down_sync(0xFFFFFFFFu, byte, 2), b4 = __shfl_down_sync(0xFFFFFFFFu, byte, 4),
+                     b6 = __shfl_down_sync(0xFFFFFFFFu, byte, 6);
+      const uint32_t word = byte | (b2 << 8) | (b4 << 16) | (b6 << 24);
+      if ((lane & 7) == 0) sm.qe[4 * warp + (lane >> 3)] = word;
+      if ((lane & 7) == 1) sm.qo[4 * warp + (lane >> 3)] = word;
+      if (lane == 0) { sm.qs[warp] = qs; sm.qsum8[warp] = 8 * qsum; }
     }
-    if (lane == 0) sh_red[warp] = s1;
+    if (lane == 0) sm.red[warp] = s1;
   }
-  if (tid == 0) { sh_ncand = 0; sh_fallback = 0; sh_tbin = -1; }
-  for (int i = tid; i < kBins; i += kTopkThreads) hist[i] = 0;
-  for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
+  if (tid == 0) { sm.ncand = 0; sm.fallback = 0; sm.tbin = -1; }
+  for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
+  for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
   __syncthreads();
+  JF_PHASE(1);
 
   RowCtx ctx;
-  ctx.q = q_sm; ctx.qi = qi_sm; ctx.qs = qs_sm;
+  ctx.q = sm.q; ctx.qi = sm.qi; ctx.qs = sm.qs;
   const ModeInfo mi = mode_info(MODE);
   ctx.k_rows = p.k_data + static_cast<int64_t>(hkv) * p.num_slots * mi.k_row;
   ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
@@ -220,299 +291,427 @@ topk_select_kernel(const TopkParams p) {
   ctx.num_slots = p.num_slots;
   ctx.attn = p.attn_scale;
 
-  const float* srow = p.scores + bh * p.max_S;
-  int ncand = 0;
-  bool slow = false;
+  float row_max = kMinusBig;  // max over the splits of the scan's reference points
+#pragma unroll
+  for (int w = 0; w < kSelWarps; ++w) row_max = fmaxf(row_max, sm.w3[w][0]);
 
-  if (n <= p.sort_n) {
-    // short row: every position is a candidate
-    for (int i = tid; i < n; i += kTopkThreads) keys[i] = static_cast<uint64_t>(i);
-    ncand = n;
-  } else {
-    // ---- tier 1: histogram of approximate scores (kept in registers for the second sweep) ----
-    float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
+  int m_sel = 0;  // entries of keys[] that hold the ranked result
+  if (n > 0) {
+    int ncand = 0;
+    bool slow = false;
+
+    if (n <= p.sort_n) {
+      // short row: every position is a candidate
+      for (int i = tid; i < n; i += kSelThreads) keys[i] = static_cast<uint64_t>(i);
+      ncand = n;
+    } else {
+      float sm0 = 0.f, sm1 = 0.f;
 #pragma unroll
-    for (int w = 0; w < 32; ++w) {
-      top = fmaxf(top, sh_w3[w][0]); sm0 = fmaxf(sm0, sh_w3[w][1]); sm1 = fmaxf(sm1, sh_w3[w][2]);
-    }
-    top += 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
-    const float top64 = top * kBinsPerUnit;
-    float delta = 0.f;
-    if (MODE == JF_MODE_K3V2) {
-      // The scan and the canonical order add the same exact products q_d * k_hat_d in fp32,
-      // in different orders: each stays within (roundings) * 2^-24 * sum|q_d k_hat_d| of the
-      // exact sum (canonical: 9 roundings; tensor core: one per k-step, 8, possibly
-      // truncating).  sum|q_d k_hat_d| <= sum_g 3 * scale_g * sum_{d in g} |q_d|.  A factor 32
-      // covers both paths with slack; the last term covers the final multiply by attn_scale.
-      const float q1a = sh_red[0] + sh_red[1], q1b = sh_red[2] + sh_red[3];
-      const float mag = fabsf(p.attn_scale) * (sm0 * q1a + sm1 * q1b) * 3.0f;
-      delta = mag * (32.0f / 16777216.0f) + mag * (4.0f / 16777216.0f) + 1e-7f;
-    }
-    const bool vec = (p.max_S & 3) == 0;     // rows start on 16-byte boundaries
-    const int n_chunks = (n + kScoreChunk - 1) / kScoreChunk;
-    float sc[kScoreRegs];
-    auto pos_of = [&](int ci, int e) {
-      return vec ? ci * kScoreChunk + 4 * ((e >> 2) * kTopkThreads + tid) + (e & 3)
-                 : ci * kScoreChunk + e * kTopkThreads + tid;
-    };
-    auto load_chunk = [&](int ci) {
-      if (vec) {
-#pragma unroll
-        for (int j = 0; j < kScoreRegs / 4; ++j) {
-          const int p0 = ci * kScoreChunk + 4 * (j * kTopkThreads + tid);
-          float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-          if (p0 < n) v = *reinterpret_cast<const float4*>(srow + p0);  // max_S % 4 == 0: stays inside the row
-          sc[4 * j] = v.x; sc[4 * j + 1] = v.y; sc[4 * j + 2] = v.z; sc[4 * j + 3] = v.w;
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < kScoreRegs; ++e) {
-          const int pp = ci * kScoreChunk + e * kTopkThreads + tid;
-          sc[e] = (pp < n) ? srow[pp] : -INFINITY;
-        }
+      for (int w = 0; w < kSelWarps; ++w) { sm0 = fmaxf(sm0, sm.w3[w][1]); sm1 = fmaxf(sm1, sm.w3[w][2]); }
+      const float top = row_max + 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
+      const float top64 = top * kBinsPerUnit;
+      float delta = 0.f;
+      if (MODE == JF_MODE_K3V2) {
+        // The scan and the canonical order add the same exact products q_d * k_hat_d in fp32,
+        // in different orders: each stays within (roundings) * 2^-24 * sum|q_d k_hat_d| of the
+        // exact sum (canonical: 9 roundings; tensor core: one per k-step, 8, possibly
+        // truncating).  sum|q_d k_hat_d| <= sum_g 3 * scale_g * sum_{d in g} |q_d|.  A factor 32
+        // covers both paths with slack; the last term covers the final multiply by attn_scale.
+        const float q1a = sm.red[0] + sm.red[1], q1b = sm.red[2] + sm.red[3];
+        const float mag = fabsf(p.attn_scale) * (sm0 * q1a + sm1 * q1b) * 3.0f;
+        delta = mag * (32.0f / 16777216.0f) + mag * (4.0f / 16777216.0f) + 1e-7f;
       }
-    };
-    for (int ci = 0; ci < n_chunks; ++ci) {
-      load_chunk(ci);
-#pragma unroll
-      for (int e = 0; e < kScoreRegs; ++e)
-        if (pos_of(ci, e) < n) atomicAdd(&hist[score_bin(top64, sc[e])], 1);
-    }
-    __syncthreads();
-    {
-      // block-wide inclusive scan of the histogram, two bins per thread, written back in place
-      const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
-      const int v = h0 + h1;
-      int incl = v;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += t;
-      }
-      if (lane == 31) sh_wsum[warp] = incl;
-      __syncthreads();
-      if (warp == 0) {
-        int t = sh_wsum[lane], inc2 = t;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int u = __shfl_up_sync(0xFFFFFFFFu, inc2, o);
-          if (lane >= o) inc2 += u;
-        }
-        sh_wsum[lane] = inc2 - t;  // exclusive prefix of the warp totals
-      }
-      __syncthreads();
-      const int ex = sh_wsum[warp] + incl - v;
-      hist[2 * tid] = ex + h0;
-      hist[2 * tid + 1] = ex + v;
-      if (ex < K && ex + h0 >= K) sh_tbin = 2 * tid;
-      else if (ex + h0 < K && ex + v >= K) sh_tbin = 2 * tid + 1;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      const int tbin = sh_tbin;
       float nbf = ceilf(2.0f * delta * kBinsPerUnit) + 1.0f;
       if (!(nbf < 4096.0f)) nbf = 4096.0f;
-      const int nb = (MODE == JF_MODE_K3V2) ? static_cast<int>(nbf) : 0;
-      const int last = min(max(tbin, 0) + nb, kBins - 1);
-      sh_last = last;
-      sh_fallback = (tbin < 0 || last >= kBins - 1 || hist[last] > p.sort_n) ? 1 : 0;
-    }
-    __syncthreads();
-    if (!sh_fallback) {
-      // ---- tier 2: collect the band (positions into keys[]) ----
-      const float xlim = static_cast<float>(sh_last + 1);  // bin <= last  <=>  (top - s) * 64 < last + 1
-      for (int ci = 0; ci < n_chunks; ++ci) {
-        if (n_chunks > 1) load_chunk(ci);
+      const int nb = (MODE == JF_MODE_K3V2) ? static_cast<int>(nbf) : 0;  // K4: scan scores are canonical
+      const int n_chunks = (n + kScoreChunk - 1) / kScoreChunk;
+
+      // Block-wide: turns hist[] into inclusive prefix counts (from the top bin down) and
+      // leaves in sm.tbin the bin where the count reaches K (-1: never).
+      auto scan_hist = [&]() {
+        const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
+        const int v = h0 + h1;
+        int incl = v;
 #pragma unroll
-        for (int e = 0; e < kScoreRegs; ++e) {
-          const int pp = pos_of(ci, e);
-          if (pp < n && score_binf(top64, sc[e]) < xlim) {
-            const int slot = atomicAdd(&sh_ncand, 1);
-            if (slot < p.sort_n) keys[slot] = static_cast<uint64_t>(pp);
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        if (lane == 31) sm.wsum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+          int t = sm.wsum[lane], inc2 = t;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xFFFFFFFFu, inc2, o);
+            if (lane >= o) inc2 += u;
+          }
+          sm.wsum[lane] = inc2 - t;  // exclusive prefix of the warp totals
+        }
+        __syncthreads();
+        const int ex = sm.wsum[warp] + incl - v;
+        hist[2 * tid] = ex + h0;
+        hist[2 * tid + 1] = ex + v;
+        if (ex < K && ex + h0 >= K) sm.tbin = 2 * tid;
+        else if (ex + h0 < K && ex + v >= K) sm.tbin = 2 * tid + 1;
+        __syncthreads();
+      };
+      // Block-wide: positions whose bin is <= last go to keys[] (one shared-memory atomic per
+      // warp and chunk); returns how many there are (may exceed sort_n: then keys[] is partial).
+      auto collect = [&](int last) {
+        const float xlim = static_cast<float>(last + 1);  // bin <= last  <=>  (top - s) * 64 < last + 1
+        for (int ci = 0; ci < n_chunks; ++ci) {
+          if (n_chunks > 1) load_chunk(ci);
+          int cnt = 0;
+#pragma unroll
+          for (int e = 0; e < kScoreRegs; ++e) cnt += (pos_of(ci, e) < n && score_binf(top64, sc[e]) < xlim) ? 1 : 0;
+          int incl = cnt;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+          }
+          int base = 0;
+          if (lane == 31 && incl > 0) base = atomicAdd(&sm.ncand, incl);
+          base = __shfl_sync(0xFFFFFFFFu, base, 31);
+          if (cnt > 0) {
+            int o = base + incl - cnt;
+#pragma unroll
+            for (int e = 0; e < kScoreRegs; ++e) {
+              const int pp = pos_of(ci, e);
+              if (pp < n && score_binf(top64, sc[e]) < xlim) {
+                if (o < p.sort_n) keys[o] = static_cast<uint64_t>(pp);
+                ++o;
+              }
+            }
           }
         }
+        __syncthreads();
+        return sm.ncand;
+      };
+
+      // ---- tier 1a: a bound from group maxima.  Each thread holds four groups of positions
+      //      per chunk (stride 4096 inside a group); the K-th largest group maximum is a lower
+      //      bound of the K-th largest score, and far fewer values enter the histogram. ----
+      for (int ci = 0; ci < n_chunks; ++ci) {
+        if (ci > 0) load_chunk(ci);
+        float gm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < kScoreRegs; ++e)
+          if (pos_of(ci, e) < n) gm[e & 3] = fmaxf(gm[e & 3], sc[e]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (gm[c] > -INFINITY) atomicAdd(&hist[score_bin(top64, gm[c])], 1);
       }
       __syncthreads();
-      ncand = min(sh_ncand, p.sort_n);
-    } else {
-      slow = true;
+      JF_PHASE(2);
+      scan_hist();
+      JF_PHASE(3);
+      bool ok = false;
+      {
+        const int tbin = sm.tbin;
+        const int last = tbin + nb;
+        if (tbin >= 0 && last < kBins - 1) {
+          const int total = collect(last);
+          ok = total <= p.sort_n;
+          ncand = total;
+        }
+      }
+      if (!ok) {
+        // ---- tier 1b: histogram of every score; the band around the bin of the K-th largest ----
+        __syncthreads();
+        if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
+        for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
+        __syncthreads();
+        for (int ci = 0; ci < n_chunks; ++ci) {
+          if (n_chunks > 1) load_chunk(ci);
+#pragma unroll
+          for (int e = 0; e < kScoreRegs; ++e)
+            if (pos_of(ci, e) < n) atomicAdd(&hist[score_bin(top64, sc[e])], 1);
+        }
+        __syncthreads();
+        scan_hist();
+        const int tbin = sm.tbin;
+        const int last = min(max(tbin, 0) + nb, kBins - 1);
+        if (tbin < 0 || last >= kBins - 1 || hist[last] > p.sort_n) {
+          slow = true;
+        } else {
+          for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+          __syncthreads();
+          ncand = collect(last);
+        }
+      }
     }
-  }
-  __syncthreads();
+    __syncthreads();
+    JF_PHASE(4);
 
-  if (!slow) {
-    // ---- re-score the candidates canonically: slots, then their packed rows into shared
-    //      memory with independent loads, then one warp per candidate ----
-    for (int base = 0; base < ncand; base += kRowChunk) {
-      const int cn = min(kRowChunk, ncand - base);
-      if (tid < cn) cand_slot[tid] = slot_of(ctx, static_cast<int>(keys[base + tid]));
-      __syncthreads();
-      for (int idx = tid; idx < cn * W; idx += kTopkThreads) {
-        const int c = idx / W, w = idx - c * W;
-        const int64_t slot = cand_slot[c];
-        uint32_t v = 0u;
-        if (slot >= 0) {
-          if (MODE == JF_MODE_K3V2) {
-            v = (w < 12) ? __ldg(reinterpret_cast<const uint32_t*>(ctx.k_rows + slot * 48) + w)
-                         : __ldg(reinterpret_cast<const uint32_t*>(ctx.k_sc + slot * 2));
-          } else {
-            v = (w < 16) ? __ldg(reinterpret_cast<const uint32_t*>(ctx.k_rows + slot * 64) + w)
-                         : static_cast<uint32_t>(__ldg(ctx.k_sc + slot));
+    if (!slow) {
+      // ---- re-score the candidates canonically: slots, then their packed rows into shared
+      //      memory with independent 16-byte loads, then the canonical arithmetic ----
+      for (int base = 0; base < ncand; base += kRowChunk) {
+        const int cn = min(kRowChunk, ncand - base);
+        if (tid < cn) sm.cand_slot[tid] = slot_of(ctx, static_cast<int>(keys[base + tid]));
+        __syncthreads();
+        JF_PHASE(5);
+        {
+          // unit u = (candidate, quarter): K4 rows are 4 x 16 bytes (+ the scale with quarter 0),
+          // K3 rows 3 x 16 bytes and quarter 3 fetches the two scales
+          uint4 v[2];
+          uint32_t sc16[2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int u = tid + i * kSelThreads;
+            const int c = u >> 2, part = u & 3;
+            v[i] = make_uint4(0u, 0u, 0u, 0u);
+            sc16[i] = 0u;
+            if (c < cn) {
+              const int64_t slot = sm.cand_slot[c];
+              if (slot >= 0) {
+                if (MODE == JF_MODE_K3V2) {
+                  if (part < 3) v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * 48) + part);
+                  else sc16[i] = __ldg(reinterpret_cast<const uint32_t*>(ctx.k_sc + slot * 2));
+                } else {
+                  v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * 64) + part);
+                  if (part == 0) sc16[i] = static_cast<uint32_t>(__ldg(ctx.k_sc + slot));
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int u = tid + i * kSelThreads;
+            const int c = u >> 2, part = u & 3;
+            if (c < cn) {
+              uint32_t* r = sm.rows + c * W;
+              if (MODE == JF_MODE_K3V2) {
+                if (part < 3) { r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w; }
+                else r[12] = sc16[i];
+              } else {
+                r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w;
+                if (part == 0) r[16] = sc16[i];
+              }
+            }
           }
         }
-        rows[idx] = v;
-      }
-      __syncthreads();
-      for (int c = warp; c < cn; c += kTopkThreads / 32) {
-        const int pos = static_cast<int>(keys[base + c]);
-        const uint32_t* r = rows + c * W;
-        float s = -INFINITY;
-        if (cand_slot[c] >= 0) {
-          if (MODE == JF_MODE_K3V2)
-            s = canon_score_k3(q_sm, reinterpret_cast<const uint8_t*>(r), r[12], ctx.attn, lane);
-          else
-            s = canon_score_k4(qi_sm, qs_sm, reinterpret_cast<const uint8_t*>(r), bf16_bits_to_f32(r[16] & 0xFFFFu),
-                               ctx.attn, lane);
-        }
-        __syncwarp();
-        if (lane == 0) keys[base + c] = make_key(s, pos);
-      }
-      __syncthreads();
-    }
-  } else {
-    // ---- slow exact path: 8-level radix select on the 64-bit canonical key ----
-    if (tid == 0) { sh_prefix = 0ull; sh_remaining = K; sh_ncand = 0; }
-    __syncthreads();
-    for (int level = 7; level >= 0; --level) {
-      for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
-      __syncthreads();
-      const unsigned long long prefix = sh_prefix;
-      for (int i = warp; i < n; i += kTopkThreads / 32) {
-        const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
-        const bool match = (level == 7) || ((key >> (8 * (level + 1))) == prefix);
-        if (match && lane == 0) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
-      }
-      __syncthreads();
-      if (tid == 0) {
-        int cum = 0, rem = sh_remaining, cb = 0;
-        for (int bin = 255; bin >= 0; --bin) {
-          if (cum + hist[bin] >= rem) { cb = bin; break; }
-          cum += hist[bin];
-        }
-        sh_remaining = rem - cum;
-        sh_prefix = (prefix << 8) | static_cast<unsigned long long>(cb);
-      }
-      __syncthreads();
-    }
-    const unsigned long long tkey = sh_prefix;  // key of the k-th best; keys are unique
-    for (int i = tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
-    __syncthreads();
-    for (int i = warp; i < n; i += kTopkThreads / 32) {
-      const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
-      if (key >= tkey && lane == 0) {
-        const int pos = atomicAdd(&sh_ncand, 1);
-        if (pos < p.sort_n) keys[pos] = key;
-      }
-    }
-    __syncthreads();
-    ncand = min(sh_ncand, p.sort_n);
-  }
-  __syncthreads();
-
-  // ---- order the candidates: best first ----
-  uint64_t* ranked = keys;
-  if (p.sort_n <= 1024) {
-    // rank by counting (keys are unique): thread (c, part) counts the keys above candidate c in
-    // its share of the list; the partial counts of a candidate are added by a shuffle
-    const int parts = (ncand <= kTopkThreads / 4) ? 4 : ((ncand <= kTopkThreads / 2) ? 2 : 1);
-    const int c = tid / parts, part = tid - c * parts;
-    uint64_t mine = 0ull;
-    int rank = 0;
-    if (c < ncand) {
-      mine = keys[c];
-      for (int j = part; j < ncand; j += parts) rank += (keys[j] > mine) ? 1 : 0;
-    }
-    if (parts >= 2) rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
-    if (parts == 4) rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
-    __syncthreads();
-    if (c < ncand && part == 0) keys[rank] = mine;
-    __syncthreads();
-  } else {
-    // bitonic sort, descending, sort_n a power of two
-    for (int i = ncand + tid; i < p.sort_n; i += kTopkThreads) keys[i] = 0ull;
-    __syncthreads();
-    for (int size = 2; size <= p.sort_n; size <<= 1) {
-      for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        for (int i = tid; i < (p.sort_n >> 1); i += kTopkThreads) {
-          const int lo = 2 * i - (i & (stride - 1));
-          const int hi2 = lo + stride;
-          const bool desc = ((lo & size) == 0);
-          const uint64_t a = keys[lo], c = keys[hi2];
-          if ((a < c) == desc) { keys[lo] = c; keys[hi2] = a; }
+        __syncthreads();
+        JF_PHASE(6);
+        if (MODE == JF_MODE_K4V4) {
+          // one thread per candidate (integer arithmetic: order-free)
+          if (tid < cn) {
+            const int pos = static_cast<int>(keys[base + tid]);
+            const uint32_t* r = sm.rows + tid * W;
+            float s = -INFINITY;
+            if (sm.cand_slot[tid] >= 0)
+              s = canon_score_k4_thread(sm.qe, sm.qo, sm.qsum8, sm.qs, r, bf16_bits_to_f32(r[16] & 0xFFFFu), ctx.attn);
+            keys[base + tid] = make_key(s, pos);
+          }
+        } else {
+          // one warp per candidate, four candidates in flight per warp
+          for (int c0 = warp; c0 < cn; c0 += 4 * kSelWarps) {
+            float s[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = c0 + i * kSelWarps;
+              s[i] = -INFINITY;
+              if (c < cn && sm.cand_slot[c] >= 0) {
+                const uint32_t* r = sm.rows + c * W;
+                s[i] = canon_score_k3(sm.q, reinterpret_cast<const uint8_t*>(r), r[12], ctx.attn, lane);
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = c0 + i * kSelWarps;
+              if (c < cn && lane == i) keys[base + c] = make_key(s[i], static_cast<int>(keys[base + c]));
+            }
+          }
         }
         __syncthreads();
       }
+    } else {
+      // ---- slow exact path: 8-level radix select on the 64-bit canonical key ----
+      if (tid == 0) { sm.prefix = 0ull; sm.remaining = K; sm.ncand = 0; }
+      __syncthreads();
+      for (int level = 7; level >= 0; --level) {
+        for (int i = tid; i < 256; i += kSelThreads) hist[i] = 0;
+        __syncthreads();
+        const unsigned long long prefix = sm.prefix;
+        for (int i = warp; i < n; i += kSelWarps) {
+          const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
+          const bool match = (level == 7) || ((key >> (8 * (level + 1))) == prefix);
+          if (match && lane == 0) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+          int cum = 0, rem = sm.remaining, cb = 0;
+          for (int bin = 255; bin >= 0; --bin) {
+            if (cum + hist[bin] >= rem) { cb = bin; break; }
+            cum += hist[bin];
+          }
+          sm.remaining = rem - cum;
+          sm.prefix = (prefix << 8) | static_cast<unsigned long long>(cb);
+        }
+        __syncthreads();
+      }
+      const unsigned long long tkey = sm.prefix;  // key of the k-th best; keys are unique
+      for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+      __syncthreads();
+      for (int i = warp; i < n; i += kSelWarps) {
+        const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
+        if (key >= tkey && lane == 0) {
+          const int pos = atomicAdd(&sm.ncand, 1);
+          if (pos < p.sort_n) keys[pos] = key;
+        }
+      }
+      __syncthreads();
+      ncand = min(sm.ncand, p.sort_n);
     }
+    __syncthreads();
+
+    JF_PHASE(7);
+    // ---- order the candidates: best first ----
+    if (p.sort_n <= kSelThreads) {
+      // rank by counting (keys are unique): the ncand^2 comparisons are spread evenly, thread
+      // (c, part) counts the keys above candidate c among j = part, part + P, ...
+      int* rank = hist;
+      for (int i = tid; i < ncand; i += kSelThreads) rank[i] = 0;
+      __syncthreads();
+      const int P = kSelThreads / max(ncand, 1);
+      const int part = tid / max(ncand, 1), c = tid - part * max(ncand, 1);
+      if (part < P && ncand > 0) {
+        const uint64_t mine = keys[c];
+        int above = 0;
+#pragma unroll 4
+        for (int j = part; j < ncand; j += P) above += (keys[j] > mine) ? 1 : 0;
+        atomicAdd(&rank[c], above);
+      }
+      __syncthreads();
+      uint64_t mine = 0ull;
+      int r = 0;
+      if (tid < ncand) { mine = keys[tid]; r = rank[tid]; }
+      __syncthreads();
+      if (tid < ncand) keys[r] = mine;
+      __syncthreads();
+    } else {
+      // bitonic sort, descending, sort_n a power of two
+      for (int i = ncand + tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+      __syncthreads();
+      for (int size = 2; size <= p.sort_n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+          for (int i = tid; i < (p.sort_n >> 1); i += kSelThreads) {
+            const int lo = 2 * i - (i & (stride - 1));
+            const int hi2 = lo + stride;
+            const bool desc = ((lo & size) == 0);
+            const uint64_t a = keys[lo], c = keys[hi2];
+            if ((a < c) == desc) { keys[lo] = c; keys[hi2] = a; }
+          }
+          __syncthreads();
+        }
+      }
+    }
+    m_sel = min(ncand, K);
+    JF_PHASE(8);
   }
 
-  const int m = min(ncand, K);
-  for (int r = tid; r < K; r += kTopkThreads) {
+  for (int r = tid; r < K; r += kSelThreads) {
     int64_t idx = -1, slot = -1;
     float canon = -INFINITY;
-    if (r < m) {
-      idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(ranked[r] & 0xFFFFFFFFull));
+    if (r < m_sel) {
+      idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
       slot = slot_of(ctx, static_cast<int>(idx));
-      canon = float_from_order_key(static_cast<uint32_t>(ranked[r] >> 32));
+      canon = float_from_order_key(static_cast<uint32_t>(keys[r] >> 32));
     }
     out_idx[r] = idx;
     out_slot[r] = slot;
     out_canon[r] = canon;
   }
+  JF_PHASE(9);
+
+  if (FUSED) {
+    finish_tail<MODE>(tp, tsm, pre, row_max, n, b, h, ctx.bt, [&](int kk, int& pos, float& canon) {
+      if (kk >= m_sel) return false;
+      pos = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(keys[kk] & 0xFFFFFFFFull));
+      canon = float_from_order_key(static_cast<uint32_t>(keys[kk] >> 32));
+      return true;
+    });
+  }
 }
 
 int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
+template <int MODE, int DT>
+jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
+  const size_t smem = sizeof(TailSmem<MODE>) + sizeof(SelSmemFixed) + static_cast<size_t>(sp.sort_n) * 8;
+  constexpr size_t kMaxSmem = sizeof(TailSmem<MODE>) + sizeof(SelSmemFixed) + static_cast<size_t>(2 * JF_MAX_TOP_K) * 8;
+  static_assert(kMaxSmem <= 227 * 1024, "select kernel shared memory");
+  if (fused) {
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true>), kMaxSmem);
+    topk_select_kernel<MODE, DT, true><<<grid, kSelThreads, smem, stream>>>(sp, tp);
+  } else {
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, false>), kMaxSmem);
+    topk_select_kernel<MODE, DT, false><<<grid, kSelThreads, smem, stream>>>(sp, tp);
+  }
+  JF_CUDA_TRY(cudaGetLastError());
+  return JF_OK;
+}
+
 }  // namespace
 
-}  // namespace jf
+TailParams make_tail_params(const jf_decode_args* a, const Workspace& ws) {
+  TailParams tp{};
+  tp.scores = a->scores ? a->scores : ws.scores;
+  tp.part_o = ws.part_o; tp.part_m = ws.part_m; tp.part_l = ws.part_l;
+  tp.v_data = a->v_data; tp.v_scales = static_cast<const uint16_t*>(a->v_scales);
+  tp.o_hat = a->o_hat; tp.o_old = a->o_old_unnorm; tp.W = a->W;
+  tp.softmax_m = a->softmax_m; tp.softmax_inv_z = a->softmax_inv_z;
+  tp.num_slots = a->num_slots;
+  tp.H_q = a->H_q; tp.H_kv = a->H_kv; tp.G = a->H_q / a->H_kv;
+  tp.max_S = a->max_S;
+  tp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
+  tp.top_k = a->top_k;
+  return tp;
+}
 
-extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t stream_) {
-  using namespace jf;
+// select (fused = false) or select + finish in one kernel (fused = true)
+jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fused) {
   jf_status_t st = validate_decode_args(a);
   if (st != JF_OK) return st;
   if (!a->topk_idx || !a->topk_slots) return JF_ERR_ARG;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (fused && (!a->o_hat || !a->o_old_unnorm || !a->W)) return JF_ERR_ARG;
   Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
-  TopkParams tp{};
-  tp.scores = a->scores ? a->scores : ws.scores;
-  tp.part_m = ws.part_m; tp.part_smax = ws.part_smax;
-  tp.q = a->q; tp.k_data = a->k_data; tp.k_scales = static_cast<const uint16_t*>(a->k_scales);
-  tp.block_table = a->block_table; tp.seq_lens = a->seq_lens;
-  tp.topk_idx = a->topk_idx; tp.topk_slots = a->topk_slots; tp.sel_canon = ws.sel_canon;
-  tp.num_slots = a->num_slots;
-  tp.B = a->B; tp.H_q = a->H_q; tp.H_kv = a->H_kv; tp.G = a->H_q / a->H_kv;
-  tp.max_S = a->max_S; tp.max_blocks = a->max_blocks;
-  tp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
-  tp.top_k = a->top_k;
-  tp.sort_n = pow2_ceil(2 * a->top_k);
-  if (tp.sort_n < 512) tp.sort_n = 512;
-  tp.q_dtype = a->q_dtype;
-  tp.attn_scale = a->attn_scale;
-  constexpr size_t kFixedSmem = kBins * 4 + JF_HEAD_DIM * 4 + 16 + JF_HEAD_DIM + kRowChunk * 8 + kRowChunk * 17 * 4;
-  const size_t smem = static_cast<size_t>(tp.sort_n) * 8 + kFixedSmem;
-  constexpr size_t kTopkMaxSmem = static_cast<size_t>(2 * JF_MAX_TOP_K) * 8 + kFixedSmem;
-  dim3 grid(a->H_q, a->B);
-#define JF_TOPK(MODE, DT)                                                                              \
-  do {                                                                                                 \
-    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT>), kTopkMaxSmem);                                      \
-    topk_select_kernel<MODE, DT><<<grid, kTopkThreads, smem, stream>>>(tp);                            \
-  } while (0)
+  TopkParams sp{};
+  sp.scores = a->scores ? a->scores : ws.scores;
+  sp.part_m = ws.part_m; sp.part_smax = ws.part_smax;
+  sp.q = a->q; sp.k_data = a->k_data; sp.k_scales = static_cast<const uint16_t*>(a->k_scales);
+  sp.block_table = a->block_table; sp.seq_lens = a->seq_lens;
+  sp.topk_idx = a->topk_idx; sp.topk_slots = a->topk_slots; sp.sel_canon = ws.sel_canon;
+  sp.num_slots = a->num_slots;
+  sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = a->H_kv; sp.G = a->H_q / a->H_kv;
+  sp.max_S = a->max_S; sp.max_blocks = a->max_blocks;
+  sp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
+  sp.top_k = a->top_k;
+  sp.sort_n = pow2_ceil(2 * a->top_k);
+  if (sp.sort_n < 512) sp.sort_n = 512;
+  sp.q_dtype = a->q_dtype;
+  sp.attn_scale = a->attn_scale;
+  const TailParams tp = make_tail_params(a, ws);
+  const dim3 grid(a->H_q, a->B);
   if (a->mode == JF_MODE_K3V2) {
-    if (a->q_dtype == JF_DTYPE_BF16) JF_TOPK(JF_MODE_K3V2, JF_DTYPE_BF16); else JF_TOPK(JF_MODE_K3V2, JF_DTYPE_FP16);
-  } else {
-    if (a->q_dtype == JF_DTYPE_BF16) JF_TOPK(JF_MODE_K4V4, JF_DTYPE_BF16); else JF_TOPK(JF_MODE_K4V4, JF_DTYPE_FP16);
+    return a->q_dtype == JF_DTYPE_BF16 ? launch_select_variant<JF_MODE_K3V2, JF_DTYPE_BF16>(sp, tp, grid, stream, fused)
+                                       : launch_select_variant<JF_MODE_K3V2, JF_DTYPE_FP16>(sp, tp, grid, stream, fused);
   }
-#undef JF_TOPK
-  JF_CUDA_TRY(cudaGetLastError());
-  return JF_OK;
+  return a->q_dtype == JF_DTYPE_BF16 ? launch_select_variant<JF_MODE_K4V4, JF_DTYPE_BF16>(sp, tp, grid, stream, fused)
+                                     : launch_select_variant<JF_MODE_K4V4, JF_DTYPE_FP16>(sp, tp, grid, stream, fused);
+}
+
+}  // namespace jf
+
+#ifdef JF_PHASE_TIMING
+extern "C" int jf_debug_phase_times(unsigned long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_phase_t, sizeof(g_phase_t)));
+}
+#endif
+
+extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t stream) {
+  return jf::launch_select(a, static_cast<cudaStream_t>(stream), false);
 }

@@ -149,3 +149,39 @@ def test_phases_one_by_one_equal_fused():
     step = call.result()
     for a, b in zip(fused[:7], step[:7]):
         assert torch.equal(a, b)
+
+
+def test_phases_one_by_one_equal_fused_k4v4_long_row():
+    """Long enough for the histogram tiers (ctx > 2 * top_k); K4V4; both kernels must agree bit for bit."""
+    from jetfire_b200 import ops
+    case = Case("k4v4", 2, 8, 2, 4096, seed=18)
+    kd, ks, vd, vs = case.device_cache()
+    args = (case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+            case.ctx, case.H_q, case.H_kv, 16, 256, case.attn_scale)
+    fused = ops.fused_attn_topk(*args)
+    call = ops.DecodeCall(*args)
+    call.scan(); call.select(); call.finish(); call.status()
+    step = call.result()
+    for a, b in zip(fused[:7], step[:7]):
+        assert torch.equal(a, b)
+
+
+def test_status_record_is_read_once_and_needs_no_initialisation():
+    """The workspace's status record counts only when tagged; reading an error clears it.
+    The record is written from the host here: no kernel is made to time out."""
+    import struct
+    from jetfire_b200 import ops
+    case = Case("k3v2", 1, 8, 2, 256, seed=3)
+    kd, ks, vd, vs = case.device_cache()
+    nbytes = ops.decode_workspace_bytes("k3v2", 1, case.H_q, case.H_kv, case.ctx, 32) + 256
+    ws = torch.full((nbytes,), 0xA5, dtype=torch.uint8, device="cuda")     # garbage, never zeroed
+    call = ops.DecodeCall(case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+                          case.ctx, case.H_q, case.H_kv, 16, 32, case.attn_scale, workspace=ws)
+    call.fused()
+    call.status()                                                           # untagged garbage reads as ok
+    off = (ws.data_ptr() + 255) // 256 * 256 - ws.data_ptr()
+    rec = struct.pack("<Qii", 0x4A46535441545553, 2, 0)                     # tag, JF_ERR_TIMEOUT
+    ws[off:off + 16] = torch.tensor(list(rec), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):
+        call.status()
+    call.status()                                                           # cleared by the read
