@@ -499,7 +499,7 @@ def main():
                        "l2": f"inputs larger than L2: {step_bytes / 1e6:.0f} MB of packed KV per step, each byte read once"},
             "tokens_per_s": w["batch"] * world / (ms_step * 1e-3),
             "us_per_layer": ms_step * 1e3 / n_layers,
-            "gpu_launches": 4 * n_layers * args.steps,
+            "gpu_launches": 3 * n_layers * args.steps,  # per layer: scan, select+finish, merge
             "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": sampler.summary(),
         }
         print(json.dumps(line), flush=True)

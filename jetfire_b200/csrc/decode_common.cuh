@@ -44,7 +44,6 @@ struct Workspace {
   float* part_m;     // [B][H_kv][splits][8]
   float* part_l;     // [B][H_kv][splits][8]
   float* part_smax;  // [B][H_kv][splits][2]  largest K group scale seen (per group)
-  float* sel_canon;  // [B][H_q][top_k] canonical scores of the selected positions
   float* scores;     // [B][H_q][max_S] approximate scores
   uint64_t bytes;
 };
@@ -52,7 +51,7 @@ struct Workspace {
 __host__ __device__ inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
 // Sized for the variant with the most splits (bf16 query), so one workspace serves both dtypes.
-inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv, int max_S, int top_k, bool need_scores) {
+inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv, int max_S, int /*top_k*/, bool need_scores) {
   const uint64_t splits = scan_splits(mode, JF_DTYPE_BF16, B, H_kv, max_S);
   const uint64_t pairs = static_cast<uint64_t>(B) * H_kv * splits;
   uint64_t off = 0;
@@ -63,7 +62,6 @@ inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv,
   w.part_m = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
   w.part_l = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
   w.part_smax = reinterpret_cast<float*>(p + off);  off = align_up(off + pairs * 2 * 4, 256);
-  w.sel_canon = reinterpret_cast<float*>(p + off);  off = align_up(off + static_cast<uint64_t>(B) * H_q * top_k * 4, 256);
   w.scores = reinterpret_cast<float*>(p + off);
   if (need_scores) off = align_up(off + static_cast<uint64_t>(B) * H_q * max_S * 4, 256);
   w.bytes = off;

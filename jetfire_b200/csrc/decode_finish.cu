@@ -11,7 +11,6 @@ namespace jf {
 namespace {
 
 struct FinishParams {
-  const float* sel_canon;
   const int64_t* block_table;
   const int32_t* seq_lens;
   const int64_t* topk_idx;
@@ -34,13 +33,12 @@ decode_finish_kernel(const FinishParams p, const TailParams tp) {
   const int n = min(p.seq_lens[b], tp.max_S);
   const float M = block_max_of_splits(tp.part_m, pbase, hi, tp.splits, sm_m);
   const int64_t* sel = p.topk_idx + bh * tp.top_k;
-  const float* canon_row = p.sel_canon + bh * tp.top_k;
-  finish_tail<MODE>(tp, tsm, pre, M, n, b, h, p.block_table + static_cast<int64_t>(b) * p.max_blocks,
-                    [&](int kk, int& pos, float& canon) {
+  finish_tail<MODE>(tp, tsm, TailPrefetch{}, pre, M, n, b, h, p.block_table + static_cast<int64_t>(b) * p.max_blocks,
+                    [&](int kk, int& pos, int& cidx) {
                       const int64_t v = sel[kk];
                       if (v < 0 || v >= n) return false;
                       pos = static_cast<int>(v);
-                      canon = canon_row[kk];
+                      cidx = -1;
                       return true;
                     });
 }
@@ -68,7 +66,6 @@ extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t str
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   FinishParams fp{};
-  fp.sel_canon = ws.sel_canon;
   fp.block_table = a->block_table; fp.seq_lens = a->seq_lens; fp.topk_idx = a->topk_idx;
   fp.max_blocks = a->max_blocks;
   const TailParams tp = make_tail_params(a, ws);

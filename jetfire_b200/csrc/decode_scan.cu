@@ -253,6 +253,9 @@ scan_k3v2_kernel(const ScanParams p) {
   const int64_t n_blocks_phys = p.num_slots >> 4;
 
   // One elected lane issues the four bulk copies of a page (K data, V data, K scales, V scales).
+  // The packed cache is read once per call: fetched as first-to-evict, it leaves the scores
+  // this kernel writes (and the next kernel reads) in L2.
+  const uint64_t stream_policy = l2_policy_evict_first();
   const int64_t head_rows = static_cast<int64_t>(hkv) * p.num_slots;
   const uint8_t* kd_h = p.k_data + head_rows * T::kKRow;
   const uint8_t* vd_h = p.v_data + head_rows * T::kVRow;
@@ -271,10 +274,10 @@ scan_k3v2_kernel(const ScanParams p) {
     if (elect_one()) {
       if (slow) page_valid[st_idx] = bad ? 0 : min(16, len - pg * 16);
       mbar_expect_tx_u32(bar, T::kBytes);
-      bulk_g2s_u32(dst + T::kKOff, kd_h + blk * (16 * T::kKRow), 16 * T::kKRow, bar);
-      bulk_g2s_u32(dst + T::kVOff, vd_h + blk * (16 * T::kVRow), 16 * T::kVRow, bar);
-      bulk_g2s_u32(dst + T::kKsOff, ks_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
-      bulk_g2s_u32(dst + T::kVsOff, vs_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
+      bulk_g2s_u32_hint(dst + T::kKOff, kd_h + blk * (16 * T::kKRow), 16 * T::kKRow, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T::kVOff, vd_h + blk * (16 * T::kVRow), 16 * T::kVRow, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T::kKsOff, ks_h + blk * (32 * T::kNG), 32 * T::kNG, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T::kVsOff, vs_h + blk * (32 * T::kNG), 32 * T::kNG, bar, stream_policy);
     }
   };
 

@@ -55,16 +55,12 @@ __device__ __forceinline__ void mma_u8s8_cd(int (&d)[4], const int (&c)[4], uint
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_2d_u32(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar,
+                                                uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_u32(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
       : "memory");
 }
 
@@ -213,6 +209,9 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   uint32_t slow_mask = 0u;
 
   // One elected lane issues the page's two tensor copies (K, V) and two scale copies.
+  // The packed cache is read once per call: fetched as first-to-evict, it leaves the scores
+  // this kernel writes (and the next kernel reads) in L2.
+  const uint64_t stream_policy = l2_policy_evict_first();
   auto issue = [&](int it, int st_idx, int64_t blk64) {
     const int pg = pg_begin + warp + it * kScanWarps;
     const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
@@ -225,10 +224,10 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       if (slow) page_valid[st_idx] = bad ? 0 : min(16, len - pg * 16);
       mbar_expect_tx_u32(bar, T4::kTxBytes);
       const int y = static_cast<int>(row_base + blk * 16);
-      tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, y, bar);
-      tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, y, bar);
-      bulk_g2s_u32(dst + T4::kKsOff, ks_h + blk * 16, 32, bar);
-      bulk_g2s_u32(dst + T4::kVsOff, vs_h + blk * 16, 32, bar);
+      tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, y, bar, stream_policy);
+      tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, y, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T4::kKsOff, ks_h + blk * 16, 32, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T4::kVsOff, vs_h + blk * 16, 32, bar, stream_policy);
     }
   };
 

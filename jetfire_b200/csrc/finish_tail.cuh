@@ -1,16 +1,10 @@
 // Finish stage shared by the fused select+finish kernel and the stand-alone finish kernel:
 // merge the scan's split partials (log-sum-exp) into o_hat and the softmax statistics, and
-// compute the approximate contribution of the selected set,
+// compute the approximate contribution of the selected set from the scan's own scores,
 //   W = sum_{i in T} p_i,   o_old_unnorm[d] = sum_{i in T} (p_i * vscale_i,g(d)) * vcode_i,d
-// (jetfire_vllm/csrc/int2_softmax_v.cu:738-788; V4: csrc/int4_softmax_v.cu:599-817).
-//
-// Weight swap for the selected set.  The scan's fp32 score of a position can differ from
-// the canonical score in the last bits (summation order), and the reference's Stage B uses
-// the scores its Stage A produced.  For every selected position the select stage has the
-// canonical score s_c; here the scan's weight exp(s_f - M) is replaced by exp(s_c - M) in
-// the numerator, the normaliser and the selected-set terms, so that p_i of the selected
-// set follows the canonical arithmetic and the remaining (individually small) weights keep
-// the scan's scores.
+// (jetfire_vllm/csrc/int2_softmax_v.cu:738-788; V4: csrc/int4_softmax_v.cu:599-817), as the
+// reference's Stage B does with the scores of its Stage A: what the later merge subtracts
+// is exactly what the approximate pass added for these positions.
 //
 // Both kernels run this code with the same block size, so their results are bit-equal;
 // every summation order is fixed (no floating-point atomics).
@@ -27,8 +21,13 @@ static __device__ unsigned long long g_phase_t[64];
   do {                                                                                       \
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_t[i] = clock64();    \
   } while (0)
+#define JF_PHASE_VAL(i, v)                                                                   \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_t[i] = (v);          \
+  } while (0)
 #else
 #define JF_PHASE(i) do { } while (0)
+#define JF_PHASE_VAL(i, v) do { } while (0)
 #endif
 
 namespace jf {
@@ -61,11 +60,11 @@ struct TailSmem {
   static constexpr int VW = (MODE == JF_MODE_K3V2) ? 8 : 16;  // 32-bit words per packed V row
   uint32_t v[kTailChunk * VW];                                 // first: 16-byte aligned
   int64_t slot[kTailChunk];
-  float wc[kTailChunk][2];   // canonical weight * v scale (per group)
-  float dw[kTailChunk][2];   // (canonical - scan) weight * v scale
-  float w[kTailChunk][2];    // canonical weight, weight difference
-  float red[kSelWarps][JF_HEAD_DIM][2];
-  float sum[kSelWarps][2];
+  int cidx[kTailChunk];      // candidate index in the prefetched arrays, or -1
+  float wv[kTailChunk][2];   // weight * v scale (per group)
+  float w[kTailChunk];       // weight
+  float red[kSelWarps][JF_HEAD_DIM];
+  float sum[kSelWarps];
   float o[kSplitGroups][JF_HEAD_DIM];
   float z[kSplitGroups];
 };
@@ -97,12 +96,23 @@ __device__ __forceinline__ float small_code_to_f32(uint32_t code, float bias) {
   return __uint_as_float(0x4B000000u | code) - (8388608.0f + bias);
 }
 
-// `src(kk, pos, canon)` yields the kk-th selected entry (rank order): its position and
-// canonical score; false if there is none.  M = max over the splits of the scan's
-// reference points.  n = sequence length.
+// What the fused kernel already holds in shared memory per candidate (null pointers in the
+// stand-alone kernel): slot, scan score, V scales, packed V row.  The values are the ones
+// the stand-alone kernel reads from global memory, so both give the same bits.
+struct TailPrefetch {
+  const int64_t* slot;
+  const float* score;
+  const uint32_t* vsc;    // K3: both group scales; K4: the aligned pair of scales that holds this slot's
+  const uint32_t* vrows;
+};
+
+// `src(kk, pos, cidx)` yields the kk-th selected entry (rank order): its position and its
+// index in the prefetched arrays (-1: none); false if there is no such entry.  M = max over
+// the splits of the scan's reference points.  n = sequence length.
 template <int MODE, typename Src>
-__device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>& sm, const SplitPre& pre, float M, int n,
-                                            int b, int h, const int64_t* bt, Src src) {
+__device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>& sm, const TailPrefetch& pf,
+                                            const SplitPre& pre, float M, int n, int b, int h, const int64_t* bt,
+                                            Src src) {
   constexpr int VW = TailSmem<MODE>::VW;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hkv = h / p.G, hi = h - hkv * p.G;
@@ -133,31 +143,39 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
   }
 
   JF_PHASE(21);
-  // ---- selected set: canonical weights, and their difference to the scan's ----
+  // ---- selected set: weights from the scan's scores ----
   const ModeInfo mi = mode_info(MODE);
   const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
   const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
   const float* srow = p.scores + bh * p.max_S;
-  float a_old[4] = {0.f, 0.f, 0.f, 0.f}, a_dw[4] = {0.f, 0.f, 0.f, 0.f};
-  float wsum = 0.f, dz = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float wsum = 0.f;
   const int qg = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
   for (int k0 = 0; k0 < p.top_k; k0 += kTailChunk) {
     const int kend = min(kTailChunk, p.top_k - k0);
     if (tid < kTailChunk) {
       int64_t slot = -1;
-      float wc = 0.f, dw = 0.f, vs0 = 0.f, vs1 = 0.f;
-      int pos = -1;
-      float canon = 0.f;
-      if (tid < kend && n > 0 && src(k0 + tid, pos, canon) && pos >= 0 && pos < n) {
-        const int64_t blk = bt[pos >> 4];
-        const float approx = srow[pos];  // independent of the block-table lookup
-        if (blk >= 0 && blk < (p.num_slots >> 4)) {
-          slot = blk * 16 + (pos & 15);
-          uint32_t sw;
-          if (MODE == JF_MODE_K3V2) sw = __ldg(reinterpret_cast<const uint32_t*>(v_sc + slot * 2));
-          else sw = __ldg(v_sc + slot);
-          wc = ex2((canon - M) * kLog2e);
-          dw = wc - ex2((approx - M) * kLog2e);
+      float w = 0.f, vs0 = 0.f, vs1 = 0.f;
+      int pos = -1, cidx = -1;
+      if (tid < kend && n > 0 && src(k0 + tid, pos, cidx) && pos >= 0 && pos < n) {
+        float approx = 0.f;
+        uint32_t sw = 0u;
+        if (cidx >= 0) {
+          slot = pf.slot[cidx];
+          approx = pf.score[cidx];
+          sw = pf.vsc[cidx];
+          if (MODE == JF_MODE_K4V4) sw = (slot & 1) ? (sw >> 16) : (sw & 0xFFFFu);  // the pair that holds the scale
+        } else {
+          const int64_t blk = bt[pos >> 4];
+          approx = srow[pos];  // independent of the block-table lookup
+          if (blk >= 0 && blk < (p.num_slots >> 4)) {
+            slot = blk * 16 + (pos & 15);
+            if (MODE == JF_MODE_K3V2) sw = __ldg(reinterpret_cast<const uint32_t*>(v_sc + slot * 2));
+            else sw = __ldg(v_sc + slot);
+          }
+        }
+        if (slot >= 0) {
+          w = ex2((approx - M) * kLog2e);
           if (MODE == JF_MODE_K3V2) {
             vs0 = __uint_as_float(sw << 16);
             vs1 = __uint_as_float(sw & 0xFFFF0000u);
@@ -167,9 +185,9 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
         }
       }
       sm.slot[tid] = slot;
-      sm.w[tid][0] = wc; sm.w[tid][1] = dw;
-      sm.wc[tid][0] = wc * vs0; sm.wc[tid][1] = wc * vs1;
-      sm.dw[tid][0] = dw * vs0; sm.dw[tid][1] = dw * vs1;
+      sm.cidx[tid] = cidx;
+      sm.w[tid] = w;
+      sm.wv[tid][0] = w * vs0; sm.wv[tid][1] = w * vs1;
     }
     __syncthreads();
     JF_PHASE(22);
@@ -177,8 +195,12 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
     for (int u = tid; u < kend * (VW / 4); u += kSelThreads) {
       const int c = u / (VW / 4), part = u - c * (VW / 4);
       const int64_t slot = sm.slot[c];
+      const int cidx = sm.cidx[c];
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (slot >= 0) v = __ldg(reinterpret_cast<const uint4*>(v_rows + slot * (VW * 4)) + part);
+      if (slot >= 0) {
+        if (cidx >= 0) v = reinterpret_cast<const uint4*>(pf.vrows)[cidx * (VW / 4) + part];
+        else v = __ldg(reinterpret_cast<const uint4*>(v_rows + slot * (VW * 4)) + part);
+      }
       reinterpret_cast<uint4*>(sm.v)[u] = v;
     }
     __syncthreads();
@@ -186,14 +208,14 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
     // warp w takes entries w, w + 32, ...; lane l owns channels 4l..4l+3
     {
       uint32_t raw[kTailPerWarp];
-      float fw[kTailPerWarp], fd[kTailPerWarp], w0[kTailPerWarp], w1[kTailPerWarp];
+      float fw[kTailPerWarp], w0[kTailPerWarp];
 #pragma unroll
       for (int i = 0; i < kTailPerWarp; ++i) {
-        const int j = warp + i * kSelWarps;  // < kTailChunk; rows past kend hold zero weights
+        const int j = warp + i * kSelWarps;  // < kTailChunk; entries past kend hold zero weights
         raw[i] = (MODE == JF_MODE_K3V2) ? static_cast<uint32_t>(reinterpret_cast<const uint8_t*>(sm.v + j * VW)[lane])
                                         : static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(sm.v + j * VW)[lane]);
-        fw[i] = sm.wc[j][qg]; fd[i] = sm.dw[j][qg];
-        w0[i] = sm.w[j][0]; w1[i] = sm.w[j][1];
+        fw[i] = sm.wv[j][qg];
+        w0[i] = sm.w[j];
       }
 #pragma unroll
       for (int i = 0; i < kTailPerWarp; ++i) {
@@ -210,31 +232,26 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
           c[3] = small_code_to_f32((raw[i] >> 8) & 15u, 8.0f);
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { a_old[e] = fmaf(fw[i], c[e], a_old[e]); a_dw[e] = fmaf(fd[i], c[e], a_dw[e]); }
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(fw[i], c[e], acc[e]);
         wsum += w0[i];
-        dz += w1[i];
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int e = 0; e < 4; ++e) { sm.red[warp][4 * lane + e][0] = a_old[e]; sm.red[warp][4 * lane + e][1] = a_dw[e]; }
-  if (lane == 0) { sm.sum[warp][0] = wsum; sm.sum[warp][1] = dz; }
+  for (int e = 0; e < 4; ++e) sm.red[warp][4 * lane + e] = acc[e];
+  if (lane == 0) sm.sum[warp] = wsum;
   __syncthreads();
   JF_PHASE(24);
   if (tid < JF_HEAD_DIM) {
-    float acc_old = 0.f, acc_dw = 0.f, ws = 0.f, dzs = 0.f, o = 0.f, Z = 0.f;
+    float acc_old = 0.f, ws = 0.f, o = 0.f, Z = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSelWarps; ++w) {
-      acc_old += sm.red[w][tid][0]; acc_dw += sm.red[w][tid][1];
-      ws += sm.sum[w][0]; dzs += sm.sum[w][1];
-    }
+    for (int w = 0; w < kSelWarps; ++w) { acc_old += sm.red[w][tid]; ws += sm.sum[w]; }
 #pragma unroll
     for (int gI = 0; gI < kSplitGroups; ++gI) { o += sm.o[gI][tid]; Z += sm.z[gI]; }
-    Z += dzs;
     const bool live = (Z > 0.f) && (n > 0);
     const float inv_z = live ? (1.0f / Z) : 0.f;
-    p.o_hat[bh * JF_HEAD_DIM + tid] = (o + acc_dw) * inv_z;
+    p.o_hat[bh * JF_HEAD_DIM + tid] = o * inv_z;
     p.o_old[bh * JF_HEAD_DIM + tid] = acc_old * inv_z;
     if (tid == 0) {
       p.W[bh] = ws * inv_z;

@@ -35,7 +35,7 @@ struct TopkParams {
   const int32_t* seq_lens;
   int64_t* topk_idx;
   int64_t* topk_slots;
-  float* sel_canon;
+  int32_t* status;
   int64_t num_slots;
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
   float attn_scale;
@@ -130,59 +130,58 @@ __device__ __forceinline__ int score_bin(float top64, float s) {
   return __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
 }
 
-// Canonical K4/G128 score by ONE thread.  The integer dot products are exact, so any order
-// gives the value of canon_score_k4: byte B of the packed row holds channel 2B in its high
-// nibble and channel 2B + 1 in its low nibble; `qe` / `qo` are the INT8 query's even / odd
-// channels packed four to a word, `qsum8[c]` = 8 * (sum of the query over block c) removes
-// the code offset.
-__device__ __forceinline__ float canon_score_k4_thread(const uint32_t* qe, const uint32_t* qo, const int* qsum8,
-                                                       const float* qs, const uint32_t* row, float ks, float attn) {
-  float s = 0.f;
-#pragma unroll
-  for (int blk = 0; blk < 4; ++blk) {
-    int acc = -qsum8[blk];
-#pragma unroll
-    for (int w = 4 * blk; w < 4 * blk + 4; ++w) {
-      const uint32_t word = row[w];
-      acc = __dp4a(static_cast<int>((word >> 4) & 0x0F0F0F0Fu), static_cast<int>(qe[w]), acc);
-      acc = __dp4a(static_cast<int>(word & 0x0F0F0F0Fu), static_cast<int>(qo[w]), acc);
-    }
-    s = __fmaf_rn(static_cast<float>(acc), qs[blk], s);
-  }
-  return __fmul_rn(__fmul_rn(s, ks), attn);
-}
-
 constexpr int kRowChunk = 512;                 // candidates staged in shared memory per round
-constexpr int kScoreRegs = 32;                 // scores cached per thread (32768 positions per CTA)
-constexpr int kScoreChunk = kScoreRegs * kSelThreads;
+constexpr int kChunkPos = 32768;               // positions of the row held in shared memory at a time
+constexpr int kChunkVec = kChunkPos / (4 * kSelThreads);  // float4 reads per thread and pass
 template <int MODE> struct RowWords { static constexpr int v = (MODE == JF_MODE_K3V2) ? 13 : 17; };
 
 struct SelSmemFixed {
+  uint64_t bar;               // mbarrier of the score-chunk copy
+  unsigned long long prefix;
   int hist[kBins];
   float q[JF_HEAD_DIM];
   float qs[4];
-  int qsum8[4];
-  uint32_t qe[16], qo[16];
   int8_t qi[JF_HEAD_DIM];
-  int64_t cand_slot[kRowChunk];
-  uint32_t rows[kRowChunk * 17];
   float w3[kSelWarps][3];
   float red[4];
   int wsum[kSelWarps];
-  int ncand, last, fallback, tbin, remaining;
-  unsigned long long prefix;
+  int ncand, tbin, remaining, pad_;
 };
 
-// One CTA per (query head, batch element).  FUSED: the finish stage follows in the same
-// kernel (the selected list never leaves the SM).
+// What lives in the score chunk's shared memory once the candidates are collected.
+template <int MODE>
+struct SelSmemLate {
+  TailSmem<MODE> tail;
+  uint32_t vrows[kRowChunk * TailSmem<MODE>::VW];  // packed V rows of the candidates (fused kernel)
+  int64_t cand_slot[kRowChunk];
+  uint32_t rows[kRowChunk * 17];                   // packed K rows + scales
+  uint32_t vsc[kRowChunk];                         // V scales
+};
+
+constexpr size_t kSelChunkBytes = static_cast<size_t>(kChunkPos) * 4;
+__host__ __device__ constexpr size_t sel_smem_bytes(int sort_n) {
+  // chunk | fixed | keys[sort_n] | cand_score[sort_n] | perm[sort_n] | bucket[sort_n]
+  return kSelChunkBytes + sizeof(SelSmemFixed) + static_cast<size_t>(sort_n) * 8 +
+         static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4;
+}
+
+// One CTA per (query head, batch element).  The row's approximate scores are pulled into
+// shared memory by one bulk copy per 32768 positions, issued before anything else so that
+// the prologue runs under it; every later pass over the scores reads shared memory.
+// FUSED: the finish stage follows in the same kernel.
 template <int MODE, int DT, bool FUSED>
 __global__ void __launch_bounds__(kSelThreads)
 topk_select_kernel(const TopkParams p, const TailParams tp) {
   constexpr int W = RowWords<MODE>::v;         // 32-bit words staged per candidate: data + scales
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  TailSmem<MODE>& tsm = *reinterpret_cast<TailSmem<MODE>*>(smem_raw);
-  SelSmemFixed& sm = *reinterpret_cast<SelSmemFixed*>(smem_raw + sizeof(TailSmem<MODE>));
-  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw + sizeof(TailSmem<MODE>) + sizeof(SelSmemFixed));  // [sort_n]
+  static_assert(sizeof(SelSmemLate<MODE>) <= kSelChunkBytes, "late shared memory must fit in the score chunk");
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float* chunk = reinterpret_cast<float*>(smem_raw);
+  SelSmemLate<MODE>& late = *reinterpret_cast<SelSmemLate<MODE>*>(smem_raw);
+  SelSmemFixed& sm = *reinterpret_cast<SelSmemFixed*>(smem_raw + kSelChunkBytes);
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw + kSelChunkBytes + sizeof(SelSmemFixed));  // [sort_n]
+  float* cand_score = reinterpret_cast<float*>(keys + p.sort_n);  // [sort_n] scan score per candidate
+  uint16_t* perm = reinterpret_cast<uint16_t*>(cand_score + p.sort_n);             // [sort_n] rank -> candidate
+  uint16_t* bucket = perm + p.sort_n;                                              // [sort_n] candidates grouped by bin
   int* hist = sm.hist;
 
   JF_PHASE(0);
@@ -194,48 +193,62 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   const float* srow = p.scores + bh * p.max_S;
   const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
 
-  // ---- the row's scores go to registers first: nothing else depends on them yet, so their
-  //      latency hides behind the prologue.  Positions past the sequence are masked later;
-  //      the row's allocation covers max_S. ----
-  const bool vec = (p.max_S & 3) == 0;     // rows start on 16-byte boundaries
-  float sc[kScoreRegs];
-  auto pos_of = [&](int ci, int e) {
-    return vec ? ci * kScoreChunk + 4 * ((e >> 2) * kSelThreads + tid) + (e & 3)
-               : ci * kScoreChunk + e * kSelThreads + tid;
-  };
-  auto load_chunk = [&](int ci) {
+  // ---- score chunks: bulk copy (16-byte aligned rows) or plain loads ----
+  const bool vec = ((p.max_S & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0);
+  uint32_t phase = 0;
+  auto issue_chunk = [&](int ci) {  // the row's allocation covers max_S positions
+    const int cnt = min(kChunkPos, p.max_S - ci * kChunkPos);
     if (vec) {
-#pragma unroll
-      for (int j = 0; j < kScoreRegs / 4; ++j) {
-        const int p0 = ci * kScoreChunk + 4 * (j * kSelThreads + tid);
-        float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-        if (p0 < p.max_S) v = *reinterpret_cast<const float4*>(srow + p0);  // max_S % 4 == 0: stays inside the row
-        sc[4 * j] = v.x; sc[4 * j + 1] = v.y; sc[4 * j + 2] = v.z; sc[4 * j + 3] = v.w;
+      if (tid == 0) {
+        fence_proxy_async();
+        mbar_expect_tx(&sm.bar, static_cast<uint32_t>(cnt) * 4u);
+        bulk_g2s(chunk, srow + static_cast<int64_t>(ci) * kChunkPos, static_cast<uint32_t>(cnt) * 4u, &sm.bar);
       }
     } else {
-#pragma unroll
-      for (int e = 0; e < kScoreRegs; ++e) {
-        const int pp = ci * kScoreChunk + e * kSelThreads + tid;
-        sc[e] = (pp < p.max_S) ? srow[pp] : -INFINITY;
-      }
+      for (int i = tid; i < cnt; i += kSelThreads) chunk[i] = srow[static_cast<int64_t>(ci) * kChunkPos + i];
     }
   };
-  load_chunk(0);
+  // Block-wide; positions past the sequence read as -inf afterwards.  False (for every
+  // thread) if the copy did not arrive within the wait's budget.
+  auto wait_chunk = [&](int ci, int n) {
+    bool ok = true;
+    if (vec) {
+      ok = mbar_wait(&sm.bar, phase);
+      if (!ok) ok = mbar_wait(&sm.bar, phase);  // once more for the copy still in flight
+      phase ^= 1u;
+    }
+    const int valid = max(0, min(n - ci * kChunkPos, kChunkPos));
+    if (!vec) __syncthreads();
+    for (int i = valid + tid; i < kChunkPos; i += kSelThreads) chunk[i] = -INFINITY;
+    return __syncthreads_and(ok ? 1 : 0) != 0;
+  };
+  if (tid == 0) {
+    mbar_init(&sm.bar, 1);
+    fence_barrier_init();
+  }
+
+  // ---- small loads first (they are what the prologue waits for), then the 128 KB copy ----
+  uint16_t q_bits = 0;
+  if (tid < JF_HEAD_DIM) q_bits = reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid];
+  float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
+  if (tid < p.splits) {  // the first split of this thread; the loop below takes the rest
+    top = p.part_m[(pbase + tid) * kHeadsPad + hi];
+    sm0 = p.part_smax[(pbase + tid) * 2];
+    sm1 = p.part_smax[(pbase + tid) * 2 + 1];
+  }
+  const int n_seq_raw = p.seq_lens[b];
   SplitPre pre;
   if (FUSED) split_preload(tp, pbase, hi, tid, pre);
+  issue_chunk(0);
 
-  const int n = min(p.seq_lens[b], p.max_S);
+  const int n_seq = min(n_seq_raw, p.max_S);
   int64_t* out_idx = p.topk_idx + bh * K;
   int64_t* out_slot = p.topk_slots + bh * K;
-  float* out_canon = p.sel_canon + bh * K;
 
   // ---- query row (exact values), per-group L1 norms, INT8 model for K4; split statistics ----
-  if (tid < JF_HEAD_DIM) {
-    sm.q[tid] = Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid]);
-  }
+  if (tid < JF_HEAD_DIM) sm.q[tid] = Elem<DT>::to_f32(q_bits);
   {
-    float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
-    for (int s = tid; s < p.splits; s += kSelThreads) {
+    for (int s = tid + kSelThreads; s < p.splits; s += kSelThreads) {
       top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
       sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
       sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
@@ -249,6 +262,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     if (lane == 0) { sm.w3[warp][0] = top; sm.w3[warp][1] = sm0; sm.w3[warp][2] = sm1; }
   }
   __syncthreads();
+  JF_PHASE(11);
   if (warp < 4) {  // warp w handles channels 32w..32w+31
     const float v = sm.q[32 * warp + lane];
     float a = fabsf(v), s1 = fabsf(v) + 0.001953125f;
@@ -262,21 +276,11 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       const float inv = __fdiv_rn(1.0f, qs);
       const int qv = max(-128, min(127, __float2int_rn(__fmul_rn(v, inv))));
       sm.qi[32 * warp + lane] = static_cast<int8_t>(qv);
-      int qsum = qv;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xFFFFFFFFu, qsum, o);
-      // words of four even / four odd channels: lanes 8k..8k+7 make word 4 * warp + k
-      const uint32_t byte = static_cast<uint32_t>(qv) & 0xFFu;
-      const uint32_t b2 = __shfl_down_sync(0xFFFFFFFFu, byte, 2), b4 = __shfl_down_sync(0xFFFFFFFFu, byte, 4),
-                     b6 = __shfl_down_sync(0xFFFFFFFFu, byte, 6);
-      const uint32_t word = byte | (b2 << 8) | (b4 << 16) | (b6 << 24);
-      if ((lane & 7) == 0) sm.qe[4 * warp + (lane >> 3)] = word;
-      if ((lane & 7) == 1) sm.qo[4 * warp + (lane >> 3)] = word;
-      if (lane == 0) { sm.qs[warp] = qs; sm.qsum8[warp] = 8 * qsum; }
+      if (lane == 0) sm.qs[warp] = qs;
     }
     if (lane == 0) sm.red[warp] = s1;
   }
-  if (tid == 0) { sm.ncand = 0; sm.fallback = 0; sm.tbin = -1; }
+  if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
   for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
   for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
   __syncthreads();
@@ -295,14 +299,22 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
 #pragma unroll
   for (int w = 0; w < kSelWarps; ++w) row_max = fmaxf(row_max, sm.w3[w][0]);
 
+  // the copy issued at the top must have landed before its shared memory is reused
+  bool copied = wait_chunk(0, n_seq);
+  if (!copied && tid == 0) report_status(p.status, JF_ERR_TIMEOUT);
+  const int n = copied ? n_seq : 0;   // a row whose scores did not arrive selects nothing
+  JF_PHASE(2);
+
   int m_sel = 0;  // entries of keys[] that hold the ranked result
+  bool prefetch = false;
   if (n > 0) {
     int ncand = 0;
+    int cand_last = kBins;  // bound on the candidates' canonical-score bin, when one is known
     bool slow = false;
 
     if (n <= p.sort_n) {
       // short row: every position is a candidate
-      for (int i = tid; i < n; i += kSelThreads) keys[i] = static_cast<uint64_t>(i);
+      for (int i = tid; i < n; i += kSelThreads) { keys[i] = static_cast<uint64_t>(i); cand_score[i] = chunk[i]; }
       ncand = n;
     } else {
       float sm0 = 0.f, sm1 = 0.f;
@@ -324,7 +336,14 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       float nbf = ceilf(2.0f * delta * kBinsPerUnit) + 1.0f;
       if (!(nbf < 4096.0f)) nbf = 4096.0f;
       const int nb = (MODE == JF_MODE_K3V2) ? static_cast<int>(nbf) : 0;  // K4: scan scores are canonical
-      const int n_chunks = (n + kScoreChunk - 1) / kScoreChunk;
+      const int n_chunks = (n + kChunkPos - 1) / kChunkPos;
+      const float4* chunk4 = reinterpret_cast<const float4*>(chunk);
+      // element (j, c) of thread tid is chunk position 4 * (j * 1024 + tid) + c
+      auto next_chunk = [&](int ci) {  // block-wide: replace the resident chunk by chunk ci
+        __syncthreads();
+        issue_chunk(ci);
+        if (!wait_chunk(ci, n)) { copied = false; }
+      };
 
       // Block-wide: turns hist[] into inclusive prefix counts (from the top bin down) and
       // leaves in sm.tbin the bin where the count reaches K (-1: never).
@@ -358,55 +377,84 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       };
       // Block-wide: positions whose bin is <= last go to keys[] (one shared-memory atomic per
       // warp and chunk); returns how many there are (may exceed sort_n: then keys[] is partial).
+      float hm[kChunkVec];  // per float4 of the resident chunk: its largest score (tier 1a's pass)
+      bool have_hm = false;
       auto collect = [&](int last) {
-        const float xlim = static_cast<float>(last + 1);  // bin <= last  <=>  (top - s) * 64 < last + 1
+        // bin <= last  <=>  fma(s, -64, top64) < last + 1; one comparison per score against a
+        // threshold a little below the exact boundary (a few extra candidates are harmless)
+        const float xlim = static_cast<float>(last + 1);
+        int running = 0;  // candidates found in earlier chunks
+        const float thr = (top64 - xlim) * (1.0f / kBinsPerUnit) - (fabsf(top64) + xlim) * (1.0f / (kBinsPerUnit * 2097152.0f)) - 1e-30f;
         for (int ci = 0; ci < n_chunks; ++ci) {
-          if (n_chunks > 1) load_chunk(ci);
-          int cnt = 0;
+          if (n_chunks > 1) next_chunk(ci);
+          uint32_t mask = 0u;
 #pragma unroll
-          for (int e = 0; e < kScoreRegs; ++e) cnt += (pos_of(ci, e) < n && score_binf(top64, sc[e]) < xlim) ? 1 : 0;
+          for (int j = 0; j < kChunkVec; ++j) {
+            if (have_hm && !(hm[j] > thr)) continue;  // nothing of this float4 can qualify
+            const float4 v = chunk4[j * kSelThreads + tid];
+            if (v.x > thr) mask |= 1u << (4 * j);
+            if (v.y > thr) mask |= 1u << (4 * j + 1);
+            if (v.z > thr) mask |= 1u << (4 * j + 2);
+            if (v.w > thr) mask |= 1u << (4 * j + 3);
+          }
+          JF_PHASE(30);
+          const int cnt = __popc(mask);
           int incl = cnt;
 #pragma unroll
           for (int o = 1; o < 32; o <<= 1) {
             const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
             if (lane >= o) incl += t;
           }
-          int base = 0;
-          if (lane == 31 && incl > 0) base = atomicAdd(&sm.ncand, incl);
-          base = __shfl_sync(0xFFFFFFFFu, base, 31);
-          if (cnt > 0) {
-            int o = base + incl - cnt;
+          // warp totals -> every warp's offset (no atomics: 32 same-address atomics with a
+          // return value cost more than the whole pass)
+          __syncthreads();   // the previous round's reads of wsum are done
+          if (lane == 31) sm.wsum[warp] = incl;
+          __syncthreads();
+          int wt = sm.wsum[lane], winc = wt;
 #pragma unroll
-            for (int e = 0; e < kScoreRegs; ++e) {
-              const int pp = pos_of(ci, e);
-              if (pp < n && score_binf(top64, sc[e]) < xlim) {
-                if (o < p.sort_n) keys[o] = static_cast<uint64_t>(pp);
-                ++o;
-              }
-            }
+          for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, winc, o);
+            if (lane >= o) winc += t;
+          }
+          const int base = running + __shfl_sync(0xFFFFFFFFu, winc - wt, warp);
+          running += __shfl_sync(0xFFFFFFFFu, winc, 31);
+          int o = base + incl - cnt;
+          JF_PHASE(31);
+          while (mask) {
+            const int e = __ffs(mask) - 1;
+            mask &= mask - 1u;
+            const int at = 4 * ((e >> 2) * kSelThreads + tid) + (e & 3);
+            if (o < p.sort_n) { keys[o] = static_cast<uint64_t>(ci * kChunkPos + at); cand_score[o] = chunk[at]; }
+            ++o;
           }
         }
+        JF_PHASE(32);
         __syncthreads();
-        return sm.ncand;
+        JF_PHASE(33);
+        return running;
       };
 
       // ---- tier 1a: a bound from group maxima.  Each thread holds four groups of positions
       //      per chunk (stride 4096 inside a group); the K-th largest group maximum is a lower
       //      bound of the K-th largest score, and far fewer values enter the histogram. ----
       for (int ci = 0; ci < n_chunks; ++ci) {
-        if (ci > 0) load_chunk(ci);
+        if (ci > 0) next_chunk(ci);
         float gm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < kScoreRegs; ++e)
-          if (pos_of(ci, e) < n) gm[e & 3] = fmaxf(gm[e & 3], sc[e]);
+        for (int j = 0; j < kChunkVec; ++j) {
+          const float4 v = chunk4[j * kSelThreads + tid];
+          gm[0] = fmaxf(gm[0], v.x); gm[1] = fmaxf(gm[1], v.y); gm[2] = fmaxf(gm[2], v.z); gm[3] = fmaxf(gm[3], v.w);
+          hm[j] = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           if (gm[c] > -INFINITY) atomicAdd(&hist[score_bin(top64, gm[c])], 1);
       }
+      have_hm = n_chunks == 1;  // hm[] describes the chunk that stays resident
       __syncthreads();
-      JF_PHASE(2);
-      scan_hist();
       JF_PHASE(3);
+      scan_hist();
+      JF_PHASE(4);
       bool ok = false;
       {
         const int tbin = sm.tbin;
@@ -415,6 +463,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           const int total = collect(last);
           ok = total <= p.sort_n;
           ncand = total;
+          JF_PHASE_VAL(40, total);
+          cand_last = last + nb;
         }
       }
       if (!ok) {
@@ -424,10 +474,15 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
         __syncthreads();
         for (int ci = 0; ci < n_chunks; ++ci) {
-          if (n_chunks > 1) load_chunk(ci);
+          if (n_chunks > 1) next_chunk(ci);
 #pragma unroll
-          for (int e = 0; e < kScoreRegs; ++e)
-            if (pos_of(ci, e) < n) atomicAdd(&hist[score_bin(top64, sc[e])], 1);
+          for (int j = 0; j < kChunkVec; ++j) {
+            const float4 v = chunk4[j * kSelThreads + tid];
+            if (v.x > -INFINITY) atomicAdd(&hist[score_bin(top64, v.x)], 1);
+            if (v.y > -INFINITY) atomicAdd(&hist[score_bin(top64, v.y)], 1);
+            if (v.z > -INFINITY) atomicAdd(&hist[score_bin(top64, v.z)], 1);
+            if (v.w > -INFINITY) atomicAdd(&hist[score_bin(top64, v.w)], 1);
+          }
         }
         __syncthreads();
         scan_hist();
@@ -439,71 +494,91 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
           __syncthreads();
           ncand = collect(last);
+          cand_last = last + nb;
         }
       }
+      if (!copied) {  // a later chunk did not arrive: select nothing
+        if (tid == 0) report_status(p.status, JF_ERR_TIMEOUT);
+        ncand = 0;
+        slow = false;
+      }
     }
-    __syncthreads();
-    JF_PHASE(4);
+    __syncthreads();   // every read of the score chunk is done: its memory is reused from here on
+    JF_PHASE(5);
 
+    // the fused finish stage takes slots, scores and V rows of the candidates from shared memory
+    prefetch = FUSED && !slow && ncand <= kRowChunk && p.sort_n <= kSelThreads;
     if (!slow) {
       // ---- re-score the candidates canonically: slots, then their packed rows into shared
       //      memory with independent 16-byte loads, then the canonical arithmetic ----
       for (int base = 0; base < ncand; base += kRowChunk) {
         const int cn = min(kRowChunk, ncand - base);
-        if (tid < cn) sm.cand_slot[tid] = slot_of(ctx, static_cast<int>(keys[base + tid]));
+        if (tid < cn) late.cand_slot[tid] = slot_of(ctx, static_cast<int>(keys[base + tid]));
         __syncthreads();
-        JF_PHASE(5);
+        JF_PHASE(6);
         {
-          // unit u = (candidate, quarter): K4 rows are 4 x 16 bytes (+ the scale with quarter 0),
-          // K3 rows 3 x 16 bytes and quarter 3 fetches the two scales
-          uint4 v[2];
-          uint32_t sc16[2];
+          // unit u = (candidate, part), eight per candidate, each at most one 16-byte access.
+          // K3: parts 0-2 the K row, 3 the K scales, 4-5 the V row, 6 the V scales.  K4: parts
+          // 4-7 the V row (part 4 also its scale); its K rows are not needed.
+          // The K side is needed at once and comes through registers; the V side (only when the
+          // finish stage will use it) is copied asynchronously and awaited before that stage.
+          constexpr int kUnroll = 8 * kRowChunk / kSelThreads;
+          constexpr int kKParts = (MODE == JF_MODE_K3V2) ? 3 : 4, kVParts = (MODE == JF_MODE_K3V2) ? 2 : 4;
+          constexpr int VW = TailSmem<MODE>::VW;
+          const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
+          const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+          uint4 v[kUnroll];
+          uint32_t sc16[kUnroll];
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < kUnroll; ++i) {
             const int u = tid + i * kSelThreads;
-            const int c = u >> 2, part = u & 3;
+            const int c = u >> 3, part = u & 7;
             v[i] = make_uint4(0u, 0u, 0u, 0u);
             sc16[i] = 0u;
-            if (c < cn) {
-              const int64_t slot = sm.cand_slot[c];
-              if (slot >= 0) {
-                if (MODE == JF_MODE_K3V2) {
-                  if (part < 3) v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * 48) + part);
-                  else sc16[i] = __ldg(reinterpret_cast<const uint32_t*>(ctx.k_sc + slot * 2));
-                } else {
-                  v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * 64) + part);
-                  if (part == 0) sc16[i] = static_cast<uint32_t>(__ldg(ctx.k_sc + slot));
+            if (c < cn && (part < 4 ? MODE == JF_MODE_K3V2 : prefetch)) {
+              const int64_t slot = late.cand_slot[c];
+              if (part < 4) {
+                if (slot >= 0) {
+                  if (part < kKParts) v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * (16 * kKParts)) + part);
+                  if (MODE == JF_MODE_K3V2) { if (part == 3) sc16[i] = __ldg(reinterpret_cast<const uint32_t*>(ctx.k_sc + slot * 2)); }
+                  else { if (part == 0) sc16[i] = static_cast<uint32_t>(__ldg(ctx.k_sc + slot)); }
                 }
+              } else if (part < 4 + kVParts) {
+                uint4* dst = reinterpret_cast<uint4*>(late.vrows + c * VW) + (part - 4);
+                if (slot >= 0) cp_async_16(dst, reinterpret_cast<const uint4*>(v_rows + slot * (16 * kVParts)) + (part - 4));
+                else *dst = make_uint4(0u, 0u, 0u, 0u);
+                if (MODE == JF_MODE_K4V4 && part == 4) {
+                  // the 2-byte scale travels as the aligned 4-byte pair that holds it
+                  if (slot >= 0) cp_async_4(&late.vsc[c], v_sc + (slot & ~static_cast<int64_t>(1)));
+                  else late.vsc[c] = 0u;
+                }
+              } else if (MODE == JF_MODE_K3V2 && part == 6) {
+                if (slot >= 0) cp_async_4(&late.vsc[c], v_sc + slot * 2);
+                else late.vsc[c] = 0u;
               }
             }
           }
+          cp_async_commit();
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < kUnroll; ++i) {
             const int u = tid + i * kSelThreads;
-            const int c = u >> 2, part = u & 3;
-            if (c < cn) {
-              uint32_t* r = sm.rows + c * W;
-              if (MODE == JF_MODE_K3V2) {
-                if (part < 3) { r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w; }
-                else r[12] = sc16[i];
-              } else {
-                r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w;
-                if (part == 0) r[16] = sc16[i];
-              }
+            const int c = u >> 3, part = u & 7;
+            if (MODE == JF_MODE_K3V2 && c < cn && part < 4) {
+              uint32_t* r = late.rows + c * W;
+              if (part < kKParts) { r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w; }
+              if (MODE == JF_MODE_K3V2) { if (part == 3) r[12] = sc16[i]; }
+              else { if (part == 0) r[16] = sc16[i]; }
             }
           }
         }
         __syncthreads();
-        JF_PHASE(6);
+        JF_PHASE(7);
         if (MODE == JF_MODE_K4V4) {
-          // one thread per candidate (integer arithmetic: order-free)
+          // K4: the scan's score is the canonical one bit for bit (exact integer dot products,
+          // the same fp32 rescale order), so nothing is recomputed
           if (tid < cn) {
             const int pos = static_cast<int>(keys[base + tid]);
-            const uint32_t* r = sm.rows + tid * W;
-            float s = -INFINITY;
-            if (sm.cand_slot[tid] >= 0)
-              s = canon_score_k4_thread(sm.qe, sm.qo, sm.qsum8, sm.qs, r, bf16_bits_to_f32(r[16] & 0xFFFFu), ctx.attn);
-            keys[base + tid] = make_key(s, pos);
+            keys[base + tid] = make_key(late.cand_slot[tid] >= 0 ? cand_score[base + tid] : -INFINITY, pos);
           }
         } else {
           // one warp per candidate, four candidates in flight per warp
@@ -513,8 +588,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             for (int i = 0; i < 4; ++i) {
               const int c = c0 + i * kSelWarps;
               s[i] = -INFINITY;
-              if (c < cn && sm.cand_slot[c] >= 0) {
-                const uint32_t* r = sm.rows + c * W;
+              if (c < cn && late.cand_slot[c] >= 0) {
+                const uint32_t* r = late.rows + c * W;
                 s[i] = canon_score_k3(sm.q, reinterpret_cast<const uint8_t*>(r), r[12], ctx.attn, lane);
               }
             }
@@ -567,30 +642,69 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       ncand = min(sm.ncand, p.sort_n);
     }
     __syncthreads();
+    JF_PHASE(8);
 
-    JF_PHASE(7);
     // ---- order the candidates: best first ----
     if (p.sort_n <= kSelThreads) {
-      // rank by counting (keys are unique): the ncand^2 comparisons are spread evenly, thread
-      // (c, part) counts the keys above candidate c among j = part, part + P, ...
-      int* rank = hist;
-      for (int i = tid; i < ncand; i += kSelThreads) rank[i] = 0;
+      // Rank by buckets: a candidate's rank is the number of candidates in finer score bins
+      // above its own plus the number of larger keys inside its bin.  Bins are `f` times finer
+      // than the selection histogram's (the candidates span few of those); a larger canonical
+      // score never lands in a later bin, so the result is the exact order of the keys, and
+      // crowded bins (massive ties) only cost time.
+      int f = 1;
+      while (f < 16 && (cand_last + 2) * f * 2 <= kBins) f *= 2;
+      const float fscale = kBinsPerUnit * static_cast<float>(f);
+      const float ftop = (row_max + 4.0f) * fscale;
+      for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
       __syncthreads();
-      const int P = kSelThreads / max(ncand, 1);
-      const int part = tid / max(ncand, 1), c = tid - part * max(ncand, 1);
-      if (part < P && ncand > 0) {
-        const uint64_t mine = keys[c];
-        int above = 0;
-#pragma unroll 4
-        for (int j = part; j < ncand; j += P) above += (keys[j] > mine) ? 1 : 0;
-        atomicAdd(&rank[c], above);
+      unsigned long long mine = 0ull;
+      int fb = 0, arrival = 0;
+      if (tid < ncand) {
+        mine = keys[tid];
+        const float sc = float_from_order_key(static_cast<uint32_t>(mine >> 32));
+        const float x = fminf(fmaxf(fmaf(sc, -fscale, ftop), 0.0f), static_cast<float>(kBins - 1));
+        fb = __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
+        arrival = atomicAdd(&hist[fb], 1);
       }
       __syncthreads();
-      uint64_t mine = 0ull;
-      int r = 0;
-      if (tid < ncand) { mine = keys[tid]; r = rank[tid]; }
+      {
+        // exclusive prefix over the bins, two per thread, written back in place
+        const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
+        const int v = h0 + h1;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        if (lane == 31) sm.wsum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+          int t = sm.wsum[lane], inc2 = t;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xFFFFFFFFu, inc2, o);
+            if (lane >= o) inc2 += u;
+          }
+          sm.wsum[lane] = inc2 - t;
+        }
+        __syncthreads();
+        const int ex = sm.wsum[warp] + incl - v;
+        hist[2 * tid] = ex;
+        hist[2 * tid + 1] = ex + h0;
+      }
       __syncthreads();
-      if (tid < ncand) keys[r] = mine;
+      if (tid < ncand) bucket[hist[fb] + arrival] = static_cast<uint16_t>(tid);
+      __syncthreads();
+      int r = 0;
+      if (tid < ncand) {
+        const int lo = hist[fb], hi2 = (fb == kBins - 1) ? ncand : hist[fb + 1];
+        int above = 0;
+        for (int m = lo; m < hi2; ++m) above += (keys[bucket[m]] > mine) ? 1 : 0;
+        r = min(lo + above, ncand - 1);
+      }
+      __syncthreads();
+      if (tid < ncand) { keys[r] = mine; perm[r] = static_cast<uint16_t>(tid); }
       __syncthreads();
     } else {
       // bitonic sort, descending, sort_n a power of two
@@ -610,28 +724,29 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       }
     }
     m_sel = min(ncand, K);
-    JF_PHASE(8);
+    JF_PHASE(9);
   }
 
   for (int r = tid; r < K; r += kSelThreads) {
     int64_t idx = -1, slot = -1;
-    float canon = -INFINITY;
     if (r < m_sel) {
       idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
-      slot = slot_of(ctx, static_cast<int>(idx));
-      canon = float_from_order_key(static_cast<uint32_t>(keys[r] >> 32));
+      slot = prefetch ? late.cand_slot[perm[r]] : slot_of(ctx, static_cast<int>(idx));
     }
     out_idx[r] = idx;
     out_slot[r] = slot;
-    out_canon[r] = canon;
   }
-  JF_PHASE(9);
+  JF_PHASE(10);
 
   if (FUSED) {
-    finish_tail<MODE>(tp, tsm, pre, row_max, n, b, h, ctx.bt, [&](int kk, int& pos, float& canon) {
+    cp_async_wait_all();
+    __syncthreads();
+    TailPrefetch pf{};
+    if (prefetch) { pf.slot = late.cand_slot; pf.score = cand_score; pf.vsc = late.vsc; pf.vrows = late.vrows; }
+    finish_tail<MODE>(tp, late.tail, pf, pre, row_max, n_seq, b, h, ctx.bt, [&](int kk, int& pos, int& cidx) {
       if (kk >= m_sel) return false;
       pos = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(keys[kk] & 0xFFFFFFFFull));
-      canon = float_from_order_key(static_cast<uint32_t>(keys[kk] >> 32));
+      cidx = prefetch ? static_cast<int>(perm[kk]) : -1;
       return true;
     });
   }
@@ -641,8 +756,8 @@ int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 template <int MODE, int DT>
 jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
-  const size_t smem = sizeof(TailSmem<MODE>) + sizeof(SelSmemFixed) + static_cast<size_t>(sp.sort_n) * 8;
-  constexpr size_t kMaxSmem = sizeof(TailSmem<MODE>) + sizeof(SelSmemFixed) + static_cast<size_t>(2 * JF_MAX_TOP_K) * 8;
+  const size_t smem = sel_smem_bytes(sp.sort_n);
+  constexpr size_t kMaxSmem = sel_smem_bytes(2 * JF_MAX_TOP_K);
   static_assert(kMaxSmem <= 227 * 1024, "select kernel shared memory");
   if (fused) {
     JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true>), kMaxSmem);
@@ -684,7 +799,7 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   sp.part_m = ws.part_m; sp.part_smax = ws.part_smax;
   sp.q = a->q; sp.k_data = a->k_data; sp.k_scales = static_cast<const uint16_t*>(a->k_scales);
   sp.block_table = a->block_table; sp.seq_lens = a->seq_lens;
-  sp.topk_idx = a->topk_idx; sp.topk_slots = a->topk_slots; sp.sel_canon = ws.sel_canon;
+  sp.topk_idx = a->topk_idx; sp.topk_slots = a->topk_slots; sp.status = ws.status;
   sp.num_slots = a->num_slots;
   sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = a->H_kv; sp.G = a->H_q / a->H_kv;
   sp.max_S = a->max_S; sp.max_blocks = a->max_blocks;
