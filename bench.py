@@ -196,6 +196,9 @@ def build_stack(torch, ops, w, rank, device, dtype, with_mirror):
         L.out = torch.empty(w["batch"], w["H_q"], 128, dtype=dtype, device=device)
         L.out_host = torch.empty(w["batch"], w["H_q"], 128, dtype=dtype).pin_memory()
         L.event = torch.cuda.Event()
+        if with_mirror:
+            L.host_call = ops.HostCorrectionCall(L.q_host, L.k_shadow, L.v_shadow, None, L.slots_host, L.o_new_host,
+                                                 128 ** -0.5)
         layers.append(L)
     torch.cuda.synchronize()
     return layers
@@ -445,14 +448,23 @@ def main():
                 L.call.fused()
                 L.slots_host.copy_(L.call.out["topk_slots"], non_blocking=True)
                 L.event.record(main_s)
-            for L in layers:
-                L.event.synchronize()
-                ops.cpu_topk_attn(L.q_host, L.k_shadow, L.v_shadow, None, L.slots_host, L.o_new_host, 128 ** -0.5)
+
+            def merge(L):  # o_new host -> device, merge, result device -> host; on the copy stream
                 with torch.cuda.stream(copy_stream):
                     L.o_new.copy_(L.o_new_host, non_blocking=True)
                     ops.blend_unnorm_into(L.call.out["o_hat"], L.call.out["o_old_unnorm"], L.call.out["W"],
                                           L.o_new, L.out)
                     L.out_host.copy_(L.out, non_blocking=True)
+
+            prev = None
+            for L in layers:
+                L.event.synchronize()
+                L.host_call.submit()          # the worker pool takes the layer's correction ...
+                if prev is not None:
+                    merge(prev)               # ... while this thread launches the previous layer's merge
+                L.host_call.wait()
+                prev = L
+            merge(prev)
             copy_stream.synchronize()
             if world > 1:
                 for i, L in enumerate(layers):

@@ -2,8 +2,8 @@
 // KV mirror kept in host DRAM.
 //
 // Keeps the reference's design (jetfire_vllm/csrc/cpu_topk_attn.cpp:316-479, 602-690,
-// 854-956; pool: csrc/jetfire_pool.h:69-334): persistent workers, (b, h_q) rows split
-// evenly over them, per row: gather K/V rows by slot, s = (q . K) * scale in fp32,
+// 854-956; pool: csrc/jetfire_pool.h:69-334): persistent workers over the (b, h_q) rows
+// (claimed one by one from a shared counter rather than split evenly), per row: gather K/V rows by slot, s = (q . K) * scale in fp32,
 // softmax with exp, o_new = sum p * V in fp32, rounded to the mirror's 16-bit type;
 // invalid slots score -inf, an all-invalid row or a non-positive / non-finite
 // normaliser gives zeros; a store fence precedes the completion flag so that results
@@ -293,15 +293,17 @@ bool have_avx512bf16() {
   return v;
 }
 
-void run_rows(const Job& j, int wid, int n_workers, Scratch& sc) {
+// Rows are claimed one at a time from a shared counter, so a worker that loses its core
+// for a while does not hold up the rest of the job.
+void run_rows(const Job& j, std::atomic<int64_t>& next_row, Scratch& sc) {
   const int64_t total = static_cast<int64_t>(j.B) * j.H_q;
-  const int64_t start = total * wid / n_workers, end = total * (wid + 1) / n_workers;
-  if (start >= end) return;
   sc.scores.resize(static_cast<size_t>(j.K) + 16);
   sc.slots.resize(j.K);
   const bool simd = have_avx512bf16();
   if (!simd) sc.vrows.resize(static_cast<size_t>(j.K) * D);
-  for (int64_t i = start; i < end; ++i) {
+  for (;;) {
+    const int64_t i = next_row.fetch_add(1, std::memory_order_relaxed);
+    if (i >= total) break;
     const int64_t b = i / j.H_q, h = i % j.H_q;
     if (!simd) row_generic(j, sc, b, h);
     else if (j.dtype == JF_DTYPE_BF16) row_avx512<JF_DTYPE_BF16>(j, sc, b, h);
@@ -344,6 +346,7 @@ class Pool {
     {
       std::lock_guard<std::mutex> l(m_);
       job_ = j;
+      next_row_.store(0, std::memory_order_relaxed);
       pending_.store(n_, std::memory_order_release);
       gen_.fetch_add(1, std::memory_order_release);
     }
@@ -362,7 +365,7 @@ class Pool {
   }
 
  private:
-  void loop(int wid) {
+  void loop(int /*wid*/) {
     Scratch sc;
     uint64_t seen = 0;
     for (;;) {
@@ -383,7 +386,7 @@ class Pool {
         if (stop_) return;
         j = job_;
       }
-      run_rows(j, wid, n_, sc);
+      run_rows(j, next_row_, sc);
       _mm_sfence();  // results may sit in write-combined mapped memory
       if (pending_.fetch_sub(1, std::memory_order_acq_rel) == 1) {
         if (j.done_flag) {
@@ -402,6 +405,7 @@ class Pool {
   Job job_{};
   std::atomic<uint64_t> gen_{0};
   std::atomic<int> pending_{0};
+  alignas(64) std::atomic<int64_t> next_row_{0};
   bool stop_ = false;
   int n_ = 0;
 };

@@ -338,6 +338,28 @@ def cpu_topk_attn_wait(timeout_ms: int = 30000) -> None:
     check("cpu_topk_attn_wait", lib.jf_pool_wait_timeout(int(timeout_ms)))
 
 
+class HostCorrectionCall:
+    """A host correction over fixed buffers (the per-layer state of the reference's decode
+    path, ``adapter/decode_path.py:2448-2492``): the tensors are validated and their addresses
+    taken once, ``submit()`` / ``wait()`` / ``run()`` then cost one C call each.  The caller keeps
+    the buffers' contents current; the tensors themselves are kept alive here."""
+
+    def __init__(self, q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None):
+        self._args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag,
+                                "HostCorrectionCall")
+        self._keep = (q, k_shadow, v_shadow, head_map, ts_buf, o_new, done_flag)
+
+    def submit(self) -> None:
+        check("cpu_topk_attn_submit", lib.jf_pool_submit(*self._args))
+
+    @staticmethod
+    def wait(timeout_ms: int = 30000) -> None:
+        check("cpu_topk_attn_wait", lib.jf_pool_wait_timeout(int(timeout_ms)))
+
+    def run(self) -> None:
+        check("cpu_topk_attn", lib.jf_cpu_topk_attn(*self._args))
+
+
 def alloc_mapped_pinned_pair(shape, dtype):
     """``(host_tensor, device_tensor)`` over the same pinned, GPU-mapped bytes."""
     n = 1

@@ -85,3 +85,18 @@ def test_pool_submit_wait_and_single_flight():
     assert _lib.lib.jf_pool_wait_timeout(0) == 0
     with pytest.raises(RuntimeError):
         ops.cpu_topk_attn(case.q.float(), case.k_full, case.v_full, None, slots, out, case.attn_scale)
+
+
+def test_prebuilt_host_call_equals_plain_call():
+    from jetfire_b200 import ops
+    case, slots = _correction_inputs()
+    ops.set_cpu_attn_threads(3)
+    want = torch.empty(2, 8, 128, dtype=torch.bfloat16)
+    ops.cpu_topk_attn(case.q, case.k_full, case.v_full, None, slots, want, case.attn_scale)
+    out = torch.zeros_like(want)
+    call = ops.HostCorrectionCall(case.q, case.k_full, case.v_full, None, slots, out, case.attn_scale)
+    call.submit(); call.wait()
+    assert torch.equal(out, want)
+    out.zero_()
+    call.run()
+    assert torch.equal(out, want)
