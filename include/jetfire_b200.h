@@ -61,7 +61,7 @@ int32_t     jf_last_cuda_error(void);
  * IEEE divide, round-half-even, scale rounded to bf16 before the divide.
  *
  * x_tok      (T, H_kv, 128) bf16/fp16 device, element strides stride_t / stride_h,
- *            innermost contiguous, rows 8-byte aligned
+ *            innermost contiguous, rows 16-byte aligned (strides multiples of 8 elements)
  * slots      (T,) int64 device; row t goes to out[h, slots[t]]; negative = skip
  * out_data   (H_kv, num_slots, 128*nbits/8) uint8 device
  * out_scales (H_kv, num_slots, 128/group_size) bf16 device

@@ -8,14 +8,17 @@
 // groups split over three byte planes).  Negative slots are skipped
 // (jetfire_vllm/kernels/fused_quant_write.py:150-152).
 //
-// One warp owns a (token, kv-head) row: lane l holds elements 4l..4l+3 (one 8-byte
-// load); four rows per warp are loaded before any is processed so that enough bytes
-// are in flight per SM.  HBM-bound: 256 B read + 36..66 B written per row.
+// Half a warp owns a (token, kv-head) row: lane l (0..15) holds elements 8l..8l+7 (one
+// 16-byte load), which are one INT3 group, one INT4 word or one INT2 half-word of the packed
+// row, so packing needs no shuffles; the group maximum takes 3 or 4.  Each warp loads eight
+// rows (2 KB) before it processes any, so that enough bytes are in flight per SM, and the
+// slot lookup runs beside the row loads, not before them.  HBM-bound: 256 B read +
+// 36..66 B written per row.
 #include "jf_common.cuh"
 
 namespace jf {
 
-constexpr int kRowsPerWarp = 4;
+constexpr int kPairsPerWarp = 2;   // row pairs (one per half-warp) per warp
 constexpr int kWarpsPerCta = 8;
 
 struct PackSide {
@@ -27,114 +30,132 @@ struct PackSide {
 };
 
 template <int DT, int NBITS, int GS>
-__device__ __forceinline__ void pack_row(uint2 raw, uint8_t* __restrict__ out_row,
-                                         uint16_t* __restrict__ scale_row, int lane) {
+__device__ __forceinline__ void pack_row(uint4 raw, uint8_t* __restrict__ out_row,
+                                         uint16_t* __restrict__ scale_row, int sub, bool live) {
   constexpr int QMAX = (1 << (NBITS - 1)) - 1;
   constexpr int OFF = 1 << (NBITS - 1);
-  float f[4];
-  f[0] = Elem<DT>::to_f32(raw.x & 0xFFFF);
-  f[1] = Elem<DT>::to_f32(raw.x >> 16);
-  f[2] = Elem<DT>::to_f32(raw.y & 0xFFFF);
-  f[3] = Elem<DT>::to_f32(raw.y >> 16);
-  float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  float f[8];
 #pragma unroll
-  for (int o = 1; o < GS / 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = Elem<DT>::to_f32(w[i] & 0xFFFF);
+    f[2 * i + 1] = Elem<DT>::to_f32(w[i] >> 16);
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+  for (int o = 1; o < GS / 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
   const float scale = fmaxf(__fdiv_rn(amax, static_cast<float>(QMAX)), 1e-8f);
   const uint16_t sb = __bfloat16_as_ushort(__float2bfloat16_rn(scale));
   const float sf = bf16_bits_to_f32(sb);
-  uint32_t c[4];
+  // q = rint(fl(x / sf)) without an IEEE division per element: t = x * rcp(sf) is within
+  // 2^-19 of the exact quotient (|quotient| < 8, both steps within 2^-23 relative), and so is
+  // the correctly rounded quotient; unless t sits within 2^-17 of a rounding boundary k + 1/2
+  // all three round to the same integer.  Only those rare elements take the true division.
+  float rs;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rs) : "f"(sf));
+  // Rounding and float -> int without conversion instructions: t + 1.5 * 2^23 is rounded
+  // (half-even) to an integer that sits in the low mantissa bits.  The clamp to +-QMAX comes
+  // first (it commutes with rounding); an element whose t is not within 1/2 - 2^-17 of the
+  // rounded value -- near a boundary, or NaN / far out of range -- takes the true division.
+  constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+  uint32_t c[8];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float q = rintf(__fdiv_rn(f[i], sf));
-    q = fminf(fmaxf(q, -static_cast<float>(QMAX)), static_cast<float>(QMAX));
-    c[i] = static_cast<uint32_t>(static_cast<int>(q) + OFF);
-  }
-  // scales: one per group, written by the group's first lane
-  if (GS == 64) {
-    const uint32_t hi = __shfl_sync(0xFFFFFFFFu, static_cast<uint32_t>(sb), 16);
-    if (lane == 0) *reinterpret_cast<uint32_t*>(scale_row) = static_cast<uint32_t>(sb) | (hi << 16);
-  } else {
-    if (lane == 0) scale_row[0] = sb;
-  }
-  if (NBITS == 4) {
-    const uint32_t two = ((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8);
-    const uint32_t nxt = __shfl_down_sync(0xFFFFFFFFu, two, 1);
-    if ((lane & 1) == 0) reinterpret_cast<uint32_t*>(out_row)[lane >> 1] = two | (nxt << 16);
-  } else if (NBITS == 2) {
-    const uint32_t b = (c[0] << 6) | (c[1] << 4) | (c[2] << 2) | c[3];
-    const uint32_t b1 = __shfl_down_sync(0xFFFFFFFFu, b, 1);
-    const uint32_t b2 = __shfl_down_sync(0xFFFFFFFFu, b, 2);
-    const uint32_t b3 = __shfl_down_sync(0xFFFFFFFFu, b, 3);
-    if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(out_row)[lane >> 2] = b | (b1 << 8) | (b2 << 16) | (b3 << 24);
-  } else {  // NBITS == 3: eight codes -> 24 bits MSB-first, byte p of group i at out_row[16 p + i]
-    const uint32_t c12 = (c[0] << 9) | (c[1] << 6) | (c[2] << 3) | c[3];
-    const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, c12, 1);
-    const uint32_t w24 = (c12 << 12) | other;  // valid on even lanes (group lane/2)
-    const uint32_t wb = __shfl_down_sync(0xFFFFFFFFu, w24, 2);
-    const uint32_t wc = __shfl_down_sync(0xFFFFFFFFu, w24, 4);
-    const uint32_t wd = __shfl_down_sync(0xFFFFFFFFu, w24, 6);
-    if ((lane & 7) == 0) {
-      const int j = lane >> 3;  // word index inside a plane: groups 4j..4j+3
-      uint32_t* o32 = reinterpret_cast<uint32_t*>(out_row);
-#pragma unroll
-      for (int p = 0; p < 3; ++p) {
-        const int sh = 16 - 8 * p;
-        o32[4 * p + j] = ((w24 >> sh) & 255u) | (((wb >> sh) & 255u) << 8) | (((wc >> sh) & 255u) << 16) |
-                         (((wd >> sh) & 255u) << 24);
-      }
+  for (int i = 0; i < 8; ++i) {
+    const float t = f[i] * rs;
+    float tm = fminf(fmaxf(t, -static_cast<float>(QMAX)), static_cast<float>(QMAX)) + kMagic;
+    if (fabsf(t - (tm - kMagic)) > 0.5f - 0.00000762939453125f) {
+      const float q = rintf(__fdiv_rn(f[i], sf));
+      tm = fminf(fmaxf(q, -static_cast<float>(QMAX)), static_cast<float>(QMAX)) + kMagic;
     }
+    c[i] = static_cast<uint32_t>(__float_as_int(tm) - 0x4B400000 + OFF);
+  }
+  if (!live) return;  // after the shuffles: the other half of the warp may still need them
+  // scales: one per group, written by the group's first lane
+  if (GS == 64) { if ((sub & 7) == 0) scale_row[sub >> 3] = sb; }
+  else { if (sub == 0) scale_row[0] = sb; }
+  if (NBITS == 4) {        // byte B = (code 2B << 4) | code 2B+1
+    reinterpret_cast<uint32_t*>(out_row)[sub] = ((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8) |
+                                                (((c[4] << 4) | c[5]) << 16) | (((c[6] << 4) | c[7]) << 24);
+  } else if (NBITS == 2) { // byte B = four codes, first in the top bits
+    reinterpret_cast<uint16_t*>(out_row)[sub] = static_cast<uint16_t>(
+        ((c[0] << 6) | (c[1] << 4) | (c[2] << 2) | c[3]) | (((c[4] << 6) | (c[5] << 4) | (c[6] << 2) | c[7]) << 8));
+  } else {                 // eight codes -> 24 bits MSB-first, byte p of group i at out_row[16 p + i]
+    const uint32_t w24 = (c[0] << 21) | (c[1] << 18) | (c[2] << 15) | (c[3] << 12) | (c[4] << 9) | (c[5] << 6) |
+                         (c[6] << 3) | c[7];
+    out_row[sub] = static_cast<uint8_t>(w24 >> 16);
+    out_row[16 + sub] = static_cast<uint8_t>(w24 >> 8);
+    out_row[32 + sub] = static_cast<uint8_t>(w24);
   }
 }
 
+// One batch of rows per warp; residency (not a loop) overlaps the loads of some warps with
+// the arithmetic of others -- a persistent loop with a register double buffer measured slower.
 template <int DT, int GS>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 pack_append_kernel(PackSide s0, PackSide s1, int64_t T, int H, const int64_t* __restrict__ slots,
                    int64_t num_slots) {
   const PackSide s = (blockIdx.y == 0) ? s0 : s1;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, half = lane >> 4, sub = lane & 15;
   const int64_t rows = T * H;
-  const int64_t r0 = warp * kRowsPerWarp;
-  if (r0 >= rows) return;
+  const int64_t n_batches = (rows + 2 * kPairsPerWarp - 1) / (2 * kPairsPerWarp);
   constexpr int NG = 128 / GS;
   const int dp = 16 * s.nbits;
+  const bool small = rows <= 0x7FFFFFFF;   // 32-bit index arithmetic (a 64-bit division costs more than a row)
 
-  uint2 raw[kRowsPerWarp];
-  int64_t slot[kRowsPerWarp];
-  int hh[kRowsPerWarp];
+  struct Batch {
+    uint4 raw[kPairsPerWarp];
+    int64_t slot[kPairsPerWarp];
+    int hh[kPairsPerWarp];
+  };
+  auto load = [&](int64_t batch, Batch& bt) {
+    const int64_t r0 = batch * (2 * kPairsPerWarp) + half;   // this half-warp's rows: r0, r0 + 2, ...
 #pragma unroll
-  for (int i = 0; i < kRowsPerWarp; ++i) {
-    const int64_t r = r0 + i;
-    slot[i] = -1;
-    hh[i] = 0;
-    raw[i] = make_uint2(0u, 0u);
-    if (r < rows) {
-      const int64_t t = r / H;
-      hh[i] = static_cast<int>(r - t * H);
-      slot[i] = slots[t];
-      if (slot[i] >= num_slots) slot[i] = -1;  // never write outside the cache
-      if (slot[i] >= 0) {
-        const uint16_t* row = reinterpret_cast<const uint16_t*>(s.x) + t * s.stride_t + hh[i] * s.stride_h;
-        raw[i] = __ldg(reinterpret_cast<const uint2*>(row) + lane);
+    for (int i = 0; i < kPairsPerWarp; ++i) {
+      const int64_t r = r0 + 2 * i;
+      bt.slot[i] = -1;
+      bt.hh[i] = 0;
+      bt.raw[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (batch < n_batches && r < rows) {
+        int64_t t;
+        if (small) {
+          const uint32_t tq = static_cast<uint32_t>(r) / static_cast<uint32_t>(H);
+          bt.hh[i] = static_cast<int>(static_cast<uint32_t>(r) - tq * static_cast<uint32_t>(H));
+          t = tq;
+        } else {
+          t = r / H;
+          bt.hh[i] = static_cast<int>(r - t * H);
+        }
+        bt.slot[i] = slots[t];   // rows of skipped tokens are read too: the load does not wait for the slot
+        const uint16_t* row = reinterpret_cast<const uint16_t*>(s.x) + t * s.stride_t + bt.hh[i] * s.stride_h;
+        bt.raw[i] = __ldg(reinterpret_cast<const uint4*>(row) + sub);
       }
     }
-  }
+  };
+
+  const int64_t batch = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+  if (batch >= n_batches) return;
+  Batch cur;
+  load(batch, cur);
 #pragma unroll
-  for (int i = 0; i < kRowsPerWarp; ++i) {
-    if (slot[i] < 0) continue;  // warp-uniform
-    const int64_t o = static_cast<int64_t>(hh[i]) * num_slots + slot[i];
+  for (int i = 0; i < kPairsPerWarp; ++i) {
+    // the two halves of a warp may disagree here; the shuffles inside stay within a half
+    const bool live = cur.slot[i] >= 0 && cur.slot[i] < num_slots;   // never write outside the cache
+    const int64_t o = static_cast<int64_t>(cur.hh[i]) * num_slots + (live ? cur.slot[i] : 0);
     uint8_t* out_row = s.data + o * dp;
     uint16_t* scale_row = s.scales + o * NG;
-    if (s.nbits == 3) pack_row<DT, 3, GS>(raw[i], out_row, scale_row, lane);
-    else if (s.nbits == 2) pack_row<DT, 2, GS>(raw[i], out_row, scale_row, lane);
-    else pack_row<DT, 4, GS>(raw[i], out_row, scale_row, lane);
+    // every lane runs the arithmetic (full-mask shuffles); only live rows are stored
+    if (s.nbits == 3) pack_row<DT, 3, GS>(cur.raw[i], out_row, scale_row, sub, live);
+    else if (s.nbits == 2) pack_row<DT, 2, GS>(cur.raw[i], out_row, scale_row, sub, live);
+    else pack_row<DT, 4, GS>(cur.raw[i], out_row, scale_row, sub, live);
   }
 }
 
 static jf_status_t check_side(const void* x, int64_t st, int64_t sh, const void* data, const void* scales, int nbits) {
   if (!x || !data || !scales) return JF_ERR_ARG;
   if (nbits < 2 || nbits > 4) return JF_ERR_UNSUPPORTED;
-  if (!aligned(x, 8) || (st % 4) != 0 || (sh % 4) != 0) return JF_ERR_ARG;
+  if (!aligned(x, 16) || (st % 8) != 0 || (sh % 8) != 0) return JF_ERR_ARG;
   if (!aligned(data, 16) || !aligned(scales, 4)) return JF_ERR_ARG;
   return JF_OK;
 }
@@ -146,7 +167,7 @@ static jf_status_t launch_pack(const PackSide& k, const PackSide* v, int dtype, 
   if (dtype != JF_DTYPE_BF16 && dtype != JF_DTYPE_FP16) return JF_ERR_UNSUPPORTED;
   if (T == 0) return JF_OK;
   const int64_t rows = T * H;
-  const int64_t warps = (rows + kRowsPerWarp - 1) / kRowsPerWarp;
+  const int64_t warps = (rows + 2 * kPairsPerWarp - 1) / (2 * kPairsPerWarp);
   const int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
   if (ctas > 0x7FFFFFFF) return JF_ERR_UNSUPPORTED;
   dim3 grid(static_cast<unsigned>(ctas), v ? 2 : 1);

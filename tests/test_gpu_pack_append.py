@@ -58,6 +58,36 @@ def test_scatter_permuted_slots_and_skip(bits, gs):
     assert bool((data[:, -1] == 0xA5).all()), "negative slot wrote to the cache"
 
 
+@pytest.mark.parametrize("dt", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("bits,gs", [(3, 64), (2, 64), (4, 128)])
+def test_rounding_boundaries_and_many_rows(dt, bits, gs):
+    """Quotients that sit exactly on k + 1/2 (scale 1, 2^-3, 3: ties go to even), quotients one
+    ulp either side of a boundary, and a large random batch, all bit-exact against the oracle."""
+    ops = _ops()
+    qmax = (1 << (bits - 1)) - 1
+    g = torch.Generator().manual_seed(7 + bits)
+    rows = []
+    for scale in (1.0, 0.125, 3.0):
+        halves = (torch.arange(128, dtype=torch.float32) % (2 * qmax + 2) - qmax - 0.5) * scale   # ..., -1.5, -0.5, 0.5, ...
+        halves[::gs] = qmax * scale                                        # pins amax, hence the scale
+        rows.append(halves)
+        rows.append(-halves)
+    x = torch.stack(rows)
+    near = x.clone().to(dt)
+    bump = torch.nextafter(near.float(), torch.full_like(near.float(), 1e9)).to(dt)
+    x = torch.cat([x.to(dt), bump, torch.randn(4096, 128, generator=g).to(dt) * 3.0])
+    n = x.shape[0]
+    x_tok = x.reshape(n, 1, 128).cuda()
+    slots = torch.arange(n, dtype=torch.int64, device="cuda")
+    data = torch.zeros(1, n, 16 * bits, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(1, n, 128 // gs, dtype=torch.bfloat16, device="cuda")
+    getattr(ops, f"fused_quant_write_int{bits}_sym")(x_tok, slots, data, scales, gs)
+    torch.cuda.synchronize()
+    ref_d, ref_s = O.quantize_and_pack(f32_values(x), gs, bits)
+    assert np.array_equal(to_bits(scales[0]), ref_s)
+    assert np.array_equal(data[0].cpu().numpy(), ref_d)
+
+
 def test_kv_pair_and_out_of_range_slot():
     ops = _ops()
     g = torch.Generator().manual_seed(7)
