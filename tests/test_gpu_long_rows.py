@@ -1,0 +1,63 @@
+"""Rows longer than one shared-memory chunk of the select kernel (32768 positions), odd row
+strides, and the bench geometry at full size, checked against the C restatement of the
+oracle (itself pinned to the numpy oracle in test_oracle_native.py).  The packed cache is the
+one the GPU append path wrote (its bytes are pinned elsewhere), so no numpy pass over the
+whole cache is needed."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import native
+from jf_testlib import Case, to_bits, f32_values
+
+pytestmark = pytest.mark.gpu
+ATOL, RTOL = 2e-3, 1e-3
+
+
+def _run(case, top_k):
+    from jetfire_b200 import ops
+    kd, ks, vd, vs = case.device_cache()
+    res = ops.fused_attn_topk(case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(),
+                              case.seq_lens.cuda(), case.ctx, case.H_q, case.H_kv, 16, top_k, case.attn_scale,
+                              want_scores=True)
+    torch.cuda.synchronize()
+    ref = native.c_decode(case.mode, f32_values(case.q), kd.cpu().numpy(), to_bits(ks), vd.cpu().numpy(), to_bits(vs),
+                          case.block_table.numpy(), case.seq_lens.numpy(), case.ctx, top_k, case.attn_scale,
+                          want_scores=True)
+    assert np.array_equal(res.topk_idx.cpu().numpy(), ref["topk_idx"]), "top-k positions differ"
+    assert np.array_equal(res.topk_slots.cpu().numpy(), ref["topk_slots"]), "top-k slots differ"
+    sc = res.scores.cpu().numpy()
+    for b in range(case.B):
+        n = min(int(case.seq_lens[b]), case.ctx)
+        if case.mode == "k4v4":
+            assert np.array_equal(sc[b, :, :n], ref["scores"][b, :, :n]), "K4 scores are not bit-exact"
+        else:
+            assert np.abs(sc[b, :, :n] - ref["scores"][b, :, :n]).max() < 2e-2
+    for name in ("o_hat", "o_old_unnorm"):
+        got, want = getattr(res, name).cpu().numpy(), ref[name]
+        assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want)), name
+    np.testing.assert_allclose(res.W.cpu().numpy(), ref["W"], atol=1e-4, rtol=1e-3)
+    return res, ref
+
+
+@pytest.mark.parametrize("mode,B,H_q,H_kv,ctx,lens,top_k,seed", [
+    ("k4v4", 1, 8, 2, 40000, [39987], 256, 51),              # two chunks, ragged end
+    ("k3v2", 2, 4, 2, 70000, [70000, 33001], 256, 52),       # three chunks and two chunks
+    ("k3v2", 1, 4, 2, 40002, [40002], 128, 53),              # row stride not a multiple of 4: plain-copy path
+    ("k4v4", 2, 8, 2, 33000, [33000, 32768], 512, 54),       # wide k: two staging rounds
+])
+def test_rows_longer_than_one_chunk(mode, B, H_q, H_kv, ctx, lens, top_k, seed):
+    _run(Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed), top_k)
+
+
+def test_bench_geometry_full_size_k4v4():
+    """BASELINE configs[1] for one layer: B 4, 32 query / 8 KV heads, ctx 32768, top-k 256."""
+    res, _ = _run(Case("k4v4", 4, 32, 8, 32768, lens=[32768] * 4, seed=55), 256)
+    idx = res.topk_idx.cpu().numpy()
+    assert (idx >= 0).all() and (idx < 32768).all()
+    assert all(np.unique(idx[b, h]).size == 256 for b in range(4) for h in range(32))
+
+
+def test_config1_geometry_full_size_k3v2():
+    """BASELINE configs[0]: B 1, 32 query / 8 KV heads, ctx 32768, K3V2, top-k 256."""
+    _run(Case("k3v2", 1, 32, 8, 32768, lens=[32768], seed=56), 256)
