@@ -82,6 +82,48 @@ __device__ __forceinline__ float canon_score_k3(const float* q, const uint8_t* r
   return __fmul_rn(part, attn);
 }
 
+// The same value as canon_score_k3, computed by EIGHT lanes per candidate (four candidates
+// per warp): lane `sub` = lane & 7 owns the code at position sub of all 16 INT3 groups, i.e.
+// channels 32 r + 8 m + sub, whose partial sums are the canonical order's lanes sub + 8 m.
+// Code sub of a group is a 3-bit field of the 24-bit word (byte planes b0 b1 b2); for
+// sub <= 4 it lies in the 16-bit window b0:b1, otherwise in b1:b2, so two PRMTs build the
+// windows of four groups and one shift + mask yields two codes at a time.  The 8 possible
+// values bf16(float(code - 4) * scale) per scale group live one per lane and are fetched with
+// a shuffle instead of being recomputed per channel.  `qv[4 r + m]` = q[32 r + 8 m + sub].
+// Every lane of the warp must call this; lanes of a candidate get the same value.
+__device__ __forceinline__ float canon_score_k3_x8(const float (&qv)[16], const uint32_t* row, float attn, int lane) {
+  const int sub = lane & 7;
+  const uint32_t base2 = static_cast<uint32_t>(lane & 24) * 0x00010001u;  // first lane of this candidate, both halves
+  const uint32_t sw = row[12];
+  const float code_f = static_cast<float>(sub - 4);
+  const float lut0 = __bfloat162float(__float2bfloat16_rn(__fmul_rn(code_f, __uint_as_float(sw << 16))));
+  const float lut1 = __bfloat162float(__float2bfloat16_rn(__fmul_rn(code_f, __uint_as_float(sw & 0xFFFF0000u))));
+  const bool early = sub <= 4;
+  const int sh = early ? 13 - 3 * sub : 21 - 3 * sub;
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const uint32_t p0 = row[r], p1 = row[4 + r], p2 = row[8 + r];
+    const uint32_t hi = early ? p0 : p1, lo = early ? p1 : p2;
+    const uint32_t c01 = and_or(prmt(lo, hi, 0x5140u) >> sh, 0x00070007u, base2);   // groups 4r, 4r+1
+    const uint32_t c23 = and_or(prmt(lo, hi, 0x7362u) >> sh, 0x00070007u, base2);   // groups 4r+2, 4r+3
+    const float lut = (r < 2) ? lut0 : lut1;
+    const float k0 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c01 & 0xFFFFu));
+    const float k1 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c01 >> 16));
+    const float k2 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c23 & 0xFFFFu));
+    const float k3 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c23 >> 16));
+    part[0] = __fmaf_rn(qv[4 * r], k0, part[0]);
+    part[1] = __fmaf_rn(qv[4 * r + 1], k1, part[1]);
+    part[2] = __fmaf_rn(qv[4 * r + 2], k2, part[2]);
+    part[3] = __fmaf_rn(qv[4 * r + 3], k3, part[3]);
+  }
+  // butterfly distances 16 and 8 pair partials held by this lane, 4, 2, 1 pair lanes
+  float t = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xFFFFFFFFu, t, o));
+  return __fmul_rn(t, attn);
+}
+
 // Canonical K4/G128 score (jetfire_vllm/csrc/int8tc_qk_scores.cu:445-487): exact int32 dot per
 // 32-channel block against the INT8 query, s = fma(float(acc_c), qs_c, s) for c = 0..3,
 // * k_scale, * attn.  Lane l handles channels 4l..4l+3 (block l / 8).
@@ -581,24 +623,16 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             keys[base + tid] = make_key(late.cand_slot[tid] >= 0 ? cand_score[base + tid] : -INFINITY, pos);
           }
         } else {
-          // one warp per candidate, four candidates in flight per warp
-          for (int c0 = warp; c0 < cn; c0 += 4 * kSelWarps) {
-            float s[4];
+          // eight lanes per candidate, four candidates per warp and round
+          float qv[16];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int c = c0 + i * kSelWarps;
-              s[i] = -INFINITY;
-              if (c < cn && late.cand_slot[c] >= 0) {
-                const uint32_t* r = late.rows + c * W;
-                s[i] = canon_score_k3(sm.q, reinterpret_cast<const uint8_t*>(r), r[12], ctx.attn, lane);
-              }
-            }
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int c = c0 + i * kSelWarps;
-              if (c < cn && lane == i) keys[base + c] = make_key(s[i], static_cast<int>(keys[base + c]));
-            }
+          for (int i = 0; i < 16; ++i) qv[i] = sm.q[32 * (i >> 2) + 8 * (i & 3) + (lane & 7)];
+          for (int c0 = 4 * warp; c0 < cn; c0 += 4 * kSelWarps) {
+            const int c = c0 + (lane >> 3);
+            const int cc = min(c, cn - 1);           // lanes past the end keep the shuffles company
+            const float s = canon_score_k3_x8(qv, late.rows + cc * W, ctx.attn, lane);
+            if (c < cn && (lane & 7) == 0)
+              keys[base + c] = make_key(late.cand_slot[c] >= 0 ? s : -INFINITY, static_cast<int>(keys[base + c]));
           }
         }
         __syncthreads();
