@@ -28,6 +28,7 @@ decode_finish_kernel(const FinishParams p, const TailParams tp) {
   const int hkv = h / tp.G, hi = h - hkv * tp.G;
   const int64_t bh = static_cast<int64_t>(b) * tp.H_q + h;
   const int64_t pbase = (static_cast<int64_t>(b) * tp.H_kv + hkv) * tp.splits;
+  pdl_wait();
   SplitPre pre;
   split_preload(tp, pbase, hi, tid, pre);
   const int n = min(p.seq_lens[b], tp.max_S);
@@ -47,6 +48,8 @@ template <int DT>
 __global__ void merge_correct_kernel(const float* __restrict__ o_hat, const float* __restrict__ o_old,
                                      const float* __restrict__ W, const uint16_t* __restrict__ o_new,
                                      uint16_t* __restrict__ out, int total) {
+  pdl_wait();
+  pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const float w = W[i / JF_HEAD_DIM];
@@ -72,10 +75,10 @@ extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t str
   dim3 grid(a->H_q, a->B);
   if (a->mode == JF_MODE_K3V2) {
     JF_ENSURE_SMEM((decode_finish_kernel<JF_MODE_K3V2>), sizeof(TailSmem<JF_MODE_K3V2>));
-    decode_finish_kernel<JF_MODE_K3V2><<<grid, kSelThreads, sizeof(TailSmem<JF_MODE_K3V2>), stream>>>(fp, tp);
+    JF_CUDA_TRY(launch_pdl(decode_finish_kernel<JF_MODE_K3V2>, grid, dim3(kSelThreads), sizeof(TailSmem<JF_MODE_K3V2>), stream, fp, tp));
   } else {
     JF_ENSURE_SMEM((decode_finish_kernel<JF_MODE_K4V4>), sizeof(TailSmem<JF_MODE_K4V4>));
-    decode_finish_kernel<JF_MODE_K4V4><<<grid, kSelThreads, sizeof(TailSmem<JF_MODE_K4V4>), stream>>>(fp, tp);
+    JF_CUDA_TRY(launch_pdl(decode_finish_kernel<JF_MODE_K4V4>, grid, dim3(kSelThreads), sizeof(TailSmem<JF_MODE_K4V4>), stream, fp, tp));
   }
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
@@ -110,13 +113,12 @@ extern "C" jf_status_t jf_merge_correct(const float* o_hat, const float* o_old_u
   const int total = B * H_q * JF_HEAD_DIM;
   const int threads = 256, blocks = (total + threads - 1) / threads;
   if (dtype == JF_DTYPE_BF16)
-    merge_correct_kernel<JF_DTYPE_BF16><<<blocks, threads, 0, stream>>>(
-        o_hat, o_old_unnorm, W, static_cast<const uint16_t*>(o_new), static_cast<uint16_t*>(out), total);
+    JF_CUDA_TRY(launch_pdl(merge_correct_kernel<JF_DTYPE_BF16>, dim3(blocks), dim3(threads), 0, stream, o_hat,
+                           o_old_unnorm, W, static_cast<const uint16_t*>(o_new), static_cast<uint16_t*>(out), total));
   else if (dtype == JF_DTYPE_FP16)
-    merge_correct_kernel<JF_DTYPE_FP16><<<blocks, threads, 0, stream>>>(
-        o_hat, o_old_unnorm, W, static_cast<const uint16_t*>(o_new), static_cast<uint16_t*>(out), total);
+    JF_CUDA_TRY(launch_pdl(merge_correct_kernel<JF_DTYPE_FP16>, dim3(blocks), dim3(threads), 0, stream, o_hat,
+                           o_old_unnorm, W, static_cast<const uint16_t*>(o_new), static_cast<uint16_t*>(out), total));
   else
     return JF_ERR_UNSUPPORTED;
-  JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
 }

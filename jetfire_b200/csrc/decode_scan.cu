@@ -236,18 +236,19 @@ scan_k3v2_kernel(const ScanParams p) {
   const uint32_t bars0 = smem_base + kScanWarps * T::kStages * T::kBytes + warp * (T::kStages * 8);
   int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8)) + warp * T::kStages;
 
+  if (lane == 0) {
+    for (int s = 0; s < T::kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
+  }
+  fence_barrier_init();
+  __syncwarp();
+  pdl_wait();  // nothing above reads global memory
+
   const int len = min(p.seq_lens[b], p.max_S);
   const int n_pages = (len + 15) >> 4;
   const int pg_begin = split * p.pages_per_split;
   const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
   // this warp's pages: pg_begin + warp, + 4, ...
   const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;  // may be <= 0
-
-  if (lane == 0) {
-    for (int s = 0; s < T::kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
-  }
-  fence_barrier_init();
-  __syncwarp();
 
   const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
   const int64_t n_blocks_phys = p.num_slots >> 4;
@@ -369,6 +370,7 @@ scan_k3v2_kernel(const ScanParams p) {
     if (++st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
+  pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
 
   // ---------------- CTA merge: 4 warps -> one partial ----------------
@@ -461,10 +463,10 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
     static_assert(kScanWarps * T::kStages * T::kBytes >= kMergeBytes, "merge buffer");
     if (a->q_dtype == JF_DTYPE_BF16) {
       JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_BF16>, smem);
-      scan_k3v2_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
+      JF_CUDA_TRY(launch_pdl(scan_k3v2_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp));
     } else {
       JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_FP16>, smem);
-      scan_k3v2_kernel<JF_DTYPE_FP16><<<grid, kScanWarps * 32, smem, stream>>>(sp);
+      JF_CUDA_TRY(launch_pdl(scan_k3v2_kernel<JF_DTYPE_FP16>, grid, dim3(kScanWarps * 32), smem, stream, sp));
     }
     JF_CUDA_TRY(cudaGetLastError());
   } else {

@@ -188,17 +188,18 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   int32_t* page_valid =
       reinterpret_cast<int32_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8)) + warp * T4::kStages;
 
-  const int len = min(p.seq_lens[b], p.max_S);
-  const int n_pages = (len + 15) >> 4;
-  const int pg_begin = split * p.pages_per_split;
-  const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
-  const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;
-
   if (lane == 0) {
     for (int s = 0; s < T4::kStages; ++s) mbar_init(&bars[s], 1);
   }
   fence_barrier_init();
   __syncwarp();
+  pdl_wait();  // nothing above reads global memory
+
+  const int len = min(p.seq_lens[b], p.max_S);
+  const int n_pages = (len + 15) >> 4;
+  const int pg_begin = split * p.pages_per_split;
+  const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
+  const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;
 
   const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
   const int64_t n_blocks_phys = p.num_slots >> 4;
@@ -322,6 +323,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
+  pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
 
   __syncthreads();
@@ -410,10 +412,10 @@ jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaS
   static_assert(kScanWarps * T4::kStages * T4::kBytes >= kMergeBytes, "merge buffer");
   if (q_dtype == JF_DTYPE_BF16) {
     JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_BF16>, smem);
-    scan_k4v4_kernel<JF_DTYPE_BF16><<<grid, kScanWarps * 32, smem, stream>>>(sp, k_map, v_map);
+    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map));
   } else {
     JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_FP16>, smem);
-    scan_k4v4_kernel<JF_DTYPE_FP16><<<grid, kScanWarps * 32, smem, stream>>>(sp, k_map, v_map);
+    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_FP16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map));
   }
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;

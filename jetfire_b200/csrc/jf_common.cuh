@@ -41,6 +41,22 @@ inline jf_status_t cuda_fail(cudaError_t e) {
     }                                                                                          \
   } while (0)
 
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 constexpr int kNumSMs = 148;  // B200
@@ -136,6 +152,15 @@ __device__ __forceinline__ void bulk_g2s_u32(uint32_t dst, const void* src, uint
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// Programmatic dependent launch.  A kernel launched with launch_pdl may start while the
+// kernel before it in the stream is still running (after that kernel's CTAs have all called
+// pdl_trigger or exited); it must call pdl_wait before it touches any global memory, which
+// returns once the earlier kernel has completed and its writes are visible.  Without the
+// launch attribute both are no-ops.  Only work that needs no global memory (barrier
+// initialisation, address arithmetic) is placed ahead of pdl_wait.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Per-thread asynchronous copies global -> shared (no register staging); 16 bytes need
 // 16-byte aligned addresses, 4 bytes 4-byte aligned ones.
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {

@@ -268,6 +268,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     mbar_init(&sm.bar, 1);
     fence_barrier_init();
   }
+  pdl_wait();  // nothing above reads global memory
 
   // ---- small loads first (they are what the prologue waits for), then the 128 KB copy ----
   uint16_t q_bits = 0;
@@ -761,6 +762,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     JF_PHASE(9);
   }
 
+  pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   for (int r = tid; r < K; r += kSelThreads) {
     int64_t idx = -1, slot = -1;
     if (r < m_sel) {
@@ -795,10 +797,10 @@ jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, di
   static_assert(kMaxSmem <= 227 * 1024, "select kernel shared memory");
   if (fused) {
     JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true>), kMaxSmem);
-    topk_select_kernel<MODE, DT, true><<<grid, kSelThreads, smem, stream>>>(sp, tp);
+    JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, true>, grid, dim3(kSelThreads), smem, stream, sp, tp));
   } else {
     JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, false>), kMaxSmem);
-    topk_select_kernel<MODE, DT, false><<<grid, kSelThreads, smem, stream>>>(sp, tp);
+    JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, false>, grid, dim3(kSelThreads), smem, stream, sp, tp));
   }
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
