@@ -177,6 +177,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // swizzled tiles must sit on 512-byte boundaries: align by hand (1 KB of slack is allocated)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  JF_PHASE(0);
   const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // uniform by construction
   const int g = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -194,14 +195,30 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   fence_barrier_init();
   __syncwarp();
   pdl_wait();  // nothing above reads global memory
+  JF_PHASE(1);
 
-  const int len = min(p.seq_lens[b], p.max_S);
-  const int n_pages = (len + 15) >> 4;
+  // The first loads (sequence length, the block-table entries of the first ring of pages, the
+  // query) do not depend on one another: all are issued here, so the prologue pays one
+  // memory latency before the first copies can start, and the query arithmetic then runs
+  // while those copies are in flight.
   const int pg_begin = split * p.pages_per_split;
+  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
+  const int len_raw = p.seq_lens[b];
+  int64_t blk_first[T4::kStages];
+#pragma unroll
+  for (int it = 0; it < T4::kStages; ++it)   // entries past the row's end are never used
+    blk_first[it] = (pg_begin + warp + it * kScanWarps < p.max_blocks) ? bt_row[it * kScanWarps] : -1;
+  // warp w prepares the query's 32-channel block w for the whole CTA (see below)
+  uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
+  if (g < p.G) {   // the 8 channels 32 w + 8 tig + {0..7} are 16 contiguous bytes
+    const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + hkv * p.G + g) * JF_HEAD_DIM;
+    q_raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + qbase + 32 * warp + 8 * tig));
+  }
+  const int len = min(len_raw, p.max_S);
+  const int n_pages = (len + 15) >> 4;
   const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
   const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;
 
-  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
   const int64_t n_blocks_phys = p.num_slots >> 4;
   const int64_t row_base = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
   const uint16_t* ks_h = p.k_scales + row_base;
@@ -233,26 +250,25 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   };
 
   {
-    const int pro = min(T4::kStages, my_n);
-    for (int it = 0; it < pro; ++it) issue(it, it, bt_row[it * kScanWarps]);
+#pragma unroll
+    for (int it = 0; it < T4::kStages; ++it)
+      if (it < my_n) issue(it, it, blk_first[it]);
   }
   int64_t next_blk = 0;
   if (T4::kStages < my_n) next_blk = bt_row[T4::kStages * kScanWarps];
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
-  //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones. ----
+  //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones.
+  //      The four warps need identical fragments: warp w quantises block c = w and the CTA
+  //      exchanges the results through shared memory (a quarter of the arithmetic per warp). ----
   K4State st;
   {
-    const int h = hkv * p.G + g;
-    const bool live = g < p.G;
-    const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + h) * JF_HEAD_DIM;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    static_assert(kScanWarps == 4, "one warp per 32-channel query block");
+    uint32_t* qx = reinterpret_cast<uint32_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8 + 4));  // [c][6][32]
+    {
       float v[8];
       float amax = 0.f;
-      uint4 raw = make_uint4(0u, 0u, 0u, 0u);  // the 8 channels are 16 contiguous bytes
-      if (live) raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + qbase + 32 * c + 8 * tig));
-      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+      const uint32_t rw[4] = {q_raw.x, q_raw.y, q_raw.z, q_raw.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         v[j] = Elem<DT>::to_f32(static_cast<uint16_t>((j & 1) ? (rw[j >> 1] >> 16) : (rw[j >> 1] & 0xFFFFu)));
@@ -270,12 +286,24 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       }
       sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
       sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-      st.qb[c][0] = (qi[0] & 255) | ((qi[2] & 255) << 8) | ((qi[4] & 255) << 16) | ((qi[6] & 255) << 24);
-      st.qb[c][1] = (qi[1] & 255) | ((qi[3] & 255) << 8) | ((qi[5] & 255) << 16) | ((qi[7] & 255) << 24);
-      st.qs_h0[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig);
-      st.qs_h1[c] = __shfl_sync(0xFFFFFFFFu, qs, 8 * tig + 4);
-      st.init_h0[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig);
-      st.init_h1[c] = -8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig + 4);
+      uint32_t* mine = qx + warp * (6 * 32) + lane;
+      mine[0] = (qi[0] & 255) | ((qi[2] & 255) << 8) | ((qi[4] & 255) << 16) | ((qi[6] & 255) << 24);
+      mine[32] = (qi[1] & 255) | ((qi[3] & 255) << 8) | ((qi[5] & 255) << 16) | ((qi[7] & 255) << 24);
+      mine[64] = __float_as_uint(__shfl_sync(0xFFFFFFFFu, qs, 8 * tig));
+      mine[96] = __float_as_uint(__shfl_sync(0xFFFFFFFFu, qs, 8 * tig + 4));
+      mine[128] = static_cast<uint32_t>(-8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig));
+      mine[160] = static_cast<uint32_t>(-8 * __shfl_sync(0xFFFFFFFFu, sum, 8 * tig + 4));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t* src = qx + c * (6 * 32) + lane;
+      st.qb[c][0] = src[0];
+      st.qb[c][1] = src[32];
+      st.qs_h0[c] = __uint_as_float(src[64]);
+      st.qs_h1[c] = __uint_as_float(src[96]);
+      st.init_h0[c] = static_cast<int>(src[128]);
+      st.init_h1[c] = static_cast<int>(src[160]);
     }
   }
 #pragma unroll
@@ -301,6 +329,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
 
+  JF_PHASE(2);
   int st_idx = 0;
   uint32_t parity = 0u;
   for (int it = 0; it < my_n; ++it) {
@@ -310,6 +339,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       failed = true;
       break;
     }
+    if (it == 0) JF_PHASE(3);
     const uint32_t sb = stages0 + st_idx * T4::kBytes;
     if (slow_mask & (1u << st_idx)) k4v4_page<true>(st, sb, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
     else k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
@@ -323,10 +353,13 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
+  JF_PHASE(4);
+  JF_PHASE_VAL(10, my_n);
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
 
   __syncthreads();
+  JF_PHASE(5);
   {
     float* wo = reinterpret_cast<float*>(smem) + warp * (kHeadsPad * JF_HEAD_DIM);
 #pragma unroll
@@ -341,6 +374,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     }
   }
   cta_merge_store(p, smem, st.l0, st.l1, st.m_ref0, st.m_ref1, 0.f, 0.f, split, hkv, b);
+  JF_PHASE(6);
 }
 
 // ---- tensor maps -----------------------------------------------------------------------
@@ -400,6 +434,12 @@ jf_status_t page_map(const void* base, uint64_t rows, CUtensorMap* out) {
 
 }  // namespace
 
+#ifdef JF_PHASE_TIMING
+extern "C" int jf_debug_scan_times(unsigned long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_phase_t, sizeof(g_phase_t)));
+}
+#endif
+
 jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(sp.H_kv) * static_cast<uint64_t>(sp.num_slots);
   if (rows > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
@@ -408,7 +448,7 @@ jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaS
   if (st != JF_OK) return st;
   st = page_map(sp.v_data, rows, &v_map);
   if (st != JF_OK) return st;
-  const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + 1024;
+  const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4 + 1024;  // ring, barriers, page lengths, query exchange, alignment slack
   static_assert(kScanWarps * T4::kStages * T4::kBytes >= kMergeBytes, "merge buffer");
   if (q_dtype == JF_DTYPE_BF16) {
     JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_BF16>, smem);

@@ -12,24 +12,6 @@
 
 #include "decode_common.cuh"
 
-// Phase stamps for tuning: compiled out unless JF_PHASE_TIMING is defined; then CTA (0, 0)
-// of the select kernel records clock64() at each JF_PHASE(i) and jf_debug_phase_times
-// (topk_select.cu) copies the stamps out.
-#ifdef JF_PHASE_TIMING
-static __device__ unsigned long long g_phase_t[64];
-#define JF_PHASE(i)                                                                          \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_t[i] = clock64();    \
-  } while (0)
-#define JF_PHASE_VAL(i, v)                                                                   \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_t[i] = (v);          \
-  } while (0)
-#else
-#define JF_PHASE(i) do { } while (0)
-#define JF_PHASE_VAL(i, v) do { } while (0)
-#endif
-
 namespace jf {
 
 constexpr int kSelThreads = 1024;

@@ -10,6 +10,24 @@
 
 #include "../../include/jetfire_b200.h"
 
+// Phase stamps for tuning: compiled out unless JF_PHASE_TIMING is defined; then the first
+// CTA of a kernel records clock64() at each JF_PHASE(i) (one table per source file) and the
+// jf_debug_*_times functions copy the stamps out.
+#ifdef JF_PHASE_TIMING
+static __device__ unsigned long long g_phase_t[64];
+#define JF_PHASE(i)                                                                          \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_phase_t[i] = clock64();    \
+  } while (0)
+#define JF_PHASE_VAL(i, v)                                                                   \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_phase_t[i] = (v);          \
+  } while (0)
+#else
+#define JF_PHASE(i) do { } while (0)
+#define JF_PHASE_VAL(i, v) do { } while (0)
+#endif
+
 namespace jf {
 
 // Per-thread record of the last failing CUDA call (read through jf_last_cuda_error).
