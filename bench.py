@@ -48,7 +48,7 @@ WORKLOADS = {
 }
 BYTES_PER_TOKEN_HEAD = {"k3v2": 88, "k4v4": 132}
 MODE_BITS = {"k3v2": (3, 2, 64), "k4v4": (4, 4, 128)}
-DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 93.4, "k4v4": 142.6}   # measured with ncu, see profiles/
+DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 91.4, "k4v4": 137.5}   # measured with ncu, see profiles/
 
 
 def parse_args():
