@@ -394,6 +394,22 @@ def main():
     ms_step = float(t.item()) / args.steps
     value = step_bytes * world / (ms_step * 1e-3) / 1e9
 
+    # diagnostic (outside the timed region): each rank's step without the gather, so that a slow
+    # GPU can be told from the coupling of the ranks through the collective
+    per_rank_ms = None
+    if world > 1:
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        c0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        c1.record()
+        torch.cuda.synchronize()
+        mine = torch.tensor([c0.elapsed_time(c1) / args.steps], dtype=torch.float64, device=device)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        per_rank_ms = [round(float(x.item()), 4) for x in every]
+
     # ---- roofline of the scan kernel alone ----
     for L in layers:
         L.call.scan()
@@ -501,6 +517,7 @@ def main():
             "tokens_per_s": w["batch"] * world / (ms_step * 1e-3),
             "us_per_layer": ms_step * 1e3 / n_layers,
             "gpu_launches": 3 * n_layers * args.steps,  # per layer: scan, select+finish, merge
+            "per_rank_ms_without_gather": per_rank_ms,
             "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": sampler.summary(),
         }
         print(json.dumps(line), flush=True)
