@@ -86,7 +86,7 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 struct K4State {
   uint32_t qb[4][2];          // INT8 query fragments (B operand of the K MMA)
   float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
-  int init_h0[4], init_h1[4]; // -8 * sum(qi) per block for those heads
+  int init[4][4];             // -8 * sum(qi) per block for those heads, laid out as the MMA's C operand
   float oacc[8][4];
   float m_ref0, m_ref1, l0, l1;
   uint32_t k_off[4];          // swizzled byte offsets of this lane's K words, per 32-channel block
@@ -114,8 +114,7 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const uint32_t w0 = kw[c][0], w1 = kw[c][1];
-    const int init[4] = {st.init_h0[c], st.init_h1[c], st.init_h0[c], st.init_h1[c]};
-    mma_u8s8_cd(acc[c], init, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu,
+    mma_u8s8_cd(acc[c], st.init[c], (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu,
                 st.qb[c][0], st.qb[c][1]);
   }
   const float ks0 = __uint_as_float(ksb0 << 16), ks1 = __uint_as_float(ksb1 << 16);
@@ -178,6 +177,15 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   // swizzled tiles must sit on 512-byte boundaries: align by hand (1 KB of slack is allocated)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   JF_PHASE(0);
+  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  JF_CTA_STAMP(cta_lin, 0);
+#ifdef JF_PHASE_TIMING
+  if (threadIdx.x == 0 && cta_lin < 1024) {
+    unsigned smid__;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid__));
+    g_cta_t[cta_lin * 8 + 5] = smid__;
+  }
+#endif
   const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // uniform by construction
   const int g = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -196,6 +204,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   __syncwarp();
   pdl_wait();  // nothing above reads global memory
   JF_PHASE(1);
+  JF_CTA_STAMP(cta_lin, 1);
 
   // The first loads (sequence length, the block-table entries of the first ring of pages, the
   // query) do not depend on one another: all are issued here, so the prologue pays one
@@ -302,8 +311,8 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       st.qb[c][1] = src[32];
       st.qs_h0[c] = __uint_as_float(src[64]);
       st.qs_h1[c] = __uint_as_float(src[96]);
-      st.init_h0[c] = static_cast<int>(src[128]);
-      st.init_h1[c] = static_cast<int>(src[160]);
+      st.init[c][0] = st.init[c][2] = static_cast<int>(src[128]);
+      st.init[c][1] = st.init[c][3] = static_cast<int>(src[160]);
     }
   }
 #pragma unroll
@@ -330,6 +339,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const float attn = p.attn_scale;
 
   JF_PHASE(2);
+  JF_CTA_STAMP(cta_lin, 2);
   int st_idx = 0;
   uint32_t parity = 0u;
   for (int it = 0; it < my_n; ++it) {
@@ -354,6 +364,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   }
 
   JF_PHASE(4);
+  JF_CTA_STAMP(cta_lin, 3);
   JF_PHASE_VAL(10, my_n);
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
@@ -375,6 +386,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   }
   cta_merge_store(p, smem, st.l0, st.l1, st.m_ref0, st.m_ref1, 0.f, 0.f, split, hkv, b);
   JF_PHASE(6);
+  JF_CTA_STAMP(cta_lin, 4);
 }
 
 // ---- tensor maps -----------------------------------------------------------------------
@@ -437,6 +449,9 @@ jf_status_t page_map(const void* base, uint64_t rows, CUtensorMap* out) {
 #ifdef JF_PHASE_TIMING
 extern "C" int jf_debug_scan_times(unsigned long long* out) {
   return static_cast<int>(cudaMemcpyFromSymbol(out, g_phase_t, sizeof(g_phase_t)));
+}
+extern "C" int jf_debug_scan_cta_times(unsigned long long* out) {   // [1024][8] globaltimer stamps
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_cta_t, sizeof(g_cta_t)));
 }
 #endif
 

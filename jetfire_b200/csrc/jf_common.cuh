@@ -23,9 +23,20 @@ static __device__ unsigned long long g_phase_t[64];
   do {                                                                                       \
     if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_phase_t[i] = (v);          \
   } while (0)
+// per-CTA wall-clock stamps (globaltimer, ns): slot k of CTA `cta`
+static __device__ unsigned long long g_cta_t[1024 * 8];
+#define JF_CTA_STAMP(cta, k)                                                                 \
+  do {                                                                                       \
+    if (threadIdx.x == 0 && (cta) < 1024) {                                                  \
+      unsigned long long t__;                                                                \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
+      g_cta_t[(cta) * 8 + (k)] = t__;                                                        \
+    }                                                                                        \
+  } while (0)
 #else
 #define JF_PHASE(i) do { } while (0)
 #define JF_PHASE_VAL(i, v) do { } while (0)
+#define JF_CTA_STAMP(cta, k) do { } while (0)
 #endif
 
 namespace jf {
