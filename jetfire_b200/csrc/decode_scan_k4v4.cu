@@ -167,6 +167,113 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
   }
 }
 
+// Two full 16-token pages at once, written out so that the two pages' instruction streams
+// interleave (the asm statements keep their program order): all shared-memory loads first,
+// the integer MMAs of both pages alternating, one softmax step over both pages' scores (one
+// reference-point check instead of two), then the P.V MMAs of both pages into the same
+// accumulator tiles.  A warp is one long dependent chain per page; with four warps per
+// scheduler that chain, not the instruction count, set the pace.
+__device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32_t sbB, float attn, float* spA0,
+                                               float* spA1, float* spB0, float* spB1, bool st0, bool st1) {
+  uint32_t kwA[4][2], kwB[4][2];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t a = sbA + st.k_off[c], b = sbB + st.k_off[c];
+    kwA[c][0] = lds32<0>(a); kwA[c][1] = lds32<512>(a);
+    kwB[c][0] = lds32<0>(b); kwB[c][1] = lds32<512>(b);
+  }
+  const uint32_t saA = sbA + st.s_off, saB = sbB + st.s_off;
+  const uint32_t ksA0 = lds16<0>(saA), ksA1 = lds16<16>(saA), vsA0b = lds16<32>(saA), vsA1b = lds16<48>(saA);
+  const uint32_t ksB0 = lds16<0>(saB), ksB1 = lds16<16>(saB), vsB0b = lds16<32>(saB), vsB1b = lds16<48>(saB);
+  int accA[4][4], accB[4][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t a0 = kwA[c][0], a1 = kwA[c][1], b0 = kwB[c][0], b1 = kwB[c][1];
+    mma_u8s8_cd(accA[c], st.init[c], (a0 >> 4) & 0x0F0F0F0Fu, (a1 >> 4) & 0x0F0F0F0Fu, a0 & 0x0F0F0F0Fu, a1 & 0x0F0F0F0Fu,
+                st.qb[c][0], st.qb[c][1]);
+    mma_u8s8_cd(accB[c], st.init[c], (b0 >> 4) & 0x0F0F0F0Fu, (b1 >> 4) & 0x0F0F0F0Fu, b0 & 0x0F0F0F0Fu, b1 & 0x0F0F0F0Fu,
+                st.qb[c][0], st.qb[c][1]);
+  }
+  // V words of both pages: requested now, used after the softmax
+  const uint32_t vA0 = sbA + st.v_offA, vA1 = sbA + st.v_offB, vB0 = sbB + st.v_offA, vB1 = sbB + st.v_offB;
+  const uint2 WaA = lds64<0>(vA0), WbA = lds64<0>(vA1), WcA = lds64<512>(vA0), WdA = lds64<512>(vA1);
+  const uint2 WaB = lds64<0>(vB0), WbB = lds64<0>(vB1), WcB = lds64<512>(vB0), WdB = lds64<512>(vB1);
+  float sA[4] = {0.f, 0.f, 0.f, 0.f}, sB[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    sA[0] = __fmaf_rn(static_cast<float>(accA[c][0]), st.qs_h0[c], sA[0]);
+    sB[0] = __fmaf_rn(static_cast<float>(accB[c][0]), st.qs_h0[c], sB[0]);
+    sA[1] = __fmaf_rn(static_cast<float>(accA[c][1]), st.qs_h1[c], sA[1]);
+    sB[1] = __fmaf_rn(static_cast<float>(accB[c][1]), st.qs_h1[c], sB[1]);
+    sA[2] = __fmaf_rn(static_cast<float>(accA[c][2]), st.qs_h0[c], sA[2]);
+    sB[2] = __fmaf_rn(static_cast<float>(accB[c][2]), st.qs_h0[c], sB[2]);
+    sA[3] = __fmaf_rn(static_cast<float>(accA[c][3]), st.qs_h1[c], sA[3]);
+    sB[3] = __fmaf_rn(static_cast<float>(accB[c][3]), st.qs_h1[c], sB[3]);
+  }
+  {
+    const float kA0 = __uint_as_float(ksA0 << 16), kA1 = __uint_as_float(ksA1 << 16);
+    const float kB0 = __uint_as_float(ksB0 << 16), kB1 = __uint_as_float(ksB1 << 16);
+    sA[0] = __fmul_rn(__fmul_rn(sA[0], kA0), attn); sB[0] = __fmul_rn(__fmul_rn(sB[0], kB0), attn);
+    sA[1] = __fmul_rn(__fmul_rn(sA[1], kA0), attn); sB[1] = __fmul_rn(__fmul_rn(sB[1], kB0), attn);
+    sA[2] = __fmul_rn(__fmul_rn(sA[2], kA1), attn); sB[2] = __fmul_rn(__fmul_rn(sB[2], kB1), attn);
+    sA[3] = __fmul_rn(__fmul_rn(sA[3], kA1), attn); sB[3] = __fmul_rn(__fmul_rn(sB[3], kB1), attn);
+  }
+  if (st0) { spA0[0] = sA[0]; spA0[8] = sA[2]; spB0[0] = sB[0]; spB0[8] = sB[2]; }
+  if (st1) { spA1[0] = sA[1]; spA1[8] = sA[3]; spB1[0] = sB[1]; spB1[8] = sB[3]; }
+
+  // ---- one online-softmax step over both pages (same arithmetic per score as softmax_step) ----
+  float pA[4], pB[4];
+  {
+    float mx0 = fmaxf(fmaxf(sA[0], sA[2]), fmaxf(sB[0], sB[2])), mx1 = fmaxf(fmaxf(sA[1], sA[3]), fmaxf(sB[1], sB[3]));
+    const bool need = (mx0 > st.m_ref0 + 4.0f) || (mx1 > st.m_ref1 + 4.0f);
+    if (__any_sync(0xFFFFFFFFu, need)) {
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, o));
+      }
+      const float n0 = fmaxf(st.m_ref0, mx0), n1 = fmaxf(st.m_ref1, mx1);
+      const float f0 = ex2((st.m_ref0 - n0) * kLog2e), f1 = ex2((st.m_ref1 - n1) * kLog2e);
+      st.l0 *= f0; st.l1 *= f1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { st.oacc[i][0] *= f0; st.oacc[i][1] *= f1; st.oacc[i][2] *= f0; st.oacc[i][3] *= f1; }
+      st.m_ref0 = n0; st.m_ref1 = n1;
+    }
+    const float mb0 = st.m_ref0 * kLog2e, mb1 = st.m_ref1 * kLog2e;
+    pA[0] = ex2(fmaf(sA[0], kLog2e, -mb0)); pB[0] = ex2(fmaf(sB[0], kLog2e, -mb0));
+    pA[1] = ex2(fmaf(sA[1], kLog2e, -mb1)); pB[1] = ex2(fmaf(sB[1], kLog2e, -mb1));
+    pA[2] = ex2(fmaf(sA[2], kLog2e, -mb0)); pB[2] = ex2(fmaf(sB[2], kLog2e, -mb0));
+    pA[3] = ex2(fmaf(sA[3], kLog2e, -mb1)); pB[3] = ex2(fmaf(sB[3], kLog2e, -mb1));
+    st.l0 += (pA[0] + pA[2]) + (pB[0] + pB[2]);
+    st.l1 += (pA[1] + pA[3]) + (pB[1] + pB[3]);
+  }
+
+  // ---- (P * vscale).V for both pages ----
+  const float vsA0 = __uint_as_float(vsA0b << 16), vsA1 = __uint_as_float(vsA1b << 16);
+  const float vsB0 = __uint_as_float(vsB0b << 16), vsB1 = __uint_as_float(vsB1b << 16);
+  const uint32_t A0 = movmatrix_trans(pack_f16x2_sat(pA[0] * vsA0, pA[1] * vsA0));
+  const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(pB[0] * vsB0, pB[1] * vsB0));
+  const uint32_t A1 = movmatrix_trans(pack_f16x2_sat(pA[2] * vsA1, pA[3] * vsA1));
+  const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(pB[2] * vsB1, pB[3] * vsB1));
+  const uint32_t waA[2] = {WaA.x, WaA.y}, wbA[2] = {WbA.x, WbA.y}, wcA[2] = {WcA.x, WcA.y}, wdA[2] = {WdA.x, WdA.y};
+  const uint32_t waB[2] = {WaB.x, WaB.y}, wbB[2] = {WbB.x, WbB.y}, wcB[2] = {WcB.x, WcB.y}, wdB[2] = {WdB.x, WdB.y};
+#pragma unroll
+  for (int wi = 0; wi < 2; ++wi) {
+#pragma unroll
+    for (int bp = 0; bp < 2; ++bp) {
+      const uint32_t sel = bp ? 0x7632u : 0x5410u;
+      const uint32_t XA = prmt(waA[wi], wbA[wi], sel), XB = prmt(wcA[wi], wdA[wi], sel);
+      const uint32_t YA = prmt(waB[wi], wbB[wi], sel), YB = prmt(wcB[wi], wdB[wi], sel);
+      const uint32_t XA2 = XA >> 8, XB2 = XB >> 8, YA2 = YA >> 8, YB2 = YB >> 8;
+      const int mt = 4 * wi + 2 * bp;
+      mma_f16_16816(st.oacc[mt], v4_field<0>(XA), v4_field<4>(XA), v4_field<0>(XB), v4_field<4>(XB), A0, A1);
+      mma_f16_16816(st.oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), A0, A1);
+      mma_f16_16816(st.oacc[mt], v4_field<0>(YA), v4_field<4>(YA), v4_field<0>(YB), v4_field<4>(YB), B0, B1);
+      mma_f16_16816(st.oacc[mt + 1], v4_field<0>(YA2), v4_field<4>(YA2), v4_field<0>(YB2), v4_field<4>(YB2), B0, B1);
+    }
+  }
+}
+
 }  // namespace
 
 template <int DT>
@@ -263,8 +370,10 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     for (int it = 0; it < T4::kStages; ++it)
       if (it < my_n) issue(it, it, blk_first[it]);
   }
-  int64_t next_blk = 0;
+  // block-table entries of the next two refills (a round refills up to two stages)
+  int64_t next_blk = 0, next_blk1 = 0;
   if (T4::kStages < my_n) next_blk = bt_row[T4::kStages * kScanWarps];
+  if (T4::kStages + 1 < my_n) next_blk1 = bt_row[(T4::kStages + 1) * kScanWarps];
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
   //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones.
@@ -342,8 +451,16 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   JF_CTA_STAMP(cta_lin, 2);
   int st_idx = 0;
   uint32_t parity = 0u;
-  for (int it = 0; it < my_n; ++it) {
-    if (!mbar_wait(&bars[st_idx], parity)) {
+  int it = 0;
+  while (it < my_n) {
+    // two pages per round when both are full pages; a partial / invalid page goes alone
+    int st2 = st_idx + 1;
+    uint32_t par2 = parity;
+    if (st2 == T4::kStages) { st2 = 0; par2 ^= 1u; }
+    const bool pair = (it + 1 < my_n) && !(slow_mask & ((1u << st_idx) | (1u << st2)));
+    bool ok = mbar_wait(&bars[st_idx], parity);
+    if (ok && pair) ok = mbar_wait(&bars[st2], par2);
+    if (!ok) {
       for (int j = it + 1; j < min(my_n, it + T4::kStages); ++j)
         mbar_wait(&bars[j % T4::kStages], (j / T4::kStages) & 1, 1000000ull);
       failed = true;
@@ -351,16 +468,27 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     }
     if (it == 0) JF_PHASE(3);
     const uint32_t sb = stages0 + st_idx * T4::kBytes;
-    if (slow_mask & (1u << st_idx)) k4v4_page<true>(st, sb, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
-    else k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
-    __syncwarp();
-    if (it + T4::kStages < my_n) {
-      issue(it + T4::kStages, st_idx, next_blk);
-      if (it + T4::kStages + 1 < my_n) next_blk = bt_row[(it + T4::kStages + 1) * kScanWarps];
+    if (pair) {
+      k4v4_page_pair(st, sb, stages0 + st2 * T4::kBytes, attn, sp0, sp1, sp0 + 16 * kScanWarps, sp1 + 16 * kScanWarps,
+                     st0, st1);
+    } else if (slow_mask & (1u << st_idx)) {
+      k4v4_page<true>(st, sb, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
+    } else {
+      k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
     }
-    sp0 += 16 * kScanWarps;
-    sp1 += 16 * kScanWarps;
-    if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
+    __syncwarp();
+    const int n_done = pair ? 2 : 1;
+    for (int k = 0; k < n_done; ++k) {
+      if (it + T4::kStages < my_n) {
+        issue(it + T4::kStages, st_idx, next_blk);
+        next_blk = next_blk1;
+        if (it + T4::kStages + 2 < my_n) next_blk1 = bt_row[(it + T4::kStages + 2) * kScanWarps];
+      }
+      sp0 += 16 * kScanWarps;
+      sp1 += 16 * kScanWarps;
+      ++it;
+      if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
+    }
   }
 
   JF_PHASE(4);
