@@ -42,6 +42,35 @@ def _report(title, t, marks):
     print(f"{title}: " + " | ".join(parts) + f" | total {t[marks[-1][0]] - t[marks[0][0]]} cycles")
 
 
+def _cta_timeline():
+    """Per-CTA wall-clock stamps of the last K4V4 scan launch (globaltimer, ns): when the CTAs
+    started, entered and left their page loops and finished; and the loop time by the CTA's
+    launch rank on its SM (the warp scheduler favours the older CTAs)."""
+    import numpy as np
+    fn = getattr(_lib.lib, "jf_debug_scan_cta_times", None)
+    if fn is None:
+        raise SystemExit("rebuild with JF_NVCC_EXTRA=-DJF_PHASE_TIMING")
+    buf = (C.c_ulonglong * (1024 * 8))()
+    fn(buf)
+    t = np.array(list(buf), dtype=np.int64).reshape(1024, 8)
+    t = t[t[:, 0] > 0]   # the CTAs that ran (this tool launches one shape only)
+    t0 = t[:, 0].min()
+    span = lambda a: f"{int(a.min() - t0)} / {int(np.median(a) - t0)} / {int(a.max() - t0)}"
+    print(f"  ns from the first CTA's start (min / median / max over {len(t)} CTAs): start {span(t[:, 0])}, "
+          f"past the wait for the previous kernel {span(t[:, 1])}, loop start {span(t[:, 2])}, "
+          f"loop end {span(t[:, 3])}, end {span(t[:, 4])}")
+    loop = t[:, 3] - t[:, 2]
+    print(f"  loop ns min / median / max: {int(loop.min())} / {int(np.median(loop))} / {int(loop.max())}")
+    sm = t[:, 5]
+    by_rank = {}
+    for s_ in np.unique(sm):
+        idx = np.sort(np.where(sm == s_)[0])
+        for r, i in enumerate(idx):
+            by_rank.setdefault((len(idx), r), []).append(loop[i])
+    print("  median loop ns by (CTAs on the SM, launch rank): " +
+          ", ".join(f"({k[0]},{k[1]}): {int(np.median(v))}" for k, v in sorted(by_rank.items())))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", default="k4v4", choices=("k4v4", "k3v2"))
@@ -49,6 +78,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--top-k", type=int, default=256)
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--cta-timeline", action="store_true", help="per-CTA wall-clock summary of the K4V4 scan")
     a = ap.parse_args()
     kb, vb, gs = {"k4v4": (4, 4, 128), "k3v2": (3, 2, 64)}[a.mode]
     H_q, H_kv, dev = 32, 8, torch.device("cuda", 0)
@@ -72,6 +102,8 @@ def main():
         torch.cuda.synchronize()
         if a.mode == "k4v4":
             _report("scan_k4v4", _stamps("jf_debug_scan_times"), SCAN_MARKS)
+            if a.cta_timeline:
+                _cta_timeline()
         _report(f"select+finish {a.mode}", _stamps("jf_debug_phase_times"), SELECT_MARKS)
 
 
