@@ -204,6 +204,24 @@ jf_status_t jf_pool_submit(const void* q, const void* k_shadow, const void* v_sh
 jf_status_t jf_pool_wait_timeout(int32_t timeout_ms);
 jf_status_t jf_pool_shutdown(void);
 
+/* Stream-ordered form (create_cpu_topk_submit_ctx / stream_submit_cpu_topk_attn /
+ * stream_wait_cpu_topk_attn, jetfire_vllm/csrc/cpu_topk_attn.cpp:2147-2312): a context fixes
+ * the job's buffers; `submit` queues a host callback on the stream that hands the job to the
+ * pool when the stream gets there (after the copy of the selected slots to host memory),
+ * `wait` queues one that holds the stream until the job is done, so a merge kernel queued
+ * after it reads a finished o_new.  Both callbacks wait at most wait_ms (default 30000); a
+ * wait that ran out is reported once by jf_submit_ctx_status.  The context must outlive every
+ * stream operation (and CUDA graph) that refers to it. */
+jf_status_t jf_submit_ctx_create(const void* q, const void* k_shadow, const void* v_shadow,
+                                 const int64_t* head_map, const int64_t* ts_buf, void* o_new,
+                                 int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                 int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
+                                 int32_t wait_ms, int64_t* handle);
+jf_status_t jf_submit_ctx_destroy(int64_t handle);
+jf_status_t jf_submit_ctx_status(int64_t handle);
+jf_status_t jf_stream_submit_cpu_topk_attn(jf_stream_t stream, int64_t handle);
+jf_status_t jf_stream_wait_cpu_topk_attn(jf_stream_t stream, int64_t handle);
+
 /* Pinned host memory mapped into the device address space
  * (alloc_mapped_pinned_pair, jetfire_vllm/csrc/cpu_topk_attn.cpp:958-1040). */
 jf_status_t jf_alloc_mapped(uint64_t bytes, void** host_ptr, void** device_ptr);

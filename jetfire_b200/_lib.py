@@ -71,6 +71,13 @@ _SIGS = {
     "jf_pool_submit": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                      C.c_void_p]),
     "jf_pool_wait_timeout": (C.c_int32, [C.c_int32]),
+    "jf_submit_ctx_create": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
+                                                                           C.c_void_p, C.c_int32,
+                                                                           C.POINTER(C.c_int64)]),
+    "jf_submit_ctx_destroy": (C.c_int32, [C.c_int64]),
+    "jf_submit_ctx_status": (C.c_int32, [C.c_int64]),
+    "jf_stream_submit_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),
+    "jf_stream_wait_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),
     "jf_pool_shutdown": (C.c_int32, []),
     "jf_alloc_mapped": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "jf_free_mapped": (C.c_int32, [C.c_void_p]),

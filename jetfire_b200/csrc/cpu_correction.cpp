@@ -25,6 +25,8 @@
 
 #include <immintrin.h>
 
+#include <cuda_runtime_api.h>
+
 #include "../../include/jetfire_b200.h"
 
 namespace {
@@ -342,9 +344,9 @@ class Pool {
   }
   // false if a job is still in flight
   bool submit(const Job& j) {
-    if (pending_.load(std::memory_order_acquire) != 0) return false;
     {
       std::lock_guard<std::mutex> l(m_);
+      if (pending_.load(std::memory_order_acquire) != 0) return false;   // checked under the lock: submitters may race
       job_ = j;
       next_row_.store(0, std::memory_order_relaxed);
       pending_.store(n_, std::memory_order_release);
@@ -492,3 +494,94 @@ extern "C" jf_status_t jf_cpu_topk_attn(const void* q, const void* k_shadow, con
   if (st != JF_OK) return st;
   return jf_pool_wait_timeout(30000);
 }
+
+// ---- stream-ordered submit / wait -----------------------------------------------------
+// The reference queues the host correction into the CUDA stream with cudaLaunchHostFunc
+// (jetfire_vllm/csrc/cpu_topk_attn.cpp:1268-1290, :2239-2312): one callback hands the job to
+// the worker pool when the stream reaches it (the selected slots are in host memory by then),
+// a later callback blocks the stream until the job is done, so the merge kernel that follows
+// sees o_new.  Callbacks run on a driver thread and call no CUDA API.  Both waits are
+// bounded; a wait that runs out is recorded in the context and reported by
+// jf_submit_ctx_status.
+namespace {
+
+struct SubmitCtx {
+  Job job;
+  std::atomic<int32_t> error{JF_OK};
+  int32_t wait_ms = 30000;
+  alignas(64) int64_t own_flag = 0;   // completion flag when the caller gave none
+};
+
+void CUDART_CB submit_callback(void* ud) {
+  auto* c = static_cast<SubmitCtx*>(ud);
+  ensure_pool();
+  // single job in flight: an earlier layer's job may still be running
+  reinterpret_cast<std::atomic<int64_t>*>(c->job.done_flag)->store(0, std::memory_order_release);
+  // another stream's callback may take the pool first: try again until this job is in
+  const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(c->wait_ms);
+  for (;;) {
+    if (!pool().wait(c->wait_ms)) { c->error.store(JF_ERR_TIMEOUT); return; }
+    if (pool().submit(c->job)) return;
+    if (std::chrono::steady_clock::now() > t_end) { c->error.store(JF_ERR_TIMEOUT); return; }
+  }
+}
+
+// Waits for THIS context's job (its completion flag), not for an idle pool: the next layer's
+// job may already be running by the time this callback gets to look.
+void CUDART_CB wait_callback(void* ud) {
+  auto* c = static_cast<SubmitCtx*>(ud);
+  auto* flag = reinterpret_cast<std::atomic<int64_t>*>(c->job.done_flag);
+  const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(c->wait_ms);
+  for (int spin = 0;; ++spin) {
+    if (flag->load(std::memory_order_acquire) != 0) return;
+    if (c->error.load() != JF_OK) return;   // the submit never happened
+    if (spin < 20000) { _mm_pause(); continue; }
+    if (std::chrono::steady_clock::now() > t_end) { c->error.store(JF_ERR_TIMEOUT); return; }
+    std::this_thread::sleep_for(std::chrono::microseconds(20));
+  }
+}
+
+}  // namespace
+
+extern "C" jf_status_t jf_submit_ctx_create(const void* q, const void* k_shadow, const void* v_shadow,
+                                            const int64_t* head_map, const int64_t* ts_buf, void* o_new,
+                                            int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots,
+                                            int32_t K, float scale, int64_t* done_flag, int32_t wait_ms,
+                                            int64_t* handle) {
+  if (!handle) return JF_ERR_ARG;
+  auto* c = new SubmitCtx();
+  jf_status_t st = make_job(c->job, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                            scale, done_flag);
+  if (st != JF_OK) { delete c; return st; }
+  if (!done_flag) c->job.done_flag = &c->own_flag;
+  if (wait_ms > 0) c->wait_ms = wait_ms;
+  *handle = static_cast<int64_t>(reinterpret_cast<intptr_t>(c));
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_submit_ctx_destroy(int64_t handle) {
+  if (!handle) return JF_ERR_ARG;
+  delete reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle));
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_submit_ctx_status(int64_t handle) {
+  if (!handle) return JF_ERR_ARG;
+  return static_cast<jf_status_t>(reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle))->error.exchange(JF_OK));
+}
+
+extern "C" jf_status_t jf_stream_submit_cpu_topk_attn(jf_stream_t stream, int64_t handle) {
+  if (!handle) return JF_ERR_ARG;
+  ensure_pool();   // threads are started here, not inside the callback
+  const cudaError_t e = cudaLaunchHostFunc(static_cast<cudaStream_t>(stream), submit_callback,
+                                           reinterpret_cast<void*>(static_cast<intptr_t>(handle)));
+  return e == cudaSuccess ? JF_OK : JF_ERR_CUDA;
+}
+
+extern "C" jf_status_t jf_stream_wait_cpu_topk_attn(jf_stream_t stream, int64_t handle) {
+  if (!handle) return JF_ERR_ARG;
+  const cudaError_t e = cudaLaunchHostFunc(static_cast<cudaStream_t>(stream), wait_callback,
+                                           reinterpret_cast<void*>(static_cast<intptr_t>(handle)));
+  return e == cudaSuccess ? JF_OK : JF_ERR_CUDA;
+}
+

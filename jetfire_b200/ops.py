@@ -359,6 +359,37 @@ class HostCorrectionCall:
     def run(self) -> None:
         check("cpu_topk_attn", lib.jf_cpu_topk_attn(*self._args))
 
+    # -- stream-ordered form (the reference's create_cpu_topk_submit_ctx /
+    #    stream_submit_cpu_topk_attn / stream_wait_cpu_topk_attn, csrc/cpu_topk_attn.cpp:2147-2312) --
+    def _handle(self) -> int:
+        if getattr(self, "_ctx", None) is None:
+            h = C.c_int64(0)
+            check("create_cpu_topk_submit_ctx", lib.jf_submit_ctx_create(*self._args, 0, C.byref(h)))
+            self._ctx = h.value
+        return self._ctx
+
+    def stream_submit(self, stream=None) -> None:
+        """Queue the submit on ``stream`` (default: current): the job starts when the stream gets
+        there.  ``ts_buf`` and ``q`` must be in host memory by then (stream-ordered copies)."""
+        s = stream.cuda_stream if stream is not None else _stream()
+        check("stream_submit_cpu_topk_attn", lib.jf_stream_submit_cpu_topk_attn(s, self._handle()))
+
+    def stream_wait(self, stream=None) -> None:
+        """Queue a host wait on ``stream``: work queued after it runs once the job is done."""
+        s = stream.cuda_stream if stream is not None else _stream()
+        check("stream_wait_cpu_topk_attn", lib.jf_stream_wait_cpu_topk_attn(s, self._handle()))
+
+    def stream_status(self) -> None:
+        """Raises if a queued submit or wait ran out of time (call after synchronising)."""
+        if getattr(self, "_ctx", None) is not None:
+            check("cpu_topk_submit_ctx", lib.jf_submit_ctx_status(self._ctx))
+
+    def close(self) -> None:
+        """Free the native context; no stream operation or graph may refer to it any more."""
+        if getattr(self, "_ctx", None) is not None:
+            lib.jf_submit_ctx_destroy(self._ctx)
+            self._ctx = None
+
 
 def alloc_mapped_pinned_pair(shape, dtype):
     """``(host_tensor, device_tensor)`` over the same pinned, GPU-mapped bytes."""

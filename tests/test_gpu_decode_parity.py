@@ -185,3 +185,45 @@ def test_status_record_is_read_once_and_needs_no_initialisation():
     with pytest.raises(RuntimeError):
         call.status()
     call.status()                                                           # cleared by the read
+
+
+def test_stream_ordered_host_correction_matches_blocking_call():
+    """stream_submit / stream_wait (host callbacks in the CUDA stream) around the slot copy and
+    the merge give the blocking path's result, for several layers queued without host syncs."""
+    from jetfire_b200 import ops
+    case = Case("k3v2", 2, 8, 2, 1024, seed=71)
+    kd, ks, vd, vs = case.device_cache()
+    top_k, n_layers = 64, 4
+    g = torch.Generator().manual_seed(5)
+    qs = [torch.randn(case.B, case.H_q, 128, generator=g).to(case.dtype).pin_memory() for _ in range(n_layers)]
+    main, side = torch.cuda.current_stream(), torch.cuda.Stream()
+    layers = []
+    for q_host in qs:
+        q = q_host.cuda()
+        call = ops.DecodeCall(case.mode, q, kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+                              case.ctx, case.H_q, case.H_kv, 16, top_k, case.attn_scale)
+        slots_host = torch.empty(case.B, case.H_q, top_k, dtype=torch.int64).pin_memory()
+        o_new_host = torch.zeros(case.B, case.H_q, 128, dtype=case.dtype).pin_memory()
+        host = ops.HostCorrectionCall(q_host, case.k_full, case.v_full, None, slots_host, o_new_host, case.attn_scale)
+        layers.append((call, slots_host, o_new_host, host, torch.empty_like(q), torch.empty_like(q), torch.cuda.Event()))
+    ops.set_cpu_attn_threads(4)
+    for call, slots_host, o_new_host, host, o_new, out, ev in layers:      # everything queued, no host sync
+        call.fused()
+        slots_host.copy_(call.out["topk_slots"], non_blocking=True)
+        host.stream_submit(main)
+        ev.record(main)
+        side.wait_event(ev)
+        host.stream_wait(side)
+        with torch.cuda.stream(side):
+            o_new.copy_(o_new_host, non_blocking=True)
+            ops.blend_unnorm_into(call.out["o_hat"], call.out["o_old_unnorm"], call.out["W"], o_new, out)
+    torch.cuda.synchronize()
+    for call, slots_host, o_new_host, host, o_new, out, ev in layers:
+        host.stream_status()
+        want_new = torch.empty_like(o_new_host)
+        ops.cpu_topk_attn(host._keep[0], case.k_full, case.v_full, None, slots_host, want_new, case.attn_scale)
+        assert torch.equal(o_new_host, want_new)
+        want = torch.empty_like(out)
+        ops.blend_unnorm_into(call.out["o_hat"], call.out["o_old_unnorm"], call.out["W"], want_new.cuda(), want)
+        assert torch.equal(out, want)
+        host.close()
