@@ -328,7 +328,9 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     cores = os.cpu_count() or 1
-    cpu_threads = args.cpu_threads or max(1, cores // world)
+    # one core per rank stays with the thread that drives the GPU: with a worker on every core the
+    # driving thread is preempted and every layer waits for it (16 workers: 7.2 ms per step, 15: 5.5)
+    cpu_threads = args.cpu_threads or max(1, cores // world - 1)
     ops.set_cpu_attn_threads(cpu_threads)
 
     do_e2e = not args.no_e2e

@@ -418,8 +418,9 @@ Pool& pool() {
 }
 std::atomic<int> g_threads{0};
 
+// One hardware thread is left to the thread that submits jobs and drives the GPU.
 int default_threads() {
-  int n = static_cast<int>(std::thread::hardware_concurrency());
+  int n = static_cast<int>(std::thread::hardware_concurrency()) - 1;
   if (n <= 0) n = 1;
   return n > 64 ? 64 : n;
 }
