@@ -444,6 +444,8 @@ def main():
     # (token, KV head), scaled to this launch by the units it processes (traffic grows in
     # proportion); figures and commands: profiles/scan_k4v4_b4_ctx32k.md, scan_k3v2_b4_ctx32k.md
     roofline["traffic"] = DRAM_BYTES_PER_TOKEN_HEAD[w["mode"]] * w["batch"] * w["H_kv"] * w["ctx"]
+    # the same fraction for the whole layer (scan + select+finish + merge, from `value`)
+    roofline["layer_frac"] = value / world / peak
 
     # ---- end to end with the host in the loop ----
     e2e = None

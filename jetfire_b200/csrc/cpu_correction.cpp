@@ -236,6 +236,10 @@ JF_AVX512 void row_avx512(const Job& j, Scratch& sc, int64_t b, int64_t h) {
   float max_score = -INFINITY;
   for (int k = 0; k < K; ++k) {
     prefetch_row(j.ks, k + kAhead);
+    if (k + kAhead < K && slots[k + kAhead] >= 0) {   // V rows on their way to L2 for pass 2
+      const char* a = reinterpret_cast<const char*>(j.vs + slots[k + kAhead]);
+      for (int l = 0; l < 4; ++l) _mm_prefetch(a + 64 * l, _MM_HINT_T1);
+    }
     if (slots[k] < 0) { scores[k] = -INFINITY; continue; }
     const uint16_t* kr = j.ks + slots[k];
     __m512 acc = _mm512_setzero_ps();
