@@ -261,6 +261,21 @@ def fused_attn_topk(mode, q, k_data, k_scales, v_data, v_scales, block_table, se
     return call.result()
 
 
+def int2_fused_attn_topk(q, k_data, k_scales, k_zp, v_data, v_scales, block_table, seq_lens,
+                         max_S, H_q, H_kv, block_size, top_k, attn_scale):
+    """The reference's single-call op under its own name and argument order
+    (``kernels/int2_fused_attn_topk.py:5-10``, ``csrc/int2_fused_attn_topk.cu:404``):
+    ``(o_hat, topk_slots, o_old_unnorm, W)``.  The mode follows the packed row widths
+    (K 48 B / V 32 B: K3V2; 64 B / 64 B: K4V4); ``k_zp`` (asymmetric INT2 keys) must be None."""
+    _require(k_zp is None, "int2_fused_attn_topk: asymmetric keys (k_zp) are not supported")
+    widths = (int(k_data.shape[-1]), int(v_data.shape[-1]))
+    _require(widths in ((48, 32), (64, 64)), f"int2_fused_attn_topk: unsupported packed widths {widths}")
+    mode = "k3v2" if widths == (48, 32) else "k4v4"
+    r = fused_attn_topk(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
+                        max_S, H_q, H_kv, block_size, top_k, attn_scale)
+    return r.o_hat, r.topk_slots, r.o_old_unnorm, r.W
+
+
 # ---------------------------------------------------------------------------------------
 # correction merge
 # ---------------------------------------------------------------------------------------
@@ -287,6 +302,21 @@ def blend_unnorm_into(o_hat, o_old_unnorm, W, o_new, out) -> None:
 # ---------------------------------------------------------------------------------------
 # host correction
 # ---------------------------------------------------------------------------------------
+
+def wait_and_blend_unnorm_into(done_flag, o_hat, o_old_unnorm, W, o_new, out, timeout_s: float = 30.0) -> None:
+    """Spin on the host correction's completion flag, then launch the merge
+    (``csrc/blend.cu:320-376``; ``o_new`` is the device alias of mapped host memory, so no
+    copy is needed).  Unlike the reference the wait is bounded: ``RuntimeError`` after
+    ``timeout_s``."""
+    import time
+    _require(done_flag.dtype == torch.int64 and done_flag.numel() == 1 and not done_flag.is_cuda,
+             "wait_and_blend_unnorm_into: done_flag must be a 1-element int64 CPU tensor")
+    t_end = time.monotonic() + float(timeout_s)
+    while int(done_flag[0]) == 0:
+        if time.monotonic() > t_end:
+            raise RuntimeError("wait_and_blend_unnorm_into: the host correction did not finish in time")
+    blend_unnorm_into(o_hat, o_old_unnorm, W, o_new, out)
+
 
 def set_cpu_attn_threads(n: int) -> None:
     check("set_cpu_attn_threads", lib.jf_set_cpu_attn_threads(int(n)))

@@ -227,3 +227,33 @@ def test_stream_ordered_host_correction_matches_blocking_call():
         ops.blend_unnorm_into(call.out["o_hat"], call.out["o_old_unnorm"], call.out["W"], want_new.cuda(), want)
         assert torch.equal(out, want)
         host.close()
+
+
+def test_reference_named_ops_int2_fused_and_wait_and_blend():
+    """``int2_fused_attn_topk`` (reference name and argument order) and ``wait_and_blend_unnorm_into``
+    over a mapped o_new / completion flag give the plain calls' results."""
+    from jetfire_b200 import ops
+    case = Case("k4v4", 2, 8, 2, 1024, seed=81)
+    kd, ks, vd, vs = case.device_cache()
+    qd, bt, sl = case.q.cuda(), case.block_table.cuda(), case.seq_lens.cuda()
+    o_hat, slots, o_old, W = ops.int2_fused_attn_topk(qd, kd, ks, None, vd, vs, bt, sl, case.ctx, case.H_q, case.H_kv,
+                                                      16, 64, case.attn_scale)
+    ref = ops.fused_attn_topk("k4v4", qd, kd, ks, vd, vs, bt, sl, case.ctx, case.H_q, case.H_kv, 16, 64, case.attn_scale)
+    assert torch.equal(o_hat, ref.o_hat) and torch.equal(slots, ref.topk_slots)
+    assert torch.equal(o_old, ref.o_old_unnorm) and torch.equal(W, ref.W)
+    with pytest.raises(RuntimeError):
+        ops.int2_fused_attn_topk(qd, kd, ks, torch.zeros(1), vd, vs, bt, sl, case.ctx, case.H_q, case.H_kv, 16, 64,
+                                 case.attn_scale)
+    o_new_host, o_new_dev = ops.alloc_mapped_pinned_pair((case.B, case.H_q, 128), case.dtype)
+    flag = torch.zeros(1, dtype=torch.int64)
+    ops.set_cpu_attn_threads(3)
+    ops.cpu_topk_attn_submit(case.q, case.k_full, case.v_full, None, slots.cpu(), o_new_host, case.attn_scale, flag)
+    out = torch.empty(case.B, case.H_q, 128, dtype=case.dtype, device="cuda")
+    ops.wait_and_blend_unnorm_into(flag, o_hat, o_old, W, o_new_dev, out)
+    torch.cuda.synchronize()
+    want = torch.empty_like(out)
+    ops.blend_unnorm_into(o_hat, o_old, W, o_new_host.cuda(), want)
+    assert torch.equal(out, want)
+    never = torch.zeros(1, dtype=torch.int64)
+    with pytest.raises(RuntimeError):
+        ops.wait_and_blend_unnorm_into(never, o_hat, o_old, W, o_new_dev, out, timeout_s=0.05)
