@@ -157,7 +157,7 @@ class Layer:
     pass
 
 
-def build_stack(torch, ops, w, rank, device, dtype, with_mirror):
+def build_stack(torch, ops, w, rank, device, dtype, mirror_layers):
     kb, vb, gs = MODE_BITS[w["mode"]]
     ng = 128 // gs
     t = w["batch"] * w["ctx"]
@@ -177,6 +177,7 @@ def build_stack(torch, ops, w, rank, device, dtype, with_mirror):
         L.k_scales = torch.empty(w["H_kv"], t, ng, dtype=torch.bfloat16, device=device)
         L.v_scales = torch.empty(w["H_kv"], t, ng, dtype=torch.bfloat16, device=device)
         ops.fused_quant_write_kv(k, v, slots, L.k_data, L.k_scales, L.v_data, L.v_scales, gs, kb, vb)
+        with_mirror = li < mirror_layers
         if with_mirror:  # full-precision mirror in host DRAM, (H_kv, num_slots, 128)
             L.k_shadow = torch.empty(w["H_kv"], t, 128, dtype=dtype)
             L.v_shadow = torch.empty(w["H_kv"], t, 128, dtype=dtype)
@@ -334,7 +335,22 @@ def main():
     ops.set_cpu_attn_threads(cpu_threads)
 
     do_e2e = not args.no_e2e
-    layers = build_stack(torch, ops, w, rank, device, dtype, with_mirror=do_e2e)
+    # The end-to-end leg needs the full-precision mirror of every layer in host DRAM (17 GB per
+    # rank at the default workload).  If all ranks' mirrors would take more than 40 % of the free
+    # host memory, the leg runs over the first layers only (its throughput is per layer anyway).
+    mirror_layers = w["layers"] if do_e2e else 0
+    if do_e2e:
+        import psutil
+        per_layer = 2 * w["H_kv"] * w["batch"] * w["ctx"] * 128 * 2
+        need = per_layer * w["layers"] * world
+        budget = 0.4 * psutil.virtual_memory().available
+        if need > budget:
+            mirror_layers = max(2, min(w["layers"], int(w["layers"] * budget / need)))
+        if world > 1:   # rank 0 decides for everyone
+            ml = torch.tensor([mirror_layers], dtype=torch.int64, device=device)
+            dist.broadcast(ml, 0)
+            mirror_layers = int(ml.item())
+    layers = build_stack(torch, ops, w, rank, device, dtype, mirror_layers)
     n_layers = len(layers)
     step_bytes = layer_bytes(w) * n_layers
 
@@ -451,10 +467,11 @@ def main():
     e2e = None
     if do_e2e:
         copy_stream = torch.cuda.Stream()
+        e2e_layers = layers[:mirror_layers]
 
         def e2e_step():
             main_s = torch.cuda.current_stream()
-            for L in layers:
+            for L in e2e_layers:
                 L.q.copy_(L.q_host, non_blocking=True)
                 L.call.fused()
                 L.slots_host.copy_(L.call.out["topk_slots"], non_blocking=True)
@@ -468,7 +485,7 @@ def main():
                     L.out_host.copy_(L.out, non_blocking=True)
 
             prev = None
-            for L in layers:
+            for L in e2e_layers:
                 L.event.synchronize()
                 L.host_call.submit()          # the worker pool takes the layer's correction ...
                 if prev is not None:
@@ -494,12 +511,19 @@ def main():
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         dt = float(tt.item())
         esz = 2
-        h2d = n_layers * 2 * w["batch"] * w["H_q"] * 128 * esz
-        d2h = n_layers * (w["batch"] * w["H_q"] * w["top_k"] * 8 + w["batch"] * w["H_q"] * 128 * esz)
-        e2e = {"value": step_bytes * world / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
-               "d2h_bytes_per_step": d2h * world, "ms_per_step": dt * 1e3, "steps": e2e_steps,
-               "tokens_per_s": w["batch"] * world / dt, "host_threads_per_rank": cpu_threads,
+        n_e2e = len(e2e_layers)
+        h2d = n_e2e * 2 * w["batch"] * w["H_q"] * 128 * esz
+        d2h = n_e2e * (w["batch"] * w["H_q"] * w["top_k"] * 8 + w["batch"] * w["H_q"] * 128 * esz)
+        # dt covers n_e2e layers; ms_per_step and tokens/s are scaled to the workload's layer count
+        dt_full = dt * n_layers / n_e2e
+        e2e = {"value": layer_bytes(w) * n_e2e * world / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": d2h * world, "ms_per_step": dt_full * 1e3, "steps": e2e_steps,
+               "layers_measured": n_e2e,
+               "tokens_per_s": w["batch"] * world / dt_full, "host_threads_per_rank": cpu_threads,
                "timing": "host wall clock around barrier + synchronize (host work is inside the region)"}
+        if n_e2e < n_layers:
+            e2e["note"] = (f"host memory: mirrors of {n_e2e} of {n_layers} layers; the copies above are per measured "
+                           "step, ms_per_step and tokens_per_s are scaled to all layers")
         for L in layers:
             L.call.status()
 
