@@ -50,6 +50,14 @@ def test_rows_longer_than_one_chunk(mode, B, H_q, H_kv, ctx, lens, top_k, seed):
     _run(Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed), top_k)
 
 
+@pytest.mark.parametrize("mode,top_k,ctx", [("k4v4", 1024, 8192), ("k3v2", 2048, 8192), ("k3v2", 1024, 2000)])
+def test_wide_top_k(mode, top_k, ctx):
+    """top-k above 512: the sort buffer no longer fits the counting / bucket ranking (bitonic
+    path), the finish stage gathers its own rows; ctx 2000 < 2 * top_k takes the
+    every-position-is-a-candidate path."""
+    _run(Case(mode, 2, 8, 2, ctx, lens=[ctx, ctx - 37], seed=57 + top_k), top_k)
+
+
 def test_bench_geometry_full_size_k4v4():
     """BASELINE configs[1] for one layer: B 4, 32 query / 8 KV heads, ctx 32768, top-k 256."""
     res, _ = _run(Case("k4v4", 4, 32, 8, 32768, lens=[32768] * 4, seed=55), 256)
