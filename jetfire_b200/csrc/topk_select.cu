@@ -268,42 +268,20 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     mbar_init(&sm.bar, 1);
     fence_barrier_init();
   }
-  pdl_wait();  // nothing above reads global memory
-
-  // ---- small loads first (they are what the prologue waits for), then the 128 KB copy ----
+  // In the fused call this kernel directly follows the scan, and what the scan itself read (the
+  // query, the sequence lengths) was complete before the scan started: the query model and the
+  // zeroing below need nothing of the scan's output and run while the scan's last CTAs finish.
+  // The stand-alone select may follow any kernel, so there the wait comes first.
+  if (!FUSED) pdl_wait();
   uint16_t q_bits = 0;
   if (tid < JF_HEAD_DIM) q_bits = reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid];
-  float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
-  if (tid < p.splits) {  // the first split of this thread; the loop below takes the rest
-    top = p.part_m[(pbase + tid) * kHeadsPad + hi];
-    sm0 = p.part_smax[(pbase + tid) * 2];
-    sm1 = p.part_smax[(pbase + tid) * 2 + 1];
-  }
   const int n_seq_raw = p.seq_lens[b];
-  SplitPre pre;
-  if (FUSED) split_preload(tp, pbase, hi, tid, pre);
-  issue_chunk(0);
-
   const int n_seq = min(n_seq_raw, p.max_S);
   int64_t* out_idx = p.topk_idx + bh * K;
   int64_t* out_slot = p.topk_slots + bh * K;
 
-  // ---- query row (exact values), per-group L1 norms, INT8 model for K4; split statistics ----
+  // ---- query row (exact values), per-group L1 norms, INT8 model for K4 ----
   if (tid < JF_HEAD_DIM) sm.q[tid] = Elem<DT>::to_f32(q_bits);
-  {
-    for (int s = tid + kSelThreads; s < p.splits; s += kSelThreads) {
-      top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
-      sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
-      sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
-      sm0 = fmaxf(sm0, __shfl_xor_sync(0xFFFFFFFFu, sm0, o));
-      sm1 = fmaxf(sm1, __shfl_xor_sync(0xFFFFFFFFu, sm1, o));
-    }
-    if (lane == 0) { sm.w3[warp][0] = top; sm.w3[warp][1] = sm0; sm.w3[warp][2] = sm1; }
-  }
   __syncthreads();
   JF_PHASE(11);
   if (warp < 4) {  // warp w handles channels 32w..32w+31
@@ -326,6 +304,32 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
   for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
   for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+
+  // ---- the scan's results: split statistics first (small), then the 128 KB score chunk ----
+  if (FUSED) pdl_wait();
+  float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
+  if (tid < p.splits) {  // the first split of this thread; the loop below takes the rest
+    top = p.part_m[(pbase + tid) * kHeadsPad + hi];
+    sm0 = p.part_smax[(pbase + tid) * 2];
+    sm1 = p.part_smax[(pbase + tid) * 2 + 1];
+  }
+  SplitPre pre;
+  if (FUSED) split_preload(tp, pbase, hi, tid, pre);
+  issue_chunk(0);
+  {
+    for (int s = tid + kSelThreads; s < p.splits; s += kSelThreads) {
+      top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
+      sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
+      sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
+      sm0 = fmaxf(sm0, __shfl_xor_sync(0xFFFFFFFFu, sm0, o));
+      sm1 = fmaxf(sm1, __shfl_xor_sync(0xFFFFFFFFu, sm1, o));
+    }
+    if (lane == 0) { sm.w3[warp][0] = top; sm.w3[warp][1] = sm0; sm.w3[warp][2] = sm1; }
+  }
   __syncthreads();
   JF_PHASE(1);
 
