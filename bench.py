@@ -4,8 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Workload (``config.workload``): one decode step = one pass of the hot path over every layer
-of a stack with independent, seeded synthetic KV per layer.  Default = the second entry of
-BASELINE.json's ``configs``: Llama-3.1-8B layer geometry (32 query heads, 8 KV heads,
+of a stack with independent, seeded synthetic KV per layer.  Default = the configuration the headline
+metric is quoted on: Llama-3.1-8B layer geometry (32 query heads, 8 KV heads,
 head_dim 128), mode K4V4 (group 128), batch 4, context 32768, top-k 256, 32 layers.
 Other workloads: ``--workload c1|c3|c4`` or explicit ``--mode/--batch/--ctx/--layers/...``.
 
@@ -48,7 +48,7 @@ WORKLOADS = {
 }
 BYTES_PER_TOKEN_HEAD = {"k3v2": 88, "k4v4": 132}
 MODE_BITS = {"k3v2": (3, 2, 64), "k4v4": (4, 4, 128)}
-DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 91.4, "k4v4": 137.5}   # measured with ncu, see profiles/
+DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 91.4, "k4v4": 137.5}   # dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture
 
 
 def parse_args():
@@ -458,7 +458,7 @@ def main():
                 "algorithmic_bytes_per_launch": layer_bytes(w), "traffic": None}
     # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the scan kernel, per
     # (token, KV head), scaled to this launch by the units it processes (traffic grows in
-    # proportion); figures and commands: profiles/scan_k4v4_b4_ctx32k.md, scan_k3v2_b4_ctx32k.md
+    # proportion)
     roofline["traffic"] = DRAM_BYTES_PER_TOKEN_HEAD[w["mode"]] * w["batch"] * w["H_kv"] * w["ctx"]
     # the same fraction for the whole layer (scan + select+finish + merge, from `value`)
     roofline["layer_frac"] = value / world / peak

@@ -59,7 +59,7 @@ def test_wide_top_k(mode, top_k, ctx):
 
 
 def test_bench_geometry_full_size_k4v4():
-    """BASELINE configs[1] for one layer: B 4, 32 query / 8 KV heads, ctx 32768, top-k 256."""
+    """One layer of the headline bench workload at full size: K4V4, B 4, 32 query / 8 KV heads, ctx 32768, top-k 256."""
     res, _ = _run(Case("k4v4", 4, 32, 8, 32768, lens=[32768] * 4, seed=55), 256)
     idx = res.topk_idx.cpu().numpy()
     assert (idx >= 0).all() and (idx < 32768).all()
@@ -67,5 +67,5 @@ def test_bench_geometry_full_size_k4v4():
 
 
 def test_config1_geometry_full_size_k3v2():
-    """BASELINE configs[0]: B 1, 32 query / 8 KV heads, ctx 32768, K3V2, top-k 256."""
+    """The single-sequence configuration at full size: K3V2, B 1, 32 query / 8 KV heads, ctx 32768, top-k 256."""
     _run(Case("k3v2", 1, 32, 8, 32768, lens=[32768], seed=56), 256)
