@@ -484,15 +484,18 @@ def main():
                                           L.o_new, L.out)
                     L.out_host.copy_(L.out, non_blocking=True)
 
+            # The next layer's correction is queued before the previous one is waited for, so the
+            # workers flow from one job into the next; merges are launched as jobs complete.
             prev = None
             for L in e2e_layers:
                 L.event.synchronize()
-                L.host_call.submit()          # the worker pool takes the layer's correction ...
+                ticket = L.host_call.submit()
                 if prev is not None:
-                    merge(prev)               # ... while this thread launches the previous layer's merge
-                L.host_call.wait()
-                prev = L
-            merge(prev)
+                    L.host_call.wait_ticket(prev[1])
+                    merge(prev[0])
+                prev = (L, ticket)
+            prev[0].host_call.wait_ticket(prev[1])
+            merge(prev[0])
             copy_stream.synchronize()
             if world > 1:
                 dist.all_gather_into_tensor(gathered, my_out)

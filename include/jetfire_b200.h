@@ -195,13 +195,22 @@ jf_status_t jf_set_cpu_attn_threads(int32_t n);
 int32_t     jf_get_cpu_attn_threads(void);
 
 /* Asynchronous form: submit returns at once, wait blocks up to timeout_ms
- * (JF_ERR_TIMEOUT if the job is still running; it can be waited on again). */
+ * (JF_ERR_TIMEOUT if jobs are still running; it can be waited on again).  Up to four jobs
+ * can be queued (JF_ERR_STATE when the queue is full); workers move from one job to the
+ * next without idling.  jf_pool_wait_timeout waits for every queued job, jf_pool_wait_ticket
+ * for one.  Jobs that share a done_flag must not be queued together. */
 jf_status_t jf_pool_init(int32_t n_threads);
 jf_status_t jf_pool_submit(const void* q, const void* k_shadow, const void* v_shadow,
                            const int64_t* head_map, const int64_t* ts_buf, void* o_new,
                            int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
                            int64_t num_slots, int32_t K, float scale, int64_t* done_flag);
+jf_status_t jf_pool_submit_ticket(const void* q, const void* k_shadow, const void* v_shadow,
+                                  const int64_t* head_map, const int64_t* ts_buf, void* o_new,
+                                  int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                  int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
+                                  int64_t* ticket);
 jf_status_t jf_pool_wait_timeout(int32_t timeout_ms);
+jf_status_t jf_pool_wait_ticket(int64_t ticket, int32_t timeout_ms);
 jf_status_t jf_pool_shutdown(void);
 
 /* Stream-ordered form (create_cpu_topk_submit_ctx / stream_submit_cpu_topk_attn /

@@ -70,7 +70,10 @@ _SIGS = {
     "jf_pool_init": (C.c_int32, [C.c_int32]),
     "jf_pool_submit": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                      C.c_void_p]),
+    "jf_pool_submit_ticket": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
+                                                                            C.c_void_p, C.POINTER(C.c_int64)]),
     "jf_pool_wait_timeout": (C.c_int32, [C.c_int32]),
+    "jf_pool_wait_ticket": (C.c_int32, [C.c_int64, C.c_int32]),
     "jf_submit_ctx_create": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                            C.c_void_p, C.c_int32,
                                                                            C.POINTER(C.c_int64)]),

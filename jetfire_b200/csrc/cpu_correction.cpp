@@ -299,27 +299,29 @@ bool have_avx512bf16() {
   return v;
 }
 
-// Rows are claimed one at a time from a shared counter, so a worker that loses its core
-// for a while does not hold up the rest of the job.
-void run_rows(const Job& j, std::atomic<int64_t>& next_row, Scratch& sc) {
-  const int64_t total = static_cast<int64_t>(j.B) * j.H_q;
-  sc.scores.resize(static_cast<size_t>(j.K) + 16);
-  sc.slots.resize(j.K);
+// One row of the job (rows are claimed one at a time from the job's counter, so a worker that
+// loses its core for a while does not hold up the rest).
+void run_row(const Job& j, int64_t i, Scratch& sc) {
+  if (sc.scores.size() < static_cast<size_t>(j.K) + 16) sc.scores.resize(static_cast<size_t>(j.K) + 16);
+  if (sc.slots.size() < static_cast<size_t>(j.K)) sc.slots.resize(j.K);
   const bool simd = have_avx512bf16();
-  if (!simd) sc.vrows.resize(static_cast<size_t>(j.K) * D);
-  for (;;) {
-    const int64_t i = next_row.fetch_add(1, std::memory_order_relaxed);
-    if (i >= total) break;
-    const int64_t b = i / j.H_q, h = i % j.H_q;
-    if (!simd) row_generic(j, sc, b, h);
-    else if (j.dtype == JF_DTYPE_BF16) row_avx512<JF_DTYPE_BF16>(j, sc, b, h);
-    else row_avx512<JF_DTYPE_FP16>(j, sc, b, h);
-  }
+  if (!simd && sc.vrows.size() < static_cast<size_t>(j.K) * D) sc.vrows.resize(static_cast<size_t>(j.K) * D);
+  const int64_t b = i / j.H_q, h = i % j.H_q;
+  if (!simd) row_generic(j, sc, b, h);
+  else if (j.dtype == JF_DTYPE_BF16) row_avx512<JF_DTYPE_BF16>(j, sc, b, h);
+  else row_avx512<JF_DTYPE_FP16>(j, sc, b, h);
 }
 
-// ---- worker pool: one job in flight ----------------------------------------------------
+// ---- worker pool: a short queue of jobs ------------------------------------------------
+// Up to kQueue jobs can be submitted ahead.  A worker that finds no rows left in a job moves
+// on to the next one at once, without waiting for the others, so the workers stay busy across
+// job boundaries (with one job at a time every job ended with a tail of idle workers and began
+// with a wake-up).  A job is complete when its last row is; its slot is reused when, in
+// addition, every worker has left it.
 class Pool {
  public:
+  static constexpr int kQueue = 4;
+
   ~Pool() { shutdown(); }
   int size() const { return n_; }
   bool running() const { return n_ > 0; }
@@ -329,9 +331,10 @@ class Pool {
     std::lock_guard<std::mutex> g(api_);
     n_ = n;
     stop_ = false;
-    gen_.store(0);
-    pending_.store(0);
-    for (int i = 0; i < n; ++i) workers_.emplace_back([this, i] { loop(i); });
+    submitted_.store(0);
+    completed_.store(0);
+    for (auto& sl : slots_) { sl.left.store(n); sl.done_id.store(0); }   // "everyone has left": free
+    for (int i = 0; i < n; ++i) workers_.emplace_back([this] { loop(); });
   }
   void shutdown() {
     std::lock_guard<std::mutex> g(api_);
@@ -339,79 +342,120 @@ class Pool {
     {
       std::lock_guard<std::mutex> l(m_);
       stop_ = true;
-      gen_.fetch_add(1);
     }
     cv_.notify_all();
     for (auto& t : workers_) t.join();
     workers_.clear();
     n_ = 0;
   }
-  // false if a job is still in flight
-  bool submit(const Job& j) {
-    {
-      std::lock_guard<std::mutex> l(m_);
-      if (pending_.load(std::memory_order_acquire) != 0) return false;   // checked under the lock: submitters may race
-      job_ = j;
-      next_row_.store(0, std::memory_order_relaxed);
-      pending_.store(n_, std::memory_order_release);
-      gen_.fetch_add(1, std::memory_order_release);
+  // Queues the job; false if the queue is full (its oldest slot is still in use).  `ticket`
+  // identifies the job for wait_ticket.
+  bool submit(const Job& j, uint64_t* ticket = nullptr) {
+    const auto t_end = std::chrono::steady_clock::now() + std::chrono::seconds(2);
+    for (;;) {
+      std::unique_lock<std::mutex> l(m_);
+      const uint64_t id = submitted_.load(std::memory_order_relaxed);
+      Slot& sl = slots_[id % kQueue];
+      if (id >= kQueue && sl.done_id.load(std::memory_order_acquire) != id - kQueue + 1) return false;  // queue full
+      if (sl.left.load(std::memory_order_acquire) != n_) {
+        // the slot's job is complete but a worker that lost its core has not stepped past it yet
+        l.unlock();
+        if (std::chrono::steady_clock::now() > t_end) return false;
+        std::this_thread::yield();
+        continue;
+      }
+      sl.job = j;
+      sl.total = static_cast<int64_t>(j.B) * j.H_q;
+      sl.next_row.store(0, std::memory_order_relaxed);
+      sl.rows_done.store(0, std::memory_order_relaxed);
+      sl.left.store(0, std::memory_order_relaxed);
+      submitted_.store(id + 1, std::memory_order_release);
+      if (ticket) *ticket = id;
+      break;
     }
     cv_.notify_all();
     return true;
   }
-  // true when no job is in flight within the timeout
+  // true when every submitted job is complete within the timeout
   bool wait(int timeout_ms) {
-    const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
-    for (int spin = 0; spin < 20000; ++spin) {
-      if (pending_.load(std::memory_order_acquire) == 0) return true;
-      _mm_pause();
-    }
-    std::unique_lock<std::mutex> l(m_);
-    return done_cv_.wait_until(l, t_end, [this] { return pending_.load(std::memory_order_acquire) == 0; });
+    return wait_until([this] { return completed_.load(std::memory_order_acquire) == submitted_.load(std::memory_order_acquire); },
+                      timeout_ms);
+  }
+  // true when job `ticket` is complete within the timeout
+  bool wait_ticket(uint64_t ticket, int timeout_ms) {
+    Slot& sl = slots_[ticket % kQueue];
+    return wait_until([&sl, ticket] { return sl.done_id.load(std::memory_order_acquire) >= ticket + 1; }, timeout_ms);
   }
 
  private:
-  void loop(int /*wid*/) {
+  struct Slot {
+    Job job{};
+    int64_t total = 0;
+    alignas(64) std::atomic<int64_t> next_row{0};
+    alignas(64) std::atomic<int64_t> rows_done{0};
+    std::atomic<int> left{0};          // workers that have finished with this job
+    std::atomic<uint64_t> done_id{0};  // id + 1 of the last job completed in this slot
+  };
+
+  template <typename Pred>
+  bool wait_until(Pred done, int timeout_ms) {
+    const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    for (int spin = 0; spin < 20000; ++spin) {
+      if (done()) return true;
+      _mm_pause();
+    }
+    std::unique_lock<std::mutex> l(m_);
+    return done_cv_.wait_until(l, t_end, done);
+  }
+
+  void loop() {
     Scratch sc;
-    uint64_t seen = 0;
+    uint64_t my = 0;   // the next job this worker takes part in
     for (;;) {
-      // short spin for back-to-back layers, then park
+      // short spin for back-to-back jobs, then park
       bool got = false;
       for (int spin = 0; spin < 4000; ++spin) {
-        if (gen_.load(std::memory_order_acquire) != seen) { got = true; break; }
+        if (submitted_.load(std::memory_order_acquire) > my) { got = true; break; }
         _mm_pause();
       }
       if (!got) {
         std::unique_lock<std::mutex> l(m_);
-        cv_.wait(l, [&] { return gen_.load(std::memory_order_acquire) != seen; });
+        cv_.wait(l, [&] { return stop_ || submitted_.load(std::memory_order_acquire) > my; });
       }
-      Job j;
-      {
+      if (submitted_.load(std::memory_order_acquire) <= my) {   // woken to stop, and nothing left to do
         std::lock_guard<std::mutex> l(m_);
-        seen = gen_.load(std::memory_order_acquire);
         if (stop_) return;
-        j = job_;
+        continue;
       }
-      run_rows(j, next_row_, sc);
-      _mm_sfence();  // results may sit in write-combined mapped memory
-      if (pending_.fetch_sub(1, std::memory_order_acq_rel) == 1) {
-        if (j.done_flag) {
-          reinterpret_cast<std::atomic<int64_t>*>(j.done_flag)->store(1, std::memory_order_release);
-          _mm_sfence();
+      Slot& sl = slots_[my % kQueue];
+      const Job j = sl.job;
+      const int64_t total = sl.total;
+      for (;;) {
+        const int64_t i = sl.next_row.fetch_add(1, std::memory_order_relaxed);
+        if (i >= total) break;
+        run_row(j, i, sc);
+        _mm_sfence();  // results may sit in write-combined mapped memory
+        if (sl.rows_done.fetch_add(1, std::memory_order_acq_rel) + 1 == total) {   // the job's last row
+          if (j.done_flag) {
+            reinterpret_cast<std::atomic<int64_t>*>(j.done_flag)->store(1, std::memory_order_release);
+            _mm_sfence();
+          }
+          sl.done_id.store(my + 1, std::memory_order_release);
+          completed_.fetch_add(1, std::memory_order_acq_rel);
+          std::lock_guard<std::mutex> l(m_);
+          done_cv_.notify_all();
         }
-        std::lock_guard<std::mutex> l(m_);
-        done_cv_.notify_all();
       }
+      sl.left.fetch_add(1, std::memory_order_acq_rel);
+      ++my;
     }
   }
 
   std::mutex api_, m_;
   std::condition_variable cv_, done_cv_;
   std::vector<std::thread> workers_;
-  Job job_{};
-  std::atomic<uint64_t> gen_{0};
-  std::atomic<int> pending_{0};
-  alignas(64) std::atomic<int64_t> next_row_{0};
+  Slot slots_[kQueue];
+  std::atomic<uint64_t> submitted_{0}, completed_{0};
   bool stop_ = false;
   int n_ = 0;
 };
@@ -446,6 +490,26 @@ void ensure_pool() {
   if (!pool().running() || pool().size() != want) pool().start(want);
 }
 
+// The pool with the configured worker count; a change of the count waits for queued jobs first.
+jf_status_t ready_pool() {
+  int want = g_threads.load();
+  if (want <= 0) want = default_threads();
+  if (pool().running() && pool().size() == want) return JF_OK;
+  if (pool().running() && !pool().wait(30000)) return JF_ERR_TIMEOUT;
+  ensure_pool();
+  return JF_OK;
+}
+
+jf_status_t submit_job(const Job& j, int64_t* ticket) {
+  jf_status_t st = ready_pool();
+  if (st != JF_OK) return st;
+  if (j.done_flag) reinterpret_cast<std::atomic<int64_t>*>(j.done_flag)->store(0, std::memory_order_release);
+  uint64_t t = 0;
+  if (!pool().submit(j, &t)) return JF_ERR_STATE;   // queue full
+  if (ticket) *ticket = static_cast<int64_t>(t);
+  return JF_OK;
+}
+
 }  // namespace
 
 extern "C" jf_status_t jf_set_cpu_attn_threads(int32_t n) {
@@ -473,10 +537,25 @@ extern "C" jf_status_t jf_pool_submit(const void* q, const void* k_shadow, const
   jf_status_t st = make_job(j, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
                             scale, done_flag);
   if (st != JF_OK) return st;
-  if (pool().running() && !pool().wait(0)) return JF_ERR_STATE;  // single job in flight
-  ensure_pool();
-  if (done_flag) reinterpret_cast<std::atomic<int64_t>*>(done_flag)->store(0, std::memory_order_release);
-  return pool().submit(j) ? JF_OK : JF_ERR_STATE;
+  return submit_job(j, nullptr);
+}
+
+extern "C" jf_status_t jf_pool_submit_ticket(const void* q, const void* k_shadow, const void* v_shadow,
+                                             const int64_t* head_map, const int64_t* ts_buf, void* o_new,
+                                             int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots,
+                                             int32_t K, float scale, int64_t* done_flag, int64_t* ticket) {
+  if (!ticket) return JF_ERR_ARG;
+  Job j;
+  jf_status_t st = make_job(j, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                            scale, done_flag);
+  if (st != JF_OK) return st;
+  return submit_job(j, ticket);
+}
+
+extern "C" jf_status_t jf_pool_wait_ticket(int64_t ticket, int32_t timeout_ms) {
+  if (ticket < 0) return JF_ERR_ARG;
+  if (!pool().running()) return JF_ERR_STATE;
+  return pool().wait_ticket(static_cast<uint64_t>(ticket), timeout_ms < 0 ? 0 : timeout_ms) ? JF_OK : JF_ERR_TIMEOUT;
 }
 
 extern "C" jf_status_t jf_pool_wait_timeout(int32_t timeout_ms) {
@@ -522,12 +601,11 @@ void CUDART_CB submit_callback(void* ud) {
   ensure_pool();
   // single job in flight: an earlier layer's job may still be running
   reinterpret_cast<std::atomic<int64_t>*>(c->job.done_flag)->store(0, std::memory_order_release);
-  // another stream's callback may take the pool first: try again until this job is in
+  // the queue may be full: wait for it to drain and try again, within the budget
   const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(c->wait_ms);
   for (;;) {
-    if (!pool().wait(c->wait_ms)) { c->error.store(JF_ERR_TIMEOUT); return; }
     if (pool().submit(c->job)) return;
-    if (std::chrono::steady_clock::now() > t_end) { c->error.store(JF_ERR_TIMEOUT); return; }
+    if (!pool().wait(c->wait_ms) || std::chrono::steady_clock::now() > t_end) { c->error.store(JF_ERR_TIMEOUT); return; }
   }
 }
 

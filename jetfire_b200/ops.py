@@ -379,8 +379,15 @@ class HostCorrectionCall:
                                 "HostCorrectionCall")
         self._keep = (q, k_shadow, v_shadow, head_map, ts_buf, o_new, done_flag)
 
-    def submit(self) -> None:
-        check("cpu_topk_attn_submit", lib.jf_pool_submit(*self._args))
+    def submit(self) -> int:
+        """Queue the job (up to four can wait in the pool); returns its ticket for ``wait_ticket``."""
+        t = C.c_int64(0)
+        check("cpu_topk_attn_submit", lib.jf_pool_submit_ticket(*self._args, C.byref(t)))
+        return t.value
+
+    @staticmethod
+    def wait_ticket(ticket: int, timeout_ms: int = 30000) -> None:
+        check("cpu_topk_attn_wait", lib.jf_pool_wait_ticket(int(ticket), int(timeout_ms)))
 
     @staticmethod
     def wait(timeout_ms: int = 30000) -> None:

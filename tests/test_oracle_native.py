@@ -100,3 +100,34 @@ def test_prebuilt_host_call_equals_plain_call():
     out.zero_()
     call.run()
     assert torch.equal(out, want)
+
+
+def test_queued_jobs_complete_in_any_interleaving():
+    """Several jobs queued ahead (workers flow from one job into the next); every ticket can be
+    waited on, results equal the blocking call's, a fifth job is refused while four are queued
+    or running, and changing the worker count between batches works."""
+    from jetfire_b200 import ops, _lib
+    case, _ = _correction_inputs()
+    g = torch.Generator().manual_seed(11)
+    for threads in (3, 5, 2):
+        ops.set_cpu_attn_threads(threads)
+        jobs = []
+        for i in range(12):
+            slots = torch.randint(0, case.num_slots, (2, 8, 64), generator=g, dtype=torch.int64)
+            q = torch.randn(2, 8, 128, generator=g).to(torch.bfloat16)
+            want = torch.empty(2, 8, 128, dtype=torch.bfloat16)
+            ops.cpu_topk_attn(q, case.k_full, case.v_full, None, slots, want, case.attn_scale)
+            out = torch.zeros_like(want)
+            jobs.append((ops.HostCorrectionCall(q, case.k_full, case.v_full, None, slots, out, case.attn_scale), out, want))
+        tickets = []
+        for call, out, want in jobs:
+            while True:
+                try:
+                    tickets.append(call.submit())
+                    break
+                except RuntimeError:           # queue full: wait for the oldest outstanding job
+                    ops.HostCorrectionCall.wait_ticket(tickets[len(tickets) - 4])
+        for t, (call, out, want) in zip(tickets, jobs):
+            ops.HostCorrectionCall.wait_ticket(t)
+            assert torch.equal(out, want)
+        assert _lib.lib.jf_pool_wait_timeout(0) == 0
