@@ -277,8 +277,8 @@ scan_k3v2_kernel(const ScanParams p) {
       mbar_expect_tx_u32(bar, T::kBytes);
       bulk_g2s_u32_hint(dst + T::kKOff, kd_h + blk * (16 * T::kKRow), 16 * T::kKRow, bar, stream_policy);
       bulk_g2s_u32_hint(dst + T::kVOff, vd_h + blk * (16 * T::kVRow), 16 * T::kVRow, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T::kKsOff, ks_h + blk * (32 * T::kNG), 32 * T::kNG, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T::kVsOff, vs_h + blk * (32 * T::kNG), 32 * T::kNG, bar, stream_policy);
+      bulk_g2s_u32(dst + T::kKsOff, ks_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
+      bulk_g2s_u32(dst + T::kVsOff, vs_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
     }
   };
 

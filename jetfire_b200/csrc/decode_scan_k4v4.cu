@@ -360,8 +360,8 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       const int y = static_cast<int>(row_base + blk * 16);
       tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, y, bar, stream_policy);
       tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, y, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T4::kKsOff, ks_h + blk * 16, 32, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T4::kVsOff, vs_h + blk * 16, 32, bar, stream_policy);
+      bulk_g2s_u32(dst + T4::kKsOff, ks_h + blk * 16, 32, bar);
+      bulk_g2s_u32(dst + T4::kVsOff, vs_h + blk * 16, 32, bar);
     }
   };
 
