@@ -534,6 +534,17 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_baseline = run_cpu_baseline(w, args.dtype)
 
+    # clocks of every rank's GPU during the timed region: the slowest one decides the step
+    clocks = sampler.summary()
+    if world > 1:
+        every_clock = [None] * world
+        dist.all_gather_object(every_clock, clocks)
+        known = [c["sm_mhz"] for c in every_clock if c["sm_mhz"] is not None]
+        clocks = {"sm_mhz": min(known) if known else None, "sm_max_mhz": clocks["sm_max_mhz"],
+                  "reasons": sorted({r for c in every_clock for r in c["reasons"]}),
+                  "samples": min(c["samples"] for c in every_clock),
+                  "per_rank_sm_mhz": [c["sm_mhz"] for c in every_clock],
+                  "per_rank_reasons": [c["reasons"] for c in every_clock]}
     if rank == 0:
         line = {
             "metric": "decode_attn_packed_kv_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -549,7 +560,7 @@ def main():
             "us_per_layer": ms_step * 1e3 / n_layers,
             "gpu_launches": 3 * n_layers * args.steps,  # per layer: scan, select+finish, merge
             "per_rank_ms_without_gather": per_rank_ms,
-            "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": sampler.summary(),
+            "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -84,6 +84,53 @@ jf_status_t jf_pack_append_kv(const void* key_tok, const void* value_tok, int32_
                               int32_t group_size, jf_stream_t stream);
 
 /* ---------------------------------------------------------------------------------
+ * Appending to the host mirror.
+ *
+ * The reference keeps every appended K/V row in full precision in host memory
+ * (k_shadow / v_shadow (H_kv, num_slots, 128) 16-bit, jetfire_vllm/adapter/
+ * cache_store.py:311-323) and fills it per append with a device-to-host copy, a host
+ * synchronisation and an index_copy_ (:746-756), or under CUDA graphs with pinned staging
+ * and a host callback (:616-640; create_shadow_append_submit_ctx and
+ * stream_submit_shadow_append, jetfire_vllm/csrc/cpu_topk_attn.cpp:1611-1665, bindings
+ * :2509-2663).  Two replacements, both ordered by the stream alone:
+ *
+ * jf_pack_append_kv_mirror: the packing kernel also stores each live row's 256 raw bytes to
+ *   k_mirror / v_mirror, DEVICE-VISIBLE pointers to the mirrors (mapped pinned host memory
+ *   from jf_alloc_mapped, or an existing allocation made visible with jf_map_host; device
+ *   memory works too).  The mirror's element type is the tokens' (rows are copied bit for
+ *   bit).  Rows are in host memory when the stream reaches the point after the launch.
+ *
+ * jf_stream_mirror_append: for mirrors in ordinary host memory.  A context owns mapped
+ *   pinned staging for max_tokens tokens; the call enqueues, per chunk of max_tokens, one
+ *   kernel that writes rows, slots and count into the staging and one host callback that
+ *   scatters them into the mirror.  Negative or out-of-range slots are skipped.  The
+ *   context must outlive the stream work that uses it (synchronise before destroying).
+ * ------------------------------------------------------------------------------- */
+jf_status_t jf_pack_append_kv_mirror(const void* key_tok, const void* value_tok, int32_t dtype,
+                                     int64_t T, int32_t H_kv,
+                                     int64_t k_stride_t, int64_t k_stride_h,
+                                     int64_t v_stride_t, int64_t v_stride_h,
+                                     const int64_t* slots,
+                                     uint8_t* k_data, void* k_scales, uint8_t* v_data, void* v_scales,
+                                     int64_t num_slots, int32_t k_bits, int32_t v_bits,
+                                     int32_t group_size, void* k_mirror, void* v_mirror,
+                                     jf_stream_t stream);
+jf_status_t jf_mirror_append_ctx_create(void* k_shadow, void* v_shadow, int32_t H_kv,
+                                        int64_t num_slots, int64_t max_tokens, int64_t* handle);
+jf_status_t jf_mirror_append_ctx_destroy(int64_t handle);
+/* rows written / skipped and chunks scattered so far (any pointer may be null) */
+jf_status_t jf_mirror_append_ctx_stats(int64_t handle, int64_t* rows_written,
+                                       int64_t* rows_skipped, int64_t* chunks);
+jf_status_t jf_stream_mirror_append(jf_stream_t stream, int64_t handle, const void* key_tok,
+                                    const void* value_tok, int64_t T,
+                                    int64_t k_stride_t, int64_t k_stride_h,
+                                    int64_t v_stride_t, int64_t v_stride_h,
+                                    const int64_t* slots);
+/* Page-lock an existing host allocation and return the pointer the GPU sees it at. */
+jf_status_t jf_map_host(void* host_ptr, uint64_t bytes, void** device_ptr);
+jf_status_t jf_unmap_host(void* host_ptr);
+
+/* ---------------------------------------------------------------------------------
  * Fused low-bit decode attention.
  *
  * One call of jf_decode_fused does what the reference spreads over Stage A

@@ -55,6 +55,20 @@ _SIGS = {
                                       C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "jf_pack_append_kv_mirror": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
+                                             C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                             C.c_void_p, C.c_void_p, C.c_void_p]),
+    "jf_mirror_append_ctx_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
+                                                C.POINTER(C.c_int64)]),
+    "jf_mirror_append_ctx_destroy": (C.c_int32, [C.c_int64]),
+    "jf_mirror_append_ctx_stats": (C.c_int32, [C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                               C.POINTER(C.c_int64)]),
+    "jf_stream_mirror_append": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
+                                            C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "jf_map_host": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "jf_unmap_host": (C.c_int32, [C.c_void_p]),
     "jf_decode_workspace_bytes": (C.c_uint64, [C.c_int32] * 6),
     "jf_decode_scan": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_topk_select": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),

@@ -5,6 +5,15 @@ Layout (unchanged from the reference): ``k_data (H_kv, num_slots, 128*kbits/8) u
 ``k_scales (H_kv, num_slots, 128/group) bf16``, the same for V, ``slot_filled (num_slots,)
 bool``; mirror ``k_shadow / v_shadow (H_kv, num_slots, 128)`` in host DRAM in the model's
 16-bit dtype.  ``num_slots = num_blocks * 16``.
+
+Three ways to fill the mirror on an append (``mirror_append``):
+  * ``"mapped"`` -- the mirror is mapped pinned host memory and the packing kernel stores the
+    rows into it itself: one launch, no host step (the default when a mirror is kept);
+  * ``"stream"`` -- ordinary host memory; rows go through pinned staging and a host callback
+    in the CUDA stream (the reference's graph-mode path, cache_store.py:616-640);
+  * ``"sync"``   -- copy, host synchronisation and ``index_copy_`` as in the reference's eager
+    path (cache_store.py:746-756).
+With the first two, ``flush_pending_writes`` makes the mirror current for host readers.
 """
 from __future__ import annotations
 
@@ -16,9 +25,12 @@ from .config import JetFireConfig
 
 class JetFireCacheStore:
     def __init__(self, *, num_blocks: int, num_kv_heads: int, head_dim: int, cfg: JetFireConfig,
-                 device, dtype=torch.bfloat16, shadow_enabled: bool = True, block_size: int = 16):
+                 device, dtype=torch.bfloat16, shadow_enabled: bool = True, block_size: int = 16,
+                 mirror_append: str = "mapped", stream_chunk_tokens: int = 4096):
         if head_dim != 128 or block_size != 16:
             raise ValueError("the decode path is built for head_dim 128 and block_size 16")
+        if mirror_append not in ("mapped", "stream", "sync"):
+            raise ValueError("mirror_append must be 'mapped', 'stream' or 'sync'")
         self.cfg = cfg
         self.block_size = block_size
         self.num_blocks = int(num_blocks)
@@ -38,9 +50,22 @@ class JetFireCacheStore:
         self.slot_filled = torch.zeros(self.num_slots, dtype=torch.bool, **dev)
         self.written_count = 0
         self.shadow_enabled = bool(shadow_enabled)
+        self.mirror_append = mirror_append
+        self._k_shadow_dev = self._v_shadow_dev = None
+        self._append_ctx = None
+        self._pending_event = None
         if self.shadow_enabled:
-            self.k_shadow = torch.zeros(num_kv_heads, self.num_slots, head_dim, dtype=dtype)
-            self.v_shadow = torch.zeros(num_kv_heads, self.num_slots, head_dim, dtype=dtype)
+            shape = (num_kv_heads, self.num_slots, head_dim)
+            if mirror_append == "mapped":
+                self.k_shadow, self._k_shadow_dev = ops.alloc_mapped_pinned_pair(shape, dtype)
+                self.v_shadow, self._v_shadow_dev = ops.alloc_mapped_pinned_pair(shape, dtype)
+                self.k_shadow.zero_()
+                self.v_shadow.zero_()
+            else:
+                self.k_shadow = torch.zeros(*shape, dtype=dtype)
+                self.v_shadow = torch.zeros(*shape, dtype=dtype)
+                if mirror_append == "stream":
+                    self._append_ctx = ops.MirrorAppendCtx(self.k_shadow, self.v_shadow, stream_chunk_tokens)
         else:
             self.k_shadow = self.v_shadow = None
 
@@ -51,11 +76,24 @@ class JetFireCacheStore:
         if key_tok.shape != value_tok.shape or key_tok.dim() != 3:
             raise RuntimeError("write_slots: key/value must be (T, H_kv, 128) and match")
         slot_idx = slot_idx.to(torch.int64)
-        ops.fused_quant_write_kv(key_tok, value_tok, slot_idx, self.k_data, self.k_scales, self.v_data,
-                                 self.v_scales, self.group_size, self.k_nbits, self.v_nbits)
+        mapped = self.shadow_enabled and self.mirror_append == "mapped"
+        if mapped:
+            ops.fused_quant_write_kv_mirror(key_tok, value_tok, slot_idx, self.k_data, self.k_scales, self.v_data,
+                                            self.v_scales, self.group_size, self.k_nbits, self.v_nbits,
+                                            self._k_shadow_dev, self._v_shadow_dev)
+        else:
+            ops.fused_quant_write_kv(key_tok, value_tok, slot_idx, self.k_data, self.k_scales, self.v_data,
+                                     self.v_scales, self.group_size, self.k_nbits, self.v_nbits)
         valid = slot_idx >= 0
         self.slot_filled[slot_idx[valid]] = True
         self.written_count += int(key_tok.shape[0])
+        if self.shadow_enabled and self.mirror_append == "stream":
+            self._append_ctx.append(key_tok, value_tok, slot_idx)
+        if self.shadow_enabled and self.mirror_append != "sync":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._pending_event = ev
+            return
         if self.shadow_enabled:
             idx_cpu = slot_idx.to("cpu")                       # host sync, as in the reference's eager path
             keep = idx_cpu >= 0
@@ -66,5 +104,8 @@ class JetFireCacheStore:
             self.v_shadow.index_copy_(1, idx_cpu, v_cpu)
 
     def flush_pending_writes(self) -> None:
-        """Appends are synchronous here; kept for interface parity (cache_store.py:1340-1387)."""
-        return None
+        """Wait until every appended row is in the mirror (cache_store.py:1340-1387).  Needed
+        before a host thread reads the mirror; work on the same CUDA stream needs nothing."""
+        ev, self._pending_event = self._pending_event, None
+        if ev is not None:
+            ev.synchronize()

@@ -14,6 +14,14 @@
 // rows (2 KB) before it processes any, so that enough bytes are in flight per SM, and the
 // slot lookup runs beside the row loads, not before them.  HBM-bound: 256 B read +
 // 36..66 B written per row.
+//
+// Mirror rows: the reference keeps every appended row in full precision in host memory
+// (jetfire_vllm/adapter/cache_store.py:311-323) and fills it with a device-to-host copy, a
+// host synchronisation and an index_copy_ per append (:746-756), or through pinned staging
+// and a host callback under CUDA graphs (:616-640).  Here the kernel that packs a row also
+// stores its 256 raw bytes -- already in the half-warp's registers as sixteen 16-byte pieces
+// -- straight into the mirror through a device-visible pointer (mapped pinned host memory),
+// one coalesced 256-byte write per row, so an append is one launch with no host step.
 #include "jf_common.cuh"
 
 namespace jf {
@@ -27,6 +35,7 @@ struct PackSide {
   uint8_t* data;
   uint16_t* scales;
   int nbits;
+  uint16_t* mirror;   // (H_kv, num_slots, 128) 16-bit rows, device-visible; may be null
 };
 
 template <int DT, int NBITS, int GS>
@@ -145,6 +154,7 @@ pack_append_kernel(PackSide s0, PackSide s1, int64_t T, int H, const int64_t* __
     const int64_t o = static_cast<int64_t>(cur.hh[i]) * num_slots + (live ? cur.slot[i] : 0);
     uint8_t* out_row = s.data + o * dp;
     uint16_t* scale_row = s.scales + o * NG;
+    if (s.mirror != nullptr && live) reinterpret_cast<uint4*>(s.mirror + o * JF_HEAD_DIM)[sub] = cur.raw[i];
     // every lane runs the arithmetic (full-mask shuffles); only live rows are stored
     if (s.nbits == 3) pack_row<DT, 3, GS>(cur.raw[i], out_row, scale_row, sub, live);
     else if (s.nbits == 2) pack_row<DT, 2, GS>(cur.raw[i], out_row, scale_row, sub, live);
@@ -192,7 +202,7 @@ extern "C" jf_status_t jf_pack_append(const void* x_tok, int32_t dtype, int64_t 
                                       int32_t nbits, int32_t group_size, jf_stream_t stream) {
   jf_status_t st = jf::check_side(x_tok, stride_t, stride_h, out_data, out_scales, nbits);
   if (st != JF_OK) return st;
-  jf::PackSide k{x_tok, stride_t, stride_h, out_data, static_cast<uint16_t*>(out_scales), nbits};
+  jf::PackSide k{x_tok, stride_t, stride_h, out_data, static_cast<uint16_t*>(out_scales), nbits, nullptr};
   return jf::launch_pack(k, nullptr, dtype, T, H_kv, slots, num_slots, group_size,
                          static_cast<cudaStream_t>(stream));
 }
@@ -207,8 +217,28 @@ extern "C" jf_status_t jf_pack_append_kv(const void* key_tok, const void* value_
   if (st != JF_OK) return st;
   st = jf::check_side(value_tok, v_stride_t, v_stride_h, v_data, v_scales, v_bits);
   if (st != JF_OK) return st;
-  jf::PackSide k{key_tok, k_stride_t, k_stride_h, k_data, static_cast<uint16_t*>(k_scales), k_bits};
-  jf::PackSide v{value_tok, v_stride_t, v_stride_h, v_data, static_cast<uint16_t*>(v_scales), v_bits};
+  jf::PackSide k{key_tok, k_stride_t, k_stride_h, k_data, static_cast<uint16_t*>(k_scales), k_bits, nullptr};
+  jf::PackSide v{value_tok, v_stride_t, v_stride_h, v_data, static_cast<uint16_t*>(v_scales), v_bits, nullptr};
+  return jf::launch_pack(k, &v, dtype, T, H_kv, slots, num_slots, group_size,
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" jf_status_t jf_pack_append_kv_mirror(const void* key_tok, const void* value_tok, int32_t dtype,
+                                                int64_t T, int32_t H_kv, int64_t k_stride_t, int64_t k_stride_h,
+                                                int64_t v_stride_t, int64_t v_stride_h, const int64_t* slots,
+                                                uint8_t* k_data, void* k_scales, uint8_t* v_data, void* v_scales,
+                                                int64_t num_slots, int32_t k_bits, int32_t v_bits,
+                                                int32_t group_size, void* k_mirror, void* v_mirror,
+                                                jf_stream_t stream) {
+  jf_status_t st = jf::check_side(key_tok, k_stride_t, k_stride_h, k_data, k_scales, k_bits);
+  if (st != JF_OK) return st;
+  st = jf::check_side(value_tok, v_stride_t, v_stride_h, v_data, v_scales, v_bits);
+  if (st != JF_OK) return st;
+  if (!k_mirror || !v_mirror || !jf::aligned(k_mirror, 16) || !jf::aligned(v_mirror, 16)) return JF_ERR_ARG;
+  jf::PackSide k{key_tok, k_stride_t, k_stride_h, k_data, static_cast<uint16_t*>(k_scales), k_bits,
+                 static_cast<uint16_t*>(k_mirror)};
+  jf::PackSide v{value_tok, v_stride_t, v_stride_h, v_data, static_cast<uint16_t*>(v_scales), v_bits,
+                 static_cast<uint16_t*>(v_mirror)};
   return jf::launch_pack(k, &v, dtype, T, H_kv, slots, num_slots, group_size,
                          static_cast<cudaStream_t>(stream));
 }

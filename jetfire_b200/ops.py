@@ -119,6 +119,108 @@ def fused_quant_write_int4_sym_kv(key_tok, value_tok, slot_idx, k_data, k_scales
     fused_quant_write_kv(key_tok, value_tok, slot_idx, k_data, k_scales, v_data, v_scales, group_size, 4, 4)
 
 
+def _check_mirror(t, key_tok, k_data, name):
+    _require(t.is_cuda and t.is_contiguous() and t.dtype == key_tok.dtype and t.dim() == 3
+             and t.shape[0] == k_data.shape[0] and t.shape[1] == k_data.shape[1] and t.shape[2] == 128,
+             f"{name}: mirror must be a contiguous device-visible (H_kv, num_slots, 128) tensor of the tokens' dtype")
+
+
+def fused_quant_write_kv_mirror(key_tok, value_tok, slot_idx, k_data, k_scales, v_data, v_scales,
+                                group_size, k_bits, v_bits, k_mirror_dev, v_mirror_dev):
+    """``fused_quant_write_kv`` that also stores every live row, bit for bit, into the mirrors.
+    ``k_mirror_dev / v_mirror_dev`` are the DEVICE views of mapped host mirrors (the second
+    tensor of ``alloc_mapped_pinned_pair``, or ``map_host_tensor`` of an existing one): the
+    append is one launch with no host step, in place of the reference's copy + sync +
+    index_copy_ (jetfire_vllm/adapter/cache_store.py:746-756)."""
+    name = "fused_quant_write_kv_mirror"
+    _check_side(key_tok, k_data, k_scales, k_bits, group_size, name)
+    _check_side(value_tok, v_data, v_scales, v_bits, group_size, name)
+    _require(key_tok.shape == value_tok.shape and key_tok.dtype == value_tok.dtype,
+             f"{name}: key/value shape or dtype mismatch")
+    _require(k_data.shape[1] == v_data.shape[1], f"{name}: K and V caches differ in num_slots")
+    _require(slot_idx.is_cuda and slot_idx.dtype == torch.int64 and slot_idx.dim() == 1
+             and slot_idx.shape[0] == key_tok.shape[0], f"{name}: slot_idx must be (T,) int64 CUDA")
+    _check_mirror(k_mirror_dev, key_tok, k_data, name)
+    _check_mirror(v_mirror_dev, key_tok, k_data, name)
+    slot_idx = slot_idx.contiguous()
+    st = lib.jf_pack_append_kv_mirror(key_tok.data_ptr(), value_tok.data_ptr(), _dtype_id(key_tok),
+                                      key_tok.shape[0], key_tok.shape[1],
+                                      key_tok.stride(0), key_tok.stride(1), value_tok.stride(0), value_tok.stride(1),
+                                      slot_idx.data_ptr(), k_data.data_ptr(), k_scales.data_ptr(),
+                                      v_data.data_ptr(), v_scales.data_ptr(), k_data.shape[1],
+                                      k_bits, v_bits, group_size, k_mirror_dev.data_ptr(), v_mirror_dev.data_ptr(),
+                                      _stream())
+    check(name, st)
+
+
+def map_host_tensor(host: torch.Tensor) -> torch.Tensor:
+    """Page-lock an existing contiguous CPU tensor and return a CUDA tensor over the same bytes
+    (for ``fused_quant_write_kv_mirror``).  ``unmap_host_tensor(host)`` undoes it."""
+    _require(not host.is_cuda and host.is_contiguous(), "map_host_tensor: contiguous CPU tensor expected")
+    nbytes = host.numel() * host.element_size()
+    d = C.c_void_p()
+    check("map_host_tensor", lib.jf_map_host(host.data_ptr(), nbytes, C.byref(d)))
+    dev_ptr = d.value
+
+    class _DevView:
+        __cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (dev_ptr, False), "version": 2, "strides": None}
+
+    return torch.as_tensor(_DevView(), device="cuda").view(host.dtype)[:host.numel()].reshape(host.shape)
+
+
+def unmap_host_tensor(host: torch.Tensor) -> None:
+    check("unmap_host_tensor", lib.jf_unmap_host(host.data_ptr()))
+
+
+class MirrorAppendCtx:
+    """Stream-ordered append to mirrors in ordinary host memory (the reference's
+    create_shadow_append_submit_ctx + stream_submit_shadow_append,
+    jetfire_vllm/csrc/cpu_topk_attn.cpp:1611-1665, with its pinned staging of
+    adapter/cache_store.py:616-640 owned by the context).  ``append`` returns at once; the
+    rows are in the mirror when the stream has passed the work it enqueued."""
+
+    def __init__(self, k_shadow: torch.Tensor, v_shadow: torch.Tensor, max_tokens: int):
+        _require(not k_shadow.is_cuda and not v_shadow.is_cuda and k_shadow.is_contiguous()
+                 and v_shadow.is_contiguous() and k_shadow.shape == v_shadow.shape and k_shadow.dim() == 3
+                 and k_shadow.shape[2] == 128 and k_shadow.dtype == v_shadow.dtype
+                 and k_shadow.dtype in (torch.bfloat16, torch.float16),
+                 "MirrorAppendCtx: mirrors must be contiguous CPU (H_kv, num_slots, 128) 16-bit tensors")
+        self._keep = (k_shadow, v_shadow)
+        h = C.c_int64()
+        check("MirrorAppendCtx", lib.jf_mirror_append_ctx_create(k_shadow.data_ptr(), v_shadow.data_ptr(),
+                                                                 k_shadow.shape[0], k_shadow.shape[1],
+                                                                 int(max_tokens), C.byref(h)))
+        self.handle = h.value
+
+    def append(self, key_tok, value_tok, slot_idx):
+        name = "MirrorAppendCtx.append"
+        k_shadow = self._keep[0]
+        _require(self.handle != 0, f"{name}: context was closed")
+        _require(key_tok.is_cuda and value_tok.is_cuda and key_tok.shape == value_tok.shape and key_tok.dim() == 3
+                 and key_tok.shape[1] == k_shadow.shape[0] and key_tok.shape[2] == 128
+                 and key_tok.dtype == k_shadow.dtype and value_tok.dtype == k_shadow.dtype
+                 and key_tok.stride(2) == 1 and value_tok.stride(2) == 1,
+                 f"{name}: key/value must be CUDA (T, H_kv, 128) of the mirror's dtype, innermost contiguous")
+        _require(slot_idx.is_cuda and slot_idx.dtype == torch.int64 and slot_idx.dim() == 1
+                 and slot_idx.shape[0] == key_tok.shape[0], f"{name}: slot_idx must be (T,) int64 CUDA")
+        slot_idx = slot_idx.contiguous()
+        check(name, lib.jf_stream_mirror_append(_stream(), self.handle, key_tok.data_ptr(), value_tok.data_ptr(),
+                                                key_tok.shape[0], key_tok.stride(0), key_tok.stride(1),
+                                                value_tok.stride(0), value_tok.stride(1), slot_idx.data_ptr()))
+
+    def stats(self):
+        w, s, c = C.c_int64(), C.c_int64(), C.c_int64()
+        check("MirrorAppendCtx.stats", lib.jf_mirror_append_ctx_stats(self.handle, C.byref(w), C.byref(s), C.byref(c)))
+        return {"rows_written": w.value, "rows_skipped": s.value, "chunks": c.value}
+
+    def close(self):
+        """Synchronise the work that uses the context first."""
+        if self.handle:
+            lib.jf_mirror_append_ctx_destroy(self.handle)
+            self.handle = 0
+
+
 # ---------------------------------------------------------------------------------------
 # fused decode attention
 # ---------------------------------------------------------------------------------------

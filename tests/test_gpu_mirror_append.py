@@ -1,0 +1,175 @@
+"""Appending to the host mirror: rows stored by the packing kernel into a mapped mirror, the
+stream-ordered staged path for ordinary host memory, and the adapter's cache store + decode
+entry on top of them, against the oracle.
+
+Gates: mirror rows and packed bytes bit-exact; attention outputs within 2e-3 max-abs + 1e-3
+relative (+ one bf16 ulp for the final store)."""
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import jf_oracle as O
+from jf_testlib import Case, MODES, f32_values, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _tokens(T, H, dtype, seed, pad=0):
+    """(T, H, 128) key / value tokens; pad > 0 makes the token stride wider than H * 128."""
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(T, H + pad, 128, generator=g).to(dtype).cuda()[:, :H]
+    v = torch.randn(T, H + pad, 128, generator=g).to(dtype).cuda()[:, :H]
+    return k, v
+
+
+def _caches(mode, H, num_slots):
+    kb, vb, gs = MODES[mode]
+    ng = 128 // gs
+    kd = torch.full((H, num_slots, 16 * kb), 0xA5, dtype=torch.uint8, device="cuda")
+    vd = torch.full((H, num_slots, 16 * vb), 0xA5, dtype=torch.uint8, device="cuda")
+    ks = torch.zeros(H, num_slots, ng, dtype=torch.bfloat16, device="cuda")
+    vs = torch.zeros_like(ks)
+    return kd, ks, vd, vs
+
+
+def _expected_mirror(tok, slots, num_slots, fill):
+    """Rows of live tokens at their slots, `fill` bits elsewhere (later tokens win a slot)."""
+    T, H, _ = tok.shape
+    want = np.full((H, num_slots, 128), fill, dtype=np.uint16)
+    bits = to_bits(tok.contiguous())
+    for t, s in enumerate(slots.tolist()):
+        if 0 <= s < num_slots:
+            want[:, s] = bits[t]
+    return want
+
+
+@pytest.mark.parametrize("mode,dtype,pad", [("k3v2", torch.bfloat16, 0), ("k4v4", torch.float16, 3),
+                                             ("k4v4", torch.bfloat16, 1)])
+def test_packing_kernel_stores_mirror_rows(mode, dtype, pad):
+    from jetfire_b200 import ops
+    kb, vb, gs = MODES[mode]
+    T, H, num_slots = 37, 3, 64
+    k_tok, v_tok = _tokens(T, H, dtype, 5, pad)
+    slots = torch.randperm(num_slots, generator=torch.Generator().manual_seed(6))[:T].to(torch.int64)
+    slots[4] = -1
+    slots[11] = -7
+    slots[20] = num_slots + 2        # out of range: skipped on both sides
+    kd, ks, vd, vs = _caches(mode, H, num_slots)
+    kd2, ks2, vd2, vs2 = _caches(mode, H, num_slots)
+    km_host, km_dev = ops.alloc_mapped_pinned_pair((H, num_slots, 128), dtype)
+    vm_host, vm_dev = ops.alloc_mapped_pinned_pair((H, num_slots, 128), dtype)
+    km_host.view(torch.int16).fill_(0x1234)
+    vm_host.view(torch.int16).fill_(0x1234)
+    ops.fused_quant_write_kv_mirror(k_tok, v_tok, slots.cuda(), kd, ks, vd, vs, gs, kb, vb, km_dev, vm_dev)
+    ops.fused_quant_write_kv(k_tok, v_tok, slots.cuda(), kd2, ks2, vd2, vs2, gs, kb, vb)
+    torch.cuda.synchronize()
+    for a, b in ((kd, kd2), (ks, ks2), (vd, vd2), (vs, vs2)):
+        assert torch.equal(a, b), "the mirror store changed the packed cache"
+    assert np.array_equal(to_bits(km_host), _expected_mirror(k_tok, slots, num_slots, 0x1234))
+    assert np.array_equal(to_bits(vm_host), _expected_mirror(v_tok, slots, num_slots, 0x1234))
+    with pytest.raises(RuntimeError):   # the mirror must have the tokens' dtype
+        other = torch.float16 if dtype == torch.bfloat16 else torch.bfloat16
+        ops.fused_quant_write_kv_mirror(k_tok, v_tok, slots.cuda(), kd, ks, vd, vs, gs, kb, vb,
+                                        km_dev.view(other), vm_dev.view(other))
+
+
+def test_stream_ordered_append_to_ordinary_host_memory():
+    """Several chunks through the pinned staging (max_tokens 5, 23 tokens), padding slots
+    skipped, a second append ordered behind the first on the same stream."""
+    from jetfire_b200 import ops
+    T, H, num_slots = 23, 2, 48
+    k_tok, v_tok = _tokens(T, H, torch.bfloat16, 8, pad=2)
+    slots = torch.randperm(num_slots, generator=torch.Generator().manual_seed(9))[:T].to(torch.int64)
+    slots[0] = -1
+    slots[22] = num_slots            # out of range
+    k_shadow = torch.zeros(H, num_slots, 128, dtype=torch.bfloat16)
+    v_shadow = torch.zeros(H, num_slots, 128, dtype=torch.bfloat16)
+    ctx = ops.MirrorAppendCtx(k_shadow, v_shadow, max_tokens=5)
+    ctx.append(k_tok, v_tok, slots.cuda())
+    k2, v2 = _tokens(3, H, torch.bfloat16, 10)
+    slots2 = slots[1:4].clone()      # overwrites three of the rows just written
+    ctx.append(k2, v2, slots2.cuda())
+    torch.cuda.synchronize()
+    want_k = _expected_mirror(k_tok, slots, num_slots, 0)
+    want_v = _expected_mirror(v_tok, slots, num_slots, 0)
+    for t, s in enumerate(slots2.tolist()):
+        want_k[:, s] = to_bits(k2)[t]
+        want_v[:, s] = to_bits(v2)[t]
+    assert np.array_equal(to_bits(k_shadow), want_k)
+    assert np.array_equal(to_bits(v_shadow), want_v)
+    st = ctx.stats()
+    assert st["chunks"] == 5 + 1 and st["rows_written"] == (21 + 3) * H and st["rows_skipped"] == 2 * H
+    with pytest.raises(RuntimeError):
+        ctx.append(k_tok.half(), v_tok.half(), slots.cuda())
+    ctx.close()
+    with pytest.raises(RuntimeError):
+        ctx.append(k_tok, v_tok, slots.cuda())
+
+
+def test_map_host_tensor_makes_an_existing_mirror_device_visible():
+    from jetfire_b200 import ops
+    host = torch.zeros(2, 16, 128, dtype=torch.bfloat16)
+    dev = ops.map_host_tensor(host)
+    try:
+        dev.copy_(torch.ones_like(dev))
+        torch.cuda.synchronize()
+        assert bool((host == 1).all())
+    finally:
+        del dev
+        ops.unmap_host_tensor(host)
+
+
+@pytest.mark.parametrize("mode_name,mode", [("SymInt3K_SymInt2V", "k3v2"), ("SymInt4K_SymInt4V", "k4v4")])
+def test_cache_store_append_modes_and_decode_entry(mode_name, mode):
+    """Prefill chunk + one decode token per sequence through the store, with each way of
+    filling the mirror; the three mirrors are equal bit for bit, the packed cache is the
+    oracle's, and the decode entry (scan, selection, host correction over the mirror, merge)
+    gives the oracle's output."""
+    from jetfire_b200.adapter.cache_store import JetFireCacheStore
+    from jetfire_b200.adapter.config import JetFireConfig
+    from jetfire_b200.adapter.decode_path import make_decode_metadata, try_jetfire_decode
+    case = Case(mode, 2, 8, 2, 400, lens=[400, 263], seed=21)
+    cfg = JetFireConfig(mode=mode_name, top_k=64, group_size=MODES[mode][2], cpu_attn_threads=2)
+    key_all = case.k_full.transpose(0, 1).contiguous().cuda()     # (num_slots, H_kv, 128): token t -> slot t
+    val_all = case.v_full.transpose(0, 1).contiguous().cuda()
+    # the last token of every sequence arrives as the decode-step append
+    last_slots = []
+    for b in range(case.B):
+        n = int(case.seq_lens[b])
+        last_slots.append(int(case.block_table[b, (n - 1) // 16]) * 16 + (n - 1) % 16)
+    last = torch.tensor(last_slots, dtype=torch.int64)
+    first = torch.tensor([s for s in range(case.num_slots) if s not in set(last_slots)], dtype=torch.int64)
+    first_padded = torch.cat([first, torch.tensor([-1, -1], dtype=torch.int64)])   # padding as vLLM sends it
+    stores = {}
+    for how in ("mapped", "stream", "sync"):
+        st = JetFireCacheStore(num_blocks=case.n_blocks, num_kv_heads=case.H_kv, head_dim=128, cfg=cfg,
+                               device="cuda", dtype=case.dtype, mirror_append=how, stream_chunk_tokens=100)
+        pad_rows = torch.zeros(2, case.H_kv, 128, dtype=case.dtype, device="cuda")
+        st.write_slots(torch.cat([key_all[first.cuda()], pad_rows]), torch.cat([val_all[first.cuda()], pad_rows]),
+                       first_padded.cuda())
+        st.write_slots(key_all[last.cuda()], val_all[last.cuda()], last.cuda())
+        st.flush_pending_writes()
+        stores[how] = st
+    okd, oks, ovd, ovs = case.oracle_cache()
+    for how, st in stores.items():
+        assert np.array_equal(to_bits(st.k_shadow), to_bits(case.k_full)), f"{how}: K mirror differs"
+        assert np.array_equal(to_bits(st.v_shadow), to_bits(case.v_full)), f"{how}: V mirror differs"
+        assert np.array_equal(st.k_data.cpu().numpy(), okd) and np.array_equal(to_bits(st.k_scales), oks)
+        assert np.array_equal(st.v_data.cpu().numpy(), ovd) and np.array_equal(to_bits(st.v_scales), ovs)
+        assert bool(st.slot_filled.all())
+    ref = case.oracle_step(64)
+    want = O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["out"]))
+    md = make_decode_metadata(case.seq_lens.cuda(), case.block_table.cuda())
+    impl = SimpleNamespace(scale=case.attn_scale, attn_type=SimpleNamespace(name="DECODER"))
+    layer = SimpleNamespace(num_heads=case.H_q, num_kv_heads=case.H_kv, head_size=128, layer_name="l0")
+    for how, st in stores.items():
+        out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
+        got = try_jetfire_decode(impl=impl, layer=layer, query=case.q.cuda(), attn_metadata=md,
+                                 output=out, store=st, cfg=cfg)
+        assert got is out
+        torch.cuda.synchronize()
+        err = np.abs(f32_values(out).reshape(case.B, case.H_q, 128) - want)
+        lim = 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)
+        assert (err <= lim).all(), f"{how}: max err {err.max():.3e}"
