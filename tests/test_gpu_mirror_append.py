@@ -173,3 +173,84 @@ def test_cache_store_append_modes_and_decode_entry(mode_name, mode):
         err = np.abs(f32_values(out).reshape(case.B, case.H_q, 128) - want)
         lim = 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)
         assert (err <= lim).all(), f"{how}: max err {err.max():.3e}"
+
+
+def test_decode_steps_replayed_as_one_cuda_graph_with_host_nodes():
+    """A whole decode step of one layer captured once and replayed: append of the new token
+    (packed cache + mapped mirror, one kernel), query upload, scan + selection, slot download,
+    host correction submitted and joined by host nodes in the graph, o_new upload, merge.  No
+    host synchronisation inside a step; every replay's output is the oracle's for the sequence
+    lengths of that step."""
+    from jetfire_b200 import ops
+    mode, top_k, steps = "k3v2", 64, 3
+    kb, vb, gs = MODES[mode]
+    len0 = [300, 200]
+    case = Case(mode, 2, 8, 2, 512, lens=[n + steps for n in len0], seed=33)
+    slot_of = lambda b, pos: int(case.block_table[b, pos // 16]) * 16 + pos % 16
+    kd, ks, vd, vs = _caches(mode, case.H_kv, case.num_slots)
+    km_host, km_dev = ops.alloc_mapped_pinned_pair((case.H_kv, case.num_slots, 128), case.dtype)
+    vm_host, vm_dev = ops.alloc_mapped_pinned_pair((case.H_kv, case.num_slots, 128), case.dtype)
+    km_host.zero_()
+    vm_host.zero_()
+    key_all = case.k_full.transpose(0, 1).contiguous().cuda()     # token rows by slot
+    val_all = case.v_full.transpose(0, 1).contiguous().cuda()
+    init = torch.tensor([slot_of(b, p) for b in range(case.B) for p in range(len0[b])], dtype=torch.int64).cuda()
+    ops.fused_quant_write_kv_mirror(key_all[init], val_all[init], init, kd, ks, vd, vs, gs, kb, vb, km_dev, vm_dev)
+    # static buffers of the captured step
+    new_k = torch.zeros(case.B, case.H_kv, 128, dtype=case.dtype, device="cuda")
+    new_v = torch.zeros_like(new_k)
+    new_slots = torch.zeros(case.B, dtype=torch.int64, device="cuda")
+    seq_lens = torch.tensor(len0, dtype=torch.int32, device="cuda")
+    q_host = torch.zeros(case.B, case.H_q, 128, dtype=case.dtype).pin_memory()
+    q = torch.zeros(case.B, case.H_q, 128, dtype=case.dtype, device="cuda")
+    slots_host = torch.empty(case.B, case.H_q, top_k, dtype=torch.int64).pin_memory()
+    o_new_host = torch.zeros(case.B, case.H_q, 128, dtype=case.dtype).pin_memory()
+    o_new = torch.empty_like(q)
+    out = torch.empty_like(q)
+    call = ops.DecodeCall(mode, q, kd, ks, vd, vs, case.block_table.cuda(), seq_lens, case.ctx, case.H_q,
+                          case.H_kv, 16, top_k, case.attn_scale)
+    host = ops.HostCorrectionCall(q_host, km_host, vm_host, None, slots_host, o_new_host, case.attn_scale)
+    ops.set_cpu_attn_threads(3)
+
+    def step(stream):
+        ops.fused_quant_write_kv_mirror(new_k, new_v, new_slots, kd, ks, vd, vs, gs, kb, vb, km_dev, vm_dev)
+        q.copy_(q_host, non_blocking=True)
+        call.fused()
+        slots_host.copy_(call.out["topk_slots"], non_blocking=True)
+        host.stream_submit(stream)
+        host.stream_wait(stream)
+        o_new.copy_(o_new_host, non_blocking=True)
+        ops.blend_unnorm_into(call.out["o_hat"], call.out["o_old_unnorm"], call.out["W"], o_new, out)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):       # eager once: kernel attributes, worker threads
+        new_slots.fill_(-1)             # nothing is appended by the warm-up
+        step(side)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step(torch.cuda.current_stream())
+    g = torch.Generator().manual_seed(4)
+    for t in range(steps):
+        lens_now = [n + t + 1 for n in len0]
+        slots_t = torch.tensor([slot_of(b, len0[b] + t) for b in range(case.B)], dtype=torch.int64)
+        new_k.copy_(key_all[slots_t.cuda()])
+        new_v.copy_(val_all[slots_t.cuda()])
+        new_slots.copy_(slots_t)
+        seq_lens.copy_(torch.tensor(lens_now, dtype=torch.int32))
+        case.q = torch.randn(case.B, case.H_q, 128, generator=g).to(case.dtype)
+        q_host.copy_(case.q)
+        graph.replay()
+        torch.cuda.synchronize()
+        host.stream_status()
+        call.status()
+        case.seq_lens = torch.tensor(lens_now, dtype=torch.int32)
+        ref = case.oracle_step(top_k)
+        assert np.array_equal(slots_host.numpy(), ref["topk_slots"]), f"step {t}: selected slots differ"
+        want = O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["out"]))
+        err = np.abs(f32_values(out) - want)
+        lim = 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)
+        assert (err <= lim).all(), f"step {t}: max err {err.max():.3e}"
+    host.close()
