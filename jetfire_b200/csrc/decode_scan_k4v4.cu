@@ -83,10 +83,17 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   return v;
 }
 
+// The integer accumulators start at -8 * sum(qi) + kAccMagic (the bits of the float 1.5 * 2^23):
+// the sum the MMA returns, read as a float, is then 1.5 * 2^23 + acc exactly (|acc| < 2^22: at
+// most 32 * 127 * 15), and one subtraction gives float(acc) -- the same value an int-to-float
+// conversion returns, on the FMA pipe instead of the conversion unit.
+constexpr int kAccMagic = 0x4B400000;
+__device__ __forceinline__ float acc_to_f32(int acc_biased) { return __int_as_float(acc_biased) - 12582912.0f; }
+
 struct K4State {
   uint32_t qb[4][2];          // INT8 query fragments (B operand of the K MMA)
   float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
-  int init[4][4];             // -8 * sum(qi) per block for those heads, laid out as the MMA's C operand
+  int init[4][4];             // -8 * sum(qi) + kAccMagic per block for those heads, laid out as the MMA's C operand
   float oacc[8][4];
   float m_ref0, m_ref1, l0, l1;
   uint32_t k_off[4];          // swizzled byte offsets of this lane's K words, per 32-channel block
@@ -122,10 +129,10 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    s0 = __fmaf_rn(static_cast<float>(acc[c][0]), st.qs_h0[c], s0);
-    s1 = __fmaf_rn(static_cast<float>(acc[c][1]), st.qs_h1[c], s1);
-    s2 = __fmaf_rn(static_cast<float>(acc[c][2]), st.qs_h0[c], s2);
-    s3 = __fmaf_rn(static_cast<float>(acc[c][3]), st.qs_h1[c], s3);
+    s0 = __fmaf_rn(acc_to_f32(acc[c][0]), st.qs_h0[c], s0);
+    s1 = __fmaf_rn(acc_to_f32(acc[c][1]), st.qs_h1[c], s1);
+    s2 = __fmaf_rn(acc_to_f32(acc[c][2]), st.qs_h0[c], s2);
+    s3 = __fmaf_rn(acc_to_f32(acc[c][3]), st.qs_h1[c], s3);
   }
   s0 = __fmul_rn(__fmul_rn(s0, ks0), attn);
   s1 = __fmul_rn(__fmul_rn(s1, ks0), attn);
@@ -201,14 +208,14 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
   float sA[4] = {0.f, 0.f, 0.f, 0.f}, sB[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    sA[0] = __fmaf_rn(static_cast<float>(accA[c][0]), st.qs_h0[c], sA[0]);
-    sB[0] = __fmaf_rn(static_cast<float>(accB[c][0]), st.qs_h0[c], sB[0]);
-    sA[1] = __fmaf_rn(static_cast<float>(accA[c][1]), st.qs_h1[c], sA[1]);
-    sB[1] = __fmaf_rn(static_cast<float>(accB[c][1]), st.qs_h1[c], sB[1]);
-    sA[2] = __fmaf_rn(static_cast<float>(accA[c][2]), st.qs_h0[c], sA[2]);
-    sB[2] = __fmaf_rn(static_cast<float>(accB[c][2]), st.qs_h0[c], sB[2]);
-    sA[3] = __fmaf_rn(static_cast<float>(accA[c][3]), st.qs_h1[c], sA[3]);
-    sB[3] = __fmaf_rn(static_cast<float>(accB[c][3]), st.qs_h1[c], sB[3]);
+    sA[0] = __fmaf_rn(acc_to_f32(accA[c][0]), st.qs_h0[c], sA[0]);
+    sB[0] = __fmaf_rn(acc_to_f32(accB[c][0]), st.qs_h0[c], sB[0]);
+    sA[1] = __fmaf_rn(acc_to_f32(accA[c][1]), st.qs_h1[c], sA[1]);
+    sB[1] = __fmaf_rn(acc_to_f32(accB[c][1]), st.qs_h1[c], sB[1]);
+    sA[2] = __fmaf_rn(acc_to_f32(accA[c][2]), st.qs_h0[c], sA[2]);
+    sB[2] = __fmaf_rn(acc_to_f32(accB[c][2]), st.qs_h0[c], sB[2]);
+    sA[3] = __fmaf_rn(acc_to_f32(accA[c][3]), st.qs_h1[c], sA[3]);
+    sB[3] = __fmaf_rn(acc_to_f32(accB[c][3]), st.qs_h1[c], sB[3]);
   }
   {
     const float kA0 = __uint_as_float(ksA0 << 16), kA1 = __uint_as_float(ksA1 << 16);
@@ -420,8 +427,8 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       st.qb[c][1] = src[32];
       st.qs_h0[c] = __uint_as_float(src[64]);
       st.qs_h1[c] = __uint_as_float(src[96]);
-      st.init[c][0] = st.init[c][2] = static_cast<int>(src[128]);
-      st.init[c][1] = st.init[c][3] = static_cast<int>(src[160]);
+      st.init[c][0] = st.init[c][2] = static_cast<int>(src[128]) + kAccMagic;
+      st.init[c][1] = st.init[c][3] = static_cast<int>(src[160]) + kAccMagic;
     }
   }
 #pragma unroll
