@@ -17,11 +17,12 @@
 //
 // Compute: tokens sit on the MMA M axis and the (<= 8) query heads on N = 8.  Packed codes
 // are expanded in registers straight into the A fragments of mma.sync.m16n8k16 (the
-// dequantised tile never goes through shared memory): a 3-/2-/4-bit field is OR-ed into
-// the mantissa of an fp16 constant (1024 + code * 2^pos), the bias is subtracted exactly,
-// and the 2^pos factor is undone on the other operand (K: folded into Q) or on the output
-// row (V).  Group scales are applied in fp32 after the K MMA and folded into P before the
-// V MMA, so the integer codes stay exact in fp16.
+// dequantised tile never goes through shared memory).  A masked 2-/3-/4-bit field, read as a
+// 16-bit float, is a subnormal number code * 2^pos * 2^-24 (fp16) or * 2^-133 (bf16): V fields go
+// to the tensor core as they are (one AND per two codes), K fields take one bf16x2 fma that
+// applies offset, group scale and the reference's bf16 rounding together.  The power-of-two
+// factors are undone on the other operand (K: folded into Q) or on the output row (V); the V
+// group scale is folded into P, the V codes' offset leaves through a sum(P) tile at the end.
 #include "decode_scan.cuh"
 
 namespace jf {
@@ -39,8 +40,6 @@ __device__ __forceinline__ constexpr int v2_pos(int f) { return f <= 4 ? 2 * f :
 // 16-bit load, codes MSB-first inside a byte
 __device__ __forceinline__ constexpr int v2_dlocal(int f) { return 4 * (f >> 2) + 3 - (f & 3); }
 
-constexpr uint32_t kMagicBf16 = 0x43004300u;  // bf16 128.0 in both halves
-constexpr uint32_t kOneBf16x2 = 0x3F803F80u;
 
 // Shared-memory loads with a 32-bit address and an immediate offset: one instruction each,
 // no 64-bit pointer arithmetic in the loop.
@@ -69,21 +68,41 @@ __device__ __forceinline__ uint32_t join16(uint32_t lo, uint32_t hi) {
   return d;
 }
 
-// Dequantised K in the reference's rounding, scaled by 2^POS:
-//   ((v & field) | 128) - (128 + 4 * 2^POS) == (code - 4) * 2^POS        exact in bf16
-//   bf16_rn(that * scale)                   == 2^POS * bf16(float(code - 4) * scale)
-// which is jetfire_vllm/csrc/int3_qk_scores.cu:94-99 (a power of two commutes with the
-// rounding); the 2^POS is undone by the query operand.  Both steps are single bf16x2 fmas.
+// Dequantised K in the reference's rounding, times a power of two, in ONE bf16x2 fma per two
+// codes.  The masked 3-bit field, read as bf16, is the subnormal f * 2^POS * 2^-133 (exponent
+// bits zero).  With S = scale * 2^100 and C = -4 * 2^POS * 2^-133 * S = -scale * 2^(POS - 31)
+// (both exact: powers of two times the scale),
+//   fma(field, S, C) = bf16_rn((f - 4) * scale * 2^(POS - 33)) = 2^(POS - 33) * bf16_rn((f - 4) * scale):
+// the fma rounds once, and a power of two commutes with the rounding -- which is
+// jetfire_vllm/csrc/int3_qk_scores.cu:94-99.  The factor 2^(POS - 33) is undone by the query
+// operand.  (An 8-bit scale times a 3-bit integer needs at most 10 bits: exact before rounding.)
+struct K3Scale {
+  uint32_t S;     // scale * 2^100, both halves
+  uint32_t C[5];  // -scale * 2^(POS - 31) for POS = 0..4, both halves (POS 2 is unused)
+};
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ K3Scale k3_scale(uint32_t scale2) {
+  K3Scale k;
+  k.S = mul_bf16x2(scale2, 0x71807180u);        // 2^100
+  k.C[0] = mul_bf16x2(scale2, 0xB000B000u);     // -2^-31
+  k.C[1] = mul_bf16x2(scale2, 0xB080B080u);     // -2^-30
+  k.C[2] = 0u;
+  k.C[3] = mul_bf16x2(scale2, 0xB180B180u);     // -2^-28
+  k.C[4] = mul_bf16x2(scale2, 0xB200B200u);     // -2^-27
+  return k;
+}
 template <int POS>
-__device__ __forceinline__ uint32_t k3_field(uint32_t v, uint32_t scale2) {
+__device__ __forceinline__ uint32_t k3_field(uint32_t v, const K3Scale& k) {
   constexpr uint32_t m = (7u << POS) | (7u << (POS + 16));
-  constexpr uint32_t negb = (0xC300u | (4u << POS)) * 0x10001u;  // -(128 + 4 * 2^POS)
-  const uint32_t t = fma_bf16x2(and_or(v, m, kMagicBf16), kOneBf16x2, negb);
-  return fma_bf16x2(t, scale2, 0u);
+  return fma_bf16x2(v & m, k.S, k.C[POS]);
 }
 // One 32-bit word of each byte plane (4 INT3 groups = 32 channels of one row) -> 16 bf16x2
 // registers R[pair][code]: pair p holds groups (2p, 2p+1) in its (low, high) halves.
-__device__ __forceinline__ void k3_unpack_row(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t scale2,
+__device__ __forceinline__ void k3_unpack_row(uint32_t P0, uint32_t P1, uint32_t P2, const K3Scale& scale2,
                                               uint32_t (&R)[2][8]) {
 #pragma unroll
   for (int pr = 0; pr < 2; ++pr) {
@@ -116,18 +135,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return d;
 }
 
+// A V field as an fp16 operand without arithmetic: the masked 2-bit field, read as fp16, is the
+// subnormal code * 2^POS * 2^-24.  The codes' offset of 2 is not removed per element: one extra
+// MMA per page and group against a row of ones collects sum(P), and the epilogue forms
+// 2^(24 - POS) * acc - 2 * sum(P).
 template <int POS>
 __device__ __forceinline__ uint32_t v2_field(uint32_t v) {
   constexpr uint32_t m = (3u << POS) | (3u << (POS + 16));
-  constexpr uint32_t b = (0x6400u | (2u << POS)) * 0x10001u;
-  return hsub2_u32(and_or(v, m, kMagic), b);
+  return v & m;
 }
+constexpr uint32_t kOnesF16x2 = 0x3C003C00u;
 
 // Per-warp state that lives across pages.
 template <int QT>
 struct K3State {
   uint32_t qf[QT][8][2];   // query fragments (B operand of the K MMA)
-  float oacc[8][4];        // output accumulators, O^T fragments
+  float oacc[10][4];       // output accumulators, O^T fragments; tiles 8, 9: sum of the P operand per V group
   float m_ref0, m_ref1, l0, l1;
   uint32_t smax_bits;      // largest K group scale seen (bf16 bits; positive floats order as integers)
   uint32_t ks_sel;         // PRMT selector: this lane's K group scale into both halves
@@ -166,8 +189,8 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
     const uint32_t sc0 = prmt(ksw0, ksw0, st.ks_sel), sc1 = prmt(ksw1, ksw1, st.ks_sel);
     st.smax_bits = max(st.smax_bits, max(sc0 & 0x7FFFu, sc1 & 0x7FFFu));
     uint32_t R0[2][8], R1[2][8];
-    k3_unpack_row(kw0, kw1, kw2, sc0, R0);
-    k3_unpack_row(kw3, kw4, kw5, sc1, R1);
+    k3_unpack_row(kw0, kw1, kw2, k3_scale(sc0), R0);
+    k3_unpack_row(kw3, kw4, kw5, k3_scale(sc1), R1);
 #pragma unroll
     for (int t = 0; t < QT; ++t)
 #pragma unroll
@@ -211,6 +234,7 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
     mma_f16_16816(st.oacc[qh * 4 + 1], v2_field<4>(XA), v2_field<6>(XA), v2_field<4>(XB), v2_field<6>(XB), B0, B1);
     mma_f16_16816(st.oacc[qh * 4 + 2], v2_field<8>(XA), v2_field<0>(XA2), v2_field<8>(XB), v2_field<0>(XB2), B0, B1);
     mma_f16_16816(st.oacc[qh * 4 + 3], v2_field<2>(XA2), v2_field<4>(XA2), v2_field<2>(XB2), v2_field<4>(XB2), B0, B1);
+    mma_f16_16816(st.oacc[8 + qh], kOnesF16x2, kOnesF16x2, kOnesF16x2, kOnesF16x2, B0, B1);
   }
 }
 
@@ -290,7 +314,7 @@ scan_k3v2_kernel(const ScanParams p) {
   int64_t next_blk = 0;
   if (T::kStages < my_n) next_blk = bt_row[T::kStages * kScanWarps];
 
-  // ---- query fragments: B operand of the K MMA, scaled by 2^-pos of the code it meets.
+  // ---- query fragments: B operand of the K MMA, scaled by 2^(33 - pos) of the code it meets.
   //      Lane (head n = g, tig) covers channels 32 tig + 8 j + x (group j, code x); k-step x
   //      pairs groups (0,1) in b0 and (2,3) in b1.  A bf16 query is used as is; an fp16 query
   //      (11-bit significand) is split exactly into two bf16 terms, hi + lo. ----
@@ -313,7 +337,7 @@ scan_k3v2_kernel(const ScanParams p) {
     };
 #pragma unroll
     for (int x = 0; x < 8; ++x) {
-      const float sc = 1.0f / static_cast<float>(1 << k3_pos(x));
+      const float sc = 8589934592.0f / static_cast<float>(1 << k3_pos(x));   // 2^(33 - POS), see k3_field
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int d0 = 16 * half + x;  // group j = 2 * half
@@ -329,7 +353,7 @@ scan_k3v2_kernel(const ScanParams p) {
   }
   st.ks_sel = (tig >> 1) ? 0x3232u : 0x1010u;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
+  for (int i = 0; i < 10; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
   st.m_ref0 = kMinusBig; st.m_ref1 = kMinusBig; st.l0 = 0.f; st.l1 = 0.f;
   st.smax_bits = 0u;
   bool failed = false;
@@ -382,11 +406,12 @@ scan_k3v2_kernel(const ScanParams p) {
       const int qh = mt >> 2, ml = mt & 3;
       const int fa = 2 * ml, fb = 2 * ml + 1;
       const int da = 64 * qh + 8 * g + v2_dlocal(fa), db = 64 * qh + 8 * g + v2_dlocal(fb);
-      const float ua = 1.0f / static_cast<float>(1 << v2_pos(fa)), ub = 1.0f / static_cast<float>(1 << v2_pos(fb));
-      wo[(2 * tig) * JF_HEAD_DIM + da] = st.oacc[mt][0] * ua;
-      wo[(2 * tig + 1) * JF_HEAD_DIM + da] = st.oacc[mt][1] * ua;
-      wo[(2 * tig) * JF_HEAD_DIM + db] = st.oacc[mt][2] * ub;
-      wo[(2 * tig + 1) * JF_HEAD_DIM + db] = st.oacc[mt][3] * ub;
+      // 2^(24 - POS) * sum(P * field) - 2 * sum(P): the codes' offset leaves here (see v2_field)
+      const float ua = 16777216.0f / static_cast<float>(1 << v2_pos(fa)), ub = 16777216.0f / static_cast<float>(1 << v2_pos(fb));
+      wo[(2 * tig) * JF_HEAD_DIM + da] = fmaf(st.oacc[mt][0], ua, -2.0f * st.oacc[8 + qh][0]);
+      wo[(2 * tig + 1) * JF_HEAD_DIM + da] = fmaf(st.oacc[mt][1], ua, -2.0f * st.oacc[8 + qh][1]);
+      wo[(2 * tig) * JF_HEAD_DIM + db] = fmaf(st.oacc[mt][2], ub, -2.0f * st.oacc[8 + qh][2]);
+      wo[(2 * tig + 1) * JF_HEAD_DIM + db] = fmaf(st.oacc[mt][3], ub, -2.0f * st.oacc[8 + qh][3]);
     }
   }
   const float smax = __uint_as_float(st.smax_bits << 16);

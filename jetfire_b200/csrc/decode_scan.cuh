@@ -116,8 +116,9 @@ __device__ __forceinline__ void cta_merge_store(const ScanParams& p, uint8_t* sm
 // Online-softmax step shared by the modes: the reference point may lag the true maximum
 // by less than 4 (so exp stays below e^4 and the fp16 P operand cannot overflow); the
 // exact warp-wide maximum is only taken when a score runs ahead of it.
+template <int NT>
 __device__ __forceinline__ void softmax_step(float s0, float s1, float s2, float s3, float& m_ref0, float& m_ref1,
-                                             float& l0, float& l1, float (&oacc)[8][4], float& p0, float& p1,
+                                             float& l0, float& l1, float (&oacc)[NT][4], float& p0, float& p1,
                                              float& p2, float& p3) {
   float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
   const bool need = (mx0 > m_ref0 + 4.0f) || (mx1 > m_ref1 + 4.0f);
@@ -131,7 +132,7 @@ __device__ __forceinline__ void softmax_step(float s0, float s1, float s2, float
     const float f0 = ex2((m_ref0 - n0) * kLog2e), f1 = ex2((m_ref1 - n1) * kLog2e);
     l0 *= f0; l1 *= f1;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { oacc[i][0] *= f0; oacc[i][1] *= f1; oacc[i][2] *= f0; oacc[i][3] *= f1; }
+    for (int i = 0; i < NT; ++i) { oacc[i][0] *= f0; oacc[i][1] *= f1; oacc[i][2] *= f0; oacc[i][3] *= f1; }
     m_ref0 = n0; m_ref1 = n1;
   }
   const float mb0 = m_ref0 * kLog2e, mb1 = m_ref1 * kLog2e;

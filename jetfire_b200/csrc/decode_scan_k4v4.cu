@@ -38,13 +38,18 @@ __device__ __forceinline__ constexpr int row_token(int r) {
   return ((r >> 2) & 1) | (((r >> 1) & 1) << 2) | ((r & 1) << 1);
 }
 
+// A V nibble as an fp16 operand without any arithmetic: the masked field, read as fp16, is the
+// subnormal code * 2^POS * 2^-24 (exponent bits zero), which the tensor core multiplies exactly.
+// The codes' offset of 8 is not removed per element: the accumulators collect sum(P * code),
+// one extra MMA per page against a row of ones collects sum(P), and the epilogue forms
+// 2^(24 - POS) * acc - 8 * sum(P).  (fp32 accumulation; the accumulated terms are about three
+// times larger than with the offset removed, far inside the output tolerance.)
 template <int POS>
 __device__ __forceinline__ uint32_t v4_field(uint32_t v) {
-  // ((v & nibble) | 1024) - (1024 + 8 * 2^POS) == (code - 8) * 2^POS, exact in fp16
   constexpr uint32_t m = (15u << POS) | (15u << (POS + 16));
-  constexpr uint32_t b = (0x6400u | (8u << POS)) * 0x10001u;
-  return hsub2_u32(and_or(v, m, kMagic), b);
+  return v & m;
 }
+constexpr uint32_t kOnesF16x2 = 0x3C003C00u;
 
 __device__ __forceinline__ void mma_u8s8_cd(int (&d)[4], const int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                             uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -94,7 +99,7 @@ struct K4State {
   uint32_t qb[4][2];          // INT8 query fragments (B operand of the K MMA)
   float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
   int init[4][4];             // -8 * sum(qi) + kAccMagic per block for those heads, laid out as the MMA's C operand
-  float oacc[8][4];
+  float oacc[9][4];           // output tiles 0..7; tile 8: sum of the P operand per head (see v4_field)
   float m_ref0, m_ref1, l0, l1;
   uint32_t k_off[4];          // swizzled byte offsets of this lane's K words, per 32-channel block
   uint32_t v_offA, v_offB;    // swizzled byte offsets of this lane's V words for tokens tA, tB
@@ -172,6 +177,7 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
       mma_f16_16816(st.oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), B0, B1);
     }
   }
+  mma_f16_16816(st.oacc[8], kOnesF16x2, kOnesF16x2, kOnesF16x2, kOnesF16x2, B0, B1);
 }
 
 // Two full 16-token pages at once, written out so that the two pages' instruction streams
@@ -243,7 +249,7 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
       const float f0 = ex2((st.m_ref0 - n0) * kLog2e), f1 = ex2((st.m_ref1 - n1) * kLog2e);
       st.l0 *= f0; st.l1 *= f1;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { st.oacc[i][0] *= f0; st.oacc[i][1] *= f1; st.oacc[i][2] *= f0; st.oacc[i][3] *= f1; }
+      for (int i = 0; i < 9; ++i) { st.oacc[i][0] *= f0; st.oacc[i][1] *= f1; st.oacc[i][2] *= f0; st.oacc[i][3] *= f1; }
       st.m_ref0 = n0; st.m_ref1 = n1;
     }
     const float mb0 = st.m_ref0 * kLog2e, mb1 = st.m_ref1 * kLog2e;
@@ -279,6 +285,8 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
       mma_f16_16816(st.oacc[mt + 1], v4_field<0>(YA2), v4_field<4>(YA2), v4_field<0>(YB2), v4_field<4>(YB2), B0, B1);
     }
   }
+  mma_f16_16816(st.oacc[8], kOnesF16x2, kOnesF16x2, kOnesF16x2, kOnesF16x2, A0, A1);
+  mma_f16_16816(st.oacc[8], kOnesF16x2, kOnesF16x2, kOnesF16x2, kOnesF16x2, B0, B1);
 }
 
 }  // namespace
@@ -432,7 +440,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     }
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
+  for (int i = 0; i < 9; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
   st.m_ref0 = kMinusBig; st.m_ref1 = kMinusBig; st.l0 = 0.f; st.l1 = 0.f;
   bool failed = false;
 
@@ -513,10 +521,11 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       const int wi = mt >> 2, bp = (mt >> 1) & 1, e = mt & 1;
       const int dlo = 16 * g + 8 * wi + 4 * bp + 2 * e + 1;  // low nibble of the byte: odd channel
       const int dhi = dlo - 1;                               // high nibble: even channel
-      wo[(2 * tig) * JF_HEAD_DIM + dlo] = st.oacc[mt][0];
-      wo[(2 * tig + 1) * JF_HEAD_DIM + dlo] = st.oacc[mt][1];
-      wo[(2 * tig) * JF_HEAD_DIM + dhi] = st.oacc[mt][2] * 0.0625f;
-      wo[(2 * tig + 1) * JF_HEAD_DIM + dhi] = st.oacc[mt][3] * 0.0625f;
+      // 2^(24 - POS) * sum(P * field) - 8 * sum(P): the codes' offset leaves here (see v4_field)
+      wo[(2 * tig) * JF_HEAD_DIM + dlo] = fmaf(st.oacc[mt][0], 16777216.0f, -8.0f * st.oacc[8][0]);
+      wo[(2 * tig + 1) * JF_HEAD_DIM + dlo] = fmaf(st.oacc[mt][1], 16777216.0f, -8.0f * st.oacc[8][1]);
+      wo[(2 * tig) * JF_HEAD_DIM + dhi] = fmaf(st.oacc[mt][2], 1048576.0f, -8.0f * st.oacc[8][2]);
+      wo[(2 * tig + 1) * JF_HEAD_DIM + dhi] = fmaf(st.oacc[mt][3], 1048576.0f, -8.0f * st.oacc[8][3]);
     }
   }
   cta_merge_store(p, smem, st.l0, st.l1, st.m_ref0, st.m_ref1, 0.f, 0.f, split, hkv, b);
