@@ -480,6 +480,7 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
   const int pages = (a->max_S + 15) / 16;
   sp.pages_per_split = (pages + sp.splits - 1) / sp.splits;
+  sp.pages_per_warp = (sp.pages_per_split + kScanWarps - 1) / kScanWarps;
   sp.attn_scale = a->attn_scale;
   dim3 grid(sp.splits, a->H_kv, a->B);
   if (a->mode == JF_MODE_K3V2) {

@@ -36,10 +36,12 @@ struct ScanParams {
   int32_t* status;
   int64_t num_slots;
   int B, H_q, H_kv, G, max_S, max_blocks, splits, pages_per_split;
+  int pages_per_warp;   // a warp's contiguous share of a split: ceil(pages_per_split / kScanWarps)
   float attn_scale;
 };
 
 constexpr uint32_t kMagic = 0x64006400u;  // fp16 1024.0 in both halves
+constexpr int kBtChunk = 16;              // block-table entries fetched per load (one per lane of a half-warp)
 
 template <int DT>
 __device__ __forceinline__ float load_q(const void* q, int64_t idx) {

@@ -332,13 +332,25 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   // query) do not depend on one another: all are issued here, so the prologue pays one
   // memory latency before the first copies can start, and the query arithmetic then runs
   // while those copies are in flight.
-  const int pg_begin = split * p.pages_per_split;
-  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
+  // Warp w owns a contiguous quarter of the split's pages, so its block-table entries are
+  // contiguous too: sixteen lanes fetch sixteen entries with one load, a whole chunk ahead of
+  // its use, and park them in shared memory (kBtChunk entries per half of a two-chunk buffer).
+  // A load issued while megabytes of page copies are queued in the memory system takes several
+  // microseconds; fetched one entry at a time, a page or two ahead, those loads stalled the loop.
+  const int pg_first = split * p.pages_per_split + warp * p.pages_per_warp;
+  const int64_t* bt_w = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_first;
+  const int bt_avail = p.max_blocks - pg_first;   // entries of the row from this warp's first page on
   const int len_raw = p.seq_lens[b];
+  int64_t* bt_s = reinterpret_cast<int64_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4) +
+                  warp * (2 * kBtChunk);
+  auto bt_load = [&](int chunk) -> int64_t {   // lanes 0..15: entry 16 * chunk + lane (never read when out of range)
+    const int e = chunk * kBtChunk + lane;
+    return (lane < kBtChunk && e < bt_avail) ? bt_w[e] : -1;
+  };
+  int64_t bt_pend = bt_load(0);
   int64_t blk_first[T4::kStages];
 #pragma unroll
-  for (int it = 0; it < T4::kStages; ++it)   // entries past the row's end are never used
-    blk_first[it] = (pg_begin + warp + it * kScanWarps < p.max_blocks) ? bt_row[it * kScanWarps] : -1;
+  for (int it = 0; it < T4::kStages; ++it) blk_first[it] = __shfl_sync(0xFFFFFFFFu, bt_pend, it);
   // warp w prepares the query's 32-channel block w for the whole CTA (see below)
   uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
   if (g < p.G) {   // the 8 channels 32 w + 8 tig + {0..7} are 16 contiguous bytes
@@ -347,8 +359,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   }
   const int len = min(len_raw, p.max_S);
   const int n_pages = (len + 15) >> 4;
-  const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
-  const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;
+  const int my_n = max(0, min(min(pg_first + p.pages_per_warp, (split + 1) * p.pages_per_split), n_pages) - pg_first);
 
   const int64_t n_blocks_phys = p.num_slots >> 4;
   const int64_t row_base = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
@@ -362,7 +373,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   // this kernel writes (and the next kernel reads) in L2.
   const uint64_t stream_policy = l2_policy_evict_first();
   auto issue = [&](int it, int st_idx, int64_t blk64) {
-    const int pg = pg_begin + warp + it * kScanWarps;
+    const int pg = pg_first + it;
     const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
     const bool slow = bad || pg == last_pg;
     slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
@@ -386,9 +397,11 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       if (it < my_n) issue(it, it, blk_first[it]);
   }
   // block-table entries of the next two refills (a round refills up to two stages)
-  int64_t next_blk = 0, next_blk1 = 0;
-  if (T4::kStages < my_n) next_blk = bt_row[T4::kStages * kScanWarps];
-  if (T4::kStages + 1 < my_n) next_blk1 = bt_row[(T4::kStages + 1) * kScanWarps];
+  // chunk 0 to shared memory, chunk 1 requested
+  if (lane < kBtChunk) bt_s[lane] = bt_pend;
+  int bt_stored = 0;   // chunks 0..bt_stored are in shared memory; chunk bt_stored + 1 is in bt_pend
+  bt_pend = bt_load(1);
+  __syncwarp();
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
   //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones.
@@ -457,7 +470,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   }
   const int h0 = hkv * p.G + 2 * tig;
   float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0 +
-               static_cast<int64_t>(pg_begin + warp) * 16;
+               static_cast<int64_t>(pg_first) * 16;
   float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
@@ -484,8 +497,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     if (it == 0) JF_PHASE(3);
     const uint32_t sb = stages0 + st_idx * T4::kBytes;
     if (pair) {
-      k4v4_page_pair(st, sb, stages0 + st2 * T4::kBytes, attn, sp0, sp1, sp0 + 16 * kScanWarps, sp1 + 16 * kScanWarps,
-                     st0, st1);
+      k4v4_page_pair(st, sb, stages0 + st2 * T4::kBytes, attn, sp0, sp1, sp0 + 16, sp1 + 16, st0, st1);
     } else if (slow_mask & (1u << st_idx)) {
       k4v4_page<true>(st, sb, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
     } else {
@@ -493,14 +505,17 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     }
     __syncwarp();
     const int n_done = pair ? 2 : 1;
+    // the refills below read entries up to it + kStages + 1: bring their chunk in first
+    if (((it + T4::kStages + 1) >> 4) > bt_stored) {
+      ++bt_stored;
+      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_pend;
+      bt_pend = bt_load(bt_stored + 1);
+      __syncwarp();
+    }
     for (int k = 0; k < n_done; ++k) {
-      if (it + T4::kStages < my_n) {
-        issue(it + T4::kStages, st_idx, next_blk);
-        next_blk = next_blk1;
-        if (it + T4::kStages + 2 < my_n) next_blk1 = bt_row[(it + T4::kStages + 2) * kScanWarps];
-      }
-      sp0 += 16 * kScanWarps;
-      sp1 += 16 * kScanWarps;
+      if (it + T4::kStages < my_n) issue(it + T4::kStages, st_idx, bt_s[(it + T4::kStages) & (2 * kBtChunk - 1)]);
+      sp0 += 16;
+      sp1 += 16;
       ++it;
       if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
     }
@@ -607,7 +622,9 @@ jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaS
   if (st != JF_OK) return st;
   st = page_map(sp.v_data, rows, &v_map);
   if (st != JF_OK) return st;
-  const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4 + 1024;  // ring, barriers, page lengths, query exchange, alignment slack
+  // ring, barriers, page lengths, query exchange, block-table chunks, alignment slack
+  const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4 +
+                      kScanWarps * 2 * kBtChunk * 8 + 1024;
   static_assert(kScanWarps * T4::kStages * T4::kBytes >= kMergeBytes, "merge buffer");
   if (q_dtype == JF_DTYPE_BF16) {
     JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_BF16>, smem);
