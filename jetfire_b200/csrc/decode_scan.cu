@@ -259,6 +259,7 @@ scan_k3v2_kernel(const ScanParams p) {
   const uint32_t stages0 = smem_base + warp * (T::kStages * T::kBytes);
   const uint32_t bars0 = smem_base + kScanWarps * T::kStages * T::kBytes + warp * (T::kStages * 8);
   int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8)) + warp * T::kStages;
+  int64_t* bt_s = reinterpret_cast<int64_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8 + 4)) + warp * (2 * kBtChunk);
 
   if (lane == 0) {
     for (int s = 0; s < T::kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
@@ -269,12 +270,20 @@ scan_k3v2_kernel(const ScanParams p) {
 
   const int len = min(p.seq_lens[b], p.max_S);
   const int n_pages = (len + 15) >> 4;
-  const int pg_begin = split * p.pages_per_split;
-  const int pg_end = min(pg_begin + p.pages_per_split, n_pages);
-  // this warp's pages: pg_begin + warp, + 4, ...
-  const int my_n = (pg_end - pg_begin - warp + kScanWarps - 1) / kScanWarps;  // may be <= 0
-
-  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_begin + warp;
+  // Warp w owns a contiguous quarter of the split's pages, so its block-table entries are
+  // contiguous too: sixteen lanes fetch sixteen entries with one load, a whole chunk ahead of
+  // its use, and park them in shared memory.  (A load issued while megabytes of page copies are
+  // queued in the memory system takes microseconds; fetched one entry at a time, a page or two
+  // ahead, those loads stalled the loop.)
+  const int pg_first = split * p.pages_per_split + warp * p.pages_per_warp;
+  const int my_n = max(0, min(min(pg_first + p.pages_per_warp, (split + 1) * p.pages_per_split), n_pages) - pg_first);
+  const int64_t* bt_w = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_first;
+  const int bt_avail = p.max_blocks - pg_first;   // entries of the row from this warp's first page on
+  auto bt_load = [&](int chunk) -> int64_t {   // lanes 0..15: entry 16 * chunk + lane (never read when out of range)
+    const int e = chunk * kBtChunk + lane;
+    return (lane < kBtChunk && e < bt_avail) ? bt_w[e] : -1;
+  };
+  int64_t bt_pend = bt_load(0);
   const int64_t n_blocks_phys = p.num_slots >> 4;
 
   // One elected lane issues the four bulk copies of a page (K data, V data, K scales, V scales).
@@ -289,7 +298,7 @@ scan_k3v2_kernel(const ScanParams p) {
   const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
   uint32_t slow_mask = 0u;  // stages whose page needs the masked path
   auto issue = [&](int it, int st_idx, int64_t blk64) {
-    const int pg = pg_begin + warp + it * kScanWarps;
+    const int pg = pg_first + it;
     const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
     const bool slow = bad || pg == last_pg;
     slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
@@ -306,13 +315,15 @@ scan_k3v2_kernel(const ScanParams p) {
     }
   };
 
-  // prologue
+  // prologue: chunk 0 to shared memory, chunk 1 requested, the ring filled
+  if (lane < kBtChunk) bt_s[lane] = bt_pend;
+  int bt_stored = 0;   // chunks 0..bt_stored are in shared memory; chunk bt_stored + 1 is in bt_pend
+  bt_pend = bt_load(1);
+  __syncwarp();
   {
     const int pro = min(T::kStages, my_n);
-    for (int it = 0; it < pro; ++it) issue(it, it, bt_row[it * kScanWarps]);
+    for (int it = 0; it < pro; ++it) issue(it, it, bt_s[it]);
   }
-  int64_t next_blk = 0;
-  if (T::kStages < my_n) next_blk = bt_row[T::kStages * kScanWarps];
 
   // ---- query fragments: B operand of the K MMA, scaled by 2^(33 - pos) of the code it meets.
   //      Lane (head n = g, tig) covers channels 32 tig + 8 j + x (group j, code x); k-step x
@@ -364,7 +375,7 @@ scan_k3v2_kernel(const ScanParams p) {
   const uint32_t s_addr_off = T::kKsOff + t0 * 4;
   const int h0 = hkv * p.G + 2 * tig;
   float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0 +
-               static_cast<int64_t>(pg_begin + warp) * 16;
+               static_cast<int64_t>(pg_first) * 16;
   float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
@@ -385,12 +396,15 @@ scan_k3v2_kernel(const ScanParams p) {
     else
       k3v2_page<kQTerms, false>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, 16, attn, sp0, sp1, st0, st1);
     __syncwarp();
-    if (it + T::kStages < my_n) {
-      issue(it + T::kStages, st_idx, next_blk);
-      if (it + T::kStages + 1 < my_n) next_blk = bt_row[(it + T::kStages + 1) * kScanWarps];
+    if (((it + T::kStages) >> 4) > bt_stored) {   // the refill below reads entry it + kStages: bring its chunk in
+      ++bt_stored;
+      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_pend;
+      bt_pend = bt_load(bt_stored + 1);
+      __syncwarp();
     }
-    sp0 += 16 * kScanWarps;
-    sp1 += 16 * kScanWarps;
+    if (it + T::kStages < my_n) issue(it + T::kStages, st_idx, bt_s[(it + T::kStages) & (2 * kBtChunk - 1)]);
+    sp0 += 16;
+    sp1 += 16;
     if (++st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
@@ -485,7 +499,7 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   dim3 grid(sp.splits, a->H_kv, a->B);
   if (a->mode == JF_MODE_K3V2) {
     using T = Tile<JF_MODE_K3V2>;
-    const size_t smem = kScanWarps * T::kStages * (T::kBytes + 8 + 4);
+    const size_t smem = kScanWarps * T::kStages * (T::kBytes + 8 + 4) + kScanWarps * 2 * kBtChunk * 8;  // ring, barriers, page lengths, block-table chunks
     static_assert(kScanWarps * T::kStages * T::kBytes >= kMergeBytes, "merge buffer");
     if (a->q_dtype == JF_DTYPE_BF16) {
       JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_BF16>, smem);
