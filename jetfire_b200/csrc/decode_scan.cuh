@@ -17,7 +17,7 @@ template <> struct Tile<JF_MODE_K4V4> {
   static constexpr int kKRow = 64, kVRow = 64, kNG = 1;
   static constexpr int kKOff = 0, kVOff = 1024, kKsOff = 2048, kVsOff = 2080, kBytes = 2560;
   static constexpr int kTxBytes = 2112;
-  static constexpr int kStages = 5;   // 4 CTAs (16 warps) per SM
+  static constexpr int kStages = 4;   // 4 CTAs (16 warps) per SM
 };
 
 struct ScanParams {

@@ -321,6 +321,9 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
 
   if (lane == 0) {
     for (int s = 0; s < T4::kStages; ++s) mbar_init(&bars[s], 1);
+    // the tensor maps are kernel parameters, not results of the previous kernel: fetch them now
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map)) : "memory");
   }
   fence_barrier_init();
   __syncwarp();
