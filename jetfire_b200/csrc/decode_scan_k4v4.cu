@@ -344,16 +344,16 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int64_t* bt_w = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_first;
   const int bt_avail = p.max_blocks - pg_first;   // entries of the row from this warp's first page on
   const int len_raw = p.seq_lens[b];
-  int64_t* bt_s = reinterpret_cast<int64_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4) +
-                  warp * (2 * kBtChunk);
+  // what is parked per page: the first cache row of its block (the tensor copies' y coordinate)
+  // and how many of its 16 tokens are live -- worked out by sixteen lanes at once when a chunk
+  // arrives, so that issuing a page's copies is a shared-memory read and the copies
+  int2* bt_s = reinterpret_cast<int2*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4) +
+               warp * (2 * kBtChunk);
   auto bt_load = [&](int chunk) -> int64_t {   // lanes 0..15: entry 16 * chunk + lane (never read when out of range)
     const int e = chunk * kBtChunk + lane;
     return (lane < kBtChunk && e < bt_avail) ? bt_w[e] : -1;
   };
   int64_t bt_pend = bt_load(0);
-  int64_t blk_first[T4::kStages];
-#pragma unroll
-  for (int it = 0; it < T4::kStages; ++it) blk_first[it] = __shfl_sync(0xFFFFFFFFu, bt_pend, it);
   // warp w prepares the query's 32-channel block w for the whole CTA (see below)
   uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
   if (g < p.G) {   // the 8 channels 32 w + 8 tig + {0..7} are 16 contiguous bytes
@@ -365,9 +365,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int my_n = max(0, min(min(pg_first + p.pages_per_warp, (split + 1) * p.pages_per_split), n_pages) - pg_first);
 
   const int64_t n_blocks_phys = p.num_slots >> 4;
-  const int64_t row_base = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
-  const uint16_t* ks_h = p.k_scales + row_base;
-  const uint16_t* vs_h = p.v_scales + row_base;
+  const int64_t head_row0 = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
   const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
   uint32_t slow_mask = 0u;
 
@@ -375,36 +373,40 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   // The packed cache is read once per call: fetched as first-to-evict, it leaves the scores
   // this kernel writes (and the next kernel reads) in L2.
   const uint64_t stream_policy = l2_policy_evict_first();
-  auto issue = [&](int it, int st_idx, int64_t blk64) {
-    const int pg = pg_first + it;
+  // entry e of this warp (page pg_first + e) from its block id: an invalid block id reads
+  // block 0 and counts no live token; the sequence's last page may be partial
+  auto bt_entry = [&](int64_t blk64, int e) -> int2 {
+    const int pg = pg_first + e;
     const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
-    const bool slow = bad || pg == last_pg;
+    const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
+    return make_int2(static_cast<int>(head_row0 + (bad ? 0 : blk64) * 16), valid);
+  };
+  auto issue = [&](int st_idx, int2 ent) {
+    const bool slow = ent.y != 16;
     slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
-    const int64_t blk = bad ? 0 : blk64;
     const uint32_t bar = bars0 + st_idx * 8;
     const uint32_t dst = stages0 + st_idx * T4::kBytes;
     if (elect_one()) {
-      if (slow) page_valid[st_idx] = bad ? 0 : min(16, len - pg * 16);
+      if (slow) page_valid[st_idx] = ent.y;
       mbar_expect_tx_u32(bar, T4::kTxBytes);
-      const int y = static_cast<int>(row_base + blk * 16);
-      tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, y, bar, stream_policy);
-      tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, y, bar, stream_policy);
-      bulk_g2s_u32(dst + T4::kKsOff, ks_h + blk * 16, 32, bar);
-      bulk_g2s_u32(dst + T4::kVsOff, vs_h + blk * 16, 32, bar);
+      tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, ent.x, bar, stream_policy);
+      tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, ent.x, bar, stream_policy);
+      bulk_g2s_u32(dst + T4::kKsOff, p.k_scales + ent.x, 32, bar);
+      bulk_g2s_u32(dst + T4::kVsOff, p.v_scales + ent.x, 32, bar);
     }
   };
 
-  {
-#pragma unroll
-    for (int it = 0; it < T4::kStages; ++it)
-      if (it < my_n) issue(it, it, blk_first[it]);
-  }
-  // block-table entries of the next two refills (a round refills up to two stages)
-  // chunk 0 to shared memory, chunk 1 requested
-  if (lane < kBtChunk) bt_s[lane] = bt_pend;
+  // chunk 0 to shared memory, chunk 1 requested, the ring filled
+  if (lane < kBtChunk) bt_s[lane] = bt_entry(bt_pend, lane);
   int bt_stored = 0;   // chunks 0..bt_stored are in shared memory; chunk bt_stored + 1 is in bt_pend
   bt_pend = bt_load(1);
   __syncwarp();
+  {
+#pragma unroll
+    for (int it = 0; it < T4::kStages; ++it)
+      if (it < my_n) issue(it, bt_s[it]);
+  }
+  // block-table entries of the next two refills (a round refills up to two stages)
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
   //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones.
@@ -511,12 +513,12 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     // the refills below read entries up to it + kStages + 1: bring their chunk in first
     if (((it + T4::kStages + 1) >> 4) > bt_stored) {
       ++bt_stored;
-      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_pend;
+      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_entry(bt_pend, bt_stored * kBtChunk + lane);
       bt_pend = bt_load(bt_stored + 1);
       __syncwarp();
     }
     for (int k = 0; k < n_done; ++k) {
-      if (it + T4::kStages < my_n) issue(it + T4::kStages, st_idx, bt_s[(it + T4::kStages) & (2 * kBtChunk - 1)]);
+      if (it + T4::kStages < my_n) issue(st_idx, bt_s[(it + T4::kStages) & (2 * kBtChunk - 1)]);
       sp0 += 16;
       sp1 += 16;
       ++it;
