@@ -259,7 +259,8 @@ scan_k3v2_kernel(const ScanParams p) {
   const uint32_t stages0 = smem_base + warp * (T::kStages * T::kBytes);
   const uint32_t bars0 = smem_base + kScanWarps * T::kStages * T::kBytes + warp * (T::kStages * 8);
   int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8)) + warp * T::kStages;
-  int64_t* bt_s = reinterpret_cast<int64_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8 + 4)) + warp * (2 * kBtChunk);
+  // parked per page: the first cache row of its block and how many of its 16 tokens are live
+  int2* bt_s = reinterpret_cast<int2*>(smem + kScanWarps * T::kStages * (T::kBytes + 8 + 4)) + warp * (2 * kBtChunk);
 
   if (lane == 0) {
     for (int s = 0; s < T::kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
@@ -291,38 +292,43 @@ scan_k3v2_kernel(const ScanParams p) {
   // this kernel writes (and the next kernel reads) in L2.
   const uint64_t stream_policy = l2_policy_evict_first();
   const int64_t head_rows = static_cast<int64_t>(hkv) * p.num_slots;
-  const uint8_t* kd_h = p.k_data + head_rows * T::kKRow;
-  const uint8_t* vd_h = p.v_data + head_rows * T::kVRow;
-  const uint8_t* ks_h = reinterpret_cast<const uint8_t*>(p.k_scales + head_rows * T::kNG);
-  const uint8_t* vs_h = reinterpret_cast<const uint8_t*>(p.v_scales + head_rows * T::kNG);
+  const uint8_t* ks_b = reinterpret_cast<const uint8_t*>(p.k_scales);
+  const uint8_t* vs_b = reinterpret_cast<const uint8_t*>(p.v_scales);
   const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
   uint32_t slow_mask = 0u;  // stages whose page needs the masked path
-  auto issue = [&](int it, int st_idx, int64_t blk64) {
-    const int pg = pg_first + it;
+  // entry e of this warp (page pg_first + e) from its block id, worked out by sixteen lanes at
+  // once when a chunk arrives: an invalid block id reads block 0 and counts no live token; the
+  // sequence's last page may be partial
+  auto bt_entry = [&](int64_t blk64, int e) -> int2 {
+    const int pg = pg_first + e;
     const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
-    const bool slow = bad || pg == last_pg;
+    const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
+    return make_int2(static_cast<int>(head_rows + (bad ? 0 : blk64) * 16), valid);
+  };
+  auto issue = [&](int st_idx, int2 ent) {
+    const bool slow = ent.y != 16;
     slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
-    const int64_t blk = bad ? 0 : blk64;
     const uint32_t bar = bars0 + st_idx * 8;
     const uint32_t dst = stages0 + st_idx * T::kBytes;
+    const int64_t row = ent.x;
     if (elect_one()) {
-      if (slow) page_valid[st_idx] = bad ? 0 : min(16, len - pg * 16);
+      if (slow) page_valid[st_idx] = ent.y;
       mbar_expect_tx_u32(bar, T::kBytes);
-      bulk_g2s_u32_hint(dst + T::kKOff, kd_h + blk * (16 * T::kKRow), 16 * T::kKRow, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T::kVOff, vd_h + blk * (16 * T::kVRow), 16 * T::kVRow, bar, stream_policy);
-      bulk_g2s_u32(dst + T::kKsOff, ks_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
-      bulk_g2s_u32(dst + T::kVsOff, vs_h + blk * (32 * T::kNG), 32 * T::kNG, bar);
+      bulk_g2s_u32_hint(dst + T::kKOff, p.k_data + row * T::kKRow, 16 * T::kKRow, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + row * T::kVRow, 16 * T::kVRow, bar, stream_policy);
+      bulk_g2s_u32(dst + T::kKsOff, ks_b + row * (2 * T::kNG), 32 * T::kNG, bar);
+      bulk_g2s_u32(dst + T::kVsOff, vs_b + row * (2 * T::kNG), 32 * T::kNG, bar);
     }
   };
 
   // prologue: chunk 0 to shared memory, chunk 1 requested, the ring filled
-  if (lane < kBtChunk) bt_s[lane] = bt_pend;
+  if (lane < kBtChunk) bt_s[lane] = bt_entry(bt_pend, lane);
   int bt_stored = 0;   // chunks 0..bt_stored are in shared memory; chunk bt_stored + 1 is in bt_pend
   bt_pend = bt_load(1);
   __syncwarp();
   {
     const int pro = min(T::kStages, my_n);
-    for (int it = 0; it < pro; ++it) issue(it, it, bt_s[it]);
+    for (int it = 0; it < pro; ++it) issue(it, bt_s[it]);
   }
 
   // ---- query fragments: B operand of the K MMA, scaled by 2^(33 - pos) of the code it meets.
@@ -398,11 +404,11 @@ scan_k3v2_kernel(const ScanParams p) {
     __syncwarp();
     if (((it + T::kStages) >> 4) > bt_stored) {   // the refill below reads entry it + kStages: bring its chunk in
       ++bt_stored;
-      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_pend;
+      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_entry(bt_pend, bt_stored * kBtChunk + lane);
       bt_pend = bt_load(bt_stored + 1);
       __syncwarp();
     }
-    if (it + T::kStages < my_n) issue(it + T::kStages, st_idx, bt_s[(it + T::kStages) & (2 * kBtChunk - 1)]);
+    if (it + T::kStages < my_n) issue(st_idx, bt_s[(it + T::kStages) & (2 * kBtChunk - 1)]);
     sp0 += 16;
     sp1 += 16;
     if (++st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
