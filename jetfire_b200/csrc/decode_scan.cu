@@ -258,7 +258,6 @@ scan_k3v2_kernel(const ScanParams p) {
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t stages0 = smem_base + warp * (T::kStages * T::kBytes);
   const uint32_t bars0 = smem_base + kScanWarps * T::kStages * T::kBytes + warp * (T::kStages * 8);
-  int32_t* page_valid = reinterpret_cast<int32_t*>(smem + kScanWarps * T::kStages * (T::kBytes + 8)) + warp * T::kStages;
   // parked per page: the first cache row of its block and how many of its 16 tokens are live
   int2* bt_s = reinterpret_cast<int2*>(smem + kScanWarps * T::kStages * (T::kBytes + 8 + 4)) + warp * (2 * kBtChunk);
 
@@ -295,7 +294,6 @@ scan_k3v2_kernel(const ScanParams p) {
   const uint8_t* ks_b = reinterpret_cast<const uint8_t*>(p.k_scales);
   const uint8_t* vs_b = reinterpret_cast<const uint8_t*>(p.v_scales);
   const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
-  uint32_t slow_mask = 0u;  // stages whose page needs the masked path
   // entry e of this warp (page pg_first + e) from its block id, worked out by sixteen lanes at
   // once when a chunk arrives: an invalid block id reads block 0 and counts no live token; the
   // sequence's last page may be partial
@@ -306,13 +304,10 @@ scan_k3v2_kernel(const ScanParams p) {
     return make_int2(static_cast<int>(head_rows + (bad ? 0 : blk64) * 16), valid);
   };
   auto issue = [&](int st_idx, int2 ent) {
-    const bool slow = ent.y != 16;
-    slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
     const uint32_t bar = bars0 + st_idx * 8;
     const uint32_t dst = stages0 + st_idx * T::kBytes;
     const int64_t row = ent.x;
     if (elect_one()) {
-      if (slow) page_valid[st_idx] = ent.y;
       mbar_expect_tx_u32(bar, T::kBytes);
       bulk_g2s_u32_hint(dst + T::kKOff, p.k_data + row * T::kKRow, 16 * T::kKRow, bar, stream_policy);
       bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + row * T::kVRow, 16 * T::kVRow, bar, stream_policy);
@@ -397,8 +392,9 @@ scan_k3v2_kernel(const ScanParams p) {
       break;
     }
     const uint32_t sb = stages0 + st_idx * T::kBytes;
-    if (slow_mask & (1u << st_idx))
-      k3v2_page<kQTerms, true>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
+    const int live = bt_s[it & (2 * kBtChunk - 1)].y;   // the page's parked entry is still resident
+    if (live != 16)
+      k3v2_page<kQTerms, true>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, live, attn, sp0, sp1, st0, st1);
     else
       k3v2_page<kQTerms, false>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, 16, attn, sp0, sp1, st0, st1);
     __syncwarp();

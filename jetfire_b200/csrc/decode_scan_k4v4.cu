@@ -316,8 +316,6 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const uint32_t stages0 = smem_base + warp * (T4::kStages * T4::kBytes);
   const uint32_t bars0 = smem_base + kScanWarps * T4::kStages * T4::kBytes + warp * (T4::kStages * 8);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * T4::kStages * T4::kBytes) + warp * T4::kStages;
-  int32_t* page_valid =
-      reinterpret_cast<int32_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8)) + warp * T4::kStages;
 
   if (lane == 0) {
     for (int s = 0; s < T4::kStages; ++s) mbar_init(&bars[s], 1);
@@ -367,7 +365,6 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int64_t n_blocks_phys = p.num_slots >> 4;
   const int64_t head_row0 = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
   const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
-  uint32_t slow_mask = 0u;
 
   // One elected lane issues the page's two tensor copies (K, V) and two scale copies.
   // The packed cache is read once per call: fetched as first-to-evict, it leaves the scores
@@ -382,12 +379,9 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     return make_int2(static_cast<int>(head_row0 + (bad ? 0 : blk64) * 16), valid);
   };
   auto issue = [&](int st_idx, int2 ent) {
-    const bool slow = ent.y != 16;
-    slow_mask = (slow_mask & ~(1u << st_idx)) | (static_cast<uint32_t>(slow) << st_idx);
     const uint32_t bar = bars0 + st_idx * 8;
     const uint32_t dst = stages0 + st_idx * T4::kBytes;
     if (elect_one()) {
-      if (slow) page_valid[st_idx] = ent.y;
       mbar_expect_tx_u32(bar, T4::kTxBytes);
       tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, ent.x, bar, stream_policy);
       tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, ent.x, bar, stream_policy);
@@ -490,7 +484,10 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     int st2 = st_idx + 1;
     uint32_t par2 = parity;
     if (st2 == T4::kStages) { st2 = 0; par2 ^= 1u; }
-    const bool pair = (it + 1 < my_n) && !(slow_mask & ((1u << st_idx) | (1u << st2)));
+    // live tokens of this page and the next, from their parked entries (still resident: a chunk
+    // is overwritten 16 pages after its last entry was issued)
+    const int live_a = bt_s[it & (2 * kBtChunk - 1)].y, live_b = bt_s[(it + 1) & (2 * kBtChunk - 1)].y;
+    const bool pair = (it + 1 < my_n) && live_a == 16 && live_b == 16;
     bool ok = mbar_wait(&bars[st_idx], parity);
     if (ok && pair) ok = mbar_wait(&bars[st2], par2);
     if (!ok) {
@@ -503,8 +500,8 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     const uint32_t sb = stages0 + st_idx * T4::kBytes;
     if (pair) {
       k4v4_page_pair(st, sb, stages0 + st2 * T4::kBytes, attn, sp0, sp1, sp0 + 16, sp1 + 16, st0, st1);
-    } else if (slow_mask & (1u << st_idx)) {
-      k4v4_page<true>(st, sb, t0, page_valid[st_idx], attn, sp0, sp1, st0, st1);
+    } else if (live_a != 16) {
+      k4v4_page<true>(st, sb, t0, live_a, attn, sp0, sp1, st0, st1);
     } else {
       k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
     }
