@@ -378,16 +378,20 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
     return make_int2(static_cast<int>(head_row0 + (bad ? 0 : blk64) * 16), valid);
   };
-  auto issue = [&](int st_idx, int2 ent) {
+  auto copies = [&](int st_idx, int row) {   // by one lane: a page's four copies into a stage
     const uint32_t bar = bars0 + st_idx * 8;
     const uint32_t dst = stages0 + st_idx * T4::kBytes;
-    if (elect_one()) {
-      mbar_expect_tx_u32(bar, T4::kTxBytes);
-      tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, ent.x, bar, stream_policy);
-      tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, ent.x, bar, stream_policy);
-      bulk_g2s_u32(dst + T4::kKsOff, p.k_scales + ent.x, 32, bar);
-      bulk_g2s_u32(dst + T4::kVsOff, p.v_scales + ent.x, 32, bar);
-    }
+    mbar_expect_tx_u32(bar, T4::kTxBytes);
+    tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, row, bar, stream_policy);
+    tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, row, bar, stream_policy);
+    bulk_g2s_u32(dst + T4::kKsOff, p.k_scales + row, 32, bar);
+    bulk_g2s_u32(dst + T4::kVsOff, p.v_scales + row, 32, bar);
+  };
+  auto issue = [&](int st_idx, int2 ent) {
+    if (elect_one()) copies(st_idx, ent.x);
+  };
+  auto issue2 = [&](int st_a, int2 ent_a, int st_b, int2 ent_b) {
+    if (elect_one()) { copies(st_a, ent_a.x); copies(st_b, ent_b.x); }
   };
 
   // chunk 0 to shared memory, chunk 1 requested, the ring filled
@@ -506,7 +510,6 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
     }
     __syncwarp();
-    const int n_done = pair ? 2 : 1;
     // the refills below read entries up to it + kStages + 1: bring their chunk in first
     if (((it + T4::kStages + 1) >> 4) > bt_stored) {
       ++bt_stored;
@@ -514,13 +517,23 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       bt_pend = bt_load(bt_stored + 1);
       __syncwarp();
     }
-    for (int k = 0; k < n_done; ++k) {
-      if (it + T4::kStages < my_n) issue(st_idx, bt_s[(it + T4::kStages) & (2 * kBtChunk - 1)]);
+    const int e0 = it + T4::kStages;   // first page to fetch into the stage(s) just freed
+    if (pair) {
+      if (e0 + 1 < my_n) issue2(st_idx, bt_s[e0 & (2 * kBtChunk - 1)], st2, bt_s[(e0 + 1) & (2 * kBtChunk - 1)]);
+      else if (e0 < my_n) issue(st_idx, bt_s[e0 & (2 * kBtChunk - 1)]);
+      sp0 += 32;
+      sp1 += 32;
+      it += 2;
+      st_idx = st2 + 1;
+      parity = par2;
+    } else {
+      if (e0 < my_n) issue(st_idx, bt_s[e0 & (2 * kBtChunk - 1)]);
       sp0 += 16;
       sp1 += 16;
       ++it;
-      if (++st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
+      ++st_idx;
     }
+    if (st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
   JF_PHASE(4);
