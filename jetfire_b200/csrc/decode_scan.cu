@@ -303,17 +303,20 @@ scan_k3v2_kernel(const ScanParams p) {
     const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
     return make_int2(static_cast<int>(head_rows + (bad ? 0 : blk64) * 16), valid);
   };
-  auto issue = [&](int st_idx, int2 ent) {
+  auto copies = [&](int st_idx, int64_t row) {   // by one lane: a page's four copies into a stage
     const uint32_t bar = bars0 + st_idx * 8;
     const uint32_t dst = stages0 + st_idx * T::kBytes;
-    const int64_t row = ent.x;
-    if (elect_one()) {
-      mbar_expect_tx_u32(bar, T::kBytes);
-      bulk_g2s_u32_hint(dst + T::kKOff, p.k_data + row * T::kKRow, 16 * T::kKRow, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + row * T::kVRow, 16 * T::kVRow, bar, stream_policy);
-      bulk_g2s_u32(dst + T::kKsOff, ks_b + row * (2 * T::kNG), 32 * T::kNG, bar);
-      bulk_g2s_u32(dst + T::kVsOff, vs_b + row * (2 * T::kNG), 32 * T::kNG, bar);
-    }
+    mbar_expect_tx_u32(bar, T::kBytes);
+    bulk_g2s_u32_hint(dst + T::kKOff, p.k_data + row * T::kKRow, 16 * T::kKRow, bar, stream_policy);
+    bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + row * T::kVRow, 16 * T::kVRow, bar, stream_policy);
+    bulk_g2s_u32(dst + T::kKsOff, ks_b + row * (2 * T::kNG), 32 * T::kNG, bar);
+    bulk_g2s_u32(dst + T::kVsOff, vs_b + row * (2 * T::kNG), 32 * T::kNG, bar);
+  };
+  auto issue = [&](int st_idx, int2 ent) {
+    if (elect_one()) copies(st_idx, ent.x);
+  };
+  auto issue2 = [&](int st_idx, int2 ent_a, int2 ent_b) {   // stages st_idx and st_idx + 1
+    if (elect_one()) { copies(st_idx, ent_a.x); copies(st_idx + 1, ent_b.x); }
   };
 
   // prologue: chunk 0 to shared memory, chunk 1 requested, the ring filled
@@ -381,33 +384,46 @@ scan_k3v2_kernel(const ScanParams p) {
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
 
+  // Two pages per round (the ring depth is even, so a round's stages are st_idx and st_idx + 1
+  // and share a phase): the pages are processed one after the other, and the ring bookkeeping
+  // and the election of the copying lane are paid once per round.
+  static_assert(T::kStages % 2 == 0, "a round takes two adjacent stages");
   int st_idx = 0;
   uint32_t parity = 0u;
-  for (int it = 0; it < my_n; ++it) {
-    if (!mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + st_idx, parity)) {
-      // give the copies that were already issued a short, bounded chance to land
-      for (int j = it + 1; j < min(my_n, it + T::kStages); ++j)
-        mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + (j % T::kStages), (j / T::kStages) & 1, 1000000ull);
-      failed = true;
-      break;
+  for (int it = 0; it < my_n && !failed;) {
+    const int n_here = (it + 1 < my_n) ? 2 : 1;
+#pragma unroll 1
+    for (int k = 0; k < n_here; ++k) {
+      if (!mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + st_idx + k, parity)) {
+        // give the copies that were already issued a short, bounded chance to land
+        for (int j = it + k + 1; j < min(my_n, it + T::kStages); ++j)
+          mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + (j % T::kStages), (j / T::kStages) & 1, 1000000ull);
+        failed = true;
+        break;
+      }
+      const uint32_t sb = stages0 + (st_idx + k) * T::kBytes;
+      const int live = bt_s[(it + k) & (2 * kBtChunk - 1)].y;   // the page's parked entry is still resident
+      if (live != 16)
+        k3v2_page<kQTerms, true>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, live, attn, sp0, sp1, st0, st1);
+      else
+        k3v2_page<kQTerms, false>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, 16, attn, sp0, sp1, st0, st1);
+      sp0 += 16;
+      sp1 += 16;
     }
-    const uint32_t sb = stages0 + st_idx * T::kBytes;
-    const int live = bt_s[it & (2 * kBtChunk - 1)].y;   // the page's parked entry is still resident
-    if (live != 16)
-      k3v2_page<kQTerms, true>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, live, attn, sp0, sp1, st0, st1);
-    else
-      k3v2_page<kQTerms, false>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, 16, attn, sp0, sp1, st0, st1);
+    if (failed) break;
     __syncwarp();
-    if (((it + T::kStages) >> 4) > bt_stored) {   // the refill below reads entry it + kStages: bring its chunk in
+    if (((it + T::kStages + 1) >> 4) > bt_stored) {   // the refills below read entries up to it + kStages + 1
       ++bt_stored;
       if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_entry(bt_pend, bt_stored * kBtChunk + lane);
       bt_pend = bt_load(bt_stored + 1);
       __syncwarp();
     }
-    if (it + T::kStages < my_n) issue(st_idx, bt_s[(it + T::kStages) & (2 * kBtChunk - 1)]);
-    sp0 += 16;
-    sp1 += 16;
-    if (++st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
+    const int e0 = it + T::kStages;   // first page to fetch into the stages just freed
+    if (e0 + 1 < my_n) issue2(st_idx, bt_s[e0 & (2 * kBtChunk - 1)], bt_s[(e0 + 1) & (2 * kBtChunk - 1)]);
+    else if (e0 < my_n) issue(st_idx, bt_s[e0 & (2 * kBtChunk - 1)]);
+    it += n_here;
+    st_idx += 2;   // a single page only ends the range
+    if (st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
   }
 
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
