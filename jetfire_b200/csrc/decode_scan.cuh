@@ -13,11 +13,18 @@ template <> struct Tile<JF_MODE_K3V2> {
   static constexpr int kStages = 8;   // pages in flight per warp
 };
 template <> struct Tile<JF_MODE_K4V4> {
-  // K and V tiles are written by swizzled tensor copies and sit on 1024-byte boundaries
+  // A warp's ring is made of two-page slots: [K page A | K page B | V page A | V page B |
+  // K scales A, B | V scales A, B].  Two pages whose blocks are neighbours in the cache are
+  // fetched as one 32-row tensor copy per tensor and one 64-byte copy per scale array; the
+  // tiles are written by swizzled tensor copies and sit on 1024-byte boundaries.
   static constexpr int kKRow = 64, kVRow = 64, kNG = 1;
-  static constexpr int kKOff = 0, kVOff = 1024, kKsOff = 2048, kVsOff = 2080, kBytes = 2560;
-  static constexpr int kTxBytes = 2112;
-  static constexpr int kStages = 4;   // 4 CTAs (16 warps) per SM
+  static constexpr int kPageBytes = 1024;                 // K (or V) data of one page
+  static constexpr int kVOff = 2048;                      // V page, from the K page of the same half
+  static constexpr int kScaleOff = 4096;                  // K scales of half 0, from the slot base
+  static constexpr int kVsOff = 64;                       // V scales, from the K scales of the same half
+  static constexpr int kSlotBytes = 4608;
+  static constexpr int kPageTx = 2112;                    // bytes that land per page
+  static constexpr int kSlots = 2;                        // two-page slots per warp (4 CTAs = 16 warps per SM)
 };
 
 struct ScanParams {

@@ -95,6 +95,16 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 constexpr int kAccMagic = 0x4B400000;
 __device__ __forceinline__ float acc_to_f32(int acc_biased) { return __int_as_float(acc_biased) - 12582912.0f; }
 
+// Shared memory of a CTA: the warps' rings, their barriers (one per two-page slot), the query
+// exchange buffer, the parked block-table entries.
+constexpr int kPagesInFlight = 2 * T4::kSlots;                                  // per warp
+constexpr int kRingBytes = kScanWarps * T4::kSlots * T4::kSlotBytes;
+constexpr int kBarOff = kRingBytes;
+constexpr int kQxOff = kBarOff + 64;                                            // 4 warps x 2 barriers
+constexpr int kBtOff = kQxOff + kScanWarps * 6 * 32 * 4;
+constexpr int kSmemBytes = kBtOff + kScanWarps * 2 * kBtChunk * 8 + 1024;       // + alignment slack
+static_assert(kScanWarps * T4::kSlots * 8 <= 64 && kRingBytes >= kMergeBytes && kBtOff % 16 == 0, "layout");
+
 struct K4State {
   uint32_t qb[4][2];          // INT8 query fragments (B operand of the K MMA)
   float qs_h0[4], qs_h1[4];   // block scales of the heads this lane's score columns belong to
@@ -107,9 +117,11 @@ struct K4State {
 };
 
 // One 16-token page; kPartial as in the K3V2 kernel.
+// `sb` = shared-memory address of the page's K tile (its V tile follows at kVOff), `ss` = of its
+// K scales (its V scales follow at kVsOff).
 template <bool kPartial>
-__device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int valid, float attn, float* sp0,
-                                          float* sp1, bool st0, bool st1) {
+__device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, uint32_t ss, int t0, int valid, float attn,
+                                          float* sp0, float* sp1, bool st0, bool st1) {
   // ---------------- K: nibbles -> u8 fragments, exact integer Q.K^T per block ----------------
   // all shared-memory reads of the page are issued up front
   uint32_t kw[4][2];
@@ -118,8 +130,8 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
     const uint32_t a = sb + st.k_off[c];
     kw[c][0] = lds32<0>(a); kw[c][1] = lds32<512>(a);
   }
-  const uint32_t sa = sb + st.s_off;
-  const uint32_t ksb0 = lds16<0>(sa), ksb1 = lds16<16>(sa), vsb0 = lds16<32>(sa), vsb1 = lds16<48>(sa);
+  const uint32_t sa = ss + st.s_off;
+  const uint32_t ksb0 = lds16<0>(sa), ksb1 = lds16<16>(sa), vsb0 = lds16<T4::kVsOff>(sa), vsb1 = lds16<T4::kVsOff + 16>(sa);
   const uint32_t aA = sb + st.v_offA, aB = sb + st.v_offB;
   const uint2 Wa = lds64<0>(aA), Wb = lds64<0>(aB), Wc = lds64<512>(aA), Wd = lds64<512>(aB);
   int acc[4][4];
@@ -186,8 +198,9 @@ __device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, int t0, int 
 // reference-point check instead of two), then the P.V MMAs of both pages into the same
 // accumulator tiles.  A warp is one long dependent chain per page; with four warps per
 // scheduler that chain, not the instruction count, set the pace.
-__device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32_t sbB, float attn, float* spA0,
-                                               float* spA1, float* spB0, float* spB1, bool st0, bool st1) {
+__device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32_t sbB, uint32_t ssA, uint32_t ssB,
+                                               float attn, float* spA0, float* spA1, float* spB0, float* spB1,
+                                               bool st0, bool st1) {
   uint32_t kwA[4][2], kwB[4][2];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -195,9 +208,9 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
     kwA[c][0] = lds32<0>(a); kwA[c][1] = lds32<512>(a);
     kwB[c][0] = lds32<0>(b); kwB[c][1] = lds32<512>(b);
   }
-  const uint32_t saA = sbA + st.s_off, saB = sbB + st.s_off;
-  const uint32_t ksA0 = lds16<0>(saA), ksA1 = lds16<16>(saA), vsA0b = lds16<32>(saA), vsA1b = lds16<48>(saA);
-  const uint32_t ksB0 = lds16<0>(saB), ksB1 = lds16<16>(saB), vsB0b = lds16<32>(saB), vsB1b = lds16<48>(saB);
+  const uint32_t saA = ssA + st.s_off, saB = ssB + st.s_off;
+  const uint32_t ksA0 = lds16<0>(saA), ksA1 = lds16<16>(saA), vsA0b = lds16<T4::kVsOff>(saA), vsA1b = lds16<T4::kVsOff + 16>(saA);
+  const uint32_t ksB0 = lds16<0>(saB), ksB1 = lds16<16>(saB), vsB0b = lds16<T4::kVsOff>(saB), vsB1b = lds16<T4::kVsOff + 16>(saB);
   int accA[4][4], accB[4][4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -294,7 +307,8 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
 template <int DT>
 __global__ void __launch_bounds__(kScanWarps * 32, 4)
 scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
-                 const __grid_constant__ CUtensorMap v_map) {
+                 const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_map2,
+                 const __grid_constant__ CUtensorMap v_map2) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // swizzled tiles must sit on 512-byte boundaries: align by hand (1 KB of slack is allocated)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -313,15 +327,15 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t stages0 = smem_base + warp * (T4::kStages * T4::kBytes);
-  const uint32_t bars0 = smem_base + kScanWarps * T4::kStages * T4::kBytes + warp * (T4::kStages * 8);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kScanWarps * T4::kStages * T4::kBytes) + warp * T4::kStages;
+  const uint32_t slots0 = smem_base + warp * (T4::kSlots * T4::kSlotBytes);
+  const uint32_t bars0 = smem_base + kBarOff + warp * (T4::kSlots * 8);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff) + warp * T4::kSlots;
 
   if (lane == 0) {
-    for (int s = 0; s < T4::kStages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < T4::kSlots; ++s) mbar_init(&bars[s], 1);
     // the tensor maps are kernel parameters, not results of the previous kernel: fetch them now
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map2)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map2)) : "memory");
   }
   fence_barrier_init();
   __syncwarp();
@@ -345,8 +359,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   // what is parked per page: the first cache row of its block (the tensor copies' y coordinate)
   // and how many of its 16 tokens are live -- worked out by sixteen lanes at once when a chunk
   // arrives, so that issuing a page's copies is a shared-memory read and the copies
-  int2* bt_s = reinterpret_cast<int2*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4) +
-               warp * (2 * kBtChunk);
+  int2* bt_s = reinterpret_cast<int2*>(smem + kBtOff) + warp * (2 * kBtChunk);
   auto bt_load = [&](int chunk) -> int64_t {   // lanes 0..15: entry 16 * chunk + lane (never read when out of range)
     const int e = chunk * kBtChunk + lane;
     return (lane < kBtChunk && e < bt_avail) ? bt_w[e] : -1;
@@ -378,20 +391,35 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
     return make_int2(static_cast<int>(head_row0 + (bad ? 0 : blk64) * 16), valid);
   };
-  auto copies = [&](int st_idx, int row) {   // by one lane: a page's four copies into a stage
-    const uint32_t bar = bars0 + st_idx * 8;
-    const uint32_t dst = stages0 + st_idx * T4::kBytes;
-    mbar_expect_tx_u32(bar, T4::kTxBytes);
-    tma_load_2d_u32(dst + T4::kKOff, &k_map, 0, row, bar, stream_policy);
-    tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, row, bar, stream_policy);
-    bulk_g2s_u32(dst + T4::kKsOff, p.k_scales + row, 32, bar);
-    bulk_g2s_u32(dst + T4::kVsOff, p.v_scales + row, 32, bar);
-  };
-  auto issue = [&](int st_idx, int2 ent) {
-    if (elect_one()) copies(st_idx, ent.x);
-  };
-  auto issue2 = [&](int st_a, int2 ent_a, int st_b, int2 ent_b) {
-    if (elect_one()) { copies(st_a, ent_a.x); copies(st_b, ent_b.x); }
+  // By one elected lane: the copies of one or two pages into slot `sl`.  Two pages whose blocks
+  // are neighbours in the cache take one 32-row tensor copy per tensor and one 64-byte copy per
+  // scale array; otherwise each page takes its own four copies.  Either way everything lands on
+  // the slot's barrier.
+  auto refill = [&](int sl, int2 ent_a, int2 ent_b, bool two) {
+    if (elect_one()) {
+      const uint32_t bar = bars0 + sl * 8;
+      const uint32_t dst = slots0 + sl * T4::kSlotBytes;
+      const int ra = ent_a.x, rb = ent_b.x;
+      if (two && rb == ra + 16) {
+        mbar_expect_tx_u32(bar, 2 * T4::kPageTx);
+        tma_load_2d_u32(dst, &k_map2, 0, ra, bar, stream_policy);
+        tma_load_2d_u32(dst + T4::kVOff, &v_map2, 0, ra, bar, stream_policy);
+        bulk_g2s_u32(dst + T4::kScaleOff, p.k_scales + ra, 64, bar);
+        bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff, p.v_scales + ra, 64, bar);
+      } else {
+        mbar_expect_tx_u32(bar, two ? 2 * T4::kPageTx : T4::kPageTx);
+        tma_load_2d_u32(dst, &k_map, 0, ra, bar, stream_policy);
+        tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, ra, bar, stream_policy);
+        bulk_g2s_u32(dst + T4::kScaleOff, p.k_scales + ra, 32, bar);
+        bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff, p.v_scales + ra, 32, bar);
+        if (two) {
+          tma_load_2d_u32(dst + T4::kPageBytes, &k_map, 0, rb, bar, stream_policy);
+          tma_load_2d_u32(dst + T4::kPageBytes + T4::kVOff, &v_map, 0, rb, bar, stream_policy);
+          bulk_g2s_u32(dst + T4::kScaleOff + 32, p.k_scales + rb, 32, bar);
+          bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff + 32, p.v_scales + rb, 32, bar);
+        }
+      }
+    }
   };
 
   // chunk 0 to shared memory, chunk 1 requested, the ring filled
@@ -401,10 +429,9 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   __syncwarp();
   {
 #pragma unroll
-    for (int it = 0; it < T4::kStages; ++it)
-      if (it < my_n) issue(it, bt_s[it]);
+    for (int sl = 0; sl < T4::kSlots; ++sl)
+      if (2 * sl < my_n) refill(sl, bt_s[2 * sl], bt_s[2 * sl + 1], 2 * sl + 1 < my_n);
   }
-  // block-table entries of the next two refills (a round refills up to two stages)
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
   //      32c + 8 tig + {0..7}; even channels meet the high nibbles, odd the low ones.
@@ -413,7 +440,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   K4State st;
   {
     static_assert(kScanWarps == 4, "one warp per 32-channel query block");
-    uint32_t* qx = reinterpret_cast<uint32_t*>(smem + kScanWarps * T4::kStages * (T4::kBytes + 8 + 4));  // [c][6][32]
+    uint32_t* qx = reinterpret_cast<uint32_t*>(smem + kQxOff);  // [c][6][32]
     {
       float v[8];
       float amax = 0.f;
@@ -466,10 +493,10 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     const int tA = row_token(2 * tig), tB = row_token(2 * tig + 1);  // tokens of P.V k-slots
     const int vchunk = g >> 1, vsub = 8 * (g & 1);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) st.k_off[c] = T4::kKOff + t0 * 64 + 4 * tig + ((c ^ ksw) << 4);
+    for (int c = 0; c < 4; ++c) st.k_off[c] = t0 * 64 + 4 * tig + ((c ^ ksw) << 4);
     st.v_offA = T4::kVOff + tA * 64 + ((vchunk ^ ((tA >> 1) & 3)) << 4) + vsub;
     st.v_offB = T4::kVOff + tB * 64 + ((vchunk ^ ((tB >> 1) & 3)) << 4) + vsub;
-    st.s_off = T4::kKsOff + t0 * 2;
+    st.s_off = t0 * 2;
   }
   const int h0 = hkv * p.G + 2 * tig;
   float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0 +
@@ -480,60 +507,46 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
 
   JF_PHASE(2);
   JF_CTA_STAMP(cta_lin, 2);
-  int st_idx = 0;
+  // A round takes one slot: two pages (one at the end of the range).  Two full pages go through
+  // the interleaved pair path; a partial or invalid page is processed on its own.
+  int sl = 0;
   uint32_t parity = 0u;
-  int it = 0;
-  while (it < my_n) {
-    // two pages per round when both are full pages; a partial / invalid page goes alone
-    int st2 = st_idx + 1;
-    uint32_t par2 = parity;
-    if (st2 == T4::kStages) { st2 = 0; par2 ^= 1u; }
-    // live tokens of this page and the next, from their parked entries (still resident: a chunk
-    // is overwritten 16 pages after its last entry was issued)
+  for (int it = 0; it < my_n; it += 2) {
+    const bool two = it + 1 < my_n;
+    // live tokens of the pages, from their parked entries (still resident: a chunk is
+    // overwritten 16 pages after its last entry was issued)
     const int live_a = bt_s[it & (2 * kBtChunk - 1)].y, live_b = bt_s[(it + 1) & (2 * kBtChunk - 1)].y;
-    const bool pair = (it + 1 < my_n) && live_a == 16 && live_b == 16;
-    bool ok = mbar_wait(&bars[st_idx], parity);
-    if (ok && pair) ok = mbar_wait(&bars[st2], par2);
-    if (!ok) {
-      for (int j = it + 1; j < min(my_n, it + T4::kStages); ++j)
-        mbar_wait(&bars[j % T4::kStages], (j / T4::kStages) & 1, 1000000ull);
+    if (!mbar_wait(&bars[sl], parity)) {
+      if (it + 2 < my_n) mbar_wait(&bars[sl ^ 1], parity ^ static_cast<uint32_t>(sl), 1000000ull);
       failed = true;
       break;
     }
     if (it == 0) JF_PHASE(3);
-    const uint32_t sb = stages0 + st_idx * T4::kBytes;
-    if (pair) {
-      k4v4_page_pair(st, sb, stages0 + st2 * T4::kBytes, attn, sp0, sp1, sp0 + 16, sp1 + 16, st0, st1);
-    } else if (live_a != 16) {
-      k4v4_page<true>(st, sb, t0, live_a, attn, sp0, sp1, st0, st1);
+    const uint32_t sb = slots0 + sl * T4::kSlotBytes, ss = sb + T4::kScaleOff;
+    if (two && live_a == 16 && live_b == 16) {
+      k4v4_page_pair(st, sb, sb + T4::kPageBytes, ss, ss + 32, attn, sp0, sp1, sp0 + 16, sp1 + 16, st0, st1);
     } else {
-      k4v4_page<false>(st, sb, t0, 16, attn, sp0, sp1, st0, st1);
+      if (live_a != 16) k4v4_page<true>(st, sb, ss, t0, live_a, attn, sp0, sp1, st0, st1);
+      else k4v4_page<false>(st, sb, ss, t0, 16, attn, sp0, sp1, st0, st1);
+      if (two) {
+        if (live_b != 16) k4v4_page<true>(st, sb + T4::kPageBytes, ss + 32, t0, live_b, attn, sp0 + 16, sp1 + 16, st0, st1);
+        else k4v4_page<false>(st, sb + T4::kPageBytes, ss + 32, t0, 16, attn, sp0 + 16, sp1 + 16, st0, st1);
+      }
     }
     __syncwarp();
-    // the refills below read entries up to it + kStages + 1: bring their chunk in first
-    if (((it + T4::kStages + 1) >> 4) > bt_stored) {
+    // the refill below reads entries up to it + kPagesInFlight + 1: bring their chunk in first
+    if (((it + kPagesInFlight + 1) >> 4) > bt_stored) {
       ++bt_stored;
       if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_entry(bt_pend, bt_stored * kBtChunk + lane);
       bt_pend = bt_load(bt_stored + 1);
       __syncwarp();
     }
-    const int e0 = it + T4::kStages;   // first page to fetch into the stage(s) just freed
-    if (pair) {
-      if (e0 + 1 < my_n) issue2(st_idx, bt_s[e0 & (2 * kBtChunk - 1)], st2, bt_s[(e0 + 1) & (2 * kBtChunk - 1)]);
-      else if (e0 < my_n) issue(st_idx, bt_s[e0 & (2 * kBtChunk - 1)]);
-      sp0 += 32;
-      sp1 += 32;
-      it += 2;
-      st_idx = st2 + 1;
-      parity = par2;
-    } else {
-      if (e0 < my_n) issue(st_idx, bt_s[e0 & (2 * kBtChunk - 1)]);
-      sp0 += 16;
-      sp1 += 16;
-      ++it;
-      ++st_idx;
-    }
-    if (st_idx == T4::kStages) { st_idx = 0; parity ^= 1u; }
+    const int e0 = it + kPagesInFlight;   // first page to fetch into the slot just freed
+    if (e0 < my_n) refill(sl, bt_s[e0 & (2 * kBtChunk - 1)], bt_s[(e0 + 1) & (2 * kBtChunk - 1)], e0 + 1 < my_n);
+    sp0 += 32;
+    sp1 += 32;
+    sl ^= 1;
+    if (sl == 0) parity ^= 1u;
   }
 
   JF_PHASE(4);
@@ -585,27 +598,28 @@ EncodeFn encode_fn() {
 struct MapKey {
   const void* base;
   uint64_t rows;
-  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows; }
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && box_rows == o.box_rows; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.base) ^ (std::hash<uint64_t>()(k.rows) * 1000003u);
+    return std::hash<const void*>()(k.base) ^ (std::hash<uint64_t>()(k.rows * 64 + k.box_rows) * 1000003u);
   }
 };
 
-// (rows x 64 bytes) view of a packed tensor, box = one 16-row page, 64-byte swizzle.
-jf_status_t page_map(const void* base, uint64_t rows, CUtensorMap* out) {
+// (rows x 64 bytes) view of a packed tensor, box = one 16-row page or two (32 rows), 64-byte swizzle.
+jf_status_t page_map(const void* base, uint64_t rows, uint32_t box_rows, CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   std::lock_guard<std::mutex> lock(mu);
-  const MapKey key{base, rows};
+  const MapKey key{base, rows, box_rows};
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return JF_OK; }
   EncodeFn fn = encode_fn();
   if (!fn) return JF_ERR_CUDA;
   const cuuint64_t dims[2] = {64, rows};
   const cuuint64_t strides[1] = {64};
-  const cuuint32_t box[2] = {64, 16};
+  const cuuint32_t box[2] = {64, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -632,21 +646,21 @@ extern "C" int jf_debug_scan_cta_times(unsigned long long* out) {   // [1024][8]
 jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(sp.H_kv) * static_cast<uint64_t>(sp.num_slots);
   if (rows > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
-  CUtensorMap k_map, v_map;
-  jf_status_t st = page_map(sp.k_data, rows, &k_map);
+  CUtensorMap k_map, v_map, k_map2, v_map2;
+  jf_status_t st = page_map(sp.k_data, rows, 16, &k_map);
+  if (st == JF_OK) st = page_map(sp.v_data, rows, 16, &v_map);
+  if (st == JF_OK) st = page_map(sp.k_data, rows, 32, &k_map2);
+  if (st == JF_OK) st = page_map(sp.v_data, rows, 32, &v_map2);
   if (st != JF_OK) return st;
-  st = page_map(sp.v_data, rows, &v_map);
-  if (st != JF_OK) return st;
-  // ring, barriers, page lengths, query exchange, block-table chunks, alignment slack
-  const size_t smem = kScanWarps * T4::kStages * (T4::kBytes + 8 + 4) + kScanWarps * 6 * 32 * 4 +
-                      kScanWarps * 2 * kBtChunk * 8 + 1024;
-  static_assert(kScanWarps * T4::kStages * T4::kBytes >= kMergeBytes, "merge buffer");
+  const size_t smem = kSmemBytes;
   if (q_dtype == JF_DTYPE_BF16) {
     JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_BF16>, smem);
-    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map));
+    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map,
+                           k_map2, v_map2));
   } else {
     JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_FP16>, smem);
-    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_FP16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map));
+    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_FP16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map,
+                           k_map2, v_map2));
   }
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;

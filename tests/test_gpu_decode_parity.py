@@ -105,6 +105,25 @@ def test_k4v4_short_and_ragged():
     check_case(Case("k4v4", 3, 32, 4, 512, lens=[17, 257, 512], seed=36, dtype=torch.float16), 256)
 
 
+@pytest.mark.parametrize("mode", ["k4v4", "k3v2"])
+def test_neighbouring_blocks_and_mixed_tables(mode):
+    """Block tables whose consecutive pages sit in neighbouring cache blocks (the K4V4 scan then
+    fetches two pages per copy), tables that mix neighbouring and scattered blocks, odd page
+    counts and a partial last page."""
+    case = Case(mode, 3, 8, 2, 1000, lens=[1000, 777, 33], seed=44, spare_blocks=3)
+    per = case.block_table.shape[1]
+    ident = torch.arange(case.B * per, dtype=torch.int64).reshape(case.B, per)
+    case.block_table = ident.clone()
+    check_case(case, 64)
+    mixed = ident.clone()
+    mixed[0, 5], mixed[0, 6] = ident[0, 6].item(), ident[0, 5].item()   # a descending pair
+    mixed[1, 10:20] = ident[1, 10:20].flip(0)                           # a reversed run
+    mixed[2, 1] = ident[2, 2].item() + 1                                # a gap of one block (the last one is spare)
+    mixed[2, 2] = case.n_blocks - 1
+    case.block_table = mixed
+    check_case(case, 64)
+
+
 def test_k3v2_fp16_inputs():
     check_case(Case("k3v2", 2, 8, 2, 1024, seed=11, dtype=torch.float16), 128)
 
