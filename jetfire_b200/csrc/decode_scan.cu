@@ -156,7 +156,8 @@ struct K3State {
   uint32_t ks_sel;         // PRMT selector: this lane's K group scale into both halves
 };
 
-// One 16-token page.  `sb` = shared-memory address of the stage.  kPartial: the last page of
+// One 16-token page.  `sb` = shared-memory address of the ring slot; the offsets select the
+// page's half of it.  kPartial: the last page of
 // a sequence (or a page whose block id was invalid) -- rows at or past `valid` are neutralised;
 // the common full-page instance carries none of that logic.
 template <int QT, bool kPartial>
@@ -167,7 +168,7 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
   // ---------------- K: unpack + Q.K^T ----------------
   const uint32_t sa = sb + s_addr_off;
   uint32_t ksw0 = lds32<0>(sa), ksw1 = lds32<32>(sa);
-  const uint32_t vsw0 = lds32<64>(sa), vsw1 = lds32<96>(sa);
+  const uint32_t vsw0 = lds32<T::kVsRel>(sa), vsw1 = lds32<T::kVsRel + 32>(sa);
   float vs00 = __uint_as_float(vsw0 << 16), vs01 = __uint_as_float(vsw0 & 0xFFFF0000u);
   float vs10 = __uint_as_float(vsw1 << 16), vs11 = __uint_as_float(vsw1 & 0xFFFF0000u);
   if (kPartial) {
@@ -256,13 +257,15 @@ scan_k3v2_kernel(const ScanParams p) {
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t stages0 = smem_base + warp * (T::kStages * T::kBytes);
-  const uint32_t bars0 = smem_base + kScanWarps * T::kStages * T::kBytes + warp * (T::kStages * 8);
+  constexpr int kRingBytes = kScanWarps * T::kSlots * T::kSlotBytes;
+  constexpr int kPagesInFlight = 2 * T::kSlots;
+  const uint32_t slots0 = smem_base + warp * (T::kSlots * T::kSlotBytes);
+  const uint32_t bars0 = smem_base + kRingBytes + warp * (T::kSlots * 8);   // one barrier per slot
   // parked per page: the first cache row of its block and how many of its 16 tokens are live
-  int2* bt_s = reinterpret_cast<int2*>(smem + kScanWarps * T::kStages * (T::kBytes + 8 + 4)) + warp * (2 * kBtChunk);
+  int2* bt_s = reinterpret_cast<int2*>(smem + kRingBytes + kScanWarps * T::kSlots * 8) + warp * (2 * kBtChunk);
 
   if (lane == 0) {
-    for (int s = 0; s < T::kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
+    for (int s = 0; s < T::kSlots; ++s) mbar_init(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + s, 1);
   }
   fence_barrier_init();
   __syncwarp();
@@ -303,20 +306,28 @@ scan_k3v2_kernel(const ScanParams p) {
     const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
     return make_int2(static_cast<int>(head_rows + (bad ? 0 : blk64) * 16), valid);
   };
-  auto copies = [&](int st_idx, int64_t row) {   // by one lane: a page's four copies into a stage
-    const uint32_t bar = bars0 + st_idx * 8;
-    const uint32_t dst = stages0 + st_idx * T::kBytes;
-    mbar_expect_tx_u32(bar, T::kBytes);
-    bulk_g2s_u32_hint(dst + T::kKOff, p.k_data + row * T::kKRow, 16 * T::kKRow, bar, stream_policy);
-    bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + row * T::kVRow, 16 * T::kVRow, bar, stream_policy);
-    bulk_g2s_u32(dst + T::kKsOff, ks_b + row * (2 * T::kNG), 32 * T::kNG, bar);
-    bulk_g2s_u32(dst + T::kVsOff, vs_b + row * (2 * T::kNG), 32 * T::kNG, bar);
-  };
-  auto issue = [&](int st_idx, int2 ent) {
-    if (elect_one()) copies(st_idx, ent.x);
-  };
-  auto issue2 = [&](int st_idx, int2 ent_a, int2 ent_b) {   // stages st_idx and st_idx + 1
-    if (elect_one()) { copies(st_idx, ent_a.x); copies(st_idx + 1, ent_b.x); }
+  // By one elected lane: the copies of one or two pages into slot `sl`.  Two pages whose blocks
+  // are neighbours in the cache take one copy per array; otherwise each page takes its own four.
+  // Either way everything lands on the slot's barrier.
+  auto refill = [&](int sl, int2 ent_a, int2 ent_b, bool two) {
+    if (elect_one()) {
+      const uint32_t bar = bars0 + sl * 8;
+      const uint32_t dst = slots0 + sl * T::kSlotBytes;
+      const int64_t ra = ent_a.x, rb = ent_b.x;
+      const bool joined = two && rb == ra + 16;
+      const uint32_t n = joined ? 2u : 1u;
+      mbar_expect_tx_u32(bar, two ? 2 * T::kPageTx : T::kPageTx);
+      bulk_g2s_u32_hint(dst, p.k_data + ra * T::kKRow, n * T::kKPage, bar, stream_policy);
+      bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + ra * T::kVRow, n * T::kVPage, bar, stream_policy);
+      bulk_g2s_u32(dst + T::kKsOff, ks_b + ra * (2 * T::kNG), n * T::kSPage, bar);
+      bulk_g2s_u32(dst + T::kKsOff + T::kVsRel, vs_b + ra * (2 * T::kNG), n * T::kSPage, bar);
+      if (two && !joined) {
+        bulk_g2s_u32_hint(dst + T::kKPage, p.k_data + rb * T::kKRow, T::kKPage, bar, stream_policy);
+        bulk_g2s_u32_hint(dst + T::kVOff + T::kVPage, p.v_data + rb * T::kVRow, T::kVPage, bar, stream_policy);
+        bulk_g2s_u32(dst + T::kKsOff + T::kSPage, ks_b + rb * (2 * T::kNG), T::kSPage, bar);
+        bulk_g2s_u32(dst + T::kKsOff + T::kVsRel + T::kSPage, vs_b + rb * (2 * T::kNG), T::kSPage, bar);
+      }
+    }
   };
 
   // prologue: chunk 0 to shared memory, chunk 1 requested, the ring filled
@@ -324,10 +335,8 @@ scan_k3v2_kernel(const ScanParams p) {
   int bt_stored = 0;   // chunks 0..bt_stored are in shared memory; chunk bt_stored + 1 is in bt_pend
   bt_pend = bt_load(1);
   __syncwarp();
-  {
-    const int pro = min(T::kStages, my_n);
-    for (int it = 0; it < pro; ++it) issue(it, bt_s[it]);
-  }
+  for (int sl = 0; sl < T::kSlots; ++sl)
+    if (2 * sl < my_n) refill(sl, bt_s[2 * sl], bt_s[2 * sl + 1], 2 * sl + 1 < my_n);
 
   // ---- query fragments: B operand of the K MMA, scaled by 2^(33 - pos) of the code it meets.
   //      Lane (head n = g, tig) covers channels 32 tig + 8 j + x (group j, code x); k-step x
@@ -374,7 +383,7 @@ scan_k3v2_kernel(const ScanParams p) {
   bool failed = false;
 
   const int t0 = (g >> 1) | ((g & 1) << 2);  // token of MMA row g (rows g + 8 -> t0 + 8)
-  const uint32_t k_addr_off = T::kKOff + t0 * T::kKRow + tig * 4;
+  const uint32_t k_addr_off = t0 * T::kKRow + tig * 4;               // in the slot's first half
   const uint32_t v_addr_off = T::kVOff + tig * T::kVRow + 2 * g;
   const uint32_t s_addr_off = T::kKsOff + t0 * 4;
   const int h0 = hkv * p.G + 2 * tig;
@@ -384,46 +393,43 @@ scan_k3v2_kernel(const ScanParams p) {
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
 
-  // Two pages per round (the ring depth is even, so a round's stages are st_idx and st_idx + 1
-  // and share a phase): the pages are processed one after the other, and the ring bookkeeping
-  // and the election of the copying lane are paid once per round.
-  static_assert(T::kStages % 2 == 0, "a round takes two adjacent stages");
-  int st_idx = 0;
+  // A round takes one slot: two pages (one at the end of the range), processed one after the
+  // other; the ring bookkeeping and the election of the copying lane are paid once per round.
+  int sl = 0;
   uint32_t parity = 0u;
-  for (int it = 0; it < my_n && !failed;) {
+  for (int it = 0; it < my_n; it += 2) {
     const int n_here = (it + 1 < my_n) ? 2 : 1;
+    if (!mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + sl, parity)) {
+      // give the copies that were already issued a short, bounded chance to land
+      for (int j = 1; j < T::kSlots && it + 2 * j < my_n; ++j) {
+        const int o = (sl + j) % T::kSlots;
+        mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + o, o > sl ? parity : parity ^ 1u, 1000000ull);
+      }
+      failed = true;
+      break;
+    }
+    const uint32_t sb = slots0 + sl * T::kSlotBytes;
 #pragma unroll 1
     for (int k = 0; k < n_here; ++k) {
-      if (!mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + st_idx + k, parity)) {
-        // give the copies that were already issued a short, bounded chance to land
-        for (int j = it + k + 1; j < min(my_n, it + T::kStages); ++j)
-          mbar_wait(reinterpret_cast<uint64_t*>(smem + (bars0 - smem_base)) + (j % T::kStages), (j / T::kStages) & 1, 1000000ull);
-        failed = true;
-        break;
-      }
-      const uint32_t sb = stages0 + (st_idx + k) * T::kBytes;
       const int live = bt_s[(it + k) & (2 * kBtChunk - 1)].y;   // the page's parked entry is still resident
+      const uint32_t ko = k_addr_off + k * T::kKPage, vo = v_addr_off + k * T::kVPage, so = s_addr_off + k * T::kSPage;
       if (live != 16)
-        k3v2_page<kQTerms, true>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, live, attn, sp0, sp1, st0, st1);
+        k3v2_page<kQTerms, true>(st, sb, ko, vo, so, t0, live, attn, sp0, sp1, st0, st1);
       else
-        k3v2_page<kQTerms, false>(st, sb, k_addr_off, v_addr_off, s_addr_off, t0, 16, attn, sp0, sp1, st0, st1);
+        k3v2_page<kQTerms, false>(st, sb, ko, vo, so, t0, 16, attn, sp0, sp1, st0, st1);
       sp0 += 16;
       sp1 += 16;
     }
-    if (failed) break;
     __syncwarp();
-    if (((it + T::kStages + 1) >> 4) > bt_stored) {   // the refills below read entries up to it + kStages + 1
+    if (((it + kPagesInFlight + 1) >> 4) > bt_stored) {   // the refill below reads entries up to it + kPagesInFlight + 1
       ++bt_stored;
       if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_entry(bt_pend, bt_stored * kBtChunk + lane);
       bt_pend = bt_load(bt_stored + 1);
       __syncwarp();
     }
-    const int e0 = it + T::kStages;   // first page to fetch into the stages just freed
-    if (e0 + 1 < my_n) issue2(st_idx, bt_s[e0 & (2 * kBtChunk - 1)], bt_s[(e0 + 1) & (2 * kBtChunk - 1)]);
-    else if (e0 < my_n) issue(st_idx, bt_s[e0 & (2 * kBtChunk - 1)]);
-    it += n_here;
-    st_idx += 2;   // a single page only ends the range
-    if (st_idx == T::kStages) { st_idx = 0; parity ^= 1u; }
+    const int e0 = it + kPagesInFlight;   // first page to fetch into the slot just freed
+    if (e0 < my_n) refill(sl, bt_s[e0 & (2 * kBtChunk - 1)], bt_s[(e0 + 1) & (2 * kBtChunk - 1)], e0 + 1 < my_n);
+    if (++sl == T::kSlots) { sl = 0; parity ^= 1u; }
   }
 
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
@@ -517,8 +523,8 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   dim3 grid(sp.splits, a->H_kv, a->B);
   if (a->mode == JF_MODE_K3V2) {
     using T = Tile<JF_MODE_K3V2>;
-    const size_t smem = kScanWarps * T::kStages * (T::kBytes + 8 + 4) + kScanWarps * 2 * kBtChunk * 8;  // ring, barriers, page lengths, block-table chunks
-    static_assert(kScanWarps * T::kStages * T::kBytes >= kMergeBytes, "merge buffer");
+    const size_t smem = kScanWarps * T::kSlots * (T::kSlotBytes + 8) + kScanWarps * 2 * kBtChunk * 8;  // ring, barriers, block-table chunks
+    static_assert(kScanWarps * T::kSlots * T::kSlotBytes >= kMergeBytes, "merge buffer");
     if (a->q_dtype == JF_DTYPE_BF16) {
       JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_BF16>, smem);
       JF_CUDA_TRY(launch_pdl(scan_k3v2_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp));

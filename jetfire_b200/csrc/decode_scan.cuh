@@ -8,9 +8,15 @@ namespace jf {
 
 template <int MODE> struct Tile;
 template <> struct Tile<JF_MODE_K3V2> {
+  // A warp's ring is made of two-page slots: [K page A | K page B | V page A | V page B |
+  // K scales A, B | V scales A, B]; two pages whose blocks are neighbours in the cache are
+  // fetched with one bulk copy per array.
   static constexpr int kKRow = 48, kVRow = 32, kNG = 2;
-  static constexpr int kKOff = 0, kVOff = 768, kKsOff = 1280, kVsOff = 1344, kBytes = 1408;
-  static constexpr int kStages = 8;   // pages in flight per warp
+  static constexpr int kKPage = 768, kVPage = 512, kSPage = 64;   // bytes per page and array
+  static constexpr int kVOff = 1536, kKsOff = 2560, kVsRel = 128; // slot-relative; V scales from the K scales
+  static constexpr int kSlotBytes = 2816;
+  static constexpr int kPageTx = 1408;    // bytes that land per page
+  static constexpr int kSlots = 4;        // two-page slots per warp: eight pages in flight
 };
 template <> struct Tile<JF_MODE_K4V4> {
   // A warp's ring is made of two-page slots: [K page A | K page B | V page A | V page B |
