@@ -48,7 +48,7 @@ WORKLOADS = {
 }
 BYTES_PER_TOKEN_HEAD = {"k3v2": 88, "k4v4": 132}
 MODE_BITS = {"k3v2": (3, 2, 64), "k4v4": (4, 4, 128)}
-DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 91.4, "k4v4": 137.5}   # dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture
+DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 91.2, "k4v4": 137.3}   # dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture
 
 
 def parse_args():
