@@ -11,9 +11,13 @@
 // which materialise scores and weights in HBM and read V once per *query* head.
 //
 // Data movement: a 16-token page of the cache is contiguous per tensor (768 B of INT3 K,
-// 512 B of INT2 V, 64 + 64 B of bf16 scales for K3V2), so each page is fetched with four
-// bulk-async copies (TMA, non-tensor form) into a per-warp ring of shared-memory stages,
-// completion counted on an mbarrier.  A page is exactly one MMA M tile.
+// 512 B of INT2 V, 64 + 64 B of bf16 scales for K3V2), so a page is fetched with four
+// bulk-async copies (TMA, non-tensor form) into a per-warp ring of two-page slots in shared
+// memory, completion counted on the slot's mbarrier; two pages in neighbouring cache blocks
+// share their copies.  A page is exactly one MMA M tile.  Block-table entries are fetched
+// sixteen at a time, a chunk ahead of their use, and parked in shared memory together with
+// what the copies need, so that the loop never waits for a global load and the warp-uniform
+// work per page stays small.
 //
 // Compute: tokens sit on the MMA M axis and the (<= 8) query heads on N = 8.  Packed codes
 // are expanded in registers straight into the A fragments of mma.sync.m16n8k16 (the

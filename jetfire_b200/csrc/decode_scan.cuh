@@ -1,4 +1,4 @@
-// Pieces shared by the per-mode scan kernels: parameters, stage geometry, the CTA-level
+// Pieces shared by the per-mode scan kernels: parameters, ring-slot geometry, the CTA-level
 // merge of the four warps' partials.
 #pragma once
 
