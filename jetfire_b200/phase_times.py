@@ -42,6 +42,13 @@ def _report(title, t, marks):
     print(f"{title}: " + " | ".join(parts) + f" | total {t[marks[-1][0]] - t[marks[0][0]]} cycles")
 
 
+def _collect_detail(t):
+    """Inside 'collect candidates' (stamps 30..33 of the select kernel's first collection)."""
+    if t[30] and t[33]:
+        print(f"  collect: threshold pass {t[30] - t[4]} | offsets {t[31] - t[30]} | scatter {t[32] - t[31]} | "
+              f"barrier {t[33] - t[32]} | to the next phase {t[5] - t[33]}")
+
+
 def _cta_timeline():
     """Per-CTA wall-clock stamps of the last K4V4 scan launch (globaltimer, ns): when the CTAs
     started, entered and left their page loops and finished; and the loop time by the CTA's
@@ -104,7 +111,9 @@ def main():
             _report("scan_k4v4", _stamps("jf_debug_scan_times"), SCAN_MARKS)
             if a.cta_timeline:
                 _cta_timeline()
-        _report(f"select+finish {a.mode}", _stamps("jf_debug_phase_times"), SELECT_MARKS)
+        sel = _stamps("jf_debug_phase_times")
+        _report(f"select+finish {a.mode}", sel, SELECT_MARKS)
+        _collect_detail(sel)
 
 
 if __name__ == "__main__":
