@@ -435,14 +435,21 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         for (int ci = 0; ci < n_chunks; ++ci) {
           if (n_chunks > 1) next_chunk(ci);
           uint32_t mask = 0u;
+          // which of the thread's float4s can hold a candidate at all (branch-free; most threads
+          // find none and skip the loads altogether)
+          uint32_t hits = (1u << kChunkVec) - 1u;
+          if (have_hm) {
+            hits = 0u;
 #pragma unroll
-          for (int j = 0; j < kChunkVec; ++j) {
-            if (have_hm && !(hm[j] > thr)) continue;  // nothing of this float4 can qualify
+            for (int j = 0; j < kChunkVec; ++j) hits |= static_cast<uint32_t>(hm[j] > thr) << j;
+          }
+          while (hits) {
+            const int j = __ffs(hits) - 1;
+            hits &= hits - 1u;
             const float4 v = chunk4[j * kSelThreads + tid];
-            if (v.x > thr) mask |= 1u << (4 * j);
-            if (v.y > thr) mask |= 1u << (4 * j + 1);
-            if (v.z > thr) mask |= 1u << (4 * j + 2);
-            if (v.w > thr) mask |= 1u << (4 * j + 3);
+            const uint32_t m4 = static_cast<uint32_t>(v.x > thr) | (static_cast<uint32_t>(v.y > thr) << 1) |
+                                (static_cast<uint32_t>(v.z > thr) << 2) | (static_cast<uint32_t>(v.w > thr) << 3);
+            mask |= m4 << (4 * j);
           }
           JF_PHASE(30);
           const int cnt = __popc(mask);
@@ -454,7 +461,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           }
           // warp totals -> every warp's offset (no atomics: 32 same-address atomics with a
           // return value cost more than the whole pass)
-          __syncthreads();   // the previous round's reads of wsum are done
+          if (ci > 0) __syncthreads();   // the previous round's reads of wsum are done (the first round follows a barrier)
           if (lane == 31) sm.wsum[warp] = incl;
           __syncthreads();
           int wt = sm.wsum[lane], winc = wt;
