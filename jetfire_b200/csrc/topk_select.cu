@@ -422,8 +422,9 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         else if (ex + h0 < K && ex + v >= K) sm.tbin = 2 * tid + 1;
         __syncthreads();
       };
-      // Block-wide: positions whose bin is <= last go to keys[] (one shared-memory atomic per
-      // warp and chunk); returns how many there are (may exceed sort_n: then keys[] is partial).
+      // Block-wide: positions whose bin is <= last go to keys[], in position order (offsets from
+      // a warp scan and a block scan, no atomics); returns how many there are (may exceed
+      // sort_n: then keys[] is partial).
       float hm[kChunkVec];  // per float4 of the resident chunk: its largest score (tier 1a's pass)
       bool have_hm = false;
       auto collect = [&](int last) {
