@@ -43,6 +43,25 @@ enum { JF_DTYPE_BF16 = 0, JF_DTYPE_FP16 = 1 };
  * group 64, K4V4 = SymInt4K_SymInt4V with group 128. */
 enum { JF_MODE_K3V2 = 0, JF_MODE_K4V4 = 1 };
 
+/* jf_decode_scan can run the two halves of the reference's pipeline separately, for callers
+ * that keep the reference's Stage A / Stage B call structure:
+ *   JF_SCAN_K_ONLY  scores (into args->scores and the workspace) and the softmax sums; reads
+ *                   q and the K cache only -- with jf_topk_select this is Stage A
+ *                   (int3_qk_scores_topk, jetfire_vllm/csrc/int3_qk_scores.cu:562-633);
+ *   JF_SCAN_V_ONLY  output partials from the scores in args->scores (an input here) and the
+ *                   V cache only -- with jf_decode_finish this is Stage B
+ *                   (int2_softmax_v_with_pre_corr_wvs2, csrc/int2_softmax_v.cu:792-901).
+ * Both give the bits of the one-pass scan. */
+enum { JF_SCAN_ALL = 0, JF_SCAN_K_ONLY = 1, JF_SCAN_V_ONLY = 2 };
+
+/* Weights of the softmax.V product.  JF_STAGE_B_FP32: full-precision weights, the reference's
+ * wvs2 / wvs2_scores kernels (csrc/int2_softmax_v.cu:681-705, csrc/int4_softmax_v.cu:599-817).
+ * JF_STAGE_B_INT8P (K4V4 only): the reference's plan for a configured batch above 1
+ * (jetfire_vllm/adapter/release_policy.py:443-451): per tile of 32 tokens and query head,
+ * p * v_scale is rounded to 127 levels of the tile's largest value, tiles laid out over 8
+ * splits of ceil(max_S / 8) positions (csrc/int8tc_softmax_v_fused.cu:62, 1049-1053, 1203-1311). */
+enum { JF_STAGE_B_FP32 = 0, JF_STAGE_B_INT8P = 1 };
+
 #define JF_HEAD_DIM   128
 #define JF_BLOCK_SIZE 16
 #define JF_MAX_TOP_K  2048
@@ -126,6 +145,22 @@ jf_status_t jf_stream_mirror_append(jf_stream_t stream, int64_t handle, const vo
                                     int64_t k_stride_t, int64_t k_stride_h,
                                     int64_t v_stride_t, int64_t v_stride_h,
                                     const int64_t* slots);
+/* The reference's own staged form (create_shadow_append_submit_ctx / stream_submit_shadow_append,
+ * jetfire_vllm/csrc/cpu_topk_attn.cpp:1611-1665, 2186-2248): the caller owns pinned host staging
+ * k_append / v_append (T, H_kv, 128) 16-bit and slots (T,) int64 and fills them with its own
+ * stream-ordered copies; `submit` queues a host callback that scatters the staged rows into the
+ * mirror (k_shadow / v_shadow (H_kv, num_slots, 128)), skipping negative or out-of-range slots.
+ * The context and the buffers must outlive every stream operation that refers to them. */
+jf_status_t jf_shadow_append_ctx_create(const void* k_append, const void* v_append,
+                                        const int64_t* slots, int64_t T, int32_t H_kv,
+                                        void* k_shadow, void* v_shadow, int64_t num_slots,
+                                        int64_t* handle);
+jf_status_t jf_shadow_append_ctx_destroy(int64_t handle);
+jf_status_t jf_shadow_append_ctx_calls(int64_t handle, int64_t* calls);
+jf_status_t jf_stream_submit_shadow_append(jf_stream_t stream, int64_t handle);
+/* 64-bit store to device-visible memory in stream order (stream_write_value64,
+ * jetfire_vllm/csrc/cpu_topk_attn.cpp:1293-1312); device_ptr 8-byte aligned. */
+jf_status_t jf_stream_write_value64(jf_stream_t stream, void* device_ptr, int64_t value);
 /* Page-lock an existing host allocation and return the pointer the GPU sees it at. */
 jf_status_t jf_map_host(void* host_ptr, uint64_t bytes, void** device_ptr);
 jf_status_t jf_unmap_host(void* host_ptr);
@@ -149,11 +184,11 @@ typedef struct jf_decode_args {
   int32_t block_size;    /* must be 16                                             */
   int32_t top_k;         /* 1..JF_MAX_TOP_K                                        */
   int32_t max_blocks;    /* row stride of block_table, >= ceil(max_S / 16)         */
-  int32_t reserved0;
+  int32_t scan_parts;    /* JF_SCAN_*: what jf_decode_scan computes (0 = everything) */
   float   attn_scale;
-  int32_t reserved1;
+  int32_t stage_b;       /* JF_STAGE_B_*: arithmetic of the weights that meet V     */
   int64_t num_slots;     /* slots per KV head in the packed cache                  */
-  const void*    q;            /* (B, H_q, 128) contiguous                         */
+  const void*    q;            /* (B, H_q, 128) contiguous (may be NULL for JF_SCAN_V_ONLY) */
   const uint8_t* k_data;       /* (H_kv, num_slots, 48 | 64)                       */
   const void*    k_scales;     /* (H_kv, num_slots, NG) bf16                       */
   const uint8_t* v_data;       /* (H_kv, num_slots, 32 | 64)                       */
@@ -162,7 +197,8 @@ typedef struct jf_decode_args {
   const int32_t* seq_lens;     /* (B,)                                             */
   /* outputs */
   float*   scores;        /* optional (B, H_q, max_S): approximate scores, -inf past the
-                             sequence end; NULL keeps them in the workspace only   */
+                             sequence end; NULL keeps them in the workspace only;
+                             JF_SCAN_V_ONLY, select and finish read them from here   */
   int64_t* topk_idx;      /* (B, H_q, top_k) positions, (score desc, index asc), -1 pad */
   int64_t* topk_slots;    /* (B, H_q, top_k) physical slots, -1 pad                */
   float*   o_hat;         /* (B, H_q, 128)                                          */
@@ -187,10 +223,19 @@ jf_status_t jf_topk_select(const jf_decode_args* args, jf_stream_t stream);
  * csrc/int2_softmax_v.cu:738-788). */
 jf_status_t jf_decode_finish(const jf_decode_args* args, jf_stream_t stream);
 jf_status_t jf_decode_fused(const jf_decode_args* args, jf_stream_t stream);
+/* Exact row maximum m and 1 / sum exp(s - m) over positions [0, min(seq_lens[b], max_S)) of
+ * stored scores (B, H_q, max_S): the two extra outputs of the reference's
+ * int8tc_qk_scores_topk_stats (jetfire_vllm/csrc/int8tc_qk_scores.cu:1790-1800, 2426-2482).
+ * An empty row gives m = 0 and 1/Z = 0. */
+jf_status_t jf_softmax_stats(const float* scores, const int32_t* seq_lens, float* softmax_m,
+                             float* softmax_inv_z, int32_t B, int32_t H_q, int32_t max_S,
+                             jf_stream_t stream);
 /* Reads back (synchronously, after the stream drained) the status record of the
  * workspace: 0, or JF_ERR_TIMEOUT if a bounded wait inside a kernel ran out since the
  * record was last read.  Reading an error clears it.  The workspace needs no
- * initialisation: only a record that a kernel tagged counts. */
+ * initialisation: only a record that a kernel tagged counts.  With args->workspace NULL it
+ * reads (and clears) the record of the calls made through jf_decode_fused_static on the
+ * current device instead. */
 jf_status_t jf_decode_status(const jf_decode_args* args, jf_stream_t stream);
 
 /* ---------------------------------------------------------------------------------
@@ -211,6 +256,8 @@ jf_status_t jf_decode_status(const jf_decode_args* args, jf_stream_t stream);
  * calls must not overlap on the same GPU (they would race); results do not depend on what
  * was left behind.  The first call on each device resolves the array's address and should
  * be made before any stream capture begins.  Never calls cudaMalloc / cudaFree.
+ * A bounded wait that ran out inside one of its kernels is recorded at the start of the
+ * array; read it with jf_decode_status on an argument block whose workspace is NULL.
  * ------------------------------------------------------------------------------- */
 #define JF_STATIC_SCRATCH_BYTES (64ull << 20)
 jf_status_t jf_decode_fused_static(const jf_decode_args* args, jf_stream_t stream);
@@ -238,6 +285,10 @@ jf_status_t jf_cpu_topk_attn(const void* q, const void* k_shadow, const void* v_
                              const int64_t* head_map, const int64_t* ts_buf, void* o_new,
                              int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
                              int64_t num_slots, int32_t K, float scale, int64_t* done_flag);
+/* Host-side wait for a completion flag written by the correction workers (the host half of
+ * wait_and_blend_unnorm_into, jetfire_vllm/csrc/blend.cu:320-376): returns JF_OK once *flag is
+ * non-zero, JF_ERR_TIMEOUT after timeout_ms.  Does not touch the GPU. */
+jf_status_t jf_wait_flag(const int64_t* flag, int32_t timeout_ms);
 jf_status_t jf_set_cpu_attn_threads(int32_t n);
 int32_t     jf_get_cpu_attn_threads(void);
 

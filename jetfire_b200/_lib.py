@@ -15,6 +15,8 @@ JF_ERR_ARG, JF_ERR_UNSUPPORTED, JF_ERR_WORKSPACE, JF_ERR_STATIC_LIMIT = -1, -2, 
 JF_ERR_CUDA, JF_ERR_TIMEOUT, JF_ERR_STATE = 1, 2, 3
 JF_DTYPE_BF16, JF_DTYPE_FP16 = 0, 1
 JF_MODE_K3V2, JF_MODE_K4V4 = 0, 1
+JF_SCAN_ALL, JF_SCAN_K_ONLY, JF_SCAN_V_ONLY = 0, 1, 2
+JF_STAGE_B_FP32, JF_STAGE_B_INT8P = 0, 1
 
 
 class JetFireError(RuntimeError):
@@ -31,8 +33,8 @@ class DecodeArgs(C.Structure):
         ("mode", C.c_int32), ("q_dtype", C.c_int32),
         ("B", C.c_int32), ("H_q", C.c_int32), ("H_kv", C.c_int32),
         ("max_S", C.c_int32), ("block_size", C.c_int32), ("top_k", C.c_int32),
-        ("max_blocks", C.c_int32), ("reserved0", C.c_int32),
-        ("attn_scale", C.c_float), ("reserved1", C.c_int32),
+        ("max_blocks", C.c_int32), ("scan_parts", C.c_int32),
+        ("attn_scale", C.c_float), ("stage_b", C.c_int32),
         ("num_slots", C.c_int64),
         ("q", C.c_void_p), ("k_data", C.c_void_p), ("k_scales", C.c_void_p),
         ("v_data", C.c_void_p), ("v_scales", C.c_void_p),
@@ -67,6 +69,12 @@ _SIGS = {
                                                C.POINTER(C.c_int64)]),
     "jf_stream_mirror_append": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
                                             C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "jf_shadow_append_ctx_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                                C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(C.c_int64)]),
+    "jf_shadow_append_ctx_destroy": (C.c_int32, [C.c_int64]),
+    "jf_shadow_append_ctx_calls": (C.c_int32, [C.c_int64, C.POINTER(C.c_int64)]),
+    "jf_stream_submit_shadow_append": (C.c_int32, [C.c_void_p, C.c_int64]),
+    "jf_stream_write_value64": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64]),
     "jf_map_host": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]),
     "jf_unmap_host": (C.c_int32, [C.c_void_p]),
     "jf_decode_workspace_bytes": (C.c_uint64, [C.c_int32] * 6),
@@ -75,10 +83,12 @@ _SIGS = {
     "jf_decode_finish": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_fused": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_status": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "jf_softmax_stats": (C.c_int32, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p]),
     "jf_decode_fused_static": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_merge_correct": (C.c_int32, [C.c_void_p] * 5 + [C.c_int32] * 3 + [C.c_void_p]),
     "jf_cpu_topk_attn": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                        C.c_void_p]),
+    "jf_wait_flag": (C.c_int32, [C.c_void_p, C.c_int32]),
     "jf_set_cpu_attn_threads": (C.c_int32, [C.c_int32]),
     "jf_get_cpu_attn_threads": (C.c_int32, []),
     "jf_pool_init": (C.c_int32, [C.c_int32]),

@@ -47,7 +47,10 @@ class JetFireCacheStore:
         self.v_data = torch.zeros(num_kv_heads, self.num_slots, head_dim * self.v_nbits // 8, dtype=torch.uint8, **dev)
         self.k_scales = torch.zeros(num_kv_heads, self.num_slots, ng, dtype=torch.bfloat16, **dev)
         self.v_scales = torch.zeros(num_kv_heads, self.num_slots, ng, dtype=torch.bfloat16, **dev)
-        self.slot_filled = torch.zeros(self.num_slots, dtype=torch.bool, **dev)
+        # one spare entry at the end takes the writes of padding / out-of-range slots, so that the
+        # bookkeeping below is a plain scatter with no host step (and can be captured in a graph)
+        self._filled_buf = torch.zeros(self.num_slots + 1, dtype=torch.bool, **dev)
+        self.slot_filled = self._filled_buf[:self.num_slots]
         self.written_count = 0
         self.shadow_enabled = bool(shadow_enabled)
         self.mirror_append = mirror_append
@@ -84,19 +87,23 @@ class JetFireCacheStore:
         else:
             ops.fused_quant_write_kv(key_tok, value_tok, slot_idx, self.k_data, self.k_scales, self.v_data,
                                      self.v_scales, self.group_size, self.k_nbits, self.v_nbits)
-        valid = slot_idx >= 0
-        self.slot_filled[slot_idx[valid]] = True
+        live = (slot_idx >= 0) & (slot_idx < self.num_slots)   # what the packing kernel wrote
+        self._filled_buf.index_fill_(0, torch.where(live, slot_idx, self.num_slots), True)
         self.written_count += int(key_tok.shape[0])
         if self.shadow_enabled and self.mirror_append == "stream":
             self._append_ctx.append(key_tok, value_tok, slot_idx)
         if self.shadow_enabled and self.mirror_append != "sync":
-            ev = torch.cuda.Event()
-            ev.record()
-            self._pending_event = ev
+            # Under stream capture the append is a node of the graph being built: whoever replays
+            # the graph orders host reads of the mirror against it, and no event is recorded here
+            # (the reference's graph path skips its bookkeeping as well, cache_store.py:611-614).
+            if not torch.cuda.is_current_stream_capturing():
+                ev = torch.cuda.Event()
+                ev.record()
+                self._pending_event = ev
             return
         if self.shadow_enabled:
             idx_cpu = slot_idx.to("cpu")                       # host sync, as in the reference's eager path
-            keep = idx_cpu >= 0
+            keep = (idx_cpu >= 0) & (idx_cpu < self.num_slots)
             idx_cpu = idx_cpu[keep]
             k_cpu = key_tok.to("cpu")[keep].transpose(0, 1).to(self.dtype)
             v_cpu = value_tok.to("cpu")[keep].transpose(0, 1).to(self.dtype)

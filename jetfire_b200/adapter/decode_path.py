@@ -17,20 +17,7 @@ import torch
 from .. import ops
 from .cache_store import JetFireCacheStore
 from .config import SUPPORTED_TOP_K, JetFireConfig, get_jetfire_config
-
-_HEAD_MAP_CPU: dict[tuple[int, int, int, int], torch.Tensor] = {}
-
-
-def _get_head_map_cpu(B: int, H_q: int, num_groups: int, K: int) -> torch.Tensor:
-    """(B, H_q, K) int64 head map for the host gather: entry = h_q // num_groups."""
-    key = (B, H_q, num_groups, K)
-    out = _HEAD_MAP_CPU.get(key)
-    if out is None:
-        hm = (torch.arange(H_q, dtype=torch.int64) // num_groups).unsqueeze(1).expand(H_q, K)
-        out = hm.unsqueeze(0).expand(B, H_q, K).contiguous()
-        _HEAD_MAP_CPU[key] = out
-    return out
-
+from .sharding import cpu_threads_per_rank
 
 def _select_top_k(config_top_k: int, seq_len: int, supported: tuple[int, ...]) -> int | None:
     """Largest supported width <= the sequence length (short sequences are padded with -1),
@@ -79,6 +66,19 @@ class _DecodeBuffers:
 
 
 _BUFFERS: dict[tuple, _DecodeBuffers] = {}
+_WORKERS_SET: int | None = None
+
+
+def _set_worker_count(cfg: JetFireConfig) -> None:
+    """Size the correction pool once: the configured count, capped by this rank's share of the
+    host cores (the ranks of a node share them; ``sharding.cpu_threads_per_rank``)."""
+    global _WORKERS_SET
+    import os
+    world = int(os.environ.get("WORLD_SIZE", "1") or 1)
+    want = max(1, min(int(cfg.cpu_attn_threads), cpu_threads_per_rank(os.cpu_count() or 1, world)))
+    if _WORKERS_SET != want:
+        ops.set_cpu_attn_threads(want)
+        _WORKERS_SET = want
 
 
 def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table: torch.Tensor,
@@ -97,16 +97,18 @@ def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table
     bt = block_table if block_table.dtype == torch.int64 else block_table.to(torch.int64)
     lens = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
     max_S = min(int(bt.shape[1]) * store.block_size, ((int(max_seq_len) + 15) // 16) * 16)
-    res = ops.fused_attn_topk(cfg.kernel_mode, q, store.k_data, store.k_scales, store.v_data, store.v_scales,
-                              bt, lens, max_S, num_heads, store.num_kv_heads, store.block_size, top_k, scale)
+    call = ops.DecodeCall(cfg.kernel_mode, q, store.k_data, store.k_scales, store.v_data, store.v_scales,
+                          bt, lens, max_S, num_heads, store.num_kv_heads, store.block_size, top_k, scale)
+    call.fused()
+    res = call.result()
     key = (B, num_heads, top_k, q.dtype)
     buf = _BUFFERS.get(key)
     if buf is None:
         buf = _BUFFERS[key] = _DecodeBuffers(B, num_heads, top_k, q.dtype)
     buf.q_host.copy_(q, non_blocking=True)
     buf.ts_host.copy_(res.topk_slots, non_blocking=True)
-    torch.cuda.current_stream().synchronize()
-    ops.set_cpu_attn_threads(cfg.cpu_attn_threads)
+    call.status()   # synchronises the stream; raises if a bounded wait inside a kernel ran out
+    _set_worker_count(cfg)
     ops.cpu_topk_attn(buf.q_host, store.k_shadow, store.v_shadow, None, buf.ts_host, buf.o_new_host, scale)
     o_new = buf.o_new_host.to(q.device, non_blocking=True)
     out_view = output[:B].view(B, num_heads, 128)

@@ -512,6 +512,26 @@ jf_status_t submit_job(const Job& j, int64_t* ticket) {
 
 }  // namespace
 
+// Blocks (spin with pauses, then short sleeps) until *flag is non-zero or the time is up.
+extern "C" jf_status_t jf_wait_flag(const int64_t* flag, int32_t timeout_ms) {
+  if (!flag) return JF_ERR_ARG;
+  const auto t_end = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
+  const volatile int64_t* f = flag;
+  for (int spins = 0;; ++spins) {
+    if (*f != 0) {
+      std::atomic_thread_fence(std::memory_order_acquire);
+      return JF_OK;
+    }
+    if (spins < 20000) {
+      _mm_pause();
+    } else {
+      if (std::chrono::steady_clock::now() > t_end) return JF_ERR_TIMEOUT;
+      std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+    if ((spins & 1023) == 1023 && std::chrono::steady_clock::now() > t_end) return (*f != 0) ? JF_OK : JF_ERR_TIMEOUT;
+  }
+}
+
 extern "C" jf_status_t jf_set_cpu_attn_threads(int32_t n) {
   if (n <= 0 || n > 1024) return JF_ERR_ARG;
   g_threads.store(n);

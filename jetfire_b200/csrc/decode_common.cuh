@@ -26,10 +26,10 @@ __host__ __device__ inline int scan_ctas_per_sm(int mode, int q_dtype) {
 // How many splits of the page range one (b, h_kv) pair is cut into: as many as fit in ONE
 // wave of resident CTAs (a second, partial wave would idle most of the GPU), but at least
 // two pages per warp.  Depends only on its arguments, so every launch agrees.
-__host__ __device__ inline int scan_splits(int mode, int q_dtype, int B, int H_kv, int max_S) {
+inline int scan_splits(int mode, int q_dtype, int B, int H_kv, int max_S) {
   const int pages = (max_S + JF_BLOCK_SIZE - 1) / JF_BLOCK_SIZE;
   const int pairs = B * H_kv;
-  int target = (kNumSMs * scan_ctas_per_sm(mode, q_dtype)) / pairs;
+  int target = (num_sms() * scan_ctas_per_sm(mode, q_dtype)) / pairs;
   int cap = pages / 8;
   if (cap < 1) cap = 1;
   if (target > cap) target = cap;
@@ -82,5 +82,7 @@ __device__ __forceinline__ void report_status(int32_t* status, int code) {
 #endif
 
 jf_status_t validate_decode_args(const jf_decode_args* a);
+// device address of the library's built-in scratch array on the current device (decode_static.cu)
+jf_status_t static_scratch_address(void** out);
 
 }  // namespace jf

@@ -44,6 +44,43 @@ decode_finish_kernel(const FinishParams p, const TailParams tp) {
                     });
 }
 
+// Exact row maximum and 1 / sum exp(s - max) of a stored score row, as the reference's
+// statistics-emitting select computes them (jetfire_vllm/csrc/int8tc_qk_scores.cu:1790-1800):
+// an empty or all -inf row gives m = 0, and a non-positive sum gives 1/Z = 0.
+// One CTA per (query head, batch element); sums in a fixed order.
+__global__ void __launch_bounds__(256)
+softmax_stats_kernel(const float* __restrict__ scores, const int32_t* __restrict__ seq_lens, float* __restrict__ out_m,
+                     float* __restrict__ out_inv_z, int H_q, int max_S) {
+  __shared__ float red[8];
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  const int n = max(0, min(seq_lens[b], max_S));
+  const float* row = scores + (static_cast<int64_t>(b) * H_q + h) * max_S;
+  float m = -INFINITY;
+  for (int i = tid; i < n; i += 256) m = fmaxf(m, row[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < 8; ++w) m = fmaxf(m, red[w]);
+  if (!isfinite(m)) m = 0.f;
+  __syncthreads();
+  float z = 0.f;
+  for (int i = tid; i < n; i += 256) z += __expf(row[i] - m);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xFFFFFFFFu, z, o);
+  if (lane == 0) red[warp] = z;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w];
+    out_m[static_cast<int64_t>(b) * H_q + h] = m;
+    out_inv_z[static_cast<int64_t>(b) * H_q + h] = t > 0.f ? 1.0f / t : 0.f;
+  }
+}
+
 template <int DT>
 __global__ void merge_correct_kernel(const float* __restrict__ o_hat, const float* __restrict__ o_old,
                                      const float* __restrict__ W, const uint16_t* __restrict__ o_new,
@@ -84,8 +121,19 @@ extern "C" jf_status_t jf_decode_finish(const jf_decode_args* a, jf_stream_t str
   return JF_OK;
 }
 
+extern "C" jf_status_t jf_softmax_stats(const float* scores, const int32_t* seq_lens, float* softmax_m,
+                                        float* softmax_inv_z, int32_t B, int32_t H_q, int32_t max_S,
+                                        jf_stream_t stream_) {
+  using namespace jf;
+  if (!scores || !seq_lens || !softmax_m || !softmax_inv_z || B <= 0 || H_q <= 0 || max_S <= 0) return JF_ERR_ARG;
+  JF_CUDA_TRY(launch_pdl(softmax_stats_kernel, dim3(H_q, B), dim3(256), 0, static_cast<cudaStream_t>(stream_), scores,
+                         seq_lens, softmax_m, softmax_inv_z, static_cast<int>(H_q), static_cast<int>(max_S)));
+  return JF_OK;
+}
+
 // scan, then select + finish in one kernel
 extern "C" jf_status_t jf_decode_fused(const jf_decode_args* a, jf_stream_t stream) {
+  if (a && a->scan_parts != JF_SCAN_ALL) return JF_ERR_ARG;   // the fused step needs both halves
   jf_status_t st = jf_decode_scan(a, stream);
   if (st != JF_OK) return st;
   return jf::launch_select(a, static_cast<cudaStream_t>(stream), true);
@@ -93,13 +141,19 @@ extern "C" jf_status_t jf_decode_fused(const jf_decode_args* a, jf_stream_t stre
 
 extern "C" jf_status_t jf_decode_status(const jf_decode_args* a, jf_stream_t stream_) {
   using namespace jf;
-  if (!a || !a->workspace) return JF_ERR_ARG;
+  if (!a) return JF_ERR_ARG;
+  // no workspace: the calls went through jf_decode_fused_static, whose record is in the built-in array
+  void* record = a->workspace;
+  if (!record) {
+    const jf_status_t st = static_scratch_address(&record);
+    if (st != JF_OK) return st;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   struct { unsigned long long tag; int32_t code; int32_t pad; } host{};
-  JF_CUDA_TRY(cudaMemcpyAsync(&host, a->workspace, sizeof(host), cudaMemcpyDeviceToHost, stream));
+  JF_CUDA_TRY(cudaMemcpyAsync(&host, record, sizeof(host), cudaMemcpyDeviceToHost, stream));
   JF_CUDA_TRY(cudaStreamSynchronize(stream));
   if (host.tag != kStatusTag || host.code == 0) return JF_OK;
-  JF_CUDA_TRY(cudaMemsetAsync(a->workspace, 0, sizeof(host), stream));
+  JF_CUDA_TRY(cudaMemsetAsync(record, 0, sizeof(host), stream));
   JF_CUDA_TRY(cudaStreamSynchronize(stream));
   return static_cast<jf_status_t>(host.code);
 }

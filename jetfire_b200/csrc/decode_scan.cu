@@ -164,15 +164,19 @@ struct K3State {
 // page's half of it.  kPartial: the last page of
 // a sequence (or a page whose block id was invalid) -- rows at or past `valid` are neutralised;
 // the common full-page instance carries none of that logic.
-template <int QT, bool kPartial>
+// kParts: 0 = scores and output partials; 1 = scores and softmax sums only (no V);
+// 2 = output partials from scores read back from memory (no K).
+template <int QT, bool kPartial, int kParts>
 __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t k_addr_off, uint32_t v_addr_off,
                                           uint32_t s_addr_off, int t0, int valid, float attn, float* sp0,
                                           float* sp1, bool st0, bool st1) {
   using T = Tile<JF_MODE_K3V2>;
+  constexpr bool kDoK = kParts != 2, kDoV = kParts != 1;
   // ---------------- K: unpack + Q.K^T ----------------
   const uint32_t sa = sb + s_addr_off;
-  uint32_t ksw0 = lds32<0>(sa), ksw1 = lds32<32>(sa);
-  const uint32_t vsw0 = lds32<T::kVsRel>(sa), vsw1 = lds32<T::kVsRel + 32>(sa);
+  uint32_t ksw0 = 0u, ksw1 = 0u, vsw0 = 0u, vsw1 = 0u;
+  if (kDoK) { ksw0 = lds32<0>(sa); ksw1 = lds32<32>(sa); }
+  if (kDoV) { vsw0 = lds32<T::kVsRel>(sa); vsw1 = lds32<T::kVsRel + 32>(sa); }
   float vs00 = __uint_as_float(vsw0 << 16), vs01 = __uint_as_float(vsw0 & 0xFFFF0000u);
   float vs10 = __uint_as_float(vsw1 << 16), vs11 = __uint_as_float(vsw1 & 0xFFFF0000u);
   if (kPartial) {
@@ -181,16 +185,21 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
   }
   // all shared-memory reads of the page are issued up front (the loads keep their source order)
   const uint32_t ka = sb + k_addr_off;
-  const uint32_t kw0 = lds32<0>(ka), kw1 = lds32<16>(ka), kw2 = lds32<32>(ka);
-  const uint32_t kw3 = lds32<8 * T::kKRow>(ka), kw4 = lds32<8 * T::kKRow + 16>(ka), kw5 = lds32<8 * T::kKRow + 32>(ka);
+  uint32_t kw0 = 0u, kw1 = 0u, kw2 = 0u, kw3 = 0u, kw4 = 0u, kw5 = 0u;
+  if (kDoK) {
+    kw0 = lds32<0>(ka); kw1 = lds32<16>(ka); kw2 = lds32<32>(ka);
+    kw3 = lds32<8 * T::kKRow>(ka); kw4 = lds32<8 * T::kKRow + 16>(ka); kw5 = lds32<8 * T::kKRow + 32>(ka);
+  }
   const uint32_t va_addr = sb + v_addr_off;
-  uint32_t vh[2][4];
-  vh[0][0] = lds16<0>(va_addr); vh[0][1] = lds16<4 * T::kVRow>(va_addr);
-  vh[0][2] = lds16<8 * T::kVRow>(va_addr); vh[0][3] = lds16<12 * T::kVRow>(va_addr);
-  vh[1][0] = lds16<16>(va_addr); vh[1][1] = lds16<4 * T::kVRow + 16>(va_addr);
-  vh[1][2] = lds16<8 * T::kVRow + 16>(va_addr); vh[1][3] = lds16<12 * T::kVRow + 16>(va_addr);
+  uint32_t vh[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
+  if (kDoV) {
+    vh[0][0] = lds16<0>(va_addr); vh[0][1] = lds16<4 * T::kVRow>(va_addr);
+    vh[0][2] = lds16<8 * T::kVRow>(va_addr); vh[0][3] = lds16<12 * T::kVRow>(va_addr);
+    vh[1][0] = lds16<16>(va_addr); vh[1][1] = lds16<4 * T::kVRow + 16>(va_addr);
+    vh[1][2] = lds16<8 * T::kVRow + 16>(va_addr); vh[1][3] = lds16<12 * T::kVRow + 16>(va_addr);
+  }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  {
+  if (kDoK) {
     const uint32_t sc0 = prmt(ksw0, ksw0, st.ks_sel), sc1 = prmt(ksw1, ksw1, st.ks_sel);
     st.smax_bits = max(st.smax_bits, max(sc0 & 0x7FFFu, sc1 & 0x7FFFu));
     uint32_t R0[2][8], R1[2][8];
@@ -208,22 +217,34 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
   float s1 = acc[1] * attn;  // row g,   head 2tig+1
   float s2 = acc[2] * attn;  // row g+8, head 2tig
   float s3 = acc[3] * attn;  // row g+8, head 2tig+1
+  const bool lo = !kPartial || t0 < valid, hi = !kPartial || t0 + 8 < valid;
+  if (!kDoK) {
+    // the scores an earlier scan stored (heads past the group stay at 0: their columns are dropped)
+    if (st0 && lo) s0 = sp0[0];
+    if (st0 && hi) s2 = sp0[8];
+    if (st1 && lo) s1 = sp1[0];
+    if (st1 && hi) s3 = sp1[8];
+  }
   if (kPartial) {
-    const bool lo = t0 < valid, hi = t0 + 8 < valid;
     if (!lo) { s0 = s1 = -INFINITY; }
     if (!hi) { s2 = s3 = -INFINITY; }
-    if (st0 && lo) sp0[0] = s0;
-    if (st0 && hi) sp0[8] = s2;
-    if (st1 && lo) sp1[0] = s1;
-    if (st1 && hi) sp1[8] = s3;
-  } else {
-    if (st0) { sp0[0] = s0; sp0[8] = s2; }
-    if (st1) { sp1[0] = s1; sp1[8] = s3; }
+  }
+  if (kDoK) {
+    if (kPartial) {
+      if (st0 && lo) sp0[0] = s0;
+      if (st0 && hi) sp0[8] = s2;
+      if (st1 && lo) sp1[0] = s1;
+      if (st1 && hi) sp1[8] = s3;
+    } else {
+      if (st0) { sp0[0] = s0; sp0[8] = s2; }
+      if (st1) { sp1[0] = s1; sp1[8] = s3; }
+    }
   }
 
   // ---------------- online softmax ----------------
   float p0, p1, p2, p3;
   softmax_step(s0, s1, s2, s3, st.m_ref0, st.m_ref1, st.l0, st.l1, st.oacc, p0, p1, p2, p3);
+  if (!kDoV) return;
 
   // ---------------- V: unpack + (P * vscale).V ----------------
 #pragma unroll
@@ -248,11 +269,13 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
 // ------------------------------------------------------------------------------------
 // K3V2
 // ------------------------------------------------------------------------------------
-template <int DT>
+template <int DT, int kParts>
 __global__ void __launch_bounds__(kScanWarps * 32, (DT == JF_DTYPE_FP16) ? 3 : 4)
 scan_k3v2_kernel(const ScanParams p) {
   using T = Tile<JF_MODE_K3V2>;
   constexpr int kQTerms = (DT == JF_DTYPE_FP16) ? 2 : 1;
+  constexpr bool kDoK = kParts != 2, kDoV = kParts != 1;
+  constexpr uint32_t kTxPage = (kDoK ? T::kKPage + T::kSPage : 0) + (kDoV ? T::kVPage + T::kSPage : 0);
   extern __shared__ __align__(128) uint8_t smem[];
   // the warp index is the same for all lanes; routing it through a shuffle tells the
   // compiler so, and lets stage / barrier addresses live in uniform registers
@@ -320,16 +343,24 @@ scan_k3v2_kernel(const ScanParams p) {
       const int64_t ra = ent_a.x, rb = ent_b.x;
       const bool joined = two && rb == ra + 16;
       const uint32_t n = joined ? 2u : 1u;
-      mbar_expect_tx_u32(bar, two ? 2 * T::kPageTx : T::kPageTx);
-      bulk_g2s_u32_hint(dst, p.k_data + ra * T::kKRow, n * T::kKPage, bar, stream_policy);
-      bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + ra * T::kVRow, n * T::kVPage, bar, stream_policy);
-      bulk_g2s_u32(dst + T::kKsOff, ks_b + ra * (2 * T::kNG), n * T::kSPage, bar);
-      bulk_g2s_u32(dst + T::kKsOff + T::kVsRel, vs_b + ra * (2 * T::kNG), n * T::kSPage, bar);
+      mbar_expect_tx_u32(bar, two ? 2 * kTxPage : kTxPage);
+      if (kDoK) {
+        bulk_g2s_u32_hint(dst, p.k_data + ra * T::kKRow, n * T::kKPage, bar, stream_policy);
+        bulk_g2s_u32(dst + T::kKsOff, ks_b + ra * (2 * T::kNG), n * T::kSPage, bar);
+      }
+      if (kDoV) {
+        bulk_g2s_u32_hint(dst + T::kVOff, p.v_data + ra * T::kVRow, n * T::kVPage, bar, stream_policy);
+        bulk_g2s_u32(dst + T::kKsOff + T::kVsRel, vs_b + ra * (2 * T::kNG), n * T::kSPage, bar);
+      }
       if (two && !joined) {
-        bulk_g2s_u32_hint(dst + T::kKPage, p.k_data + rb * T::kKRow, T::kKPage, bar, stream_policy);
-        bulk_g2s_u32_hint(dst + T::kVOff + T::kVPage, p.v_data + rb * T::kVRow, T::kVPage, bar, stream_policy);
-        bulk_g2s_u32(dst + T::kKsOff + T::kSPage, ks_b + rb * (2 * T::kNG), T::kSPage, bar);
-        bulk_g2s_u32(dst + T::kKsOff + T::kVsRel + T::kSPage, vs_b + rb * (2 * T::kNG), T::kSPage, bar);
+        if (kDoK) {
+          bulk_g2s_u32_hint(dst + T::kKPage, p.k_data + rb * T::kKRow, T::kKPage, bar, stream_policy);
+          bulk_g2s_u32(dst + T::kKsOff + T::kSPage, ks_b + rb * (2 * T::kNG), T::kSPage, bar);
+        }
+        if (kDoV) {
+          bulk_g2s_u32_hint(dst + T::kVOff + T::kVPage, p.v_data + rb * T::kVRow, T::kVPage, bar, stream_policy);
+          bulk_g2s_u32(dst + T::kKsOff + T::kVsRel + T::kSPage, vs_b + rb * (2 * T::kNG), T::kSPage, bar);
+        }
       }
     }
   };
@@ -347,7 +378,7 @@ scan_k3v2_kernel(const ScanParams p) {
   //      pairs groups (0,1) in b0 and (2,3) in b1.  A bf16 query is used as is; an fp16 query
   //      (11-bit significand) is split exactly into two bf16 terms, hi + lo. ----
   K3State<kQTerms> st;
-  {
+  if (kDoK) {
     const int h = hkv * p.G + g;
     const bool live = g < p.G;
     const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + h) * JF_HEAD_DIM;
@@ -418,9 +449,9 @@ scan_k3v2_kernel(const ScanParams p) {
       const int live = bt_s[(it + k) & (2 * kBtChunk - 1)].y;   // the page's parked entry is still resident
       const uint32_t ko = k_addr_off + k * T::kKPage, vo = v_addr_off + k * T::kVPage, so = s_addr_off + k * T::kSPage;
       if (live != 16)
-        k3v2_page<kQTerms, true>(st, sb, ko, vo, so, t0, live, attn, sp0, sp1, st0, st1);
+        k3v2_page<kQTerms, true, kParts>(st, sb, ko, vo, so, t0, live, attn, sp0, sp1, st0, st1);
       else
-        k3v2_page<kQTerms, false>(st, sb, ko, vo, so, t0, 16, attn, sp0, sp1, st0, st1);
+        k3v2_page<kQTerms, false, kParts>(st, sb, ko, vo, so, t0, 16, attn, sp0, sp1, st0, st1);
       sp0 += 16;
       sp1 += 16;
     }
@@ -477,13 +508,32 @@ jf_status_t validate_decode_args(const jf_decode_args* a) {
   if (a->top_k < 1 || a->top_k > JF_MAX_TOP_K) return JF_ERR_UNSUPPORTED;
   if (a->max_blocks < (a->max_S + 15) / 16) return JF_ERR_ARG;
   if (a->num_slots <= 0 || (a->num_slots % 16) != 0) return JF_ERR_ARG;
-  if (!a->q || !a->k_data || !a->k_scales || !a->v_data || !a->v_scales || !a->block_table || !a->seq_lens)
-    return JF_ERR_ARG;
+  // the scan kernels carry a page's first cache row (over all KV heads) as a 32-bit integer
+  if (static_cast<uint64_t>(a->H_kv) * static_cast<uint64_t>(a->num_slots) > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
+  if (a->scan_parts < JF_SCAN_ALL || a->scan_parts > JF_SCAN_V_ONLY) return JF_ERR_ARG;
+  if (a->stage_b != JF_STAGE_B_FP32 && a->stage_b != JF_STAGE_B_INT8P) return JF_ERR_ARG;
+  if (a->stage_b == JF_STAGE_B_INT8P && a->mode != JF_MODE_K4V4) return JF_ERR_UNSUPPORTED;
+  const bool need_k = a->scan_parts != JF_SCAN_V_ONLY, need_v = a->scan_parts != JF_SCAN_K_ONLY;
+  if (!a->block_table || !a->seq_lens) return JF_ERR_ARG;
+  if (need_k && (!a->q || !a->k_data || !a->k_scales)) return JF_ERR_ARG;
+  if (need_v && (!a->v_data || !a->v_scales)) return JF_ERR_ARG;
+  if (!need_k && !a->scores) return JF_ERR_ARG;   // the scores are this call's input
   if (!aligned(a->k_data, 16) || !aligned(a->v_data, 16) || !aligned(a->k_scales, 16) || !aligned(a->v_scales, 16))
     return JF_ERR_ARG;
   if (!a->workspace || !aligned(a->workspace, 256)) return JF_ERR_WORKSPACE;
   if (a->workspace_bytes < jf_decode_workspace_bytes(a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k))
     return JF_ERR_WORKSPACE;
+  return JF_OK;
+}
+
+template <int DT, int kParts>
+jf_status_t launch_k3v2(const ScanParams& sp, dim3 grid, cudaStream_t stream) {
+  using T = Tile<JF_MODE_K3V2>;
+  const size_t smem = kScanWarps * T::kSlots * (T::kSlotBytes + 8) + kScanWarps * 2 * kBtChunk * 8;  // ring, barriers, block-table chunks
+  static_assert(kScanWarps * T::kSlots * T::kSlotBytes >= kMergeBytes, "merge buffer");
+  JF_ENSURE_SMEM((scan_k3v2_kernel<DT, kParts>), smem);
+  JF_CUDA_TRY(launch_pdl(scan_k3v2_kernel<DT, kParts>, grid, dim3(kScanWarps * 32), smem, stream, sp));
+  JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
 }
 
@@ -524,24 +574,24 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.pages_per_split = (pages + sp.splits - 1) / sp.splits;
   sp.pages_per_warp = (sp.pages_per_split + kScanWarps - 1) / kScanWarps;
   sp.attn_scale = a->attn_scale;
+  sp.q_dtype = a->q_dtype;
   dim3 grid(sp.splits, a->H_kv, a->B);
   if (a->mode == JF_MODE_K3V2) {
-    using T = Tile<JF_MODE_K3V2>;
-    const size_t smem = kScanWarps * T::kSlots * (T::kSlotBytes + 8) + kScanWarps * 2 * kBtChunk * 8;  // ring, barriers, block-table chunks
-    static_assert(kScanWarps * T::kSlots * T::kSlotBytes >= kMergeBytes, "merge buffer");
-    if (a->q_dtype == JF_DTYPE_BF16) {
-      JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_BF16>, smem);
-      JF_CUDA_TRY(launch_pdl(scan_k3v2_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp));
+    // the query's type only matters where the query is read
+    const int dt = a->scan_parts == JF_SCAN_V_ONLY ? JF_DTYPE_BF16 : a->q_dtype;
+    if (dt == JF_DTYPE_BF16) {
+      if (a->scan_parts == JF_SCAN_ALL) st = launch_k3v2<JF_DTYPE_BF16, 0>(sp, grid, stream);
+      else if (a->scan_parts == JF_SCAN_K_ONLY) st = launch_k3v2<JF_DTYPE_BF16, 1>(sp, grid, stream);
+      else st = launch_k3v2<JF_DTYPE_BF16, 2>(sp, grid, stream);
     } else {
-      JF_ENSURE_SMEM(scan_k3v2_kernel<JF_DTYPE_FP16>, smem);
-      JF_CUDA_TRY(launch_pdl(scan_k3v2_kernel<JF_DTYPE_FP16>, grid, dim3(kScanWarps * 32), smem, stream, sp));
+      if (a->scan_parts == JF_SCAN_ALL) st = launch_k3v2<JF_DTYPE_FP16, 0>(sp, grid, stream);
+      else st = launch_k3v2<JF_DTYPE_FP16, 1>(sp, grid, stream);
     }
-    JF_CUDA_TRY(cudaGetLastError());
   } else {
-    st = launch_scan_k4v4(sp, a->q_dtype, grid, stream);
-    if (st != JF_OK) return st;
+    st = launch_scan_k4v4(sp, a->stage_b == JF_STAGE_B_INT8P, a->scan_parts, grid, stream);
   }
-  if (a->scores) {
+  if (st != JF_OK) return st;
+  if (a->scores && a->scan_parts != JF_SCAN_V_ONLY) {
     fill_neg_inf_tail_kernel<<<a->B * a->H_q, 256, 0, stream>>>(a->scores, a->seq_lens, a->H_q, a->max_S);
     JF_CUDA_TRY(cudaGetLastError());
   }

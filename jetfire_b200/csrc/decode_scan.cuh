@@ -51,6 +51,10 @@ struct ScanParams {
   int B, H_q, H_kv, G, max_S, max_blocks, splits, pages_per_split;
   int pages_per_warp;   // a warp's contiguous share of a split: ceil(pages_per_split / kScanWarps)
   float attn_scale;
+  int q_dtype;
+  // K4V4: work is cut into two-page tiles (see scan_k4v4_kernel)
+  int n_tiles, tiles_per_split, tiles_per_warp, ref_chunk;
+  int tile_base[9];
 };
 
 constexpr uint32_t kMagic = 0x64006400u;  // fp16 1024.0 in both halves
@@ -157,6 +161,8 @@ __device__ __forceinline__ void softmax_step(float s0, float s1, float s2, float
   l1 += p1 + p3;
 }
 
-jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaStream_t stream);
+// parts: 0 = scores and output partials, 1 = scores and softmax sums only, 2 = output partials from
+// stored scores; int8p: the reference's batch > 1 weight rounding
+jf_status_t launch_scan_k4v4(ScanParams sp, bool int8p, int parts, dim3 grid, cudaStream_t stream);
 
 }  // namespace jf

@@ -20,6 +20,7 @@
 // with bits 1..2 of the row index -- fragment loads then touch all banks once.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 #include <unordered_map>
 
@@ -96,13 +97,13 @@ constexpr int kAccMagic = 0x4B400000;
 __device__ __forceinline__ float acc_to_f32(int acc_biased) { return __int_as_float(acc_biased) - 12582912.0f; }
 
 // Shared memory of a CTA: the warps' rings, their barriers (one per two-page slot), the query
-// exchange buffer, the parked block-table entries.
+// exchange buffer, the parked tile descriptors.
 constexpr int kPagesInFlight = 2 * T4::kSlots;                                  // per warp
 constexpr int kRingBytes = kScanWarps * T4::kSlots * T4::kSlotBytes;
 constexpr int kBarOff = kRingBytes;
 constexpr int kQxOff = kBarOff + 64;                                            // 4 warps x 2 barriers
 constexpr int kBtOff = kQxOff + kScanWarps * 6 * 32 * 4;
-constexpr int kSmemBytes = kBtOff + kScanWarps * 2 * kBtChunk * 8 + 1024;       // + alignment slack
+constexpr int kSmemBytes = kBtOff + kScanWarps * 2 * kBtChunk * 16 + 1024;      // tile descriptors + alignment slack
 static_assert(kScanWarps * T4::kSlots * 8 <= 64 && kRingBytes >= kMergeBytes && kBtOff % 16 == 0, "layout");
 
 struct K4State {
@@ -116,136 +117,122 @@ struct K4State {
   uint32_t s_off;             // byte offset of this lane's scale entries
 };
 
-// One 16-token page; kPartial as in the K3V2 kernel.
-// `sb` = shared-memory address of the page's K tile (its V tile follows at kVOff), `ss` = of its
-// K scales (its V scales follow at kVsOff).
-template <bool kPartial>
-__device__ __forceinline__ void k4v4_page(K4State& st, uint32_t sb, uint32_t ss, int t0, int valid, float attn,
-                                          float* sp0, float* sp1, bool st0, bool st1) {
-  // ---------------- K: nibbles -> u8 fragments, exact integer Q.K^T per block ----------------
-  // all shared-memory reads of the page are issued up front
-  uint32_t kw[4][2];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const uint32_t a = sb + st.k_off[c];
-    kw[c][0] = lds32<0>(a); kw[c][1] = lds32<512>(a);
+// One tile: two 16-token pages (the second may be absent) processed together, written out so
+// that the two pages' instruction streams interleave (the asm statements keep their program
+// order): all shared-memory loads first, the integer MMAs of both pages alternating, one
+// softmax step over both pages' scores (one reference-point check instead of two), then the
+// P.V MMAs of both pages into the same accumulator tiles.  A warp is one long dependent chain
+// per page; with four warps per scheduler that chain, not the instruction count, set the pace.
+//
+// `sbA / sbB` = shared-memory addresses of the pages' K tiles (V tiles follow at kVOff),
+// `ssA / ssB` = of their K scales (V scales follow at kVsOff).
+// kMasked: `mask` holds, per page, the range [lo, hi) of its 16 tokens that belong to this tile
+//   (the last page of a sequence, a page whose block id was invalid, a page cut by a boundary of
+//   the reference's splits, an absent second page); tokens outside score -inf and weigh nothing.
+// kInt8P: the weights follow the reference's batch > 1 Stage B for this mode
+//   (jetfire_vllm/csrc/int8tc_softmax_v_fused.cu:1203-1235): per tile of 32 tokens and query
+//   head, pv = p * v_scale is rounded to 127 levels of the tile's largest pv before it meets V.
+//   (The reference then multiplies integers and rescales; here the rounded pv goes on as a
+//   16-bit float -- the same numbers up to 2^-12 relative.)  The reference normalises p before
+//   rounding and this kernel after (online softmax), which changes neither the levels nor the
+//   rounding except for ties at the last float bit.
+// kParts: 0 = scores and output partials; 1 = scores and softmax sums only (no V);
+//   2 = output partials from scores read back from memory (no K).
+template <bool kInt8P, bool kMasked, int kParts>
+__device__ __forceinline__ void k4v4_tile(K4State& st, uint32_t sbA, uint32_t sbB, uint32_t ssA, uint32_t ssB,
+                                          int mask, int t0, float attn, float* spA0, float* spA1, bool st0, bool st1) {
+  constexpr bool kDoK = kParts != 2, kDoV = kParts != 1;
+  bool aLo = true, aHi = true, bLo = true, bHi = true;   // is this lane's token of page A / B (rows g, g + 8) in the tile
+  if (kMasked) {
+    const int loA = mask & 31, hiA = (mask >> 5) & 31, loB = (mask >> 10) & 31, hiB = (mask >> 15) & 31;
+    aLo = t0 >= loA && t0 < hiA;  aHi = t0 + 8 >= loA && t0 + 8 < hiA;
+    bLo = t0 >= loB && t0 < hiB;  bHi = t0 + 8 >= loB && t0 + 8 < hiB;
   }
-  const uint32_t sa = ss + st.s_off;
-  const uint32_t ksb0 = lds16<0>(sa), ksb1 = lds16<16>(sa), vsb0 = lds16<T4::kVsOff>(sa), vsb1 = lds16<T4::kVsOff + 16>(sa);
-  const uint32_t aA = sb + st.v_offA, aB = sb + st.v_offB;
-  const uint2 Wa = lds64<0>(aA), Wb = lds64<0>(aB), Wc = lds64<512>(aA), Wd = lds64<512>(aB);
-  int acc[4][4];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const uint32_t w0 = kw[c][0], w1 = kw[c][1];
-    mma_u8s8_cd(acc[c], st.init[c], (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu,
-                st.qb[c][0], st.qb[c][1]);
-  }
-  const float ks0 = __uint_as_float(ksb0 << 16), ks1 = __uint_as_float(ksb1 << 16);
-  float vs0 = __uint_as_float(vsb0 << 16), vs1 = __uint_as_float(vsb1 << 16);
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    s0 = __fmaf_rn(acc_to_f32(acc[c][0]), st.qs_h0[c], s0);
-    s1 = __fmaf_rn(acc_to_f32(acc[c][1]), st.qs_h1[c], s1);
-    s2 = __fmaf_rn(acc_to_f32(acc[c][2]), st.qs_h0[c], s2);
-    s3 = __fmaf_rn(acc_to_f32(acc[c][3]), st.qs_h1[c], s3);
-  }
-  s0 = __fmul_rn(__fmul_rn(s0, ks0), attn);
-  s1 = __fmul_rn(__fmul_rn(s1, ks0), attn);
-  s2 = __fmul_rn(__fmul_rn(s2, ks1), attn);
-  s3 = __fmul_rn(__fmul_rn(s3, ks1), attn);
-  if (kPartial) {
-    const bool lo = t0 < valid, hi = t0 + 8 < valid;
-    if (!lo) { s0 = s1 = -INFINITY; vs0 = 0.f; }
-    if (!hi) { s2 = s3 = -INFINITY; vs1 = 0.f; }
-    if (st0 && lo) sp0[0] = s0;
-    if (st0 && hi) sp0[8] = s2;
-    if (st1 && lo) sp1[0] = s1;
-    if (st1 && hi) sp1[8] = s3;
-  } else {
-    if (st0) { sp0[0] = s0; sp0[8] = s2; }
-    if (st1) { sp1[0] = s1; sp1[8] = s3; }
-  }
-
-  // ---------------- online softmax ----------------
-  float p0, p1, p2, p3;
-  softmax_step(s0, s1, s2, s3, st.m_ref0, st.m_ref1, st.l0, st.l1, st.oacc, p0, p1, p2, p3);
-
-  // ---------------- V: nibbles -> fp16 fragments, (P * vscale).V ----------------
-  const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * vs0, p1 * vs0));  // tokens tA, tB
-  const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vs1, p3 * vs1));  // tokens tA+8, tB+8
-  const uint32_t wa[2] = {Wa.x, Wa.y}, wb[2] = {Wb.x, Wb.y}, wc[2] = {Wc.x, Wc.y}, wd[2] = {Wd.x, Wd.y};
-#pragma unroll
-  for (int wi = 0; wi < 2; ++wi) {
-#pragma unroll
-    for (int bp = 0; bp < 2; ++bp) {
-      const uint32_t sel = bp ? 0x7632u : 0x5410u;
-      const uint32_t XA = prmt(wa[wi], wb[wi], sel), XB = prmt(wc[wi], wd[wi], sel);
-      const uint32_t XA2 = XA >> 8, XB2 = XB >> 8;
-      const int mt = 4 * wi + 2 * bp;
-      // low nibble -> output row g, high nibble -> output row g + 8
-      mma_f16_16816(st.oacc[mt], v4_field<0>(XA), v4_field<4>(XA), v4_field<0>(XB), v4_field<4>(XB), B0, B1);
-      mma_f16_16816(st.oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), B0, B1);
-    }
-  }
-  mma_f16_16816(st.oacc[8], kOnesF16x2, kOnesF16x2, kOnesF16x2, kOnesF16x2, B0, B1);
-}
-
-// Two full 16-token pages at once, written out so that the two pages' instruction streams
-// interleave (the asm statements keep their program order): all shared-memory loads first,
-// the integer MMAs of both pages alternating, one softmax step over both pages' scores (one
-// reference-point check instead of two), then the P.V MMAs of both pages into the same
-// accumulator tiles.  A warp is one long dependent chain per page; with four warps per
-// scheduler that chain, not the instruction count, set the pace.
-__device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32_t sbB, uint32_t ssA, uint32_t ssB,
-                                               float attn, float* spA0, float* spA1, float* spB0, float* spB1,
-                                               bool st0, bool st1) {
-  uint32_t kwA[4][2], kwB[4][2];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const uint32_t a = sbA + st.k_off[c], b = sbB + st.k_off[c];
-    kwA[c][0] = lds32<0>(a); kwA[c][1] = lds32<512>(a);
-    kwB[c][0] = lds32<0>(b); kwB[c][1] = lds32<512>(b);
-  }
-  const uint32_t saA = ssA + st.s_off, saB = ssB + st.s_off;
-  const uint32_t ksA0 = lds16<0>(saA), ksA1 = lds16<16>(saA), vsA0b = lds16<T4::kVsOff>(saA), vsA1b = lds16<T4::kVsOff + 16>(saA);
-  const uint32_t ksB0 = lds16<0>(saB), ksB1 = lds16<16>(saB), vsB0b = lds16<T4::kVsOff>(saB), vsB1b = lds16<T4::kVsOff + 16>(saB);
-  int accA[4][4], accB[4][4];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const uint32_t a0 = kwA[c][0], a1 = kwA[c][1], b0 = kwB[c][0], b1 = kwB[c][1];
-    mma_u8s8_cd(accA[c], st.init[c], (a0 >> 4) & 0x0F0F0F0Fu, (a1 >> 4) & 0x0F0F0F0Fu, a0 & 0x0F0F0F0Fu, a1 & 0x0F0F0F0Fu,
-                st.qb[c][0], st.qb[c][1]);
-    mma_u8s8_cd(accB[c], st.init[c], (b0 >> 4) & 0x0F0F0F0Fu, (b1 >> 4) & 0x0F0F0F0Fu, b0 & 0x0F0F0F0Fu, b1 & 0x0F0F0F0Fu,
-                st.qb[c][0], st.qb[c][1]);
-  }
-  // V words of both pages: requested now, used after the softmax
-  const uint32_t vA0 = sbA + st.v_offA, vA1 = sbA + st.v_offB, vB0 = sbB + st.v_offA, vB1 = sbB + st.v_offB;
-  const uint2 WaA = lds64<0>(vA0), WbA = lds64<0>(vA1), WcA = lds64<512>(vA0), WdA = lds64<512>(vA1);
-  const uint2 WaB = lds64<0>(vB0), WbB = lds64<0>(vB1), WcB = lds64<512>(vB0), WdB = lds64<512>(vB1);
+  float* spB0 = spA0 + 16;
+  float* spB1 = spA1 + 16;
   float sA[4] = {0.f, 0.f, 0.f, 0.f}, sB[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t saA = ssA + st.s_off, saB = ssB + st.s_off;
+  if (kDoK) {
+    uint32_t kwA[4][2], kwB[4][2];
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    sA[0] = __fmaf_rn(acc_to_f32(accA[c][0]), st.qs_h0[c], sA[0]);
-    sB[0] = __fmaf_rn(acc_to_f32(accB[c][0]), st.qs_h0[c], sB[0]);
-    sA[1] = __fmaf_rn(acc_to_f32(accA[c][1]), st.qs_h1[c], sA[1]);
-    sB[1] = __fmaf_rn(acc_to_f32(accB[c][1]), st.qs_h1[c], sB[1]);
-    sA[2] = __fmaf_rn(acc_to_f32(accA[c][2]), st.qs_h0[c], sA[2]);
-    sB[2] = __fmaf_rn(acc_to_f32(accB[c][2]), st.qs_h0[c], sB[2]);
-    sA[3] = __fmaf_rn(acc_to_f32(accA[c][3]), st.qs_h1[c], sA[3]);
-    sB[3] = __fmaf_rn(acc_to_f32(accB[c][3]), st.qs_h1[c], sB[3]);
-  }
-  {
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t a = sbA + st.k_off[c], b = sbB + st.k_off[c];
+      kwA[c][0] = lds32<0>(a); kwA[c][1] = lds32<512>(a);
+      kwB[c][0] = lds32<0>(b); kwB[c][1] = lds32<512>(b);
+    }
+    const uint32_t ksA0 = lds16<0>(saA), ksA1 = lds16<16>(saA), ksB0 = lds16<0>(saB), ksB1 = lds16<16>(saB);
+    int accA[4][4], accB[4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t a0 = kwA[c][0], a1 = kwA[c][1], b0 = kwB[c][0], b1 = kwB[c][1];
+      mma_u8s8_cd(accA[c], st.init[c], (a0 >> 4) & 0x0F0F0F0Fu, (a1 >> 4) & 0x0F0F0F0Fu, a0 & 0x0F0F0F0Fu, a1 & 0x0F0F0F0Fu,
+                  st.qb[c][0], st.qb[c][1]);
+      mma_u8s8_cd(accB[c], st.init[c], (b0 >> 4) & 0x0F0F0F0Fu, (b1 >> 4) & 0x0F0F0F0Fu, b0 & 0x0F0F0F0Fu, b1 & 0x0F0F0F0Fu,
+                  st.qb[c][0], st.qb[c][1]);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      sA[0] = __fmaf_rn(acc_to_f32(accA[c][0]), st.qs_h0[c], sA[0]);
+      sB[0] = __fmaf_rn(acc_to_f32(accB[c][0]), st.qs_h0[c], sB[0]);
+      sA[1] = __fmaf_rn(acc_to_f32(accA[c][1]), st.qs_h1[c], sA[1]);
+      sB[1] = __fmaf_rn(acc_to_f32(accB[c][1]), st.qs_h1[c], sB[1]);
+      sA[2] = __fmaf_rn(acc_to_f32(accA[c][2]), st.qs_h0[c], sA[2]);
+      sB[2] = __fmaf_rn(acc_to_f32(accB[c][2]), st.qs_h0[c], sB[2]);
+      sA[3] = __fmaf_rn(acc_to_f32(accA[c][3]), st.qs_h1[c], sA[3]);
+      sB[3] = __fmaf_rn(acc_to_f32(accB[c][3]), st.qs_h1[c], sB[3]);
+    }
     const float kA0 = __uint_as_float(ksA0 << 16), kA1 = __uint_as_float(ksA1 << 16);
     const float kB0 = __uint_as_float(ksB0 << 16), kB1 = __uint_as_float(ksB1 << 16);
     sA[0] = __fmul_rn(__fmul_rn(sA[0], kA0), attn); sB[0] = __fmul_rn(__fmul_rn(sB[0], kB0), attn);
     sA[1] = __fmul_rn(__fmul_rn(sA[1], kA0), attn); sB[1] = __fmul_rn(__fmul_rn(sB[1], kB0), attn);
     sA[2] = __fmul_rn(__fmul_rn(sA[2], kA1), attn); sB[2] = __fmul_rn(__fmul_rn(sB[2], kB1), attn);
     sA[3] = __fmul_rn(__fmul_rn(sA[3], kA1), attn); sB[3] = __fmul_rn(__fmul_rn(sB[3], kB1), attn);
+  } else {
+    // the scores an earlier scan stored (heads past the group stay at 0: their columns are dropped)
+    if (st0) {
+      if (aLo) sA[0] = spA0[0];
+      if (aHi) sA[2] = spA0[8];
+      if (bLo) sB[0] = spB0[0];
+      if (bHi) sB[2] = spB0[8];
+    }
+    if (st1) {
+      if (aLo) sA[1] = spA1[0];
+      if (aHi) sA[3] = spA1[8];
+      if (bLo) sB[1] = spB1[0];
+      if (bHi) sB[3] = spB1[8];
+    }
   }
-  if (st0) { spA0[0] = sA[0]; spA0[8] = sA[2]; spB0[0] = sB[0]; spB0[8] = sB[2]; }
-  if (st1) { spA1[0] = sA[1]; spA1[8] = sA[3]; spB1[0] = sB[1]; spB1[8] = sB[3]; }
+  // V words and scales of both pages: requested now, used after the softmax
+  uint2 WaA, WbA, WcA, WdA, WaB, WbB, WcB, WdB;
+  float vsA0 = 0.f, vsA1 = 0.f, vsB0 = 0.f, vsB1 = 0.f;
+  if (kDoV) {
+    const uint32_t vA0 = sbA + st.v_offA, vA1 = sbA + st.v_offB, vB0 = sbB + st.v_offA, vB1 = sbB + st.v_offB;
+    WaA = lds64<0>(vA0); WbA = lds64<0>(vA1); WcA = lds64<512>(vA0); WdA = lds64<512>(vA1);
+    WaB = lds64<0>(vB0); WbB = lds64<0>(vB1); WcB = lds64<512>(vB0); WdB = lds64<512>(vB1);
+    vsA0 = __uint_as_float(lds16<T4::kVsOff>(saA) << 16); vsA1 = __uint_as_float(lds16<T4::kVsOff + 16>(saA) << 16);
+    vsB0 = __uint_as_float(lds16<T4::kVsOff>(saB) << 16); vsB1 = __uint_as_float(lds16<T4::kVsOff + 16>(saB) << 16);
+  }
+  if (kMasked) {
+    if (!aLo) { sA[0] = sA[1] = -INFINITY; vsA0 = 0.f; }
+    if (!aHi) { sA[2] = sA[3] = -INFINITY; vsA1 = 0.f; }
+    if (!bLo) { sB[0] = sB[1] = -INFINITY; vsB0 = 0.f; }
+    if (!bHi) { sB[2] = sB[3] = -INFINITY; vsB1 = 0.f; }
+  }
+  if (kDoK) {
+    if (kMasked) {
+      if (st0 && aLo) spA0[0] = sA[0];
+      if (st0 && aHi) spA0[8] = sA[2];
+      if (st0 && bLo) spB0[0] = sB[0];
+      if (st0 && bHi) spB0[8] = sB[2];
+      if (st1 && aLo) spA1[0] = sA[1];
+      if (st1 && aHi) spA1[8] = sA[3];
+      if (st1 && bLo) spB1[0] = sB[1];
+      if (st1 && bHi) spB1[8] = sB[3];
+    } else {
+      if (st0) { spA0[0] = sA[0]; spA0[8] = sA[2]; spB0[0] = sB[0]; spB0[8] = sB[2]; }
+      if (st1) { spA1[0] = sA[1]; spA1[8] = sA[3]; spB1[0] = sB[1]; spB1[8] = sB[3]; }
+    }
+  }
 
   // ---- one online-softmax step over both pages (same arithmetic per score as softmax_step) ----
   float pA[4], pB[4];
@@ -261,8 +248,10 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
       const float n0 = fmaxf(st.m_ref0, mx0), n1 = fmaxf(st.m_ref1, mx1);
       const float f0 = ex2((st.m_ref0 - n0) * kLog2e), f1 = ex2((st.m_ref1 - n1) * kLog2e);
       st.l0 *= f0; st.l1 *= f1;
+      if (kDoV) {
 #pragma unroll
-      for (int i = 0; i < 9; ++i) { st.oacc[i][0] *= f0; st.oacc[i][1] *= f1; st.oacc[i][2] *= f0; st.oacc[i][3] *= f1; }
+        for (int i = 0; i < 9; ++i) { st.oacc[i][0] *= f0; st.oacc[i][1] *= f1; st.oacc[i][2] *= f0; st.oacc[i][3] *= f1; }
+      }
       st.m_ref0 = n0; st.m_ref1 = n1;
     }
     const float mb0 = st.m_ref0 * kLog2e, mb1 = st.m_ref1 * kLog2e;
@@ -273,14 +262,33 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
     st.l0 += (pA[0] + pA[2]) + (pB[0] + pB[2]);
     st.l1 += (pA[1] + pA[3]) + (pB[1] + pB[3]);
   }
+  if (!kDoV) return;
 
   // ---- (P * vscale).V for both pages ----
-  const float vsA0 = __uint_as_float(vsA0b << 16), vsA1 = __uint_as_float(vsA1b << 16);
-  const float vsB0 = __uint_as_float(vsB0b << 16), vsB1 = __uint_as_float(vsB1b << 16);
-  const uint32_t A0 = movmatrix_trans(pack_f16x2_sat(pA[0] * vsA0, pA[1] * vsA0));
-  const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(pB[0] * vsB0, pB[1] * vsB0));
-  const uint32_t A1 = movmatrix_trans(pack_f16x2_sat(pA[2] * vsA1, pA[3] * vsA1));
-  const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(pB[2] * vsB1, pB[3] * vsB1));
+  float wA[4] = {pA[0] * vsA0, pA[1] * vsA0, pA[2] * vsA1, pA[3] * vsA1};
+  float wB[4] = {pB[0] * vsB0, pB[1] * vsB0, pB[2] * vsB1, pB[3] * vsB1};
+  if (kInt8P) {
+    // largest pv of the tile per query head: this lane's four tokens, then the eight lanes that
+    // hold the other tokens of the same head pair
+    float a0 = fmaxf(fmaxf(wA[0], wA[2]), fmaxf(wB[0], wB[2])), a1 = fmaxf(fmaxf(wA[1], wA[3]), fmaxf(wB[1], wB[3]));
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      a0 = fmaxf(a0, __shfl_xor_sync(0xFFFFFFFFu, a0, o));
+      a1 = fmaxf(a1, __shfl_xor_sync(0xFFFFFFFFu, a1, o));
+    }
+    const float sc0 = a0 * (1.0f / 127.0f), sc1 = a1 * (1.0f / 127.0f);
+    const float in0 = sc0 > 0.f ? __frcp_rn(sc0) : 0.f, in1 = sc1 > 0.f ? __frcp_rn(sc1) : 0.f;
+    // round to nearest (ties to even) by adding and removing 1.5 * 2^23: 0 <= pv / scale <= 127
+    constexpr float kRnd = 12582912.0f;
+    wA[0] = (fmaf(wA[0], in0, kRnd) - kRnd) * sc0; wA[1] = (fmaf(wA[1], in1, kRnd) - kRnd) * sc1;
+    wA[2] = (fmaf(wA[2], in0, kRnd) - kRnd) * sc0; wA[3] = (fmaf(wA[3], in1, kRnd) - kRnd) * sc1;
+    wB[0] = (fmaf(wB[0], in0, kRnd) - kRnd) * sc0; wB[1] = (fmaf(wB[1], in1, kRnd) - kRnd) * sc1;
+    wB[2] = (fmaf(wB[2], in0, kRnd) - kRnd) * sc0; wB[3] = (fmaf(wB[3], in1, kRnd) - kRnd) * sc1;
+  }
+  const uint32_t A0 = movmatrix_trans(pack_f16x2_sat(wA[0], wA[1]));
+  const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(wB[0], wB[1]));
+  const uint32_t A1 = movmatrix_trans(pack_f16x2_sat(wA[2], wA[3]));
+  const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(wB[2], wB[3]));
   const uint32_t waA[2] = {WaA.x, WaA.y}, wbA[2] = {WbA.x, WbA.y}, wcA[2] = {WcA.x, WcA.y}, wdA[2] = {WdA.x, WdA.y};
   const uint32_t waB[2] = {WaB.x, WaB.y}, wbB[2] = {WbB.x, WbB.y}, wcB[2] = {WcB.x, WcB.y}, wdB[2] = {WdB.x, WdB.y};
 #pragma unroll
@@ -292,6 +300,7 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
       const uint32_t YA = prmt(waB[wi], wbB[wi], sel), YB = prmt(wcB[wi], wdB[wi], sel);
       const uint32_t XA2 = XA >> 8, XB2 = XB >> 8, YA2 = YA >> 8, YB2 = YB >> 8;
       const int mt = 4 * wi + 2 * bp;
+      // low nibble -> output row g, high nibble -> output row g + 8
       mma_f16_16816(st.oacc[mt], v4_field<0>(XA), v4_field<4>(XA), v4_field<0>(XB), v4_field<4>(XB), A0, A1);
       mma_f16_16816(st.oacc[mt + 1], v4_field<0>(XA2), v4_field<4>(XA2), v4_field<0>(XB2), v4_field<4>(XB2), A0, A1);
       mma_f16_16816(st.oacc[mt], v4_field<0>(YA), v4_field<4>(YA), v4_field<0>(YB), v4_field<4>(YB), B0, B1);
@@ -302,26 +311,25 @@ __device__ __forceinline__ void k4v4_page_pair(K4State& st, uint32_t sbA, uint32
   mma_f16_16816(st.oacc[8], kOnesF16x2, kOnesF16x2, kOnesF16x2, kOnesF16x2, B0, B1);
 }
 
+constexpr int kFullTile = (16 << 5) | (16 << 15) | (2 << 20);   // both pages whole
+
 }  // namespace
 
-template <int DT>
+// Work is cut into tiles of two pages.  kInt8P = false: tile T is pages 2T, 2T + 1 of the
+// sequence.  kInt8P = true: tiles are the reference's -- positions are cut into 8 splits of
+// ceil(max_S / 8), and inside a split the 32-token tiles start at the split's first 16-token
+// block (jetfire_vllm/csrc/int8tc_softmax_v_fused.cu:62, 1049-1053); a block that a split boundary
+// cuts belongs to two tiles, each with its own tokens.  p.tile_base[s] = first tile of split s.
+// A CTA takes a contiguous range of tiles, each of its warps a contiguous quarter of it.
+template <bool kInt8P, int kParts>
 __global__ void __launch_bounds__(kScanWarps * 32, 4)
 scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
                  const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_map2,
                  const __grid_constant__ CUtensorMap v_map2) {
+  constexpr bool kDoK = kParts != 2, kDoV = kParts != 1;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // swizzled tiles must sit on 512-byte boundaries: align by hand (1 KB of slack is allocated)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  JF_PHASE(0);
-  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  JF_CTA_STAMP(cta_lin, 0);
-#ifdef JF_PHASE_TIMING
-  if (threadIdx.x == 0 && cta_lin < 1024) {
-    unsigned smid__;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid__));
-    g_cta_t[cta_lin * 8 + 5] = smid__;
-  }
-#endif
   const int warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;  // uniform by construction
   const int g = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -334,103 +342,143 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   if (lane == 0) {
     for (int s = 0; s < T4::kSlots; ++s) mbar_init(&bars[s], 1);
     // the tensor maps are kernel parameters, not results of the previous kernel: fetch them now
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map2)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map2)) : "memory");
+    if (kDoK) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map2)) : "memory");
+    if (kDoV) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map2)) : "memory");
   }
   fence_barrier_init();
   __syncwarp();
   pdl_wait();  // nothing above reads global memory
-  JF_PHASE(1);
-  JF_CTA_STAMP(cta_lin, 1);
 
-  // The first loads (sequence length, the block-table entries of the first ring of pages, the
-  // query) do not depend on one another: all are issued here, so the prologue pays one
-  // memory latency before the first copies can start, and the query arithmetic then runs
-  // while those copies are in flight.
-  // Warp w owns a contiguous quarter of the split's pages, so its block-table entries are
-  // contiguous too: sixteen lanes fetch sixteen entries with one load, a whole chunk ahead of
-  // its use, and park them in shared memory (kBtChunk entries per half of a two-chunk buffer).
-  // A load issued while megabytes of page copies are queued in the memory system takes several
-  // microseconds; fetched one entry at a time, a page or two ahead, those loads stalled the loop.
-  const int pg_first = split * p.pages_per_split + warp * p.pages_per_warp;
-  const int64_t* bt_w = p.block_table + static_cast<int64_t>(b) * p.max_blocks + pg_first;
-  const int bt_avail = p.max_blocks - pg_first;   // entries of the row from this warp's first page on
-  const int len_raw = p.seq_lens[b];
-  // what is parked per page: the first cache row of its block (the tensor copies' y coordinate)
-  // and how many of its 16 tokens are live -- worked out by sixteen lanes at once when a chunk
-  // arrives, so that issuing a page's copies is a shared-memory read and the copies
-  int2* bt_s = reinterpret_cast<int2*>(smem + kBtOff) + warp * (2 * kBtChunk);
-  auto bt_load = [&](int chunk) -> int64_t {   // lanes 0..15: entry 16 * chunk + lane (never read when out of range)
-    const int e = chunk * kBtChunk + lane;
-    return (lane < kBtChunk && e < bt_avail) ? bt_w[e] : -1;
+  // The first loads (sequence length, the block-table entries of the first tiles, the query) do
+  // not depend on one another: all are issued here, so the prologue pays one memory latency before
+  // the first copies can start, and the query arithmetic then runs while those copies are in flight.
+  const int t_first = split * p.tiles_per_split + warp * p.tiles_per_warp;          // this warp's tiles
+  const int t_end = min(min(t_first + p.tiles_per_warp, (split + 1) * p.tiles_per_split), p.n_tiles);
+  const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+  const int len = min(p.seq_lens[b], p.max_S);
+  const int64_t n_blocks_phys = p.num_slots >> 4;
+  const int head_row0 = static_cast<int>(static_cast<int64_t>(hkv) * p.num_slots);  // first cache row of this KV head
+
+  // Tile T of the warp (tile t_first + T of the row): its first page and the token ranges of its
+  // pages, packed as lo_A | hi_A << 5 | lo_B << 10 | hi_B << 15 | pages << 20; 0 = no such tile
+  // (past the warp's range or past the sequence; such tiles are a suffix of the range).
+  auto tile_geom = [&](int T, int& pageA) -> int {
+    const int gT = t_first + T;
+    pageA = 0;
+    if (gT >= t_end) return 0;
+    int s_lo = 0, s_hi = len;
+    pageA = 2 * gT;
+    if (kInt8P) {
+      int s = 0, base = 0;
+#pragma unroll
+      for (int i = 1; i < 8; ++i)
+        if (gT >= p.tile_base[i]) { s = i; base = p.tile_base[i]; }
+      s_lo = s * p.ref_chunk;
+      s_hi = min(s_lo + p.ref_chunk, len);
+      pageA = (s_lo >> 4) + 2 * (gT - base);
+    }
+    const int blk_end = (s_hi + 15) >> 4;
+    if (s_lo >= s_hi || pageA >= blk_end) return 0;
+    const int pa = pageA * 16;
+    const int two = (pageA + 1 < blk_end) ? 1 : 0;
+    const int loA = max(s_lo - pa, 0), hiA = min(s_hi - pa, 16);
+    const int hiB = two ? min(s_hi - pa - 16, 16) : 0;
+    return loA | (hiA << 5) | (hiB << 15) | ((1 + two) << 20);
   };
-  int64_t bt_pend = bt_load(0);
+  // Descriptors are worked out sixteen tiles at a time by sixteen lanes, a whole chunk ahead of
+  // their use (a global load issued while megabytes of page copies are queued in the memory
+  // system takes several microseconds; fetched a tile or two ahead, those loads stalled the
+  // loop), and parked in shared memory: x / y = first cache row of page A / B, z = the token
+  // ranges, w = page A's index in the sequence.
+  int4* desc_s = reinterpret_cast<int4*>(smem + kBtOff) + warp * (2 * kBtChunk);
+  struct Pending { int64_t ba, bb; int pageA, mask; };
+  auto desc_load = [&](int chunk) -> Pending {
+    Pending r{-1, -1, 0, 0};
+    if (lane < kBtChunk) {
+      r.mask = tile_geom(chunk * kBtChunk + lane, r.pageA);
+      if (r.mask) {
+        if (r.pageA < p.max_blocks) r.ba = bt_row[r.pageA];
+        if ((r.mask >> 20) == 2 && r.pageA + 1 < p.max_blocks) r.bb = bt_row[r.pageA + 1];
+      }
+    }
+    return r;
+  };
+  // an invalid block id reads block 0 and counts no live token
+  auto desc_make = [&](const Pending& r) -> int4 {
+    int mask = r.mask;
+    const bool badA = r.ba < 0 || r.ba >= n_blocks_phys, badB = r.bb < 0 || r.bb >= n_blocks_phys;
+    if (badA) mask &= ~0x3FF;
+    if (badB) mask &= ~(0x3FF << 10);
+    const int rowA = head_row0 + static_cast<int>(badA ? 0 : r.ba) * 16;
+    const int rowB = (mask >> 20) == 2 ? head_row0 + static_cast<int>(badB ? 0 : r.bb) * 16 : -1;
+    return make_int4(rowA, rowB, mask, r.pageA);
+  };
+  Pending pend = desc_load(0);
   // warp w prepares the query's 32-channel block w for the whole CTA (see below)
   uint4 q_raw = make_uint4(0u, 0u, 0u, 0u);
-  if (g < p.G) {   // the 8 channels 32 w + 8 tig + {0..7} are 16 contiguous bytes
+  if (kDoK && g < p.G) {   // the 8 channels 32 w + 8 tig + {0..7} are 16 contiguous bytes
     const int64_t qbase = (static_cast<int64_t>(b) * p.H_q + hkv * p.G + g) * JF_HEAD_DIM;
     q_raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.q) + qbase + 32 * warp + 8 * tig));
   }
-  const int len = min(len_raw, p.max_S);
-  const int n_pages = (len + 15) >> 4;
-  const int my_n = max(0, min(min(pg_first + p.pages_per_warp, (split + 1) * p.pages_per_split), n_pages) - pg_first);
 
-  const int64_t n_blocks_phys = p.num_slots >> 4;
-  const int64_t head_row0 = static_cast<int64_t>(hkv) * p.num_slots;  // first cache row of this KV head
-  const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
-
-  // One elected lane issues the page's two tensor copies (K, V) and two scale copies.
+  // One elected lane issues a tile's copies: per page a tensor copy for K and one for V and two
+  // scale copies; two pages whose blocks are neighbours in the cache take one 32-row tensor copy
+  // per tensor and one 64-byte copy per scale array.  Everything lands on the slot's barrier.
   // The packed cache is read once per call: fetched as first-to-evict, it leaves the scores
   // this kernel writes (and the next kernel reads) in L2.
   const uint64_t stream_policy = l2_policy_evict_first();
-  // entry e of this warp (page pg_first + e) from its block id: an invalid block id reads
-  // block 0 and counts no live token; the sequence's last page may be partial
-  auto bt_entry = [&](int64_t blk64, int e) -> int2 {
-    const int pg = pg_first + e;
-    const bool bad = blk64 < 0 || blk64 >= n_blocks_phys;
-    const int valid = bad ? 0 : (pg == last_pg ? len - pg * 16 : 16);
-    return make_int2(static_cast<int>(head_row0 + (bad ? 0 : blk64) * 16), valid);
-  };
-  // By one elected lane: the copies of one or two pages into slot `sl`.  Two pages whose blocks
-  // are neighbours in the cache take one 32-row tensor copy per tensor and one 64-byte copy per
-  // scale array; otherwise each page takes its own four copies.  Either way everything lands on
-  // the slot's barrier.
-  auto refill = [&](int sl, int2 ent_a, int2 ent_b, bool two) {
+  constexpr uint32_t kTxPage = (kDoK ? 1056u : 0u) + (kDoV ? 1056u : 0u);
+  auto refill = [&](int sl, int4 d) {
     if (elect_one()) {
       const uint32_t bar = bars0 + sl * 8;
       const uint32_t dst = slots0 + sl * T4::kSlotBytes;
-      const int ra = ent_a.x, rb = ent_b.x;
+      const int ra = d.x, rb = d.y;
+      const bool two = rb >= 0;
       if (two && rb == ra + 16) {
-        mbar_expect_tx_u32(bar, 2 * T4::kPageTx);
-        tma_load_2d_u32(dst, &k_map2, 0, ra, bar, stream_policy);
-        tma_load_2d_u32(dst + T4::kVOff, &v_map2, 0, ra, bar, stream_policy);
-        bulk_g2s_u32(dst + T4::kScaleOff, p.k_scales + ra, 64, bar);
-        bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff, p.v_scales + ra, 64, bar);
+        mbar_expect_tx_u32(bar, 2 * kTxPage);
+        if (kDoK) {
+          tma_load_2d_u32(dst, &k_map2, 0, ra, bar, stream_policy);
+          bulk_g2s_u32(dst + T4::kScaleOff, p.k_scales + ra, 64, bar);
+        }
+        if (kDoV) {
+          tma_load_2d_u32(dst + T4::kVOff, &v_map2, 0, ra, bar, stream_policy);
+          bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff, p.v_scales + ra, 64, bar);
+        }
       } else {
-        mbar_expect_tx_u32(bar, two ? 2 * T4::kPageTx : T4::kPageTx);
-        tma_load_2d_u32(dst, &k_map, 0, ra, bar, stream_policy);
-        tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, ra, bar, stream_policy);
-        bulk_g2s_u32(dst + T4::kScaleOff, p.k_scales + ra, 32, bar);
-        bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff, p.v_scales + ra, 32, bar);
+        mbar_expect_tx_u32(bar, two ? 2 * kTxPage : kTxPage);
+        if (kDoK) {
+          tma_load_2d_u32(dst, &k_map, 0, ra, bar, stream_policy);
+          bulk_g2s_u32(dst + T4::kScaleOff, p.k_scales + ra, 32, bar);
+        }
+        if (kDoV) {
+          tma_load_2d_u32(dst + T4::kVOff, &v_map, 0, ra, bar, stream_policy);
+          bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff, p.v_scales + ra, 32, bar);
+        }
         if (two) {
-          tma_load_2d_u32(dst + T4::kPageBytes, &k_map, 0, rb, bar, stream_policy);
-          tma_load_2d_u32(dst + T4::kPageBytes + T4::kVOff, &v_map, 0, rb, bar, stream_policy);
-          bulk_g2s_u32(dst + T4::kScaleOff + 32, p.k_scales + rb, 32, bar);
-          bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff + 32, p.v_scales + rb, 32, bar);
+          if (kDoK) {
+            tma_load_2d_u32(dst + T4::kPageBytes, &k_map, 0, rb, bar, stream_policy);
+            bulk_g2s_u32(dst + T4::kScaleOff + 32, p.k_scales + rb, 32, bar);
+          }
+          if (kDoV) {
+            tma_load_2d_u32(dst + T4::kPageBytes + T4::kVOff, &v_map, 0, rb, bar, stream_policy);
+            bulk_g2s_u32(dst + T4::kScaleOff + T4::kVsOff + 32, p.v_scales + rb, 32, bar);
+          }
         }
       }
     }
   };
 
   // chunk 0 to shared memory, chunk 1 requested, the ring filled
-  if (lane < kBtChunk) bt_s[lane] = bt_entry(bt_pend, lane);
-  int bt_stored = 0;   // chunks 0..bt_stored are in shared memory; chunk bt_stored + 1 is in bt_pend
-  bt_pend = bt_load(1);
+  if (lane < kBtChunk) desc_s[lane] = desc_make(pend);
+  int stored = 0;   // chunks 0..stored are in shared memory; chunk stored + 1 is in `pend`
+  pend = desc_load(1);
   __syncwarp();
   {
 #pragma unroll
-    for (int sl = 0; sl < T4::kSlots; ++sl)
-      if (2 * sl < my_n) refill(sl, bt_s[2 * sl], bt_s[2 * sl + 1], 2 * sl + 1 < my_n);
+    for (int sl = 0; sl < T4::kSlots; ++sl) {
+      const int4 d = desc_s[sl];
+      if (d.z) refill(sl, d);
+    }
   }
 
   // ---- query: INT8 per 32-channel block.  Lane (head n = g, tig) owns channels
@@ -438,7 +486,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   //      The four warps need identical fragments: warp w quantises block c = w and the CTA
   //      exchanges the results through shared memory (a quarter of the arithmetic per warp). ----
   K4State st;
-  {
+  if (kDoK) {
     static_assert(kScanWarps == 4, "one warp per 32-channel query block");
     uint32_t* qx = reinterpret_cast<uint32_t*>(smem + kQxOff);  // [c][6][32]
     {
@@ -447,7 +495,8 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       const uint32_t rw[4] = {q_raw.x, q_raw.y, q_raw.z, q_raw.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        v[j] = Elem<DT>::to_f32(static_cast<uint16_t>((j & 1) ? (rw[j >> 1] >> 16) : (rw[j >> 1] & 0xFFFFu)));
+        const uint16_t bits = static_cast<uint16_t>((j & 1) ? (rw[j >> 1] >> 16) : (rw[j >> 1] & 0xFFFFu));
+        v[j] = p.q_dtype == JF_DTYPE_FP16 ? Elem<JF_DTYPE_FP16>::to_f32(bits) : Elem<JF_DTYPE_BF16>::to_f32(bits);
         amax = fmaxf(amax, fabsf(v[j]));
       }
       amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
@@ -499,64 +548,49 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     st.s_off = t0 * 2;
   }
   const int h0 = hkv * p.G + 2 * tig;
-  float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0 +
-               static_cast<int64_t>(pg_first) * 16;
+  float* sp0 = p.scores + (static_cast<int64_t>(b) * p.H_q + h0) * p.max_S + t0;
   float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
 
-  JF_PHASE(2);
-  JF_CTA_STAMP(cta_lin, 2);
-  // A round takes one slot: two pages (one at the end of the range).  Two full pages go through
-  // the interleaved pair path; a partial or invalid page is processed on its own.
+  // A round takes one slot: one tile.  Tiles of two whole pages go through the unmasked path.
   int sl = 0;
   uint32_t parity = 0u;
-  for (int it = 0; it < my_n; it += 2) {
-    const bool two = it + 1 < my_n;
-    // live tokens of the pages, from their parked entries (still resident: a chunk is
-    // overwritten 16 pages after its last entry was issued)
-    const int live_a = bt_s[it & (2 * kBtChunk - 1)].y, live_b = bt_s[(it + 1) & (2 * kBtChunk - 1)].y;
+  for (int it = 0; it < p.tiles_per_warp; ++it) {
+    // the tile's parked descriptor is still resident: a chunk is overwritten 16 tiles after its
+    // last entry was issued
+    const int4 d = desc_s[it & (2 * kBtChunk - 1)];
+    if (d.z == 0) break;
     if (!mbar_wait(&bars[sl], parity)) {
-      if (it + 2 < my_n) mbar_wait(&bars[sl ^ 1], parity ^ static_cast<uint32_t>(sl), 1000000ull);
+      if (desc_s[(it + 1) & (2 * kBtChunk - 1)].z) mbar_wait(&bars[sl ^ 1], parity ^ static_cast<uint32_t>(sl), 1000000ull);
       failed = true;
       break;
     }
-    if (it == 0) JF_PHASE(3);
     const uint32_t sb = slots0 + sl * T4::kSlotBytes, ss = sb + T4::kScaleOff;
-    if (two && live_a == 16 && live_b == 16) {
-      k4v4_page_pair(st, sb, sb + T4::kPageBytes, ss, ss + 32, attn, sp0, sp1, sp0 + 16, sp1 + 16, st0, st1);
-    } else {
-      if (live_a != 16) k4v4_page<true>(st, sb, ss, t0, live_a, attn, sp0, sp1, st0, st1);
-      else k4v4_page<false>(st, sb, ss, t0, 16, attn, sp0, sp1, st0, st1);
-      if (two) {
-        if (live_b != 16) k4v4_page<true>(st, sb + T4::kPageBytes, ss + 32, t0, live_b, attn, sp0 + 16, sp1 + 16, st0, st1);
-        else k4v4_page<false>(st, sb + T4::kPageBytes, ss + 32, t0, 16, attn, sp0 + 16, sp1 + 16, st0, st1);
-      }
-    }
+    float* spA0 = sp0 + static_cast<int64_t>(d.w) * 16;
+    float* spA1 = sp1 + static_cast<int64_t>(d.w) * 16;
+    if (d.z == kFullTile)
+      k4v4_tile<kInt8P, false, kParts>(st, sb, sb + T4::kPageBytes, ss, ss + 32, d.z, t0, attn, spA0, spA1, st0, st1);
+    else
+      k4v4_tile<kInt8P, true, kParts>(st, sb, sb + T4::kPageBytes, ss, ss + 32, d.z, t0, attn, spA0, spA1, st0, st1);
     __syncwarp();
-    // the refill below reads entries up to it + kPagesInFlight + 1: bring their chunk in first
-    if (((it + kPagesInFlight + 1) >> 4) > bt_stored) {
-      ++bt_stored;
-      if (lane < kBtChunk) bt_s[(bt_stored & 1) * kBtChunk + lane] = bt_entry(bt_pend, bt_stored * kBtChunk + lane);
-      bt_pend = bt_load(bt_stored + 1);
+    // the refill below reads the descriptor of tile it + kSlots: bring its chunk in first
+    if (((it + T4::kSlots) >> 4) > stored) {
+      ++stored;
+      if (lane < kBtChunk) desc_s[(stored & 1) * kBtChunk + lane] = desc_make(pend);
+      pend = desc_load(stored + 1);
       __syncwarp();
     }
-    const int e0 = it + kPagesInFlight;   // first page to fetch into the slot just freed
-    if (e0 < my_n) refill(sl, bt_s[e0 & (2 * kBtChunk - 1)], bt_s[(e0 + 1) & (2 * kBtChunk - 1)], e0 + 1 < my_n);
-    sp0 += 32;
-    sp1 += 32;
+    const int4 dn = desc_s[(it + T4::kSlots) & (2 * kBtChunk - 1)];
+    if (it + T4::kSlots < p.tiles_per_warp && dn.z) refill(sl, dn);
     sl ^= 1;
     if (sl == 0) parity ^= 1u;
   }
 
-  JF_PHASE(4);
-  JF_CTA_STAMP(cta_lin, 3);
-  JF_PHASE_VAL(10, my_n);
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
 
   __syncthreads();
-  JF_PHASE(5);
   {
     float* wo = reinterpret_cast<float*>(smem) + warp * (kHeadsPad * JF_HEAD_DIM);
 #pragma unroll
@@ -572,8 +606,6 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     }
   }
   cta_merge_store(p, smem, st.l0, st.l1, st.m_ref0, st.m_ref1, 0.f, 0.f, split, hkv, b);
-  JF_PHASE(6);
-  JF_CTA_STAMP(cta_lin, 4);
 }
 
 // ---- tensor maps -----------------------------------------------------------------------
@@ -634,36 +666,56 @@ jf_status_t page_map(const void* base, uint64_t rows, uint32_t box_rows, CUtenso
 
 }  // namespace
 
-#ifdef JF_PHASE_TIMING
-extern "C" int jf_debug_scan_times(unsigned long long* out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_phase_t, sizeof(g_phase_t)));
-}
-extern "C" int jf_debug_scan_cta_times(unsigned long long* out) {   // [1024][8] globaltimer stamps
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_cta_t, sizeof(g_cta_t)));
-}
-#endif
-
-jf_status_t launch_scan_k4v4(const ScanParams& sp, int q_dtype, dim3 grid, cudaStream_t stream) {
-  const uint64_t rows = static_cast<uint64_t>(sp.H_kv) * static_cast<uint64_t>(sp.num_slots);
-  if (rows > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
-  CUtensorMap k_map, v_map, k_map2, v_map2;
-  jf_status_t st = page_map(sp.k_data, rows, 16, &k_map);
-  if (st == JF_OK) st = page_map(sp.v_data, rows, 16, &v_map);
-  if (st == JF_OK) st = page_map(sp.k_data, rows, 32, &k_map2);
-  if (st == JF_OK) st = page_map(sp.v_data, rows, 32, &v_map2);
-  if (st != JF_OK) return st;
+template <bool kInt8P, int kParts>
+jf_status_t launch_variant(const ScanParams& sp, dim3 grid, cudaStream_t stream, const CUtensorMap& k_map,
+                           const CUtensorMap& v_map, const CUtensorMap& k_map2, const CUtensorMap& v_map2) {
   const size_t smem = kSmemBytes;
-  if (q_dtype == JF_DTYPE_BF16) {
-    JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_BF16>, smem);
-    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_BF16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map,
-                           k_map2, v_map2));
-  } else {
-    JF_ENSURE_SMEM(scan_k4v4_kernel<JF_DTYPE_FP16>, smem);
-    JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<JF_DTYPE_FP16>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map,
-                           k_map2, v_map2));
-  }
+  JF_ENSURE_SMEM((scan_k4v4_kernel<kInt8P, kParts>), smem);
+  JF_CUDA_TRY(launch_pdl(scan_k4v4_kernel<kInt8P, kParts>, grid, dim3(kScanWarps * 32), smem, stream, sp, k_map, v_map,
+                         k_map2, v_map2));
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
+}
+
+// `sp` arrives with everything but the tile geometry filled in.
+jf_status_t launch_scan_k4v4(ScanParams sp, bool int8p, int parts, dim3 grid, cudaStream_t stream) {
+  const uint64_t rows = static_cast<uint64_t>(sp.H_kv) * static_cast<uint64_t>(sp.num_slots);
+  if (rows > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
+  // tiles of the longest row this call can see (the kernel drops those past a row's own length)
+  if (int8p && parts != 1) {
+    sp.ref_chunk = (sp.max_S + 7) / 8;
+    int n = 0;
+    for (int s = 0; s < 8; ++s) {
+      sp.tile_base[s] = n;
+      const int lo = s * sp.ref_chunk, hi = std::min(lo + sp.ref_chunk, sp.max_S);
+      if (lo < hi) n += ((hi + 15) / 16 - lo / 16 + 1) / 2;
+    }
+    sp.tile_base[8] = n;
+    sp.n_tiles = n;
+  } else {
+    int8p = false;   // the tiling only matters where weights meet V
+    sp.ref_chunk = sp.max_S;
+    sp.n_tiles = ((sp.max_S + 15) / 16 + 1) / 2;
+    for (int s = 0; s <= 8; ++s) sp.tile_base[s] = s ? sp.n_tiles : 0;
+  }
+  sp.tiles_per_split = (sp.n_tiles + sp.splits - 1) / sp.splits;
+  sp.tiles_per_warp = (sp.tiles_per_split + kScanWarps - 1) / kScanWarps;
+  // a tensor map of a tensor the call does not read is never used by the kernel; the other one stands in
+  const void* k_base = sp.k_data ? static_cast<const void*>(sp.k_data) : static_cast<const void*>(sp.v_data);
+  const void* v_base = sp.v_data ? static_cast<const void*>(sp.v_data) : static_cast<const void*>(sp.k_data);
+  CUtensorMap k_map, v_map, k_map2, v_map2;
+  jf_status_t st = page_map(k_base, rows, 16, &k_map);
+  if (st == JF_OK) st = page_map(v_base, rows, 16, &v_map);
+  if (st == JF_OK) st = page_map(k_base, rows, 32, &k_map2);
+  if (st == JF_OK) st = page_map(v_base, rows, 32, &v_map2);
+  if (st != JF_OK) return st;
+  if (parts == 1) return launch_variant<false, 1>(sp, grid, stream, k_map, v_map, k_map2, v_map2);
+  if (parts == 2) {
+    return int8p ? launch_variant<true, 2>(sp, grid, stream, k_map, v_map, k_map2, v_map2)
+                 : launch_variant<false, 2>(sp, grid, stream, k_map, v_map, k_map2, v_map2);
+  }
+  return int8p ? launch_variant<true, 0>(sp, grid, stream, k_map, v_map, k_map2, v_map2)
+               : launch_variant<false, 0>(sp, grid, stream, k_map, v_map, k_map2, v_map2);
 }
 
 }  // namespace jf

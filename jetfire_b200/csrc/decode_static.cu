@@ -52,6 +52,12 @@ jf_status_t static_scratch(void** out) {
 
 }  // namespace
 
+// For jf_decode_status: the status record of calls made through this entry point sits at the
+// start of the built-in array (the kernels find it where a caller's workspace would hold it).
+namespace jf {
+jf_status_t static_scratch_address(void** out) { return static_scratch(out); }
+}
+
 extern "C" jf_status_t jf_decode_fused_static(const jf_decode_args* a, jf_stream_t stream) {
   if (!a) return JF_ERR_ARG;
   if (a->mode != JF_MODE_K3V2) return JF_ERR_UNSUPPORTED;  // see the header: K3V2 only

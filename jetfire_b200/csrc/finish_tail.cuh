@@ -101,7 +101,6 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
   const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
 
-  JF_PHASE(20);
   // ---- merge splits (unnormalised): thread (group, d) sums splits group, group + 8, ... ----
   {
     const int d = tid & (JF_HEAD_DIM - 1), grp = tid >> 7;
@@ -124,7 +123,6 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
     if (d == 0) sm.z[grp] = Z;
   }
 
-  JF_PHASE(21);
   // ---- selected set: weights from the scan's scores ----
   const ModeInfo mi = mode_info(MODE);
   const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
@@ -172,7 +170,6 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       sm.wv[tid][0] = w * vs0; sm.wv[tid][1] = w * vs1;
     }
     __syncthreads();
-    JF_PHASE(22);
     // packed V rows, one 16-byte load per thread
     for (int u = tid; u < kend * (VW / 4); u += kSelThreads) {
       const int c = u / (VW / 4), part = u - c * (VW / 4);
@@ -186,7 +183,6 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       reinterpret_cast<uint4*>(sm.v)[u] = v;
     }
     __syncthreads();
-    JF_PHASE(23);
     // warp w takes entries w, w + 32, ...; lane l owns channels 4l..4l+3
     {
       uint32_t raw[kTailPerWarp];
@@ -224,7 +220,6 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
   for (int e = 0; e < 4; ++e) sm.red[warp][4 * lane + e] = acc[e];
   if (lane == 0) sm.sum[warp] = wsum;
   __syncthreads();
-  JF_PHASE(24);
   if (tid < JF_HEAD_DIM) {
     float acc_old = 0.f, ws = 0.f, o = 0.f, Z = 0.f;
 #pragma unroll
@@ -241,7 +236,6 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       if (p.softmax_inv_z) p.softmax_inv_z[bh] = inv_z;
     }
   }
-  JF_PHASE(25);
 }
 
 // Shared by both kernels: the merged reference point M = max over the splits, block-wide.

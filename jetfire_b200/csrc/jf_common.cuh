@@ -10,35 +10,6 @@
 
 #include "../../include/jetfire_b200.h"
 
-// Phase stamps for tuning: compiled out unless JF_PHASE_TIMING is defined; then the first
-// CTA of a kernel records clock64() at each JF_PHASE(i) (one table per source file) and the
-// jf_debug_*_times functions copy the stamps out.
-#ifdef JF_PHASE_TIMING
-static __device__ unsigned long long g_phase_t[64];
-#define JF_PHASE(i)                                                                          \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_phase_t[i] = clock64();    \
-  } while (0)
-#define JF_PHASE_VAL(i, v)                                                                   \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) g_phase_t[i] = (v);          \
-  } while (0)
-// per-CTA wall-clock stamps (globaltimer, ns): slot k of CTA `cta`
-static __device__ unsigned long long g_cta_t[1024 * 8];
-#define JF_CTA_STAMP(cta, k)                                                                 \
-  do {                                                                                       \
-    if (threadIdx.x == 0 && (cta) < 1024) {                                                  \
-      unsigned long long t__;                                                                \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
-      g_cta_t[(cta) * 8 + (k)] = t__;                                                        \
-    }                                                                                        \
-  } while (0)
-#else
-#define JF_PHASE(i) do { } while (0)
-#define JF_PHASE_VAL(i, v) do { } while (0)
-#define JF_CTA_STAMP(cta, k) do { } while (0)
-#endif
-
 namespace jf {
 
 // Per-thread record of the last failing CUDA call (read through jf_last_cuda_error).
@@ -88,7 +59,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-constexpr int kNumSMs = 148;  // B200
+// Multiprocessors of the current device (asked once per device; 148 on a B200, which is also the
+// answer when no device can be asked, so that size queries work on a machine without a GPU).
+int num_sms();
 
 // ---- dtype loads ---------------------------------------------------------------
 template <int DT> struct Elem;

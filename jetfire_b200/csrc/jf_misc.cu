@@ -3,7 +3,21 @@
 
 namespace jf {
 thread_local int32_t g_last_cuda_error = 0;
+
+int num_sms() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
 }
+}  // namespace jf
 
 extern "C" const char* jf_status_string(jf_status_t st) {
   switch (st) {

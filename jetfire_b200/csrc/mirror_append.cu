@@ -98,8 +98,102 @@ void CUDART_CB scatter_callback(void* ud) {
   c->chunks.fetch_add(1, std::memory_order_release);
 }
 
+// The reference's own form of the staged append (create_shadow_append_submit_ctx /
+// stream_submit_shadow_append, jetfire_vllm/csrc/cpu_topk_attn.cpp:1611-1665, 2186-2248): the
+// caller owns pinned staging tensors k_append / v_append (T, H_kv, 128) and slots (T,) that its
+// own stream-ordered copies fill; the callback scatters them into the mirror.
+constexpr uint64_t kShadowCtxTag = 0x4A46534841444F57ull;  // "JFSHADOW"
+struct ShadowAppendCtx {
+  uint64_t tag = kShadowCtxTag;
+  const uint16_t* k_append = nullptr;
+  const uint16_t* v_append = nullptr;
+  const int64_t* slots = nullptr;
+  uint16_t* k_shadow = nullptr;
+  uint16_t* v_shadow = nullptr;
+  int64_t T = 0, num_slots = 0;
+  int32_t H_kv = 0;
+  std::atomic<int64_t> calls{0};
+};
+
+void CUDART_CB shadow_append_callback(void* ud) {
+  auto* c = static_cast<ShadowAppendCtx*>(ud);
+  const int64_t head_stride = c->num_slots * JF_HEAD_DIM;
+  for (int64_t t = 0; t < c->T; ++t) {
+    const int64_t slot = c->slots[t];
+    if (slot < 0 || slot >= c->num_slots) continue;
+    for (int h = 0; h < c->H_kv; ++h) {
+      std::memcpy(c->k_shadow + h * head_stride + slot * JF_HEAD_DIM, c->k_append + (t * c->H_kv + h) * JF_HEAD_DIM, JF_HEAD_DIM * 2);
+      std::memcpy(c->v_shadow + h * head_stride + slot * JF_HEAD_DIM, c->v_append + (t * c->H_kv + h) * JF_HEAD_DIM, JF_HEAD_DIM * 2);
+    }
+  }
+  c->calls.fetch_add(1, std::memory_order_release);
+}
+
 }  // namespace
 }  // namespace jf
+
+extern "C" jf_status_t jf_shadow_append_ctx_create(const void* k_append, const void* v_append, const int64_t* slots,
+                                                   int64_t T, int32_t H_kv, void* k_shadow, void* v_shadow,
+                                                   int64_t num_slots, int64_t* handle) {
+  using namespace jf;
+  if (!k_append || !v_append || !slots || !k_shadow || !v_shadow || !handle || T < 0 || H_kv <= 0 || num_slots <= 0)
+    return JF_ERR_ARG;
+  auto* c = new (std::nothrow) ShadowAppendCtx();
+  if (!c) return JF_ERR_STATE;
+  c->k_append = static_cast<const uint16_t*>(k_append);
+  c->v_append = static_cast<const uint16_t*>(v_append);
+  c->slots = slots;
+  c->k_shadow = static_cast<uint16_t*>(k_shadow);
+  c->v_shadow = static_cast<uint16_t*>(v_shadow);
+  c->T = T; c->H_kv = H_kv; c->num_slots = num_slots;
+  *handle = static_cast<int64_t>(reinterpret_cast<intptr_t>(c));
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_shadow_append_ctx_destroy(int64_t handle) {
+  auto* c = reinterpret_cast<jf::ShadowAppendCtx*>(static_cast<intptr_t>(handle));
+  if (!c || c->tag != jf::kShadowCtxTag) return JF_ERR_ARG;
+  c->tag = 0;
+  delete c;
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_shadow_append_ctx_calls(int64_t handle, int64_t* calls) {
+  auto* c = reinterpret_cast<jf::ShadowAppendCtx*>(static_cast<intptr_t>(handle));
+  if (!c || c->tag != jf::kShadowCtxTag || !calls) return JF_ERR_ARG;
+  *calls = c->calls.load(std::memory_order_acquire);
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_stream_submit_shadow_append(jf_stream_t stream, int64_t handle) {
+  using namespace jf;
+  auto* c = reinterpret_cast<ShadowAppendCtx*>(static_cast<intptr_t>(handle));
+  if (!c || c->tag != kShadowCtxTag) return JF_ERR_ARG;
+  JF_CUDA_TRY(cudaLaunchHostFunc(static_cast<cudaStream_t>(stream), shadow_append_callback, c));
+  return JF_OK;
+}
+
+// A 64-bit store to device-visible memory in stream order (stream_write_value64,
+// jetfire_vllm/csrc/cpu_topk_attn.cpp:1293-1312): the reference clears its completion flag this
+// way before it queues a correction.  The driver call is looked up at run time.
+extern "C" jf_status_t jf_stream_write_value64(jf_stream_t stream, void* device_ptr, int64_t value) {
+  using namespace jf;
+  if (!device_ptr || (reinterpret_cast<uintptr_t>(device_ptr) & 7)) return JF_ERR_ARG;
+  using Fn = int (*)(void*, unsigned long long, unsigned long long, unsigned int);
+  static Fn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue64", &sym, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<Fn>(sym);
+  }();
+  if (!fn) return JF_ERR_UNSUPPORTED;
+  const int r = fn(stream, static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(device_ptr)),
+                   static_cast<unsigned long long>(value), 0u);
+  if (r != 0) { g_last_cuda_error = r; return JF_ERR_CUDA; }
+  return JF_OK;
+}
 
 extern "C" jf_status_t jf_mirror_append_ctx_create(void* k_shadow, void* v_shadow, int32_t H_kv, int64_t num_slots,
                                                    int64_t max_tokens, int64_t* handle) {

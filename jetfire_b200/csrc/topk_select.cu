@@ -226,7 +226,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   uint16_t* bucket = perm + p.sort_n;                                              // [sort_n] candidates grouped by bin
   int* hist = sm.hist;
 
-  JF_PHASE(0);
   const int h = blockIdx.x, b = blockIdx.y;
   const int hkv = h / p.G, hi = h - hkv * p.G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -283,7 +282,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   // ---- query row (exact values), per-group L1 norms, INT8 model for K4 ----
   if (tid < JF_HEAD_DIM) sm.q[tid] = Elem<DT>::to_f32(q_bits);
   __syncthreads();
-  JF_PHASE(11);
   if (warp < 4) {  // warp w handles channels 32w..32w+31
     const float v = sm.q[32 * warp + lane];
     float a = fabsf(v), s1 = fabsf(v) + 0.001953125f;
@@ -331,7 +329,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     if (lane == 0) { sm.w3[warp][0] = top; sm.w3[warp][1] = sm0; sm.w3[warp][2] = sm1; }
   }
   __syncthreads();
-  JF_PHASE(1);
 
   RowCtx ctx;
   ctx.q = sm.q; ctx.qi = sm.qi; ctx.qs = sm.qs;
@@ -350,7 +347,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   bool copied = wait_chunk(0, n_seq);
   if (!copied && tid == 0) report_status(p.status, JF_ERR_TIMEOUT);
   const int n = copied ? n_seq : 0;   // a row whose scores did not arrive selects nothing
-  JF_PHASE(2);
 
   int m_sel = 0;  // entries of keys[] that hold the ranked result
   bool prefetch = false;
@@ -452,7 +448,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
                                 (static_cast<uint32_t>(v.z > thr) << 2) | (static_cast<uint32_t>(v.w > thr) << 3);
             mask |= m4 << (4 * j);
           }
-          JF_PHASE(30);
           const int cnt = __popc(mask);
           int incl = cnt;
 #pragma unroll
@@ -474,7 +469,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           const int base = running + __shfl_sync(0xFFFFFFFFu, winc - wt, warp);
           running += __shfl_sync(0xFFFFFFFFu, winc, 31);
           int o = base + incl - cnt;
-          JF_PHASE(31);
           while (mask) {
             const int e = __ffs(mask) - 1;
             mask &= mask - 1u;
@@ -483,9 +477,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             ++o;
           }
         }
-        JF_PHASE(32);
         __syncthreads();
-        JF_PHASE(33);
         return running;
       };
 
@@ -507,9 +499,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       }
       have_hm = n_chunks == 1;  // hm[] describes the chunk that stays resident
       __syncthreads();
-      JF_PHASE(3);
       scan_hist();
-      JF_PHASE(4);
       bool ok = false;
       {
         const int tbin = sm.tbin;
@@ -518,7 +508,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           const int total = collect(last);
           ok = total <= p.sort_n;
           ncand = total;
-          JF_PHASE_VAL(40, total);
           cand_last = last + nb;
         }
       }
@@ -559,7 +548,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       }
     }
     __syncthreads();   // every read of the score chunk is done: its memory is reused from here on
-    JF_PHASE(5);
 
     // the fused finish stage takes slots, scores and V rows of the candidates from shared memory
     prefetch = FUSED && !slow && ncand <= kRowChunk && p.sort_n <= kSelThreads;
@@ -570,7 +558,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         const int cn = min(kRowChunk, ncand - base);
         if (tid < cn) late.cand_slot[tid] = slot_of(ctx, static_cast<int>(keys[base + tid]));
         __syncthreads();
-        JF_PHASE(6);
         {
           // unit u = (candidate, part), eight per candidate, each at most one 16-byte access.
           // K3: parts 0-2 the K row, 3 the K scales, 4-5 the V row, 6 the V scales.  K4: parts
@@ -627,7 +614,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           }
         }
         __syncthreads();
-        JF_PHASE(7);
         if (MODE == JF_MODE_K4V4) {
           // K4: the scan's score is the canonical one bit for bit (exact integer dot products,
           // the same fp32 rescale order), so nothing is recomputed
@@ -689,7 +675,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       ncand = min(sm.ncand, p.sort_n);
     }
     __syncthreads();
-    JF_PHASE(8);
 
     // ---- order the candidates: best first ----
     if (p.sort_n <= kSelThreads) {
@@ -771,7 +756,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       }
     }
     m_sel = min(ncand, K);
-    JF_PHASE(9);
   }
 
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
@@ -784,7 +768,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     out_idx[r] = idx;
     out_slot[r] = slot;
   }
-  JF_PHASE(10);
 
   if (FUSED) {
     cp_async_wait_all();
@@ -868,12 +851,6 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
 }
 
 }  // namespace jf
-
-#ifdef JF_PHASE_TIMING
-extern "C" int jf_debug_phase_times(unsigned long long* out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_phase_t, sizeof(g_phase_t)));
-}
-#endif
 
 extern "C" jf_status_t jf_topk_select(const jf_decode_args* a, jf_stream_t stream) {
   return jf::launch_select(a, static_cast<cudaStream_t>(stream), false);

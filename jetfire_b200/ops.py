@@ -237,6 +237,8 @@ class FusedAttnOut(NamedTuple):
 
 
 _WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_PARTS = {"all": _lib.JF_SCAN_ALL, "k": _lib.JF_SCAN_K_ONLY, "v": _lib.JF_SCAN_V_ONLY}
+_STAGE_B = {"fp32": _lib.JF_STAGE_B_FP32, "int8p": _lib.JF_STAGE_B_INT8P}
 
 
 def decode_workspace_bytes(mode, B, H_q, H_kv, max_S, top_k) -> int:
@@ -259,38 +261,56 @@ def get_workspace(nbytes: int, device) -> torch.Tensor:
 
 class DecodeCall:
     """Argument block for the decode entry points, built once and reusable (pointers are
-    captured; tensors are kept alive here)."""
+    captured; tensors are kept alive here).
+
+    ``stage_b``: ``"fp32"`` (full-precision softmax weights) or ``"int8p"`` (K4V4 only: the
+    reference's batch > 1 arithmetic, weights rounded to 127 levels per 32-token tile).
+    ``parts``: ``"all"``, ``"k"`` (scores and softmax sums only: q and the K cache; V tensors may be
+    None) or ``"v"`` (output partials from ``scores``, an input then: the V cache; q and K tensors
+    may be None).  ``scores`` / ``topk_idx``: existing tensors to use instead of fresh ones."""
 
     def __init__(self, mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
                  max_S, H_q, H_kv, block_size, top_k, attn_scale, *, workspace=None,
-                 want_scores=False, out=None):
+                 want_scores=False, out=None, stage_b="fp32", parts="all", scores=None, topk_idx=None):
         name = "fused_attn_topk"
         mode_id = MODE_IDS[mode] if isinstance(mode, str) else int(mode)
         k_bits, v_bits, gs = MODE_BITS[mode_id]
-        for t, nm in ((q, "q"), (k_data, "k_data"), (k_scales, "k_scales"), (v_data, "v_data"),
-                      (v_scales, "v_scales"), (block_table, "block_table"), (seq_lens, "seq_lens")):
-            _require(t.is_cuda, f"{name}: {nm} must be CUDA")
-        _require(q.dim() == 3 and q.shape[1] == H_q and q.shape[2] == 128, f"{name}: q must be (B, H_q, 128)")
-        q = q.contiguous()
-        B = q.shape[0]
-        _require(k_data.dtype == torch.uint8 and v_data.dtype == torch.uint8, f"{name}: packed data must be uint8")
-        _require(k_scales.dtype == torch.bfloat16 and v_scales.dtype == torch.bfloat16, f"{name}: scales must be bf16")
-        _require(k_data.is_contiguous() and v_data.is_contiguous() and k_scales.is_contiguous()
-                 and v_scales.is_contiguous(), f"{name}: cache tensors must be contiguous")
-        _require(k_data.shape[0] == H_kv and k_data.shape[2] == _packed_dim(k_bits),
-                 f"{name}: k_data must be (H_kv, num_slots, {_packed_dim(k_bits)})")
-        _require(v_data.shape[0] == H_kv and v_data.shape[2] == _packed_dim(v_bits),
-                 f"{name}: v_data must be (H_kv, num_slots, {_packed_dim(v_bits)})")
-        num_slots = k_data.shape[1]
+        _require(parts in _PARTS and stage_b in _STAGE_B, f"{name}: bad parts / stage_b")
+        need_k, need_v = parts != "v", parts != "k"
         ng = 128 // gs
-        _require(k_scales.numel() == H_kv * num_slots * ng and v_scales.numel() == H_kv * num_slots * ng,
-                 f"{name}: scales must hold {ng} group(s) per slot")
+        dev = block_table.device
+        _require(block_table.is_cuda and seq_lens.is_cuda, f"{name}: block_table / seq_lens must be CUDA")
+        B = int(seq_lens.shape[0])
+        num_slots = None
+        if need_k:
+            for t, nm in ((q, "q"), (k_data, "k_data"), (k_scales, "k_scales")):
+                _require(t is not None and t.is_cuda, f"{name}: {nm} must be CUDA")
+            _require(q.dim() == 3 and q.shape[0] == B and q.shape[1] == H_q and q.shape[2] == 128,
+                     f"{name}: q must be (B, H_q, 128)")
+            q = q.contiguous()
+            _require(k_data.dtype == torch.uint8 and k_scales.dtype == torch.bfloat16,
+                     f"{name}: packed data must be uint8, scales bf16")
+            _require(k_data.is_contiguous() and k_scales.is_contiguous(), f"{name}: cache tensors must be contiguous")
+            _require(k_data.dim() == 3 and k_data.shape[0] == H_kv and k_data.shape[2] == _packed_dim(k_bits),
+                     f"{name}: k_data must be (H_kv, num_slots, {_packed_dim(k_bits)})")
+            num_slots = k_data.shape[1]
+            _require(k_scales.numel() == H_kv * num_slots * ng, f"{name}: scales must hold {ng} group(s) per slot")
+        if need_v:
+            for t, nm in ((v_data, "v_data"), (v_scales, "v_scales")):
+                _require(t is not None and t.is_cuda, f"{name}: {nm} must be CUDA")
+            _require(v_data.dtype == torch.uint8 and v_scales.dtype == torch.bfloat16,
+                     f"{name}: packed data must be uint8, scales bf16")
+            _require(v_data.is_contiguous() and v_scales.is_contiguous(), f"{name}: cache tensors must be contiguous")
+            _require(v_data.dim() == 3 and v_data.shape[0] == H_kv and v_data.shape[2] == _packed_dim(v_bits),
+                     f"{name}: v_data must be (H_kv, num_slots, {_packed_dim(v_bits)})")
+            _require(num_slots is None or num_slots == v_data.shape[1], f"{name}: K and V caches differ in num_slots")
+            num_slots = v_data.shape[1]
+            _require(v_scales.numel() == H_kv * num_slots * ng, f"{name}: scales must hold {ng} group(s) per slot")
         _require(block_table.dtype == torch.int64 and block_table.dim() == 2 and block_table.shape[0] == B,
                  f"{name}: block_table must be (B, max_blocks) int64")
         _require(seq_lens.dtype == torch.int32 and seq_lens.shape == (B,), f"{name}: seq_lens must be (B,) int32")
         block_table = block_table.contiguous()
         seq_lens = seq_lens.contiguous()
-        dev = q.device
         nbytes = decode_workspace_bytes(mode_id, B, H_q, H_kv, max_S, top_k)
         _require(nbytes > 0, f"{name}: bad shape")
         if workspace is None:
@@ -303,24 +323,34 @@ class DecodeCall:
                 o_hat=torch.empty(B, H_q, 128, **f32), o_old_unnorm=torch.empty(B, H_q, 128, **f32),
                 W=torch.empty(B, H_q, **f32), softmax_m=torch.empty(B, H_q, **f32),
                 softmax_inv_z=torch.empty(B, H_q, **f32),
-                topk_idx=torch.empty(B, H_q, top_k, dtype=torch.int64, device=dev),
                 topk_slots=torch.empty(B, H_q, top_k, dtype=torch.int64, device=dev),
             )
-        scores = torch.empty(B, H_q, max_S, **f32) if want_scores else None
+            out["topk_idx"] = topk_idx if topk_idx is not None else \
+                torch.empty(B, H_q, top_k, dtype=torch.int64, device=dev)
+        if scores is not None:
+            _require(scores.is_cuda and scores.dtype == torch.float32 and scores.is_contiguous()
+                     and tuple(scores.shape) == (B, H_q, max_S), f"{name}: scores must be contiguous f32 (B, H_q, max_S)")
+        elif want_scores:
+            scores = torch.empty(B, H_q, max_S, **f32)
+        _require(need_k or scores is not None, f"{name}: parts='v' needs the scores")
+        _require(out["topk_idx"].is_cuda and out["topk_idx"].dtype == torch.int64 and out["topk_idx"].is_contiguous()
+                 and tuple(out["topk_idx"].shape) == (B, H_q, top_k), f"{name}: topk_idx must be contiguous int64 (B, H_q, k)")
         self.out = out
         self.scores = scores
         self._keep = (q, k_data, k_scales, v_data, v_scales, block_table, seq_lens, workspace)
+        ptr = lambda t: t.data_ptr() if t is not None else None
         a = DecodeArgs()
-        a.mode, a.q_dtype = mode_id, _dtype_id(q)
+        a.mode, a.q_dtype = mode_id, (_dtype_id(q) if need_k else _lib.JF_DTYPE_BF16)
         a.B, a.H_q, a.H_kv = B, H_q, H_kv
         a.max_S, a.block_size, a.top_k = int(max_S), int(block_size), int(top_k)
         a.max_blocks = block_table.shape[1]
+        a.scan_parts, a.stage_b = _PARTS[parts], _STAGE_B[stage_b]
         a.attn_scale = float(attn_scale)
         a.num_slots = num_slots
-        a.q, a.k_data, a.k_scales = q.data_ptr(), k_data.data_ptr(), k_scales.data_ptr()
-        a.v_data, a.v_scales = v_data.data_ptr(), v_scales.data_ptr()
+        a.q, a.k_data, a.k_scales = (ptr(q), ptr(k_data), ptr(k_scales)) if need_k else (None, None, None)
+        a.v_data, a.v_scales = (ptr(v_data), ptr(v_scales)) if need_v else (None, None)
         a.block_table, a.seq_lens = block_table.data_ptr(), seq_lens.data_ptr()
-        a.scores = scores.data_ptr() if scores is not None else None
+        a.scores = ptr(scores)
         a.topk_idx, a.topk_slots = out["topk_idx"].data_ptr(), out["topk_slots"].data_ptr()
         a.o_hat, a.o_old_unnorm, a.W = out["o_hat"].data_ptr(), out["o_old_unnorm"].data_ptr(), out["W"].data_ptr()
         a.softmax_m, a.softmax_inv_z = out["softmax_m"].data_ptr(), out["softmax_inv_z"].data_ptr()
@@ -340,6 +370,13 @@ class DecodeCall:
     def fused(self):
         check("jf_decode_fused", lib.jf_decode_fused(self._ref, _stream()))
 
+    def exact_stats(self):
+        """Exact row maximum and 1 / sum exp(s - max) of the stored scores into ``softmax_m`` /
+        ``softmax_inv_z`` (what the reference's ``*_topk_stats`` ops return)."""
+        a = self.args
+        check("jf_softmax_stats", lib.jf_softmax_stats(a.scores, a.seq_lens, a.softmax_m, a.softmax_inv_z,
+                                                       a.B, a.H_q, a.max_S, _stream()))
+
     def status(self):
         """Synchronises the stream and raises if a kernel recorded a bounded-wait timeout."""
         check("jf_decode_status", lib.jf_decode_status(self._ref, _stream()))
@@ -352,13 +389,13 @@ class DecodeCall:
 
 def fused_attn_topk(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
                     max_S, H_q, H_kv, block_size, top_k, attn_scale, *, workspace=None,
-                    want_scores=False) -> FusedAttnOut:
+                    want_scores=False, stage_b="fp32") -> FusedAttnOut:
     """One call: approximate attention over the packed cache, exact top-k, and the
     selected set's approximate contribution.  Returns ``(o_hat, topk_slots, o_old_unnorm,
     W, ...)`` -- the first four as the reference's ``int2_fused_attn_topk``."""
     call = DecodeCall(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
                       max_S, H_q, H_kv, block_size, top_k, attn_scale, workspace=workspace,
-                      want_scores=want_scores)
+                      want_scores=want_scores, stage_b=stage_b)
     call.fused()
     return call.result()
 
@@ -376,6 +413,97 @@ def int2_fused_attn_topk(q, k_data, k_scales, k_zp, v_data, v_scales, block_tabl
     r = fused_attn_topk(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
                         max_S, H_q, H_kv, block_size, top_k, attn_scale)
     return r.o_hat, r.topk_slots, r.o_old_unnorm, r.W
+
+
+# -- the reference's Stage A / Stage B ops under their own names, argument order and return lists,
+#    so that its decode path (jetfire_vllm/adapter/decode_path.py:2081-2131, 2785-2935) can call this
+#    library unchanged.  Stage A = the scan's K half + the exact select; Stage B = the scan's V half
+#    over the given scores + the finish stage.  Both halves give the bits of the one-pass scan. --
+
+def _stage_a(mode, name, q, k_data, k_scales, block_table, seq_lens, max_S, H_q, H_kv, block_size,
+             attn_scale, top_k, stats):
+    _require(int(block_size) == 16, f"{name}: block_size must be 16")
+    call = DecodeCall(mode, q, k_data, k_scales, None, None, block_table, seq_lens, int(max_S), int(H_q), int(H_kv),
+                      int(block_size), int(top_k), float(attn_scale), want_scores=True, parts="k")
+    call.scan()
+    call.select()
+    out = [call.scores, call.out["topk_idx"], call.out["topk_slots"]]
+    if stats:
+        call.exact_stats()
+        out += [call.out["softmax_m"], call.out["softmax_inv_z"]]
+    return out
+
+
+def int3_qk_scores_topk(q, k_data, k_scales, block_table, seq_lens, max_S, H_q, H_kv, block_size, attn_scale, top_k):
+    """``[scores f32 (B,H_q,max_S), topk_idx i64 (B,H_q,k), topk_slots i64 (B,H_q,k)]``
+    (jetfire_vllm/csrc/int3_qk_scores.cu:562-633).  Unlike the reference, the lists are ordered
+    (score descending, position ascending) and ties go to the lower position."""
+    return _stage_a("k3v2", "int3_qk_scores_topk", q, k_data, k_scales, block_table, seq_lens, max_S, H_q, H_kv,
+                    block_size, attn_scale, top_k, False)
+
+
+def int8tc_qk_scores_topk_stats(q, k_data, k_scales, block_table, seq_lens, max_S, H_q, H_kv, block_size,
+                                attn_scale, top_k):
+    """``[scores, topk_idx, topk_slots, softmax_m f32 (B,H_q), softmax_inv_z f32 (B,H_q)]``
+    (jetfire_vllm/csrc/int8tc_qk_scores.cu:2426-2482)."""
+    return _stage_a("k4v4", "int8tc_qk_scores_topk_stats", q, k_data, k_scales, block_table, seq_lens, max_S, H_q,
+                    H_kv, block_size, attn_scale, top_k, True)
+
+
+def _stage_b(mode, name, stage_b, scores, v_data, v_scales, block_table, seq_lens, topk_idx, max_S, H_q, H_kv,
+             block_size, top_k, out=None):
+    _require(int(block_size) == 16, f"{name}: block_size must be 16")
+    _require(scores.is_cuda and scores.dtype == torch.float32 and scores.dim() == 3, f"{name}: scores must be f32 (B,H_q,max_S)")
+    _require(topk_idx.is_cuda and topk_idx.dtype == torch.int64 and topk_idx.dim() == 3
+             and topk_idx.shape[2] == int(top_k), f"{name}: topk_idx must be int64 (B,H_q,top_k)")
+    B = scores.shape[0]
+    if out is not None:
+        for t, shape in zip(out, ((B, int(H_q), 128), (B, int(H_q), 128), (B, int(H_q)))):
+            _require(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == shape,
+                     f"{name}: outputs must be contiguous f32 of shapes (B,H_q,128), (B,H_q,128), (B,H_q)")
+        f32 = dict(dtype=torch.float32, device=scores.device)
+        out = dict(o_hat=out[0], o_old_unnorm=out[1], W=out[2], softmax_m=torch.empty(B, int(H_q), **f32),
+                   softmax_inv_z=torch.empty(B, int(H_q), **f32), topk_idx=topk_idx.contiguous(),
+                   topk_slots=torch.empty_like(topk_idx))
+    call = DecodeCall(mode, None, None, None, v_data, v_scales, block_table, seq_lens, int(max_S), int(H_q), int(H_kv),
+                      int(block_size), int(top_k), 1.0, parts="v", stage_b=stage_b, scores=scores.contiguous(),
+                      topk_idx=topk_idx.contiguous(), out=out)
+    call.scan()
+    call.finish()
+    return [call.out["o_hat"], call.out["o_old_unnorm"], call.out["W"]]
+
+
+def int2_softmax_v_with_pre_corr_wvs2(scores, v_data, v_scales, block_table, seq_lens, topk_idx, max_S, H_q, H_kv,
+                                      block_size, top_k):
+    """``[o_hat f32 (B,H_q,128), o_old_unnorm f32 (B,H_q,128), W f32 (B,H_q)]``
+    (jetfire_vllm/csrc/int2_softmax_v.cu:792-901)."""
+    return _stage_b("k3v2", "int2_softmax_v_with_pre_corr_wvs2", "fp32", scores, v_data, v_scales, block_table,
+                    seq_lens, topk_idx, max_S, H_q, H_kv, block_size, top_k)
+
+
+def int2_softmax_v_with_pre_corr_wvs2_inplace(scores, v_data, v_scales, block_table, seq_lens, topk_idx, weights,
+                                              o_hat, o_old_unnorm, W_out, max_S, H_q, H_kv, block_size, top_k) -> None:
+    """Caller-owned outputs (jetfire_vllm/csrc/int2_softmax_v.cu:903-1025).  ``weights`` (the
+    reference's materialised softmax) is not needed and left untouched; the outputs are
+    overwritten, so they need not be zeroed."""
+    _stage_b("k3v2", "int2_softmax_v_with_pre_corr_wvs2_inplace", "fp32", scores, v_data, v_scales, block_table,
+             seq_lens, topk_idx, max_S, H_q, H_kv, block_size, top_k, out=(o_hat, o_old_unnorm, W_out))
+
+
+def int4_softmax_v_with_pre_corr_wvs2_scores(scores, v_data, v_scales, block_table, seq_lens, topk_idx, max_S, H_q,
+                                             H_kv, block_size, top_k):
+    """K4V4 Stage B with full-precision weights (jetfire_vllm/csrc/int4_softmax_v.cu:2203-2235)."""
+    return _stage_b("k4v4", "int4_softmax_v_with_pre_corr_wvs2_scores", "fp32", scores, v_data, v_scales, block_table,
+                    seq_lens, topk_idx, max_S, H_q, H_kv, block_size, top_k)
+
+
+def int8tc_softmax_v_with_pre_corr_reg_stats(scores, softmax_m, softmax_inv_z, v_data, v_scales, block_table, seq_lens,
+                                             topk_idx, max_S, H_q, H_kv, block_size, top_k):
+    """K4V4 Stage B of the batch > 1 plan, weights rounded per 32-token tile
+    (jetfire_vllm/csrc/int8tc_softmax_v_fused.cu:1591-1604).  ``softmax_m / softmax_inv_z`` are
+    accepted for the signature; the normaliser is recomputed from ``scores`` (the same value)."""
+    return _stage_b("k4v4", "int8tc_softmax_v_with_pre_corr_reg_stats", "int8p", scores, v_data, v_scales,
+                    block_table, seq_lens, topk_idx, max_S, H_q, H_kv, block_size, top_k)
 
 
 # ---------------------------------------------------------------------------------------
@@ -410,13 +538,13 @@ def wait_and_blend_unnorm_into(done_flag, o_hat, o_old_unnorm, W, o_new, out, ti
     (``csrc/blend.cu:320-376``; ``o_new`` is the device alias of mapped host memory, so no
     copy is needed).  Unlike the reference the wait is bounded: ``RuntimeError`` after
     ``timeout_s``."""
-    import time
     _require(done_flag.dtype == torch.int64 and done_flag.numel() == 1 and not done_flag.is_cuda,
              "wait_and_blend_unnorm_into: done_flag must be a 1-element int64 CPU tensor")
-    t_end = time.monotonic() + float(timeout_s)
-    while int(done_flag[0]) == 0:
-        if time.monotonic() > t_end:
-            raise RuntimeError("wait_and_blend_unnorm_into: the host correction did not finish in time")
+    # the wait runs in C with the interpreter lock released, so other Python threads keep going
+    st = lib.jf_wait_flag(done_flag.data_ptr(), int(float(timeout_s) * 1000.0))
+    if st == _lib.JF_ERR_TIMEOUT:
+        raise RuntimeError("wait_and_blend_unnorm_into: the host correction did not finish in time")
+    check("wait_and_blend_unnorm_into", st)
     blend_unnorm_into(o_hat, o_old_unnorm, W, o_new, out)
 
 
@@ -528,6 +656,89 @@ class HostCorrectionCall:
         if getattr(self, "_ctx", None) is not None:
             lib.jf_submit_ctx_destroy(self._ctx)
             self._ctx = None
+
+
+# -- the reference's stream-ordered host ops under their own names (bindings at
+#    jetfire_vllm/csrc/cpu_topk_attn.cpp:2509-2663).  Handles are plain integers; the contexts and
+#    the tensors they point into live until the process ends, as in the reference (:1433-1435). --
+
+_CTX_KEEP: list = []
+
+
+def create_cpu_topk_submit_ctx(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, flag_host) -> int:
+    """Context over pre-allocated decode buffers (all CPU; ``flag_host`` a 1-element int64 tensor,
+    set to 1 when a submitted job is done).  Returns the handle for ``stream_submit_cpu_topk_attn``."""
+    args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, flag_host, "create_cpu_topk_submit_ctx")
+    h = C.c_int64(0)
+    check("create_cpu_topk_submit_ctx", lib.jf_submit_ctx_create(*args, 0, C.byref(h)))
+    _CTX_KEEP.append((q, k_shadow, v_shadow, head_map, ts_buf, o_new, flag_host))
+    return h.value
+
+
+def stream_submit_cpu_topk_attn(stream_id: int, ctx_handle: int) -> None:
+    """Queue a host callback on the stream (a raw ``cudaStream_t`` as an integer) that hands the
+    context's job to the worker pool when the stream gets there.  Capturable in a CUDA graph."""
+    check("stream_submit_cpu_topk_attn", lib.jf_stream_submit_cpu_topk_attn(int(stream_id), int(ctx_handle)))
+
+
+def stream_wait_cpu_topk_attn(stream_id: int, ctx_handle: int) -> None:
+    """Queue a host callback that holds the stream until the context's job is done (bounded:
+    30 s, then the timeout is reported by the context's status)."""
+    check("stream_wait_cpu_topk_attn", lib.jf_stream_wait_cpu_topk_attn(int(stream_id), int(ctx_handle)))
+
+
+def stream_write_value64(stream_id: int, flag_device: torch.Tensor, value: int) -> None:
+    """Stream-ordered 64-bit store to the device half of an ``alloc_mapped_pinned_pair``."""
+    _require(flag_device.is_cuda and flag_device.dtype == torch.int64 and flag_device.numel() == 1,
+             "stream_write_value64: flag_device must be a 1-element int64 CUDA tensor")
+    check("stream_write_value64", lib.jf_stream_write_value64(int(stream_id), flag_device.data_ptr(), int(value)))
+
+
+def submit_cpu_topk_attn_async(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, flag) -> None:
+    """Returns at once; the last worker stores 1 to ``flag`` when ``o_new`` is complete."""
+    cpu_topk_attn_submit(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, flag)
+
+
+def wait_for_flag(flag: torch.Tensor, timeout_s: float = 30.0) -> None:
+    """Block (interpreter lock released) until ``flag`` reads non-zero; unlike the reference the
+    wait is bounded."""
+    _require(flag.dtype == torch.int64 and flag.numel() == 1 and not flag.is_cuda,
+             "wait_for_flag: flag must be a 1-element int64 CPU tensor")
+    check("wait_for_flag", lib.jf_wait_flag(flag.data_ptr(), int(float(timeout_s) * 1000.0)))
+
+
+def create_shadow_append_submit_ctx(k_append, v_append, slots, k_shadow, v_shadow) -> int:
+    """Context for appending decode tokens to the host mirror in stream order: ``k_append /
+    v_append (T, H_kv, 128)`` and ``slots (T,) int64`` are pinned CPU staging tensors that the
+    caller's stream-ordered copies fill; ``stream_submit_shadow_append`` scatters them."""
+    name = "create_shadow_append_submit_ctx"
+    for t, nm in ((k_append, "k_append"), (v_append, "v_append"), (slots, "slots"), (k_shadow, "k_shadow"),
+                  (v_shadow, "v_shadow")):
+        _require(not t.is_cuda and t.is_contiguous(), f"{name}: {nm} must be a contiguous CPU tensor")
+    _require(k_append.dim() == 3 and v_append.shape == k_append.shape and k_append.shape[2] == 128
+             and k_append.dtype in (torch.bfloat16, torch.float16) and v_append.dtype == k_append.dtype,
+             f"{name}: k_append / v_append must be (T, H_kv, 128) 16-bit and match")
+    _require(slots.dim() == 1 and slots.dtype == torch.int64 and slots.shape[0] == k_append.shape[0],
+             f"{name}: slots must be (T,) int64")
+    _require(k_shadow.dim() == 3 and v_shadow.shape == k_shadow.shape and k_shadow.shape[0] == k_append.shape[1]
+             and k_shadow.shape[2] == 128 and k_shadow.dtype == k_append.dtype and v_shadow.dtype == k_append.dtype,
+             f"{name}: mirrors must be (H_kv, num_slots, 128) of the staging dtype")
+    h = C.c_int64(0)
+    check(name, lib.jf_shadow_append_ctx_create(k_append.data_ptr(), v_append.data_ptr(), slots.data_ptr(),
+                                                k_append.shape[0], k_append.shape[1], k_shadow.data_ptr(),
+                                                v_shadow.data_ptr(), k_shadow.shape[1], C.byref(h)))
+    _CTX_KEEP.append((k_append, v_append, slots, k_shadow, v_shadow))
+    return h.value
+
+
+def stream_submit_shadow_append(stream_id: int, ctx_handle: int) -> None:
+    check("stream_submit_shadow_append", lib.jf_stream_submit_shadow_append(int(stream_id), int(ctx_handle)))
+
+
+def get_shadow_append_count(ctx_handle: int) -> int:
+    n = C.c_int64(0)
+    check("get_shadow_append_count", lib.jf_shadow_append_ctx_calls(int(ctx_handle), C.byref(n)))
+    return n.value
 
 
 def alloc_mapped_pinned_pair(shape, dtype):

@@ -10,6 +10,9 @@
   Built only where the checkout exists; outputs are git-ignored and travel with the tree.
 
     python -m oracle.build_oracle [reference_root]
+
+The reference checkout is found from the argument, else the ``JETFIRE_REFERENCE_ROOT``
+environment variable, else a directory named ``reference`` next to this repository.
 """
 from __future__ import annotations
 
@@ -51,8 +54,15 @@ def ref_module_path(isa: str) -> Path:
     return REF_OUT / f"jetfire_cpu_topk_attn_ref_{isa}.so"
 
 
-def build_ref(ref_root: str | Path = "/root/reference", force: bool = False) -> list[Path]:
-    src = Path(ref_root) / "jetfire_vllm" / "csrc" / "cpu_topk_attn.cpp"
+def reference_root(arg: str | Path | None = None) -> Path:
+    if arg:
+        return Path(arg)
+    env = os.environ.get("JETFIRE_REFERENCE_ROOT")
+    return Path(env) if env else HERE.parent.parent / "reference"
+
+
+def build_ref(ref_root: str | Path | None = None, force: bool = False) -> list[Path]:
+    src = reference_root(ref_root) / "jetfire_vllm" / "csrc" / "cpu_topk_attn.cpp"
     if not src.exists():
         return [ref_module_path(i) for i in ISA_FLAGS if ref_module_path(i).exists()]
     from torch.utils.cpp_extension import include_paths, library_paths
@@ -90,5 +100,5 @@ def build_all() -> None:
 if __name__ == "__main__":
     build_c(force=True)
     print(C_LIB)
-    for p in build_ref(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True):
+    for p in build_ref(sys.argv[1] if len(sys.argv) > 1 else None, force=True):
         print(p)

@@ -11,6 +11,7 @@
  *   K4/G128 scores   csrc/int8tc_qk_scores.cu:272-290, 445-487 (INT8 query)
  *   top-k            csrc/int3_qk_scores.cu:426-554, order (score desc, position asc)
  *   Stage B (fp32)   csrc/int2_softmax_v.cu:120-143, 681-705, 738-788
+ *   Stage B (INT8-P) csrc/int8tc_softmax_v_fused.cu:62, 1049-1053, 1203-1311 (K4V4, batch > 1 plan)
  * One (batch, query head) row per OpenMP task.
  */
 #include <math.h>
@@ -64,13 +65,14 @@ int jf_oracle_num_threads(void) {
  * scores may be NULL; if given it is (B,H_q,max_S) and filled up to each row's length.
  * Returns 0.
  */
-int jf_oracle_decode(int mode, const float* q, const uint8_t* k_data, const uint16_t* k_scales,
+static int jf_oracle_decode_impl(int mode, int stage_b, const float* q, const uint8_t* k_data, const uint16_t* k_scales,
                      const uint8_t* v_data, const uint16_t* v_scales, const int64_t* block_table,
                      const int32_t* seq_lens, int B, int H_q, int H_kv, int max_S, int max_blocks,
                      int64_t num_slots, float attn_scale, int top_k, int n_threads, float* scores,
                      int64_t* topk_idx, int64_t* topk_slots, float* o_hat, float* o_old, float* W,
                      float* soft_m, float* soft_inv_z) {
   const int G = H_q / H_kv;
+  if (stage_b && !mode) return -1; /* the INT8-P arithmetic exists for K4V4 only */
   const int k_row = mode ? 64 : 48, v_row = mode ? 64 : 32, ng = mode ? 1 : 2;
 #ifdef _OPENMP
   if (n_threads > 0) omp_set_num_threads(n_threads);
@@ -162,7 +164,47 @@ int jf_oracle_decode(int mode, const float* q, const uint8_t* k_data, const uint
     if (!isfinite(mx)) mx = 0.f;
     for (int p = 0; p < n; ++p) z += exp((double)(s[p] - mx));
     const double inv_z = z > 0 ? 1.0 / z : 0.0;
-    for (int pass = 0; pass < 2; ++pass) {
+    if (stage_b) {
+      /* INT8-P o_hat: positions cut into 8 splits of ceil(max_S / 8); inside a split 32-token
+       * tiles start at the split's first 16-token block; per tile pv = p * vs (p normalised, fp32),
+       * scale = max|pv| / 127, pq = clamp(rint(pv * (1 / scale)), -127, 127),
+       * o_hat += float(sum pq * code) * scale in fp32. */
+      float ohf[128];
+      for (int d = 0; d < 128; ++d) ohf[d] = 0.f;
+      const float mxf = mx, inv_zf = (float)inv_z;
+      const int chunk = (max_S + 7) / 8;
+      for (int sp = 0; sp < 8; ++sp) {
+        const int lo = sp * chunk, hi = (sp + 1) * chunk < n ? (sp + 1) * chunk : n;
+        if (lo >= hi) continue;
+        for (int t0 = (lo / 16) * 16; t0 < hi; t0 += 32) {
+          const int a = t0 > lo ? t0 : lo, e = t0 + 32 < hi ? t0 + 32 : hi;
+          float pv[32], amax = 0.f;
+          for (int p = a; p < e; ++p) {
+            const int64_t slot = block_table[(int64_t)b * max_blocks + (p >> 4)] * 16 + (p & 15);
+            const float pr = expf(s[p] - mxf) * inv_zf;
+            pv[p - a] = pr * bf16f(v_scales[(int64_t)hk * num_slots + slot]);
+            if (fabsf(pv[p - a]) > amax) amax = fabsf(pv[p - a]);
+          }
+          const float scale = amax / 127.0f;
+          if (!(scale > 0.f)) continue;
+          const float inv_scale = 1.0f / scale;
+          int acc[128];
+          for (int d = 0; d < 128; ++d) acc[d] = 0;
+          for (int p = a; p < e; ++p) {
+            int pq = (int)nearbyintf(pv[p - a] * inv_scale);
+            if (pq > 127) pq = 127;
+            if (pq < -127) pq = -127;
+            const int64_t slot = block_table[(int64_t)b * max_blocks + (p >> 4)] * 16 + (p & 15);
+            const uint8_t* vr = v_data + ((int64_t)hk * num_slots + slot) * v_row;
+            for (int d = 0; d < 128; ++d)
+              acc[d] += pq * ((int)((d & 1) ? (vr[d >> 1] & 15) : (vr[d >> 1] >> 4)) - 8);
+          }
+          for (int d = 0; d < 128; ++d) ohf[d] += (float)acc[d] * scale;
+        }
+      }
+      for (int d = 0; d < 128; ++d) oh[d] = ohf[d];
+    }
+    for (int pass = stage_b ? 1 : 0; pass < 2; ++pass) {
       const int cnt = pass ? (top_k < n ? top_k : n) : n;
       double* dst = pass ? oo : oh;
       for (int r = 0; r < cnt; ++r) {
@@ -198,4 +240,27 @@ int jf_oracle_decode(int mode, const float* q, const uint8_t* k_data, const uint
     free(cand);
   }
   return 0;
+}
+
+int jf_oracle_decode(int mode, const float* q, const uint8_t* k_data, const uint16_t* k_scales,
+                     const uint8_t* v_data, const uint16_t* v_scales, const int64_t* block_table,
+                     const int32_t* seq_lens, int B, int H_q, int H_kv, int max_S, int max_blocks,
+                     int64_t num_slots, float attn_scale, int top_k, int n_threads, float* scores,
+                     int64_t* topk_idx, int64_t* topk_slots, float* o_hat, float* o_old, float* W,
+                     float* soft_m, float* soft_inv_z) {
+  return jf_oracle_decode_impl(mode, 0, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens, B, H_q, H_kv,
+                               max_S, max_blocks, num_slots, attn_scale, top_k, n_threads, scores, topk_idx,
+                               topk_slots, o_hat, o_old, W, soft_m, soft_inv_z);
+}
+
+/* stage_b: 0 = fp32 weights, 1 = the INT8-P arithmetic (mode 1 only). */
+int jf_oracle_decode_stage_b(int mode, int stage_b, const float* q, const uint8_t* k_data, const uint16_t* k_scales,
+                             const uint8_t* v_data, const uint16_t* v_scales, const int64_t* block_table,
+                             const int32_t* seq_lens, int B, int H_q, int H_kv, int max_S, int max_blocks,
+                             int64_t num_slots, float attn_scale, int top_k, int n_threads, float* scores,
+                             int64_t* topk_idx, int64_t* topk_slots, float* o_hat, float* o_old, float* W,
+                             float* soft_m, float* soft_inv_z) {
+  return jf_oracle_decode_impl(mode, stage_b, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens, B, H_q,
+                               H_kv, max_S, max_blocks, num_slots, attn_scale, top_k, n_threads, scores, topk_idx,
+                               topk_slots, o_hat, o_old, W, soft_m, soft_inv_z);
 }

@@ -26,6 +26,8 @@ def _c_lib():
         lib.jf_oracle_decode.restype = C.c_int
         lib.jf_oracle_decode.argtypes = [C.c_int] + [C.c_void_p] * 7 + [C.c_int] * 5 + [C.c_int64, C.c_float,
                                                                                    C.c_int, C.c_int] + [C.c_void_p] * 8
+        lib.jf_oracle_decode_stage_b.restype = C.c_int
+        lib.jf_oracle_decode_stage_b.argtypes = [C.c_int] + lib.jf_oracle_decode.argtypes
         lib.jf_oracle_num_threads.restype = C.c_int
         _C = lib
     return _C
@@ -36,8 +38,9 @@ def c_num_threads() -> int:
 
 
 def c_decode(mode: str, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens, max_s, top_k,
-             attn_scale, n_threads: int = 0, want_scores: bool = False):
-    """Run the C restatement.  Arrays as in ``jf_oracle.decode_step`` (scales as bf16 bits)."""
+             attn_scale, n_threads: int = 0, want_scores: bool = False, stage_b: str = "fp32"):
+    """Run the C restatement.  Arrays as in ``jf_oracle.decode_step`` (scales as bf16 bits);
+    ``stage_b="int8p"`` (K4V4 only) selects the reference's batch > 1 Stage-B arithmetic."""
     q = np.ascontiguousarray(q, np.float32)
     k_data, v_data = np.ascontiguousarray(k_data, np.uint8), np.ascontiguousarray(v_data, np.uint8)
     k_scales, v_scales = np.ascontiguousarray(k_scales, np.uint16), np.ascontiguousarray(v_scales, np.uint16)
@@ -51,8 +54,8 @@ def c_decode(mode: str, q, k_data, k_scales, v_data, v_scales, block_table, seq_
                inv_z=np.empty((b_n, h_q), np.float32))
     scores = np.full((b_n, h_q, max_s), -np.inf, np.float32) if want_scores else None
     p = lambda a: a.ctypes.data_as(C.c_void_p) if a is not None else None
-    rc = _c_lib().jf_oracle_decode(
-        {"k3v2": 0, "k4v4": 1}[mode], p(q), p(k_data), p(k_scales), p(v_data), p(v_scales), p(block_table),
+    rc = _c_lib().jf_oracle_decode_stage_b(
+        {"k3v2": 0, "k4v4": 1}[mode], {"fp32": 0, "int8p": 1}[stage_b], p(q), p(k_data), p(k_scales), p(v_data), p(v_scales), p(block_table),
         p(seq_lens), b_n, h_q, h_kv, int(max_s), block_table.shape[1], num_slots, float(attn_scale), int(top_k),
         int(n_threads), p(scores), p(out["topk_idx"]), p(out["topk_slots"]), p(out["o_hat"]),
         p(out["o_old_unnorm"]), p(out["W"]), p(out["m"]), p(out["inv_z"]))

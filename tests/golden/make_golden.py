@@ -13,6 +13,7 @@ exact rounding ties (x / scale == n + 0.5) and saturating values.
 """
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -46,7 +47,9 @@ def build_inputs(seed: int) -> torch.Tensor:
 
 
 def main() -> int:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # the reference checkout: argument, else $JETFIRE_REFERENCE_ROOT, else `reference` beside the repo
+    default = os.environ.get("JETFIRE_REFERENCE_ROOT") or str(Path(__file__).resolve().parents[3] / "reference")
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else default)
     sys.path.insert(0, str(ref_root))
     from jetfire_vllm.kernels.intN_pack import quantize_and_pack, unpack
 

@@ -6,8 +6,7 @@ import pytest
 import torch
 
 from jetfire_b200.adapter import config as jcfg
-from jetfire_b200.adapter.decode_path import (_decode_unsupported, _get_head_map_cpu, _select_top_k,
-                                              make_decode_metadata)
+from jetfire_b200.adapter.decode_path import _decode_unsupported, _select_top_k, make_decode_metadata
 
 
 @pytest.mark.parametrize("length,expected", [(1, 32), (17, 32), (31, 32), (32, 32), (63, 32), (64, 64),
@@ -22,11 +21,26 @@ def test_empty_or_unsupported_decode_width_is_rejected(requested, length, suppor
     assert _select_top_k(requested, length, supported) is None
 
 
-def test_tp2_local_gqa_map_keeps_heads_inside_local_shadow():
-    mapping = _get_head_map_cpu(2, 32, 8, 256)
-    assert mapping.shape == (2, 32, 256) and mapping.is_contiguous()
-    for h in range(32):
-        assert bool((mapping[:, h] == h // 8).all())
+def test_tp2_local_gqa_default_head_map_keeps_heads_inside_local_shadow():
+    """A TP-2 rank of a 64/8-head model sees 32 query heads over 4 local KV heads (the reference's
+    tests/test_runtime_edge_cases.py:29-48).  The host correction called without a head map must
+    gather query head h from local KV head h // 8 -- the same rows an explicit map selects."""
+    from jetfire_b200 import ops
+    from oracle import jf_oracle as O
+    g = torch.Generator().manual_seed(7)
+    B, H_q, H_kv, K, slots = 2, 32, 4, 16, 64
+    q = torch.randn(B, H_q, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(H_kv, slots, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(H_kv, slots, 128, generator=g).to(torch.bfloat16)
+    ts = torch.randint(0, slots, (B, H_q, K), generator=g, dtype=torch.int64)
+    hm = torch.from_numpy(O.head_map(B, H_q, H_q // H_kv, K))
+    for h in range(H_q):
+        assert bool((hm[:, h] == h // 8).all())
+    a, b = torch.empty_like(q), torch.empty_like(q)
+    ops.set_cpu_attn_threads(2)
+    ops.cpu_topk_attn(q, k, v, None, ts, a, 128 ** -0.5)
+    ops.cpu_topk_attn(q, k, v, hm, ts, b, 128 ** -0.5)
+    assert torch.equal(a, b)
 
 
 def test_config_from_environment(monkeypatch):

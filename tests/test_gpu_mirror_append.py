@@ -175,6 +175,40 @@ def test_cache_store_append_modes_and_decode_entry(mode_name, mode):
         assert (err <= lim).all(), f"{how}: max err {err.max():.3e}"
 
 
+def test_store_append_is_capturable_and_skips_out_of_range_slots():
+    """``write_slots`` with a mapped mirror is launches only: it can be captured in a CUDA graph and
+    replayed, and slots that are negative or beyond the cache (which the packing kernel skips)
+    neither mark anything filled nor disturb the device."""
+    from jetfire_b200.adapter.cache_store import JetFireCacheStore
+    from jetfire_b200.adapter.config import JetFireConfig
+    cfg = JetFireConfig(mode="SymInt3K_SymInt2V", top_k=32, group_size=64, cpu_attn_threads=2)
+    st = JetFireCacheStore(num_blocks=4, num_kv_heads=2, head_dim=128, cfg=cfg, device="cuda",
+                           dtype=torch.bfloat16, mirror_append="mapped")
+    g = torch.Generator().manual_seed(3)
+    key = torch.randn(6, 2, 128, generator=g).to(torch.bfloat16).cuda()
+    val = torch.randn(6, 2, 128, generator=g).to(torch.bfloat16).cuda()
+    slots = torch.tensor([5, -1, 63, 64, 1 << 40, 0], dtype=torch.int64, device="cuda")   # 64 and 2^40 are out of range
+    st.write_slots(key, val, slots)          # eager once (sets kernel attributes), then captured
+    st.flush_pending_writes()
+    st._filled_buf.zero_()
+    st.k_shadow.zero_()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            st.write_slots(key, val, slots)
+    graph.replay()
+    torch.cuda.synchronize()
+    filled = st.slot_filled.cpu().numpy()
+    assert sorted(np.flatnonzero(filled).tolist()) == [0, 5, 63]
+    for t, s_ in ((0, 5), (2, 63), (5, 0)):
+        assert torch.equal(st.k_shadow[:, s_], key[t].cpu())
+    untouched = [s_ for s_ in range(64) if s_ not in (0, 5, 63)]
+    assert not st.k_shadow[:, untouched].any()
+
+
 def test_decode_steps_replayed_as_one_cuda_graph_with_host_nodes():
     """A whole decode step of one layer captured once and replayed: append of the new token
     (packed cache + mapped mirror, one kernel), query upload, scan + selection, slot download,

@@ -26,6 +26,25 @@ def test_c_restatement_equals_numpy(mode, seed):
     np.testing.assert_allclose(c["W"], ref["W"], atol=2e-6)
 
 
+@pytest.mark.parametrize("ctx,lens,seed", [(1024, [1024, 513, 17], 14), (1000, [1000, 999, 0], 15), (336, [336, 40], 16)])
+def test_c_int8p_stage_b_equals_numpy(ctx, lens, seed):
+    """The C restatement of the K4V4 batch > 1 Stage B (weights rounded per 32-token tile, tiles laid
+    out over the reference's 8 splits) against the numpy one, with max_S that cuts 16-token blocks
+    between splits (1000 / 8 = 125) as well as aligned ones."""
+    case = Case("k4v4", len(lens), 8, 2, ctx, lens=lens, seed=seed)
+    ref = case.oracle_step(32, stage_b="int8p", with_correction=False)
+    kd, ks, vd, vs = case.oracle_cache()
+    c = native.c_decode("k4v4", f32_values(case.q), kd, ks, vd, vs, case.block_table.numpy(),
+                        case.seq_lens.numpy(), case.ctx, 32, case.attn_scale, n_threads=2, stage_b="int8p")
+    assert np.array_equal(c["topk_idx"], ref["topk_idx"])
+    # the two differ only in the float type of exp (and so, rarely, in one rounding step of one weight)
+    np.testing.assert_allclose(c["o_hat"], ref["o_hat"], atol=2e-5)
+    np.testing.assert_allclose(c["o_old_unnorm"], ref["o_old_unnorm"], atol=2e-6)
+    np.testing.assert_allclose(c["W"], ref["W"], atol=2e-6)
+    fp32 = case.oracle_step(32, with_correction=False)
+    assert np.abs(ref["o_hat"] - fp32["o_hat"]).max() > 1e-4, "the rounding must be visible against fp32 weights"
+
+
 def _correction_inputs(dtype=torch.bfloat16, K=64):
     case = Case("k3v2", 2, 8, 2, 512, seed=9, dtype=dtype)
     g = torch.Generator().manual_seed(1)

@@ -63,3 +63,63 @@ def test_rejects_requests_beyond_the_built_in_buffer():
     a.mode = _lib.JF_MODE_K4V4
     assert _lib.lib.jf_decode_fused_static(C.byref(a), None) == _lib.JF_ERR_UNSUPPORTED
     assert _lib.lib.jf_decode_fused_static(None, None) == _lib.JF_ERR_ARG
+
+
+def _packed_problem(B, H_q, H_kv, max_S, lens, num_slots, top_k, seed):
+    """Argument block over a small random packed cache (bytes and scales drawn directly: only the
+    two entry points are compared here, the arithmetic is pinned elsewhere) with a block table wide
+    enough for ``max_S`` -- the scratch a call needs grows with max_S, not with the tokens present."""
+    from jetfire_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    dev = dict(device="cuda")
+    kd = torch.randint(0, 256, (H_kv, num_slots, 48), dtype=torch.uint8, generator=g, **dev)
+    vd = torch.randint(0, 256, (H_kv, num_slots, 32), dtype=torch.uint8, generator=g, **dev)
+    ks = (torch.rand(H_kv, num_slots, 2, generator=g, **dev) + 0.5).to(torch.bfloat16)
+    vs = (torch.rand(H_kv, num_slots, 2, generator=g, **dev) + 0.5).to(torch.bfloat16)
+    q = torch.randn(B, H_q, 128, generator=g, **dev).to(torch.bfloat16)
+    bt = torch.zeros(B, (max_S + 15) // 16, dtype=torch.int64, **dev)
+    per = num_slots // 16 // B
+    for b in range(B):
+        bt[b, :per] = torch.arange(b * per, (b + 1) * per, dtype=torch.int64, **dev)
+    sl = torch.tensor(lens, dtype=torch.int32, **dev)
+    return ("k3v2", q, kd, ks, vd, vs, bt, sl, max_S, H_q, H_kv, 16, top_k, 128 ** -0.5)
+
+
+def _largest_max_s_that_fits(B, H_q, H_kv, top_k):
+    from jetfire_b200 import _lib
+    need = lambda s: _lib.lib.jf_decode_workspace_bytes(_lib.JF_MODE_K3V2, B, H_q, H_kv, s, top_k)
+    max_s = 262144
+    while need(max_s) > STATIC_BYTES:
+        max_s -= 16
+    assert need(max_s) <= STATIC_BYTES < need(max_s + 16)
+    return max_s
+
+
+def test_limit_is_exact_and_the_call_allocates_nothing():
+    """The largest request that fits the built-in array is served (same bits as the workspace
+    entry point), the next larger one is refused, and a call changes nothing about the device's
+    free memory -- which is the reason this entry point exists."""
+    from jetfire_b200 import _lib, ops
+    B, H_q, H_kv, top_k = 2, 32, 8, 64
+    max_s = _largest_max_s_that_fits(B, H_q, H_kv, top_k)
+    args = _packed_problem(B, H_q, H_kv, max_s, [4000, 1000], 8192, top_k, seed=5)
+    ref = ops.DecodeCall(*args)
+    ref.fused()
+    mine = ops.DecodeCall(*args)
+    mine.args.workspace, mine.args.workspace_bytes = None, 0
+    stream = torch.cuda.current_stream().cuda_stream
+    assert _lib.lib.jf_decode_fused_static(C.byref(mine.args), stream) == 0
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    assert _lib.lib.jf_decode_fused_static(C.byref(mine.args), stream) == 0      # nothing but this call in between
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the static entry point changed the device's free memory"
+    for name in ("topk_idx", "topk_slots", "o_hat", "o_old_unnorm", "W"):
+        assert torch.equal(mine.out[name], ref.out[name]), name
+    # a timed-out wait inside its kernels would be recorded in the built-in array: none here
+    assert _lib.lib.jf_decode_status(C.byref(mine.args), stream) == 0
+    too_big = _lib.DecodeArgs()
+    C.memmove(C.byref(too_big), C.byref(mine.args), C.sizeof(_lib.DecodeArgs))
+    too_big.max_S = max_s + 16
+    too_big.max_blocks = (max_s + 16 + 15) // 16
+    assert _lib.lib.jf_decode_fused_static(C.byref(too_big), stream) == _lib.JF_ERR_STATIC_LIMIT
