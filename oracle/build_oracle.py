@@ -8,6 +8,17 @@
   replaced by explicit ISA sets so that the binary can run on another host: ``avx512bf16``
   (the reference's SIMD path) and ``avx2`` (its scalar template, auto-vectorised).
   Built only where the checkout exists; outputs are git-ignored and travel with the tree.
+* ``oracle/_ref/jetfire_<kernel>_ref.so`` -- the reference's own GPU kernels for the two paper
+  modes, compiled UNMODIFIED from the same checkout for sm_100: Stage A ``int3_qk_scores.cu`` and
+  ``int8tc_qk_scores.cu``, Stage B ``int2_softmax_v.cu``, ``int4_softmax_v.cu`` and
+  ``int8tc_softmax_v_fused.cu``, and ``blend.cu``.  The first, third, fourth and last carry no
+  architecture flag in their loaders (``jetfire_vllm/kernels/int3_split.py:40-46``,
+  ``int2_split.py:60-66``, ``int4_split.py:60-66``, ``blend.py:45-46``), so this is what the
+  reference's own JIT build produces on a B200.  The two ``int8tc_*`` loaders pin sm_90 / sm_90a
+  (``kernels/int8tc_qk_scores.py:43-48``, ``int8tc_softmax_v_fused.py:49-54``); their sources are
+  compiled as they are with only that flag changed to sm_100 (and ``--use_fast_math`` kept for the
+  second) -- labelled "flag edit" wherever their numbers are shown.  They pin the restated scan /
+  top-k / Stage B arithmetic on the GPU box and give a same-box GPU baseline.
 
     python -m oracle.build_oracle [reference_root]
 
@@ -92,13 +103,69 @@ def build_ref(ref_root: str | Path | None = None, force: bool = False) -> list[P
     return outs
 
 
+# name -> (source under jetfire_vllm/csrc, extra nvcc flags, label)
+REF_GPU = {
+    "int3_qk_scores": ("int3_qk_scores.cu", [], "unmodified"),
+    "int2_softmax_v": ("int2_softmax_v.cu", [], "unmodified"),
+    "int4_softmax_v": ("int4_softmax_v.cu", [], "unmodified"),
+    "blend": ("blend.cu", [], "unmodified"),
+    "int8tc_qk_scores": ("int8tc_qk_scores.cu", [], "flag edit: sm_90 -> sm_100"),
+    "int8tc_softmax_v_fused": ("int8tc_softmax_v_fused.cu", ["--use_fast_math"], "flag edit: sm_90a -> sm_100"),
+}
+
+
+def ref_gpu_path(name: str) -> Path:
+    return REF_OUT / f"jetfire_{name}_ref.so"
+
+
+def build_ref_gpu(ref_root: str | Path | None = None, force: bool = False, jobs: int = 0) -> list[Path]:
+    """The reference's GPU kernels as torch extension modules for sm_100 (a few minutes each; run
+    ``jobs`` at a time, default: one per two host cores)."""
+    csrc = reference_root(ref_root) / "jetfire_vllm" / "csrc"
+    outs = [ref_gpu_path(n) for n in REF_GPU]
+    if not csrc.exists():
+        return [o for o in outs if o.exists()]
+    from torch.utils.cpp_extension import include_paths, library_paths
+    import torch
+    REF_OUT.mkdir(exist_ok=True)
+    incs = [f"-I{p}" for p in include_paths()] + [f"-I{sysconfig.get_paths()['include']}"]
+    libdirs = library_paths() + [str(CUDA_HOME / "lib64")]
+    todo = []
+    for name, (src, extra, _label) in REF_GPU.items():
+        out = ref_gpu_path(name)
+        if not force and out.exists():
+            continue
+        mod = out.name[:-3]
+        todo.append([str(CUDA_HOME / "bin" / "nvcc"), "-O3", "-std=c++17", "-gencode", "arch=compute_100,code=sm_100",
+                     *extra, "-Xcompiler", "-fPIC", "-Xcompiler", "-O3", "-shared", f"-DTORCH_EXTENSION_NAME={mod}",
+                     "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+                     "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__",
+                     "-D__CUDA_NO_BFLOAT16_CONVERSIONS__", "-D__CUDA_NO_HALF2_OPERATORS__", "--expt-relaxed-constexpr",
+                     *incs, str(csrc / src), "-o", str(out), *[f"-L{d}" for d in libdirs],
+                     "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"])
+    jobs = jobs or max(1, (os.cpu_count() or 2) // 2)
+    running = []
+    while todo or running:
+        while todo and len(running) < jobs:
+            cmd = todo.pop(0)
+            running.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        cmd, p = running.pop(0)
+        out_text, _ = p.communicate()
+        if p.returncode != 0:
+            raise RuntimeError("reference GPU kernel build failed: " + " ".join(cmd) + "\n" + out_text[-4000:])
+    return outs
+
+
 def build_all() -> None:
     build_c()
     build_ref()
+    build_ref_gpu()
 
 
 if __name__ == "__main__":
     build_c(force=True)
     print(C_LIB)
     for p in build_ref(sys.argv[1] if len(sys.argv) > 1 else None, force=True):
+        print(p)
+    for p in build_ref_gpu(sys.argv[1] if len(sys.argv) > 1 else None, force=True):
         print(p)

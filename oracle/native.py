@@ -4,6 +4,8 @@
 ``ref_cpu_topk_attn_module``: the reference's own ``cpu_topk_attn`` extension built by
 ``oracle/build_oracle.py`` (None when it was never built, e.g. the reference checkout is
 absent and no prebuilt file travelled with the tree).
+``ref_gpu_module``: one of the reference's own GPU kernels built for sm_100 by the same script
+(None when absent or when it does not load).
 """
 from __future__ import annotations
 
@@ -109,4 +111,28 @@ def ref_cpu_topk_attn_module(isa: str | None = None):
         print(f"[oracle] reference extension failed to load: {exc}")
         mod = None
     _REF[isa] = mod
+    return mod
+
+
+_REF_GPU = {}
+
+
+def ref_gpu_module(name: str):
+    """The reference's GPU extension ``name`` (a key of ``build_oracle.REF_GPU``: ``int3_qk_scores``,
+    ``int2_softmax_v``, ``int4_softmax_v``, ``int8tc_qk_scores``, ``int8tc_softmax_v_fused``,
+    ``blend``) compiled from its unmodified source for sm_100, or None."""
+    if name in _REF_GPU:
+        return _REF_GPU[name]
+    path = HERE / "_ref" / f"jetfire_{name}_ref.so"
+    mod = None
+    if path.exists():
+        import torch  # noqa: F401  (the extension links against libtorch)
+        try:
+            spec = importlib.util.spec_from_file_location(path.name[:-3], str(path))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+        except Exception as exc:  # pragma: no cover - depends on the host
+            print(f"[oracle] reference GPU extension {name} failed to load: {exc}")
+            mod = None
+    _REF_GPU[name] = mod
     return mod
