@@ -223,6 +223,9 @@ jf_status_t jf_topk_select(const jf_decode_args* args, jf_stream_t stream);
  * csrc/int2_softmax_v.cu:738-788). */
 jf_status_t jf_decode_finish(const jf_decode_args* args, jf_stream_t stream);
 jf_status_t jf_decode_fused(const jf_decode_args* args, jf_stream_t stream);
+/* The second kernel of jf_decode_fused on its own (select and finish in one launch), for a scan
+ * that was launched separately; same outputs, same bits. */
+jf_status_t jf_select_finish(const jf_decode_args* args, jf_stream_t stream);
 /* Exact row maximum m and 1 / sum exp(s - m) over positions [0, min(seq_lens[b], max_S)) of
  * stored scores (B, H_q, max_S): the two extra outputs of the reference's
  * int8tc_qk_scores_topk_stats (jetfire_vllm/csrc/int8tc_qk_scores.cu:1790-1800, 2426-2482).

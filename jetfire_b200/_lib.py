@@ -82,6 +82,7 @@ _SIGS = {
     "jf_topk_select": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_finish": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_fused": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "jf_select_finish": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_status": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_softmax_stats": (C.c_int32, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p]),
     "jf_decode_fused_static": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),

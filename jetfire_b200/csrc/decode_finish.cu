@@ -139,6 +139,12 @@ extern "C" jf_status_t jf_decode_fused(const jf_decode_args* a, jf_stream_t stre
   return jf::launch_select(a, static_cast<cudaStream_t>(stream), true);
 }
 
+// select + finish in one kernel, after a scan that ran on its own (the second half of jf_decode_fused)
+extern "C" jf_status_t jf_select_finish(const jf_decode_args* a, jf_stream_t stream) {
+  if (a && a->scan_parts == JF_SCAN_K_ONLY) return JF_ERR_ARG;   // the finish stage needs the V side
+  return jf::launch_select(a, static_cast<cudaStream_t>(stream), true);
+}
+
 extern "C" jf_status_t jf_decode_status(const jf_decode_args* a, jf_stream_t stream_) {
   using namespace jf;
   if (!a) return JF_ERR_ARG;

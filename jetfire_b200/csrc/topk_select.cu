@@ -389,8 +389,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       };
 
       // Block-wide: turns hist[] into inclusive prefix counts (from the top bin down) and
-      // leaves in sm.tbin the bin where the count reaches K (-1: never).
-      auto scan_hist = [&]() {
+      // leaves in sm.tbin the bin where the count reaches `want` (-1: never).
+      auto scan_hist = [&](int want) {
         const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
         const int v = h0 + h1;
         int incl = v;
@@ -414,28 +414,24 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         const int ex = sm.wsum[warp] + incl - v;
         hist[2 * tid] = ex + h0;
         hist[2 * tid + 1] = ex + v;
-        if (ex < K && ex + h0 >= K) sm.tbin = 2 * tid;
-        else if (ex + h0 < K && ex + v >= K) sm.tbin = 2 * tid + 1;
+        if (ex < want && ex + h0 >= want) sm.tbin = 2 * tid;
+        else if (ex + h0 < want && ex + v >= want) sm.tbin = 2 * tid + 1;
         __syncthreads();
       };
-      // Block-wide: positions whose bin is <= last go to keys[], in position order (offsets from
-      // a warp scan and a block scan, no atomics); returns how many there are (may exceed
-      // sort_n: then keys[] is partial).
+      // Block-wide: positions whose score passes the test against `thr` (kind 0: greater, 1: greater
+      // or equal, 2: equal) go to keys[off0 ...], in position order (offsets from a warp scan and a
+      // block scan, no atomics); entries at or past `cap` are dropped.  Returns how many passed.
       float hm[kChunkVec];  // per float4 of the resident chunk: its largest score (tier 1a's pass)
       bool have_hm = false;
-      auto collect = [&](int last) {
-        // bin <= last  <=>  fma(s, -64, top64) < last + 1; one comparison per score against a
-        // threshold a little below the exact boundary (a few extra candidates are harmless)
-        const float xlim = static_cast<float>(last + 1);
+      auto collect = [&](float thr, int kind, int off0, int cap) {
         int running = 0;  // candidates found in earlier chunks
-        const float thr = (top64 - xlim) * (1.0f / kBinsPerUnit) - (fabsf(top64) + xlim) * (1.0f / (kBinsPerUnit * 2097152.0f)) - 1e-30f;
         for (int ci = 0; ci < n_chunks; ++ci) {
           if (n_chunks > 1) next_chunk(ci);
           uint32_t mask = 0u;
           // which of the thread's float4s can hold a candidate at all (branch-free; most threads
           // find none and skip the loads altogether)
           uint32_t hits = (1u << kChunkVec) - 1u;
-          if (have_hm) {
+          if (have_hm && kind == 0) {
             hits = 0u;
 #pragma unroll
             for (int j = 0; j < kChunkVec; ++j) hits |= static_cast<uint32_t>(hm[j] > thr) << j;
@@ -444,8 +440,16 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             const int j = __ffs(hits) - 1;
             hits &= hits - 1u;
             const float4 v = chunk4[j * kSelThreads + tid];
-            const uint32_t m4 = static_cast<uint32_t>(v.x > thr) | (static_cast<uint32_t>(v.y > thr) << 1) |
-                                (static_cast<uint32_t>(v.z > thr) << 2) | (static_cast<uint32_t>(v.w > thr) << 3);
+            uint32_t m4;
+            if (kind == 0)
+              m4 = static_cast<uint32_t>(v.x > thr) | (static_cast<uint32_t>(v.y > thr) << 1) |
+                   (static_cast<uint32_t>(v.z > thr) << 2) | (static_cast<uint32_t>(v.w > thr) << 3);
+            else if (kind == 1)
+              m4 = static_cast<uint32_t>(v.x >= thr) | (static_cast<uint32_t>(v.y >= thr) << 1) |
+                   (static_cast<uint32_t>(v.z >= thr) << 2) | (static_cast<uint32_t>(v.w >= thr) << 3);
+            else
+              m4 = static_cast<uint32_t>(v.x == thr) | (static_cast<uint32_t>(v.y == thr) << 1) |
+                   (static_cast<uint32_t>(v.z == thr) << 2) | (static_cast<uint32_t>(v.w == thr) << 3);
             mask |= m4 << (4 * j);
           }
           const int cnt = __popc(mask);
@@ -457,7 +461,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           }
           // warp totals -> every warp's offset (no atomics: 32 same-address atomics with a
           // return value cost more than the whole pass)
-          if (ci > 0) __syncthreads();   // the previous round's reads of wsum are done (the first round follows a barrier)
+          __syncthreads();   // the previous round's (or caller's) reads of wsum are done
           if (lane == 31) sm.wsum[warp] = incl;
           __syncthreads();
           int wt = sm.wsum[lane], winc = wt;
@@ -468,12 +472,12 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           }
           const int base = running + __shfl_sync(0xFFFFFFFFu, winc - wt, warp);
           running += __shfl_sync(0xFFFFFFFFu, winc, 31);
-          int o = base + incl - cnt;
+          int o = off0 + base + incl - cnt;
           while (mask) {
             const int e = __ffs(mask) - 1;
             mask &= mask - 1u;
             const int at = 4 * ((e >> 2) * kSelThreads + tid) + (e & 3);
-            if (o < p.sort_n) { keys[o] = static_cast<uint64_t>(ci * kChunkPos + at); cand_score[o] = chunk[at]; }
+            if (o < cap) { keys[o] = static_cast<uint64_t>(ci * kChunkPos + at); cand_score[o] = chunk[at]; }
             ++o;
           }
         }
@@ -499,47 +503,78 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       }
       have_hm = n_chunks == 1;  // hm[] describes the chunk that stays resident
       __syncthreads();
-      scan_hist();
+      scan_hist(K);
       bool ok = false;
       {
         const int tbin = sm.tbin;
         const int last = tbin + nb;
         if (tbin >= 0 && last < kBins - 1) {
-          const int total = collect(last);
+          // bin <= last  <=>  fma(s, -64, top64) < last + 1; one comparison per score against a
+          // threshold a little below the exact boundary (a few extra candidates are harmless)
+          const float xlim = static_cast<float>(last + 1);
+          const float thr = (top64 - xlim) * (1.0f / kBinsPerUnit) - (fabsf(top64) + xlim) * (1.0f / (kBinsPerUnit * 2097152.0f)) - 1e-30f;
+          const int total = collect(thr, 0, 0, p.sort_n);
           ok = total <= p.sort_n;
           ncand = total;
           cand_last = last + nb;
         }
       }
       if (!ok) {
-        // ---- tier 1b: histogram of every score; the band around the bin of the K-th largest ----
-        __syncthreads();
-        if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
-        for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
-        __syncthreads();
-        for (int ci = 0; ci < n_chunks; ++ci) {
-          if (n_chunks > 1) next_chunk(ci);
-#pragma unroll
-          for (int j = 0; j < kChunkVec; ++j) {
-            const float4 v = chunk4[j * kSelThreads + tid];
-            if (v.x > -INFINITY) atomicAdd(&hist[score_bin(top64, v.x)], 1);
-            if (v.y > -INFINITY) atomicAdd(&hist[score_bin(top64, v.y)], 1);
-            if (v.z > -INFINITY) atomicAdd(&hist[score_bin(top64, v.z)], 1);
-            if (v.w > -INFINITY) atomicAdd(&hist[score_bin(top64, v.w)], 1);
-          }
-        }
-        __syncthreads();
-        scan_hist();
-        const int tbin = sm.tbin;
-        const int last = min(max(tbin, 0) + nb, kBins - 1);
-        if (tbin < 0 || last >= kBins - 1 || hist[last] > p.sort_n) {
-          slow = true;
-        } else {
-          for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+        // ---- tier 1b (rows the fixed bins do not fit: a score far above the rest, scores packed
+        //      closer than a bin, or too many in the band): the K-th largest approximate score
+        //      EXACTLY, by a radix select over the order-preserving keys of the resident scores --
+        //      three levels of 11, 11 and 10 bits, each one pass over shared memory -- and then
+        //      the positions at or above it (minus the band for K3V2).  Independent of the range and
+        //      the spacing of the scores, and a few passes over the row at most. ----
+        have_hm = false;
+        uint32_t prefix = 0u;
+        int want = K;
+        for (int level = 0; level < 3; ++level) {
+          const int bits = (level == 2) ? 10 : 11, shift = (level == 0) ? 21 : (level == 1) ? 10 : 0;
+          const uint32_t dmask = (1u << bits) - 1u;
           __syncthreads();
-          ncand = collect(last);
-          cand_last = last + nb;
+          if (tid == 0) sm.tbin = -1;
+          for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
+          __syncthreads();
+          for (int ci = 0; ci < n_chunks; ++ci) {
+            if (n_chunks > 1) next_chunk(ci);
+#pragma unroll
+            for (int j = 0; j < kChunkVec; ++j) {
+              const float4 v = chunk4[j * kSelThreads + tid];
+              const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                if (e[c] > -INFINITY) {
+                  const uint32_t key = float_order_key(e[c]);
+                  // larger keys first: digit d goes to bin kBins - 1 - d
+                  if (level == 0 || (key >> (shift + bits)) == prefix)
+                    atomicAdd(&hist[kBins - 1 - static_cast<int>((key >> shift) & dmask)], 1);
+                }
+              }
+            }
+          }
+          __syncthreads();
+          scan_hist(want);
+          const int tb = max(sm.tbin, 0);
+          want -= (tb > 0) ? hist[tb - 1] : 0;   // hist[] now holds inclusive counts from the top bin down
+          prefix = (prefix << bits) | static_cast<uint32_t>(kBins - 1 - tb);
         }
+        const float kth = float_from_order_key(prefix);   // the K-th largest approximate score
+        __syncthreads();
+        for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+        __syncthreads();
+        if (MODE == JF_MODE_K4V4) {
+          // the scores are canonical: everything above the K-th, then the lowest positions among
+          // those equal to it (the collection runs in position order) -- exactly K candidates
+          const int n_gt = collect(kth, 0, 0, p.sort_n);
+          collect(kth, 2, n_gt, K);
+          ncand = K;
+        } else {
+          const int total = collect(kth - 2.0f * delta - 1e-30f, 1, 0, p.sort_n);
+          if (total > p.sort_n) slow = true;   // more scores inside the band than the sort buffer holds: massive ties
+          ncand = min(total, p.sort_n);
+        }
+        cand_last = kBins;
       }
       if (!copied) {  // a later chunk did not arrive: select nothing
         if (tid == 0) report_status(p.status, JF_ERR_TIMEOUT);

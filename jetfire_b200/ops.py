@@ -370,6 +370,10 @@ class DecodeCall:
     def fused(self):
         check("jf_decode_fused", lib.jf_decode_fused(self._ref, _stream()))
 
+    def select_finish(self):
+        """Select and finish in one kernel, after ``scan()`` (together: ``fused()``)."""
+        check("jf_select_finish", lib.jf_select_finish(self._ref, _stream()))
+
     def exact_stats(self):
         """Exact row maximum and 1 / sum exp(s - max) of the stored scores into ``softmax_m`` /
         ``softmax_inv_z`` (what the reference's ``*_topk_stats`` ops return)."""

@@ -96,3 +96,43 @@ def test_qwen3_moe_geometry_full_size_k3v2():
 def test_context_131072(mode, stage_b):
     """The longest context of the sweep, one sequence and one shorter one: four select chunks per row."""
     _run(Case(mode, 2, 8, 2, 131072, lens=[131072, 100003], seed=61), 256, stage_b=stage_b)
+
+
+def _select_us(case, top_k, reps=5):
+    """Device time of the select kernel alone (CUDA events on the launching stream, best of `reps`)."""
+    from jetfire_b200 import ops
+    kd, ks, vd, vs = case.device_cache()
+    call = ops.DecodeCall(case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+                          case.ctx, case.H_q, case.H_kv, 16, top_k, case.attn_scale)
+    call.scan(); call.select(); torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); call.select(); e1.record(); torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3)
+    call.status()
+    return best
+
+
+@pytest.mark.parametrize("mode", ["k3v2", "k4v4"])
+@pytest.mark.parametrize("shape", ["outlier", "flat"])
+def test_rows_that_do_not_fit_the_fixed_bins_stay_exact_and_fast(mode, shape):
+    """Rows on which the first selection tier gives up -- one score far above all others (the k-th
+    largest then lies outside the histogram's range) or scores packed far closer than a bin -- take
+    the exact radix tier.  The result is still the oracle's, and such a row may cost a few extra
+    passes over shared memory, not a scan of the cache per pass: at most 10x an ordinary row."""
+    normal = Case(mode, 1, 8, 2, 32768, lens=[32768], seed=70)
+    odd = Case(mode, 1, 8, 2, 32768, lens=[32768], seed=70)
+    if shape == "outlier":
+        # the key at position 12345 of every KV head points along the query of the group's first head
+        for hk in range(odd.H_kv):
+            slot = int(odd.block_table[0, 12345 // 16]) * 16 + 12345 % 16
+            odd.k_full[hk, slot] = (40.0 * odd.q[0, hk * 4].float()).to(odd.dtype)
+    else:
+        odd.q = (odd.q.float() * 2.0 ** -12).to(odd.dtype)     # every score within a few 1e-3 of zero
+    res, ref = _run(odd, 256)
+    if shape == "outlier":
+        assert int(res.topk_idx[0, 0, 0]) == 12345
+    t_norm, t_odd = _select_us(normal, 256), _select_us(odd, 256)
+    print(f"{mode} {shape}: select {t_odd:.1f} us against {t_norm:.1f} us for an ordinary row")
+    assert t_odd <= 10.0 * t_norm
