@@ -75,3 +75,18 @@ def make_backend():
             return FlashAttentionMetadataBuilder
 
     return JetFireAttentionBackend
+
+
+_BACKEND = None
+
+
+def __getattr__(name):
+    """``JetFireAttentionBackend`` / ``JetFireAttentionImpl`` resolve lazily (the class path vLLM's
+    registry is given, see ``registry.JETFIRE_BACKEND_PATH``), so importing this module does not
+    import vLLM."""
+    global _BACKEND
+    if name in ("JetFireAttentionBackend", "JetFireAttentionImpl"):
+        if _BACKEND is None:
+            _BACKEND = make_backend()
+        return _BACKEND if name == "JetFireAttentionBackend" else _BACKEND.get_impl_cls()
+    raise AttributeError(name)

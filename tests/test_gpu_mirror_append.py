@@ -209,6 +209,59 @@ def test_store_append_is_capturable_and_skips_out_of_range_slots():
     assert not st.k_shadow[:, untouched].any()
 
 
+def test_backend_routes_append_and_decode_through_installed_stores(monkeypatch):
+    """The attention-backend shim as vLLM drives it: ``install_layer_stores`` with the planned cache
+    geometry, ``do_kv_cache_update`` per layer with vLLM's padded slot mapping, ``forward`` for a
+    decode batch (served here, result = the oracle's) and for a prefill batch (handed to the native
+    implementation untouched)."""
+    from jetfire_b200.adapter.config import JetFireConfig
+    from jetfire_b200.adapter.decode_path import make_decode_metadata
+    from jetfire_b200.adapter.jetfire_backend import JetFireAttentionImplMixin, get_layer_store
+    from jetfire_b200.adapter.registry import install_layer_stores
+    case = Case("k3v2", 2, 8, 2, 300, lens=[300, 123], seed=27)
+    cfg = JetFireConfig(mode="SymInt3K_SymInt2V", top_k=64, group_size=64, cpu_attn_threads=2)
+
+    class Native:
+        calls = []
+
+        def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None, output_scale=None,
+                    output_block_scale=None):
+            Native.calls.append("forward")
+            return "native"
+
+        def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping):
+            Native.calls.append("update")
+
+    class Impl(JetFireAttentionImplMixin, Native):
+        scale = case.attn_scale
+        attn_type = SimpleNamespace(name="DECODER")
+
+    import jetfire_b200.adapter.jetfire_backend as jb
+    monkeypatch.setattr(jb, "get_jetfire_config", lambda: cfg)   # the configuration this test runs under
+    layer = SimpleNamespace(num_heads=case.H_q, num_kv_heads=case.H_kv, head_size=128, layer_name="model.layers.0.attn")
+    odd = SimpleNamespace(num_heads=8, num_kv_heads=2, head_size=64, layer_name="model.layers.1.attn")
+    stores = install_layer_stores({layer.layer_name: layer, odd.layer_name: odd}, num_blocks=case.n_blocks, cfg=cfg,
+                                  dtype=case.dtype)
+    assert list(stores) == [layer.layer_name] and get_layer_store(odd.layer_name) is None
+    impl = Impl()
+    key = case.k_full.transpose(0, 1).contiguous().cuda().reshape(case.num_slots, case.H_kv * 128)
+    val = case.v_full.transpose(0, 1).contiguous().cuda().reshape(case.num_slots, case.H_kv * 128)
+    slot_mapping = torch.arange(case.num_slots, dtype=torch.int64, device="cuda")
+    impl.do_kv_cache_update(layer, key, val, None, slot_mapping)
+    assert Native.calls == ["update"]                        # vLLM's own cache still gets its update
+    md = make_decode_metadata(case.seq_lens.cuda(), case.block_table.cuda())
+    out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
+    got = impl.forward(layer, case.q.cuda().reshape(case.B, -1), None, None, None, md, output=out)
+    assert got is out and Native.calls == ["update"]
+    torch.cuda.synchronize()
+    ref = case.oracle_step(64)
+    want = O.bf16_bits_to_f32(O.f32_to_bf16_bits(ref["out"]))
+    err = np.abs(f32_values(out).reshape(case.B, case.H_q, 128) - want)
+    assert (err <= 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)).all(), f"max err {err.max():.3e}"
+    prefill = SimpleNamespace(**{**vars(md), "max_query_len": 7})
+    assert impl.forward(layer, case.q.cuda().reshape(case.B, -1), None, None, None, prefill, output=out) == "native"
+
+
 def test_decode_steps_replayed_as_one_cuda_graph_with_host_nodes():
     """A whole decode step of one layer captured once and replayed: append of the new token
     (packed cache + mapped mirror, one kernel), query upload, scan + selection, slot download,
