@@ -98,7 +98,6 @@ __device__ __forceinline__ float acc_to_f32(int acc_biased) { return __int_as_fl
 
 // Shared memory of a CTA: the warps' rings, their barriers (one per two-page slot), the query
 // exchange buffer, the parked tile descriptors.
-constexpr int kPagesInFlight = 2 * T4::kSlots;                                  // per warp
 constexpr int kRingBytes = kScanWarps * T4::kSlots * T4::kSlotBytes;
 constexpr int kBarOff = kRingBytes;
 constexpr int kQxOff = kBarOff + 64;                                            // 4 warps x 2 barriers

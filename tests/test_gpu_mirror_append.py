@@ -251,7 +251,7 @@ def test_backend_routes_append_and_decode_through_installed_stores(monkeypatch):
     assert Native.calls == ["update"]                        # vLLM's own cache still gets its update
     md = make_decode_metadata(case.seq_lens.cuda(), case.block_table.cuda())
     out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
-    got = impl.forward(layer, case.q.cuda().reshape(case.B, -1), None, None, None, md, output=out)
+    got = impl.forward(layer, case.q.cuda(), None, None, None, md, output=out)
     assert got is out and Native.calls == ["update"]
     torch.cuda.synchronize()
     ref = case.oracle_step(64)
@@ -259,7 +259,7 @@ def test_backend_routes_append_and_decode_through_installed_stores(monkeypatch):
     err = np.abs(f32_values(out).reshape(case.B, case.H_q, 128) - want)
     assert (err <= 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)).all(), f"max err {err.max():.3e}"
     prefill = SimpleNamespace(**{**vars(md), "max_query_len": 7})
-    assert impl.forward(layer, case.q.cuda().reshape(case.B, -1), None, None, None, prefill, output=out) == "native"
+    assert impl.forward(layer, case.q.cuda(), None, None, None, prefill, output=out) == "native"
 
 
 def test_decode_steps_replayed_as_one_cuda_graph_with_host_nodes():
