@@ -365,6 +365,21 @@ def time_loop(torch, fn, reps):
     return e0.elapsed_time(e1) * 1e3 / reps
 
 
+def time_graph(torch, fn, reps):
+    """The same for a sequence of launches replayed as one CUDA graph, so that short kernels are
+    timed on the device and not by how fast the host can launch them."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return time_loop(torch, g.replay, reps)
+
+
 def per_kernel_times(torch, ops, w, layers, reps):
     """Each kernel of a layer replayed on its own over all layers (inputs larger than L2 in total)."""
     n = len(layers)
@@ -381,9 +396,9 @@ def per_kernel_times(torch, ops, w, layers, reps):
         for L in layers:
             merge(ops, L)
 
-    t_scan = time_loop(torch, scans, reps) / n
-    t_sel = time_loop(torch, selects, reps) / n
-    t_mrg = time_loop(torch, merges, reps) / n
+    t_scan = time_graph(torch, scans, reps) / n
+    t_sel = time_graph(torch, selects, reps) / n
+    t_mrg = time_graph(torch, merges, reps) / n
     return {"scan_us": t_scan, "select_finish_us": t_sel, "merge_us": t_mrg}
 
 

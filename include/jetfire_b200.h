@@ -65,7 +65,7 @@ enum { JF_STAGE_B_FP32 = 0, JF_STAGE_B_INT8P = 1 };
 #define JF_HEAD_DIM   128
 #define JF_BLOCK_SIZE 16
 #define JF_MAX_TOP_K  2048
-#define JF_MAX_GROUP  8     /* query heads per KV head handled in one pass */
+#define JF_MAX_GROUP  16    /* query heads per KV head: 1..8, or 16 (handled as two halves of 8) */
 
 const char* jf_status_string(jf_status_t st);
 int32_t     jf_version(void);
@@ -179,7 +179,7 @@ jf_status_t jf_unmap_host(void* host_ptr);
 typedef struct jf_decode_args {
   int32_t mode;          /* JF_MODE_*                                              */
   int32_t q_dtype;       /* JF_DTYPE_* of q                                        */
-  int32_t B, H_q, H_kv;  /* H_q / H_kv in {1,2,4,8}                                */
+  int32_t B, H_q, H_kv;  /* H_q / H_kv in 1..8 or 16                               */
   int32_t max_S;         /* positions [0, min(seq_lens[b], max_S)) are attended    */
   int32_t block_size;    /* must be 16                                             */
   int32_t top_k;         /* 1..JF_MAX_TOP_K                                        */

@@ -51,7 +51,8 @@ def _decode_unsupported(*, impl, layer, query, attn_metadata, cfg: JetFireConfig
         return "layer_config_missing"
     if int(query.shape[-1]) != store.head_dim:
         return "head_dim_mismatch"
-    if int(layer.num_heads) % int(layer.num_kv_heads) != 0 or int(layer.num_heads) // int(layer.num_kv_heads) > 8:
+    ratio = int(layer.num_heads) // max(int(layer.num_kv_heads), 1)
+    if int(layer.num_heads) % int(layer.num_kv_heads) != 0 or (ratio > 8 and ratio != 16):
         return "gqa_ratio"
     return None
 

@@ -18,6 +18,17 @@ __host__ __device__ inline ModeInfo mode_info(int mode) {
   return ModeInfo{3, 2, 64, 2, 48, 32};
 }
 
+// The scan puts the query heads of one KV head on the eight columns of an MMA.  A GQA group of
+// 16 (the reference's limit, jetfire_vllm/adapter/release_policy.py:31-34) is handled as two
+// "virtual" KV heads of eight query heads each that read the same cache rows: every kernel sees
+// H_kv << shift heads of G >> shift query heads and indexes the cache with (head >> shift).
+struct HeadGeom { int H_kv, G, shift; };
+__host__ __device__ inline HeadGeom head_geom(int H_q, int H_kv) {
+  const int G = H_q / H_kv;
+  const int shift = (G > kHeadsPad) ? 1 : 0;
+  return HeadGeom{H_kv << shift, G >> shift, shift};
+}
+
 // Resident scan CTAs per SM (set by registers / shared memory of the kernel variant).
 __host__ __device__ inline int scan_ctas_per_sm(int mode, int q_dtype) {
   return (mode == JF_MODE_K3V2 && q_dtype == JF_DTYPE_FP16) ? 3 : 4;
@@ -52,8 +63,9 @@ __host__ __device__ inline uint64_t align_up(uint64_t x, uint64_t a) { return (x
 
 // Sized for the variant with the most splits (bf16 query), so one workspace serves both dtypes.
 inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv, int max_S, int /*top_k*/, bool need_scores) {
-  const uint64_t splits = scan_splits(mode, JF_DTYPE_BF16, B, H_kv, max_S);
-  const uint64_t pairs = static_cast<uint64_t>(B) * H_kv * splits;
+  const HeadGeom hg = head_geom(H_q, H_kv);
+  const uint64_t splits = scan_splits(mode, JF_DTYPE_BF16, B, hg.H_kv, max_S);
+  const uint64_t pairs = static_cast<uint64_t>(B) * hg.H_kv * splits;
   uint64_t off = 0;
   uint8_t* p = static_cast<uint8_t*>(base);
   Workspace w{};

@@ -320,7 +320,7 @@ scan_k3v2_kernel(const ScanParams p) {
   // The packed cache is read once per call: fetched as first-to-evict, it leaves the scores
   // this kernel writes (and the next kernel reads) in L2.
   const uint64_t stream_policy = l2_policy_evict_first();
-  const int64_t head_rows = static_cast<int64_t>(hkv) * p.num_slots;
+  const int64_t head_rows = static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots;
   const uint8_t* ks_b = reinterpret_cast<const uint8_t*>(p.k_scales);
   const uint8_t* vs_b = reinterpret_cast<const uint8_t*>(p.v_scales);
   const int last_pg = (len & 15) ? (n_pages - 1) : -1;   // the only page that can be partial
@@ -502,7 +502,7 @@ jf_status_t validate_decode_args(const jf_decode_args* a) {
   if (a->B <= 0 || a->H_q <= 0 || a->H_kv <= 0 || a->max_S <= 0) return JF_ERR_ARG;
   if (a->H_q % a->H_kv != 0) return JF_ERR_ARG;
   const int G = a->H_q / a->H_kv;
-  if (G > JF_MAX_GROUP) return JF_ERR_UNSUPPORTED;
+  if (G > kHeadsPad && G != JF_MAX_GROUP) return JF_ERR_UNSUPPORTED;   // 1..8, or 16 as two halves
   if (a->block_size != JF_BLOCK_SIZE) return JF_ERR_UNSUPPORTED;
   if (a->max_S > 262144) return JF_ERR_UNSUPPORTED;
   if (a->top_k < 1 || a->top_k > JF_MAX_TOP_K) return JF_ERR_UNSUPPORTED;
@@ -567,15 +567,16 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.part_o = ws.part_o; sp.part_m = ws.part_m; sp.part_l = ws.part_l; sp.part_smax = ws.part_smax;
   sp.status = ws.status;
   sp.num_slots = a->num_slots;
-  sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = a->H_kv; sp.G = a->H_q / a->H_kv;
+  const HeadGeom hg = head_geom(a->H_q, a->H_kv);
+  sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = hg.H_kv; sp.G = hg.G; sp.kv_shift = hg.shift;
   sp.max_S = a->max_S; sp.max_blocks = a->max_blocks;
-  sp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
+  sp.splits = scan_splits(a->mode, a->q_dtype, a->B, hg.H_kv, a->max_S);
   const int pages = (a->max_S + 15) / 16;
   sp.pages_per_split = (pages + sp.splits - 1) / sp.splits;
   sp.pages_per_warp = (sp.pages_per_split + kScanWarps - 1) / kScanWarps;
   sp.attn_scale = a->attn_scale;
   sp.q_dtype = a->q_dtype;
-  dim3 grid(sp.splits, a->H_kv, a->B);
+  dim3 grid(sp.splits, hg.H_kv, a->B);
   if (a->mode == JF_MODE_K3V2) {
     // the query's type only matters where the query is read
     const int dt = a->scan_parts == JF_SCAN_V_ONLY ? JF_DTYPE_BF16 : a->q_dtype;

@@ -52,6 +52,7 @@ struct ScanParams {
   int pages_per_warp;   // a warp's contiguous share of a split: ceil(pages_per_split / kScanWarps)
   float attn_scale;
   int q_dtype;
+  int kv_shift;         // cache head = KV head >> kv_shift (see head_geom)
   // K4V4: work is cut into two-page tiles (see scan_k4v4_kernel)
   int n_tiles, tiles_per_split, tiles_per_warp, ref_chunk;
   int tile_base[9];

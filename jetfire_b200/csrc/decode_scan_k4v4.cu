@@ -356,7 +356,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int64_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
   const int len = min(p.seq_lens[b], p.max_S);
   const int64_t n_blocks_phys = p.num_slots >> 4;
-  const int head_row0 = static_cast<int>(static_cast<int64_t>(hkv) * p.num_slots);  // first cache row of this KV head
+  const int head_row0 = static_cast<int>(static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots);  // first cache row of this KV head
 
   // Tile T of the warp (tile t_first + T of the row): its first page and the token ranges of its
   // pages, packed as lo_A | hi_A << 5 | lo_B << 10 | hi_B << 15 | pages << 20; 0 = no such tile
@@ -678,7 +678,7 @@ jf_status_t launch_variant(const ScanParams& sp, dim3 grid, cudaStream_t stream,
 
 // `sp` arrives with everything but the tile geometry filled in.
 jf_status_t launch_scan_k4v4(ScanParams sp, bool int8p, int parts, dim3 grid, cudaStream_t stream) {
-  const uint64_t rows = static_cast<uint64_t>(sp.H_kv) * static_cast<uint64_t>(sp.num_slots);
+  const uint64_t rows = static_cast<uint64_t>(sp.H_kv >> sp.kv_shift) * static_cast<uint64_t>(sp.num_slots);
   if (rows > 0x7FFFFFFFull) return JF_ERR_UNSUPPORTED;
   // tiles of the longest row this call can see (the kernel drops those past a row's own length)
   if (int8p && parts != 1) {

@@ -35,6 +35,7 @@ struct TailParams {
   float* softmax_inv_z;
   int64_t num_slots;
   int H_q, H_kv, G, max_S, splits, top_k;
+  int kv_shift;   // cache head = KV head >> kv_shift (see head_geom)
 };
 
 template <int MODE>
@@ -125,8 +126,8 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
 
   // ---- selected set: weights from the scan's scores ----
   const ModeInfo mi = mode_info(MODE);
-  const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
-  const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+  const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.v_row;
+  const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
   const float* srow = p.scores + bh * p.max_S;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float wsum = 0.f;

@@ -38,6 +38,7 @@ struct TopkParams {
   int32_t* status;
   int64_t num_slots;
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
+  int kv_shift;   // cache head = KV head >> kv_shift (see head_geom)
   float attn_scale;
 };
 
@@ -333,8 +334,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   RowCtx ctx;
   ctx.q = sm.q; ctx.qi = sm.qi; ctx.qs = sm.qs;
   const ModeInfo mi = mode_info(MODE);
-  ctx.k_rows = p.k_data + static_cast<int64_t>(hkv) * p.num_slots * mi.k_row;
-  ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+  ctx.k_rows = p.k_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.k_row;
+  ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
   ctx.bt = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
   ctx.num_slots = p.num_slots;
   ctx.attn = p.attn_scale;
@@ -602,8 +603,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           constexpr int kUnroll = 8 * kRowChunk / kSelThreads;
           constexpr int kKParts = (MODE == JF_MODE_K3V2) ? 3 : 4, kVParts = (MODE == JF_MODE_K3V2) ? 2 : 4;
           constexpr int VW = TailSmem<MODE>::VW;
-          const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
-          const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+          const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.v_row;
+          const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
           uint4 v[kUnroll];
           uint32_t sc16[kUnroll];
 #pragma unroll
@@ -942,8 +943,8 @@ topk_select_wide_kernel(const TopkParams p, const TailParams tp) {
   RowCtx ctx;
   ctx.q = sm.q; ctx.qi = sm.qi; ctx.qs = sm.qs;
   const ModeInfo mi = mode_info(MODE);
-  ctx.k_rows = p.k_data + static_cast<int64_t>(hkv) * p.num_slots * mi.k_row;
-  ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+  ctx.k_rows = p.k_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.k_row;
+  ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
   ctx.bt = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
   ctx.num_slots = p.num_slots;
   ctx.attn = p.attn_scale;
@@ -1347,8 +1348,8 @@ topk_select_wide_kernel(const TopkParams p, const TailParams tp) {
       tail.o[vg][d] = o;
       if (d == 0) tail.z[vg] = Z;
     }
-    const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv) * p.num_slots * mi.v_row;
-    const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv) * p.num_slots * mi.ng;
+    const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.v_row;
+    const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
     float acc[4][4];
     float wsum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -1479,9 +1480,10 @@ TailParams make_tail_params(const jf_decode_args* a, const Workspace& ws) {
   tp.o_hat = a->o_hat; tp.o_old = a->o_old_unnorm; tp.W = a->W;
   tp.softmax_m = a->softmax_m; tp.softmax_inv_z = a->softmax_inv_z;
   tp.num_slots = a->num_slots;
-  tp.H_q = a->H_q; tp.H_kv = a->H_kv; tp.G = a->H_q / a->H_kv;
+  const HeadGeom hg = head_geom(a->H_q, a->H_kv);
+  tp.H_q = a->H_q; tp.H_kv = hg.H_kv; tp.G = hg.G; tp.kv_shift = hg.shift;
   tp.max_S = a->max_S;
-  tp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
+  tp.splits = scan_splits(a->mode, a->q_dtype, a->B, hg.H_kv, a->max_S);
   tp.top_k = a->top_k;
   return tp;
 }
@@ -1500,9 +1502,10 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   sp.block_table = a->block_table; sp.seq_lens = a->seq_lens;
   sp.topk_idx = a->topk_idx; sp.topk_slots = a->topk_slots; sp.status = ws.status;
   sp.num_slots = a->num_slots;
-  sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = a->H_kv; sp.G = a->H_q / a->H_kv;
+  const HeadGeom hg = head_geom(a->H_q, a->H_kv);
+  sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = hg.H_kv; sp.G = hg.G; sp.kv_shift = hg.shift;
   sp.max_S = a->max_S; sp.max_blocks = a->max_blocks;
-  sp.splits = scan_splits(a->mode, a->q_dtype, a->B, a->H_kv, a->max_S);
+  sp.splits = scan_splits(a->mode, a->q_dtype, a->B, hg.H_kv, a->max_S);
   sp.top_k = a->top_k;
   sp.sort_n = pow2_ceil(2 * a->top_k);
   if (sp.sort_n < 512) sp.sort_n = 512;

@@ -85,4 +85,8 @@ def test_decode_gate_reasons():
     md.use_cascade = False
     assert _decode_unsupported(attn_metadata=md, **{**args, "store": None}) == "layer_config_missing"
     layer16 = SimpleNamespace(layer_name="l0", num_heads=32, num_kv_heads=2, head_size=128)
-    assert _decode_unsupported(attn_metadata=md, **{**args, "layer": layer16}) == "gqa_ratio"
+    assert _decode_unsupported(attn_metadata=md, **{**args, "layer": layer16}) is None      # ratio 16: two halves of 8
+    layer12 = SimpleNamespace(layer_name="l0", num_heads=24, num_kv_heads=2, head_size=128)
+    assert _decode_unsupported(attn_metadata=md, **{**args, "layer": layer12}) == "gqa_ratio"
+    layer32 = SimpleNamespace(layer_name="l0", num_heads=64, num_kv_heads=2, head_size=128)
+    assert _decode_unsupported(attn_metadata=md, **{**args, "layer": layer32}) == "gqa_ratio"

@@ -148,6 +148,14 @@ def test_k4v4_int8p_matches_the_reference_batched_arithmetic(B, H_q, H_kv, ctx, 
     assert d8 < d32 or d32 < 1e-4
 
 
+@pytest.mark.parametrize("mode,stage_b", [("k3v2", "fp32"), ("k4v4", "fp32"), ("k4v4", "int8p")])
+def test_gqa_group_of_sixteen(mode, stage_b):
+    """The reference's largest GQA ratio (adapter/release_policy.py:31-34, csrc/int3_qk_scores.cu:621-629):
+    16 query heads per KV head, handled as two halves of eight that read the same cache rows."""
+    check_case(Case(mode, 2, 32, 2, 1536, lens=[1536, 1000], seed=47), 128, stage_b=stage_b)
+    check_case(Case(mode, 1, 16, 1, 300, seed=48), 32, stage_b=stage_b)
+
+
 def test_k4v4_short_and_ragged():
     case = Case("k4v4", 4, 8, 2, 512, lens=[0, 1, 17, 512], seed=35)
     check_case(case, 32)
