@@ -819,643 +819,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   }
 }
 
-// ------------------------------------------------------------------------------------------
-// The same selection and finish stage for calls with MORE ROWS THAN MULTIPROCESSORS.
-//
-// The kernel above gives a row a whole multiprocessor (1024 threads, the row's scores staged
-// in shared memory): the shortest path for one row, but its phases are chains of barriers that
-// keep a multiprocessor a third busy, and with more rows than multiprocessors they queue up.
-// Here a row gets 256 threads and ~56 KB of shared memory, three or four rows share a
-// multiprocessor and hide one another's waits, and the scores are read where the scan left
-// them (second-level cache) instead of being staged: two passes in the common case (group
-// maxima for a bound, then the candidates), three more in the exact radix tier.
-//
-// Results are the same bits: the selection is exact either way, and the finish stage adds in
-// the order of the kernel above -- its 8 split groups and 32 warps are walked as "virtual"
-// groups and warps by the 2 x 128 threads and 8 warps here.
-// ------------------------------------------------------------------------------------------
-constexpr int kWT = 256;
-constexpr int kWW = kWT / 32;
-constexpr int kWRows = 512;                  // K3V2 candidates re-scored per round
-constexpr int kWGather = 4 * kWRows / kWT;   // 16-byte (or scale) loads per thread and round
-
-struct alignas(16) WideFixed {
-  int hist[kBins];
-  float q[JF_HEAD_DIM];
-  float qs[4];
-  int8_t qi[JF_HEAD_DIM];
-  float w3[kWW][3];
-  float red[4];
-  int wsum[kWW];
-  unsigned long long prefix;
-  int ncand, tbin, remaining, pad_;
-};
-
-template <int MODE>
-struct alignas(16) WideTail {
-  static constexpr int VW = TailSmem<MODE>::VW;
-  uint32_t v[kTailChunk * VW];
-  int64_t slot[kTailChunk];
-  float wv[kTailChunk][2];
-  float w[kTailChunk];
-  float red[kSelWarps][JF_HEAD_DIM];     // one row per warp of the one-row-per-multiprocessor kernel
-  float sum[kSelWarps];
-  float o[kSplitGroups][JF_HEAD_DIM];    // one row per split group of that kernel
-  float z[kSplitGroups];
-};
-
-template <int MODE>
-__host__ __device__ constexpr size_t wide_smem_bytes(int sort_n) {
-  // fixed | keys | cand_slot | cand_score | perm | bucket | max(packed K rows of a round, finish buffers)
-  return sizeof(WideFixed) + static_cast<size_t>(sort_n) * (8 + 8 + 4 + 2 + 2) +
-         (sizeof(WideTail<MODE>) > static_cast<size_t>(kWRows) * 52 ? sizeof(WideTail<MODE>) : static_cast<size_t>(kWRows) * 52);
-}
-
-template <int MODE, int DT>
-__global__ void __launch_bounds__(kWT, 3)
-topk_select_wide_kernel(const TopkParams p, const TailParams tp) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  WideFixed& sm = *reinterpret_cast<WideFixed*>(smem_raw);
-  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw + sizeof(WideFixed));
-  int64_t* cand_slot = reinterpret_cast<int64_t*>(keys + p.sort_n);
-  float* cand_score = reinterpret_cast<float*>(cand_slot + p.sort_n);
-  uint16_t* perm = reinterpret_cast<uint16_t*>(cand_score + p.sort_n);
-  uint16_t* bucket = perm + p.sort_n;
-  uint8_t* uni = reinterpret_cast<uint8_t*>(bucket + p.sort_n);
-  uint32_t* rows = reinterpret_cast<uint32_t*>(uni);
-  WideTail<MODE>& tail = *reinterpret_cast<WideTail<MODE>*>(uni);
-  int* hist = sm.hist;
-
-  const int h = blockIdx.x, b = blockIdx.y;
-  const int hkv = h / p.G, hi = h - hkv * p.G;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int K = p.top_k;
-  const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
-  const float* srow = p.scores + bh * p.max_S;
-  const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
-
-  // What the scan itself read (the query, the sequence lengths) was complete before the scan
-  // started: the query model and the zeroing run while the scan's last CTAs finish.
-  uint16_t q_bits = 0;
-  if (tid < JF_HEAD_DIM) q_bits = reinterpret_cast<const uint16_t*>(p.q)[bh * JF_HEAD_DIM + tid];
-  const int n = max(0, min(p.seq_lens[b], p.max_S));
-  int64_t* out_idx = p.topk_idx + bh * K;
-  int64_t* out_slot = p.topk_slots + bh * K;
-  if (tid < JF_HEAD_DIM) sm.q[tid] = Elem<DT>::to_f32(q_bits);
-  __syncthreads();
-  if (warp < 4) {  // warp w handles channels 32w..32w+31
-    const float v = sm.q[32 * warp + lane];
-    float a = fabsf(v), s1 = fabsf(v) + 0.001953125f;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-      s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, o);
-    }
-    if (MODE == JF_MODE_K4V4) {
-      const float qs = fmaxf(__fdiv_rn(a, 127.0f), 1e-12f);
-      const float inv = __fdiv_rn(1.0f, qs);
-      const int qv = max(-128, min(127, __float2int_rn(__fmul_rn(v, inv))));
-      sm.qi[32 * warp + lane] = static_cast<int8_t>(qv);
-      if (lane == 0) sm.qs[warp] = qs;
-    }
-    if (lane == 0) sm.red[warp] = s1;
-  }
-  if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
-  for (int i = tid; i < kBins; i += kWT) hist[i] = 0;
-  for (int i = tid; i < p.sort_n; i += kWT) keys[i] = 0ull;
-
-  pdl_wait();
-  float top = kMinusBig, sm0 = 0.f, sm1 = 0.f;
-  for (int s = tid; s < p.splits; s += kWT) {
-    top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
-    sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
-    sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
-    sm0 = fmaxf(sm0, __shfl_xor_sync(0xFFFFFFFFu, sm0, o));
-    sm1 = fmaxf(sm1, __shfl_xor_sync(0xFFFFFFFFu, sm1, o));
-  }
-  if (lane == 0) { sm.w3[warp][0] = top; sm.w3[warp][1] = sm0; sm.w3[warp][2] = sm1; }
-  __syncthreads();
-
-  RowCtx ctx;
-  ctx.q = sm.q; ctx.qi = sm.qi; ctx.qs = sm.qs;
-  const ModeInfo mi = mode_info(MODE);
-  ctx.k_rows = p.k_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.k_row;
-  ctx.k_sc = p.k_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
-  ctx.bt = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
-  ctx.num_slots = p.num_slots;
-  ctx.attn = p.attn_scale;
-
-  float row_max = kMinusBig;  // max over the splits of the scan's reference points
-  sm0 = 0.f; sm1 = 0.f;
-#pragma unroll
-  for (int w = 0; w < kWW; ++w) {
-    row_max = fmaxf(row_max, sm.w3[w][0]);
-    sm0 = fmaxf(sm0, sm.w3[w][1]);
-    sm1 = fmaxf(sm1, sm.w3[w][2]);
-  }
-
-  // Scores straight from memory, four positions at a time; positions at or past the length read
-  // as -inf.  (Rows start on 16-byte boundaries when max_S is a multiple of four.)
-  const bool vec = ((p.max_S & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.scores) & 15) == 0);
-  const int n4 = (n + 3) >> 2;
-  auto load4 = [&](int i4) -> float4 {
-    float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    if (i4 >= n4) return v;
-    const int pos = 4 * i4;
-    if (vec) {
-      v = __ldg(reinterpret_cast<const float4*>(srow) + i4);
-    } else {
-      v.x = srow[pos];
-      if (pos + 1 < n) v.y = srow[pos + 1];
-      if (pos + 2 < n) v.z = srow[pos + 2];
-      if (pos + 3 < n) v.w = srow[pos + 3];
-    }
-    if (pos + 1 >= n) v.y = -INFINITY;
-    if (pos + 2 >= n) v.z = -INFINITY;
-    if (pos + 3 >= n) v.w = -INFINITY;
-    return v;
-  };
-
-  // Block-wide: hist[] becomes inclusive counts from the top bin down; sm.tbin = the bin where the
-  // count reaches `want` (-1: never).  Thread t owns bins 8t .. 8t + 7.
-  auto scan_hist = [&](int want) {
-    int hb[8], v = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { hb[i] = hist[8 * tid + i]; v += hb[i]; }
-    int incl = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    if (lane == 31) sm.wsum[warp] = incl;
-    __syncthreads();
-    int before = incl - v;
-#pragma unroll
-    for (int w = 0; w < kWW; ++w) before += (w < warp) ? sm.wsum[w] : 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int after = before + hb[i];
-      hist[8 * tid + i] = after;
-      if (before < want && after >= want) sm.tbin = 8 * tid + i;
-      before = after;
-    }
-    __syncthreads();
-  };
-  // Block-wide: positions whose score is above (kind 0) or at or above (kind 1) `thr` go to
-  // keys[] / cand_score[] in any order (the ranking orders them by the full key); returns how
-  // many there are (more than sort_n: the lists are partial).
-  auto collect = [&](float thr, int kind) {
-    for (int base = 0; base < n4; base += 2 * kWT) {
-      const float4 va = load4(base + tid), vb = load4(base + kWT + tid);
-      const float e[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        if (kind == 0 ? (e[c] > thr) : (e[c] >= thr)) {
-          const int at = atomicAdd(&sm.ncand, 1);
-          if (at < p.sort_n) {
-            keys[at] = static_cast<uint64_t>(4 * (base + (c >> 2) * kWT + tid) + (c & 3));
-            cand_score[at] = e[c];
-          }
-        }
-      }
-    }
-    __syncthreads();
-    return sm.ncand;
-  };
-
-  int m_sel = 0;
-  if (n > 0) {
-    int ncand = 0;
-    int cand_last = kBins;
-    bool slow = false;
-    if (n <= p.sort_n) {
-      for (int i = tid; i < n; i += kWT) { keys[i] = static_cast<uint64_t>(i); cand_score[i] = srow[i]; }
-      ncand = n;
-    } else {
-      const float top_b = row_max + 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
-      const float top64 = top_b * kBinsPerUnit;
-      float delta = 0.f;
-      if (MODE == JF_MODE_K3V2) {   // the same bound as in the kernel above
-        const float q1a = sm.red[0] + sm.red[1], q1b = sm.red[2] + sm.red[3];
-        const float mag = fabsf(p.attn_scale) * (sm0 * q1a + sm1 * q1b) * 3.0f;
-        delta = mag * (32.0f / 16777216.0f) + mag * (4.0f / 16777216.0f) + 1e-7f;
-      }
-      float nbf = ceilf(2.0f * delta * kBinsPerUnit) + 1.0f;
-      if (!(nbf < 4096.0f)) nbf = 4096.0f;
-      const int nb = (MODE == JF_MODE_K3V2) ? static_cast<int>(nbf) : 0;
-      bool ok = false;
-      if (n > 16 * K) {
-        // ---- tier 1a: the K-th largest maximum of groups of eight positions bounds the K-th
-        //      largest score from below; one shared-memory atomic per group ----
-        for (int base = 0; base < n4; base += 2 * kWT) {
-          const float4 va = load4(base + tid), vb = load4(base + kWT + tid);
-          const float gm = fmaxf(fmaxf(fmaxf(va.x, va.y), fmaxf(va.z, va.w)), fmaxf(fmaxf(vb.x, vb.y), fmaxf(vb.z, vb.w)));
-          if (gm > -INFINITY) atomicAdd(&hist[score_bin(top64, gm)], 1);
-        }
-        __syncthreads();
-        scan_hist(K);
-        const int tbin = sm.tbin;
-        const int last = tbin + nb;
-        if (tbin >= 0 && last < kBins - 1) {
-          const float xlim = static_cast<float>(last + 1);
-          const float thr = (top64 - xlim) * (1.0f / kBinsPerUnit) - (fabsf(top64) + xlim) * (1.0f / (kBinsPerUnit * 2097152.0f)) - 1e-30f;
-          const int total = collect(thr, 0);
-          ok = total <= p.sort_n;
-          ncand = total;
-          cand_last = last + nb;
-        }
-      }
-      if (!ok) {
-        // ---- tier 1b: the K-th largest approximate score exactly, by a radix select over the
-        //      order-preserving keys (11 + 11 + 10 bits, one pass over the row each) ----
-        uint32_t prefix = 0u;
-        int want = K;
-        for (int level = 0; level < 3; ++level) {
-          const int bits = (level == 2) ? 10 : 11, shift = (level == 0) ? 21 : (level == 1) ? 10 : 0;
-          const uint32_t dmask = (1u << bits) - 1u;
-          __syncthreads();
-          if (tid == 0) sm.tbin = -1;
-          for (int i = tid; i < kBins; i += kWT) hist[i] = 0;
-          __syncthreads();
-          for (int base = 0; base < n4; base += 2 * kWT) {
-            const float4 va = load4(base + tid), vb = load4(base + kWT + tid);
-            const float e[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              if (e[c] > -INFINITY) {
-                const uint32_t key = float_order_key(e[c]);
-                if (level == 0 || (key >> (shift + bits)) == prefix)
-                  atomicAdd(&hist[kBins - 1 - static_cast<int>((key >> shift) & dmask)], 1);
-              }
-            }
-          }
-          __syncthreads();
-          scan_hist(want);
-          const int tb = max(sm.tbin, 0);
-          want -= (tb > 0) ? hist[tb - 1] : 0;
-          prefix = (prefix << bits) | static_cast<uint32_t>(kBins - 1 - tb);
-        }
-        const float kth = float_from_order_key(prefix);
-        __syncthreads();
-        if (tid == 0) sm.ncand = 0;
-        for (int i = tid; i < p.sort_n; i += kWT) keys[i] = 0ull;
-        __syncthreads();
-        if (MODE == JF_MODE_K4V4) {
-          // everything above the K-th, then the lowest positions among those equal to it: one warp
-          // walks the row in position order until the list is full
-          const int n_gt = collect(kth, 0);
-          if (warp == 0) {
-            int have = n_gt;
-            for (int i0 = 0; i0 < n4 && have < K; i0 += 32) {
-              const float4 v = load4(i0 + lane);
-              const float e[4] = {v.x, v.y, v.z, v.w};
-              int cnt = 0;
-#pragma unroll
-              for (int c = 0; c < 4; ++c) cnt += (e[c] == kth) ? 1 : 0;
-              int incl = cnt;
-#pragma unroll
-              for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += t;
-              }
-              int at = have + incl - cnt;
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                if (e[c] == kth) {
-                  if (at < K) { keys[at] = static_cast<uint64_t>(4 * (i0 + lane) + c); cand_score[at] = kth; }
-                  ++at;
-                }
-              }
-              have += __shfl_sync(0xFFFFFFFFu, incl, 31);
-            }
-          }
-          __syncthreads();
-          ncand = K;
-        } else {
-          const int total = collect(kth - 2.0f * delta - 1e-30f, 1);
-          if (total > p.sort_n) slow = true;   // more scores inside the band than the sort buffer holds: massive ties
-          ncand = min(total, p.sort_n);
-        }
-        cand_last = kBins;
-      }
-    }
-    __syncthreads();
-
-    if (!slow) {
-      // ---- slots, then (K3V2) the candidates' packed K rows and their canonical scores ----
-      for (int i = tid; i < ncand; i += kWT) cand_slot[i] = slot_of(ctx, static_cast<int>(keys[i]));
-      __syncthreads();
-      if (MODE == JF_MODE_K4V4) {
-        // the scan's score is the canonical one bit for bit
-        for (int i = tid; i < ncand; i += kWT)
-          keys[i] = make_key(cand_slot[i] >= 0 ? cand_score[i] : -INFINITY, static_cast<int>(keys[i]));
-      } else {
-        float qv[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) qv[i] = sm.q[32 * (i >> 2) + 8 * (i & 3) + (lane & 7)];
-        for (int base = 0; base < ncand; base += kWRows) {
-          const int cn = min(kWRows, ncand - base);
-          // unit u = (candidate, part): parts 0-2 the 48 packed bytes, part 3 the two group scales
-          uint4 v[kWGather];
-#pragma unroll
-          for (int i = 0; i < kWGather; ++i) {
-            const int u = tid + i * kWT;
-            const int c = u >> 2, part = u & 3;
-            v[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (c < cn) {
-              const int64_t slot = cand_slot[base + c];
-              if (slot >= 0) {
-                if (part < 3) v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * 48) + part);
-                else v[i].x = __ldg(reinterpret_cast<const uint32_t*>(ctx.k_sc + slot * 2));
-              }
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < kWGather; ++i) {
-            const int u = tid + i * kWT;
-            const int c = u >> 2, part = u & 3;
-            if (c < cn) {
-              uint32_t* r = rows + c * 13;
-              if (part < 3) { r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w; }
-              else r[12] = v[i].x;
-            }
-          }
-          __syncthreads();
-          for (int c0 = 4 * warp; c0 < cn; c0 += 4 * kWW) {
-            const int c = c0 + (lane >> 3);
-            const int cc = min(c, cn - 1);           // lanes past the end keep the shuffles company
-            const float s = canon_score_k3_x8(qv, rows + cc * 13, ctx.attn, lane);
-            if (c < cn && (lane & 7) == 0)
-              keys[base + c] = make_key(cand_slot[base + c] >= 0 ? s : -INFINITY, static_cast<int>(keys[base + c]));
-          }
-          __syncthreads();
-        }
-      }
-    } else {
-      // ---- slow exact path (massive ties inside the band): 8-level radix select on the 64-bit
-      //      canonical key computed on the fly ----
-      if (tid == 0) { sm.prefix = 0ull; sm.remaining = K; sm.ncand = 0; }
-      __syncthreads();
-      for (int level = 7; level >= 0; --level) {
-        for (int i = tid; i < 256; i += kWT) hist[i] = 0;
-        __syncthreads();
-        const unsigned long long prefix = sm.prefix;
-        for (int i = warp; i < n; i += kWW) {
-          const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
-          const bool match = (level == 7) || ((key >> (8 * (level + 1))) == prefix);
-          if (match && lane == 0) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
-        }
-        __syncthreads();
-        if (tid == 0) {
-          int cum = 0, rem = sm.remaining, cb = 0;
-          for (int bin = 255; bin >= 0; --bin) {
-            if (cum + hist[bin] >= rem) { cb = bin; break; }
-            cum += hist[bin];
-          }
-          sm.remaining = rem - cum;
-          sm.prefix = (prefix << 8) | static_cast<unsigned long long>(cb);
-        }
-        __syncthreads();
-      }
-      const unsigned long long tkey = sm.prefix;
-      for (int i = tid; i < p.sort_n; i += kWT) keys[i] = 0ull;
-      __syncthreads();
-      for (int i = warp; i < n; i += kWW) {
-        const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
-        if (key >= tkey && lane == 0) {
-          const int pos = atomicAdd(&sm.ncand, 1);
-          if (pos < p.sort_n) keys[pos] = key;
-        }
-      }
-      __syncthreads();
-      ncand = min(sm.ncand, p.sort_n);
-      for (int i = tid; i < ncand; i += kWT) {
-        const int pos = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(keys[i] & 0xFFFFFFFFull));
-        cand_slot[i] = slot_of(ctx, pos);
-        cand_score[i] = srow[pos];
-      }
-    }
-    __syncthreads();
-
-    // ---- order the candidates, best first: rank by buckets as in the kernel above (a candidate's
-    //      rank = candidates in finer score bins above its own + larger keys inside its bin) ----
-    {
-      int f = 1;
-      while (f < 16 && (cand_last + 2) * f * 2 <= kBins) f *= 2;
-      const float fscale = kBinsPerUnit * static_cast<float>(f);
-      const float ftop = (row_max + 4.0f) * fscale;
-      for (int i = tid; i < kBins; i += kWT) hist[i] = 0;
-      __syncthreads();
-      constexpr int kPer = 4;   // sort_n <= 4 * kWT
-      unsigned long long mine[kPer];
-      int fb[kPer], arrival[kPer];
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) {
-        const int i = tid + j * kWT;
-        mine[j] = 0ull; fb[j] = 0; arrival[j] = 0;
-        if (i < ncand) {
-          mine[j] = keys[i];
-          const float sc = float_from_order_key(static_cast<uint32_t>(mine[j] >> 32));
-          const float x = fminf(fmaxf(fmaf(sc, -fscale, ftop), 0.0f), static_cast<float>(kBins - 1));
-          fb[j] = __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
-          arrival[j] = atomicAdd(&hist[fb[j]], 1);
-        }
-      }
-      __syncthreads();
-      {
-        // exclusive prefix over the bins, eight per thread, written back in place
-        int hb[8], v = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { hb[i] = hist[8 * tid + i]; v += hb[i]; }
-        int incl = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-          if (lane >= o) incl += t;
-        }
-        if (lane == 31) sm.wsum[warp] = incl;
-        __syncthreads();
-        int before = incl - v;
-#pragma unroll
-        for (int w = 0; w < kWW; ++w) before += (w < warp) ? sm.wsum[w] : 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { hist[8 * tid + i] = before; before += hb[i]; }
-      }
-      __syncthreads();
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) {
-        const int i = tid + j * kWT;
-        if (i < ncand) bucket[hist[fb[j]] + arrival[j]] = static_cast<uint16_t>(i);
-      }
-      __syncthreads();
-      int rk[kPer];
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) {
-        const int i = tid + j * kWT;
-        rk[j] = 0;
-        if (i < ncand) {
-          const int lo = hist[fb[j]], hi2 = (fb[j] == kBins - 1) ? ncand : hist[fb[j] + 1];
-          int above = 0;
-          for (int m = lo; m < hi2; ++m) above += (keys[bucket[m]] > mine[j]) ? 1 : 0;
-          rk[j] = min(lo + above, ncand - 1);
-        }
-      }
-      __syncthreads();
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) {
-        const int i = tid + j * kWT;
-        if (i < ncand) { keys[rk[j]] = mine[j]; perm[rk[j]] = static_cast<uint16_t>(i); }
-      }
-      __syncthreads();
-    }
-    m_sel = min(ncand, K);
-  }
-
-  pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
-  for (int r = tid; r < K; r += kWT) {
-    int64_t idx = -1, slot = -1;
-    if (r < m_sel) {
-      idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
-      slot = cand_slot[perm[r]];
-    }
-    out_idx[r] = idx;
-    out_slot[r] = slot;
-  }
-  __syncthreads();   // the finish buffers reuse the packed-row area
-
-  // ---- finish: merge the splits; W and o_old_unnorm of the selected set.  Every sum runs in the
-  //      order of finish_tail (finish_tail.cuh): thread (g2, d) walks split groups g2, g2 + 2,
-  //      g2 + 4, g2 + 6 of that code, warp w its warps w, w + 8, w + 16, w + 24. ----
-  {
-    constexpr int VW = WideTail<MODE>::VW;
-    const float M = row_max;
-    const int d = tid & (JF_HEAD_DIM - 1), g2 = tid >> 7;
-#pragma unroll
-    for (int j = 0; j < kSplitGroups / 2; ++j) {
-      const int vg = g2 + 2 * j;
-      float o = 0.f, Z = 0.f;
-      for (int s = vg; s < p.splits; s += kSplitGroups) {
-        const int64_t e = (pbase + s) * kHeadsPad + hi;
-        const float w = ex2((tp.part_m[e] - M) * kLog2e);
-        Z = fmaf(tp.part_l[e], w, Z);
-        o = fmaf(tp.part_o[e * JF_HEAD_DIM + d], w, o);
-      }
-      tail.o[vg][d] = o;
-      if (d == 0) tail.z[vg] = Z;
-    }
-    const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.v_row;
-    const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
-    float acc[4][4];
-    float wsum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-    const int qg = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
-    for (int k0 = 0; k0 < K; k0 += kTailChunk) {
-      const int kend = min(kTailChunk, K - k0);
-      {
-        int64_t slot = -1;
-        float w = 0.f, vs0 = 0.f, vs1 = 0.f;
-        const int kk = k0 + tid;
-        if (tid < kend && n > 0 && kk < m_sel) {
-          const int ci = perm[kk];
-          slot = cand_slot[ci];
-          if (slot >= 0) {
-            uint32_t sw;
-            if (MODE == JF_MODE_K3V2) sw = __ldg(reinterpret_cast<const uint32_t*>(v_sc + slot * 2));
-            else sw = __ldg(v_sc + slot);
-            w = ex2((cand_score[ci] - M) * kLog2e);
-            if (MODE == JF_MODE_K3V2) {
-              vs0 = __uint_as_float(sw << 16);
-              vs1 = __uint_as_float(sw & 0xFFFF0000u);
-            } else {
-              vs0 = vs1 = __uint_as_float(sw << 16);
-            }
-          }
-        }
-        tail.slot[tid] = slot;
-        tail.w[tid] = w;
-        tail.wv[tid][0] = w * vs0; tail.wv[tid][1] = w * vs1;
-      }
-      __syncthreads();
-      for (int u = tid; u < kend * (VW / 4); u += kWT) {
-        const int c = u / (VW / 4), part = u - c * (VW / 4);
-        const int64_t slot = tail.slot[c];
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (slot >= 0) v = __ldg(reinterpret_cast<const uint4*>(v_rows + slot * (VW * 4)) + part);
-        reinterpret_cast<uint4*>(tail.v)[u] = v;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int vw = warp + kWW * j;
-#pragma unroll
-        for (int i = 0; i < kTailPerWarp; ++i) {
-          const int jx = vw + i * kSelWarps;
-          if (jx >= kend || tail.slot[jx] < 0) continue;  // warp-uniform
-          const uint32_t raw = (MODE == JF_MODE_K3V2) ? static_cast<uint32_t>(reinterpret_cast<const uint8_t*>(tail.v + jx * VW)[lane])
-                                                      : static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(tail.v + jx * VW)[lane]);
-          const float fw = tail.wv[jx][qg];
-          float c[4];
-          if (MODE == JF_MODE_K3V2) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) c[e] = small_code_to_f32((raw >> ((3 - e) * 2)) & 3u, 2.0f);
-          } else {
-            c[0] = small_code_to_f32((raw >> 4) & 15u, 8.0f);
-            c[1] = small_code_to_f32(raw & 15u, 8.0f);
-            c[2] = small_code_to_f32((raw >> 12) & 15u, 8.0f);
-            c[3] = small_code_to_f32((raw >> 8) & 15u, 8.0f);
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[j][e] = fmaf(fw, c[e], acc[j][e]);
-          wsum[j] += tail.w[jx];
-        }
-      }
-      __syncthreads();
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int vw = warp + kWW * j;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) tail.red[vw][4 * lane + e] = acc[j][e];
-      if (lane == 0) tail.sum[vw] = wsum[j];
-    }
-    __syncthreads();
-    if (tid < JF_HEAD_DIM) {
-      float acc_old = 0.f, ws = 0.f, o = 0.f, Z = 0.f;
-#pragma unroll
-      for (int w = 0; w < kSelWarps; ++w) { acc_old += tail.red[w][tid]; ws += tail.sum[w]; }
-#pragma unroll
-      for (int gI = 0; gI < kSplitGroups; ++gI) { o += tail.o[gI][tid]; Z += tail.z[gI]; }
-      const bool live = (Z > 0.f) && (n > 0);
-      const float inv_z = live ? (1.0f / Z) : 0.f;
-      tp.o_hat[bh * JF_HEAD_DIM + tid] = o * inv_z;
-      tp.o_old[bh * JF_HEAD_DIM + tid] = acc_old * inv_z;
-      if (tid == 0) {
-        tp.W[bh] = ws * inv_z;
-        if (tp.softmax_m) tp.softmax_m[bh] = live ? M : 0.f;
-        if (tp.softmax_inv_z) tp.softmax_inv_z[bh] = inv_z;
-      }
-    }
-  }
-}
-
 int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 template <int MODE, int DT>
 jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
-  // more rows than multiprocessors: several rows per multiprocessor (same results, bit for bit)
-  if (fused && sp.sort_n <= 4 * kWT && static_cast<int64_t>(grid.x) * grid.y > num_sms()) {
-    constexpr size_t kMaxWide = wide_smem_bytes<MODE>(4 * kWT);
-    JF_ENSURE_SMEM((topk_select_wide_kernel<MODE, DT>), kMaxWide);
-    JF_CUDA_TRY(launch_pdl(topk_select_wide_kernel<MODE, DT>, grid, dim3(kWT), wide_smem_bytes<MODE>(sp.sort_n), stream, sp, tp));
-    JF_CUDA_TRY(cudaGetLastError());
-    return JF_OK;
-  }
   const size_t smem = sel_smem_bytes(sp.sort_n);
   constexpr size_t kMaxSmem = sel_smem_bytes(2 * JF_MAX_TOP_K);
   static_assert(kMaxSmem <= 227 * 1024, "select kernel shared memory");

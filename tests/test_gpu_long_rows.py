@@ -136,48 +136,3 @@ def test_rows_that_do_not_fit_the_fixed_bins_stay_exact_and_fast(mode, shape):
     t_norm, t_odd = _select_us(normal, 256), _select_us(odd, 256)
     print(f"{mode} {shape}: select {t_odd:.1f} us against {t_norm:.1f} us for an ordinary row")
     assert t_odd <= 10.0 * t_norm
-
-
-@pytest.mark.parametrize("mode,B,H_q,H_kv,ctx,lens,top_k,stage_b,seed", [
-    ("k3v2", 10, 16, 2, 6000, None, 256, "fp32", 80),                    # 160 rows: histogram tier
-    ("k4v4", 10, 16, 2, 6000, None, 256, "int8p", 81),
-    ("k3v2", 20, 8, 2, 3000, [3000] * 17 + [700, 17, 0], 128, "fp32", 82),  # short rows: the radix tier and "every position"
-    ("k4v4", 5, 32, 8, 40000, None, 512, "fp32", 83),                    # wide k, rows longer than 32768
-])
-def test_more_rows_than_multiprocessors_same_bits_as_one_row_per_multiprocessor(mode, B, H_q, H_kv, ctx, lens, top_k,
-                                                                                  stage_b, seed):
-    """With more (sequence, query head) rows than the GPU has multiprocessors the fused step runs its
-    several-rows-per-multiprocessor select+finish kernel.  Selection is exact either way and the finish
-    stage adds in the same order, so the fused call must give the bits of the phase-by-phase API
-    (which always uses the one-row-per-multiprocessor kernels) -- and the oracle's answer."""
-    from jetfire_b200 import ops
-    case = Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed)
-    assert B * H_q > torch.cuda.get_device_properties(0).multi_processor_count
-    res, _ = _run(case, top_k, stage_b=stage_b)
-    kd, ks, vd, vs = case.device_cache()
-    call = ops.DecodeCall(case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
-                          case.ctx, case.H_q, case.H_kv, 16, top_k, case.attn_scale, stage_b=stage_b)
-    call.scan(); call.select(); call.finish(); call.status()
-    step = call.result()
-    for name in ("topk_idx", "topk_slots", "o_hat", "o_old_unnorm", "W", "softmax_m", "softmax_inv_z"):
-        assert torch.equal(getattr(res, name), getattr(step, name)), name
-
-
-@pytest.mark.parametrize("mode", ["k3v2", "k4v4"])
-@pytest.mark.parametrize("shape", ["outlier", "flat", "ties"])
-def test_odd_rows_with_more_rows_than_multiprocessors(mode, shape):
-    """The same odd rows as above (one score far above the rest, scores packed closer than a bin) and
-    massive ties, through the several-rows-per-multiprocessor kernel."""
-    case = Case(mode, 6, 32, 8, 4096, lens=[4096] * 5 + [999], seed=90)
-    if shape == "outlier":
-        for b in range(case.B):
-            for hk in range(case.H_kv):
-                slot = int(case.block_table[b, 777 // 16]) * 16 + 777 % 16
-                case.k_full[hk, slot] = (40.0 * case.q[b, hk * 4].float()).to(case.dtype)
-    elif shape == "flat":
-        case.q = (case.q.float() * 2.0 ** -12).to(case.dtype)
-    else:
-        case.k_full.zero_()
-    res, _ = _run(case, 64)
-    if shape == "ties":
-        assert np.array_equal(res.topk_idx.cpu().numpy()[0, 0], np.arange(64))
