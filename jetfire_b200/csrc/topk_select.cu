@@ -39,6 +39,7 @@ struct TopkParams {
   int64_t num_slots;
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
   int kv_shift;   // cache head = KV head >> kv_shift (see head_geom)
+  int hm_chunks;  // score chunks whose per-float4 maxima fit the shared-memory side table (0: none)
   float attn_scale;
 };
 
@@ -173,7 +174,7 @@ __device__ __forceinline__ int score_bin(float top64, float s) {
   return __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
 }
 
-constexpr int kRowChunk = 512;                 // candidates staged in shared memory per round
+constexpr int kRowChunk = 768;                 // candidates staged in shared memory per round (top-k 512 and its band in one)
 constexpr int kChunkPos = 32768;               // positions of the row held in shared memory at a time
 constexpr int kChunkVec = kChunkPos / (4 * kSelThreads);  // float4 reads per thread and pass
 template <int MODE> struct RowWords { static constexpr int v = (MODE == JF_MODE_K3V2) ? 13 : 17; };
@@ -197,15 +198,17 @@ struct SelSmemLate {
   TailSmem<MODE> tail;
   uint32_t vrows[kRowChunk * TailSmem<MODE>::VW];  // packed V rows of the candidates (fused kernel)
   int64_t cand_slot[kRowChunk];
-  uint32_t rows[kRowChunk * 17];                   // packed K rows + scales
+  uint32_t rows[(MODE == JF_MODE_K3V2) ? kRowChunk * 13 : 4];   // K3V2: packed K rows + scales (K4V4 re-scores nothing)
   uint32_t vsc[kRowChunk];                         // V scales
 };
 
 constexpr size_t kSelChunkBytes = static_cast<size_t>(kChunkPos) * 4;
-__host__ __device__ constexpr size_t sel_smem_bytes(int sort_n) {
-  // chunk | fixed | keys[sort_n] | cand_score[sort_n] | perm[sort_n] | bucket[sort_n]
+constexpr size_t kHmChunkBytes = static_cast<size_t>(kChunkVec) * kSelThreads * 2;   // side table of one chunk
+constexpr size_t kSelSmemLimit = 227 * 1024;
+__host__ __device__ constexpr size_t sel_smem_bytes(int sort_n, int hm_chunks = 0) {
+  // chunk | fixed | keys[sort_n] | cand_score[sort_n] | perm[sort_n] | bucket[sort_n] | hm16[hm_chunks]
   return kSelChunkBytes + sizeof(SelSmemFixed) + static_cast<size_t>(sort_n) * 8 +
-         static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4;
+         static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(hm_chunks) * kHmChunkBytes;
 }
 
 // One CTA per (query head, batch element).  The row's approximate scores are pulled into
@@ -225,6 +228,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   float* cand_score = reinterpret_cast<float*>(keys + p.sort_n);  // [sort_n] scan score per candidate
   uint16_t* perm = reinterpret_cast<uint16_t*>(cand_score + p.sort_n);             // [sort_n] rank -> candidate
   uint16_t* bucket = perm + p.sort_n;                                              // [sort_n] candidates grouped by bin
+  // Rows of several chunks: an upper bound (16 bits of the order-preserving key, rounded up) of the
+  // largest score of every float4 the histogram pass saw, [chunk][j][thread].  The collection then
+  // fetches only the float4s that can hold a candidate instead of streaming the row a second time.
+  uint16_t* hm16 = bucket + p.sort_n;
   int* hist = sm.hist;
 
   const int h = blockIdx.x, b = blockIdx.y;
@@ -424,10 +431,11 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       // block scan, no atomics); entries at or past `cap` are dropped.  Returns how many passed.
       float hm[kChunkVec];  // per float4 of the resident chunk: its largest score (tier 1a's pass)
       bool have_hm = false;
-      auto collect = [&](float thr, int kind, int off0, int cap) {
+      auto collect = [&](float thr, int kind, int off0, int cap, bool use16 = false) {
         int running = 0;  // candidates found in earlier chunks
+        const uint32_t thr16 = float_order_key(thr) >> 16;
         for (int ci = 0; ci < n_chunks; ++ci) {
-          if (n_chunks > 1) next_chunk(ci);
+          if (n_chunks > 1 && !use16) next_chunk(ci);
           uint32_t mask = 0u;
           // which of the thread's float4s can hold a candidate at all (branch-free; most threads
           // find none and skip the loads altogether)
@@ -436,11 +444,26 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             hits = 0u;
 #pragma unroll
             for (int j = 0; j < kChunkVec; ++j) hits |= static_cast<uint32_t>(hm[j] > thr) << j;
+          } else if (use16) {
+            hits = 0u;
+#pragma unroll
+            for (int j = 0; j < kChunkVec; ++j)
+              hits |= static_cast<uint32_t>(hm16[(ci * kChunkVec + j) * kSelThreads + tid] >= thr16) << j;
           }
           while (hits) {
             const int j = __ffs(hits) - 1;
             hits &= hits - 1u;
-            const float4 v = chunk4[j * kSelThreads + tid];
+            float4 v;
+            if (use16) {   // straight from memory; positions at or past the length read as -inf
+              const int pos = ci * kChunkPos + 4 * (j * kSelThreads + tid);
+              v = *reinterpret_cast<const float4*>(srow + pos);
+              if (pos >= n) v.x = -INFINITY;
+              if (pos + 1 >= n) v.y = -INFINITY;
+              if (pos + 2 >= n) v.z = -INFINITY;
+              if (pos + 3 >= n) v.w = -INFINITY;
+            } else {
+              v = chunk4[j * kSelThreads + tid];
+            }
             uint32_t m4;
             if (kind == 0)
               m4 = static_cast<uint32_t>(v.x > thr) | (static_cast<uint32_t>(v.y > thr) << 1) |
@@ -478,7 +501,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             const int e = __ffs(mask) - 1;
             mask &= mask - 1u;
             const int at = 4 * ((e >> 2) * kSelThreads + tid) + (e & 3);
-            if (o < cap) { keys[o] = static_cast<uint64_t>(ci * kChunkPos + at); cand_score[o] = chunk[at]; }
+            if (o < cap) {
+              keys[o] = static_cast<uint64_t>(ci * kChunkPos + at);
+              cand_score[o] = use16 ? srow[ci * kChunkPos + at] : chunk[at];
+            }
             ++o;
           }
         }
@@ -486,6 +512,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         return running;
       };
 
+      const bool use_hm16 = vec && n_chunks > 1 && n_chunks <= p.hm_chunks;
       // ---- tier 1a: a bound from group maxima.  Each thread holds four groups of positions
       //      per chunk (stride 4096 inside a group); the K-th largest group maximum is a lower
       //      bound of the K-th largest score, and far fewer values enter the histogram. ----
@@ -497,6 +524,11 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           const float4 v = chunk4[j * kSelThreads + tid];
           gm[0] = fmaxf(gm[0], v.x); gm[1] = fmaxf(gm[1], v.y); gm[2] = fmaxf(gm[2], v.z); gm[3] = fmaxf(gm[3], v.w);
           hm[j] = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+          if (use_hm16) {
+            const uint32_t k32 = float_order_key(hm[j]);
+            hm16[(ci * kChunkVec + j) * kSelThreads + tid] =
+                static_cast<uint16_t>(min(0xFFFFu, (k32 >> 16) + ((k32 & 0xFFFFu) ? 1u : 0u)));
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
@@ -514,7 +546,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           // threshold a little below the exact boundary (a few extra candidates are harmless)
           const float xlim = static_cast<float>(last + 1);
           const float thr = (top64 - xlim) * (1.0f / kBinsPerUnit) - (fabsf(top64) + xlim) * (1.0f / (kBinsPerUnit * 2097152.0f)) - 1e-30f;
-          const int total = collect(thr, 0, 0, p.sort_n);
+          const int total = collect(thr, 0, 0, p.sort_n, use_hm16);
           ok = total <= p.sort_n;
           ncand = total;
           cand_last = last + nb;
@@ -823,9 +855,9 @@ int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 template <int MODE, int DT>
 jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
-  const size_t smem = sel_smem_bytes(sp.sort_n);
-  constexpr size_t kMaxSmem = sel_smem_bytes(2 * JF_MAX_TOP_K);
-  static_assert(kMaxSmem <= 227 * 1024, "select kernel shared memory");
+  const size_t smem = sel_smem_bytes(sp.sort_n, sp.hm_chunks);
+  constexpr size_t kMaxSmem = kSelSmemLimit;
+  static_assert(sel_smem_bytes(2 * JF_MAX_TOP_K) <= kSelSmemLimit, "select kernel shared memory");
   if (fused) {
     JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true>), kMaxSmem);
     JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, true>, grid, dim3(kSelThreads), smem, stream, sp, tp));
@@ -876,6 +908,10 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   sp.top_k = a->top_k;
   sp.sort_n = pow2_ceil(2 * a->top_k);
   if (sp.sort_n < 512) sp.sort_n = 512;
+  {  // rows of 2..4 score chunks get the side table if it fits beside the rest
+    const int chunks = (a->max_S + kChunkPos - 1) / kChunkPos;
+    sp.hm_chunks = (chunks >= 2 && chunks <= 4 && sel_smem_bytes(sp.sort_n, chunks) <= kSelSmemLimit) ? chunks : 0;
+  }
   sp.q_dtype = a->q_dtype;
   sp.attn_scale = a->attn_scale;
   const TailParams tp = make_tail_params(a, ws);
