@@ -899,9 +899,9 @@ def main():
 
     # ---- multi-GPU correctness (outside the timed region): layer 0 run unsharded on rank 0's GPU.
     #      The selected positions of rank 0's own rows must be identical.  The gathered outputs are
-    #      compared to one unit of the 16-bit output type: a GPU that holds fewer (sequence, KV head)
-    #      pairs cuts every row into more splits, so its fp32 sums run in a different order and the
-    #      rounded output may differ in the last place. ----
+    #      held to the output gate (2e-3 + 1e-3 relative), not to bit equality: a GPU that holds fewer
+    #      (sequence, KV head) pairs cuts every row into more splits, so its fp32 sums run in a
+    #      different order (the largest difference and the share of equal values are reported). ----
     gather_check = None
     if world > 1 and rank == 0 and not args.no_check:
         whole = Shard(0, 0, w["H_kv"], 0, w["H_q"], 0, w["batch"])
@@ -913,13 +913,12 @@ def main():
         got = full_out[0].view(w["batch"], w["H_q"], 128).float()
         want = R.out.float()
         diff = (got - want).abs()
-        unit = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
         mine_idx = layers[0].call.out["topk_idx"]
         ref_idx = R.call.out["topk_idx"][shard.b_start:shard.b_start + shard.b_count,
                                          shard.q_start:shard.q_start + shard.q_count]
         gather_check = {"layer": 0, "topk_lists_equal_to_single_gpu": bool(torch.equal(mine_idx, ref_idx)),
                         "out_max_abs_diff": float(diff.max()),
-                        "out_within_one_unit_of_the_16bit_type": bool((diff <= unit * want.abs() + 1e-6).all()),
+                        "out_within_output_gate": bool((diff <= 2e-3 + 1e-3 * want.abs()).all()),
                         "out_bit_equal_fraction": float((got == want).float().mean())}
         del ref_layers, R
         torch.cuda.empty_cache()
