@@ -55,11 +55,14 @@ struct Workspace {
   float* part_m;     // [B][H_kv][splits][8]
   float* part_l;     // [B][H_kv][splits][8]
   float* part_smax;  // [B][H_kv][splits][2]  largest K group scale seen (per group)
+  float* pmax;       // K3V2: [B][H_q][page_max_stride] largest approximate score of every pair of 16-token pages
   float* scores;     // [B][H_q][max_S] approximate scores
   uint64_t bytes;
 };
 
 __host__ __device__ inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+// entries per row of the page maxima: one per pair of 16-token pages, rounded up to whole float4s
+__host__ __device__ inline int page_max_stride(int max_S) { return (((max_S + 2 * JF_BLOCK_SIZE - 1) / (2 * JF_BLOCK_SIZE)) + 3) & ~3; }
 
 // Sized for the variant with the most splits (bf16 query), so one workspace serves both dtypes.
 inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv, int max_S, int /*top_k*/, bool need_scores) {
@@ -74,6 +77,8 @@ inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv,
   w.part_m = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
   w.part_l = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
   w.part_smax = reinterpret_cast<float*>(p + off);  off = align_up(off + pairs * 2 * 4, 256);
+  w.pmax = reinterpret_cast<float*>(p + off);
+  if (mode == JF_MODE_K3V2) off = align_up(off + static_cast<uint64_t>(B) * H_q * page_max_stride(max_S) * 4, 256);
   w.scores = reinterpret_cast<float*>(p + off);
   if (need_scores) off = align_up(off + static_cast<uint64_t>(B) * H_q * max_S * 4, 256);
   w.bytes = off;

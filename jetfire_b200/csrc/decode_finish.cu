@@ -29,12 +29,12 @@ decode_finish_kernel(const FinishParams p, const TailParams tp) {
   const int64_t bh = static_cast<int64_t>(b) * tp.H_q + h;
   const int64_t pbase = (static_cast<int64_t>(b) * tp.H_kv + hkv) * tp.splits;
   pdl_wait();
-  SplitPre pre;
-  split_preload(tp, pbase, hi, tid, pre);
+  SplitPre<kSelThreads> pre;
+  split_preload<kSelThreads>(tp, pbase, hi, tid, pre);
   const int n = min(p.seq_lens[b], tp.max_S);
   const float M = block_max_of_splits(tp.part_m, pbase, hi, tp.splits, sm_m);
   const int64_t* sel = p.topk_idx + bh * tp.top_k;
-  finish_tail<MODE>(tp, tsm, TailPrefetch{}, pre, M, n, b, h, p.block_table + static_cast<int64_t>(b) * p.max_blocks,
+  finish_tail<MODE, kSelThreads>(tp, tsm, TailPrefetch{}, pre, M, n, b, h, p.block_table + static_cast<int64_t>(b) * p.max_blocks,
                     [&](int kk, int& pos, int& cidx) {
                       const int64_t v = sel[kk];
                       if (v < 0 || v >= n) return false;

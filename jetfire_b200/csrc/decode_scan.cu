@@ -156,6 +156,7 @@ struct K3State {
   uint32_t qf[QT][8][2];   // query fragments (B operand of the K MMA)
   float oacc[10][4];       // output accumulators, O^T fragments; tiles 8, 9: sum of the P operand per V group
   float m_ref0, m_ref1, l0, l1;
+  float pm_a, pm_b;        // largest score of this lane's tokens in the current round, heads 2tig and 2tig+1
   uint32_t smax_bits;      // largest K group scale seen (bf16 bits; positive floats order as integers)
   uint32_t ks_sel;         // PRMT selector: this lane's K group scale into both halves
 };
@@ -239,16 +240,17 @@ __device__ __forceinline__ void k3v2_page(K3State<QT>& st, uint32_t sb, uint32_t
       if (st0) { sp0[0] = s0; sp0[8] = s2; }
       if (st1) { sp1[0] = s1; sp1[8] = s3; }
     }
+    // running maxima of this lane's tokens, for the page-pair maxima the select kernel reads
+    st.pm_a = fmaxf(st.pm_a, fmaxf(s0, s2));
+    st.pm_b = fmaxf(st.pm_b, fmaxf(s1, s3));
   }
 
   // ---------------- online softmax ----------------
   float p0, p1, p2, p3;
   softmax_step(s0, s1, s2, s3, st.m_ref0, st.m_ref1, st.l0, st.l1, st.oacc, p0, p1, p2, p3);
-  if (!kDoV) return;
-
   // ---------------- V: unpack + (P * vscale).V ----------------
 #pragma unroll
-  for (int qh = 0; qh < 2; ++qh) {
+  for (int qh = 0; kDoV && qh < 2; ++qh) {
     const float va = qh ? vs01 : vs00, vb = qh ? vs11 : vs10;
     const uint32_t B0 = movmatrix_trans(pack_f16x2_sat(p0 * va, p1 * va));  // tokens tig, tig+4
     const uint32_t B1 = movmatrix_trans(pack_f16x2_sat(p2 * vb, p3 * vb));  // tokens tig+8, tig+12
@@ -415,6 +417,7 @@ scan_k3v2_kernel(const ScanParams p) {
   for (int i = 0; i < 10; ++i) { st.oacc[i][0] = st.oacc[i][1] = st.oacc[i][2] = st.oacc[i][3] = 0.f; }
   st.m_ref0 = kMinusBig; st.m_ref1 = kMinusBig; st.l0 = 0.f; st.l1 = 0.f;
   st.smax_bits = 0u;
+  st.pm_a = st.pm_b = -INFINITY;
   bool failed = false;
 
   const int t0 = (g >> 1) | ((g & 1) << 2);  // token of MMA row g (rows g + 8 -> t0 + 8)
@@ -426,6 +429,12 @@ scan_k3v2_kernel(const ScanParams p) {
                static_cast<int64_t>(pg_first) * 16;
   float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
+  // Page-pair maxima (pages 2m, 2m+1; a warp's range starts at an even page): after the round's
+  // butterfly the lanes with bits 2 and 3 clear hold them -- lane bit 4 clear: head 2tig, set: 2tig+1.
+  const int pm_head = 2 * tig + (lane >> 4);
+  float* pmw = (kDoK && (lane & 12) == 0 && pm_head < p.G)
+                   ? p.pmax + (static_cast<int64_t>(b) * p.H_q + hkv * p.G + pm_head) * p.np_stride + (pg_first >> 1)
+                   : nullptr;
   const float attn = p.attn_scale;
 
   // A round takes one slot: two pages (one at the end of the range), processed one after the
@@ -454,6 +463,16 @@ scan_k3v2_kernel(const ScanParams p) {
         k3v2_page<kQTerms, false, kParts>(st, sb, ko, vo, so, t0, 16, attn, sp0, sp1, st0, st1);
       sp0 += 16;
       sp1 += 16;
+    }
+    if (kDoK) {
+      // largest score of the round's pages per head: the halves of the warp trade one head for the
+      // other (each lane sends one value and keeps one), then reduce over lane bits 3 and 2
+      const bool up = (lane & 16) != 0;
+      float v = fmaxf(up ? st.pm_b : st.pm_a, __shfl_xor_sync(0xFFFFFFFFu, up ? st.pm_a : st.pm_b, 16));
+      v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 8));
+      v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 4));
+      if (pmw) *pmw++ = v;
+      st.pm_a = st.pm_b = -INFINITY;
     }
     __syncwarp();
     if (((it + kPagesInFlight + 1) >> 4) > bt_stored) {   // the refill below reads entries up to it + kPagesInFlight + 1
@@ -564,6 +583,7 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.v_data = a->v_data;  sp.v_scales = static_cast<const uint16_t*>(a->v_scales);
   sp.block_table = a->block_table;  sp.seq_lens = a->seq_lens;
   sp.scores = a->scores ? a->scores : ws.scores;
+  sp.pmax = ws.pmax; sp.np_stride = page_max_stride(a->max_S);
   sp.part_o = ws.part_o; sp.part_m = ws.part_m; sp.part_l = ws.part_l; sp.part_smax = ws.part_smax;
   sp.status = ws.status;
   sp.num_slots = a->num_slots;
@@ -574,6 +594,12 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   const int pages = (a->max_S + 15) / 16;
   sp.pages_per_split = (pages + sp.splits - 1) / sp.splits;
   sp.pages_per_warp = (sp.pages_per_split + kScanWarps - 1) / kScanWarps;
+  if (a->mode == JF_MODE_K3V2) {
+    // every warp's range starts at an even page, so that the pairs of pages a round takes are the
+    // pairs (2m, 2m+1) of the row -- the groups of the page maxima
+    sp.pages_per_split = (sp.pages_per_split + 1) & ~1;
+    sp.pages_per_warp = (((sp.pages_per_split + kScanWarps - 1) / kScanWarps) + 1) & ~1;
+  }
   sp.attn_scale = a->attn_scale;
   sp.q_dtype = a->q_dtype;
   dim3 grid(sp.splits, hg.H_kv, a->B);

@@ -42,6 +42,7 @@ struct ScanParams {
   const int64_t* block_table;
   const int32_t* seq_lens;
   float* scores;
+  float* pmax;          // K3V2: largest score of every pair of pages, [B][H_q][np_stride] (see the select kernel)
   float* part_o;
   float* part_m;
   float* part_l;
@@ -53,6 +54,7 @@ struct ScanParams {
   float attn_scale;
   int q_dtype;
   int kv_shift;         // cache head = KV head >> kv_shift (see head_geom)
+  int np_stride;        // entries per row of pmax
   // K4V4: work is cut into two-page tiles (see scan_k4v4_kernel)
   int n_tiles, tiles_per_split, tiles_per_warp, ref_chunk;
   int tile_base[9];

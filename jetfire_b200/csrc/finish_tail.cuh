@@ -6,18 +6,20 @@
 // reference's Stage B does with the scores of its Stage A: what the later merge subtracts
 // is exactly what the approximate pass added for these positions.
 //
-// Both kernels run this code with the same block size, so their results are bit-equal;
-// every summation order is fixed (no floating-point atomics).
+// Every summation order is fixed (no floating-point atomics) and does not depend on the block
+// size: a block of NT threads plays the 1024 thread-items and the 32 warps of the widest
+// block one after the other, so every kernel that runs this code gives the same bits.
 #pragma once
 
 #include "decode_common.cuh"
 
 namespace jf {
 
-constexpr int kSelThreads = 1024;
+
+constexpr int kSelThreads = 1024;                        // widest block; the unit of the fixed orders below
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kSplitGroups = kSelThreads / JF_HEAD_DIM;  // split partials are summed in 8 strided groups
-constexpr int kSplitPre = 4;                             // partials per thread fetched ahead of use
+constexpr int kSplitPre = 4;                             // partials per thread fetched ahead of use (all its items together)
 constexpr int kTailChunk = 256;                          // selected entries staged per round
 constexpr int kTailPerWarp = kTailChunk / kSelWarps;
 
@@ -54,21 +56,30 @@ struct TailSmem {
 
 // The first kSplitPre split partials of thread (group, d), loaded before they are needed so
 // that their latency hides behind other work.
+// Thread-item `it` = (group it >> 7, channel it & 127) of the 1024; a thread of an NT-wide block
+// owns items tid, tid + NT, ... and preloads the first kSplitPre * NT / 1024 splits of each.
+template <int NT>
 struct SplitPre {
-  float m[kSplitPre], l[kSplitPre], o[kSplitPre];
+  static constexpr int kItems = kSelThreads / NT, kPer = kSplitPre / kItems;
+  float m[kItems][kPer], l[kItems][kPer], o[kItems][kPer];
 };
 
-__device__ __forceinline__ void split_preload(const TailParams& p, int64_t pbase, int hi, int tid, SplitPre& r) {
-  const int d = tid & (JF_HEAD_DIM - 1), grp = tid >> 7;
+template <int NT>
+__device__ __forceinline__ void split_preload(const TailParams& p, int64_t pbase, int hi, int tid, SplitPre<NT>& r) {
 #pragma unroll
-  for (int i = 0; i < kSplitPre; ++i) {
-    const int s = grp + i * kSplitGroups;
-    r.m[i] = kMinusBig; r.l[i] = 0.f; r.o[i] = 0.f;
-    if (s < p.splits) {
-      const int64_t e = (pbase + s) * kHeadsPad + hi;
-      r.m[i] = p.part_m[e];
-      r.l[i] = p.part_l[e];
-      r.o[i] = p.part_o[e * JF_HEAD_DIM + d];
+  for (int k = 0; k < SplitPre<NT>::kItems; ++k) {
+    const int it = tid + k * NT;
+    const int d = it & (JF_HEAD_DIM - 1), grp = it >> 7;
+#pragma unroll
+    for (int i = 0; i < SplitPre<NT>::kPer; ++i) {
+      const int s = grp + i * kSplitGroups;
+      r.m[k][i] = kMinusBig; r.l[k][i] = 0.f; r.o[k][i] = 0.f;
+      if (s < p.splits) {
+        const int64_t e = (pbase + s) * kHeadsPad + hi;
+        r.m[k][i] = p.part_m[e];
+        r.l[k][i] = p.part_l[e];
+        r.o[k][i] = p.part_o[e * JF_HEAD_DIM + d];
+      }
     }
   }
 }
@@ -92,29 +103,33 @@ struct TailPrefetch {
 // `src(kk, pos, cidx)` yields the kk-th selected entry (rank order): its position and its
 // index in the prefetched arrays (-1: none); false if there is no such entry.  M = max over
 // the splits of the scan's reference points.  n = sequence length.
-template <int MODE, typename Src>
+template <int MODE, int NT, typename Src>
 __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>& sm, const TailPrefetch& pf,
-                                            const SplitPre& pre, float M, int n, int b, int h, const int64_t* bt,
+                                            const SplitPre<NT>& pre, float M, int n, int b, int h, const int64_t* bt,
                                             Src src) {
   constexpr int VW = TailSmem<MODE>::VW;
+  constexpr int kW = NT / 32;                 // warps of this block
+  constexpr int kPre = SplitPre<NT>::kPer;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hkv = h / p.G, hi = h - hkv * p.G;
   const int64_t bh = static_cast<int64_t>(b) * p.H_q + h;
   const int64_t pbase = (static_cast<int64_t>(b) * p.H_kv + hkv) * p.splits;
 
   // ---- merge splits (unnormalised): thread (group, d) sums splits group, group + 8, ... ----
-  {
-    const int d = tid & (JF_HEAD_DIM - 1), grp = tid >> 7;
+#pragma unroll
+  for (int k = 0; k < SplitPre<NT>::kItems; ++k) {
+    const int it = tid + k * NT;
+    const int d = it & (JF_HEAD_DIM - 1), grp = it >> 7;
     float o = 0.f, Z = 0.f;
 #pragma unroll
-    for (int i = 0; i < kSplitPre; ++i) {
+    for (int i = 0; i < kPre; ++i) {
       if (grp + i * kSplitGroups < p.splits) {
-        const float w = ex2((pre.m[i] - M) * kLog2e);
-        Z = fmaf(pre.l[i], w, Z);
-        o = fmaf(pre.o[i], w, o);
+        const float w = ex2((pre.m[k][i] - M) * kLog2e);
+        Z = fmaf(pre.l[k][i], w, Z);
+        o = fmaf(pre.o[k][i], w, o);
       }
     }
-    for (int s = grp + kSplitPre * kSplitGroups; s < p.splits; s += kSplitGroups) {
+    for (int s = grp + kPre * kSplitGroups; s < p.splits; s += kSplitGroups) {
       const int64_t e = (pbase + s) * kHeadsPad + hi;
       const float w = ex2((p.part_m[e] - M) * kLog2e);
       Z = fmaf(p.part_l[e], w, Z);
@@ -129,8 +144,10 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
   const uint8_t* v_rows = p.v_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.v_row;
   const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
   const float* srow = p.scores + bh * p.max_S;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  float wsum = 0.f;
+  constexpr int kVW = kSelWarps / kW;   // warps of the widest block this warp plays: warp, warp + kW, ...
+  float acc[kVW][4], wsum[kVW];
+#pragma unroll
+  for (int k = 0; k < kVW; ++k) { acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f; wsum[k] = 0.f; }
   const int qg = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
   for (int k0 = 0; k0 < p.top_k; k0 += kTailChunk) {
     const int kend = min(kTailChunk, p.top_k - k0);
@@ -172,7 +189,7 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
     }
     __syncthreads();
     // packed V rows, one 16-byte load per thread
-    for (int u = tid; u < kend * (VW / 4); u += kSelThreads) {
+    for (int u = tid; u < kend * (VW / 4); u += NT) {
       const int c = u / (VW / 4), part = u - c * (VW / 4);
       const int64_t slot = sm.slot[c];
       const int cidx = sm.cidx[c];
@@ -184,13 +201,15 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       reinterpret_cast<uint4*>(sm.v)[u] = v;
     }
     __syncthreads();
-    // warp w takes entries w, w + 32, ...; lane l owns channels 4l..4l+3
-    {
+    // warp w (of 32) takes entries w, w + 32, ...; lane l owns channels 4l..4l+3
+#pragma unroll
+    for (int k = 0; k < kVW; ++k) {
+      const int vwarp = warp + k * kW;
       uint32_t raw[kTailPerWarp];
       float fw[kTailPerWarp], w0[kTailPerWarp];
 #pragma unroll
       for (int i = 0; i < kTailPerWarp; ++i) {
-        const int j = warp + i * kSelWarps;  // < kTailChunk; entries past kend hold zero weights
+        const int j = vwarp + i * kSelWarps;  // < kTailChunk; entries past kend hold zero weights
         raw[i] = (MODE == JF_MODE_K3V2) ? static_cast<uint32_t>(reinterpret_cast<const uint8_t*>(sm.v + j * VW)[lane])
                                         : static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(sm.v + j * VW)[lane]);
         fw[i] = sm.wv[j][qg];
@@ -198,7 +217,7 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       }
 #pragma unroll
       for (int i = 0; i < kTailPerWarp; ++i) {
-        const int j = warp + i * kSelWarps;
+        const int j = vwarp + i * kSelWarps;
         if (j >= kend || sm.slot[j] < 0) continue;  // warp-uniform
         float c[4];
         if (MODE == JF_MODE_K3V2) {
@@ -211,15 +230,18 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
           c[3] = small_code_to_f32((raw[i] >> 8) & 15u, 8.0f);
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] = fmaf(fw[i], c[e], acc[e]);
-        wsum += w0[i];
+        for (int e = 0; e < 4; ++e) acc[k][e] = fmaf(fw[i], c[e], acc[k][e]);
+        wsum[k] += w0[i];
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int e = 0; e < 4; ++e) sm.red[warp][4 * lane + e] = acc[e];
-  if (lane == 0) sm.sum[warp] = wsum;
+  for (int k = 0; k < kVW; ++k) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sm.red[warp + k * kW][4 * lane + e] = acc[k][e];
+    if (lane == 0) sm.sum[warp + k * kW] = wsum[k];
+  }
   __syncthreads();
   if (tid < JF_HEAD_DIM) {
     float acc_old = 0.f, ws = 0.f, o = 0.f, Z = 0.f;
@@ -240,7 +262,7 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
 }
 
 // Shared by both kernels: the merged reference point M = max over the splits, block-wide.
-// `red` = 32 floats of shared memory.  Ends with a barrier.
+// `red` = 32 floats of shared memory.  Ends with a barrier.  For a block of kSelThreads threads.
 __device__ __forceinline__ float block_max_of_splits(const float* part_m, int64_t pbase, int hi, int splits, float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float M = kMinusBig;

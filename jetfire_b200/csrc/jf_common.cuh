@@ -37,6 +37,8 @@ inline jf_status_t cuda_fail(cudaError_t e) {
     if (!(done__.load(std::memory_order_acquire) & bit__)) {                                   \
       JF_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                        static_cast<int>(bytes)));                              \
+      JF_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                                       static_cast<int>(cudaSharedmemCarveoutMaxShared)));     \
       done__.fetch_or(bit__, std::memory_order_release);                                       \
     }                                                                                          \
   } while (0)
@@ -173,6 +175,9 @@ __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// until at most N of this thread's most recent groups are still in flight
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 // L2 eviction policy for streamed-once data: lines fetched with it are the first to be
 // replaced, so a stream larger than L2 does not push out what later kernels re-read.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

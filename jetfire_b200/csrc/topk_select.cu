@@ -26,6 +26,7 @@ constexpr float kBinsPerUnit = 64.0f;
 
 struct TopkParams {
   const float* scores;
+  const float* pmax;      // K3V2: the scan's page maxima, [B][H_q][np_stride]
   const float* part_m;
   const float* part_smax;
   const void* q;
@@ -40,6 +41,7 @@ struct TopkParams {
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
   int kv_shift;   // cache head = KV head >> kv_shift (see head_geom)
   int hm_chunks;  // score chunks whose per-float4 maxima fit the shared-memory side table (0: none)
+  int np_stride;  // entries per row of pmax
   float attn_scale;
 };
 
@@ -175,9 +177,10 @@ __device__ __forceinline__ int score_bin(float top64, float s) {
 }
 
 constexpr int kRowChunk = 768;                 // candidates staged in shared memory per round (top-k 512 and its band in one)
-constexpr int kChunkPos = 32768;               // positions of the row held in shared memory at a time
-constexpr int kChunkVec = kChunkPos / (4 * kSelThreads);  // float4 reads per thread and pass
-template <int MODE> struct RowWords { static constexpr int v = (MODE == JF_MODE_K3V2) ? 13 : 17; };
+constexpr int kChunkVec = 8;                   // float4 reads per thread and pass over a chunk
+constexpr int kChunkPosMax = 4 * kChunkVec * kSelThreads;   // positions of the row held in shared memory at a time (widest block)
+// 32-bit words per staged K row: K3V2 holds 12 of data and one of scales in a 64-byte slot (16-byte copies land aligned)
+template <int MODE> struct RowWords { static constexpr int v = 16; };
 
 struct SelSmemFixed {
   uint64_t bar;               // mbarrier of the score-chunk copy
@@ -195,36 +198,57 @@ struct SelSmemFixed {
 // What lives in the score chunk's shared memory once the candidates are collected.
 template <int MODE>
 struct SelSmemLate {
-  TailSmem<MODE> tail;
+  union {   // the K rows are done with (canonical scores) before the finish stage starts
+    TailSmem<MODE> tail;
+    uint32_t rows[(MODE == JF_MODE_K3V2) ? kRowChunk * RowWords<MODE>::v : 4];   // K3V2: packed K rows + scales (K4V4 re-scores nothing)
+  };
   uint32_t vrows[kRowChunk * TailSmem<MODE>::VW];  // packed V rows of the candidates (fused kernel)
   int64_t cand_slot[kRowChunk];
-  uint32_t rows[(MODE == JF_MODE_K3V2) ? kRowChunk * 13 : 4];   // K3V2: packed K rows + scales (K4V4 re-scores nothing)
   uint32_t vsc[kRowChunk];                         // V scales
 };
 
-constexpr size_t kSelChunkBytes = static_cast<size_t>(kChunkPos) * 4;
+constexpr size_t kSelChunkBytes = static_cast<size_t>(kChunkPosMax) * 4;
 constexpr size_t kHmChunkBytes = static_cast<size_t>(kChunkVec) * kSelThreads * 2;   // side table of one chunk
 constexpr size_t kSelSmemLimit = 227 * 1024;
-__host__ __device__ constexpr size_t sel_smem_bytes(int sort_n, int hm_chunks = 0) {
-  // chunk | fixed | keys[sort_n] | cand_score[sort_n] | perm[sort_n] | bucket[sort_n] | hm16[hm_chunks]
-  return kSelChunkBytes + sizeof(SelSmemFixed) + static_cast<size_t>(sort_n) * 8 +
+// Bytes of the first shared-memory region: the resident score chunk (whose memory the late
+// structures reuse), or -- lean kernel, which never stages the scores -- the late structures alone.
+template <int MODE, bool LEAN>
+__host__ __device__ constexpr size_t sel_region0_bytes() {
+  return LEAN ? ((sizeof(SelSmemLate<MODE>) + 127) / 128) * 128 : kSelChunkBytes;
+}
+__host__ __device__ constexpr size_t sel_smem_bytes(size_t region0, int sort_n, int hm_chunks = 0) {
+  // region 0 | fixed | keys[sort_n] | cand_score[sort_n] | perm[sort_n] | bucket[sort_n] | hm16[hm_chunks]
+  return region0 + sizeof(SelSmemFixed) + static_cast<size_t>(sort_n) * 8 +
          static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(hm_chunks) * kHmChunkBytes;
 }
+constexpr int kPmVec = 2;   // lean kernel: float4s of page maxima per thread (rows of up to 4 * kPmVec * threads pages)
 
 // One CTA per (query head, batch element).  The row's approximate scores are pulled into
 // shared memory by one bulk copy per 32768 positions, issued before anything else so that
 // the prologue runs under it; every later pass over the scores reads shared memory.
 // FUSED: the finish stage follows in the same kernel.
-template <int MODE, int DT, bool FUSED>
-__global__ void __launch_bounds__(kSelThreads)
+// LEAN (K3V2, long rows): the scores are never staged.  The scan left the largest score of every
+// pair of 16-token pages next to them; the threshold comes from a histogram of those maxima (the
+// K-th largest of them is a lower bound of the K-th largest score), and only the pairs whose
+// maximum passes it are fetched -- a few hundred 128-byte reads instead of two passes over
+// the row.  Rows the bins do not fit take the radix tier over global memory.
+// NT: threads per block -- 1024, or (lean only) 512 with two blocks per multiprocessor, so that
+// one row's chains of dependent memory round trips run under the other's arithmetic.
+template <int MODE, int DT, bool FUSED, bool LEAN, int NT>
+__global__ void __launch_bounds__(NT, kSelThreads / NT)
 topk_select_kernel(const TopkParams p, const TailParams tp) {
+  static_assert(LEAN || NT == kSelThreads, "the resident-chunk kernel is written for the widest block");
+  constexpr int kW = NT / 32;                   // warps of this block
+  constexpr int kChunkPos = 4 * kChunkVec * NT; // positions per pass over a chunk
   constexpr int W = RowWords<MODE>::v;         // 32-bit words staged per candidate: data + scales
   static_assert(sizeof(SelSmemLate<MODE>) <= kSelChunkBytes, "late shared memory must fit in the score chunk");
+  static_assert(!LEAN || MODE == JF_MODE_K3V2, "only the K3V2 scan writes page maxima");
+  constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN>();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* chunk = reinterpret_cast<float*>(smem_raw);
   SelSmemLate<MODE>& late = *reinterpret_cast<SelSmemLate<MODE>*>(smem_raw);
-  SelSmemFixed& sm = *reinterpret_cast<SelSmemFixed*>(smem_raw + kSelChunkBytes);
-  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw + kSelChunkBytes + sizeof(SelSmemFixed));  // [sort_n]
+  SelSmemFixed& sm = *reinterpret_cast<SelSmemFixed*>(smem_raw + kRegion0);
+  uint64_t* keys = reinterpret_cast<uint64_t*>(smem_raw + kRegion0 + sizeof(SelSmemFixed));  // [sort_n]
   float* cand_score = reinterpret_cast<float*>(keys + p.sort_n);  // [sort_n] scan score per candidate
   uint16_t* perm = reinterpret_cast<uint16_t*>(cand_score + p.sort_n);             // [sort_n] rank -> candidate
   uint16_t* bucket = perm + p.sort_n;                                              // [sort_n] candidates grouped by bin
@@ -254,7 +278,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         bulk_g2s(chunk, srow + static_cast<int64_t>(ci) * kChunkPos, static_cast<uint32_t>(cnt) * 4u, &sm.bar);
       }
     } else {
-      for (int i = tid; i < cnt; i += kSelThreads) chunk[i] = srow[static_cast<int64_t>(ci) * kChunkPos + i];
+      for (int i = tid; i < cnt; i += NT) chunk[i] = srow[static_cast<int64_t>(ci) * kChunkPos + i];
     }
   };
   // Block-wide; positions past the sequence read as -inf afterwards.  False (for every
@@ -268,7 +292,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     }
     const int valid = max(0, min(n - ci * kChunkPos, kChunkPos));
     if (!vec) __syncthreads();
-    for (int i = valid + tid; i < kChunkPos; i += kSelThreads) chunk[i] = -INFINITY;
+    for (int i = valid + tid; i < kChunkPos; i += NT) chunk[i] = -INFINITY;
     return __syncthreads_and(ok ? 1 : 0) != 0;
   };
   if (tid == 0) {
@@ -308,8 +332,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     if (lane == 0) sm.red[warp] = s1;
   }
   if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
-  for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
-  for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+  for (int i = tid; i < kBins; i += NT) hist[i] = 0;
+  for (int i = tid; i < p.sort_n; i += NT) keys[i] = 0ull;
 
   // ---- the scan's results: split statistics first (small), then the 128 KB score chunk ----
   if (FUSED) pdl_wait();
@@ -319,11 +343,29 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     sm0 = p.part_smax[(pbase + tid) * 2];
     sm1 = p.part_smax[(pbase + tid) * 2 + 1];
   }
-  SplitPre pre;
-  if (FUSED) split_preload(tp, pbase, hi, tid, pre);
-  issue_chunk(0);
+  SplitPre<NT> pre;
+  if (FUSED) split_preload<NT>(tp, pbase, hi, tid, pre);
+  // lean: this thread's page maxima, requested now and used after the reduction below
+  const int n_pages = (n_seq + 15) >> 4, n_pairs = (n_pages + 1) >> 1;
+  float pm[LEAN ? 4 * kPmVec : 1];
+  if (LEAN) {
+    const float4* pm4 = reinterpret_cast<const float4*>(p.pmax + bh * p.np_stride);
+#pragma unroll
+    for (int j = 0; j < kPmVec; ++j) {
+      const int i4 = j * NT + tid;
+      float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      if (4 * i4 < n_pairs) v = pm4[i4];
+      // pairs past the sequence were never written
+      pm[4 * j] = v.x;
+      pm[4 * j + 1] = (4 * i4 + 1 < n_pairs) ? v.y : -INFINITY;
+      pm[4 * j + 2] = (4 * i4 + 2 < n_pairs) ? v.z : -INFINITY;
+      pm[4 * j + 3] = (4 * i4 + 3 < n_pairs) ? v.w : -INFINITY;
+    }
+  } else {
+    issue_chunk(0);
+  }
   {
-    for (int s = tid + kSelThreads; s < p.splits; s += kSelThreads) {
+    for (int s = tid + NT; s < p.splits; s += NT) {
       top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
       sm0 = fmaxf(sm0, p.part_smax[(pbase + s) * 2]);
       sm1 = fmaxf(sm1, p.part_smax[(pbase + s) * 2 + 1]);
@@ -349,10 +391,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
 
   float row_max = kMinusBig;  // max over the splits of the scan's reference points
 #pragma unroll
-  for (int w = 0; w < kSelWarps; ++w) row_max = fmaxf(row_max, sm.w3[w][0]);
+  for (int w = 0; w < kW; ++w) row_max = fmaxf(row_max, sm.w3[w][0]);
 
   // the copy issued at the top must have landed before its shared memory is reused
-  bool copied = wait_chunk(0, n_seq);
+  bool copied = LEAN ? true : wait_chunk(0, n_seq);
   if (!copied && tid == 0) report_status(p.status, JF_ERR_TIMEOUT);
   const int n = copied ? n_seq : 0;   // a row whose scores did not arrive selects nothing
 
@@ -365,12 +407,12 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
 
     if (n <= p.sort_n) {
       // short row: every position is a candidate
-      for (int i = tid; i < n; i += kSelThreads) { keys[i] = static_cast<uint64_t>(i); cand_score[i] = chunk[i]; }
+      for (int i = tid; i < n; i += NT) { keys[i] = static_cast<uint64_t>(i); cand_score[i] = LEAN ? srow[i] : chunk[i]; }
       ncand = n;
     } else {
       float sm0 = 0.f, sm1 = 0.f;
 #pragma unroll
-      for (int w = 0; w < kSelWarps; ++w) { sm0 = fmaxf(sm0, sm.w3[w][1]); sm1 = fmaxf(sm1, sm.w3[w][2]); }
+      for (int w = 0; w < kW; ++w) { sm0 = fmaxf(sm0, sm.w3[w][1]); sm1 = fmaxf(sm1, sm.w3[w][2]); }
       const float top = row_max + 4.0f;  // the scan lets its reference point lag the true maximum by at most 4
       const float top64 = top * kBinsPerUnit;
       float delta = 0.f;
@@ -399,8 +441,11 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       // Block-wide: turns hist[] into inclusive prefix counts (from the top bin down) and
       // leaves in sm.tbin the bin where the count reaches `want` (-1: never).
       auto scan_hist = [&](int want) {
-        const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
-        const int v = h0 + h1;
+        constexpr int kPer = kBins / NT;   // consecutive bins per thread
+        int hv[kPer];
+        int v = 0;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) { hv[i] = hist[kPer * tid + i]; v += hv[i]; }
         int incl = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -410,20 +455,22 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         if (lane == 31) sm.wsum[warp] = incl;
         __syncthreads();
         if (warp == 0) {
-          int t = sm.wsum[lane], inc2 = t;
+          int t = (lane < kW) ? sm.wsum[lane] : 0, inc2 = t;
 #pragma unroll
           for (int o = 1; o < 32; o <<= 1) {
             const int u = __shfl_up_sync(0xFFFFFFFFu, inc2, o);
             if (lane >= o) inc2 += u;
           }
-          sm.wsum[lane] = inc2 - t;  // exclusive prefix of the warp totals
+          if (lane < kW) sm.wsum[lane] = inc2 - t;  // exclusive prefix of the warp totals
         }
         __syncthreads();
-        const int ex = sm.wsum[warp] + incl - v;
-        hist[2 * tid] = ex + h0;
-        hist[2 * tid + 1] = ex + v;
-        if (ex < want && ex + h0 >= want) sm.tbin = 2 * tid;
-        else if (ex + h0 < want && ex + v >= want) sm.tbin = 2 * tid + 1;
+        int run = sm.wsum[warp] + incl - v;   // count in the bins above this thread's
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+          if (run < want && run + hv[i] >= want) sm.tbin = kPer * tid + i;
+          run += hv[i];
+          hist[kPer * tid + i] = run;
+        }
         __syncthreads();
       };
       // Block-wide: positions whose score passes the test against `thr` (kind 0: greater, 1: greater
@@ -434,13 +481,18 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       auto collect = [&](float thr, int kind, int off0, int cap, bool use16 = false) {
         int running = 0;  // candidates found in earlier chunks
         const uint32_t thr16 = float_order_key(thr) >> 16;
+        const bool glob = LEAN || use16;   // the scores come straight from memory
         for (int ci = 0; ci < n_chunks; ++ci) {
-          if (n_chunks > 1 && !use16) next_chunk(ci);
+          if (n_chunks > 1 && !glob) next_chunk(ci);
           uint32_t mask = 0u;
           // which of the thread's float4s can hold a candidate at all (branch-free; most threads
           // find none and skip the loads altogether)
           uint32_t hits = (1u << kChunkVec) - 1u;
-          if (have_hm && kind == 0) {
+          if (LEAN) {
+#pragma unroll
+            for (int j = 0; j < kChunkVec; ++j)
+              if (ci * kChunkPos + 4 * (j * NT + tid) >= n) hits &= ~(1u << j);
+          } else if (have_hm && kind == 0) {
             hits = 0u;
 #pragma unroll
             for (int j = 0; j < kChunkVec; ++j) hits |= static_cast<uint32_t>(hm[j] > thr) << j;
@@ -448,21 +500,21 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             hits = 0u;
 #pragma unroll
             for (int j = 0; j < kChunkVec; ++j)
-              hits |= static_cast<uint32_t>(hm16[(ci * kChunkVec + j) * kSelThreads + tid] >= thr16) << j;
+              hits |= static_cast<uint32_t>(hm16[(ci * kChunkVec + j) * NT + tid] >= thr16) << j;
           }
           while (hits) {
             const int j = __ffs(hits) - 1;
             hits &= hits - 1u;
             float4 v;
-            if (use16) {   // straight from memory; positions at or past the length read as -inf
-              const int pos = ci * kChunkPos + 4 * (j * kSelThreads + tid);
+            if (glob) {    // straight from memory; positions at or past the length read as -inf
+              const int pos = ci * kChunkPos + 4 * (j * NT + tid);
               v = *reinterpret_cast<const float4*>(srow + pos);
               if (pos >= n) v.x = -INFINITY;
               if (pos + 1 >= n) v.y = -INFINITY;
               if (pos + 2 >= n) v.z = -INFINITY;
               if (pos + 3 >= n) v.w = -INFINITY;
             } else {
-              v = chunk4[j * kSelThreads + tid];
+              v = chunk4[j * NT + tid];
             }
             uint32_t m4;
             if (kind == 0)
@@ -488,7 +540,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           __syncthreads();   // the previous round's (or caller's) reads of wsum are done
           if (lane == 31) sm.wsum[warp] = incl;
           __syncthreads();
-          int wt = sm.wsum[lane], winc = wt;
+          int wt = (lane < kW) ? sm.wsum[lane] : 0, winc = wt;
 #pragma unroll
           for (int o = 1; o < 32; o <<= 1) {
             const int t = __shfl_up_sync(0xFFFFFFFFu, winc, o);
@@ -500,10 +552,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           while (mask) {
             const int e = __ffs(mask) - 1;
             mask &= mask - 1u;
-            const int at = 4 * ((e >> 2) * kSelThreads + tid) + (e & 3);
+            const int at = 4 * ((e >> 2) * NT + tid) + (e & 3);
             if (o < cap) {
               keys[o] = static_cast<uint64_t>(ci * kChunkPos + at);
-              cand_score[o] = use16 ? srow[ci * kChunkPos + at] : chunk[at];
+              cand_score[o] = glob ? srow[ci * kChunkPos + at] : chunk[at];
             }
             ++o;
           }
@@ -516,17 +568,17 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       // ---- tier 1a: a bound from group maxima.  Each thread holds four groups of positions
       //      per chunk (stride 4096 inside a group); the K-th largest group maximum is a lower
       //      bound of the K-th largest score, and far fewer values enter the histogram. ----
-      for (int ci = 0; ci < n_chunks; ++ci) {
+      for (int ci = 0; !LEAN && ci < n_chunks; ++ci) {
         if (ci > 0) next_chunk(ci);
         float gm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int j = 0; j < kChunkVec; ++j) {
-          const float4 v = chunk4[j * kSelThreads + tid];
+          const float4 v = chunk4[j * NT + tid];
           gm[0] = fmaxf(gm[0], v.x); gm[1] = fmaxf(gm[1], v.y); gm[2] = fmaxf(gm[2], v.z); gm[3] = fmaxf(gm[3], v.w);
           hm[j] = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
           if (use_hm16) {
             const uint32_t k32 = float_order_key(hm[j]);
-            hm16[(ci * kChunkVec + j) * kSelThreads + tid] =
+            hm16[(ci * kChunkVec + j) * NT + tid] =
                 static_cast<uint16_t>(min(0xFFFFu, (k32 >> 16) + ((k32 & 0xFFFFu) ? 1u : 0u)));
           }
         }
@@ -534,7 +586,13 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         for (int c = 0; c < 4; ++c)
           if (gm[c] > -INFINITY) atomicAdd(&hist[score_bin(top64, gm[c])], 1);
       }
-      have_hm = n_chunks == 1;  // hm[] describes the chunk that stays resident
+      have_hm = !LEAN && n_chunks == 1;  // hm[] describes the chunk that stays resident
+      if (LEAN) {
+        // the groups are the pairs of pages, their maxima came with the scan
+#pragma unroll
+        for (int i = 0; i < 4 * kPmVec; ++i)
+          if (pm[i] > -INFINITY) atomicAdd(&hist[score_bin(top64, pm[i])], 1);
+      }
       __syncthreads();
       scan_hist(K);
       bool ok = false;
@@ -546,7 +604,108 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           // threshold a little below the exact boundary (a few extra candidates are harmless)
           const float xlim = static_cast<float>(last + 1);
           const float thr = (top64 - xlim) * (1.0f / kBinsPerUnit) - (fabsf(top64) + xlim) * (1.0f / (kBinsPerUnit * 2097152.0f)) - 1e-30f;
-          const int total = collect(thr, 0, 0, p.sort_n, use_hm16);
+          int total;
+          if (LEAN) {
+            // The pages of the pairs whose maximum passes the threshold go to a list (every such
+            // pair holds a candidate, so more pairs than the sort buffer has entries means the row
+            // does not fit); then one thread per listed page fetches its sixteen scores (64 bytes, four
+            // independent loads) and appends the ones that pass.  Offsets come from one
+            // shared-memory atomic per warp: the order of the candidates in the buffer is not
+            // fixed, the ranking below does not depend on it.
+            uint16_t* page_list = perm;   // perm and bucket, contiguous: 2 * sort_n entries
+            const int list_cap = 2 * p.sort_n;
+            {
+              uint32_t flags = 0u;   // two bits per pair: its pages that exist
+#pragma unroll
+              for (int i = 0; i < 4 * kPmVec; ++i) {
+                const int pg = 2 * (4 * ((i >> 2) * NT + tid) + (i & 3));
+                if (pm[i] > thr) flags |= (pg + 1 < n_pages ? 3u : 1u) << (2 * i);
+              }
+              const int cnt = __popc(flags);
+              int incl = cnt;
+#pragma unroll
+              for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += t;
+              }
+              int base = 0;
+              if (lane == 31 && incl > 0) base = atomicAdd(&sm.ncand, incl);
+              int o = __shfl_sync(0xFFFFFFFFu, base, 31) + incl - cnt;
+              while (flags) {
+                const int i = __ffs(flags) - 1;
+                flags &= flags - 1u;
+                if (o < list_cap) page_list[o] = static_cast<uint16_t>(2 * (4 * ((i >> 3) * NT + tid) + ((i >> 1) & 3)) + (i & 1));
+                ++o;
+              }
+            }
+            __syncthreads();
+            const int n_list = sm.ncand;
+            __syncthreads();
+            if (tid == 0) sm.ncand = 0;
+            __syncthreads();
+            if (n_list <= list_cap) {
+              // the listed pages come into the (still unused) late region with asynchronous copies,
+              // all in flight at once: one trip to the scores instead of one per round of threads
+              float* stage = reinterpret_cast<float*>(smem_raw);
+              constexpr int kStageCap = static_cast<int>(sizeof(SelSmemLate<MODE>) / 64);
+              for (int b0 = 0; b0 < n_list; b0 += kStageCap) {
+                const int nb = min(kStageCap, n_list - b0);
+                for (int u = tid; u < 4 * nb; u += NT) {
+                  const int l = u >> 2, q4 = u & 3;
+                  cp_async_16(stage + 16 * l + 4 * q4, srow + 16 * static_cast<int>(page_list[b0 + l]) + 4 * q4);
+                }
+                cp_async_commit();
+                cp_async_wait_all();
+                __syncthreads();
+                for (int lb = 0; lb < nb; lb += NT) {
+                  const int l = lb + tid;
+                  uint32_t m16 = 0u;
+                  int pos0 = 0;
+                  if (l < nb) {
+                    pos0 = 16 * static_cast<int>(page_list[b0 + l]);
+                    // the four float4s of the page, starting at a different one in neighbouring
+                    // threads: the pages lie 64 bytes apart, and read in step they would collide
+                    // on two groups of banks
+                    const float4* s4 = reinterpret_cast<const float4*>(stage + 16 * l);
+                    const int rot = (l >> 1) & 3;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const int q4 = (j + rot) & 3;
+                      const float4 v = s4[q4];
+                      const uint32_t m4 = static_cast<uint32_t>(v.x > thr) | (static_cast<uint32_t>(v.y > thr) << 1) |
+                                          (static_cast<uint32_t>(v.z > thr) << 2) | (static_cast<uint32_t>(v.w > thr) << 3);
+                      m16 |= m4 << (4 * q4);
+                    }
+                    const int live = n - pos0;   // tokens of the page inside the sequence
+                    if (live < 16) m16 &= (1u << max(live, 0)) - 1u;
+                  }
+                  const int cnt = __popc(m16);
+                  int incl = cnt;
+#pragma unroll
+                  for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if (lane >= o) incl += t;
+                  }
+                  int base = 0;
+                  if (lane == 31 && incl > 0) base = atomicAdd(&sm.ncand, incl);
+                  int o = __shfl_sync(0xFFFFFFFFu, base, 31) + incl - cnt;
+                  while (m16) {   // one candidate per listed page, as a rule
+                    const int t = __ffs(m16) - 1;
+                    m16 &= m16 - 1u;
+                    if (o < p.sort_n) { keys[o] = static_cast<uint64_t>(pos0 + t); cand_score[o] = stage[16 * l + t]; }
+                    ++o;
+                  }
+                }
+                __syncthreads();
+              }
+              total = sm.ncand;
+            } else {
+              total = n_list;   // too many: the row does not fit this tier
+            }
+            __syncthreads();
+          } else {
+            total = collect(thr, 0, 0, p.sort_n, use_hm16);
+          }
           ok = total <= p.sort_n;
           ncand = total;
           cand_last = last + nb;
@@ -567,13 +726,25 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
           const uint32_t dmask = (1u << bits) - 1u;
           __syncthreads();
           if (tid == 0) sm.tbin = -1;
-          for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
+          for (int i = tid; i < kBins; i += NT) hist[i] = 0;
           __syncthreads();
           for (int ci = 0; ci < n_chunks; ++ci) {
-            if (n_chunks > 1) next_chunk(ci);
+            if (n_chunks > 1 && !LEAN) next_chunk(ci);
 #pragma unroll
             for (int j = 0; j < kChunkVec; ++j) {
-              const float4 v = chunk4[j * kSelThreads + tid];
+              float4 v;
+              if (LEAN) {
+                const int pos = ci * kChunkPos + 4 * (j * NT + tid);
+                v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                if (pos < n) {
+                  v = *reinterpret_cast<const float4*>(srow + pos);
+                  if (pos + 1 >= n) v.y = -INFINITY;
+                  if (pos + 2 >= n) v.z = -INFINITY;
+                  if (pos + 3 >= n) v.w = -INFINITY;
+                }
+              } else {
+                v = chunk4[j * NT + tid];
+              }
               const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
@@ -594,7 +765,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         }
         const float kth = float_from_order_key(prefix);   // the K-th largest approximate score
         __syncthreads();
-        for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+        for (int i = tid; i < p.sort_n; i += NT) keys[i] = 0ull;
         __syncthreads();
         if (MODE == JF_MODE_K4V4) {
           // the scores are canonical: everything above the K-th, then the lowest positions among
@@ -624,82 +795,84 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       //      memory with independent 16-byte loads, then the canonical arithmetic ----
       for (int base = 0; base < ncand; base += kRowChunk) {
         const int cn = min(kRowChunk, ncand - base);
-        if (tid < cn) late.cand_slot[tid] = slot_of(ctx, static_cast<int>(keys[base + tid]));
+        for (int c = tid; c < cn; c += NT) late.cand_slot[c] = slot_of(ctx, static_cast<int>(keys[base + c]));
         __syncthreads();
         {
-          // unit u = (candidate, part), eight per candidate, each at most one 16-byte access.
-          // K3: parts 0-2 the K row, 3 the K scales, 4-5 the V row, 6 the V scales.  K4: parts
-          // 4-7 the V row (part 4 also its scale); its K rows are not needed.
-          // The K side is needed at once and comes through registers; the V side (only when the
-          // finish stage will use it) is copied asynchronously and awaited before that stage.
-          constexpr int kUnroll = 8 * kRowChunk / kSelThreads;
-          constexpr int kKParts = (MODE == JF_MODE_K3V2) ? 3 : 4, kVParts = (MODE == JF_MODE_K3V2) ? 2 : 4;
+          // Every candidate's packed K row and scales (K3V2) and, when the finish stage will use
+          // them, its V row and scales, as asynchronous 16- and 4-byte copies: the K side in
+          // kGroups groups of candidates, the V side as a last group.  The canonical scores of a
+          // group are computed while the later groups are still on their way.
+          constexpr int kGroups = 3;
           constexpr int VW = TailSmem<MODE>::VW;
+          constexpr int kVParts = VW / 4;
           const uint8_t* v_rows = tp.v_data + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.v_row;
           const uint16_t* v_sc = tp.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
-          uint4 v[kUnroll];
-          uint32_t sc16[kUnroll];
+          const int per = (cn + kGroups - 1) / kGroups;
+          if (MODE == JF_MODE_K3V2) {
 #pragma unroll
-          for (int i = 0; i < kUnroll; ++i) {
-            const int u = tid + i * kSelThreads;
-            const int c = u >> 3, part = u & 7;
-            v[i] = make_uint4(0u, 0u, 0u, 0u);
-            sc16[i] = 0u;
-            if (c < cn && (part < 4 ? MODE == JF_MODE_K3V2 : prefetch)) {
+            for (int g = 0; g < kGroups; ++g) {
+              const int c_lo = g * per, c_n = max(0, min(cn, c_lo + per) - c_lo);
+              for (int u = tid; u < 4 * c_n; u += NT) {
+                const int c = c_lo + (u >> 2), part = u & 3;
+                const int64_t slot = late.cand_slot[c];
+                uint32_t* r = late.rows + c * W;
+                if (part < 3) {
+                  if (slot >= 0) cp_async_16(r + 4 * part, ctx.k_rows + slot * 48 + 16 * part);
+                  else *reinterpret_cast<uint4*>(r + 4 * part) = make_uint4(0u, 0u, 0u, 0u);
+                } else {
+                  if (slot >= 0) cp_async_4(r + 12, ctx.k_sc + slot * 2);
+                  else r[12] = 0u;
+                }
+              }
+              cp_async_commit();
+            }
+          }
+          if (prefetch) {
+            for (int u = tid; u < 4 * cn; u += NT) {
+              const int c = u >> 2, part = u & 3;
               const int64_t slot = late.cand_slot[c];
-              if (part < 4) {
-                if (slot >= 0) {
-                  if (part < kKParts) v[i] = __ldg(reinterpret_cast<const uint4*>(ctx.k_rows + slot * (16 * kKParts)) + part);
-                  if (MODE == JF_MODE_K3V2) { if (part == 3) sc16[i] = __ldg(reinterpret_cast<const uint32_t*>(ctx.k_sc + slot * 2)); }
-                  else { if (part == 0) sc16[i] = static_cast<uint32_t>(__ldg(ctx.k_sc + slot)); }
-                }
-              } else if (part < 4 + kVParts) {
-                uint4* dst = reinterpret_cast<uint4*>(late.vrows + c * VW) + (part - 4);
-                if (slot >= 0) cp_async_16(dst, reinterpret_cast<const uint4*>(v_rows + slot * (16 * kVParts)) + (part - 4));
+              if (part < kVParts) {
+                uint4* dst = reinterpret_cast<uint4*>(late.vrows + c * VW) + part;
+                if (slot >= 0) cp_async_16(dst, reinterpret_cast<const uint4*>(v_rows + slot * (16 * kVParts)) + part);
                 else *dst = make_uint4(0u, 0u, 0u, 0u);
-                if (MODE == JF_MODE_K4V4 && part == 4) {
-                  // the 2-byte scale travels as the aligned 4-byte pair that holds it
-                  if (slot >= 0) cp_async_4(&late.vsc[c], v_sc + (slot & ~static_cast<int64_t>(1)));
-                  else late.vsc[c] = 0u;
-                }
-              } else if (MODE == JF_MODE_K3V2 && part == 6) {
-                if (slot >= 0) cp_async_4(&late.vsc[c], v_sc + slot * 2);
-                else late.vsc[c] = 0u;
+              }
+              // the scales: K3V2 both groups' (4 bytes); K4V4 the aligned 4-byte pair that holds the 2-byte scale
+              if (part == ((MODE == JF_MODE_K3V2) ? 2 : 0)) {
+                if (slot < 0) late.vsc[c] = 0u;
+                else if (MODE == JF_MODE_K3V2) cp_async_4(&late.vsc[c], v_sc + slot * 2);
+                else cp_async_4(&late.vsc[c], v_sc + (slot & ~static_cast<int64_t>(1)));
               }
             }
           }
           cp_async_commit();
-#pragma unroll
-          for (int i = 0; i < kUnroll; ++i) {
-            const int u = tid + i * kSelThreads;
-            const int c = u >> 3, part = u & 7;
-            if (MODE == JF_MODE_K3V2 && c < cn && part < 4) {
-              uint32_t* r = late.rows + c * W;
-              if (part < kKParts) { r[4 * part] = v[i].x; r[4 * part + 1] = v[i].y; r[4 * part + 2] = v[i].z; r[4 * part + 3] = v[i].w; }
-              if (MODE == JF_MODE_K3V2) { if (part == 3) r[12] = sc16[i]; }
-              else { if (part == 0) r[16] = sc16[i]; }
+          if (MODE == JF_MODE_K4V4) {
+            // K4: the scan's score is the canonical one bit for bit (exact integer dot products,
+            // the same fp32 rescale order), so nothing is recomputed
+            for (int c = tid; c < cn; c += NT) {
+              const int pos = static_cast<int>(keys[base + c]);
+              keys[base + c] = make_key(late.cand_slot[c] >= 0 ? cand_score[base + c] : -INFINITY, pos);
             }
-          }
-        }
-        __syncthreads();
-        if (MODE == JF_MODE_K4V4) {
-          // K4: the scan's score is the canonical one bit for bit (exact integer dot products,
-          // the same fp32 rescale order), so nothing is recomputed
-          if (tid < cn) {
-            const int pos = static_cast<int>(keys[base + tid]);
-            keys[base + tid] = make_key(late.cand_slot[tid] >= 0 ? cand_score[base + tid] : -INFINITY, pos);
-          }
-        } else {
-          // eight lanes per candidate, four candidates per warp and round
-          float qv[16];
+          } else {
+            // eight lanes per candidate, four candidates per warp and round
+            float qv[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) qv[i] = sm.q[32 * (i >> 2) + 8 * (i & 3) + (lane & 7)];
-          for (int c0 = 4 * warp; c0 < cn; c0 += 4 * kSelWarps) {
-            const int c = c0 + (lane >> 3);
-            const int cc = min(c, cn - 1);           // lanes past the end keep the shuffles company
-            const float s = canon_score_k3_x8(qv, late.rows + cc * W, ctx.attn, lane);
-            if (c < cn && (lane & 7) == 0)
-              keys[base + c] = make_key(late.cand_slot[c] >= 0 ? s : -INFINITY, static_cast<int>(keys[base + c]));
+            for (int i = 0; i < 16; ++i) qv[i] = sm.q[32 * (i >> 2) + 8 * (i & 3) + (lane & 7)];
+#pragma unroll
+            for (int g = 0; g < kGroups; ++g) {
+              // groups 0..g have landed once at most (kGroups - 1 - g) K groups and the V group are in flight
+              if (g == 0) cp_async_wait_group<kGroups>();
+              else if (g == 1) cp_async_wait_group<kGroups - 1>();
+              else cp_async_wait_group<kGroups - 2>();
+              __syncthreads();
+              const int c_lo = g * per, c_hi = min(cn, c_lo + per);
+              for (int c0 = c_lo + 4 * warp; c0 < c_hi; c0 += 4 * kW) {
+                const int c = c0 + (lane >> 3);
+                const int cc = min(c, c_hi - 1);        // lanes past the end keep the shuffles company
+                const float s = canon_score_k3_x8(qv, late.rows + cc * W, ctx.attn, lane);
+                if (c < c_hi && (lane & 7) == 0)
+                  keys[base + c] = make_key(late.cand_slot[c] >= 0 ? s : -INFINITY, static_cast<int>(keys[base + c]));
+              }
+            }
           }
         }
         __syncthreads();
@@ -709,10 +882,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       if (tid == 0) { sm.prefix = 0ull; sm.remaining = K; sm.ncand = 0; }
       __syncthreads();
       for (int level = 7; level >= 0; --level) {
-        for (int i = tid; i < 256; i += kSelThreads) hist[i] = 0;
+        for (int i = tid; i < 256; i += NT) hist[i] = 0;
         __syncthreads();
         const unsigned long long prefix = sm.prefix;
-        for (int i = warp; i < n; i += kSelWarps) {
+        for (int i = warp; i < n; i += kW) {
           const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
           const bool match = (level == 7) || ((key >> (8 * (level + 1))) == prefix);
           if (match && lane == 0) atomicAdd(&hist[(key >> (8 * level)) & 255u], 1);
@@ -730,9 +903,9 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         __syncthreads();
       }
       const unsigned long long tkey = sm.prefix;  // key of the k-th best; keys are unique
-      for (int i = tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+      for (int i = tid; i < p.sort_n; i += NT) keys[i] = 0ull;
       __syncthreads();
-      for (int i = warp; i < n; i += kSelWarps) {
+      for (int i = warp; i < n; i += kW) {
         const uint64_t key = canon_key_global<MODE>(ctx, i, lane);
         if (key >= tkey && lane == 0) {
           const int pos = atomicAdd(&sm.ncand, 1);
@@ -750,27 +923,36 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       // above its own plus the number of larger keys inside its bin.  Bins are `f` times finer
       // than the selection histogram's (the candidates span few of those); a larger canonical
       // score never lands in a later bin, so the result is the exact order of the keys, and
-      // crowded bins (massive ties) only cost time.
+      // crowded bins (massive ties) only cost time.  A thread owns candidates tid, tid + NT, ...
+      constexpr int kCand = kSelThreads / NT;
       int f = 1;
       while (f < 16 && (cand_last + 2) * f * 2 <= kBins) f *= 2;
       const float fscale = kBinsPerUnit * static_cast<float>(f);
       const float ftop = (row_max + 4.0f) * fscale;
-      for (int i = tid; i < kBins; i += kSelThreads) hist[i] = 0;
+      for (int i = tid; i < kBins; i += NT) hist[i] = 0;
       __syncthreads();
-      unsigned long long mine = 0ull;
-      int fb = 0, arrival = 0;
-      if (tid < ncand) {
-        mine = keys[tid];
-        const float sc = float_from_order_key(static_cast<uint32_t>(mine >> 32));
-        const float x = fminf(fmaxf(fmaf(sc, -fscale, ftop), 0.0f), static_cast<float>(kBins - 1));
-        fb = __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
-        arrival = atomicAdd(&hist[fb], 1);
+      unsigned long long mine[kCand];
+      int fb[kCand], arrival[kCand];
+#pragma unroll
+      for (int k = 0; k < kCand; ++k) {
+        const int c = tid + k * NT;
+        mine[k] = 0ull; fb[k] = 0; arrival[k] = 0;
+        if (c < ncand) {
+          mine[k] = keys[c];
+          const float sc = float_from_order_key(static_cast<uint32_t>(mine[k] >> 32));
+          const float x = fminf(fmaxf(fmaf(sc, -fscale, ftop), 0.0f), static_cast<float>(kBins - 1));
+          fb[k] = __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
+          arrival[k] = atomicAdd(&hist[fb[k]], 1);
+        }
       }
       __syncthreads();
       {
-        // exclusive prefix over the bins, two per thread, written back in place
-        const int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
-        const int v = h0 + h1;
+        // exclusive prefix over the bins, kPer per thread, written back in place
+        constexpr int kPer = kBins / NT;
+        int hv[kPer];
+        int v = 0;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) { hv[i] = hist[kPer * tid + i]; v += hv[i]; }
         int incl = v;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -780,39 +962,51 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
         if (lane == 31) sm.wsum[warp] = incl;
         __syncthreads();
         if (warp == 0) {
-          int t = sm.wsum[lane], inc2 = t;
+          int t = (lane < kW) ? sm.wsum[lane] : 0, inc2 = t;
 #pragma unroll
           for (int o = 1; o < 32; o <<= 1) {
             const int u = __shfl_up_sync(0xFFFFFFFFu, inc2, o);
             if (lane >= o) inc2 += u;
           }
-          sm.wsum[lane] = inc2 - t;
+          if (lane < kW) sm.wsum[lane] = inc2 - t;
         }
         __syncthreads();
-        const int ex = sm.wsum[warp] + incl - v;
-        hist[2 * tid] = ex;
-        hist[2 * tid + 1] = ex + h0;
+        int run = sm.wsum[warp] + incl - v;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) { hist[kPer * tid + i] = run; run += hv[i]; }
       }
       __syncthreads();
-      if (tid < ncand) bucket[hist[fb] + arrival] = static_cast<uint16_t>(tid);
-      __syncthreads();
-      int r = 0;
-      if (tid < ncand) {
-        const int lo = hist[fb], hi2 = (fb == kBins - 1) ? ncand : hist[fb + 1];
-        int above = 0;
-        for (int m = lo; m < hi2; ++m) above += (keys[bucket[m]] > mine) ? 1 : 0;
-        r = min(lo + above, ncand - 1);
+#pragma unroll
+      for (int k = 0; k < kCand; ++k) {
+        const int c = tid + k * NT;
+        if (c < ncand) bucket[hist[fb[k]] + arrival[k]] = static_cast<uint16_t>(c);
       }
       __syncthreads();
-      if (tid < ncand) { keys[r] = mine; perm[r] = static_cast<uint16_t>(tid); }
+      int r[kCand];
+#pragma unroll
+      for (int k = 0; k < kCand; ++k) {
+        r[k] = 0;
+        if (tid + k * NT < ncand) {
+          const int lo = hist[fb[k]], hi2 = (fb[k] == kBins - 1) ? ncand : hist[fb[k] + 1];
+          int above = 0;
+          for (int m = lo; m < hi2; ++m) above += (keys[bucket[m]] > mine[k]) ? 1 : 0;
+          r[k] = min(lo + above, ncand - 1);
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < kCand; ++k) {
+        const int c = tid + k * NT;
+        if (c < ncand) { keys[r[k]] = mine[k]; perm[r[k]] = static_cast<uint16_t>(c); }
+      }
       __syncthreads();
     } else {
       // bitonic sort, descending, sort_n a power of two
-      for (int i = ncand + tid; i < p.sort_n; i += kSelThreads) keys[i] = 0ull;
+      for (int i = ncand + tid; i < p.sort_n; i += NT) keys[i] = 0ull;
       __syncthreads();
       for (int size = 2; size <= p.sort_n; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
-          for (int i = tid; i < (p.sort_n >> 1); i += kSelThreads) {
+          for (int i = tid; i < (p.sort_n >> 1); i += NT) {
             const int lo = 2 * i - (i & (stride - 1));
             const int hi2 = lo + stride;
             const bool desc = ((lo & size) == 0);
@@ -827,7 +1021,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   }
 
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
-  for (int r = tid; r < K; r += kSelThreads) {
+  for (int r = tid; r < K; r += NT) {
     int64_t idx = -1, slot = -1;
     if (r < m_sel) {
       idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<uint32_t>(keys[r] & 0xFFFFFFFFull));
@@ -842,7 +1036,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
     __syncthreads();
     TailPrefetch pf{};
     if (prefetch) { pf.slot = late.cand_slot; pf.score = cand_score; pf.vsc = late.vsc; pf.vrows = late.vrows; }
-    finish_tail<MODE>(tp, late.tail, pf, pre, row_max, n_seq, b, h, ctx.bt, [&](int kk, int& pos, int& cidx) {
+    finish_tail<MODE, NT>(tp, late.tail, pf, pre, row_max, n_seq, b, h, ctx.bt, [&](int kk, int& pos, int& cidx) {
       if (kk >= m_sel) return false;
       pos = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(keys[kk] & 0xFFFFFFFFull));
       cidx = prefetch ? static_cast<int>(perm[kk]) : -1;
@@ -853,20 +1047,30 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
 
 int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
-template <int MODE, int DT>
+template <int MODE, int DT, bool LEAN, int NT>
 jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
-  const size_t smem = sel_smem_bytes(sp.sort_n, sp.hm_chunks);
-  constexpr size_t kMaxSmem = kSelSmemLimit;
-  static_assert(sel_smem_bytes(2 * JF_MAX_TOP_K) <= kSelSmemLimit, "select kernel shared memory");
+  constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN>();
+  const size_t smem = sel_smem_bytes(kRegion0, sp.sort_n, LEAN ? 0 : sp.hm_chunks);
+  constexpr size_t kMaxSmem = LEAN ? sel_smem_bytes(kRegion0, 2 * JF_MAX_TOP_K) : kSelSmemLimit;
+  static_assert(sel_smem_bytes(kSelChunkBytes, 2 * JF_MAX_TOP_K) <= kSelSmemLimit, "select kernel shared memory");
+  // two blocks of the narrow lean kernel share a multiprocessor at the top-k widths that take it
+  static_assert(!LEAN || 2 * (sel_smem_bytes(kRegion0, 1024) + 1024) <= 228 * 1024, "two lean blocks per multiprocessor");
   if (fused) {
-    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true>), kMaxSmem);
-    JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, true>, grid, dim3(kSelThreads), smem, stream, sp, tp));
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true, LEAN, NT>), kMaxSmem);
+    JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, true, LEAN, NT>, grid, dim3(NT), smem, stream, sp, tp));
   } else {
-    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, false>), kMaxSmem);
-    JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, false>, grid, dim3(kSelThreads), smem, stream, sp, tp));
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, false, LEAN, NT>), kMaxSmem);
+    JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, false, LEAN, NT>, grid, dim3(NT), smem, stream, sp, tp));
   }
   JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
+}
+
+template <int MODE, bool LEAN, int NT>
+jf_status_t launch_select_dtype(const jf_decode_args* a, const TopkParams& sp, const TailParams& tp, dim3 grid,
+                                cudaStream_t stream, bool fused) {
+  return a->q_dtype == JF_DTYPE_BF16 ? launch_select_variant<MODE, JF_DTYPE_BF16, LEAN, NT>(sp, tp, grid, stream, fused)
+                                     : launch_select_variant<MODE, JF_DTYPE_FP16, LEAN, NT>(sp, tp, grid, stream, fused);
 }
 
 }  // namespace
@@ -896,6 +1100,7 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   TopkParams sp{};
   sp.scores = a->scores ? a->scores : ws.scores;
+  sp.pmax = ws.pmax; sp.np_stride = page_max_stride(a->max_S);
   sp.part_m = ws.part_m; sp.part_smax = ws.part_smax;
   sp.q = a->q; sp.k_data = a->k_data; sp.k_scales = static_cast<const uint16_t*>(a->k_scales);
   sp.block_table = a->block_table; sp.seq_lens = a->seq_lens;
@@ -909,19 +1114,27 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   sp.sort_n = pow2_ceil(2 * a->top_k);
   if (sp.sort_n < 512) sp.sort_n = 512;
   {  // rows of 2..4 score chunks get the side table if it fits beside the rest
-    const int chunks = (a->max_S + kChunkPos - 1) / kChunkPos;
-    sp.hm_chunks = (chunks >= 2 && chunks <= 4 && sel_smem_bytes(sp.sort_n, chunks) <= kSelSmemLimit) ? chunks : 0;
+    const int chunks = (a->max_S + kChunkPosMax - 1) / kChunkPosMax;
+    sp.hm_chunks = (chunks >= 2 && chunks <= 4 && sel_smem_bytes(kSelChunkBytes, sp.sort_n, chunks) <= kSelSmemLimit) ? chunks : 0;
   }
   sp.q_dtype = a->q_dtype;
   sp.attn_scale = a->attn_scale;
   const TailParams tp = make_tail_params(a, ws);
   const dim3 grid(a->H_q, a->B);
   if (a->mode == JF_MODE_K3V2) {
-    return a->q_dtype == JF_DTYPE_BF16 ? launch_select_variant<JF_MODE_K3V2, JF_DTYPE_BF16>(sp, tp, grid, stream, fused)
-                                       : launch_select_variant<JF_MODE_K3V2, JF_DTYPE_FP16>(sp, tp, grid, stream, fused);
+    // Long rows take the lean kernel (threshold from the scan's page-pair maxima): enough pairs for
+    // the K-th largest pair maximum to be a tight bound, and score rows that 16-byte loads can
+    // read.  With more rows than multiprocessors the narrow block runs two rows per
+    // multiprocessor; otherwise a row's latency is what counts and the wide block takes it.
+    const int pairs = (a->max_S + 31) / 32;
+    // (whole pages only: a listed page is fetched whole, and the last row's must end inside the buffer)
+    const bool lean = pairs >= 4 * a->top_k && (a->max_S & 15) == 0 && (reinterpret_cast<uintptr_t>(sp.scores) & 15) == 0;
+    const bool narrow = a->B * a->H_q > num_sms() && sp.sort_n <= 1024;
+    if (lean && narrow && pairs <= 4 * kPmVec * 512) return launch_select_dtype<JF_MODE_K3V2, true, 512>(a, sp, tp, grid, stream, fused);
+    if (lean && pairs <= 4 * kPmVec * kSelThreads) return launch_select_dtype<JF_MODE_K3V2, true, kSelThreads>(a, sp, tp, grid, stream, fused);
+    return launch_select_dtype<JF_MODE_K3V2, false, kSelThreads>(a, sp, tp, grid, stream, fused);
   }
-  return a->q_dtype == JF_DTYPE_BF16 ? launch_select_variant<JF_MODE_K4V4, JF_DTYPE_BF16>(sp, tp, grid, stream, fused)
-                                     : launch_select_variant<JF_MODE_K4V4, JF_DTYPE_FP16>(sp, tp, grid, stream, fused);
+  return launch_select_dtype<JF_MODE_K4V4, false, kSelThreads>(a, sp, tp, grid, stream, fused);
 }
 
 }  // namespace jf

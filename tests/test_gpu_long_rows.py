@@ -1,5 +1,7 @@
 """Rows longer than one shared-memory chunk of the select kernel (32768 positions), odd row
-strides, and the bench geometry at full size, checked against the C restatement of the
+strides, the select kernel that works from the scan's page-pair maxima (long K3V2 rows; one
+block of 1024 threads per row, or two of 512 per multiprocessor once there are more rows than
+multiprocessors), and the bench geometry at full size, checked against the C restatement of the
 oracle (itself pinned to the numpy oracle in test_oracle_native.py).  The packed cache is the
 one the GPU append path wrote (its bytes are pinned elsewhere), so no numpy pass over the
 whole cache is needed."""
@@ -50,6 +52,19 @@ def _run(case, top_k, stage_b="fp32"):
 ])
 def test_rows_longer_than_one_chunk(mode, B, H_q, H_kv, ctx, lens, top_k, seed):
     _run(Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed), top_k)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H_q,H_kv,lens", [
+    (4, 8, 2, [32768, 3000, 300, 8209]),          # 32 rows: the wide block
+    (5, 32, 8, [32768, 32767, 2049, 511, 17]),    # 160 rows, more than multiprocessors: two narrow blocks on each
+])
+def test_page_maxima_select_with_ragged_lengths(dtype, B, H_q, H_kv, lens):
+    """K3V2 rows long enough for the threshold to come from the scan's page-pair maxima, next to
+    sequences of the same batch that are too short for it: fewer pairs than top-k (the exact radix
+    tier over memory), fewer positions than the sort buffer (every position a candidate), a
+    partial last page."""
+    _run(Case("k3v2", B, H_q, H_kv, 32768, lens=lens, seed=62 + B, dtype=dtype), 256)
 
 
 @pytest.mark.parametrize("mode,top_k,ctx", [("k4v4", 1024, 8192), ("k3v2", 2048, 8192), ("k3v2", 1024, 2000)])
