@@ -59,11 +59,6 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
   asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
   return v;
 }
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
 // lo | (hi << 16) for two 16-bit values, as an integer multiply-add (runs on the FMA pipe,
 // which has twice the throughput of the logic pipe that PRMT/SHL/LOP3 share)
 __device__ __forceinline__ uint32_t join16(uint32_t lo, uint32_t hi) {
@@ -84,11 +79,6 @@ struct K3Scale {
   uint32_t S;     // scale * 2^100, both halves
   uint32_t C[5];  // -scale * 2^(POS - 31) for POS = 0..4, both halves (POS 2 is unused)
 };
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
 __device__ __forceinline__ K3Scale k3_scale(uint32_t scale2) {
   K3Scale k;
   k.S = mul_bf16x2(scale2, 0x71807180u);        // 2^100

@@ -91,17 +91,19 @@ __device__ __forceinline__ float canon_score_k3(const float* q, const uint8_t* r
 // channels 32 r + 8 m + sub, whose partial sums are the canonical order's lanes sub + 8 m.
 // Code sub of a group is a 3-bit field of the 24-bit word (byte planes b0 b1 b2); for
 // sub <= 4 it lies in the 16-bit window b0:b1, otherwise in b1:b2, so two PRMTs build the
-// windows of four groups and one shift + mask yields two codes at a time.  The 8 possible
-// values bf16(float(code - 4) * scale) per scale group live one per lane and are fetched with
-// a shuffle instead of being recomputed per channel.  `qv[4 r + m]` = q[32 r + 8 m + sub].
+// windows of four groups and one shift + mask leaves two codes at bit 0 of the two halves of a
+// register.  Read as bf16 such a half is the subnormal code * 2^-133, and one packed fma with
+// S = scale * 2^100 and C = -4 * 2^-133 * S yields 2^-33 * bf16_rn((code - 4) * scale) for both:
+// a single rounding, and a power of two commutes with it (K scales between 2^-93 and 2^27, or
+// zero -- the scan's dequantisation rests on the same identity).  `qv[4 r + m]` =
+// 2^33 * q[32 r + 8 m + sub], so every product is the exact q * k_hat of the canonical order.
 // Every lane of the warp must call this; lanes of a candidate get the same value.
 __device__ __forceinline__ float canon_score_k3_x8(const float (&qv)[16], const uint32_t* row, float attn, int lane) {
   const int sub = lane & 7;
-  const uint32_t base2 = static_cast<uint32_t>(lane & 24) * 0x00010001u;  // first lane of this candidate, both halves
   const uint32_t sw = row[12];
-  const float code_f = static_cast<float>(sub - 4);
-  const float lut0 = __bfloat162float(__float2bfloat16_rn(__fmul_rn(code_f, __uint_as_float(sw << 16))));
-  const float lut1 = __bfloat162float(__float2bfloat16_rn(__fmul_rn(code_f, __uint_as_float(sw & 0xFFFF0000u))));
+  const uint32_t sc0 = prmt(sw, sw, 0x1010u), sc1 = prmt(sw, sw, 0x3232u);   // each group scale in both halves
+  const uint32_t S0 = mul_bf16x2(sc0, 0x71807180u), C0 = mul_bf16x2(sc0, 0xB000B000u);   // * 2^100, * -2^-31
+  const uint32_t S1 = mul_bf16x2(sc1, 0x71807180u), C1 = mul_bf16x2(sc1, 0xB000B000u);
   const bool early = sub <= 4;
   const int sh = early ? 13 - 3 * sub : 21 - 3 * sub;
   float part[4] = {0.f, 0.f, 0.f, 0.f};
@@ -109,17 +111,14 @@ __device__ __forceinline__ float canon_score_k3_x8(const float (&qv)[16], const 
   for (int r = 0; r < 4; ++r) {
     const uint32_t p0 = row[r], p1 = row[4 + r], p2 = row[8 + r];
     const uint32_t hi = early ? p0 : p1, lo = early ? p1 : p2;
-    const uint32_t c01 = and_or(prmt(lo, hi, 0x5140u) >> sh, 0x00070007u, base2);   // groups 4r, 4r+1
-    const uint32_t c23 = and_or(prmt(lo, hi, 0x7362u) >> sh, 0x00070007u, base2);   // groups 4r+2, 4r+3
-    const float lut = (r < 2) ? lut0 : lut1;
-    const float k0 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c01 & 0xFFFFu));
-    const float k1 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c01 >> 16));
-    const float k2 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c23 & 0xFFFFu));
-    const float k3 = __shfl_sync(0xFFFFFFFFu, lut, static_cast<int>(c23 >> 16));
-    part[0] = __fmaf_rn(qv[4 * r], k0, part[0]);
-    part[1] = __fmaf_rn(qv[4 * r + 1], k1, part[1]);
-    part[2] = __fmaf_rn(qv[4 * r + 2], k2, part[2]);
-    part[3] = __fmaf_rn(qv[4 * r + 3], k3, part[3]);
+    const uint32_t c01 = (prmt(lo, hi, 0x5140u) >> sh) & 0x00070007u;   // groups 4r, 4r+1
+    const uint32_t c23 = (prmt(lo, hi, 0x7362u) >> sh) & 0x00070007u;   // groups 4r+2, 4r+3
+    const uint32_t k01 = fma_bf16x2(c01, (r < 2) ? S0 : S1, (r < 2) ? C0 : C1);
+    const uint32_t k23 = fma_bf16x2(c23, (r < 2) ? S0 : S1, (r < 2) ? C0 : C1);
+    part[0] = __fmaf_rn(qv[4 * r], __uint_as_float(k01 << 16), part[0]);
+    part[1] = __fmaf_rn(qv[4 * r + 1], __uint_as_float(k01 & 0xFFFF0000u), part[1]);
+    part[2] = __fmaf_rn(qv[4 * r + 2], __uint_as_float(k23 << 16), part[2]);
+    part[3] = __fmaf_rn(qv[4 * r + 3], __uint_as_float(k23 & 0xFFFF0000u), part[3]);
   }
   // butterfly distances 16 and 8 pair partials held by this lane, 4, 2, 1 pair lanes
   float t = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
@@ -334,6 +333,19 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   if (tid == 0) { sm.ncand = 0; sm.tbin = -1; }
   for (int i = tid; i < kBins; i += NT) hist[i] = 0;
   for (int i = tid; i < p.sort_n; i += NT) keys[i] = 0ull;
+
+  // what this block reads first once the scan is done: warm the address translations now
+  if (FUSED && warp == 0) {
+    const void* first = p.part_m + pbase * kHeadsPad;
+    if (lane == 1) first = p.part_smax + pbase * 2;
+    if (lane == 2) first = tp.part_l + pbase * kHeadsPad;
+    if (lane == 3) first = tp.part_o + pbase * (kHeadsPad * JF_HEAD_DIM);
+    if (lane == 4) first = srow;
+    if (lane == 5) first = LEAN ? static_cast<const void*>(p.pmax + bh * p.np_stride) : static_cast<const void*>(srow + p.max_S - 1);
+    if (lane == 6) first = p.block_table + static_cast<int64_t>(b) * p.max_blocks;
+    if (lane == 7) first = out_idx;
+    if (lane < 8) prefetch_l2(first);
+  }
 
   // ---- the scan's results: split statistics first (small), then the 128 KB score chunk ----
   if (FUSED) pdl_wait();
@@ -856,7 +868,7 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             // eight lanes per candidate, four candidates per warp and round
             float qv[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) qv[i] = sm.q[32 * (i >> 2) + 8 * (i & 3) + (lane & 7)];
+            for (int i = 0; i < 16; ++i) qv[i] = sm.q[32 * (i >> 2) + 8 * (i & 3) + (lane & 7)] * 8589934592.0f;   // 2^33, see canon_score_k3_x8
 #pragma unroll
             for (int g = 0; g < kGroups; ++g) {
               // groups 0..g have landed once at most (kGroups - 1 - g) K groups and the V group are in flight
