@@ -66,7 +66,7 @@ BYTES_PER_TOKEN_HEAD = {"k3v2": 88, "k4v4": 132}
 MODE_BITS = {"k3v2": (3, 2, 64), "k4v4": (4, 4, 128)}
 # dram__bytes_read.sum + dram__bytes_write.sum of the scan kernel per (token, KV head), from the ncu
 # captures summarised under profiles/ (scaled to a launch by the units it processes)
-DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 91.2, "k4v4": 137.3}
+DRAM_BYTES_PER_TOKEN_HEAD = {"k3v2": 94.9, "k4v4": 137.3}
 METRIC = "decode_attn_packed_kv_GBps"
 
 
