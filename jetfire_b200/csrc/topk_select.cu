@@ -4,8 +4,11 @@
 // tensor-core accumulation (jetfire_vllm/csrc/int3_qk_scores.cu:426-554): which position
 // wins near the k-th score depends on an unspecified summation order, and the output order
 // and the choice among ties depend on atomics.  Here selection is two-tier:
-//   1. a 2048-bin histogram of the approximate scores (bin width 1/64 below an upper bound
-//      of the row maximum) finds the bin T that holds the k-th largest approximate score;
+//   1. a 2048-bin histogram (bin width 1/64 below an upper bound of the row maximum) of the
+//      maxima of small groups of positions -- taken from the staged row, or, for long K3V2 rows,
+//      the page-pair maxima the scan left -- finds a bin T at or below the k-th largest
+//      approximate score (the k-th largest group maximum is a lower bound of it); rows the bins
+//      do not fit get the k-th largest approximate score exactly from a radix select;
 //   2. every position whose approximate score can still beat it -- bins <= T + ceil(2*delta*64)
 //      + 1, with delta a bound on |approximate - canonical| (fp32 summation-order error only,
 //      the scan dequantises with the reference's rounding) -- is re-scored in the canonical
