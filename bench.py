@@ -328,10 +328,10 @@ def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=Non
         L.q_host = q_full[shard.b_start:shard.b_start + B, shard.q_start:shard.q_start + H_q].contiguous().pin_memory()
         L.q = L.q_host.to(device)
         L.call = ops.DecodeCall(w["mode"], L.q, L.k_data, L.k_scales, L.v_data, L.v_scales, block_table, seq_lens,
-                                w["ctx"], H_q, H_kv, 16, w["top_k"], 128 ** -0.5, stage_b=w["stage_b"])
+                                w["ctx"], H_q, H_kv, 16, w["top_k"], 128 ** -0.5, stage_b=w["stage_b"], slots_i32=True)
         L.o_new = torch.zeros(B, H_q, 128, dtype=dtype, device=device)
         L.o_new_host = torch.zeros(B, H_q, 128, dtype=dtype).pin_memory()
-        L.slots_host = torch.empty(B, H_q, w["top_k"], dtype=torch.int64).pin_memory()
+        L.slots_host = torch.empty(B, H_q, w["top_k"], dtype=torch.int32).pin_memory()   # 32-bit slot lists: half the D2H
         L.out = torch.empty(B, H_q, 128, dtype=dtype, device=device)
         L.out_host = torch.empty(B, H_q, 128, dtype=dtype).pin_memory()
         L.event = torch.cuda.Event()
@@ -987,7 +987,7 @@ def main():
             for L in e2e_layers:
                 L.q.copy_(L.q_host, non_blocking=True)
                 L.call.fused()
-                L.slots_host.copy_(L.call.out["topk_slots"], non_blocking=True)
+                L.slots_host.copy_(L.call.out["topk_slots_i32"], non_blocking=True)
                 L.event.record(main_s)
             # The next layer's correction is queued before the previous one is waited for, so the
             # workers flow from one job into the next; merges are launched as jobs complete.
@@ -1011,7 +1011,7 @@ def main():
             for L in e2e_layers:
                 L.q.copy_(L.q_host, non_blocking=True)
                 L.call.fused()
-                L.slots_host.copy_(L.call.out["topk_slots"], non_blocking=True)
+                L.slots_host.copy_(L.call.out["topk_slots_i32"], non_blocking=True)
                 torch.cuda.current_stream().synchronize()
                 L.host_call.run()
                 L.o_new.copy_(L.o_new_host, non_blocking=True)
@@ -1043,7 +1043,7 @@ def main():
         esz = 2
         n_e2e = len(e2e_layers)
         h2d = n_e2e * 2 * shard.b_count * shard.q_count * 128 * esz
-        d2h = n_e2e * (shard.b_count * shard.q_count * w["top_k"] * 8 + shard.b_count * shard.q_count * 128 * esz)
+        d2h = n_e2e * (shard.b_count * shard.q_count * w["top_k"] * 4 + shard.b_count * shard.q_count * 128 * esz)
         # dt covers n_e2e layers; ms_per_step and tokens/s are scaled to the workload's layer count
         dt_full, dts_full = dt * n_layers / n_e2e, dt_serial * n_layers / n_e2e
         e2e = {"value": layer_bytes(w) * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d * world,

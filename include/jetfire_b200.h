@@ -208,6 +208,9 @@ typedef struct jf_decode_args {
   float*   softmax_inv_z; /* optional (B, H_q) 1 / sum exp(s - m)                   */
   void*    workspace;     /* >= jf_decode_workspace_bytes(...), 256-byte aligned    */
   uint64_t workspace_bytes;
+  int32_t* topk_slots_i32; /* optional (B, H_q, top_k): the selected slots once more, as 32-bit
+                              integers (num_slots < 2^31), for a device-to-host copy of half the
+                              size; topk_slots may then be NULL.  No counterpart in the reference. */
 } jf_decode_args;
 
 uint64_t    jf_decode_workspace_bytes(int32_t mode, int32_t B, int32_t H_q, int32_t H_kv,
@@ -291,6 +294,13 @@ jf_status_t jf_cpu_topk_attn(const void* q, const void* k_shadow, const void* v_
                              const int64_t* head_map, const int64_t* ts_buf, void* o_new,
                              int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
                              int64_t num_slots, int32_t K, float scale, int64_t* done_flag);
+/* The same with the slots as 32-bit integers (jf_decode_args.topk_slots_i32): half the bytes on
+ * the device-to-host copy of the selected slots.  No counterpart in the reference (its slot
+ * lists are int64 throughout). */
+jf_status_t jf_cpu_topk_attn_i32(const void* q, const void* k_shadow, const void* v_shadow,
+                                 const int64_t* head_map, const int32_t* ts_buf, void* o_new,
+                                 int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                 int64_t num_slots, int32_t K, float scale, int64_t* done_flag);
 /* Host-side wait for a completion flag written by the correction workers (the host half of
  * wait_and_blend_unnorm_into, jetfire_vllm/csrc/blend.cu:320-376): returns JF_OK once *flag is
  * non-zero, JF_ERR_TIMEOUT after timeout_ms.  Does not touch the GPU. */
@@ -313,6 +323,11 @@ jf_status_t jf_pool_submit_ticket(const void* q, const void* k_shadow, const voi
                                   int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
                                   int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
                                   int64_t* ticket);
+jf_status_t jf_pool_submit_ticket_i32(const void* q, const void* k_shadow, const void* v_shadow,
+                                      const int64_t* head_map, const int32_t* ts_buf, void* o_new,
+                                      int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                      int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
+                                      int64_t* ticket);
 jf_status_t jf_pool_wait_timeout(int32_t timeout_ms);
 jf_status_t jf_pool_wait_ticket(int64_t ticket, int32_t timeout_ms);
 jf_status_t jf_pool_shutdown(void);
@@ -330,6 +345,11 @@ jf_status_t jf_submit_ctx_create(const void* q, const void* k_shadow, const void
                                  int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
                                  int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
                                  int32_t wait_ms, int64_t* handle);
+jf_status_t jf_submit_ctx_create_i32(const void* q, const void* k_shadow, const void* v_shadow,
+                                     const int64_t* head_map, const int32_t* ts_buf, void* o_new,
+                                     int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                     int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
+                                     int32_t wait_ms, int64_t* handle);
 jf_status_t jf_submit_ctx_destroy(int64_t handle);
 jf_status_t jf_submit_ctx_status(int64_t handle);
 jf_status_t jf_stream_submit_cpu_topk_attn(jf_stream_t stream, int64_t handle);

@@ -43,6 +43,7 @@ class DecodeArgs(C.Structure):
         ("o_hat", C.c_void_p), ("o_old_unnorm", C.c_void_p), ("W", C.c_void_p),
         ("softmax_m", C.c_void_p), ("softmax_inv_z", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+        ("topk_slots_i32", C.c_void_p),
     ]
 
 
@@ -89,6 +90,8 @@ _SIGS = {
     "jf_merge_correct": (C.c_int32, [C.c_void_p] * 5 + [C.c_int32] * 3 + [C.c_void_p]),
     "jf_cpu_topk_attn": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                        C.c_void_p]),
+    "jf_cpu_topk_attn_i32": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
+                                                                           C.c_void_p]),
     "jf_wait_flag": (C.c_int32, [C.c_void_p, C.c_int32]),
     "jf_set_cpu_attn_threads": (C.c_int32, [C.c_int32]),
     "jf_get_cpu_attn_threads": (C.c_int32, []),
@@ -97,11 +100,16 @@ _SIGS = {
                                                                      C.c_void_p]),
     "jf_pool_submit_ticket": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                             C.c_void_p, C.POINTER(C.c_int64)]),
+    "jf_pool_submit_ticket_i32": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
+                                                                                C.c_void_p, C.POINTER(C.c_int64)]),
     "jf_pool_wait_timeout": (C.c_int32, [C.c_int32]),
     "jf_pool_wait_ticket": (C.c_int32, [C.c_int64, C.c_int32]),
     "jf_submit_ctx_create": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                            C.c_void_p, C.c_int32,
                                                                            C.POINTER(C.c_int64)]),
+    "jf_submit_ctx_create_i32": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
+                                                                               C.c_void_p, C.c_int32,
+                                                                               C.POINTER(C.c_int64)]),
     "jf_submit_ctx_destroy": (C.c_int32, [C.c_int64]),
     "jf_submit_ctx_status": (C.c_int32, [C.c_int64]),
     "jf_stream_submit_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),

@@ -40,6 +40,7 @@ class JetFireConfig:
     cpu_attn_threads: int = 32            # :179
     max_batch_size: int = 32
     enabled: bool = True
+    slots_i32: bool = True                # selected slots cross to the host as int32 (the reference: int64)
 
     @property
     def scheme(self) -> QuantScheme:
@@ -87,7 +88,8 @@ def get_jetfire_config() -> JetFireConfig:
     if threads <= 0:
         raise ValueError("JETFIRE_CPU_ATTN_THREADS must be positive")
     _CONFIG = JetFireConfig(mode=mode, top_k=top_k, group_size=group, cpu_attn_threads=threads,
-                            max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32))
+                            max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32),
+                            slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0)
     return _CONFIG
 
 

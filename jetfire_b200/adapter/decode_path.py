@@ -60,9 +60,9 @@ def _decode_unsupported(*, impl, layer, query, attn_metadata, cfg: JetFireConfig
 class _DecodeBuffers:
     """Pinned staging for one (batch, heads, top_k) shape."""
 
-    def __init__(self, B, H_q, K, dtype):
+    def __init__(self, B, H_q, K, dtype, slot_dtype=torch.int64):
         self.q_host = torch.empty(B, H_q, 128, dtype=dtype).pin_memory()
-        self.ts_host = torch.empty(B, H_q, K, dtype=torch.int64).pin_memory()
+        self.ts_host = torch.empty(B, H_q, K, dtype=slot_dtype).pin_memory()
         self.o_new_host = torch.empty(B, H_q, 128, dtype=dtype).pin_memory()
 
 
@@ -99,15 +99,18 @@ def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table
     lens = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
     max_S = min(int(bt.shape[1]) * store.block_size, ((int(max_seq_len) + 15) // 16) * 16)
     call = ops.DecodeCall(cfg.kernel_mode, q, store.k_data, store.k_scales, store.v_data, store.v_scales,
-                          bt, lens, max_S, num_heads, store.num_kv_heads, store.block_size, top_k, scale)
+                          bt, lens, max_S, num_heads, store.num_kv_heads, store.block_size, top_k, scale,
+                          slots_i32=cfg.slots_i32)
     call.fused()
     res = call.result()
-    key = (B, num_heads, top_k, q.dtype)
+    slot_dtype = torch.int32 if cfg.slots_i32 else torch.int64
+    key = (B, num_heads, top_k, q.dtype, slot_dtype)
     buf = _BUFFERS.get(key)
     if buf is None:
-        buf = _BUFFERS[key] = _DecodeBuffers(B, num_heads, top_k, q.dtype)
+        buf = _BUFFERS[key] = _DecodeBuffers(B, num_heads, top_k, q.dtype, slot_dtype)
     buf.q_host.copy_(q, non_blocking=True)
-    buf.ts_host.copy_(res.topk_slots, non_blocking=True)
+    # the slots cross to the host as 32-bit integers (half the bytes) unless configured otherwise
+    buf.ts_host.copy_(call.out["topk_slots_i32"] if cfg.slots_i32 else res.topk_slots, non_blocking=True)
     call.status()   # synchronises the stream; raises if a bounded wait inside a kernel ran out
     _set_worker_count(cfg)
     ops.cpu_topk_attn(buf.q_host, store.k_shadow, store.v_shadow, None, buf.ts_host, buf.o_new_host, scale)

@@ -92,7 +92,8 @@ struct Job {
   const uint16_t* ks;
   const uint16_t* vs;
   const int64_t* head_map;
-  const int64_t* ts;
+  const void* ts;     // selected slots, (B, H_q, K): 64-bit integers, or 32-bit ones when ts_i32
+  bool ts_i32;
   uint16_t* o;
   int dtype, B, H_q, H_kv, K;
   int64_t num_slots;
@@ -105,6 +106,10 @@ struct Scratch {
   std::vector<float> vrows;  // K x 128 fp32 copies of the gathered V rows
   std::vector<int64_t> slots;
 };
+
+inline int64_t slot_at(const Job& j, int64_t i) {
+  return j.ts_i32 ? static_cast<int64_t>(static_cast<const int32_t*>(j.ts)[i]) : static_cast<const int64_t*>(j.ts)[i];
+}
 
 inline float load_elem(const uint16_t* p, int dtype) { return dtype == JF_DTYPE_BF16 ? bf16_to_f32(*p) : fp16_to_f32(*p); }
 
@@ -146,7 +151,7 @@ void row_generic(const Job& j, Scratch& sc, int64_t b, int64_t h) {
   float max_score = -INFINITY;
   bool any_valid = false;
   for (int k = 0; k < K; ++k) {
-    const int64_t slot = j.ts[bh * K + k];
+    const int64_t slot = slot_at(j, bh * K + k);
     const int64_t hk = j.head_map ? j.head_map[bh * K + k] : h / G;
     if (slot < 0 || slot >= j.num_slots || hk < 0 || hk >= j.H_kv) {
       scores[k] = -INFINITY;
@@ -213,7 +218,7 @@ JF_AVX512 void row_avx512(const Job& j, Scratch& sc, int64_t b, int64_t h) {
   // resolve row indices first so that prefetches can run ahead
   bool any_valid = false;
   for (int k = 0; k < K; ++k) {
-    const int64_t slot = j.ts[bh * K + k];
+    const int64_t slot = slot_at(j, bh * K + k);
     const int64_t hk = j.head_map ? j.head_map[bh * K + k] : h / G;
     const bool ok = !(slot < 0 || slot >= j.num_slots || hk < 0 || hk >= j.H_kv);
     slots[k] = ok ? (hk * j.num_slots + slot) * D : -1;
@@ -473,13 +478,14 @@ int default_threads() {
   return n > 64 ? 64 : n;
 }
 
-jf_status_t make_job(Job& j, const void* q, const void* ks, const void* vs, const int64_t* hm, const int64_t* ts,
+jf_status_t make_job(Job& j, const void* q, const void* ks, const void* vs, const int64_t* hm, const void* ts,
                      void* o, int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots, int32_t K,
-                     float scale, int64_t* done_flag) {
+                     float scale, int64_t* done_flag, bool ts_i32 = false) {
   if (!q || !ks || !vs || !ts || !o) return JF_ERR_ARG;
   if (B <= 0 || H_q <= 0 || H_kv <= 0 || K <= 0 || num_slots <= 0 || H_q % H_kv != 0) return JF_ERR_ARG;
   if (dtype != JF_DTYPE_BF16 && dtype != JF_DTYPE_FP16) return JF_ERR_UNSUPPORTED;
-  j = Job{static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ks), static_cast<const uint16_t*>(vs), hm, ts,
+  if (ts_i32 && num_slots > 0x7FFFFFFFll) return JF_ERR_ARG;
+  j = Job{static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ks), static_cast<const uint16_t*>(vs), hm, ts, ts_i32,
           static_cast<uint16_t*>(o), dtype, B, H_q, H_kv, K, num_slots, scale, done_flag};
   return JF_OK;
 }
@@ -599,6 +605,30 @@ extern "C" jf_status_t jf_cpu_topk_attn(const void* q, const void* k_shadow, con
   return jf_pool_wait_timeout(30000);
 }
 
+// The same three calls for slot lists of 32-bit integers (half the bytes on the device-to-host copy).
+extern "C" jf_status_t jf_pool_submit_ticket_i32(const void* q, const void* k_shadow, const void* v_shadow,
+                                                 const int64_t* head_map, const int32_t* ts_buf, void* o_new,
+                                                 int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots,
+                                                 int32_t K, float scale, int64_t* done_flag, int64_t* ticket) {
+  if (!ticket) return JF_ERR_ARG;
+  Job j;
+  jf_status_t st = make_job(j, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                            scale, done_flag, true);
+  if (st != JF_OK) return st;
+  return submit_job(j, ticket);
+}
+
+extern "C" jf_status_t jf_cpu_topk_attn_i32(const void* q, const void* k_shadow, const void* v_shadow,
+                                            const int64_t* head_map, const int32_t* ts_buf, void* o_new, int32_t dtype,
+                                            int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots, int32_t K,
+                                            float scale, int64_t* done_flag) {
+  int64_t ticket = 0;
+  jf_status_t st = jf_pool_submit_ticket_i32(q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv,
+                                             num_slots, K, scale, done_flag, &ticket);
+  if (st != JF_OK) return st;
+  return jf_pool_wait_ticket(ticket, 30000);
+}
+
 // ---- stream-ordered submit / wait -----------------------------------------------------
 // The reference queues the host correction into the CUDA stream with cudaLaunchHostFunc
 // (jetfire_vllm/csrc/cpu_topk_attn.cpp:1268-1290, :2239-2312): one callback hands the job to
@@ -655,6 +685,22 @@ extern "C" jf_status_t jf_submit_ctx_create(const void* q, const void* k_shadow,
   auto* c = new SubmitCtx();
   jf_status_t st = make_job(c->job, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
                             scale, done_flag);
+  if (st != JF_OK) { delete c; return st; }
+  if (!done_flag) c->job.done_flag = &c->own_flag;
+  if (wait_ms > 0) c->wait_ms = wait_ms;
+  *handle = static_cast<int64_t>(reinterpret_cast<intptr_t>(c));
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_submit_ctx_create_i32(const void* q, const void* k_shadow, const void* v_shadow,
+                                            const int64_t* head_map, const int32_t* ts_buf, void* o_new,
+                                            int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots,
+                                            int32_t K, float scale, int64_t* done_flag, int32_t wait_ms,
+                                            int64_t* handle) {
+  if (!handle) return JF_ERR_ARG;
+  auto* c = new SubmitCtx();
+  jf_status_t st = make_job(c->job, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                            scale, done_flag, true);
   if (st != JF_OK) { delete c; return st; }
   if (!done_flag) c->job.done_flag = &c->own_flag;
   if (wait_ms > 0) c->wait_ms = wait_ms;

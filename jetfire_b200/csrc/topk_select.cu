@@ -38,7 +38,8 @@ struct TopkParams {
   const int64_t* block_table;
   const int32_t* seq_lens;
   int64_t* topk_idx;
-  int64_t* topk_slots;
+  int64_t* topk_slots;       // either may be null, not both
+  int32_t* topk_slots_i32;
   int32_t* status;
   int64_t num_slots;
   int B, H_q, H_kv, G, max_S, max_blocks, splits, top_k, sort_n, q_dtype;
@@ -311,7 +312,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   const int n_seq_raw = p.seq_lens[b];
   const int n_seq = min(n_seq_raw, p.max_S);
   int64_t* out_idx = p.topk_idx + bh * K;
-  int64_t* out_slot = p.topk_slots + bh * K;
+  int64_t* out_slot = p.topk_slots ? p.topk_slots + bh * K : nullptr;
+  int32_t* out_slot32 = p.topk_slots_i32 ? p.topk_slots_i32 + bh * K : nullptr;
 
   // ---- query row (exact values), per-group L1 norms, INT8 model for K4 ----
   if (tid < JF_HEAD_DIM) sm.q[tid] = Elem<DT>::to_f32(q_bits);
@@ -1043,7 +1045,8 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       slot = prefetch ? late.cand_slot[perm[r]] : slot_of(ctx, static_cast<int>(idx));
     }
     out_idx[r] = idx;
-    out_slot[r] = slot;
+    if (out_slot) out_slot[r] = slot;
+    if (out_slot32) out_slot32[r] = static_cast<int32_t>(slot);
   }
 
   if (FUSED) {
@@ -1110,7 +1113,8 @@ TailParams make_tail_params(const jf_decode_args* a, const Workspace& ws) {
 jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fused) {
   jf_status_t st = validate_decode_args(a);
   if (st != JF_OK) return st;
-  if (!a->topk_idx || !a->topk_slots) return JF_ERR_ARG;
+  if (!a->topk_idx || (!a->topk_slots && !a->topk_slots_i32)) return JF_ERR_ARG;
+  if (a->topk_slots_i32 && a->num_slots > 0x7FFFFFFFll) return JF_ERR_ARG;
   if (fused && (!a->o_hat || !a->o_old_unnorm || !a->W)) return JF_ERR_ARG;
   Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   TopkParams sp{};
@@ -1119,7 +1123,7 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   sp.part_m = ws.part_m; sp.part_smax = ws.part_smax;
   sp.q = a->q; sp.k_data = a->k_data; sp.k_scales = static_cast<const uint16_t*>(a->k_scales);
   sp.block_table = a->block_table; sp.seq_lens = a->seq_lens;
-  sp.topk_idx = a->topk_idx; sp.topk_slots = a->topk_slots; sp.status = ws.status;
+  sp.topk_idx = a->topk_idx; sp.topk_slots = a->topk_slots; sp.topk_slots_i32 = a->topk_slots_i32; sp.status = ws.status;
   sp.num_slots = a->num_slots;
   const HeadGeom hg = head_geom(a->H_q, a->H_kv);
   sp.B = a->B; sp.H_q = a->H_q; sp.H_kv = hg.H_kv; sp.G = hg.G; sp.kv_shift = hg.shift;

@@ -267,11 +267,14 @@ class DecodeCall:
     reference's batch > 1 arithmetic, weights rounded to 127 levels per 32-token tile).
     ``parts``: ``"all"``, ``"k"`` (scores and softmax sums only: q and the K cache; V tensors may be
     None) or ``"v"`` (output partials from ``scores``, an input then: the V cache; q and K tensors
-    may be None).  ``scores`` / ``topk_idx``: existing tensors to use instead of fresh ones."""
+    may be None).  ``scores`` / ``topk_idx``: existing tensors to use instead of fresh ones.
+    ``slots_i32``: also write the selected slots as 32-bit integers (``out["topk_slots_i32"]``) --
+    half the bytes for the copy to the host; the host correction takes either width."""
 
     def __init__(self, mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
                  max_S, H_q, H_kv, block_size, top_k, attn_scale, *, workspace=None,
-                 want_scores=False, out=None, stage_b="fp32", parts="all", scores=None, topk_idx=None):
+                 want_scores=False, out=None, stage_b="fp32", parts="all", scores=None, topk_idx=None,
+                 slots_i32=False):
         name = "fused_attn_topk"
         mode_id = MODE_IDS[mode] if isinstance(mode, str) else int(mode)
         k_bits, v_bits, gs = MODE_BITS[mode_id]
@@ -335,6 +338,12 @@ class DecodeCall:
         _require(need_k or scores is not None, f"{name}: parts='v' needs the scores")
         _require(out["topk_idx"].is_cuda and out["topk_idx"].dtype == torch.int64 and out["topk_idx"].is_contiguous()
                  and tuple(out["topk_idx"].shape) == (B, H_q, top_k), f"{name}: topk_idx must be contiguous int64 (B, H_q, k)")
+        if slots_i32 and "topk_slots_i32" not in out:
+            out["topk_slots_i32"] = torch.empty(B, H_q, top_k, dtype=torch.int32, device=dev)
+        s32 = out.get("topk_slots_i32")
+        if s32 is not None:
+            _require(s32.is_cuda and s32.dtype == torch.int32 and s32.is_contiguous()
+                     and tuple(s32.shape) == (B, H_q, top_k), f"{name}: topk_slots_i32 must be contiguous int32 (B, H_q, k)")
         self.out = out
         self.scores = scores
         self._keep = (q, k_data, k_scales, v_data, v_scales, block_table, seq_lens, workspace)
@@ -355,6 +364,7 @@ class DecodeCall:
         a.o_hat, a.o_old_unnorm, a.W = out["o_hat"].data_ptr(), out["o_old_unnorm"].data_ptr(), out["W"].data_ptr()
         a.softmax_m, a.softmax_inv_z = out["softmax_m"].data_ptr(), out["softmax_inv_z"].data_ptr()
         a.workspace, a.workspace_bytes = ws_ptr, ws_bytes
+        a.topk_slots_i32 = ptr(s32)
         self.args = a
         self._ref = C.byref(a)
 
@@ -571,7 +581,8 @@ def _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag,
     H_kv, num_slots = k_shadow.shape[0], k_shadow.shape[1]
     _require(D == 128 and k_shadow.shape[2] == 128, f"{name} currently only supports D=128")
     _require(v_shadow.shape == k_shadow.shape, f"{name}: k/v mirror shape mismatch")
-    _require(ts_buf.dtype == torch.int64 and ts_buf.shape[:2] == (B, H_q), f"{name}: ts_buf must be (B,H_q,K) int64")
+    _require(ts_buf.dtype in (torch.int64, torch.int32) and ts_buf.shape[:2] == (B, H_q),
+             f"{name}: ts_buf must be (B,H_q,K) int64 (or int32: the 32-bit slot list of DecodeCall(slots_i32=True))")
     _require(o_new.shape == q.shape, f"{name}: o_new shape mismatch")
     hm_ptr = None
     if head_map is not None:
@@ -587,15 +598,24 @@ def _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag,
             _dtype_id(q), B, H_q, H_kv, num_slots, ts_buf.shape[2], float(scale), flag_ptr)
 
 
+def _i32(ts_buf) -> bool:
+    return ts_buf.dtype == torch.int32
+
+
 def cpu_topk_attn(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None) -> None:
-    """Exact attention over the selected mirror rows, blocking."""
+    """Exact attention over the selected mirror rows, blocking.  ``ts_buf`` int64 as in the
+    reference, or int32."""
     args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag, "cpu_topk_attn")
-    check("cpu_topk_attn", lib.jf_cpu_topk_attn(*args))
+    check("cpu_topk_attn", (lib.jf_cpu_topk_attn_i32 if _i32(ts_buf) else lib.jf_cpu_topk_attn)(*args))
 
 
 def cpu_topk_attn_submit(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None) -> None:
     args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag, "cpu_topk_attn_submit")
-    check("cpu_topk_attn_submit", lib.jf_pool_submit(*args))
+    if _i32(ts_buf):
+        t = C.c_int64(0)
+        check("cpu_topk_attn_submit", lib.jf_pool_submit_ticket_i32(*args, C.byref(t)))
+    else:
+        check("cpu_topk_attn_submit", lib.jf_pool_submit(*args))
 
 
 def cpu_topk_attn_wait(timeout_ms: int = 30000) -> None:
@@ -612,11 +632,15 @@ class HostCorrectionCall:
         self._args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag,
                                 "HostCorrectionCall")
         self._keep = (q, k_shadow, v_shadow, head_map, ts_buf, o_new, done_flag)
+        i32 = _i32(ts_buf)   # 32-bit slot list: the entry points of the same names with the _i32 suffix
+        self._fn_submit = lib.jf_pool_submit_ticket_i32 if i32 else lib.jf_pool_submit_ticket
+        self._fn_run = lib.jf_cpu_topk_attn_i32 if i32 else lib.jf_cpu_topk_attn
+        self._fn_ctx = lib.jf_submit_ctx_create_i32 if i32 else lib.jf_submit_ctx_create
 
     def submit(self) -> int:
         """Queue the job (up to four can wait in the pool); returns its ticket for ``wait_ticket``."""
         t = C.c_int64(0)
-        check("cpu_topk_attn_submit", lib.jf_pool_submit_ticket(*self._args, C.byref(t)))
+        check("cpu_topk_attn_submit", self._fn_submit(*self._args, C.byref(t)))
         return t.value
 
     @staticmethod
@@ -628,14 +652,14 @@ class HostCorrectionCall:
         check("cpu_topk_attn_wait", lib.jf_pool_wait_timeout(int(timeout_ms)))
 
     def run(self) -> None:
-        check("cpu_topk_attn", lib.jf_cpu_topk_attn(*self._args))
+        check("cpu_topk_attn", self._fn_run(*self._args))
 
     # -- stream-ordered form (the reference's create_cpu_topk_submit_ctx /
     #    stream_submit_cpu_topk_attn / stream_wait_cpu_topk_attn, csrc/cpu_topk_attn.cpp:2147-2312) --
     def _handle(self) -> int:
         if getattr(self, "_ctx", None) is None:
             h = C.c_int64(0)
-            check("create_cpu_topk_submit_ctx", lib.jf_submit_ctx_create(*self._args, 0, C.byref(h)))
+            check("create_cpu_topk_submit_ctx", self._fn_ctx(*self._args, 0, C.byref(h)))
             self._ctx = h.value
         return self._ctx
 
@@ -674,7 +698,8 @@ def create_cpu_topk_submit_ctx(q, k_shadow, v_shadow, head_map, ts_buf, o_new, s
     set to 1 when a submitted job is done).  Returns the handle for ``stream_submit_cpu_topk_attn``."""
     args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, flag_host, "create_cpu_topk_submit_ctx")
     h = C.c_int64(0)
-    check("create_cpu_topk_submit_ctx", lib.jf_submit_ctx_create(*args, 0, C.byref(h)))
+    check("create_cpu_topk_submit_ctx",
+          (lib.jf_submit_ctx_create_i32 if _i32(ts_buf) else lib.jf_submit_ctx_create)(*args, 0, C.byref(h)))
     _CTX_KEEP.append((q, k_shadow, v_shadow, head_map, ts_buf, o_new, flag_host))
     return h.value
 

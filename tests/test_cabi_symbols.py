@@ -45,8 +45,9 @@ def test_argument_errors_without_gpu(lib):
 
 
 def test_struct_layout_matches_header(lib):
-    # twelve 4-byte fields, one int64, sixteen pointers, one uint64
-    assert C.sizeof(lib.DecodeArgs) == 48 + 8 + 16 * 8 + 8
+    # twelve 4-byte fields, one int64, sixteen pointers, one uint64, one more pointer
+    assert C.sizeof(lib.DecodeArgs) == 48 + 8 + 16 * 8 + 8 + 8
     assert lib.DecodeArgs.num_slots.offset == 48
     assert lib.DecodeArgs.q.offset == 56
     assert lib.DecodeArgs.workspace_bytes.offset == 56 + 16 * 8
+    assert lib.DecodeArgs.topk_slots_i32.offset == 56 + 16 * 8 + 8

@@ -242,6 +242,28 @@ def test_phases_one_by_one_equal_fused_k4v4_long_row():
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("mode,ctx,top_k", [("k3v2", 1024, 128), ("k4v4", 4096, 256), ("k3v2", 32768, 256)])
+def test_slots_as_32_bit_integers_equal_the_64_bit_list(mode, ctx, top_k):
+    """The optional int32 copy of the selected slots (-1 padding included) equals the int64 list, from
+    the fused call and from the stand-alone select, in both select kernels; the phase-by-phase
+    results of a long K3V2 row (page-maxima select) equal the fused call's bit for bit."""
+    from jetfire_b200 import ops
+    case = Case(mode, 2, 8, 2, ctx, lens=[ctx, max(top_k // 2, ctx // 3 - 5)], seed=19)
+    kd, ks, vd, vs = case.device_cache()
+    args = (case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+            case.ctx, case.H_q, case.H_kv, 16, top_k, case.attn_scale)
+    call = ops.DecodeCall(*args, slots_i32=True)
+    call.fused(); call.status()
+    fused = [t.clone() for t in call.result()[:7]]
+    s32 = call.out["topk_slots_i32"].clone()
+    assert s32.dtype == torch.int32 and torch.equal(s32.to(torch.int64), fused[1])
+    call.out["topk_slots_i32"].fill_(-7)
+    call.scan(); call.select(); call.finish(); call.status()
+    assert torch.equal(call.out["topk_slots_i32"], s32)
+    for a, b in zip(fused, call.result()[:7]):
+        assert torch.equal(a, b)
+
+
 def test_status_record_is_read_once_and_needs_no_initialisation():
     """The workspace's status record counts only when tagged; reading an error clears it.
     The record is written from the host here: no kernel is made to time out."""

@@ -106,6 +106,34 @@ def test_pool_submit_wait_and_single_flight():
         ops.cpu_topk_attn(case.q.float(), case.k_full, case.v_full, None, slots, out, case.attn_scale)
 
 
+def test_slot_lists_of_32_bit_integers_give_the_same_rows():
+    """The host correction takes the selected slots as int64 (the reference's type) or as int32
+    (half the device-to-host bytes): same bits out, through the blocking call, the pool and the
+    prebuilt call; -1 padding and out-of-range slots are skipped in both widths."""
+    from jetfire_b200 import ops
+    case, slots = _correction_inputs()
+    slots = slots.clone()
+    slots[0, 0, -3:] = -1
+    slots[1, 2, 0] = case.num_slots + 5
+    slots32 = slots.to(torch.int32)
+    ops.set_cpu_attn_threads(3)
+    want = torch.empty(2, 8, 128, dtype=torch.bfloat16)
+    ops.cpu_topk_attn(case.q, case.k_full, case.v_full, None, slots, want, case.attn_scale)
+    got = torch.zeros_like(want)
+    ops.cpu_topk_attn(case.q, case.k_full, case.v_full, None, slots32, got, case.attn_scale)
+    assert torch.equal(got, want)
+    got.zero_()
+    ops.cpu_topk_attn_submit(case.q, case.k_full, case.v_full, None, slots32, got, case.attn_scale)
+    ops.cpu_topk_attn_wait(30000)
+    assert torch.equal(got, want)
+    got.zero_()
+    call = ops.HostCorrectionCall(case.q, case.k_full, case.v_full, None, slots32, got, case.attn_scale)
+    ops.HostCorrectionCall.wait_ticket(call.submit())
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        ops.cpu_topk_attn(case.q, case.k_full, case.v_full, None, slots.to(torch.int16), got, case.attn_scale)
+
+
 def test_prebuilt_host_call_equals_plain_call():
     from jetfire_b200 import ops
     case, slots = _correction_inputs()
