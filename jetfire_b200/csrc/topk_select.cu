@@ -179,9 +179,9 @@ __device__ __forceinline__ int score_bin(float top64, float s) {
   return __float_as_int(__fadd_rz(x, 8388608.0f)) & (kBins - 1);
 }
 
-constexpr int kRowChunk = 768;                 // candidates staged in shared memory per round (top-k 512 and its band in one)
+// candidates staged in shared memory per round: a top-k of 512 and its band in one (K4V4 has no band to speak of)
+template <int MODE> struct RowChunk { static constexpr int v = (MODE == JF_MODE_K3V2) ? 768 : 576; };
 constexpr int kChunkVec = 8;                   // float4 reads per thread and pass over a chunk
-constexpr int kChunkPosMax = 4 * kChunkVec * kSelThreads;   // positions of the row held in shared memory at a time (widest block)
 // 32-bit words per staged K row: K3V2 holds 12 of data and one of scales in a 64-byte slot (16-byte copies land aligned)
 template <int MODE> struct RowWords { static constexpr int v = 16; };
 
@@ -203,26 +203,27 @@ template <int MODE>
 struct SelSmemLate {
   union {   // the K rows are done with (canonical scores) before the finish stage starts
     TailSmem<MODE> tail;
-    uint32_t rows[(MODE == JF_MODE_K3V2) ? kRowChunk * RowWords<MODE>::v : 4];   // K3V2: packed K rows + scales (K4V4 re-scores nothing)
+    uint32_t rows[(MODE == JF_MODE_K3V2) ? RowChunk<MODE>::v * RowWords<MODE>::v : 4];   // K3V2: packed K rows + scales (K4V4 re-scores nothing)
   };
-  uint32_t vrows[kRowChunk * TailSmem<MODE>::VW];  // packed V rows of the candidates (fused kernel)
-  int64_t cand_slot[kRowChunk];
-  uint32_t vsc[kRowChunk];                         // V scales
+  uint32_t vrows[RowChunk<MODE>::v * TailSmem<MODE>::VW];  // packed V rows of the candidates (fused kernel)
+  int64_t cand_slot[RowChunk<MODE>::v];
+  uint32_t vsc[RowChunk<MODE>::v];                         // V scales
 };
 
-constexpr size_t kSelChunkBytes = static_cast<size_t>(kChunkPosMax) * 4;
-constexpr size_t kHmChunkBytes = static_cast<size_t>(kChunkVec) * kSelThreads * 2;   // side table of one chunk
+__host__ __device__ constexpr size_t hm_chunk_bytes(int nt) { return static_cast<size_t>(kChunkVec) * nt * 2; }   // side table of one chunk
 constexpr size_t kSelSmemLimit = 227 * 1024;
 // Bytes of the first shared-memory region: the resident score chunk (whose memory the late
 // structures reuse), or -- lean kernel, which never stages the scores -- the late structures alone.
-template <int MODE, bool LEAN>
+template <int MODE, bool LEAN, int NT>
 __host__ __device__ constexpr size_t sel_region0_bytes() {
-  return LEAN ? ((sizeof(SelSmemLate<MODE>) + 127) / 128) * 128 : kSelChunkBytes;
+  constexpr size_t late = ((sizeof(SelSmemLate<MODE>) + 127) / 128) * 128;
+  constexpr size_t chunk = static_cast<size_t>(4 * kChunkVec * NT) * 4;   // the resident chunk of an NT-wide block
+  return LEAN ? late : (chunk > late ? chunk : late);
 }
-__host__ __device__ constexpr size_t sel_smem_bytes(size_t region0, int sort_n, int hm_chunks = 0) {
+__host__ __device__ constexpr size_t sel_smem_bytes(size_t region0, int sort_n, int hm_chunks = 0, int nt = kSelThreads) {
   // region 0 | fixed | keys[sort_n] | cand_score[sort_n] | perm[sort_n] | bucket[sort_n] | hm16[hm_chunks]
   return region0 + sizeof(SelSmemFixed) + static_cast<size_t>(sort_n) * 8 +
-         static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(hm_chunks) * kHmChunkBytes;
+         static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(hm_chunks) * hm_chunk_bytes(nt);
 }
 constexpr int kPmVec = 2;   // lean kernel: float4s of page maxima per thread (rows of up to 4 * kPmVec * threads pages)
 
@@ -240,13 +241,12 @@ constexpr int kPmVec = 2;   // lean kernel: float4s of page maxima per thread (r
 template <int MODE, int DT, bool FUSED, bool LEAN, int NT>
 __global__ void __launch_bounds__(NT, kSelThreads / NT)
 topk_select_kernel(const TopkParams p, const TailParams tp) {
-  static_assert(LEAN || NT == kSelThreads, "the resident-chunk kernel is written for the widest block");
   constexpr int kW = NT / 32;                   // warps of this block
   constexpr int kChunkPos = 4 * kChunkVec * NT; // positions per pass over a chunk
   constexpr int W = RowWords<MODE>::v;         // 32-bit words staged per candidate: data + scales
-  static_assert(sizeof(SelSmemLate<MODE>) <= kSelChunkBytes, "late shared memory must fit in the score chunk");
   static_assert(!LEAN || MODE == JF_MODE_K3V2, "only the K3V2 scan writes page maxima");
-  constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN>();
+  constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN, NT>();
+  constexpr int kRowChunk = RowChunk<MODE>::v;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* chunk = reinterpret_cast<float*>(smem_raw);
   SelSmemLate<MODE>& late = *reinterpret_cast<SelSmemLate<MODE>*>(smem_raw);
@@ -1065,19 +1065,21 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
 
 int pow2_ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
+// What one of two co-resident blocks may use: half of the multiprocessor's 228 KB, less the 1 KB the system keeps per block.
+constexpr size_t kTwoBlockBytes = 228 * 1024 / 2 - 1024;
+
 template <int MODE, int DT, bool LEAN, int NT>
 jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
-  constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN>();
-  const size_t smem = sel_smem_bytes(kRegion0, sp.sort_n, LEAN ? 0 : sp.hm_chunks);
-  constexpr size_t kMaxSmem = LEAN ? sel_smem_bytes(kRegion0, 2 * JF_MAX_TOP_K) : kSelSmemLimit;
-  static_assert(sel_smem_bytes(kSelChunkBytes, 2 * JF_MAX_TOP_K) <= kSelSmemLimit, "select kernel shared memory");
-  // two blocks of the narrow lean kernel share a multiprocessor at the top-k widths that take it
-  static_assert(!LEAN || 2 * (sel_smem_bytes(kRegion0, 1024) + 1024) <= 228 * 1024, "two lean blocks per multiprocessor");
+  constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN, NT>();
+  const size_t smem = sel_smem_bytes(kRegion0, sp.sort_n, LEAN ? 0 : sp.hm_chunks, NT);
+  static_assert(sel_smem_bytes(kRegion0, 2 * JF_MAX_TOP_K) <= kSelSmemLimit, "select kernel shared memory");
+  static_assert(NT == kSelThreads || sel_smem_bytes(kRegion0, 1024) <= kTwoBlockBytes, "two narrow blocks per multiprocessor");
+  if (smem > kSelSmemLimit) return JF_ERR_UNSUPPORTED;
   if (fused) {
-    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true, LEAN, NT>), kMaxSmem);
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, true, LEAN, NT>), kSelSmemLimit);
     JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, true, LEAN, NT>, grid, dim3(NT), smem, stream, sp, tp));
   } else {
-    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, false, LEAN, NT>), kMaxSmem);
+    JF_ENSURE_SMEM((topk_select_kernel<MODE, DT, false, LEAN, NT>), kSelSmemLimit);
     JF_CUDA_TRY(launch_pdl(topk_select_kernel<MODE, DT, false, LEAN, NT>, grid, dim3(NT), smem, stream, sp, tp));
   }
   JF_CUDA_TRY(cudaGetLastError());
@@ -1132,27 +1134,42 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   sp.top_k = a->top_k;
   sp.sort_n = pow2_ceil(2 * a->top_k);
   if (sp.sort_n < 512) sp.sort_n = 512;
-  {  // rows of 2..4 score chunks get the side table if it fits beside the rest
-    const int chunks = (a->max_S + kChunkPosMax - 1) / kChunkPosMax;
-    sp.hm_chunks = (chunks >= 2 && chunks <= 4 && sel_smem_bytes(kSelChunkBytes, sp.sort_n, chunks) <= kSelSmemLimit) ? chunks : 0;
-  }
   sp.q_dtype = a->q_dtype;
   sp.attn_scale = a->attn_scale;
   const TailParams tp = make_tail_params(a, ws);
   const dim3 grid(a->H_q, a->B);
+  // With more rows than multiprocessors the 512-thread block runs two rows per multiprocessor (one
+  // row's chains of dependent memory round trips under the other's arithmetic); otherwise a row's
+  // latency is what counts and the 1024-thread block takes it.
+  const bool many = a->B * a->H_q > num_sms() && sp.sort_n <= 1024;
+  // resident-row kernel: rows of 2..4 score chunks get the side table of float4 maxima if it fits
+  auto side_table = [&](int nt, size_t region0, size_t budget) {
+    const int chunks = (a->max_S + 32 * nt - 1) / (32 * nt);
+    return (chunks >= 2 && chunks <= 4 && sel_smem_bytes(region0, sp.sort_n, chunks, nt) <= budget) ? chunks : 0;
+  };
   if (a->mode == JF_MODE_K3V2) {
     // Long rows take the lean kernel (threshold from the scan's page-pair maxima): enough pairs for
     // the K-th largest pair maximum to be a tight bound, and score rows that 16-byte loads can
-    // read.  With more rows than multiprocessors the narrow block runs two rows per
-    // multiprocessor; otherwise a row's latency is what counts and the wide block takes it.
+    // read (whole pages only: a listed page is fetched whole, and the last row's must end inside
+    // the buffer).
     const int pairs = (a->max_S + 31) / 32;
-    // (whole pages only: a listed page is fetched whole, and the last row's must end inside the buffer)
     const bool lean = pairs >= 4 * a->top_k && (a->max_S & 15) == 0 && (reinterpret_cast<uintptr_t>(sp.scores) & 15) == 0;
-    const bool narrow = a->B * a->H_q > num_sms() && sp.sort_n <= 1024;
-    if (lean && narrow && pairs <= 4 * kPmVec * 512) return launch_select_dtype<JF_MODE_K3V2, true, 512>(a, sp, tp, grid, stream, fused);
+    if (lean && many && pairs <= 4 * kPmVec * 512) return launch_select_dtype<JF_MODE_K3V2, true, 512>(a, sp, tp, grid, stream, fused);
     if (lean && pairs <= 4 * kPmVec * kSelThreads) return launch_select_dtype<JF_MODE_K3V2, true, kSelThreads>(a, sp, tp, grid, stream, fused);
+    constexpr size_t r512 = sel_region0_bytes<JF_MODE_K3V2, false, 512>();
+    if (many && sel_smem_bytes(r512, sp.sort_n, 0, 512) <= kTwoBlockBytes) {
+      sp.hm_chunks = side_table(512, r512, kTwoBlockBytes);
+      return launch_select_dtype<JF_MODE_K3V2, false, 512>(a, sp, tp, grid, stream, fused);
+    }
+    sp.hm_chunks = side_table(kSelThreads, sel_region0_bytes<JF_MODE_K3V2, false, kSelThreads>(), kSelSmemLimit);
     return launch_select_dtype<JF_MODE_K3V2, false, kSelThreads>(a, sp, tp, grid, stream, fused);
   }
+  constexpr size_t r512 = sel_region0_bytes<JF_MODE_K4V4, false, 512>();
+  if (many && sel_smem_bytes(r512, sp.sort_n, 0, 512) <= kTwoBlockBytes) {
+    sp.hm_chunks = side_table(512, r512, kTwoBlockBytes);
+    return launch_select_dtype<JF_MODE_K4V4, false, 512>(a, sp, tp, grid, stream, fused);
+  }
+  sp.hm_chunks = side_table(kSelThreads, sel_region0_bytes<JF_MODE_K4V4, false, kSelThreads>(), kSelSmemLimit);
   return launch_select_dtype<JF_MODE_K4V4, false, kSelThreads>(a, sp, tp, grid, stream, fused);
 }
 

@@ -67,6 +67,18 @@ def test_page_maxima_select_with_ragged_lengths(dtype, B, H_q, H_kv, lens):
     _run(Case("k3v2", B, H_q, H_kv, 32768, lens=lens, seed=62 + B, dtype=dtype), 256)
 
 
+@pytest.mark.parametrize("mode,ctx,lens,top_k,stage_b", [
+    ("k4v4", 4096, [4096, 4090, 300, 4096, 17], 256, "int8p"),       # one chunk of a 512-thread block
+    ("k4v4", 40000, [40000, 39999, 16385, 20000, 5], 256, "fp32"),   # three chunks, streamed twice (no side table)
+    ("k3v2", 8192, [8192, 8000, 600, 8192, 100], 256, "fp32"),       # too short for the page-maxima kernel
+    ("k3v2", 20004, [20004, 16384, 16383, 9, 20000], 128, "fp32"),   # row stride not a multiple of 16: staged rows
+])
+def test_staged_row_select_with_two_blocks_per_multiprocessor(mode, ctx, lens, top_k, stage_b):
+    """160 rows, more than multiprocessors: the kernel that stages the row in shared memory also
+    comes as a 512-thread block (16384 positions per chunk), two to a multiprocessor."""
+    _run(Case(mode, 5, 32, 8, ctx, lens=lens, seed=71), top_k, stage_b=stage_b)
+
+
 @pytest.mark.parametrize("mode,top_k,ctx", [("k4v4", 1024, 8192), ("k3v2", 2048, 8192), ("k3v2", 1024, 2000)])
 def test_wide_top_k(mode, top_k, ctx):
     """top-k above 512: the sort buffer no longer fits the counting / bucket ranking (bitonic
