@@ -90,6 +90,8 @@ def parse_args():
     ap.add_argument("--no-extra", action="store_true", help="skip the extra single-GPU configurations")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle replay of one timed row")
     ap.add_argument("--cpu-threads", type=int, default=0, help="host correction threads (0 = cores / ranks - 1)")
+    ap.add_argument("--as-shard", metavar="R/N", help="single GPU only: run the shard that rank R of an N-GPU run owns "
+                    "(same seeded data, no gather); every figure then counts that shard's bytes")
     return ap.parse_args()
 
 
@@ -792,6 +794,17 @@ def main():
     plan = shard_plan(w["H_q"], w["H_kv"], w["batch"], world)
     shard = plan[rank]
     head_shards = min(world, w["H_kv"])
+    as_shard = None
+    if args.as_shard:
+        if world != 1:
+            raise SystemExit("--as-shard is a single-GPU diagnostic")
+        r_s, n_s = (int(x) for x in args.as_shard.split("/"))
+        if not (0 <= r_s < n_s):
+            raise SystemExit("--as-shard R/N needs 0 <= R < N")
+        shard = shard_plan(w["H_q"], w["H_kv"], w["batch"], n_s)[r_s]
+        as_shard = f"{r_s}/{n_s}"
+    # bytes of one layer of the whole job (of the one shard, in the --as-shard diagnostic)
+    job_layer_bytes = layer_bytes(w, shard.b_count, shard.kv_count) if as_shard else layer_bytes(w)
 
     do_e2e = not args.no_e2e
     # The end-to-end leg needs the full-precision mirror of every layer of the shard in host DRAM.
@@ -813,7 +826,7 @@ def main():
     layers, tables = build_stack(torch, ops, w, shard, device, dtype, mirror_layers)
     t_build = time.perf_counter() - t_build
     n_layers = len(layers)
-    step_bytes_total = layer_bytes(w) * n_layers
+    step_bytes_total = job_layer_bytes * n_layers
 
     # outputs of all layers in one buffer (the gather's send buffer); gathered: TP layout per layer
     my_out = torch.empty(n_layers, shard.b_count, shard.q_count * 128, dtype=dtype, device=device)
@@ -1046,10 +1059,10 @@ def main():
         d2h = n_e2e * (shard.b_count * shard.q_count * w["top_k"] * 4 + shard.b_count * shard.q_count * 128 * esz)
         # dt covers n_e2e layers; ms_per_step and tokens/s are scaled to the workload's layer count
         dt_full, dts_full = dt * n_layers / n_e2e, dt_serial * n_layers / n_e2e
-        e2e = {"value": layer_bytes(w) * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
+        e2e = {"value": job_layer_bytes * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
                "d2h_bytes_per_step": d2h * world, "ms_per_step": dt_full * 1e3, "steps": e2e_steps,
                "layers_measured": n_e2e, "tokens_per_s": w["batch"] / dt_full, "host_threads_per_rank": cpu_threads,
-               "serial_layers": {"value": layer_bytes(w) * n_e2e / dt_serial / 1e9, "unit": "GB/s",
+               "serial_layers": {"value": job_layer_bytes * n_e2e / dt_serial / 1e9, "unit": "GB/s",
                                  "ms_per_step": dts_full * 1e3, "tokens_per_s": w["batch"] / dts_full,
                                  "what": "layer l + 1 starts after layer l's merge (host correction on the critical path)"},
                "timing": "host wall clock around barrier + synchronize (host work is inside the region)"}
@@ -1087,7 +1100,8 @@ def main():
             "sharding": (f"{head_shards} KV-head shard(s) x {world // head_shards} batch shard(s): {shard.kv_count} KV heads, "
                          f"{shard.q_count} query heads, {shard.b_count} sequences per GPU; one NCCL all-gather of the per-head "
                          f"outputs per step into (B, H_q * 128)" + (", captured as a CUDA graph" if gather_in_graph else ""))
-            if world > 1 else "single GPU",
+            if world > 1 else (f"single GPU running the shard of rank {as_shard} ({shard.kv_count} KV heads, {shard.q_count} "
+                               f"query heads, {shard.b_count} sequences)" if as_shard else "single GPU"),
             "data_generator": "counter hash (Irwin-Hall of twelve 16-bit uniforms per element), identical on GPU and CPU",
             "build_s": round(t_build, 1), "oracle_check": check, "gather_check": gather_check}
         line = {
