@@ -79,6 +79,35 @@ def test_staged_row_select_with_two_blocks_per_multiprocessor(mode, ctx, lens, t
     _run(Case(mode, 5, 32, 8, ctx, lens=lens, seed=71), top_k, stage_b=stage_b)
 
 
+def _random_cases(n, seed=2024):
+    """Seeded random geometries: every select kernel (staged row / page maxima, 1024 / 512 threads),
+    every GQA ratio, ragged lengths down to one token, top-k from 32 to 512, both dtypes."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(n):
+        mode = "k3v2" if i % 2 == 0 else "k4v4"
+        H_kv = int(rng.choice([1, 2, 4, 8]))
+        G = int(rng.choice([1, 2, 4, 8, 16]))
+        many_rows = i % 3 == 0
+        B = int(rng.integers(1, 4)) if not many_rows else max(2, -(-149 // (H_kv * G)))
+        top_k = int(rng.choice([32, 64, 128, 256, 512]))
+        # a row stride that is a multiple of 16 and long enough for the page-maxima kernel in a third of the cases
+        ctx = int(rng.choice([128 * top_k, 16 * int(rng.integers(40, 1500)), int(rng.integers(600, 24000))]))
+        ctx = min(ctx, 36000 if B * H_kv * G <= 64 else 12000)
+        lens = [int(rng.integers(1, ctx + 1)) for _ in range(B)]
+        lens[int(rng.integers(0, B))] = ctx
+        stage_b = "int8p" if (mode == "k4v4" and B > 1 and i % 4 == 1) else "fp32"
+        dtype = torch.float16 if i % 5 == 0 else torch.bfloat16
+        out.append(pytest.param(mode, B, H_kv * G, H_kv, ctx, lens, top_k, stage_b, dtype, 900 + i,
+                                id=f"{i}-{mode}-B{B}-H{H_kv * G}x{H_kv}-ctx{ctx}-k{top_k}-{stage_b}"))
+    return out
+
+
+@pytest.mark.parametrize("mode,B,H_q,H_kv,ctx,lens,top_k,stage_b,dtype,seed", _random_cases(24))
+def test_random_geometries(mode, B, H_q, H_kv, ctx, lens, top_k, stage_b, dtype, seed):
+    _run(Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed, dtype=dtype), top_k, stage_b=stage_b)
+
+
 @pytest.mark.parametrize("mode,top_k,ctx", [("k4v4", 1024, 8192), ("k3v2", 2048, 8192), ("k3v2", 1024, 2000)])
 def test_wide_top_k(mode, top_k, ctx):
     """top-k above 512: the sort buffer no longer fits the counting / bucket ranking (bitonic
