@@ -49,20 +49,45 @@ inline int scan_splits(int mode, int q_dtype, int B, int H_kv, int max_S) {
   return target;
 }
 
+// Which select kernel a call takes -- decided from the arguments alone, so that the scan (which
+// then leaves the maxima of groups of pages: K3V2 pairs of pages, K4V4 pages) and the select
+// kernel (which then takes its threshold from them and never stages the row) agree.
+//   narrow: more rows than multiprocessors -> 512-thread blocks, two per multiprocessor;
+//   lean:   the row does not fit one resident chunk of that block (32 positions per thread), there
+//           are enough groups for the K-th largest group maximum to be a tight bound, and the
+//           score rows are whole pages that 16-byte loads can read.
+// Rows of one chunk stay with the kernel that stages them: it is as fast there, and the scan
+// saves the few per cent the maxima cost it.
+struct SelectPlan { bool narrow, lean; };
+inline SelectPlan select_plan(const jf_decode_args* a, const float* scores) {
+  int sort_n = 512;
+  while (sort_n < 2 * a->top_k) sort_n <<= 1;
+  SelectPlan pl;
+  pl.narrow = a->B * a->H_q > num_sms() && sort_n <= 1024;
+  const int groups = (a->max_S + 15) / 16 / (a->mode == JF_MODE_K3V2 ? 2 : 1);
+  pl.lean = a->max_S > 32 * (pl.narrow ? 512 : 1024) && groups >= 4 * a->top_k && (a->max_S & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(scores) & 15) == 0;
+  return pl;
+}
+
 struct Workspace {
   int32_t* status;   // status record: 64-bit tag, then the error code (see report_status)
   float* part_o;     // [B][H_kv][splits][8][128]
   float* part_m;     // [B][H_kv][splits][8]
   float* part_l;     // [B][H_kv][splits][8]
   float* part_smax;  // [B][H_kv][splits][2]  largest K group scale seen (per group)
-  float* pmax;       // K3V2: [B][H_q][page_max_stride] largest approximate score of every pair of 16-token pages
+  float* pmax;       // [B][H_q][page_max_stride] largest approximate score of every pair of 16-token pages (K3V2) / every page (K4V4)
   float* scores;     // [B][H_q][max_S] approximate scores
   uint64_t bytes;
 };
 
 __host__ __device__ inline uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
-// entries per row of the page maxima: one per pair of 16-token pages, rounded up to whole float4s
-__host__ __device__ inline int page_max_stride(int max_S) { return (((max_S + 2 * JF_BLOCK_SIZE - 1) / (2 * JF_BLOCK_SIZE)) + 3) & ~3; }
+// entries per row of the page maxima, rounded up to whole float4s: K3V2 one per pair of 16-token
+// pages, K4V4 one per page
+__host__ __device__ inline int page_max_stride(int mode, int max_S) {
+  const int group = (mode == JF_MODE_K3V2) ? 2 * JF_BLOCK_SIZE : JF_BLOCK_SIZE;
+  return (((max_S + group - 1) / group) + 3) & ~3;
+}
 
 // Sized for the variant with the most splits (bf16 query), so one workspace serves both dtypes.
 inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv, int max_S, int /*top_k*/, bool need_scores) {
@@ -78,7 +103,7 @@ inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv,
   w.part_l = reinterpret_cast<float*>(p + off);     off = align_up(off + pairs * kHeadsPad * 4, 256);
   w.part_smax = reinterpret_cast<float*>(p + off);  off = align_up(off + pairs * 2 * 4, 256);
   w.pmax = reinterpret_cast<float*>(p + off);
-  if (mode == JF_MODE_K3V2) off = align_up(off + static_cast<uint64_t>(B) * H_q * page_max_stride(max_S) * 4, 256);
+  off = align_up(off + static_cast<uint64_t>(B) * H_q * page_max_stride(mode, max_S) * 4, 256);
   w.scores = reinterpret_cast<float*>(p + off);
   if (need_scores) off = align_up(off + static_cast<uint64_t>(B) * H_q * max_S * 4, 256);
   w.bytes = off;

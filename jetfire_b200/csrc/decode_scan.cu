@@ -422,7 +422,8 @@ scan_k3v2_kernel(const ScanParams p) {
   // Page-pair maxima (pages 2m, 2m+1; a warp's range starts at an even page): after the round's
   // butterfly the lanes with bits 2 and 3 clear hold them -- lane bit 4 clear: head 2tig, set: 2tig+1.
   const int pm_head = 2 * tig + (lane >> 4);
-  float* pmw = (kDoK && (lane & 12) == 0 && pm_head < p.G)
+  const bool want_pm = kDoK && p.pmax != nullptr;   // the same for the whole grid
+  float* pmw = (want_pm && (lane & 12) == 0 && pm_head < p.G)
                    ? p.pmax + (static_cast<int64_t>(b) * p.H_q + hkv * p.G + pm_head) * p.np_stride + (pg_first >> 1)
                    : nullptr;
   const float attn = p.attn_scale;
@@ -454,7 +455,7 @@ scan_k3v2_kernel(const ScanParams p) {
       sp0 += 16;
       sp1 += 16;
     }
-    if (kDoK) {
+    if (want_pm) {
       // largest score of the round's pages per head: the halves of the warp trade one head for the
       // other (each lane sends one value and keeps one), then reduce over lane bits 3 and 2
       const bool up = (lane & 16) != 0;
@@ -573,7 +574,9 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.v_data = a->v_data;  sp.v_scales = static_cast<const uint16_t*>(a->v_scales);
   sp.block_table = a->block_table;  sp.seq_lens = a->seq_lens;
   sp.scores = a->scores ? a->scores : ws.scores;
-  sp.pmax = ws.pmax; sp.np_stride = page_max_stride(a->max_S);
+  // the maxima of groups of pages, if the select kernel of this call will work from them
+  sp.pmax = select_plan(a, sp.scores).lean ? ws.pmax : nullptr;
+  sp.np_stride = page_max_stride(a->mode, a->max_S);
   sp.part_o = ws.part_o; sp.part_m = ws.part_m; sp.part_l = ws.part_l; sp.part_smax = ws.part_smax;
   sp.status = ws.status;
   sp.num_slots = a->num_slots;

@@ -139,7 +139,8 @@ struct K4State {
 //   2 = output partials from scores read back from memory (no K).
 template <bool kInt8P, bool kMasked, int kParts>
 __device__ __forceinline__ void k4v4_tile(K4State& st, uint32_t sbA, uint32_t sbB, uint32_t ssA, uint32_t ssB,
-                                          int mask, int t0, float attn, float* spA0, float* spA1, bool st0, bool st1) {
+                                          int mask, int t0, float attn, float* spA0, float* spA1, bool st0, bool st1,
+                                          bool want_pm, float* pm, int lane) {
   constexpr bool kDoK = kParts != 2, kDoV = kParts != 1;
   bool aLo = true, aHi = true, bLo = true, bHi = true;   // is this lane's token of page A / B (rows g, g + 8) in the tile
   if (kMasked) {
@@ -231,6 +232,25 @@ __device__ __forceinline__ void k4v4_tile(K4State& st, uint32_t sbA, uint32_t sb
       if (st0) { spA0[0] = sA[0]; spA0[8] = sA[2]; spB0[0] = sB[0]; spB0[8] = sB[2]; }
       if (st1) { spA1[0] = sA[1]; spA1[8] = sA[3]; spB1[0] = sB[1]; spB1[8] = sB[3]; }
     }
+  }
+
+  if (kDoK && want_pm) {
+    // Largest score of each page per head, for the select kernel's threshold.  Four values per lane
+    // (page A / B x head 2tig / 2tig+1) are reduced over the eight lanes that hold a head's tokens
+    // while the lanes trade them away: lane bit 4 keeps one head, bit 3 one page, bit 2 is reduced
+    // in full -- four shuffles per tile.  A page that a split boundary cuts belongs to two tiles:
+    // both store +inf for it ("fetch it always"), which is exact for the select kernel's purposes.
+    float a0 = fmaxf(sA[0], sA[2]), a1 = fmaxf(sA[1], sA[3]), b0 = fmaxf(sB[0], sB[2]), b1 = fmaxf(sB[1], sB[3]);
+    if (kMasked) {
+      if (mask & (1 << 22)) a0 = a1 = INFINITY;
+      if (mask & (1 << 23)) b0 = b1 = INFINITY;
+    }
+    const bool hb = (lane & 16) != 0, pb = (lane & 8) != 0;
+    const float ka = fmaxf(hb ? a1 : a0, __shfl_xor_sync(0xFFFFFFFFu, hb ? a0 : a1, 16));   // page A, this lane's head
+    const float kb = fmaxf(hb ? b1 : b0, __shfl_xor_sync(0xFFFFFFFFu, hb ? b0 : b1, 16));   // page B
+    float v = fmaxf(pb ? kb : ka, __shfl_xor_sync(0xFFFFFFFFu, pb ? ka : kb, 8));
+    v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 4));
+    if (pm && (!kMasked || !pb || ((mask >> 20) & 3) == 2)) *pm = v;   // lanes with bit 2 clear of a live head; page B only if present
   }
 
   // ---- one online-softmax step over both pages (same arithmetic per score as softmax_step) ----
@@ -359,7 +379,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   const int head_row0 = static_cast<int>(static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots);  // first cache row of this KV head
 
   // Tile T of the warp (tile t_first + T of the row): its first page and the token ranges of its
-  // pages, packed as lo_A | hi_A << 5 | lo_B << 10 | hi_B << 15 | pages << 20; 0 = no such tile
+  // pages, packed as lo_A | hi_A << 5 | lo_B << 10 | hi_B << 15 | pages << 20 | cut flags << 22; 0 = no such tile
   // (past the warp's range or past the sequence; such tiles are a suffix of the range).
   auto tile_geom = [&](int T, int& pageA) -> int {
     const int gT = t_first + T;
@@ -382,7 +402,10 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     const int two = (pageA + 1 < blk_end) ? 1 : 0;
     const int loA = max(s_lo - pa, 0), hiA = min(s_hi - pa, 16);
     const int hiB = two ? min(s_hi - pa - 16, 16) : 0;
-    return loA | (hiA << 5) | (hiB << 15) | ((1 + two) << 20);
+    // bits 22 / 23: page A / B is cut by a split boundary (another tile holds its other tokens)
+    const int cutA = (loA > 0 || (hiA < 16 && pa + hiA < len)) ? 1 : 0;
+    const int cutB = (two && hiB < 16 && pa + 16 + hiB < len) ? 1 : 0;
+    return loA | (hiA << 5) | (hiB << 15) | ((1 + two) << 20) | (cutA << 22) | (cutB << 23);
   };
   // Descriptors are worked out sixteen tiles at a time by sixteen lanes, a whole chunk ahead of
   // their use (a global load issued while megabytes of page copies are queued in the memory
@@ -397,7 +420,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
       r.mask = tile_geom(chunk * kBtChunk + lane, r.pageA);
       if (r.mask) {
         if (r.pageA < p.max_blocks) r.ba = bt_row[r.pageA];
-        if ((r.mask >> 20) == 2 && r.pageA + 1 < p.max_blocks) r.bb = bt_row[r.pageA + 1];
+        if (((r.mask >> 20) & 3) == 2 && r.pageA + 1 < p.max_blocks) r.bb = bt_row[r.pageA + 1];
       }
     }
     return r;
@@ -409,7 +432,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     if (badA) mask &= ~0x3FF;
     if (badB) mask &= ~(0x3FF << 10);
     const int rowA = head_row0 + static_cast<int>(badA ? 0 : r.ba) * 16;
-    const int rowB = (mask >> 20) == 2 ? head_row0 + static_cast<int>(badB ? 0 : r.bb) * 16 : -1;
+    const int rowB = ((mask >> 20) & 3) == 2 ? head_row0 + static_cast<int>(badB ? 0 : r.bb) * 16 : -1;
     return make_int4(rowA, rowB, mask, r.pageA);
   };
   Pending pend = desc_load(0);
@@ -551,6 +574,13 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
   float* sp1 = sp0 + p.max_S;
   const bool st0 = (2 * tig) < p.G, st1 = (2 * tig + 1) < p.G;
   const float attn = p.attn_scale;
+  // page maxima: after the tile's exchange the lanes with bit 2 clear hold them -- bit 4: head
+  // 2tig / 2tig+1, bit 3: page A / B
+  const int pm_head = 2 * tig + (lane >> 4);
+  const bool want_pm = kDoK && p.pmax != nullptr;   // the same for the whole grid
+  float* pm_row = (want_pm && (lane & 4) == 0 && pm_head < p.G)
+                      ? p.pmax + (static_cast<int64_t>(b) * p.H_q + hkv * p.G + pm_head) * p.np_stride + ((lane >> 3) & 1)
+                      : nullptr;
 
   // A round takes one slot: one tile.  Tiles of two whole pages go through the unmasked path.
   int sl = 0;
@@ -569,9 +599,11 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
     float* spA0 = sp0 + static_cast<int64_t>(d.w) * 16;
     float* spA1 = sp1 + static_cast<int64_t>(d.w) * 16;
     if (d.z == kFullTile)
-      k4v4_tile<kInt8P, false, kParts>(st, sb, sb + T4::kPageBytes, ss, ss + 32, d.z, t0, attn, spA0, spA1, st0, st1);
+      k4v4_tile<kInt8P, false, kParts>(st, sb, sb + T4::kPageBytes, ss, ss + 32, d.z, t0, attn, spA0, spA1, st0, st1,
+                                       want_pm, pm_row ? pm_row + d.w : nullptr, lane);
     else
-      k4v4_tile<kInt8P, true, kParts>(st, sb, sb + T4::kPageBytes, ss, ss + 32, d.z, t0, attn, spA0, spA1, st0, st1);
+      k4v4_tile<kInt8P, true, kParts>(st, sb, sb + T4::kPageBytes, ss, ss + 32, d.z, t0, attn, spA0, spA1, st0, st1,
+                                      want_pm, pm_row ? pm_row + d.w : nullptr, lane);
     __syncwarp();
     // the refill below reads the descriptor of tile it + kSlots: bring its chunk in first
     if (((it + T4::kSlots) >> 4) > stored) {

@@ -225,7 +225,6 @@ __host__ __device__ constexpr size_t sel_smem_bytes(size_t region0, int sort_n, 
   return region0 + sizeof(SelSmemFixed) + static_cast<size_t>(sort_n) * 8 +
          static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(sort_n) * 4 + static_cast<size_t>(hm_chunks) * hm_chunk_bytes(nt);
 }
-constexpr int kPmVec = 2;   // lean kernel: float4s of page maxima per thread (rows of up to 4 * kPmVec * threads pages)
 
 // One CTA per (query head, batch element).  The row's approximate scores are pulled into
 // shared memory by one bulk copy per 32768 positions, issued before anything else so that
@@ -244,7 +243,6 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   constexpr int kW = NT / 32;                   // warps of this block
   constexpr int kChunkPos = 4 * kChunkVec * NT; // positions per pass over a chunk
   constexpr int W = RowWords<MODE>::v;         // 32-bit words staged per candidate: data + scales
-  static_assert(!LEAN || MODE == JF_MODE_K3V2, "only the K3V2 scan writes page maxima");
   constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN, NT>();
   constexpr int kRowChunk = RowChunk<MODE>::v;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -362,25 +360,11 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   }
   SplitPre<NT> pre;
   if (FUSED) split_preload<NT>(tp, pbase, hi, tid, pre);
-  // lean: this thread's page maxima, requested now and used after the reduction below
-  const int n_pages = (n_seq + 15) >> 4, n_pairs = (n_pages + 1) >> 1;
-  float pm[LEAN ? 4 * kPmVec : 1];
-  if (LEAN) {
-    const float4* pm4 = reinterpret_cast<const float4*>(p.pmax + bh * p.np_stride);
-#pragma unroll
-    for (int j = 0; j < kPmVec; ++j) {
-      const int i4 = j * NT + tid;
-      float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-      if (4 * i4 < n_pairs) v = pm4[i4];
-      // pairs past the sequence were never written
-      pm[4 * j] = v.x;
-      pm[4 * j + 1] = (4 * i4 + 1 < n_pairs) ? v.y : -INFINITY;
-      pm[4 * j + 2] = (4 * i4 + 2 < n_pairs) ? v.z : -INFINITY;
-      pm[4 * j + 3] = (4 * i4 + 3 < n_pairs) ? v.w : -INFINITY;
-    }
-  } else {
-    issue_chunk(0);
-  }
+  // lean: the scan's maxima of groups of pages -- K3V2: pairs of pages, K4V4: single pages
+  constexpr int kGroupPages = (MODE == JF_MODE_K3V2) ? 2 : 1;
+  const int n_pages = (n_seq + 15) >> 4, n_groups = (n_pages + kGroupPages - 1) / kGroupPages;
+  const float4* pm4 = reinterpret_cast<const float4*>(p.pmax + bh * p.np_stride);
+  if (!LEAN) issue_chunk(0);
   {
     for (int s = tid + NT; s < p.splits; s += NT) {
       top = fmaxf(top, p.part_m[(pbase + s) * kHeadsPad + hi]);
@@ -605,10 +589,16 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
       }
       have_hm = !LEAN && n_chunks == 1;  // hm[] describes the chunk that stays resident
       if (LEAN) {
-        // the groups are the pairs of pages, their maxima came with the scan
+        // the groups are the scan's; their maxima came with it.  +inf marks a K4V4 page whose
+        // maximum is not known (it is always fetched below) and does not count here; groups past
+        // the sequence were never written.
+        for (int i4 = tid; 4 * i4 < n_groups; i4 += NT) {
+          const float4 v = pm4[i4];
+          const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 4 * kPmVec; ++i)
-          if (pm[i] > -INFINITY) atomicAdd(&hist[score_bin(top64, pm[i])], 1);
+          for (int c = 0; c < 4; ++c)
+            if (4 * i4 + c < n_groups && e[c] > -INFINITY && e[c] < INFINITY) atomicAdd(&hist[score_bin(top64, e[c])], 1);
+        }
       }
       __syncthreads();
       scan_hist(K);
@@ -631,12 +621,18 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
             // fixed, the ranking below does not depend on it.
             uint16_t* page_list = perm;   // perm and bucket, contiguous: 2 * sort_n entries
             const int list_cap = 2 * p.sort_n;
-            {
-              uint32_t flags = 0u;   // two bits per pair: its pages that exist
+            for (int b4 = 0; 4 * b4 < n_groups; b4 += NT) {   // the same trip count for every thread
+              const int i4 = b4 + tid;
+              uint32_t flags = 0u;   // kGroupPages bits per group: its pages that exist
+              if (4 * i4 < n_groups) {
+                const float4 v = pm4[i4];
+                const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-              for (int i = 0; i < 4 * kPmVec; ++i) {
-                const int pg = 2 * (4 * ((i >> 2) * NT + tid) + (i & 3));
-                if (pm[i] > thr) flags |= (pg + 1 < n_pages ? 3u : 1u) << (2 * i);
+                for (int c = 0; c < 4; ++c) {
+                  const int pg = kGroupPages * (4 * i4 + c);
+                  if (4 * i4 + c < n_groups && e[c] > thr)
+                    flags |= ((kGroupPages == 2 && pg + 1 < n_pages) ? 3u : 1u) << (kGroupPages * c);
+                }
               }
               const int cnt = __popc(flags);
               int incl = cnt;
@@ -649,9 +645,9 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
               if (lane == 31 && incl > 0) base = atomicAdd(&sm.ncand, incl);
               int o = __shfl_sync(0xFFFFFFFFu, base, 31) + incl - cnt;
               while (flags) {
-                const int i = __ffs(flags) - 1;
+                const int i = __ffs(flags) - 1;   // bit i: page kGroupPages * 4 * i4 + i
                 flags &= flags - 1u;
-                if (o < list_cap) page_list[o] = static_cast<uint16_t>(2 * (4 * ((i >> 3) * NT + tid) + ((i >> 1) & 3)) + (i & 1));
+                if (o < list_cap) page_list[o] = static_cast<uint16_t>(kGroupPages * 4 * i4 + i);
                 ++o;
               }
             }
@@ -1121,7 +1117,7 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   Workspace ws = carve_workspace(a->workspace, a->mode, a->B, a->H_q, a->H_kv, a->max_S, a->top_k, true);
   TopkParams sp{};
   sp.scores = a->scores ? a->scores : ws.scores;
-  sp.pmax = ws.pmax; sp.np_stride = page_max_stride(a->max_S);
+  sp.pmax = ws.pmax; sp.np_stride = page_max_stride(a->mode, a->max_S);
   sp.part_m = ws.part_m; sp.part_smax = ws.part_smax;
   sp.q = a->q; sp.k_data = a->k_data; sp.k_scales = static_cast<const uint16_t*>(a->k_scales);
   sp.block_table = a->block_table; sp.seq_lens = a->seq_lens;
@@ -1141,21 +1137,16 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   // With more rows than multiprocessors the 512-thread block runs two rows per multiprocessor (one
   // row's chains of dependent memory round trips under the other's arithmetic); otherwise a row's
   // latency is what counts and the 1024-thread block takes it.
-  const bool many = a->B * a->H_q > num_sms() && sp.sort_n <= 1024;
+  const SelectPlan plan = select_plan(a, sp.scores);
+  const bool many = plan.narrow, lean = plan.lean;
   // resident-row kernel: rows of 2..4 score chunks get the side table of float4 maxima if it fits
   auto side_table = [&](int nt, size_t region0, size_t budget) {
     const int chunks = (a->max_S + 32 * nt - 1) / (32 * nt);
     return (chunks >= 2 && chunks <= 4 && sel_smem_bytes(region0, sp.sort_n, chunks, nt) <= budget) ? chunks : 0;
   };
   if (a->mode == JF_MODE_K3V2) {
-    // Long rows take the lean kernel (threshold from the scan's page-pair maxima): enough pairs for
-    // the K-th largest pair maximum to be a tight bound, and score rows that 16-byte loads can
-    // read (whole pages only: a listed page is fetched whole, and the last row's must end inside
-    // the buffer).
-    const int pairs = (a->max_S + 31) / 32;
-    const bool lean = pairs >= 4 * a->top_k && (a->max_S & 15) == 0 && (reinterpret_cast<uintptr_t>(sp.scores) & 15) == 0;
-    if (lean && many && pairs <= 4 * kPmVec * 512) return launch_select_dtype<JF_MODE_K3V2, true, 512>(a, sp, tp, grid, stream, fused);
-    if (lean && pairs <= 4 * kPmVec * kSelThreads) return launch_select_dtype<JF_MODE_K3V2, true, kSelThreads>(a, sp, tp, grid, stream, fused);
+    if (lean && many) return launch_select_dtype<JF_MODE_K3V2, true, 512>(a, sp, tp, grid, stream, fused);
+    if (lean) return launch_select_dtype<JF_MODE_K3V2, true, kSelThreads>(a, sp, tp, grid, stream, fused);
     constexpr size_t r512 = sel_region0_bytes<JF_MODE_K3V2, false, 512>();
     if (many && sel_smem_bytes(r512, sp.sort_n, 0, 512) <= kTwoBlockBytes) {
       sp.hm_chunks = side_table(512, r512, kTwoBlockBytes);
@@ -1164,6 +1155,8 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
     sp.hm_chunks = side_table(kSelThreads, sel_region0_bytes<JF_MODE_K3V2, false, kSelThreads>(), kSelSmemLimit);
     return launch_select_dtype<JF_MODE_K3V2, false, kSelThreads>(a, sp, tp, grid, stream, fused);
   }
+  if (lean && many) return launch_select_dtype<JF_MODE_K4V4, true, 512>(a, sp, tp, grid, stream, fused);
+  if (lean) return launch_select_dtype<JF_MODE_K4V4, true, kSelThreads>(a, sp, tp, grid, stream, fused);
   constexpr size_t r512 = sel_region0_bytes<JF_MODE_K4V4, false, 512>();
   if (many && sel_smem_bytes(r512, sp.sort_n, 0, 512) <= kTwoBlockBytes) {
     sp.hm_chunks = side_table(512, r512, kTwoBlockBytes);
