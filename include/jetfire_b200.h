@@ -216,12 +216,13 @@ typedef struct jf_decode_args {
 uint64_t    jf_decode_workspace_bytes(int32_t mode, int32_t B, int32_t H_q, int32_t H_kv,
                                       int32_t max_S, int32_t top_k);
 /* scan: dequantise, Q.K^T, online softmax, P.V over the packed cache; leaves split
- * partials, approximate scores (also in args->scores if given) and, for K3V2, the largest
- * score of every pair of 16-token pages in the workspace. */
+ * partials, approximate scores (also in args->scores if given) and, for long rows, the largest
+ * score of every group of 16-token pages in the workspace (what the select kernel of the same
+ * arguments takes its threshold from). */
 jf_status_t jf_decode_scan(const jf_decode_args* args, jf_stream_t stream);
 /* select: exact top-k per query head (csrc/int3_qk_scores.cu:426-554 with a
  * deterministic order and tie rule) + slot translation (:399-417).  Works on what the scan of
- * the same arguments left in the same workspace (split statistics, the K3V2 page-pair maxima)
+ * the same arguments left in the same workspace (split statistics, the maxima of groups of pages)
  * and on the scores it wrote -- not on scores from elsewhere. */
 jf_status_t jf_topk_select(const jf_decode_args* args, jf_stream_t stream);
 /* finish: merge the split partials into o_hat and the softmax statistics, and compute
