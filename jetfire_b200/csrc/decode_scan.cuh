@@ -68,11 +68,6 @@ __device__ __forceinline__ float load_q(const void* q, int64_t idx) {
   return Elem<DT>::to_f32(reinterpret_cast<const uint16_t*>(q)[idx]);
 }
 
-__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
-  uint32_t d;
-  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
 
 // Bytes of shared memory the merge needs (per-warp output tiles + statistics).
 constexpr int kMergeBytes = (kScanWarps * kHeadsPad * JF_HEAD_DIM + 3 * kScanWarps * kHeadsPad) * 4;

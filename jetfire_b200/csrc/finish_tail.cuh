@@ -9,6 +9,12 @@
 // Every summation order is fixed (no floating-point atomics) and does not depend on the block
 // size: a block of NT threads plays the 1024 thread-items and the 32 warps of the widest
 // block one after the other, so every kernel that runs this code gives the same bits.
+//
+// The selected set's sum runs on the tensor cores like the scan's P.V: sixteen staged entries
+// are a "page" (their packed V rows lie one after the other in shared memory), the masked code
+// fields go to mma.sync.m16n8k16 as subnormal fp16 numbers without arithmetic, the weights
+// (times the V group scale, rounded to fp16 as the scan rounds its P operand) are the other
+// operand -- one column of it; the codes' offset leaves through a sum-of-weights tile.
 #pragma once
 
 #include "decode_common.cuh"
@@ -47,7 +53,6 @@ struct TailSmem {
   int64_t slot[kTailChunk];
   int cidx[kTailChunk];      // candidate index in the prefetched arrays, or -1
   float wv[kTailChunk][2];   // weight * v scale (per group)
-  float w[kTailChunk];       // weight
   float red[kSelWarps][JF_HEAD_DIM];
   float sum[kSelWarps];
   float o[kSplitGroups][JF_HEAD_DIM];
@@ -145,10 +150,9 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
   const uint16_t* v_sc = p.v_scales + static_cast<int64_t>(hkv >> p.kv_shift) * p.num_slots * mi.ng;
   const float* srow = p.scores + bh * p.max_S;
   constexpr int kVW = kSelWarps / kW;   // warps of the widest block this warp plays: warp, warp + kW, ...
-  float acc[kVW][4], wsum[kVW];
-#pragma unroll
-  for (int k = 0; k < kVW; ++k) { acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f; wsum[k] = 0.f; }
-  const int qg = (MODE == JF_MODE_K3V2) ? (lane >> 4) : 0;  // quant group of channels 4l..4l+3
+  for (int i = tid; i < kSelWarps * JF_HEAD_DIM; i += NT) (&sm.red[0][0])[i] = 0.f;
+  if (tid < kSelWarps) sm.sum[tid] = 0.f;
+  __syncthreads();
   for (int k0 = 0; k0 < p.top_k; k0 += kTailChunk) {
     const int kend = min(kTailChunk, p.top_k - k0);
     if (tid < kTailChunk) {
@@ -184,8 +188,11 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       }
       sm.slot[tid] = slot;
       sm.cidx[tid] = cidx;
-      sm.w[tid] = w;
       sm.wv[tid][0] = w * vs0; sm.wv[tid][1] = w * vs1;
+      // the weights' sum: whole warps are here (kTailChunk is a multiple of 32); fixed order
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
+      if (lane == 0) sm.sum[warp] += w;
     }
     __syncthreads();
     // packed V rows, one 16-byte load per thread
@@ -201,46 +208,90 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
       reinterpret_cast<uint4*>(sm.v)[u] = v;
     }
     __syncthreads();
-    // warp w (of 32) takes entries w, w + 32, ...; lane l owns channels 4l..4l+3
+    // Work item (group of 16 staged entries, quarter of the channels) -> warp item & 31 of the
+    // widest block; its four output tiles and the sum-of-weights tile are added to the warp's own
+    // row of sm.red (no other warp touches it).
+    {
+      const int g = lane >> 2, tig = lane & 3;
+      constexpr int kGroups = kTailChunk / 16;
+      constexpr int kParts = (MODE == JF_MODE_K3V2) ? 2 : 4;          // channel ranges per group: 64 / 32 channels
+      static_assert(kGroups * kParts <= 2 * kSelWarps, "work items per round");
 #pragma unroll
-    for (int k = 0; k < kVW; ++k) {
-      const int vwarp = warp + k * kW;
-      uint32_t raw[kTailPerWarp];
-      float fw[kTailPerWarp], w0[kTailPerWarp];
+      for (int k = 0; k < kVW * (kGroups * kParts / kSelWarps); ++k) {
+        const int item = warp + k * kW;                  // 0 .. kGroups * kParts - 1
+        const int grp = item % kGroups, part = item / kGroups;
+        if (16 * grp >= kend) continue;                  // warp-uniform: no live entry in the group
+        const int e0 = 16 * grp;
+        float t[5][4];
 #pragma unroll
-      for (int i = 0; i < kTailPerWarp; ++i) {
-        const int j = vwarp + i * kSelWarps;  // < kTailChunk; entries past kend hold zero weights
-        raw[i] = (MODE == JF_MODE_K3V2) ? static_cast<uint32_t>(reinterpret_cast<const uint8_t*>(sm.v + j * VW)[lane])
-                                        : static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(sm.v + j * VW)[lane]);
-        fw[i] = sm.wv[j][qg];
-        w0[i] = sm.w[j];
-      }
-#pragma unroll
-      for (int i = 0; i < kTailPerWarp; ++i) {
-        const int j = vwarp + i * kSelWarps;
-        if (j >= kend || sm.slot[j] < 0) continue;  // warp-uniform
-        float c[4];
+        for (int i = 0; i < 5; ++i) t[i][0] = t[i][1] = t[i][2] = t[i][3] = 0.f;
+        float* red = sm.red[item & (kSelWarps - 1)];
         if (MODE == JF_MODE_K3V2) {
+          // as the scan's V path (k-slots 2tig, 2tig+1, 2tig+8, 2tig+9 <-> entries tig, tig+4, tig+8, tig+12)
+          const int qh = part;
+          const uint8_t* page = reinterpret_cast<const uint8_t*>(sm.v + e0 * VW) + 16 * qh + 2 * g;
+          const uint32_t Ha = *reinterpret_cast<const uint16_t*>(page + tig * 32);
+          const uint32_t Hb = *reinterpret_cast<const uint16_t*>(page + (tig + 4) * 32);
+          const uint32_t Hc = *reinterpret_cast<const uint16_t*>(page + (tig + 8) * 32);
+          const uint32_t Hd = *reinterpret_cast<const uint16_t*>(page + (tig + 12) * 32);
+          uint32_t b0 = 0u, b1 = 0u;
+          if (g == 0) {   // the one column of the weight operand
+            b0 = pack_f16x2_sat(sm.wv[e0 + tig][qh], sm.wv[e0 + tig + 4][qh]);
+            b1 = pack_f16x2_sat(sm.wv[e0 + tig + 8][qh], sm.wv[e0 + tig + 12][qh]);
+          }
+          const uint32_t XA = Ha | (Hb << 16), XB = Hc | (Hd << 16);
+          const uint32_t XA2 = XA >> 10, XB2 = XB >> 10;
+          constexpr uint32_t m0 = 0x00030003u;
+          mma_f16_16816(t[0], XA & m0, XA & (m0 << 2), XB & m0, XB & (m0 << 2), b0, b1);
+          mma_f16_16816(t[1], XA & (m0 << 4), XA & (m0 << 6), XB & (m0 << 4), XB & (m0 << 6), b0, b1);
+          mma_f16_16816(t[2], XA & (m0 << 8), XA2 & m0, XB & (m0 << 8), XB2 & m0, b0, b1);
+          mma_f16_16816(t[3], XA2 & (m0 << 2), XA2 & (m0 << 4), XB2 & (m0 << 2), XB2 & (m0 << 4), b0, b1);
+          mma_f16_16816(t[4], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, b0, b1);
+          if (tig == 0) {   // column 0: rows g (fields 2ml) and g + 8 (fields 2ml + 1)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) c[e] = small_code_to_f32((raw[i] >> ((3 - e) * 2)) & 3u, 2.0f);
+            for (int ml = 0; ml < 4; ++ml) {
+              const int fa = 2 * ml, fb = 2 * ml + 1;
+              // bit position of field f in its 16-bit half (after the shift by 10 for f >= 5) and its channel
+              const int pa = fa <= 4 ? 2 * fa : 2 * fa - 10, pb = fb <= 4 ? 2 * fb : 2 * fb - 10;
+              const int da = 64 * qh + 8 * g + 4 * (fa >> 2) + 3 - (fa & 3), db = 64 * qh + 8 * g + 4 * (fb >> 2) + 3 - (fb & 3);
+              red[da] += fmaf(t[ml][0], 16777216.0f / static_cast<float>(1 << pa), -2.0f * t[4][0]);
+              red[db] += fmaf(t[ml][2], 16777216.0f / static_cast<float>(1 << pb), -2.0f * t[4][2]);
+            }
+          }
         } else {
-          c[0] = small_code_to_f32((raw[i] >> 4) & 15u, 8.0f);
-          c[1] = small_code_to_f32(raw[i] & 15u, 8.0f);
-          c[2] = small_code_to_f32((raw[i] >> 12) & 15u, 8.0f);
-          c[3] = small_code_to_f32((raw[i] >> 8) & 15u, 8.0f);
-        }
+          // as the K4V4 scan's V path: k-slots 2tig, 2tig+1 (+8) <-> entries tokA, tokB (+8)
+          const int wi = part & 1, bp = part >> 1;
+          const int tokA = ((2 * tig >> 2) & 1) | (((2 * tig >> 1) & 1) << 2) | ((2 * tig & 1) << 1);
+          const int tokB = (((2 * tig + 1) >> 2) & 1) | ((((2 * tig + 1) >> 1) & 1) << 2) | (((2 * tig + 1) & 1) << 1);
+          const uint8_t* page = reinterpret_cast<const uint8_t*>(sm.v + e0 * VW) + 8 * g + 4 * wi;   // channels 16g + 8wi ..
+          const uint32_t wa = *reinterpret_cast<const uint32_t*>(page + tokA * 64);
+          const uint32_t wb = *reinterpret_cast<const uint32_t*>(page + tokB * 64);
+          const uint32_t wc = *reinterpret_cast<const uint32_t*>(page + (tokA + 8) * 64);
+          const uint32_t wd = *reinterpret_cast<const uint32_t*>(page + (tokB + 8) * 64);
+          uint32_t b0 = 0u, b1 = 0u;
+          if (g == 0) {
+            b0 = pack_f16x2_sat(sm.wv[e0 + tokA][0], sm.wv[e0 + tokB][0]);
+            b1 = pack_f16x2_sat(sm.wv[e0 + tokA + 8][0], sm.wv[e0 + tokB + 8][0]);
+          }
+          const uint32_t sel = bp ? 0x7632u : 0x5410u;
+          const uint32_t XA = prmt(wa, wb, sel), XB = prmt(wc, wd, sel);
+          const uint32_t XA2 = XA >> 8, XB2 = XB >> 8;
+          constexpr uint32_t m0 = 0x000F000Fu;
+          mma_f16_16816(t[0], XA & m0, XA & (m0 << 4), XB & m0, XB & (m0 << 4), b0, b1);
+          mma_f16_16816(t[1], XA2 & m0, XA2 & (m0 << 4), XB2 & m0, XB2 & (m0 << 4), b0, b1);
+          mma_f16_16816(t[4], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, b0, b1);
+          if (tig == 0) {   // low nibble -> row g (odd channel), high nibble -> row g + 8 (even channel)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[k][e] = fmaf(fw[i], c[e], acc[k][e]);
-        wsum[k] += w0[i];
+            for (int e = 0; e < 2; ++e) {
+              const int dlo = 16 * g + 8 * wi + 4 * bp + 2 * e + 1;
+              red[dlo] += fmaf(t[e][0], 16777216.0f, -8.0f * t[4][0]);
+              red[dlo - 1] += fmaf(t[e][2], 1048576.0f, -8.0f * t[4][2]);
+            }
+          }
+        }
       }
     }
     __syncthreads();
-  }
-#pragma unroll
-  for (int k = 0; k < kVW; ++k) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) sm.red[warp + k * kW][4 * lane + e] = acc[k][e];
-    if (lane == 0) sm.sum[warp + k * kW] = wsum[k];
   }
   __syncthreads();
   if (tid < JF_HEAD_DIM) {
