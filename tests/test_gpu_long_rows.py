@@ -1,7 +1,7 @@
 """Rows longer than one shared-memory chunk of the select kernel (32768 positions), odd row
-strides, the select kernel that works from the scan's page-pair maxima (long K3V2 rows; one
-block of 1024 threads per row, or two of 512 per multiprocessor once there are more rows than
-multiprocessors), and the bench geometry at full size, checked against the C restatement of the
+strides, the select kernel that works from the scan's page maxima (rows longer than one staged
+chunk; one block of 1024 threads per row, or two of 512 per multiprocessor once there are more
+rows than multiprocessors), and the bench geometry at full size, checked against the C restatement of the
 oracle (itself pinned to the numpy oracle in test_oracle_native.py).  The packed cache is the
 one the GPU append path wrote (its bytes are pinned elsewhere), so no numpy pass over the
 whole cache is needed."""
