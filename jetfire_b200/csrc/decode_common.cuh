@@ -115,6 +115,10 @@ inline Workspace carve_workspace(void* base, int mode, int B, int H_q, int H_kv,
 // needs no initialisation and no launch has to clear it.  jf_decode_status reads the record
 // and clears it.
 constexpr unsigned long long kStatusTag = 0x4A46535441545553ull;  // "JFSTATUS"
+// Word 4 of the record: written by every scan -- this value if it left page maxima, 0 if not --
+// and checked by the select kernel that works from them, so that a select whose arguments do not
+// match the scan's reports JF_ERR_STATE (and selects nothing) instead of reading stale maxima.
+constexpr int32_t kPageMaxTag = 0x504D4158;  // "PMAX"
 #ifdef __CUDACC__
 __device__ __forceinline__ void report_status(int32_t* status, int code) {
   status[2] = code;

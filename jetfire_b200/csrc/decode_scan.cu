@@ -479,6 +479,7 @@ scan_k3v2_kernel(const ScanParams p) {
 
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
+  if (kDoK && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) p.status[4] = want_pm ? kPageMaxTag : 0;
 
   // ---------------- CTA merge: 4 warps -> one partial ----------------
   __syncthreads();  // every warp is done with its stages (or gave up); smem is reused below

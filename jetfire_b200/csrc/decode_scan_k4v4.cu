@@ -620,6 +620,7 @@ scan_k4v4_kernel(const ScanParams p, const __grid_constant__ CUtensorMap k_map,
 
   pdl_trigger();  // the next kernel may start its prologue; it waits for this grid before reading
   if (failed && lane == 0) report_status(p.status, JF_ERR_TIMEOUT);
+  if (kDoK && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) p.status[4] = want_pm ? kPageMaxTag : 0;
 
   __syncthreads();
   {

@@ -397,6 +397,10 @@ topk_select_kernel(const TopkParams p, const TailParams tp) {
   // the copy issued at the top must have landed before its shared memory is reused
   bool copied = LEAN ? true : wait_chunk(0, n_seq);
   if (!copied && tid == 0) report_status(p.status, JF_ERR_TIMEOUT);
+  if (LEAN && p.status[4] != kPageMaxTag) {   // the scan before this call left no page maxima: arguments do not match
+    if (tid == 0) report_status(p.status, JF_ERR_STATE);
+    copied = false;
+  }
   const int n = copied ? n_seq : 0;   // a row whose scores did not arrive selects nothing
 
   int m_sel = 0;  // entries of keys[] that hold the ranked result

@@ -79,6 +79,25 @@ def test_staged_row_select_with_two_blocks_per_multiprocessor(mode, ctx, lens, t
     _run(Case(mode, 5, 32, 8, ctx, lens=lens, seed=71), top_k, stage_b=stage_b)
 
 
+def test_select_with_other_arguments_than_the_scan_is_reported():
+    """The scan leaves page maxima only for calls whose select kernel works from them; a select
+    called with arguments under which it would (here: a smaller top-k) after a scan that left none
+    reports an error through the status record instead of selecting from stale maxima."""
+    from jetfire_b200 import ops
+    case = Case("k3v2", 1, 8, 2, 65536, lens=[65536], seed=77)
+    kd, ks, vd, vs = case.device_cache()
+    ws = torch.empty(ops.decode_workspace_bytes("k3v2", 1, 8, 2, 65536, 1024) + 256, dtype=torch.uint8, device="cuda")
+    args = (case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+            case.ctx, case.H_q, case.H_kv, 16)
+    wide = ops.DecodeCall(*args, 1024, case.attn_scale, workspace=ws)   # 2048 page pairs < 4 * 1024: rows are staged
+    narrow = ops.DecodeCall(*args, 512, case.attn_scale, workspace=ws)  # 2048 page pairs >= 4 * 512: page maxima
+    wide.scan(); narrow.select()
+    with pytest.raises(RuntimeError):
+        narrow.status()
+    narrow.scan(); narrow.select(); narrow.status()                      # matching arguments: fine
+    assert int(narrow.out["topk_idx"].min()) >= 0
+
+
 def _random_cases(n, seed=2024):
     """Seeded random geometries: every select kernel (staged row / page maxima, 1024 / 512 threads),
     every GQA ratio, ragged lengths down to one token, top-k from 32 to 512, both dtypes."""
