@@ -33,7 +33,9 @@ enum {
   JF_ERR_STATIC_LIMIT = -4, /* request needs more scratch than the built-in buffer   */
   JF_ERR_CUDA         = 1,  /* a CUDA call failed; see jf_last_cuda_error()          */
   JF_ERR_TIMEOUT      = 2,  /* a bounded wait ran out (device status word or host)   */
-  JF_ERR_STATE        = 3   /* host-side object used in the wrong state              */
+  JF_ERR_STATE        = 3   /* object used in the wrong state (host side), or -- through
+                               jf_decode_status -- a select whose arguments do not match
+                               those of the scan that filled the workspace             */
 };
 
 enum { JF_DTYPE_BF16 = 0, JF_DTYPE_FP16 = 1 };
