@@ -66,7 +66,8 @@ enum { JF_STAGE_B_FP32 = 0, JF_STAGE_B_INT8P = 1 };
 
 #define JF_HEAD_DIM   128
 #define JF_BLOCK_SIZE 16
-#define JF_MAX_TOP_K  2048
+#define JF_MAX_TOP_K  4096  /* above 2048: only for score rows of whole pages (max_S a multiple of 16,
+                               a 16-byte aligned scores pointer), else JF_ERR_UNSUPPORTED */
 #define JF_MAX_GROUP  16    /* query heads per KV head: 1..8, or 16 (handled as two halves of 8) */
 
 const char* jf_status_string(jf_status_t st);

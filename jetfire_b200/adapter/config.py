@@ -29,7 +29,7 @@ SCHEME_TO_KERNEL_MODE = {"SymInt3K_SymInt2V": "k3v2", "SymInt4K_SymInt4V": "k4v4
 
 # top-k widths the release matrix offers (jetfire_vllm/adapter/release_policy.py:31-34),
 # limited to what this library builds
-SUPPORTED_TOP_K = (32, 64, 128, 256, 512, 1024, 2048)
+SUPPORTED_TOP_K = (32, 64, 128, 256, 512, 1024, 2048, 4096)
 
 
 @dataclass(frozen=True)

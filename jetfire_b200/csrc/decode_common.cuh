@@ -58,15 +58,21 @@ inline int scan_splits(int mode, int q_dtype, int B, int H_kv, int max_S) {
 //           score rows are whole pages that 16-byte loads can read.
 // Rows of one chunk stay with the kernel that stages them: it is as fast there, and the scan
 // saves the few per cent the maxima cost it.
-struct SelectPlan { bool narrow, lean; };
+constexpr int kStagedTopK = 2048;   // widest top-k of the kernel that stages the row
+struct SelectPlan { bool narrow, lean, supported; };
 inline SelectPlan select_plan(const jf_decode_args* a, const float* scores) {
   int sort_n = 512;
   while (sort_n < 2 * a->top_k) sort_n <<= 1;
   SelectPlan pl;
   pl.narrow = a->B * a->H_q > num_sms() && sort_n <= 1024;
   const int groups = (a->max_S + 15) / 16 / (a->mode == JF_MODE_K3V2 ? 2 : 1);
-  pl.lean = a->max_S > 32 * (pl.narrow ? 512 : 1024) && groups >= 4 * a->top_k && (a->max_S & 15) == 0 &&
-            (reinterpret_cast<uintptr_t>(scores) & 15) == 0;
+  const bool readable = (a->max_S & 15) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15) == 0;
+  pl.lean = readable && a->max_S > 32 * (pl.narrow ? 512 : 1024) && groups >= 4 * a->top_k;
+  // A top-k above kStagedTopK has no room for its sort buffer beside a staged row: such calls
+  // always take the kernel that stages nothing (with few groups its histogram tier gives way to
+  // the exact radix tier over the row in L2).  pl.supported is false if they cannot.
+  pl.supported = a->top_k <= kStagedTopK || readable;
+  if (a->top_k > kStagedTopK) { pl.lean = readable; pl.narrow = false; }
   return pl;
 }
 

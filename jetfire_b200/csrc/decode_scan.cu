@@ -576,7 +576,9 @@ extern "C" jf_status_t jf_decode_scan(const jf_decode_args* a, jf_stream_t strea
   sp.block_table = a->block_table;  sp.seq_lens = a->seq_lens;
   sp.scores = a->scores ? a->scores : ws.scores;
   // the maxima of groups of pages, if the select kernel of this call will work from them
-  sp.pmax = select_plan(a, sp.scores).lean ? ws.pmax : nullptr;
+  const SelectPlan plan = select_plan(a, sp.scores);
+  if (!plan.supported) return JF_ERR_UNSUPPORTED;
+  sp.pmax = plan.lean ? ws.pmax : nullptr;
   sp.np_stride = page_max_stride(a->mode, a->max_S);
   sp.part_o = ws.part_o; sp.part_m = ws.part_m; sp.part_l = ws.part_l; sp.part_smax = ws.part_smax;
   sp.status = ws.status;

@@ -1072,7 +1072,8 @@ template <int MODE, int DT, bool LEAN, int NT>
 jf_status_t launch_select_variant(const TopkParams& sp, const TailParams& tp, dim3 grid, cudaStream_t stream, bool fused) {
   constexpr size_t kRegion0 = sel_region0_bytes<MODE, LEAN, NT>();
   const size_t smem = sel_smem_bytes(kRegion0, sp.sort_n, LEAN ? 0 : sp.hm_chunks, NT);
-  static_assert(sel_smem_bytes(kRegion0, 2 * JF_MAX_TOP_K) <= kSelSmemLimit, "select kernel shared memory");
+  static_assert(sel_smem_bytes(kRegion0, 2 * (LEAN ? JF_MAX_TOP_K : kStagedTopK)) <= kSelSmemLimit || NT != kSelThreads,
+                "select kernel shared memory");
   static_assert(NT == kSelThreads || sel_smem_bytes(kRegion0, 1024) <= kTwoBlockBytes, "two narrow blocks per multiprocessor");
   if (smem > kSelSmemLimit) return JF_ERR_UNSUPPORTED;
   if (fused) {
@@ -1142,6 +1143,7 @@ jf_status_t launch_select(const jf_decode_args* a, cudaStream_t stream, bool fus
   // row's chains of dependent memory round trips under the other's arithmetic); otherwise a row's
   // latency is what counts and the 1024-thread block takes it.
   const SelectPlan plan = select_plan(a, sp.scores);
+  if (!plan.supported) return JF_ERR_UNSUPPORTED;
   const bool many = plan.narrow, lean = plan.lean;
   // resident-row kernel: rows of 2..4 score chunks get the side table of float4 maxima if it fits
   auto side_table = [&](int nt, size_t region0, size_t budget) {

@@ -79,6 +79,22 @@ def test_staged_row_select_with_two_blocks_per_multiprocessor(mode, ctx, lens, t
     _run(Case(mode, 5, 32, 8, ctx, lens=lens, seed=71), top_k, stage_b=stage_b)
 
 
+@pytest.mark.parametrize("mode,ctx,lens", [
+    ("k3v2", 131072, [131072, 70001]),    # 4096 page pairs = top-k: the histogram tier gives way to the radix tier
+    ("k4v4", 262144, [262144, 9000]),     # 16384 pages = 4 * top-k: threshold from the page maxima; a row shorter than 2 * top-k
+])
+def test_top_k_4096(mode, ctx, lens):
+    """The widest top-k: its sort buffer has no room beside a staged row, so every such call takes the
+    kernel that works from the scan's page maxima (bitonic ranking, finish in sixteen rounds)."""
+    _run(Case(mode, 2, 4, 1, ctx, lens=lens, seed=88), 4096)
+    from jetfire_b200 import ops
+    case = Case("k3v2", 1, 2, 1, 20002, lens=[20002], seed=89)   # row stride not a multiple of 16: not served
+    kd, ks, vd, vs = case.device_cache()
+    with pytest.raises(RuntimeError):
+        ops.fused_attn_topk(case.mode, case.q.cuda(), kd, ks, vd, vs, case.block_table.cuda(), case.seq_lens.cuda(),
+                            case.ctx, case.H_q, case.H_kv, 16, 4096, case.attn_scale)
+
+
 def test_select_with_other_arguments_than_the_scan_is_reported():
     """The scan leaves page maxima only for calls whose select kernel works from them; a select
     called with arguments under which it would (here: a smaller top-k) after a scan that left none
