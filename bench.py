@@ -90,6 +90,7 @@ def parse_args():
     ap.add_argument("--no-extra", action="store_true", help="skip the extra single-GPU configurations")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle replay of one timed row")
     ap.add_argument("--cpu-threads", type=int, default=0, help="host correction threads (0 = cores / ranks - 1)")
+    ap.add_argument("--no-huge-pages", action="store_true", help="host mirrors on the system's default pages")
     ap.add_argument("--as-shard", metavar="R/N", help="single GPU only: run the shard that rank R of an N-GPU run owns "
                     "(same seeded data, no gather); every figure then counts that shard's bytes")
     return ap.parse_args()
@@ -292,7 +293,7 @@ class Layer:
     pass
 
 
-def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=None, layer0=0):
+def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=None, layer0=0, huge_pages=True):
     """Packed caches (through the product's append kernel), queries, decode calls and -- for the
     first `mirror_layers` layers -- the full-precision host mirror of this shard."""
     kb, vb, gs = MODE_BITS[w["mode"]]
@@ -319,6 +320,9 @@ def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=Non
         if with_mirror:  # full-precision mirror in host DRAM, (H_kv, num_slots, 128)
             L.k_shadow = torch.empty(H_kv, t, 128, dtype=dtype)
             L.v_shadow = torch.empty(H_kv, t, 128, dtype=dtype)
+            if huge_pages:   # before the first write: the random row gathers of the correction miss the TLB less
+                ops.advise_huge_pages(L.k_shadow)
+                ops.advise_huge_pages(L.v_shadow)
             if stage is None:
                 stage = torch.empty(H_kv, t, 128, dtype=dtype, pin_memory=True)
             for src, dst in ((k, L.k_shadow), (v, L.v_shadow)):
@@ -823,7 +827,7 @@ def main():
             dist.broadcast(ml, 0)
             mirror_layers = int(ml.item())
     t_build = time.perf_counter()
-    layers, tables = build_stack(torch, ops, w, shard, device, dtype, mirror_layers)
+    layers, tables = build_stack(torch, ops, w, shard, device, dtype, mirror_layers, huge_pages=not args.no_huge_pages)
     t_build = time.perf_counter() - t_build
     n_layers = len(layers)
     step_bytes_total = job_layer_bytes * n_layers

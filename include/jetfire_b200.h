@@ -363,6 +363,11 @@ jf_status_t jf_stream_wait_cpu_topk_attn(jf_stream_t stream, int64_t handle);
  * (alloc_mapped_pinned_pair, jetfire_vllm/csrc/cpu_topk_attn.cpp:958-1040). */
 jf_status_t jf_alloc_mapped(uint64_t bytes, void** host_ptr, void** device_ptr);
 jf_status_t jf_free_mapped(void* host_ptr);
+/* Asks the operating system to back a host range with 2 MB pages (madvise MADV_HUGEPAGE on the
+ * whole huge pages inside it) -- for mirrors in ordinary host memory, before they are first
+ * touched: the host correction's random 256-byte row gathers then miss the TLB far less.  No
+ * counterpart in the reference.  JF_ERR_UNSUPPORTED if the system refuses; harmless either way. */
+jf_status_t jf_advise_huge_pages(void* ptr, uint64_t bytes);
 
 #ifdef __cplusplus
 }

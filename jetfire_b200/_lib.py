@@ -92,6 +92,7 @@ _SIGS = {
                                                                        C.c_void_p]),
     "jf_cpu_topk_attn_i32": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                            C.c_void_p]),
+    "jf_advise_huge_pages": (C.c_int32, [C.c_void_p, C.c_uint64]),
     "jf_wait_flag": (C.c_int32, [C.c_void_p, C.c_int32]),
     "jf_set_cpu_attn_threads": (C.c_int32, [C.c_int32]),
     "jf_get_cpu_attn_threads": (C.c_int32, []),

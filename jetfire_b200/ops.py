@@ -770,6 +770,14 @@ def get_shadow_append_count(ctx_handle: int) -> int:
     return n.value
 
 
+def advise_huge_pages(host: torch.Tensor) -> bool:
+    """Ask the operating system to back a CPU tensor's memory with 2 MB pages (best right after
+    ``torch.empty``, before the first write).  For host mirrors in ordinary memory: the correction's
+    random row gathers then miss the TLB far less.  Returns False if the system refuses."""
+    _require(not host.is_cuda, "advise_huge_pages: a CPU tensor is expected")
+    return lib.jf_advise_huge_pages(host.data_ptr(), host.numel() * host.element_size()) == _lib.JF_OK
+
+
 def alloc_mapped_pinned_pair(shape, dtype):
     """``(host_tensor, device_tensor)`` over the same pinned, GPU-mapped bytes."""
     n = 1
