@@ -65,8 +65,11 @@ class JetFireCacheStore:
                 self.k_shadow.zero_()
                 self.v_shadow.zero_()
             else:
-                self.k_shadow = torch.zeros(*shape, dtype=dtype)
-                self.v_shadow = torch.zeros(*shape, dtype=dtype)
+                self.k_shadow = torch.empty(*shape, dtype=dtype)
+                self.v_shadow = torch.empty(*shape, dtype=dtype)
+                for t in (self.k_shadow, self.v_shadow):   # 2 MB pages under the mirrors, asked for before the first write
+                    ops.advise_huge_pages(t)
+                    t.zero_()
                 if mirror_append == "stream":
                     self._append_ctx = ops.MirrorAppendCtx(self.k_shadow, self.v_shadow, stream_chunk_tokens)
         else:
