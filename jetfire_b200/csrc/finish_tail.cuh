@@ -21,7 +21,6 @@
 
 namespace jf {
 
-
 constexpr int kSelThreads = 1024;                        // widest block; the unit of the fixed orders below
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kSplitGroups = kSelThreads / JF_HEAD_DIM;  // split partials are summed in 8 strided groups
