@@ -133,11 +133,30 @@ __device__ __forceinline__ void finish_tail(const TailParams& p, TailSmem<MODE>&
         o = fmaf(pre.o[k][i], w, o);
       }
     }
-    for (int s = grp + kPre * kSplitGroups; s < p.splits; s += kSplitGroups) {
-      const int64_t e = (pbase + s) * kHeadsPad + hi;
-      const float w = ex2((p.part_m[e] - M) * kLog2e);
-      Z = fmaf(p.part_l[e], w, Z);
-      o = fmaf(p.part_o[e * JF_HEAD_DIM + d], w, o);
+    // the remaining splits four at a time: the twelve loads first (with many splits -- few
+    // (sequence, KV head) pairs on the GPU -- one load after the other made this the longest part
+    // of the stage), then the sums in the same ascending order as before
+    for (int s = grp + kPre * kSplitGroups; s < p.splits; s += 4 * kSplitGroups) {
+      float pm[4], pl[4], po[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int su = s + u * kSplitGroups;
+        pm[u] = kMinusBig; pl[u] = 0.f; po[u] = 0.f;
+        if (su < p.splits) {
+          const int64_t e = (pbase + su) * kHeadsPad + hi;
+          pm[u] = p.part_m[e];
+          pl[u] = p.part_l[e];
+          po[u] = p.part_o[e * JF_HEAD_DIM + d];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s + u * kSplitGroups < p.splits) {
+          const float w = ex2((pm[u] - M) * kLog2e);
+          Z = fmaf(pl[u], w, Z);
+          o = fmaf(po[u], w, o);
+        }
+      }
     }
     sm.o[grp][d] = o;
     if (d == 0) sm.z[grp] = Z;
