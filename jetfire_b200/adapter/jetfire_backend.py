@@ -2,9 +2,10 @@
 
 vLLM's classes are imported lazily and only here, so the rest of the package works without
 vLLM.  ``JetFireAttentionImplMixin`` holds the routing (decode -> ``try_jetfire_decode``,
-append -> ``JetFireCacheStore.write_slots``); ``make_backend()`` binds it to the vLLM
-FlashAttention classes of the installed version and returns the backend class to register
-as ``CUSTOM`` (``register_backend(AttentionBackendEnum.CUSTOM, ...)``, reference
+a step with decode and prefill sequences -> ``try_jetfire_mixed``, append ->
+``JetFireCacheStore.write_slots``); ``make_backend()`` binds it to the vLLM FlashAttention
+classes of the installed version, with a metadata builder that notes the scheduler's
+decode/prefill split on the metadata, and returns the backend class to register as ``CUSTOM`` (``register_backend(AttentionBackendEnum.CUSTOM, ...)``, reference
 jetfire_vllm/adapter/registry.py:19, :61).
 """
 from __future__ import annotations
@@ -12,6 +13,7 @@ from __future__ import annotations
 from .cache_store import JetFireCacheStore
 from .config import get_jetfire_config
 from .decode_path import try_jetfire_decode
+from .mixed_batch import annotate_split_counts, try_jetfire_mixed
 
 _STORES: dict[str, JetFireCacheStore] = {}
 
@@ -35,6 +37,12 @@ class JetFireAttentionImplMixin:
                                       output=output, store=store, cfg=get_jetfire_config())
             if done is not None:
                 return done
+            if key is not None and value is not None:
+                done = try_jetfire_mixed(impl=self, layer=layer, query=query, key=key, value=value,
+                                         attn_metadata=attn_metadata, output=output, store=store,
+                                         cfg=get_jetfire_config())
+                if done is not None:
+                    return done
         return super().forward(layer, query, key, value, kv_cache, attn_metadata, output=output,
                                output_scale=output_scale, output_block_scale=output_block_scale)
 
@@ -61,6 +69,19 @@ def make_backend():
     class JetFireAttentionImpl(JetFireAttentionImplMixin, FlashAttentionImpl):
         pass
 
+    class JetFireAttentionMetadataBuilder(FlashAttentionMetadataBuilder):
+        """FlashAttention's metadata plus the decode/prefill split of the step, taken from the
+        host copies the scheduler already holds (jetfire_vllm/adapter/jetfire_backend.py:66-127)."""
+
+        def build(self, common_prefix_len, common_attn_metadata, fast_build=False):
+            metadata = super().build(common_prefix_len, common_attn_metadata, fast_build=fast_build)
+            try:
+                annotate_split_counts(metadata, common_attn_metadata.query_start_loc_cpu.tolist(),
+                                      common_attn_metadata.seq_lens_cpu.tolist())
+            except (AttributeError, ValueError):
+                pass        # without the counts a mixed step is split from the device tensors
+            return metadata
+
     class JetFireAttentionBackend(FlashAttentionBackend):
         @staticmethod
         def get_name() -> str:
@@ -72,7 +93,7 @@ def make_backend():
 
         @staticmethod
         def get_builder_cls():
-            return FlashAttentionMetadataBuilder
+            return JetFireAttentionMetadataBuilder
 
     return JetFireAttentionBackend
 

@@ -74,3 +74,19 @@ class Case:
         ops.fused_quant_write_kv(key_tok, val_tok, slots, k_data, k_scales, v_data, v_scales,
                                  self.gs, self.kb, self.vb)
         return k_data, k_scales, v_data, v_scales
+
+
+def causal_prefill_attention(*, q, k, v, out, cu_seqlens, max_seqlen, impl, layer, attn_metadata) -> None:
+    """Plain causal attention in fp32 over the sequences ``cu_seqlens`` delimits (rows of ``q
+    (T, H_q, D)``, ``k`` / ``v (T, H_kv, D)``): what a variable-length flash attention computes
+    for prefill rows without cached context.  Stands in for it in the tests of mixed steps."""
+    H_q, H_kv = q.shape[1], k.shape[1]
+    bounds = [int(x) for x in cu_seqlens]
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        qs = q[lo:hi].float().transpose(0, 1)                                   # (H_q, L, D)
+        ks = k[lo:hi].float().transpose(0, 1).repeat_interleave(H_q // H_kv, 0)
+        vs = v[lo:hi].float().transpose(0, 1).repeat_interleave(H_q // H_kv, 0)
+        s = (qs @ ks.transpose(1, 2)) * float(impl.scale)
+        L = hi - lo
+        s = s.masked_fill(torch.ones(L, L, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+        out[lo:hi].copy_((torch.softmax(s, -1) @ vs).transpose(0, 1).to(out.dtype))

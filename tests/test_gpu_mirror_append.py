@@ -262,6 +262,118 @@ def test_backend_routes_append_and_decode_through_installed_stores(monkeypatch):
     assert impl.forward(layer, case.q.cuda(), None, None, None, prefill, output=out) == "native"
 
 
+@pytest.mark.parametrize("order", ["decode_first_with_counts", "decode_first", "interleaved"])
+def test_step_with_decode_and_prefill_sequences(order):
+    """A step in which two sequences decode and two are prefilled: the decode rows come from the
+    packed cache (bit for bit what a pure decode step of those two sequences gives), the prefill
+    rows from a causal attention over the step's own keys and values, each written to its own
+    rows of the output -- with the scheduler's counts on the metadata (slices, nothing read back),
+    without them, and with the sequences interleaved."""
+    from jetfire_b200.adapter.cache_store import JetFireCacheStore
+    from jetfire_b200.adapter.config import JetFireConfig
+    from jetfire_b200.adapter.decode_path import make_decode_metadata, try_jetfire_decode
+    from jetfire_b200.adapter.mixed_batch import MixedBatchStats, annotate_split_counts, try_jetfire_mixed
+    from jf_testlib import causal_prefill_attention
+    case = Case("k3v2", 2, 8, 2, 300, lens=[300, 123], seed=41)
+    cfg = JetFireConfig(mode="SymInt3K_SymInt2V", top_k=64, group_size=64, cpu_attn_threads=2)
+    st = JetFireCacheStore(num_blocks=case.n_blocks, num_kv_heads=case.H_kv, head_dim=128, cfg=cfg, device="cuda",
+                           dtype=case.dtype, mirror_append="mapped")
+    key_all = case.k_full.transpose(0, 1).contiguous().cuda()
+    val_all = case.v_full.transpose(0, 1).contiguous().cuda()
+    st.write_slots(key_all, val_all, torch.arange(case.num_slots, dtype=torch.int64, device="cuda"))
+    st.flush_pending_writes()
+    impl = SimpleNamespace(scale=case.attn_scale, attn_type=SimpleNamespace(name="DECODER"))
+    layer = SimpleNamespace(num_heads=case.H_q, num_kv_heads=case.H_kv, head_size=128, layer_name="l0")
+    # the pure decode step of the two cached sequences
+    want_dec = torch.zeros(2, case.H_q * 128, dtype=case.dtype, device="cuda")
+    md_dec = make_decode_metadata(case.seq_lens.cuda(), case.block_table.cuda())
+    assert try_jetfire_decode(impl=impl, layer=layer, query=case.q.cuda(), attn_metadata=md_dec, output=want_dec,
+                              store=st, cfg=cfg) is want_dec
+    # the mixed step: sequences 0 and 1 decode, two new prompts of 5 and 19 tokens are prefilled
+    g = torch.Generator().manual_seed(5)
+    pre_len = [5, 19]
+    if order == "interleaved":
+        seqs = [("p", 0), ("d", 0), ("p", 1), ("d", 1)]
+    else:
+        seqs = [("d", 0), ("d", 1), ("p", 0), ("p", 1)]
+    qlens = [1 if kind == "d" else pre_len[i] for kind, i in seqs]
+    T = sum(qlens)
+    q = torch.randn(T, case.H_q, 128, generator=g).to(case.dtype).cuda()
+    k = torch.randn(T, case.H_kv, 128, generator=g).to(case.dtype).cuda()
+    v = torch.randn(T, case.H_kv, 128, generator=g).to(case.dtype).cuda()
+    starts = [0]
+    for n in qlens:
+        starts.append(starts[-1] + n)
+    n_blk = case.block_table.shape[1]
+    bt = torch.zeros(4, n_blk, dtype=case.block_table.dtype)
+    lens = []
+    for s_i, (kind, i) in enumerate(seqs):
+        if kind == "d":
+            q[starts[s_i]] = case.q[i].cuda()
+            bt[s_i] = case.block_table[i]
+            lens.append(int(case.seq_lens[i]))
+        else:
+            lens.append(pre_len[i])
+    md = SimpleNamespace(query_start_loc=torch.tensor(starts, dtype=torch.int32, device="cuda"),
+                         seq_lens=torch.tensor(lens, dtype=torch.int32, device="cuda"), block_table=bt.cuda(),
+                         max_query_len=max(qlens), max_seq_len=max(lens), num_actual_tokens=T, use_cascade=False,
+                         causal=True)
+    if order == "decode_first_with_counts":
+        annotate_split_counts(md, starts, lens)
+        assert (md.num_decodes, md.num_prefills, md.num_prefill_tokens) == (2, 2, 24)
+    out = torch.full((T, case.H_q * 128), 9.0, dtype=case.dtype, device="cuda")
+    stats = MixedBatchStats()
+    got = try_jetfire_mixed(impl=impl, layer=layer, query=q.view(T, -1), key=k.view(T, -1), value=v.view(T, -1),
+                            attn_metadata=md, output=out, store=st, cfg=cfg,
+                            prefill_attention=causal_prefill_attention, stats=stats)
+    assert got is out and stats.mixed_batch_count == 1 and not stats.handed_back
+    torch.cuda.synchronize()
+    dec_i = 0
+    for s_i, (kind, i) in enumerate(seqs):
+        lo, hi = starts[s_i], starts[s_i + 1]
+        if kind == "d":
+            assert torch.equal(out[lo], want_dec[i]), f"decode row of sequence {i} differs"
+            dec_i += 1
+        else:
+            want = torch.empty(hi - lo, case.H_q, 128, dtype=case.dtype, device="cuda")
+            causal_prefill_attention(q=q[lo:hi], k=k[lo:hi], v=v[lo:hi], out=want,
+                                     cu_seqlens=[0, hi - lo], max_seqlen=hi - lo, impl=impl, layer=None,
+                                     attn_metadata=None)
+            assert torch.equal(out[lo:hi].view(hi - lo, case.H_q, 128), want), f"prefill rows of prompt {i} differ"
+    assert dec_i == 2
+
+
+def test_default_prefill_attention_of_a_mixed_step_on_the_device():
+    """The variable-length flash attention the mixed step uses by default, against plain causal
+    attention in fp32 (bf16 inputs: agreement to bf16 rounding of values of order 1)."""
+    from jetfire_b200.adapter import mixed_batch as mb
+    from jf_testlib import causal_prefill_attention
+    try:
+        mb._resolve_flash_varlen()
+    except ImportError as exc:
+        pytest.skip(str(exc))
+    g = torch.Generator().manual_seed(9)
+    lens = [7, 33, 16]
+    T, H_q, H_kv = sum(lens), 8, 2
+    q = torch.randn(T, H_q, 128, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(T, H_kv, 128, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(T, H_kv, 128, generator=g).to(torch.bfloat16).cuda()
+    cu = torch.tensor([0, 7, 40, 56], dtype=torch.int32, device="cuda")
+    impl = SimpleNamespace(scale=128 ** -0.5, sliding_window=None, logits_soft_cap=None, alibi_slopes=None)
+    got = torch.zeros(T, H_q, 128, dtype=torch.bfloat16, device="cuda")
+    want = torch.zeros(T, H_q, 128, dtype=torch.float32, device="cuda")
+    try:
+        mb.flash_varlen_prefill(q=q, k=k, v=v, out=got, cu_seqlens=cu, max_seqlen=33, impl=impl, layer=None,
+                                attn_metadata=SimpleNamespace(causal=True))
+    except (RuntimeError, NotImplementedError, AssertionError) as exc:
+        pytest.skip(f"the installed flash attention does not run on this device: {exc}")
+    causal_prefill_attention(q=q, k=k, v=v, out=want, cu_seqlens=cu.tolist(), max_seqlen=33, impl=impl, layer=None,
+                             attn_metadata=None)
+    torch.cuda.synchronize()
+    err = (got.float() - want).abs()
+    assert float(err.max()) <= 2e-2, f"max err {float(err.max()):.3e}"
+
+
 def test_decode_steps_replayed_as_one_cuda_graph_with_host_nodes():
     """A whole decode step of one layer captured once and replayed: append of the new token
     (packed cache + mapped mirror, one kernel), query upload, scan + selection, slot download,

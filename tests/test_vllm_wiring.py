@@ -32,6 +32,15 @@ def test_backend_binds_registers_and_resolves():
         theirs = list(inspect.signature(getattr(FlashAttentionImpl, meth)).parameters)
         mine = list(inspect.signature(getattr(jb.JetFireAttentionImplMixin, meth)).parameters)
         assert mine == theirs, f"{meth}: {mine} vs {theirs}"
+    # the metadata builder is FlashAttention's, with the decode/prefill split noted on what it builds
+    from vllm.v1.attention.backends.flash_attn import FlashAttentionMetadataBuilder
+    builder = backend.get_builder_cls()
+    assert issubclass(builder, FlashAttentionMetadataBuilder) and builder is not FlashAttentionMetadataBuilder
+    assert (list(inspect.signature(builder.build).parameters)
+            == list(inspect.signature(FlashAttentionMetadataBuilder.build).parameters))
+    from vllm.v1.attention.backend import CommonAttentionMetadata
+    assert "query_start_loc_cpu" in CommonAttentionMetadata.__dataclass_fields__
+    assert isinstance(getattr(CommonAttentionMetadata, "seq_lens_cpu", None), property)
     assert ensure_jetfire_registered() is True
     assert ensure_jetfire_registered() is True            # idempotent
     resolved = AttentionBackendEnum.CUSTOM.get_class()
