@@ -91,6 +91,8 @@ def parse_args():
     ap.add_argument("--no-check", action="store_true", help="skip the oracle replay of one timed row")
     ap.add_argument("--cpu-threads", type=int, default=0, help="host correction threads (0 = cores / ranks - 1)")
     ap.add_argument("--no-huge-pages", action="store_true", help="host mirrors on the system's default pages")
+    ap.add_argument("--no-numa", action="store_true",
+                    help="leave the host mirrors and the correction workers where the system puts them")
     ap.add_argument("--as-shard", metavar="R/N", help="single GPU only: run the shard that rank R of an N-GPU run owns "
                     "(same seeded data, no gather); every figure then counts that shard's bytes")
     return ap.parse_args()
@@ -293,7 +295,8 @@ class Layer:
     pass
 
 
-def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=None, layer0=0, huge_pages=True):
+def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=None, layer0=0, huge_pages=True,
+                numa_node=-1):
     """Packed caches (through the product's append kernel), queries, decode calls and -- for the
     first `mirror_layers` layers -- the full-precision host mirror of this shard."""
     kb, vb, gs = MODE_BITS[w["mode"]]
@@ -323,6 +326,9 @@ def build_stack(torch, ops, w, shard, device, dtype, mirror_layers, n_layers=Non
             if huge_pages:   # before the first write: the random row gathers of the correction miss the TLB less
                 ops.advise_huge_pages(L.k_shadow)
                 ops.advise_huge_pages(L.v_shadow)
+            if numa_node >= 0:   # likewise before the first write
+                ops.bind_memory_to_node(L.k_shadow, numa_node)
+                ops.bind_memory_to_node(L.v_shadow, numa_node)
             if stage is None:
                 stage = torch.empty(H_kv, t, 128, dtype=dtype, pin_memory=True)
             for src, dst in ((k, L.k_shadow), (v, L.v_shadow)):
@@ -786,6 +792,20 @@ def main():
     # one core per rank stays with the thread that drives the GPU: with a worker on every core the
     # driving thread is preempted and every layer waits for it
     cpu_threads = args.cpu_threads or max(1, cores // world - 1)
+    # On a host with several memory nodes the mirrors of this rank and the workers that gather
+    # from them go to the node its GPU is attached to (nothing happens on a single-node host, or
+    # where the system does not say where the GPU sits).
+    from jetfire_b200.adapter.sharding import resolve_numa_node, workers_on_node
+    numa_nodes = ops.numa_node_count()
+    numa_node = -1 if args.no_numa else resolve_numa_node(-2, ops.numa_node_of_device(device.index or 0), numa_nodes)
+    if numa_node >= 0:
+        try:
+            node_cpus = len(ops.numa_node_cpus(numa_node))
+            if not args.cpu_threads:
+                cpu_threads = workers_on_node(cpu_threads, node_cpus - 1, (world + numa_nodes - 1) // numa_nodes)
+            ops.set_cpu_attn_node(numa_node)
+        except RuntimeError:
+            numa_node = -1
     ops.set_cpu_attn_threads(cpu_threads)
 
     # a few layers of the other single-GPU configurations first (their memory is released again)
@@ -827,7 +847,8 @@ def main():
             dist.broadcast(ml, 0)
             mirror_layers = int(ml.item())
     t_build = time.perf_counter()
-    layers, tables = build_stack(torch, ops, w, shard, device, dtype, mirror_layers, huge_pages=not args.no_huge_pages)
+    layers, tables = build_stack(torch, ops, w, shard, device, dtype, mirror_layers, huge_pages=not args.no_huge_pages,
+                                 numa_node=numa_node)
     t_build = time.perf_counter() - t_build
     n_layers = len(layers)
     step_bytes_total = job_layer_bytes * n_layers
@@ -1107,6 +1128,8 @@ def main():
             if world > 1 else (f"single GPU running the shard of rank {as_shard} ({shard.kv_count} KV heads, {shard.q_count} "
                                f"query heads, {shard.b_count} sequences)" if as_shard else "single GPU"),
             "data_generator": "counter hash (Irwin-Hall of twelve 16-bit uniforms per element), identical on GPU and CPU",
+            "host": {"cores": cores, "correction_workers": cpu_threads, "memory_nodes": numa_nodes,
+                     "mirror_node": numa_node},
             "build_s": round(t_build, 1), "oracle_check": check, "gather_check": gather_check}
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,

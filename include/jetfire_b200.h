@@ -369,6 +369,29 @@ jf_status_t jf_free_mapped(void* host_ptr);
  * counterpart in the reference.  JF_ERR_UNSUPPORTED if the system refuses; harmless either way. */
 jf_status_t jf_advise_huge_pages(void* ptr, uint64_t bytes);
 
+/* ---- NUMA placement of the mirrors and the correction workers ---------------------------------
+ * No counterpart in the reference, which leaves placement to first touch.  On a host with more
+ * than one memory node the mirror of a GPU and the workers that gather from it belong on the
+ * node that GPU is attached to; elsewhere every gathered row crosses the socket interconnect.
+ * The layout is read from sysfs (below $JF_SYSFS_ROOT when set, else /sys).
+ *
+ * jf_numa_node_count      memory nodes online (1 when the system does not say)
+ * jf_numa_node_of_device  node of the GPU's PCI function, -1 when unknown
+ * jf_numa_node_cpus       processors of a node, ascending; *count = how many exist
+ * jf_bind_memory_to_node  mbind(MPOL_BIND) of the whole pages in the range; before the memory is
+ *                         first touched or registered.  JF_ERR_UNSUPPORTED if refused.
+ * jf_alloc_mapped_on_node jf_alloc_mapped with the block bound to `node` first (-1: no binding);
+ *                         a refused binding still returns memory, placed by first touch
+ * jf_set_cpu_attn_node    correction workers run only on that node's processors (-1: anywhere);
+ *                         takes effect with the next job */
+int32_t     jf_numa_node_count(void);
+int32_t     jf_numa_node_of_device(int32_t device);
+jf_status_t jf_numa_node_cpus(int32_t node, int32_t* cpus, int32_t capacity, int32_t* count);
+jf_status_t jf_bind_memory_to_node(void* ptr, uint64_t bytes, int32_t node);
+jf_status_t jf_alloc_mapped_on_node(uint64_t bytes, int32_t node, void** host_ptr, void** device_ptr);
+jf_status_t jf_set_cpu_attn_node(int32_t node);
+int32_t     jf_get_cpu_attn_node(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,6 +93,13 @@ _SIGS = {
     "jf_cpu_topk_attn_i32": (C.c_int32, [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_int64, C.c_int32, C.c_float,
                                                                            C.c_void_p]),
     "jf_advise_huge_pages": (C.c_int32, [C.c_void_p, C.c_uint64]),
+    "jf_numa_node_count": (C.c_int32, []),
+    "jf_numa_node_of_device": (C.c_int32, [C.c_int32]),
+    "jf_numa_node_cpus": (C.c_int32, [C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_int32)]),
+    "jf_bind_memory_to_node": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_int32]),
+    "jf_alloc_mapped_on_node": (C.c_int32, [C.c_uint64, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "jf_set_cpu_attn_node": (C.c_int32, [C.c_int32]),
+    "jf_get_cpu_attn_node": (C.c_int32, []),
     "jf_wait_flag": (C.c_int32, [C.c_void_p, C.c_int32]),
     "jf_set_cpu_attn_threads": (C.c_int32, [C.c_int32]),
     "jf_get_cpu_attn_threads": (C.c_int32, []),

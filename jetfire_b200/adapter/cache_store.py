@@ -21,6 +21,7 @@ import torch
 
 from .. import ops
 from .config import JetFireConfig
+from .sharding import resolve_numa_node
 
 
 class JetFireCacheStore:
@@ -57,11 +58,17 @@ class JetFireCacheStore:
         self._k_shadow_dev = self._v_shadow_dev = None
         self._append_ctx = None
         self._pending_event = None
+        # memory node of the mirrors (and of the workers that gather from them): the GPU's own on a
+        # host with several nodes, unless configured otherwise
+        self.numa_node = -1
+        if self.shadow_enabled and self.device.type == "cuda":
+            index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+            self.numa_node = resolve_numa_node(cfg.numa_node, ops.numa_node_of_device(index), ops.numa_node_count())
         if self.shadow_enabled:
             shape = (num_kv_heads, self.num_slots, head_dim)
             if mirror_append == "mapped":
-                self.k_shadow, self._k_shadow_dev = ops.alloc_mapped_pinned_pair(shape, dtype)
-                self.v_shadow, self._v_shadow_dev = ops.alloc_mapped_pinned_pair(shape, dtype)
+                self.k_shadow, self._k_shadow_dev = ops.alloc_mapped_pinned_pair(shape, dtype, node=self.numa_node)
+                self.v_shadow, self._v_shadow_dev = ops.alloc_mapped_pinned_pair(shape, dtype, node=self.numa_node)
                 self.k_shadow.zero_()
                 self.v_shadow.zero_()
             else:
@@ -69,6 +76,8 @@ class JetFireCacheStore:
                 self.v_shadow = torch.empty(*shape, dtype=dtype)
                 for t in (self.k_shadow, self.v_shadow):   # 2 MB pages under the mirrors, asked for before the first write
                     ops.advise_huge_pages(t)
+                    if self.numa_node >= 0:
+                        ops.bind_memory_to_node(t, self.numa_node)
                     t.zero_()
                 if mirror_append == "stream":
                     self._append_ctx = ops.MirrorAppendCtx(self.k_shadow, self.v_shadow, stream_chunk_tokens)

@@ -2,7 +2,9 @@
 
 Only the two paper modes are registered; one code path, no experiment knobs.  Environment
 variables kept from the reference: ``JETFIRE_MODE``, ``JETFIRE_TOPK``, ``JETFIRE_GROUP_SIZE``,
-``JETFIRE_CPU_ATTN_THREADS``, ``JETFIRE_MAX_BATCH_SIZE``.
+``JETFIRE_CPU_ATTN_THREADS``, ``JETFIRE_MAX_BATCH_SIZE``.  Own: ``JETFIRE_SLOTS_I32`` and
+``JETFIRE_NUMA_NODE`` (``auto`` | ``off`` | a node number: where the host mirrors and the
+correction workers of this rank are placed).
 """
 from __future__ import annotations
 
@@ -32,6 +34,9 @@ SCHEME_TO_KERNEL_MODE = {"SymInt3K_SymInt2V": "k3v2", "SymInt4K_SymInt4V": "k4v4
 SUPPORTED_TOP_K = (32, 64, 128, 256, 512, 1024, 2048, 4096)
 
 
+NUMA_AUTO, NUMA_OFF = -2, -1   # the GPU's own node when the host has several / leave it to first touch
+
+
 @dataclass(frozen=True)
 class JetFireConfig:
     mode: str = "SymInt3K_SymInt2V"      # jetfire_vllm/adapter/config.py:166
@@ -41,6 +46,7 @@ class JetFireConfig:
     max_batch_size: int = 32
     enabled: bool = True
     slots_i32: bool = True                # selected slots cross to the host as int32 (the reference: int64)
+    numa_node: int = NUMA_AUTO            # memory node of mirrors and workers: NUMA_AUTO, NUMA_OFF or a node
 
     @property
     def scheme(self) -> QuantScheme:
@@ -62,6 +68,21 @@ def _int_env(name: str, default: int) -> int:
         return int(raw)
     except ValueError as exc:
         raise ValueError(f"{name} must be an integer, got {raw!r}") from exc
+
+
+def _numa_env() -> int:
+    raw = (os.environ.get("JETFIRE_NUMA_NODE") or "auto").strip().lower()
+    if raw == "auto":
+        return NUMA_AUTO
+    if raw in ("off", "none", "-1"):
+        return NUMA_OFF
+    try:
+        node = int(raw)
+    except ValueError as exc:
+        raise ValueError(f"JETFIRE_NUMA_NODE must be 'auto', 'off' or a node number, got {raw!r}") from exc
+    if node < 0:
+        raise ValueError(f"JETFIRE_NUMA_NODE must be 'auto', 'off' or a node number, got {raw!r}")
+    return node
 
 
 def get_jetfire_config() -> JetFireConfig:
@@ -89,7 +110,7 @@ def get_jetfire_config() -> JetFireConfig:
         raise ValueError("JETFIRE_CPU_ATTN_THREADS must be positive")
     _CONFIG = JetFireConfig(mode=mode, top_k=top_k, group_size=group, cpu_attn_threads=threads,
                             max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32),
-                            slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0)
+                            slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0, numa_node=_numa_env())
     return _CONFIG
 
 

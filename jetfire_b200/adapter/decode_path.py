@@ -17,7 +17,7 @@ import torch
 from .. import ops
 from .cache_store import JetFireCacheStore
 from .config import SUPPORTED_TOP_K, JetFireConfig, get_jetfire_config
-from .sharding import cpu_threads_per_rank
+from .sharding import cpu_threads_per_rank, workers_on_node
 
 def _select_top_k(config_top_k: int, seq_len: int, supported: tuple[int, ...]) -> int | None:
     """Largest supported width <= the sequence length (short sequences are padded with -1),
@@ -67,19 +67,30 @@ class _DecodeBuffers:
 
 
 _BUFFERS: dict[tuple, _DecodeBuffers] = {}
-_WORKERS_SET: int | None = None
+_WORKERS_SET: tuple[int, int] | None = None
 
 
-def _set_worker_count(cfg: JetFireConfig) -> None:
-    """Size the correction pool once: the configured count, capped by this rank's share of the
-    host cores (the ranks of a node share them; ``sharding.cpu_threads_per_rank``)."""
+def _set_worker_count(cfg: JetFireConfig, node: int = -1) -> None:
+    """Size and place the correction pool once: the configured count, capped by this rank's share
+    of the host cores (the ranks of a node share them; ``sharding.cpu_threads_per_rank``); with a
+    memory node given (the store's, where its mirrors are), the workers run on that node's
+    processors only and share them with the other ranks placed there."""
     global _WORKERS_SET
     import os
     world = int(os.environ.get("WORLD_SIZE", "1") or 1)
     want = max(1, min(int(cfg.cpu_attn_threads), cpu_threads_per_rank(os.cpu_count() or 1, world)))
-    if _WORKERS_SET != want:
+    if node >= 0:
+        try:
+            cpus = len(ops.numa_node_cpus(node))
+        except RuntimeError:
+            node, cpus = -1, 0
+        if node >= 0:
+            nodes = max(ops.numa_node_count(), 1)
+            want = workers_on_node(int(cfg.cpu_attn_threads), cpus, (world + nodes - 1) // nodes)
+    if _WORKERS_SET != (want, node):
+        ops.set_cpu_attn_node(node)
         ops.set_cpu_attn_threads(want)
-        _WORKERS_SET = want
+        _WORKERS_SET = (want, node)
 
 
 def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table: torch.Tensor,
@@ -112,7 +123,7 @@ def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table
     # the slots cross to the host as 32-bit integers (half the bytes) unless configured otherwise
     buf.ts_host.copy_(call.out["topk_slots_i32"] if cfg.slots_i32 else res.topk_slots, non_blocking=True)
     call.status()   # synchronises the stream; raises if a bounded wait inside a kernel ran out
-    _set_worker_count(cfg)
+    _set_worker_count(cfg, getattr(store, "numa_node", -1))
     ops.cpu_topk_attn(buf.q_host, store.k_shadow, store.v_shadow, None, buf.ts_host, buf.o_new_host, scale)
     o_new = buf.o_new_host.to(q.device, non_blocking=True)
     out_view = output[:B].view(B, num_heads, 128)

@@ -52,6 +52,23 @@ def cpu_threads_per_rank(cores: int, world: int) -> int:
     return max(1, cores // max(world, 1))
 
 
+def resolve_numa_node(configured: int, device_node: int, node_count: int) -> int:
+    """Memory node for a rank's host mirrors and correction workers, -1 for none.
+    ``configured``: -2 = the GPU's own node when the host has more than one and says where the
+    GPU sits, -1 = none, otherwise the node itself (ignored on a host that lacks it)."""
+    if configured == -1 or node_count <= 1:
+        return -1
+    if configured == -2:
+        return device_node if 0 <= device_node < node_count else -1
+    return configured if 0 <= configured < node_count else -1
+
+
+def workers_on_node(want: int, node_cpus: int, ranks_on_node: int) -> int:
+    """Correction workers of a rank that is confined to one memory node: that node's processors
+    are shared by the ranks placed there."""
+    return max(1, min(want, node_cpus // max(ranks_on_node, 1)))
+
+
 def gather_outputs(local_out: torch.Tensor, plan: list[Shard], B: int, H_q: int, group=None) -> torch.Tensor:
     """All-gather ``local_out (b_count, q_count, 128)`` of every rank into ``(B, H_q * 128)``.
     One collective (NCCL on GPUs, gloo on CPU); shards are equal-sized by construction."""

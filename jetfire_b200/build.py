@@ -18,7 +18,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libjetfire_b200.so"
 SOURCES = ["pack_append.cu", "decode_scan.cu", "decode_scan_k4v4.cu", "topk_select.cu", "decode_finish.cu", "decode_static.cu",
-           "jf_misc.cu", "mirror_append.cu", "cpu_correction.cpp"]
+           "jf_misc.cu", "mirror_append.cu", "cpu_correction.cpp", "numa_place.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-O3", "-Xcompiler", "-pthread"]
 
@@ -34,7 +34,7 @@ def up_to_date() -> bool:
     if not LIB.exists():
         return False
     t = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.cpp")) + \
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.cpp")) + list(CSRC.glob("*.h")) + \
         [PKG.parent / "include" / "jetfire_b200.h"]
     return all(d.stat().st_mtime <= t for d in deps)
 

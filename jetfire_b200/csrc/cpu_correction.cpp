@@ -28,6 +28,7 @@
 #include <cuda_runtime_api.h>
 
 #include "../../include/jetfire_b200.h"
+#include "numa_place.h"
 
 namespace {
 
@@ -332,17 +333,23 @@ class Pool {
 
   ~Pool() { shutdown(); }
   int size() const { return n_; }
+  int node() const { return node_; }
   bool running() const { return n_ > 0; }
 
   void start(int n) {
     shutdown();
     std::lock_guard<std::mutex> g(api_);
     n_ = n;
+    node_ = jf::worker_node();
     stop_ = false;
     submitted_.store(0);
     completed_.store(0);
     for (auto& sl : slots_) { sl.left.store(n); sl.done_id.store(0); }   // "everyone has left": free
-    for (int i = 0; i < n; ++i) workers_.emplace_back([this] { loop(); });
+    for (int i = 0; i < n; ++i)
+      workers_.emplace_back([this] {
+        if (node_ >= 0) jf::pin_this_thread_to_node(node_);   // a refusal leaves the worker unconfined
+        loop();
+      });
   }
   void shutdown() {
     std::lock_guard<std::mutex> g(api_);
@@ -466,6 +473,7 @@ class Pool {
   std::atomic<uint64_t> submitted_{0}, completed_{0};
   bool stop_ = false;
   int n_ = 0;
+  int node_ = -1;   // processors the workers were confined to when they started
 };
 
 Pool& pool() {
@@ -496,14 +504,14 @@ jf_status_t make_job(Job& j, const void* q, const void* ks, const void* vs, cons
 void ensure_pool() {
   int want = g_threads.load();
   if (want <= 0) want = default_threads();
-  if (!pool().running() || pool().size() != want) pool().start(want);
+  if (!pool().running() || pool().size() != want || pool().node() != jf::worker_node()) pool().start(want);
 }
 
 // The pool with the configured worker count; a change of the count waits for queued jobs first.
 jf_status_t ready_pool() {
   int want = g_threads.load();
   if (want <= 0) want = default_threads();
-  if (pool().running() && pool().size() == want) return JF_OK;
+  if (pool().running() && pool().size() == want && pool().node() == jf::worker_node()) return JF_OK;
   if (pool().running() && !pool().wait(30000)) return JF_ERR_TIMEOUT;
   ensure_pool();
   return JF_OK;

@@ -70,16 +70,19 @@ constexpr uint64_t kHugeThreshold = 8ull << 20;
 // Pinned host memory that the GPU can address directly, so that what one side writes the other
 // reads without an explicit copy (alloc_mapped_pinned_pair, jetfire_vllm/csrc/cpu_topk_attn.cpp:958-1040).
 // Large blocks -- the host mirrors -- are allocated on a 2 MB boundary, advised to use huge pages
-// (the host correction gathers rows from them at random) and then registered with the driver;
-// small ones, or a system that refuses any of these steps, get the driver's own allocation.
-extern "C" jf_status_t jf_alloc_mapped(uint64_t bytes, void** host_ptr, void** device_ptr) {
-  if (!host_ptr || !device_ptr || bytes == 0) return JF_ERR_ARG;
+// (the host correction gathers rows from them at random), bound to a memory node if one is asked
+// for, and then registered with the driver; small ones without a node, or a system that refuses
+// any of these steps, get the driver's own allocation.
+extern "C" jf_status_t jf_alloc_mapped_on_node(uint64_t bytes, int32_t node, void** host_ptr, void** device_ptr) {
+  if (!host_ptr || !device_ptr || bytes == 0 || node < -1) return JF_ERR_ARG;
   void* h = nullptr;
   void* d = nullptr;
-  if (bytes >= kHugeThreshold) {
-    const uint64_t rounded = (bytes + (2ull << 20) - 1) & ~((2ull << 20) - 1);
-    if (posix_memalign(&h, 2u << 20, rounded) == 0 && h) {
-      jf_advise_huge_pages(h, rounded);
+  if (bytes >= kHugeThreshold || node >= 0) {
+    const uint64_t unit = bytes >= kHugeThreshold ? (2ull << 20) : 4096ull;
+    const uint64_t rounded = (bytes + unit - 1) & ~(unit - 1);
+    if (posix_memalign(&h, unit, rounded) == 0 && h) {
+      if (bytes >= kHugeThreshold) jf_advise_huge_pages(h, rounded);
+      if (node >= 0) jf_bind_memory_to_node(h, rounded, node);   // a refusal leaves first-touch placement
       if (cudaHostRegister(h, rounded, cudaHostRegisterMapped | cudaHostRegisterPortable) == cudaSuccess) {
         if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) {
           std::lock_guard<std::mutex> lock(g_reg_mu);
@@ -101,6 +104,10 @@ extern "C" jf_status_t jf_alloc_mapped(uint64_t bytes, void** host_ptr, void** d
   *host_ptr = h;
   *device_ptr = d;
   return JF_OK;
+}
+
+extern "C" jf_status_t jf_alloc_mapped(uint64_t bytes, void** host_ptr, void** device_ptr) {
+  return jf_alloc_mapped_on_node(bytes, -1, host_ptr, device_ptr);
 }
 
 extern "C" jf_status_t jf_free_mapped(void* host_ptr) {

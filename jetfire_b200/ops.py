@@ -778,15 +778,52 @@ def advise_huge_pages(host: torch.Tensor) -> bool:
     return lib.jf_advise_huge_pages(host.data_ptr(), host.numel() * host.element_size()) == _lib.JF_OK
 
 
-def alloc_mapped_pinned_pair(shape, dtype):
-    """``(host_tensor, device_tensor)`` over the same pinned, GPU-mapped bytes."""
+def numa_node_count() -> int:
+    """Memory nodes of this host (1 when the system does not say)."""
+    return int(lib.jf_numa_node_count())
+
+
+def numa_node_of_device(device: int = 0) -> int:
+    """Memory node the GPU is attached to, -1 when unknown."""
+    return int(lib.jf_numa_node_of_device(int(device)))
+
+
+def numa_node_cpus(node: int) -> list[int]:
+    """Processors of a memory node, ascending; RuntimeError for a node the system does not list."""
+    count = C.c_int32(0)
+    check("numa_node_cpus", lib.jf_numa_node_cpus(int(node), None, 0, C.byref(count)))
+    buf = (C.c_int32 * max(count.value, 1))()
+    check("numa_node_cpus", lib.jf_numa_node_cpus(int(node), buf, count.value, C.byref(count)))
+    return [int(buf[i]) for i in range(count.value)]
+
+
+def bind_memory_to_node(host: torch.Tensor, node: int) -> bool:
+    """Bind a CPU tensor's pages to a memory node (right after ``torch.empty``, before the first
+    write and before any pinning).  Returns False if the system refuses."""
+    _require(not host.is_cuda, "bind_memory_to_node: a CPU tensor is expected")
+    return lib.jf_bind_memory_to_node(host.data_ptr(), host.numel() * host.element_size(), int(node)) == _lib.JF_OK
+
+
+def set_cpu_attn_node(node: int) -> None:
+    """Confine the correction workers to one memory node's processors (-1: anywhere); takes effect
+    with the next job."""
+    check("set_cpu_attn_node", lib.jf_set_cpu_attn_node(int(node)))
+
+
+def get_cpu_attn_node() -> int:
+    return int(lib.jf_get_cpu_attn_node())
+
+
+def alloc_mapped_pinned_pair(shape, dtype, node: int = -1):
+    """``(host_tensor, device_tensor)`` over the same pinned, GPU-mapped bytes; ``node >= 0`` asks
+    for the bytes on that memory node."""
     n = 1
     for s in shape:
         n *= int(s)
     itemsize = torch.empty(0, dtype=dtype).element_size()
     nbytes = max(n * itemsize, 1)
     h, d = C.c_void_p(), C.c_void_p()
-    check("alloc_mapped_pinned_pair", lib.jf_alloc_mapped(nbytes, C.byref(h), C.byref(d)))
+    check("alloc_mapped_pinned_pair", lib.jf_alloc_mapped_on_node(nbytes, int(node), C.byref(h), C.byref(d)))
     buf = (C.c_uint8 * nbytes).from_address(h.value)
     host = torch.frombuffer(buf, dtype=dtype, count=n).reshape(*shape)
     dev_ptr = d.value
