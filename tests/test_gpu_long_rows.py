@@ -143,6 +143,40 @@ def test_random_geometries(mode, B, H_q, H_kv, ctx, lens, top_k, stage_b, dtype,
     _run(Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed, dtype=dtype), top_k, stage_b=stage_b)
 
 
+def _random_wide_cases(n, seed=515):
+    """Seeded geometries with top-k 1024 / 2048 / 4096: rows around and below twice the top-k
+    (every position a candidate), rows of a multiple of 16 positions that may or may not be long
+    enough for the page maxima, ragged lengths, both modes and dtypes."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(n):
+        mode = "k3v2" if i % 2 == 0 else "k4v4"
+        top_k = int(rng.choice([1024, 2048, 4096]))
+        H_kv = int(rng.choice([1, 2]))
+        G = int(rng.choice([1, 4, 8, 16]))
+        B = int(rng.integers(1, 3))
+        if i % 3 == 0:
+            ctx = 16 * int(rng.integers(top_k // 16 + 1, 4500))
+        elif i % 3 == 1:
+            ctx = int(rng.integers(100, 3 * top_k))
+            if top_k > 2048:            # above 2048 the row stride has to be a multiple of 16
+                ctx = (ctx + 15) // 16 * 16
+        else:
+            ctx = 16 * int(rng.integers(2000, 4400))
+        lens = [int(rng.integers(1, ctx + 1)) for _ in range(B)]
+        lens[int(rng.integers(0, B))] = ctx
+        stage_b = "int8p" if (mode == "k4v4" and B > 1 and i % 4 == 1) else "fp32"
+        dtype = torch.float16 if i % 5 == 0 else torch.bfloat16
+        out.append(pytest.param(mode, B, H_kv * G, H_kv, ctx, lens, top_k, stage_b, dtype, 4000 + i,
+                                id=f"{i}-{mode}-B{B}-H{H_kv * G}x{H_kv}-ctx{ctx}-k{top_k}-{stage_b}"))
+    return out
+
+
+@pytest.mark.parametrize("mode,B,H_q,H_kv,ctx,lens,top_k,stage_b,dtype,seed", _random_wide_cases(18))
+def test_random_geometries_with_wide_top_k(mode, B, H_q, H_kv, ctx, lens, top_k, stage_b, dtype, seed):
+    _run(Case(mode, B, H_q, H_kv, ctx, lens=lens, seed=seed, dtype=dtype), top_k, stage_b=stage_b)
+
+
 @pytest.mark.parametrize("mode,top_k,ctx", [("k4v4", 1024, 8192), ("k3v2", 2048, 8192), ("k3v2", 1024, 2000)])
 def test_wide_top_k(mode, top_k, ctx):
     """top-k above 512: the sort buffer no longer fits the counting / bucket ranking (bitonic
