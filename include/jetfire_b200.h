@@ -250,6 +250,11 @@ jf_status_t jf_softmax_stats(const float* scores, const int32_t* seq_lens, float
  * reads (and clears) the record of the calls made through jf_decode_fused_static on the
  * current device instead. */
 jf_status_t jf_decode_status(const jf_decode_args* args, jf_stream_t stream);
+/* The same reading on a HOST copy of the first JF_STATUS_RECORD_BYTES of the workspace (the
+ * record sits at its start), for callers that must not synchronise: they copy the record in
+ * the stream after the step and look at the copy once that copy has completed.  Clears nothing. */
+#define JF_STATUS_RECORD_BYTES 16
+jf_status_t jf_decode_status_of_copy(const void* record_copy);
 
 /* ---------------------------------------------------------------------------------
  * jf_decode_fused without a workspace argument.  No counterpart in the reference (its
@@ -358,6 +363,26 @@ jf_status_t jf_submit_ctx_destroy(int64_t handle);
 jf_status_t jf_submit_ctx_status(int64_t handle);
 jf_status_t jf_stream_submit_cpu_topk_attn(jf_stream_t stream, int64_t handle);
 jf_status_t jf_stream_wait_cpu_topk_attn(jf_stream_t stream, int64_t handle);
+
+/* Host correction started and joined by the GPU through two words in mapped pinned host memory,
+ * with no host function in the stream (each costs two thread hand-overs; a layer's pair costs
+ * more than the GPU half of the step).  The reference's counterparts are the device-signal and
+ * GPU-wait variants of its graph-mode decode (jetfire_vllm/adapter/decode_path.py:2426-2438,
+ * :3061-3064: stream_write_value64 / stream_wait_value64 on a mapped flag); here the wait is a
+ * polling kernel with a time budget rather than a stream memory operation that never gives up.
+ *   jf_submit_ctx_watch       a dispatcher thread polls *trigger_host; non-zero = clear it and queue
+ *                             the context's job (whose completion flag is the context's done_flag)
+ *   jf_stream_signal_host     kernel: *done_dev = 0, then *trigger_dev = 1 (after the stream's
+ *                             earlier copies of the job's inputs have landed on the host)
+ *   jf_stream_wait_host_flag  kernel: one thread polls *flag_dev until non-zero, at most timeout_ms;
+ *                             a wait that runs out writes JF_ERR_TIMEOUT to the status record given
+ *                             (start of the decode workspace, or NULL) and the stream continues
+ * All three are capturable: a replayed graph raises the same trigger word again. */
+jf_status_t jf_submit_ctx_watch(int64_t handle, int64_t* trigger_host);
+jf_status_t jf_submit_ctx_unwatch(int64_t handle);
+jf_status_t jf_stream_signal_host(jf_stream_t stream, int64_t* done_dev, int64_t* trigger_dev);
+jf_status_t jf_stream_wait_host_flag(jf_stream_t stream, const int64_t* flag_dev, int32_t timeout_ms,
+                                     void* status_record);
 
 /* Pinned host memory mapped into the device address space
  * (alloc_mapped_pinned_pair, jetfire_vllm/csrc/cpu_topk_attn.cpp:958-1040). */

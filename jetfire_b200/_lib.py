@@ -85,6 +85,7 @@ _SIGS = {
     "jf_decode_fused": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_select_finish": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_decode_status": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "jf_decode_status_of_copy": (C.c_int32, [C.c_void_p]),
     "jf_softmax_stats": (C.c_int32, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p]),
     "jf_decode_fused_static": (C.c_int32, [C.POINTER(DecodeArgs), C.c_void_p]),
     "jf_merge_correct": (C.c_int32, [C.c_void_p] * 5 + [C.c_int32] * 3 + [C.c_void_p]),
@@ -123,6 +124,10 @@ _SIGS = {
     "jf_stream_submit_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),
     "jf_stream_wait_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),
     "jf_pool_shutdown": (C.c_int32, []),
+    "jf_submit_ctx_watch": (C.c_int32, [C.c_int64, C.c_void_p]),
+    "jf_submit_ctx_unwatch": (C.c_int32, [C.c_int64]),
+    "jf_stream_signal_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "jf_stream_wait_host_flag": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "jf_alloc_mapped": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "jf_free_mapped": (C.c_int32, [C.c_void_p]),
 }

@@ -2,7 +2,9 @@
 
 Only the two paper modes are registered; one code path, no experiment knobs.  Environment
 variables kept from the reference: ``JETFIRE_MODE``, ``JETFIRE_TOPK``, ``JETFIRE_GROUP_SIZE``,
-``JETFIRE_CPU_ATTN_THREADS``, ``JETFIRE_MAX_BATCH_SIZE``.  Own: ``JETFIRE_SLOTS_I32`` and
+``JETFIRE_CPU_ATTN_THREADS``, ``JETFIRE_MAX_BATCH_SIZE``.  Own: ``JETFIRE_SLOTS_I32``,
+``JETFIRE_STREAM_ORDERED`` (decode steps queued on the stream without a host wait),
+``JETFIRE_STREAM_SIGNAL`` (``flags`` | ``callbacks``: how such a step meets the host) and
 ``JETFIRE_NUMA_NODE`` (``auto`` | ``off`` | a node number: where the host mirrors and the
 correction workers of this rank are placed).
 """
@@ -47,6 +49,8 @@ class JetFireConfig:
     enabled: bool = True
     slots_i32: bool = True                # selected slots cross to the host as int32 (the reference: int64)
     numa_node: int = NUMA_AUTO            # memory node of mirrors and workers: NUMA_AUTO, NUMA_OFF or a node
+    stream_ordered: bool = False          # decode step queued on the stream without a host wait (capturable)
+    stream_signal: str = "flags"          # how a stream-ordered step meets the host: "flags" or "callbacks"
 
     @property
     def scheme(self) -> QuantScheme:
@@ -108,9 +112,13 @@ def get_jetfire_config() -> JetFireConfig:
     threads = _int_env("JETFIRE_CPU_ATTN_THREADS", 32)
     if threads <= 0:
         raise ValueError("JETFIRE_CPU_ATTN_THREADS must be positive")
+    signal = (os.environ.get("JETFIRE_STREAM_SIGNAL") or "flags").strip().lower()
+    if signal not in ("flags", "callbacks"):
+        raise ValueError(f"JETFIRE_STREAM_SIGNAL must be 'flags' or 'callbacks', got {signal!r}")
     _CONFIG = JetFireConfig(mode=mode, top_k=top_k, group_size=group, cpu_attn_threads=threads,
                             max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32),
-                            slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0, numa_node=_numa_env())
+                            slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0, numa_node=_numa_env(),
+                            stream_ordered=_int_env("JETFIRE_STREAM_ORDERED", 0) != 0, stream_signal=signal)
     return _CONFIG
 
 

@@ -7,6 +7,18 @@ and the op order of ``_decode_batched`` :1712-3237):
 
 The reference's Stage A / Stage B pair is one fused call here, so nothing is left to overlap
 the host correction with inside a layer; across layers the caller may pipeline.
+
+Two forms of the step.  The default one waits on the host for the selected slots, runs the
+correction and returns with the merge queued.  The stream-ordered one
+(``JetFireConfig.stream_ordered``, the reference's graph-mode decode: create_cpu_topk_submit_ctx /
+stream_submit_cpu_topk_attn / stream_wait_cpu_topk_attn, csrc/cpu_topk_attn.cpp:2147-2312, call
+sites decode_path.py:2253-2492) queues everything on the CUDA stream over buffers that keep their
+addresses -- copies, kernels, the correction's submit and join as host functions in the stream --
+and never waits on the host, so a whole step can be captured in a CUDA graph and replayed.
+``JetFireConfig.stream_signal`` chooses how the stream and the host meet: ``"flags"`` -- a kernel
+raises a word in mapped memory that a dispatcher thread polls, and a kernel polls the word the
+last worker sets (decode_path.py:2426-2438, :3061-3064 of the reference, with a bounded wait) --
+or ``"callbacks"`` -- host functions in the stream.
 """
 from __future__ import annotations
 
@@ -93,6 +105,131 @@ def _set_worker_count(cfg: JetFireConfig, node: int = -1) -> None:
         _WORKERS_SET = (want, node)
 
 
+class _StreamStep:
+    """Buffers and calls of one layer's stream-ordered decode step for one (batch, top-k) shape.
+    Everything the kernels and the host correction read or write sits at fixed addresses, so the
+    step can be captured once and replayed; the per-step inputs are copied in on the stream."""
+
+    def __init__(self, store: JetFireCacheStore, cfg: JetFireConfig, B: int, H_q: int, top_k: int,
+                 max_blocks: int, max_S: int, dtype, device, scale: float):
+        self.B, self.H_q, self.top_k, self.max_blocks, self.max_S = B, H_q, top_k, max_blocks, max_S
+        self.q = torch.zeros(B, H_q, 128, dtype=dtype, device=device)
+        self.block_table = torch.zeros(B, max_blocks, dtype=torch.int64, device=device)
+        self.seq_lens = torch.zeros(B, dtype=torch.int32, device=device)
+        self.call = ops.DecodeCall(cfg.kernel_mode, self.q, store.k_data, store.k_scales, store.v_data,
+                                   store.v_scales, self.block_table, self.seq_lens, max_S, H_q, store.num_kv_heads,
+                                   store.block_size, top_k, scale, slots_i32=cfg.slots_i32)
+        slot_dtype = torch.int32 if cfg.slots_i32 else torch.int64
+        self.slots_dev = self.call.out["topk_slots_i32"] if cfg.slots_i32 else self.call.out["topk_slots"]
+        self.q_host = torch.zeros(B, H_q, 128, dtype=dtype).pin_memory()
+        self.slots_host = torch.zeros(B, H_q, top_k, dtype=slot_dtype).pin_memory()
+        self.out = torch.zeros(B, H_q, 128, dtype=dtype, device=device)
+        self.flags = cfg.stream_signal == "flags"
+        if self.flags:
+            # the correction is started and joined through two words in mapped memory (a line apart),
+            # and its result is read by the merge kernel where the workers wrote it
+            self.words_host, self.words_dev = ops.alloc_mapped_pinned_pair((16,), torch.int64)
+            self.words_host.zero_()
+            self.o_new_host, self.o_new = ops.alloc_mapped_pinned_pair((B, H_q, 128), dtype)
+            self.o_new_host.zero_()
+            self.host = ops.HostCorrectionCall(self.q_host, store.k_shadow, store.v_shadow, None, self.slots_host,
+                                               self.o_new_host, scale, done_flag=self.words_host[8:9])
+            self.host.watch(self.words_host[0:1])
+        else:
+            self.o_new_host = torch.zeros(B, H_q, 128, dtype=dtype).pin_memory()
+            self.o_new = torch.zeros(B, H_q, 128, dtype=dtype, device=device)
+            self.host = ops.HostCorrectionCall(self.q_host, store.k_shadow, store.v_shadow, None, self.slots_host,
+                                               self.o_new_host, scale)
+        self.status_host = torch.zeros(ops.STATUS_RECORD_BYTES, dtype=torch.uint8).pin_memory()
+        self.status_event: torch.cuda.Event | None = None
+        self.captured = False
+
+    def check_previous(self) -> None:
+        """Raise if the previous eager run of this step recorded an error.  Looks only at what has
+        already arrived on the host: the record's copy once its event has completed, and the
+        correction context's own status.  Never waits."""
+        ev = self.status_event
+        if ev is not None and ev.query():
+            self.status_event = None
+            ops.decode_status_of_copy(self.status_host)
+            self.host.stream_status()
+
+    def run(self, query: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor, out_view: torch.Tensor) -> None:
+        capturing = torch.cuda.is_current_stream_capturing()
+        if not capturing:
+            self.check_previous()
+        self.q.copy_(query, non_blocking=True)
+        width = min(int(block_table.shape[1]), self.max_blocks)
+        self.block_table[:, :width].copy_(block_table[:, :width], non_blocking=True)    # converts the dtype as well
+        self.seq_lens.copy_(seq_lens, non_blocking=True)
+        self.call.fused()
+        self.q_host.copy_(self.q, non_blocking=True)
+        self.slots_host.copy_(self.slots_dev, non_blocking=True)
+        if self.flags:
+            ops.stream_signal_host(self.words_dev[8:9], self.words_dev[0:1])
+            ops.stream_wait_host_flag(self.words_dev[8:9], _HOST_WAIT_MS, self.call.status_record())
+        else:
+            self.host.stream_submit()
+            self.host.stream_wait()
+            self.o_new.copy_(self.o_new_host, non_blocking=True)
+        res = self.call.out
+        if out_view.is_contiguous():
+            ops.blend_unnorm_into(res["o_hat"], res["o_old_unnorm"], res["W"], self.o_new, out_view)
+        else:
+            ops.blend_unnorm_into(res["o_hat"], res["o_old_unnorm"], res["W"], self.o_new, self.out)
+            out_view.copy_(self.out)
+        self.status_host.copy_(self.call.status_record(), non_blocking=True)
+        if capturing:
+            self.captured = True        # a graph refers to these buffers from now on
+        else:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.status_event = ev
+
+    def status(self) -> None:
+        """For the owner of a graph, after synchronising a replay: raise if the step recorded an error."""
+        ops.decode_status_of_copy(self.status_host)
+        self.host.stream_status()
+
+
+_MAX_S_STEP = 4096      # a step object serves row lengths up to the next multiple of this
+_HOST_WAIT_MS = 5000    # budget of the kernel that waits for the host correction
+
+
+def stream_steps(store: JetFireCacheStore) -> list[_StreamStep]:
+    """Every stream-ordered step of a store (for ``status()`` once a graph replay has been
+    synchronised).  The steps live on the store: they hold its tensors' addresses."""
+    return list(getattr(store, "_stream_steps", {}).values()) + list(getattr(store, "_captured_steps", []))
+
+
+def decode_batched_stream_ordered(*, store: JetFireCacheStore, query: torch.Tensor, block_table: torch.Tensor,
+                                  seq_lens: torch.Tensor, max_seq_len: int, num_heads: int, scale: float,
+                                  output: torch.Tensor, cfg: JetFireConfig | None = None) -> torch.Tensor | None:
+    """``decode_batched`` without a host wait: everything is queued on the current stream (which
+    must be the stream the appends were queued on: the correction reads the mirror when the stream
+    reaches its submit).  Capturable.  ``max_seq_len`` is a host integer (under capture: the bound
+    the graph is to serve); the mirror must be the mapped one."""
+    cfg = cfg or get_jetfire_config()
+    B = int(seq_lens.numel())
+    top_k = _select_top_k(cfg.top_k, int(max_seq_len), SUPPORTED_TOP_K)
+    if top_k is None or not store.shadow_enabled or store.mirror_append != "mapped":
+        return None
+    width = int(block_table.shape[1])
+    need_S = min(width * store.block_size, ((int(max_seq_len) + 15) // 16) * 16)
+    steps = store.__dict__.setdefault("_stream_steps", {})
+    key = (B, num_heads, top_k, query.dtype, cfg.slots_i32, float(scale))
+    step = steps.get(key)
+    if step is None or step.max_S < need_S or step.max_blocks < min(width, (need_S + 15) // 16):
+        max_S = min(width * store.block_size, -(-need_S // _MAX_S_STEP) * _MAX_S_STEP)
+        if step is not None and step.captured:      # a graph still refers to its buffers
+            store.__dict__.setdefault("_captured_steps", []).append(step)
+        _set_worker_count(cfg, getattr(store, "numa_node", -1))
+        step = steps[key] = _StreamStep(store, cfg, B, num_heads, top_k, max_S // store.block_size, max_S,
+                                        query.dtype, query.device, float(scale))
+    step.run(query[:B], block_table, seq_lens, output[:B].view(B, num_heads, 128))
+    return output
+
+
 def decode_batched(*, store: JetFireCacheStore, query: torch.Tensor, block_table: torch.Tensor,
                    seq_lens: torch.Tensor, max_seq_len: int, num_heads: int, scale: float,
                    output: torch.Tensor, cfg: JetFireConfig | None = None) -> torch.Tensor | None:
@@ -147,7 +284,8 @@ def try_jetfire_decode(*, impl, layer, query, attn_metadata, output, store=None,
         return None
     n = int(attn_metadata.seq_lens.numel())
     q = query[:n].view(n, int(layer.num_heads), int(layer.head_size))
-    return decode_batched(store=store, query=q, block_table=attn_metadata.block_table,
+    step = decode_batched_stream_ordered if cfg.stream_ordered else decode_batched
+    return step(store=store, query=q, block_table=attn_metadata.block_table,
                           seq_lens=attn_metadata.seq_lens, max_seq_len=int(attn_metadata.max_seq_len),
                           num_heads=int(layer.num_heads), scale=float(impl.scale), output=output, cfg=cfg)
 

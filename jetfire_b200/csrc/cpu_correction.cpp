@@ -330,6 +330,7 @@ void run_row(const Job& j, int64_t i, Scratch& sc) {
 class Pool {
  public:
   static constexpr int kQueue = 4;
+  static constexpr int kSpinBeforeParkUs = 400;
 
   ~Pool() { shutdown(); }
   int size() const { return n_; }
@@ -345,11 +346,16 @@ class Pool {
     submitted_.store(0);
     completed_.store(0);
     for (auto& sl : slots_) { sl.left.store(n); sl.done_id.store(0); }   // "everyone has left": free
+    started_.store(0);
     for (int i = 0; i < n; ++i)
       workers_.emplace_back([this] {
         if (node_ >= 0) jf::pin_this_thread_to_node(node_);   // a refusal leaves the worker unconfined
+        started_.fetch_add(1, std::memory_order_release);
         loop();
       });
+    // every worker is in place (and confined) before the first job is taken
+    const auto t_end = std::chrono::steady_clock::now() + std::chrono::seconds(1);
+    while (started_.load(std::memory_order_acquire) < n && std::chrono::steady_clock::now() < t_end) std::this_thread::yield();
   }
   void shutdown() {
     std::lock_guard<std::mutex> g(api_);
@@ -427,11 +433,15 @@ class Pool {
     Scratch sc;
     uint64_t my = 0;   // the next job this worker takes part in
     for (;;) {
-      // short spin for back-to-back jobs, then park
+      // Spin for the next job, then park.  In a decode loop the jobs of consecutive layers are a
+      // GPU step apart (a few hundred microseconds at most); parked workers take tens of
+      // microseconds to get going again, so the spin outlasts such a gap.
       bool got = false;
-      for (int spin = 0; spin < 4000; ++spin) {
+      const auto spin_end = std::chrono::steady_clock::now() + std::chrono::microseconds(kSpinBeforeParkUs);
+      for (int spin = 0;; ++spin) {
         if (submitted_.load(std::memory_order_acquire) > my) { got = true; break; }
         _mm_pause();
+        if ((spin & 63) == 63 && std::chrono::steady_clock::now() > spin_end) break;
       }
       if (!got) {
         std::unique_lock<std::mutex> l(m_);
@@ -471,6 +481,7 @@ class Pool {
   std::vector<std::thread> workers_;
   Slot slots_[kQueue];
   std::atomic<uint64_t> submitted_{0}, completed_{0};
+  std::atomic<int> started_{0};
   bool stop_ = false;
   int n_ = 0;
   int node_ = -1;   // processors the workers were confined to when they started
@@ -654,6 +665,7 @@ struct SubmitCtx {
   Job job;
   std::atomic<int32_t> error{JF_OK};
   int32_t wait_ms = 30000;
+  int64_t* trigger = nullptr;         // watched by the dispatcher thread when set (jf_submit_ctx_watch)
   alignas(64) int64_t own_flag = 0;   // completion flag when the caller gave none
 };
 
@@ -668,6 +680,81 @@ void CUDART_CB submit_callback(void* ud) {
     if (pool().submit(c->job)) return;
     if (!pool().wait(c->wait_ms) || std::chrono::steady_clock::now() > t_end) { c->error.store(JF_ERR_TIMEOUT); return; }
   }
+}
+
+// Contexts whose job is started by the GPU: a kernel in the stream stores a non-zero value to the
+// context's trigger word (mapped pinned host memory) once the job's inputs have been copied to the
+// host; one dispatcher thread polls the trigger words of all watched contexts, clears the word it
+// finds set and queues that context's job.  The completion flag goes the other way: the last
+// worker sets it, a kernel in the stream polls it (jf_stream_wait_host_flag).  No host function
+// in the stream, whose two thread hand-overs per layer cost more than the GPU half of the step.
+class Dispatcher {
+ public:
+  ~Dispatcher() { stop(); }
+  void watch(SubmitCtx* c, int64_t* trigger) {
+    std::lock_guard<std::mutex> g(mu_);
+    c->trigger = trigger;
+    reinterpret_cast<std::atomic<int64_t>*>(trigger)->store(0, std::memory_order_release);
+    bool present = false;
+    for (auto* x : watched_) present |= (x == c);
+    if (!present) watched_.push_back(c);
+    if (!running_) {
+      running_ = true;
+      quit_.store(false);
+      thread_ = std::thread([this] { loop(); });
+    }
+  }
+  void unwatch(SubmitCtx* c) {
+    std::lock_guard<std::mutex> g(mu_);
+    for (size_t i = 0; i < watched_.size(); ++i)
+      if (watched_[i] == c) { watched_.erase(watched_.begin() + static_cast<long>(i)); break; }
+    c->trigger = nullptr;
+  }
+  void stop() {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      if (!running_) return;
+      running_ = false;
+      quit_.store(true);
+    }
+    thread_.join();
+  }
+
+ private:
+  void loop() {
+    auto last_hit = std::chrono::steady_clock::now();
+    for (uint64_t sweep = 0; !quit_.load(std::memory_order_acquire); ++sweep) {
+      bool hit = false;
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        for (SubmitCtx* c : watched_) {
+          auto* t = reinterpret_cast<std::atomic<int64_t>*>(c->trigger);
+          if (t->load(std::memory_order_acquire) == 0) continue;
+          t->store(0, std::memory_order_release);
+          submit_callback(c);
+          hit = true;
+        }
+      }
+      // busy while steps arrive; after 2 ms without one the sweeps thin out so that an idle process
+      // does not hold a core (the first step after a pause then waits up to one nap longer)
+      if (hit) { last_hit = std::chrono::steady_clock::now(); continue; }
+      _mm_pause();
+      if ((sweep & 63) != 63) continue;
+      const auto idle = std::chrono::steady_clock::now() - last_hit;
+      if (idle > std::chrono::seconds(1)) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+      else if (idle > std::chrono::milliseconds(2)) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+  }
+  std::mutex mu_;
+  std::vector<SubmitCtx*> watched_;
+  std::thread thread_;
+  std::atomic<bool> quit_{false};
+  bool running_ = false;
+};
+
+Dispatcher& dispatcher() {
+  static Dispatcher d;
+  return d;
 }
 
 // Waits for THIS context's job (its completion flag), not for an idle pool: the next layer's
@@ -721,7 +808,25 @@ extern "C" jf_status_t jf_submit_ctx_create_i32(const void* q, const void* k_sha
 
 extern "C" jf_status_t jf_submit_ctx_destroy(int64_t handle) {
   if (!handle) return JF_ERR_ARG;
-  delete reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle));
+  auto* c = reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle));
+  if (c->trigger) dispatcher().unwatch(c);
+  delete c;
+  return JF_OK;
+}
+
+// From now on a non-zero value stored to *trigger_host (by a kernel in a stream: see
+// jf_stream_signal_host) starts the context's job; the dispatcher clears the word when it takes
+// it.  The word must stay valid until jf_submit_ctx_unwatch / _destroy.
+extern "C" jf_status_t jf_submit_ctx_watch(int64_t handle, int64_t* trigger_host) {
+  if (!handle || !trigger_host || (reinterpret_cast<uintptr_t>(trigger_host) & 7)) return JF_ERR_ARG;
+  ensure_pool();
+  dispatcher().watch(reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle)), trigger_host);
+  return JF_OK;
+}
+
+extern "C" jf_status_t jf_submit_ctx_unwatch(int64_t handle) {
+  if (!handle) return JF_ERR_ARG;
+  dispatcher().unwatch(reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle)));
   return JF_OK;
 }
 

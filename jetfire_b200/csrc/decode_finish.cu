@@ -4,6 +4,8 @@
 // merge_correct: out = dtype(o_hat + W * float(o_new) - o_old_unnorm)
 // (jetfire_vllm/csrc/blend.cu:202-226).  The normaliser stays the approximate softmax's:
 // this is mass substitution, not a re-normalised merge.
+#include <cstring>
+
 #include "finish_tail.cuh"
 
 namespace jf {
@@ -161,6 +163,16 @@ extern "C" jf_status_t jf_decode_status(const jf_decode_args* a, jf_stream_t str
   if (host.tag != kStatusTag || host.code == 0) return JF_OK;
   JF_CUDA_TRY(cudaMemsetAsync(record, 0, sizeof(host), stream));
   JF_CUDA_TRY(cudaStreamSynchronize(stream));
+  return static_cast<jf_status_t>(host.code);
+}
+
+// The same reading on a host copy of the record's first 16 bytes, for callers that bring the
+// record over with a copy of their own in the stream (no synchronisation here, nothing cleared).
+extern "C" jf_status_t jf_decode_status_of_copy(const void* record_copy) {
+  if (!record_copy) return JF_ERR_ARG;
+  struct { unsigned long long tag; int32_t code; int32_t pad; } host{};
+  memcpy(&host, record_copy, sizeof(host));
+  if (host.tag != jf::kStatusTag || host.code == 0) return JF_OK;
   return static_cast<jf_status_t>(host.code);
 }
 

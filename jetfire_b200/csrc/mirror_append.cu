@@ -16,6 +16,7 @@
 #include <new>
 
 #include "jf_common.cuh"
+#include "decode_common.cuh"
 
 namespace jf {
 namespace {
@@ -192,6 +193,71 @@ extern "C" jf_status_t jf_stream_write_value64(jf_stream_t stream, void* device_
   const int r = fn(stream, static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(device_ptr)),
                    static_cast<unsigned long long>(value), 0u);
   if (r != 0) { g_last_cuda_error = r; return JF_ERR_CUDA; }
+  return JF_OK;
+}
+
+namespace jf {
+namespace {
+
+// Clears the completion word, then raises the trigger word: both live in mapped pinned host memory.
+// Everything queued on the stream before this kernel (the copies of the job's inputs to the host)
+// has completed when it runs; the fence orders the two stores as the host sees them.
+__global__ void signal_host_kernel(volatile long long* done, volatile long long* trigger) {
+  if (threadIdx.x == 0) {
+    *done = 0;
+    __threadfence_system();
+    *trigger = 1;
+    __threadfence_system();
+  }
+}
+
+// Polls a word in mapped pinned host memory until it is non-zero or the budget is used up; a wait
+// that ran out is recorded in the status record (and the stream carries on).
+__global__ void wait_host_flag_kernel(const volatile long long* flag, unsigned long long budget_ns, int32_t* status) {
+  if (threadIdx.x != 0) return;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (unsigned long long polls = 0; polls < (1ull << 32); ++polls) {
+    if (*flag != 0) {
+      __threadfence_system();   // what the host wrote before the flag is read after it
+      return;
+    }
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - t0 > budget_ns) break;
+    __nanosleep(polls < 64 ? 100 : 500);
+  }
+  if (status) report_status(status, JF_ERR_TIMEOUT);
+}
+
+}  // namespace
+}  // namespace jf
+
+// Queues a kernel that clears *done_dev and then sets *trigger_dev to 1 (device-visible addresses
+// of two words in mapped pinned host memory): the GPU's half of starting a host correction without
+// a host function in the stream.  The host's half is jf_submit_ctx_watch.
+extern "C" jf_status_t jf_stream_signal_host(jf_stream_t stream, int64_t* done_dev, int64_t* trigger_dev) {
+  using namespace jf;
+  if (!done_dev || !trigger_dev || ((reinterpret_cast<uintptr_t>(done_dev) | reinterpret_cast<uintptr_t>(trigger_dev)) & 7))
+    return JF_ERR_ARG;
+  signal_host_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<volatile long long*>(done_dev),
+                                                                      reinterpret_cast<volatile long long*>(trigger_dev));
+  JF_CUDA_TRY(cudaGetLastError());
+  return JF_OK;
+}
+
+// Queues a kernel that holds the stream until *flag_dev (mapped pinned host memory) is non-zero,
+// for at most timeout_ms (1..60000); a wait that runs out writes JF_ERR_TIMEOUT to the workspace's
+// status record (`status_record`: the start of the decode workspace; may be NULL) and lets the
+// stream continue.  One thread polls; nothing else of the GPU is held.
+extern "C" jf_status_t jf_stream_wait_host_flag(jf_stream_t stream, const int64_t* flag_dev, int32_t timeout_ms,
+                                                void* status_record) {
+  using namespace jf;
+  if (!flag_dev || (reinterpret_cast<uintptr_t>(flag_dev) & 7) || timeout_ms <= 0 || timeout_ms > 60000) return JF_ERR_ARG;
+  wait_host_flag_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const volatile long long*>(flag_dev), static_cast<unsigned long long>(timeout_ms) * 1000000ull,
+      static_cast<int32_t*>(status_record));
+  JF_CUDA_TRY(cudaGetLastError());
   return JF_OK;
 }
 

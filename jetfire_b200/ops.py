@@ -395,10 +395,30 @@ class DecodeCall:
         """Synchronises the stream and raises if a kernel recorded a bounded-wait timeout."""
         check("jf_decode_status", lib.jf_decode_status(self._ref, _stream()))
 
+    def status_record(self) -> torch.Tensor:
+        """The status record's bytes in the workspace (a CUDA uint8 view): copy them to pinned host
+        memory in the stream and read the copy with ``decode_status_of_copy`` -- the check without
+        a synchronisation."""
+        ws = self._keep[-1]
+        off = self.args.workspace - ws.data_ptr()
+        return ws.view(torch.uint8).reshape(-1)[off:off + STATUS_RECORD_BYTES]
+
     def result(self) -> FusedAttnOut:
         o = self.out
         return FusedAttnOut(o["o_hat"], o["topk_slots"], o["o_old_unnorm"], o["W"], o["topk_idx"],
                             o["softmax_m"], o["softmax_inv_z"], self.scores)
+
+
+STATUS_RECORD_BYTES = 16
+
+
+def decode_status_of_copy(record_copy: torch.Tensor) -> None:
+    """Raises if the host copy of a workspace's status record (``DecodeCall.status_record()``)
+    holds an error."""
+    _require(not record_copy.is_cuda and record_copy.is_contiguous()
+             and record_copy.numel() * record_copy.element_size() >= STATUS_RECORD_BYTES,
+             "decode_status_of_copy: a contiguous CPU tensor of at least 16 bytes is expected")
+    check("jf_decode_status", lib.jf_decode_status_of_copy(record_copy.data_ptr()))
 
 
 def fused_attn_topk(mode, q, k_data, k_scales, v_data, v_scales, block_table, seq_lens,
@@ -674,6 +694,15 @@ class HostCorrectionCall:
         s = stream.cuda_stream if stream is not None else _stream()
         check("stream_wait_cpu_topk_attn", lib.jf_stream_wait_cpu_topk_attn(s, self._handle()))
 
+    def watch(self, trigger_host: torch.Tensor) -> None:
+        """Let the GPU start this job: from now on a non-zero value stored to ``trigger_host`` (one
+        int64 in mapped pinned host memory, see ``stream_signal_host``) queues it; the job's
+        ``done_flag`` is set when it is complete."""
+        _require(not trigger_host.is_cuda and trigger_host.dtype == torch.int64 and trigger_host.numel() == 1,
+                 "watch: trigger_host must be a 1-element int64 CPU tensor")
+        check("submit_ctx_watch", lib.jf_submit_ctx_watch(self._handle(), trigger_host.data_ptr()))
+        self._keep = self._keep + (trigger_host,)
+
     def stream_status(self) -> None:
         """Raises if a queued submit or wait ran out of time (call after synchronising)."""
         if getattr(self, "_ctx", None) is not None:
@@ -721,6 +750,25 @@ def stream_write_value64(stream_id: int, flag_device: torch.Tensor, value: int) 
     _require(flag_device.is_cuda and flag_device.dtype == torch.int64 and flag_device.numel() == 1,
              "stream_write_value64: flag_device must be a 1-element int64 CUDA tensor")
     check("stream_write_value64", lib.jf_stream_write_value64(int(stream_id), flag_device.data_ptr(), int(value)))
+
+
+def stream_signal_host(done_dev: torch.Tensor, trigger_dev: torch.Tensor) -> None:
+    """Queue a kernel that clears ``done_dev`` and then sets ``trigger_dev`` to 1 (device halves of
+    two int64 words from ``alloc_mapped_pinned_pair``): starts the host correction whose context
+    watches the trigger word, once the stream's earlier copies have landed.  Capturable."""
+    for t in (done_dev, trigger_dev):
+        _require(t.is_cuda and t.dtype == torch.int64 and t.numel() == 1, "stream_signal_host: 1-element int64 CUDA views")
+    check("stream_signal_host", lib.jf_stream_signal_host(_stream(), done_dev.data_ptr(), trigger_dev.data_ptr()))
+
+
+def stream_wait_host_flag(flag_dev: torch.Tensor, timeout_ms: int = 2000, status_record: torch.Tensor | None = None) -> None:
+    """Queue a kernel that holds the stream until ``flag_dev`` (device half of a mapped int64 word)
+    is non-zero, for at most ``timeout_ms``; a wait that runs out is written to ``status_record``
+    (``DecodeCall.status_record()``) and the stream continues.  Capturable."""
+    _require(flag_dev.is_cuda and flag_dev.dtype == torch.int64 and flag_dev.numel() == 1,
+             "stream_wait_host_flag: flag_dev must be a 1-element int64 CUDA view")
+    rec = status_record.data_ptr() if status_record is not None else None
+    check("stream_wait_host_flag", lib.jf_stream_wait_host_flag(_stream(), flag_dev.data_ptr(), int(timeout_ms), rec))
 
 
 def submit_cpu_topk_attn_async(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, flag) -> None:

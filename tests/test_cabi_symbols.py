@@ -51,3 +51,18 @@ def test_struct_layout_matches_header(lib):
     assert lib.DecodeArgs.q.offset == 56
     assert lib.DecodeArgs.workspace_bytes.offset == 56 + 16 * 8
     assert lib.DecodeArgs.topk_slots_i32.offset == 56 + 16 * 8 + 8
+
+
+def test_status_of_a_host_copy_of_the_record(lib):
+    """The non-synchronising status check reads a 16-byte host copy of the workspace's record:
+    only a tagged record with a non-zero code counts."""
+    import struct
+    l = lib.lib
+    tag = struct.unpack("<Q", b"SUTATSFJ")[0]           # "JFSTATUS" as the kernels write it
+    assert tag == 0x4A46535441545553
+    rec = lambda t, code: C.create_string_buffer(struct.pack("<Qii", t, code, 0), 16)
+    assert l.jf_decode_status_of_copy(rec(tag, 0)) == lib.JF_OK
+    assert l.jf_decode_status_of_copy(rec(tag, 2)) == lib.JF_ERR_TIMEOUT
+    assert l.jf_decode_status_of_copy(rec(tag, 3)) == lib.JF_ERR_STATE
+    assert l.jf_decode_status_of_copy(rec(0x1234, 2)) == lib.JF_OK          # whatever the workspace held before
+    assert l.jf_decode_status_of_copy(None) == lib.JF_ERR_ARG

@@ -374,6 +374,147 @@ def test_default_prefill_attention_of_a_mixed_step_on_the_device():
     assert float(err.max()) <= 2e-2, f"max err {float(err.max()):.3e}"
 
 
+@pytest.mark.parametrize("signal", ["flags", "callbacks"])
+@pytest.mark.parametrize("mode_name,mode", [("SymInt3K_SymInt2V", "k3v2"), ("SymInt4K_SymInt4V", "k4v4")])
+def test_stream_ordered_decode_entry_eager_and_captured(mode_name, mode, signal):
+    """The decode entry in its stream-ordered form (nothing waits on the host: copies, kernels and
+    the correction's submit / join are queued on the stream over fixed buffers) gives, bit for bit,
+    what the default form gives -- run eagerly over three steps of growing sequences, and with the
+    append and the decode of a step captured in one CUDA graph that is replayed for the same steps.
+    ``signal``: the stream and the host meet through words in mapped memory (a kernel raises the
+    trigger a dispatcher thread polls; a kernel polls the completion word) or through host
+    functions in the stream."""
+    from dataclasses import replace
+    from jetfire_b200.adapter.config import JetFireConfig
+    from jetfire_b200.adapter import decode_path as dp
+    steps, len0 = 3, [300, 123]
+    case = Case(mode, 2, 8, 2, 320, lens=[n + steps for n in len0], seed=43)
+    cfg = JetFireConfig(mode=mode_name, top_k=64, group_size=MODES[mode][2], cpu_attn_threads=2)
+    cfg_so = replace(cfg, stream_ordered=True, stream_signal=signal)
+    slot_of = lambda b, pos: int(case.block_table[b, pos // 16]) * 16 + pos % 16
+    key_all = case.k_full.transpose(0, 1).contiguous().cuda()
+    val_all = case.v_full.transpose(0, 1).contiguous().cuda()
+    init = torch.tensor([slot_of(b, p) for b in range(case.B) for p in range(len0[b])], dtype=torch.int64).cuda()
+    impl = SimpleNamespace(scale=case.attn_scale, attn_type=SimpleNamespace(name="DECODER"))
+    layer = SimpleNamespace(num_heads=case.H_q, num_kv_heads=case.H_kv, head_size=128, layer_name="l0")
+    g = torch.Generator().manual_seed(6)
+    queries = [torch.randn(case.B, case.H_q, 128, generator=g).to(case.dtype).cuda() for _ in range(steps)]
+    bt = case.block_table.cuda()
+
+    # the same bound on the row length in all three runs (the split of a row into partial sums,
+    # and with it the last bits of the result, follows the bound, not the lengths)
+    bounded = lambda md: SimpleNamespace(**{**vars(md), "max_seq_len": case.ctx})
+
+    def tokens_of(t):
+        slots_t = torch.tensor([slot_of(b, len0[b] + t) for b in range(case.B)], dtype=torch.int64).cuda()
+        return key_all[slots_t], val_all[slots_t], slots_t
+
+    def fresh_store():
+        from jetfire_b200.adapter.cache_store import JetFireCacheStore
+        st = JetFireCacheStore(num_blocks=case.n_blocks, num_kv_heads=case.H_kv, head_dim=128, cfg=cfg, device="cuda",
+                               dtype=case.dtype, mirror_append="mapped")
+        st.write_slots(key_all[init], val_all[init], init)
+        st.flush_pending_writes()
+        return st
+
+    # the default form, step by step
+    want = []
+    st = fresh_store()
+    for t in range(steps):
+        k_t, v_t, s_t = tokens_of(t)
+        st.write_slots(k_t, v_t, s_t)
+        lens = torch.tensor([n + t + 1 for n in len0], dtype=torch.int32, device="cuda")
+        md = bounded(dp.make_decode_metadata(lens, bt))
+        out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
+        assert dp.try_jetfire_decode(impl=impl, layer=layer, query=queries[t], attn_metadata=md, output=out,
+                                     store=st, cfg=cfg) is out
+        torch.cuda.synchronize()
+        want.append(out.clone())
+
+    # stream-ordered, eager
+    st = fresh_store()
+    for t in range(steps):
+        k_t, v_t, s_t = tokens_of(t)
+        st.write_slots(k_t, v_t, s_t)
+        lens = torch.tensor([n + t + 1 for n in len0], dtype=torch.int32, device="cuda")
+        md = bounded(dp.make_decode_metadata(lens, bt))
+        out = torch.full((case.B, case.H_q * 128), 5.0, dtype=case.dtype, device="cuda")
+        assert dp.try_jetfire_decode(impl=impl, layer=layer, query=queries[t], attn_metadata=md, output=out,
+                                     store=st, cfg=cfg_so) is out
+        torch.cuda.synchronize()
+        assert torch.equal(out, want[t]), f"eager, step {t}"
+    for step in dp.stream_steps(st):
+        step.status()
+
+    # stream-ordered, append + decode of a step captured once and replayed
+    st = fresh_store()
+    new_k = torch.zeros(case.B, case.H_kv, 128, dtype=case.dtype, device="cuda")
+    new_v = torch.zeros_like(new_k)
+    new_slots = torch.full((case.B,), -1, dtype=torch.int64, device="cuda")
+    lens = torch.tensor(len0, dtype=torch.int32, device="cuda")
+    query = torch.zeros(case.B, case.H_q, 128, dtype=case.dtype, device="cuda")
+    out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
+    md = bounded(dp.make_decode_metadata(lens, bt))
+
+    def one_step():
+        st.write_slots(new_k, new_v, new_slots)
+        assert dp.try_jetfire_decode(impl=impl, layer=layer, query=query, attn_metadata=md, output=out,
+                                     store=st, cfg=cfg_so) is out
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):       # eager once (kernel attributes, worker threads); appends nothing
+        one_step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+    for t in range(steps):
+        k_t, v_t, s_t = tokens_of(t)
+        new_k.copy_(k_t); new_v.copy_(v_t); new_slots.copy_(s_t)
+        lens.copy_(torch.tensor([n + t + 1 for n in len0], dtype=torch.int32))
+        query.copy_(queries[t])
+        graph.replay()
+        torch.cuda.synchronize()
+        for step in dp.stream_steps(st):
+            step.status()
+        assert torch.equal(out, want[t]), f"replayed, step {t}"
+    del graph
+
+
+def test_wait_for_a_word_nothing_sets_runs_out_and_is_reported():
+    """The kernel that holds the stream for the host correction has a time budget: with a word that
+    nothing sets it gives up after the budget, writes the timeout into the status record it was
+    given and lets the stream go on; a word that is set lets it through at once."""
+    import time
+    from jetfire_b200 import ops
+    words_host, words_dev = ops.alloc_mapped_pinned_pair((16,), torch.int64)
+    words_host.zero_()
+    record = torch.zeros(ops.STATUS_RECORD_BYTES, dtype=torch.uint8, device="cuda")
+    after = torch.zeros(1, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ops.stream_wait_host_flag(words_dev[8:9], 20, record)
+    after.fill_(1.0)                                     # queued behind the wait
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert 0.015 < dt < 2.0, f"waited {dt * 1e3:.1f} ms for a budget of 20 ms"
+    assert float(after) == 1.0
+    with pytest.raises(RuntimeError):
+        ops.decode_status_of_copy(record.cpu())
+    record.zero_()
+    words_host[8] = 1
+    t0 = time.perf_counter()
+    ops.stream_wait_host_flag(words_dev[8:9], 2000, record)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5
+    ops.decode_status_of_copy(record.cpu())              # nothing recorded
+    ops.stream_signal_host(words_dev[8:9], words_dev[0:1])
+    torch.cuda.synchronize()
+    assert int(words_host[8]) == 0 and int(words_host[0]) == 1
+
+
 def test_decode_steps_replayed_as_one_cuda_graph_with_host_nodes():
     """A whole decode step of one layer captured once and replayed: append of the new token
     (packed cache + mapped mirror, one kernel), query upload, scan + selection, slot download,
