@@ -1061,6 +1061,42 @@ def main():
                 gather_step()
                 torch.cuda.current_stream().synchronize()
 
+        # The same serial chain with nothing waiting on the host inside a step: a kernel raises a word in
+        # mapped memory when a layer's slots are on the host, a dispatcher thread queues the correction,
+        # a kernel polls the word the last worker sets, and the merge reads o_new where the workers
+        # wrote it (the adapter's stream-ordered decode step).  One core goes to the dispatcher.
+        sig = []
+        for L in e2e_layers:
+            S = Layer()
+            S.words_host, S.words_dev = ops.alloc_mapped_pinned_pair((16,), torch.int64)
+            S.words_host.zero_()
+            S.o_new_host, S.o_new = ops.alloc_mapped_pinned_pair((shard.b_count, shard.q_count, 128), dtype)
+            S.o_new_host.zero_()
+            S.host_call = ops.HostCorrectionCall(L.q_host, L.k_shadow, L.v_shadow, None, L.slots_host, S.o_new_host,
+                                                 128 ** -0.5, done_flag=S.words_host[8:9])
+            sig.append(S)
+        watched = [False]
+
+        def e2e_serial_stream_step():
+            if not watched[0]:
+                for S in sig:
+                    S.host_call.watch(S.words_host[0:1])
+                watched[0] = True
+            for L, S in zip(e2e_layers, sig):
+                L.q.copy_(L.q_host, non_blocking=True)
+                L.call.fused()
+                L.slots_host.copy_(L.call.out["topk_slots_i32"], non_blocking=True)
+                ops.stream_signal_host(S.words_dev[8:9], S.words_dev[0:1])
+                ops.stream_wait_host_flag(S.words_dev[8:9], 5000, L.call.status_record())
+                res = L.call.out
+                ops.blend_unnorm_into(res["o_hat"], res["o_old_unnorm"], res["W"], S.o_new, L.out)
+            for L in e2e_layers:
+                L.out_host.copy_(L.out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            if world > 1:
+                gather_step()
+                torch.cuda.current_stream().synchronize()
+
         def timed(fn, n):
             for _ in range(2):
                 fn()
@@ -1077,7 +1113,16 @@ def main():
 
         e2e_steps = max(3, min(args.steps, 10))
         dt = timed(e2e_step, e2e_steps)
-        dt_serial = timed(e2e_serial_step, max(2, e2e_steps // 2))
+        dt_serial_wait = timed(e2e_serial_step, max(2, e2e_steps // 2))
+        check_out = e2e_layers[-1].out_host.clone()
+        ops.set_cpu_attn_threads(max(1, cpu_threads - 1))
+        dt_serial_stream = timed(e2e_serial_stream_step, max(2, e2e_steps // 2))
+        ops.set_cpu_attn_threads(cpu_threads)
+        for S in sig:
+            S.host_call.stream_status()
+            S.host_call.close()
+        serial_forms_agree = bool(torch.equal(check_out, e2e_layers[-1].out_host))
+        dt_serial = min(dt_serial_wait, dt_serial_stream)
         esz = 2
         n_e2e = len(e2e_layers)
         h2d = n_e2e * 2 * shard.b_count * shard.q_count * 128 * esz
@@ -1089,7 +1134,13 @@ def main():
                "layers_measured": n_e2e, "tokens_per_s": w["batch"] / dt_full, "host_threads_per_rank": cpu_threads,
                "serial_layers": {"value": job_layer_bytes * n_e2e / dt_serial / 1e9, "unit": "GB/s",
                                  "ms_per_step": dts_full * 1e3, "tokens_per_s": w["batch"] / dts_full,
-                                 "what": "layer l + 1 starts after layer l's merge (host correction on the critical path)"},
+                                 "what": "layer l + 1 starts after layer l's merge (host correction on the critical path)",
+                                 "how": ("stream-ordered: correction started and joined by kernels through words in mapped memory"
+                                         if dt_serial_stream <= dt_serial_wait else
+                                         "host waits for the slots, runs the correction, queues the merge"),
+                                 "host_wait_form": job_layer_bytes * n_e2e / dt_serial_wait / 1e9,
+                                 "stream_ordered_form": job_layer_bytes * n_e2e / dt_serial_stream / 1e9,
+                                 "forms_agree_bitwise": serial_forms_agree},
                "timing": "host wall clock around barrier + synchronize (host work is inside the region)"}
         if n_e2e < n_layers:
             e2e["note"] = (f"host memory: mirrors of {n_e2e} of {n_layers} layers; the copies above are per measured "

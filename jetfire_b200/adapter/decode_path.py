@@ -90,7 +90,11 @@ def _set_worker_count(cfg: JetFireConfig, node: int = -1) -> None:
     global _WORKERS_SET
     import os
     world = int(os.environ.get("WORLD_SIZE", "1") or 1)
-    want = max(1, min(int(cfg.cpu_attn_threads), cpu_threads_per_rank(os.cpu_count() or 1, world)))
+    # One core of the rank's share stays with the thread that drives the GPU (with a worker on every
+    # core that thread is preempted and every layer waits for it), one more with the dispatcher
+    # thread when the stream starts the corrections through trigger words.
+    spare = 2 if (cfg.stream_ordered and cfg.stream_signal == "flags") else 1
+    want = max(1, min(int(cfg.cpu_attn_threads), cpu_threads_per_rank(os.cpu_count() or 1, world) - spare))
     if node >= 0:
         try:
             cpus = len(ops.numa_node_cpus(node))
@@ -98,7 +102,7 @@ def _set_worker_count(cfg: JetFireConfig, node: int = -1) -> None:
             node, cpus = -1, 0
         if node >= 0:
             nodes = max(ops.numa_node_count(), 1)
-            want = workers_on_node(int(cfg.cpu_attn_threads), cpus, (world + nodes - 1) // nodes)
+            want = min(want, workers_on_node(int(cfg.cpu_attn_threads), cpus, (world + nodes - 1) // nodes))
     if _WORKERS_SET != (want, node):
         ops.set_cpu_attn_node(node)
         ops.set_cpu_attn_threads(want)
