@@ -49,7 +49,7 @@ class JetFireConfig:
     enabled: bool = True
     slots_i32: bool = True                # selected slots cross to the host as int32 (the reference: int64)
     numa_node: int = NUMA_AUTO            # memory node of mirrors and workers: NUMA_AUTO, NUMA_OFF or a node
-    stream_ordered: bool = False          # decode step queued on the stream without a host wait (capturable)
+    stream_ordered: bool = True           # decode step queued on the stream without a host wait (capturable)
     stream_signal: str = "flags"          # how a stream-ordered step meets the host: "flags" or "callbacks"
 
     @property
@@ -118,7 +118,7 @@ def get_jetfire_config() -> JetFireConfig:
     _CONFIG = JetFireConfig(mode=mode, top_k=top_k, group_size=group, cpu_attn_threads=threads,
                             max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32),
                             slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0, numa_node=_numa_env(),
-                            stream_ordered=_int_env("JETFIRE_STREAM_ORDERED", 0) != 0, stream_signal=signal)
+                            stream_ordered=_int_env("JETFIRE_STREAM_ORDERED", 1) != 0, stream_signal=signal)
     return _CONFIG
 
 

@@ -8,9 +8,10 @@ and the op order of ``_decode_batched`` :1712-3237):
 The reference's Stage A / Stage B pair is one fused call here, so nothing is left to overlap
 the host correction with inside a layer; across layers the caller may pipeline.
 
-Two forms of the step.  The default one waits on the host for the selected slots, runs the
+Two forms of the step.  The host-waiting one (``JETFIRE_STREAM_ORDERED=0``, and whenever the
+store's mirror is not the mapped one) waits on the host for the selected slots, runs the
 correction and returns with the merge queued.  The stream-ordered one
-(``JetFireConfig.stream_ordered``, the reference's graph-mode decode: create_cpu_topk_submit_ctx /
+(``JetFireConfig.stream_ordered``, the default; the reference's graph-mode decode: create_cpu_topk_submit_ctx /
 stream_submit_cpu_topk_attn / stream_wait_cpu_topk_attn, csrc/cpu_topk_attn.cpp:2147-2312, call
 sites decode_path.py:2253-2492) queues everything on the CUDA stream over buffers that keep their
 addresses -- copies, kernels, the correction's submit and join as host functions in the stream --
@@ -288,7 +289,12 @@ def try_jetfire_decode(*, impl, layer, query, attn_metadata, output, store=None,
         return None
     n = int(attn_metadata.seq_lens.numel())
     q = query[:n].view(n, int(layer.num_heads), int(layer.head_size))
-    step = decode_batched_stream_ordered if cfg.stream_ordered else decode_batched
+    # stream-ordered when configured and the store's mirror is the mapped one (the GPU appends to it in
+    # stream order); otherwise the host-waiting form, which cannot run under stream capture
+    stream_ordered = cfg.stream_ordered and store.shadow_enabled and store.mirror_append == "mapped"
+    if not stream_ordered and query.is_cuda and torch.cuda.is_current_stream_capturing():
+        return None
+    step = decode_batched_stream_ordered if stream_ordered else decode_batched
     return step(store=store, query=q, block_table=attn_metadata.block_table,
                           seq_lens=attn_metadata.seq_lens, max_seq_len=int(attn_metadata.max_seq_len),
                           num_heads=int(layer.num_heads), scale=float(impl.scale), output=output, cfg=cfg)

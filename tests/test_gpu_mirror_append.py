@@ -389,7 +389,7 @@ def test_stream_ordered_decode_entry_eager_and_captured(mode_name, mode, signal)
     from jetfire_b200.adapter import decode_path as dp
     steps, len0 = 3, [300, 123]
     case = Case(mode, 2, 8, 2, 320, lens=[n + steps for n in len0], seed=43)
-    cfg = JetFireConfig(mode=mode_name, top_k=64, group_size=MODES[mode][2], cpu_attn_threads=2)
+    cfg = JetFireConfig(mode=mode_name, top_k=64, group_size=MODES[mode][2], cpu_attn_threads=2, stream_ordered=False)
     cfg_so = replace(cfg, stream_ordered=True, stream_signal=signal)
     slot_of = lambda b, pos: int(case.block_table[b, pos // 16]) * 16 + pos % 16
     key_all = case.k_full.transpose(0, 1).contiguous().cuda()
