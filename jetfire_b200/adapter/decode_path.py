@@ -196,6 +196,11 @@ class _StreamStep:
         ops.decode_status_of_copy(self.status_host)
         self.host.stream_status()
 
+    def close(self) -> None:
+        """Release the correction context (the dispatcher stops polling its trigger word).  Only
+        once nothing queued on a stream, and no graph, refers to this step any more."""
+        self.host.close()
+
 
 _MAX_S_STEP = 4096      # a step object serves row lengths up to the next multiple of this
 _HOST_WAIT_MS = 5000    # budget of the kernel that waits for the host correction
@@ -222,12 +227,20 @@ def decode_batched_stream_ordered(*, store: JetFireCacheStore, query: torch.Tens
     width = int(block_table.shape[1])
     need_S = min(width * store.block_size, ((int(max_seq_len) + 15) // 16) * 16)
     steps = store.__dict__.setdefault("_stream_steps", {})
-    key = (B, num_heads, top_k, query.dtype, cfg.slots_i32, float(scale))
+    key = (B, num_heads, top_k, query.dtype, cfg.slots_i32, cfg.stream_signal, float(scale))
     step = steps.get(key)
     if step is None or step.max_S < need_S or step.max_blocks < min(width, (need_S + 15) // 16):
         max_S = min(width * store.block_size, -(-need_S // _MAX_S_STEP) * _MAX_S_STEP)
-        if step is not None and step.captured:      # a graph still refers to its buffers
-            store.__dict__.setdefault("_captured_steps", []).append(step)
+        if step is not None:
+            # The sequences have outgrown the step's buffers (once per _MAX_S_STEP tokens).  A step a
+            # graph refers to stays as it is; any other is released once the stream has drained --
+            # its last run may still be waiting for its correction.
+            if step.captured or torch.cuda.is_current_stream_capturing():
+                store.__dict__.setdefault("_captured_steps", []).append(step)
+            else:
+                torch.cuda.current_stream().synchronize()
+                step.check_previous()
+                step.close()
         _set_worker_count(cfg, getattr(store, "numa_node", -1))
         step = steps[key] = _StreamStep(store, cfg, B, num_heads, top_k, max_S // store.block_size, max_S,
                                         query.dtype, query.device, float(scale))

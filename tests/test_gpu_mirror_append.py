@@ -483,6 +483,39 @@ def test_stream_ordered_decode_entry_eager_and_captured(mode_name, mode, signal)
     del graph
 
 
+def test_stream_ordered_step_is_replaced_when_the_sequences_outgrow_it():
+    """The stream-ordered step holds buffers for rows up to a multiple of 4096 positions; when a
+    sequence grows past that the step is replaced (the old one released once the stream has
+    drained) and the results stay the oracle's on both sides of the boundary."""
+    from jetfire_b200.adapter.cache_store import JetFireCacheStore
+    from jetfire_b200.adapter.config import JetFireConfig
+    from jetfire_b200.adapter import decode_path as dp
+    case = Case("k3v2", 2, 8, 2, 4112, lens=[4112, 700], seed=47)
+    cfg = JetFireConfig(mode="SymInt3K_SymInt2V", top_k=64, group_size=64, cpu_attn_threads=2)
+    st = JetFireCacheStore(num_blocks=case.n_blocks, num_kv_heads=case.H_kv, head_dim=128, cfg=cfg, device="cuda",
+                           dtype=case.dtype, mirror_append="mapped")
+    st.write_slots(case.k_full.transpose(0, 1).contiguous().cuda(), case.v_full.transpose(0, 1).contiguous().cuda(),
+                   torch.arange(case.num_slots, dtype=torch.int64, device="cuda"))
+    impl = SimpleNamespace(scale=case.attn_scale, attn_type=SimpleNamespace(name="DECODER"))
+    layer = SimpleNamespace(num_heads=case.H_q, num_kv_heads=case.H_kv, head_size=128, layer_name="l0")
+    seen = []
+    for lens in ([4090, 700], [4096, 700], [4100, 640]):
+        case.seq_lens = torch.tensor(lens, dtype=torch.int32)
+        md = dp.make_decode_metadata(case.seq_lens.cuda(), case.block_table.cuda())
+        out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
+        assert dp.try_jetfire_decode(impl=impl, layer=layer, query=case.q.cuda(), attn_metadata=md, output=out,
+                                     store=st, cfg=cfg) is out
+        torch.cuda.synchronize()
+        steps = dp.stream_steps(st)
+        assert len(steps) == 1
+        steps[0].status()
+        seen.append(steps[0].max_S)
+        want = O.bf16_bits_to_f32(O.f32_to_bf16_bits(case.oracle_step(64)["out"]))
+        err = np.abs(f32_values(out).reshape(case.B, case.H_q, 128) - want)
+        assert (err <= 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)).all(), f"lens {lens}: max err {err.max():.3e}"
+    assert seen == [4096, 4096, 4112]        # the third step needs 4112 positions: all the block table has
+
+
 def test_wait_for_a_word_nothing_sets_runs_out_and_is_reported():
     """The kernel that holds the stream for the host correction has a time budget: with a word that
     nothing sets it gives up after the budget, writes the timeout into the status record it was
