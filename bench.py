@@ -1123,6 +1123,14 @@ def main():
             S.host_call.close()
         serial_forms_agree = bool(torch.equal(check_out, e2e_layers[-1].out_host))
         dt_serial = min(dt_serial_wait, dt_serial_stream)
+        # the host's share alone: the corrections of all measured layers back to back over the slot
+        # lists the last step left on the host, nothing else running (each layer's mirror is cold)
+        for L in e2e_layers[:2]:
+            L.host_call.run()
+        t0 = time.perf_counter()
+        for L in e2e_layers:
+            L.host_call.run()
+        host_only_us = (time.perf_counter() - t0) / len(e2e_layers) * 1e6
         esz = 2
         n_e2e = len(e2e_layers)
         h2d = n_e2e * 2 * shard.b_count * shard.q_count * 128 * esz
@@ -1132,6 +1140,7 @@ def main():
         e2e = {"value": job_layer_bytes * n_e2e / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d * world,
                "d2h_bytes_per_step": d2h * world, "ms_per_step": dt_full * 1e3, "steps": e2e_steps,
                "layers_measured": n_e2e, "tokens_per_s": w["batch"] / dt_full, "host_threads_per_rank": cpu_threads,
+               "us_per_layer": dt / n_e2e * 1e6, "host_correction_alone_us_per_layer": host_only_us,
                "serial_layers": {"value": job_layer_bytes * n_e2e / dt_serial / 1e9, "unit": "GB/s",
                                  "ms_per_step": dts_full * 1e3, "tokens_per_s": w["batch"] / dts_full,
                                  "what": "layer l + 1 starts after layer l's merge (host correction on the critical path)",
