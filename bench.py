@@ -91,6 +91,10 @@ def parse_args():
     ap.add_argument("--no-check", action="store_true", help="skip the oracle replay of one timed row")
     ap.add_argument("--cpu-threads", type=int, default=0, help="host correction threads (0 = cores / ranks - 1)")
     ap.add_argument("--no-huge-pages", action="store_true", help="host mirrors on the system's default pages")
+    ap.add_argument("--gpu-correction-share", default="auto", metavar="auto|F",
+                    help="end-to-end leg: fraction of the correction's rows the GPU computes straight from the host "
+                         "mirror over the host link while the workers do the rest (auto: from the two measured rates; "
+                         "0: the workers do all of it)")
     ap.add_argument("--no-numa", action="store_true",
                     help="leave the host mirrors and the correction workers where the system puts them")
     ap.add_argument("--as-shard", metavar="R/N", help="single GPU only: run the shard that rank R of an N-GPU run owns "
@@ -1014,9 +1018,80 @@ def main():
         copy_stream = torch.cuda.Stream()
         e2e_layers = layers[:mirror_layers]
 
+        # ---- the correction shared with the GPU ----
+        # The step is bounded by the workers' scattered reads of the cold mirror while the GPU and its
+        # host link idle: the GPU computes the last rows of every layer's correction itself, reading the
+        # selected mirror rows over the link (jf_gpu_topk_attn_rows), the workers the first ones.  The
+        # share follows from the two rates, measured here on the first layers.
+        n_rows = shard.b_count * shard.q_count
+        cut, share_info = n_rows, {"share": 0.0}
+        side_stream = torch.cuda.Stream()
+        want_share = args.gpu_correction_share
+        if want_share != "0":
+            try:
+                t0 = time.perf_counter()
+                for li, L in enumerate(e2e_layers):   # the mirrors become visible to the GPU (page-locked where they lie)
+                    L.k_mirror_dev = ops.map_host_tensor(L.k_shadow)
+                    L.v_mirror_dev = ops.map_host_tensor(L.v_shadow)
+                    if li == 0 and (time.perf_counter() - t0) * len(e2e_layers) > 90.0:
+                        ops.unmap_host_tensor(L.k_shadow)
+                        ops.unmap_host_tensor(L.v_shadow)
+                        raise RuntimeError(f"page-locking the mirrors would take {(time.perf_counter() - t0) * len(e2e_layers):.0f} s")
+                share_info["map_s"] = round(time.perf_counter() - t0, 2)
+                probe = e2e_layers[:min(4, len(e2e_layers))]
+                for L in probe:             # slot lists for the probe
+                    L.q.copy_(L.q_host)
+                    L.call.fused()
+                    L.slots_host.copy_(L.call.out["topk_slots_i32"])
+                torch.cuda.synchronize()
+                for L in probe[:1]:
+                    L.host_call.run()
+                t0 = time.perf_counter()
+                for L in probe:
+                    L.host_call.run()
+                host_us = (time.perf_counter() - t0) / len(probe) * 1e6
+                sample = max(1, n_rows // 8)
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                gpu_us = []
+                for L in probe:
+                    ev0.record()
+                    ops.gpu_topk_attn_rows(L.q, L.k_mirror_dev, L.v_mirror_dev, L.call.out["topk_slots_i32"], L.o_new,
+                                           128 ** -0.5, (n_rows - sample, n_rows))
+                    ev1.record()
+                    torch.cuda.synchronize()
+                    gpu_us.append(ev0.elapsed_time(ev1) * 1e3 * n_rows / sample)
+                gpu_full_us = sorted(gpu_us)[len(gpu_us) // 2]
+                # the check of the GPU's rows against the workers' (rounding of the 16-bit result apart)
+                Lc = probe[-1]
+                ref_rows = Lc.o_new_host.view(n_rows, 128)[n_rows - sample:].float()
+                got_rows = Lc.o_new.view(n_rows, 128)[n_rows - sample:].float().cpu()
+                agree = bool(((got_rows - ref_rows).abs() <= 1e-3 + 2.0 ** -7 * ref_rows.abs()).all())
+                if want_share == "auto":
+                    f = 0.9 * host_us / (host_us + gpu_full_us)     # a little less than the balance point: both sides slow each other
+                else:
+                    f = float(want_share)
+                f = min(max(f, 0.0), 0.5) if agree else 0.0
+                cut = n_rows - int(round(f * n_rows))
+                share_info.update({"share": (n_rows - cut) / n_rows, "rows_gpu": n_rows - cut, "rows_host": cut,
+                                   "host_us_per_layer_alone": host_us, "gpu_us_per_layer_alone": gpu_full_us,
+                                   "gpu_link_GBps": n_rows * w["top_k"] * 512 / gpu_full_us / 1e3,
+                                   "rows_agree_with_host": agree})
+            except Exception as exc:        # the mirrors could not be page-locked, or the probe failed: workers only
+                cut, share_info = n_rows, {"share": 0.0, "why": f"{type(exc).__name__}: {exc}"[:200]}
+        shared_calls = None                 # every rank decides for itself; rank 0 reports its own
+        if cut < n_rows:                    # the share is at most a half: the workers always have rows
+            shared_calls = [ops.HostCorrectionCall(L.q_host, L.k_shadow, L.v_shadow, None, L.slots_host, L.o_new_host,
+                                                   128 ** -0.5, rows=(0, cut)) for L in e2e_layers]
+            for L in e2e_layers:
+                L.gpu_event = torch.cuda.Event()
+
         def merge_e2e(L):  # o_new host -> device, merge, result device -> host; on the copy stream
             with torch.cuda.stream(copy_stream):
-                L.o_new.copy_(L.o_new_host, non_blocking=True)
+                if cut < n_rows:            # the workers' rows come from the host, the GPU's are in place
+                    copy_stream.wait_event(L.gpu_event)
+                    L.o_new.view(n_rows, 128)[:cut].copy_(L.o_new_host.view(n_rows, 128)[:cut], non_blocking=True)
+                else:
+                    L.o_new.copy_(L.o_new_host, non_blocking=True)
                 merge(ops, L)
                 L.out_host.copy_(L.out, non_blocking=True)
 
@@ -1027,12 +1102,18 @@ def main():
                 L.call.fused()
                 L.slots_host.copy_(L.call.out["topk_slots_i32"], non_blocking=True)
                 L.event.record(main_s)
+                if cut < n_rows:            # the GPU's rows of this layer, beside the next layers' kernels
+                    side_stream.wait_event(L.event)
+                    with torch.cuda.stream(side_stream):
+                        ops.gpu_topk_attn_rows(L.q, L.k_mirror_dev, L.v_mirror_dev, L.call.out["topk_slots_i32"], L.o_new,
+                                               128 ** -0.5, (cut, n_rows))
+                        L.gpu_event.record(side_stream)
             # The next layer's correction is queued before the previous one is waited for, so the
             # workers flow from one job into the next; merges are launched as jobs complete.
             prev = None
-            for L in e2e_layers:
+            for li, L in enumerate(e2e_layers):
                 L.event.synchronize()
-                ticket = L.host_call.submit()
+                ticket = shared_calls[li].submit() if shared_calls else L.host_call.submit()
                 if prev is not None:
                     L.host_call.wait_ticket(prev[1])
                     merge_e2e(prev[0])
@@ -1113,8 +1194,13 @@ def main():
 
         e2e_steps = max(3, min(args.steps, 10))
         dt = timed(e2e_step, e2e_steps)
+        pipelined_out = e2e_layers[-1].out_host.clone()
         dt_serial_wait = timed(e2e_serial_step, max(2, e2e_steps // 2))
         check_out = e2e_layers[-1].out_host.clone()
+        # the pipelined leg's output (some rows corrected by the GPU) against the workers-only chain
+        d_out = (pipelined_out.float() - check_out.float()).abs()
+        share_info["outputs_agree"] = bool((d_out <= 2e-3 + 2.0 ** -7 * check_out.float().abs()).all())
+        share_info["outputs_max_abs_diff"] = float(d_out.max())
         ops.set_cpu_attn_threads(max(1, cpu_threads - 1))
         dt_serial_stream = timed(e2e_serial_stream_step, max(2, e2e_steps // 2))
         ops.set_cpu_attn_threads(cpu_threads)
@@ -1141,6 +1227,9 @@ def main():
                "d2h_bytes_per_step": d2h * world, "ms_per_step": dt_full * 1e3, "steps": e2e_steps,
                "layers_measured": n_e2e, "tokens_per_s": w["batch"] / dt_full, "host_threads_per_rank": cpu_threads,
                "us_per_layer": dt / n_e2e * 1e6, "host_correction_alone_us_per_layer": host_only_us,
+               "gpu_correction": dict(share_info, mirror_bytes_read_by_gpu_per_step=(n_rows - cut) * w["top_k"] * 512 * n_e2e * world,
+                                      what="rows of the correction the GPU computes from the host mirror over the host link "
+                                           "(jf_gpu_topk_attn_rows) while the workers do the others; pipelined leg only"),
                "serial_layers": {"value": job_layer_bytes * n_e2e / dt_serial / 1e9, "unit": "GB/s",
                                  "ms_per_step": dts_full * 1e3, "tokens_per_s": w["batch"] / dts_full,
                                  "what": "layer l + 1 starts after layer l's merge (host correction on the critical path)",

@@ -364,6 +364,27 @@ jf_status_t jf_submit_ctx_status(int64_t handle);
 jf_status_t jf_stream_submit_cpu_topk_attn(jf_stream_t stream, int64_t handle);
 jf_status_t jf_stream_wait_cpu_topk_attn(jf_stream_t stream, int64_t handle);
 
+/* The correction shared between the host's workers and the GPU.  End to end a decode step is
+ * bounded by the workers' random gathers from the cold mirror while the GPU and its host link
+ * idle; jf_gpu_topk_attn_rows takes a range of the (sequence, query head) rows -- B * H_q of
+ * them, row-major -- off the workers: one block per row reads the selected K and V rows from
+ * the mirror through its DEVICE-VISIBLE address (mapped pinned memory: jf_alloc_mapped /
+ * jf_map_host), one coalesced 256-byte read each, and writes its rows of o_new on the device.
+ * Same arithmetic as jf_cpu_topk_attn in another summation order (agreement to rounding).
+ * `topk_slots` is the device slot list (int64, or int32 with slots_are_i32).
+ * jf_pool_submit_rows is jf_pool_submit_ticket for a non-empty range of rows; the rest of o_new
+ * is left alone.  No counterpart on the reference's release path (its GPU-side correction,
+ * jetfire_vllm/csrc/fused_correction.cu, works on a device-resident copy of the rows). */
+jf_status_t jf_gpu_topk_attn_rows(const void* q, const void* k_mirror_dev, const void* v_mirror_dev,
+                                  const void* topk_slots, int32_t slots_are_i32, void* o_new, int32_t dtype,
+                                  int32_t B, int32_t H_q, int32_t H_kv, int64_t num_slots, int32_t K, float scale,
+                                  int64_t row_begin, int64_t row_end, jf_stream_t stream);
+jf_status_t jf_pool_submit_rows(const void* q, const void* k_shadow, const void* v_shadow,
+                                const int64_t* head_map, const void* ts_buf, int32_t slots_are_i32,
+                                void* o_new, int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
+                                int64_t row_begin, int64_t row_end, int64_t* ticket);
+
 /* Host correction started and joined by the GPU through two words in mapped pinned host memory,
  * with no host function in the stream (each costs two thread hand-overs; a layer's pair costs
  * more than the GPU half of the step).  The reference's counterparts are the device-signal and

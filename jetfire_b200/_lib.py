@@ -124,6 +124,12 @@ _SIGS = {
     "jf_stream_submit_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),
     "jf_stream_wait_cpu_topk_attn": (C.c_int32, [C.c_void_p, C.c_int64]),
     "jf_pool_shutdown": (C.c_int32, []),
+    "jf_gpu_topk_attn_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
+                                          C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_float,
+                                          C.c_int64, C.c_int64, C.c_void_p]),
+    "jf_pool_submit_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                        C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_float,
+                                        C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_int64)]),
     "jf_submit_ctx_watch": (C.c_int32, [C.c_int64, C.c_void_p]),
     "jf_submit_ctx_unwatch": (C.c_int32, [C.c_int64]),
     "jf_stream_signal_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),

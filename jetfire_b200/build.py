@@ -18,7 +18,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libjetfire_b200.so"
 SOURCES = ["pack_append.cu", "decode_scan.cu", "decode_scan_k4v4.cu", "topk_select.cu", "decode_finish.cu", "decode_static.cu",
-           "jf_misc.cu", "mirror_append.cu", "cpu_correction.cpp", "numa_place.cpp"]
+           "jf_misc.cu", "mirror_append.cu", "mirror_correct.cu", "cpu_correction.cpp", "numa_place.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-O3", "-Xcompiler", "-pthread"]
 

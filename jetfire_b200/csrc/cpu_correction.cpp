@@ -100,6 +100,8 @@ struct Job {
   int64_t num_slots;
   float scale;
   int64_t* done_flag;
+  int64_t row_begin = 0;    // the (sequence, query head) rows [row_begin, row_begin + row_count) of the job;
+  int64_t row_count = -1;   // -1: all B * H_q of them
 };
 
 struct Scratch {
@@ -386,7 +388,7 @@ class Pool {
         continue;
       }
       sl.job = j;
-      sl.total = static_cast<int64_t>(j.B) * j.H_q;
+      sl.total = j.row_count >= 0 ? j.row_count : static_cast<int64_t>(j.B) * j.H_q;
       sl.next_row.store(0, std::memory_order_relaxed);
       sl.rows_done.store(0, std::memory_order_relaxed);
       sl.left.store(0, std::memory_order_relaxed);
@@ -458,7 +460,7 @@ class Pool {
       for (;;) {
         const int64_t i = sl.next_row.fetch_add(1, std::memory_order_relaxed);
         if (i >= total) break;
-        run_row(j, i, sc);
+        run_row(j, j.row_begin + i, sc);
         _mm_sfence();  // results may sit in write-combined mapped memory
         if (sl.rows_done.fetch_add(1, std::memory_order_acq_rel) + 1 == total) {   // the job's last row
           if (j.done_flag) {
@@ -597,6 +599,25 @@ extern "C" jf_status_t jf_pool_submit_ticket(const void* q, const void* k_shadow
   jf_status_t st = make_job(j, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
                             scale, done_flag);
   if (st != JF_OK) return st;
+  return submit_job(j, ticket);
+}
+
+// A range of the job's (sequence, query head) rows only -- rows [row_begin, row_end) of the B * H_q
+// in row-major order; the others are left to someone else (jf_gpu_topk_attn_rows) and their part
+// of o_new is not touched.  The range must not be empty.
+extern "C" jf_status_t jf_pool_submit_rows(const void* q, const void* k_shadow, const void* v_shadow,
+                                           const int64_t* head_map, const void* ts_buf, int32_t slots_are_i32,
+                                           void* o_new, int32_t dtype, int32_t B, int32_t H_q, int32_t H_kv,
+                                           int64_t num_slots, int32_t K, float scale, int64_t* done_flag,
+                                           int64_t row_begin, int64_t row_end, int64_t* ticket) {
+  if (!ticket) return JF_ERR_ARG;
+  Job j;
+  jf_status_t st = make_job(j, q, k_shadow, v_shadow, head_map, ts_buf, o_new, dtype, B, H_q, H_kv, num_slots, K,
+                            scale, done_flag, slots_are_i32 != 0);
+  if (st != JF_OK) return st;
+  if (row_begin < 0 || row_end <= row_begin || row_end > static_cast<int64_t>(B) * H_q) return JF_ERR_ARG;
+  j.row_begin = row_begin;
+  j.row_count = row_end - row_begin;
   return submit_job(j, ticket);
 }
 

@@ -648,11 +648,19 @@ class HostCorrectionCall:
     taken once, ``submit()`` / ``wait()`` / ``run()`` then cost one C call each.  The caller keeps
     the buffers' contents current; the tensors themselves are kept alive here."""
 
-    def __init__(self, q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None):
+    def __init__(self, q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag=None, rows=None):
         self._args = _host_args(q, k_shadow, v_shadow, head_map, ts_buf, o_new, scale, done_flag,
                                 "HostCorrectionCall")
         self._keep = (q, k_shadow, v_shadow, head_map, ts_buf, o_new, done_flag)
         i32 = _i32(ts_buf)   # 32-bit slot list: the entry points of the same names with the _i32 suffix
+        # rows=(begin, end): only that range of the B * H_q (sequence, query head) rows, the rest being
+        # someone else's (gpu_topk_attn_rows); submit() / run() only
+        self._rows = None
+        if rows is not None:
+            r0, r1 = int(rows[0]), int(rows[1])
+            _require(0 <= r0 < r1 <= q.shape[0] * q.shape[1], "HostCorrectionCall: rows must be a non-empty range of the B * H_q rows")
+            a = self._args
+            self._rows = (*a[:5], 1 if i32 else 0, *a[5:], r0, r1)
         self._fn_submit = lib.jf_pool_submit_ticket_i32 if i32 else lib.jf_pool_submit_ticket
         self._fn_run = lib.jf_cpu_topk_attn_i32 if i32 else lib.jf_cpu_topk_attn
         self._fn_ctx = lib.jf_submit_ctx_create_i32 if i32 else lib.jf_submit_ctx_create
@@ -660,7 +668,10 @@ class HostCorrectionCall:
     def submit(self) -> int:
         """Queue the job (up to four can wait in the pool); returns its ticket for ``wait_ticket``."""
         t = C.c_int64(0)
-        check("cpu_topk_attn_submit", self._fn_submit(*self._args, C.byref(t)))
+        if self._rows is not None:
+            check("cpu_topk_attn_submit", lib.jf_pool_submit_rows(*self._rows, C.byref(t)))
+        else:
+            check("cpu_topk_attn_submit", self._fn_submit(*self._args, C.byref(t)))
         return t.value
 
     @staticmethod
@@ -672,11 +683,15 @@ class HostCorrectionCall:
         check("cpu_topk_attn_wait", lib.jf_pool_wait_timeout(int(timeout_ms)))
 
     def run(self) -> None:
-        check("cpu_topk_attn", self._fn_run(*self._args))
+        if self._rows is not None:
+            self.wait_ticket(self.submit())
+        else:
+            check("cpu_topk_attn", self._fn_run(*self._args))
 
     # -- stream-ordered form (the reference's create_cpu_topk_submit_ctx /
     #    stream_submit_cpu_topk_attn / stream_wait_cpu_topk_attn, csrc/cpu_topk_attn.cpp:2147-2312) --
     def _handle(self) -> int:
+        _require(self._rows is None, "HostCorrectionCall: a row range is served by submit() / run() only")
         if getattr(self, "_ctx", None) is None:
             h = C.c_int64(0)
             check("create_cpu_topk_submit_ctx", self._fn_ctx(*self._args, 0, C.byref(h)))
@@ -750,6 +765,33 @@ def stream_write_value64(stream_id: int, flag_device: torch.Tensor, value: int) 
     _require(flag_device.is_cuda and flag_device.dtype == torch.int64 and flag_device.numel() == 1,
              "stream_write_value64: flag_device must be a 1-element int64 CUDA tensor")
     check("stream_write_value64", lib.jf_stream_write_value64(int(stream_id), flag_device.data_ptr(), int(value)))
+
+
+def gpu_topk_attn_rows(q, k_mirror_dev, v_mirror_dev, topk_slots, o_new, scale, rows) -> None:
+    """The top-k correction of the (sequence, query head) rows ``rows = (begin, end)`` on the GPU,
+    reading the selected K / V rows from the host mirror through its device-visible tensors (the
+    device halves of ``alloc_mapped_pinned_pair`` / ``map_host_tensor``): takes those rows off the
+    host's workers (``HostCorrectionCall(rows=...)`` for the rest).  ``q (B, H_q, 128)`` and
+    ``topk_slots (B, H_q, K)`` int64 or int32 are CUDA tensors, ``o_new (B, H_q, 128)`` a CUDA tensor
+    whose rows in the range are written.  Agrees with ``cpu_topk_attn`` to rounding."""
+    name = "gpu_topk_attn_rows"
+    for t, nm in ((q, "q"), (k_mirror_dev, "k_mirror_dev"), (v_mirror_dev, "v_mirror_dev"), (topk_slots, "topk_slots"),
+                  (o_new, "o_new")):
+        _require(t.is_cuda and t.is_contiguous(), f"{name}: {nm} must be a contiguous CUDA tensor")
+    _require(q.dim() == 3 and q.shape[2] == 128 and o_new.shape == q.shape, f"{name}: q / o_new must be (B, H_q, 128)")
+    _require(q.dtype == k_mirror_dev.dtype == v_mirror_dev.dtype == o_new.dtype, f"{name}: dtype mismatch")
+    _require(k_mirror_dev.dim() == 3 and k_mirror_dev.shape[2] == 128 and v_mirror_dev.shape == k_mirror_dev.shape,
+             f"{name}: mirrors must be (H_kv, num_slots, 128)")
+    B, H_q = int(q.shape[0]), int(q.shape[1])
+    _require(topk_slots.dtype in (torch.int64, torch.int32) and topk_slots.dim() == 3
+             and tuple(topk_slots.shape[:2]) == (B, H_q), f"{name}: topk_slots must be (B, H_q, K) int64 or int32")
+    r0, r1 = int(rows[0]), int(rows[1])
+    _require(0 <= r0 <= r1 <= B * H_q, f"{name}: rows must be a range of the B * H_q rows")
+    check(name, lib.jf_gpu_topk_attn_rows(q.data_ptr(), k_mirror_dev.data_ptr(), v_mirror_dev.data_ptr(),
+                                          topk_slots.data_ptr(), 1 if topk_slots.dtype == torch.int32 else 0,
+                                          o_new.data_ptr(), _dtype_id(q), B, H_q, int(k_mirror_dev.shape[0]),
+                                          int(k_mirror_dev.shape[1]), int(topk_slots.shape[2]), float(scale), r0, r1,
+                                          _stream()))
 
 
 def stream_signal_host(done_dev: torch.Tensor, trigger_dev: torch.Tensor) -> None:

@@ -448,3 +448,53 @@ def test_reference_named_shadow_append_scatters_staged_rows_in_stream_order():
         assert torch.equal(k_sh[:, s_], key[t].cpu()) and torch.equal(v_sh[:, s_], val[t].cpu())
     rest = [s_ for s_ in range(num_slots) if s_ not in (3, 63, 10)]
     assert not k_sh[:, rest].any() and not v_sh[:, rest].any()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("slot_dtype", [torch.int64, torch.int32])
+def test_correction_rows_on_the_gpu_over_the_host_mirror(dtype, slot_dtype):
+    """A range of the correction's rows computed by the GPU straight from the host mirror (mapped
+    pinned memory) agrees with the host correction to the rounding of the 16-bit result; entries
+    that are negative or beyond the cache are skipped, a row without a valid entry gives zeros,
+    rows outside the range are not touched; host rows + GPU rows together are the full result."""
+    from jetfire_b200 import ops
+    g = torch.Generator().manual_seed(13)
+    B, H_q, H_kv, K, slots = 3, 16, 2, 37, 4096          # K neither a multiple of 4 nor of the unrolling
+    k_host, k_dev = ops.alloc_mapped_pinned_pair((H_kv, slots, 128), dtype)
+    v_host, v_dev = ops.alloc_mapped_pinned_pair((H_kv, slots, 128), dtype)
+    k_host.copy_(torch.randn(H_kv, slots, 128, generator=g).to(dtype))
+    v_host.copy_(torch.randn(H_kv, slots, 128, generator=g).to(dtype))
+    q = torch.randn(B, H_q, 128, generator=g).to(dtype)
+    ts = torch.randint(0, slots, (B, H_q, K), generator=g, dtype=slot_dtype)
+    ts[0, 3, ::5] = -1                                     # padding of a short sequence
+    ts[1, 0, 7] = slots + 5                                # beyond the cache
+    ts[2, 9, :] = -1                                       # nothing valid at all
+    want = torch.empty_like(q)
+    ops.set_cpu_attn_threads(3)
+    ops.cpu_topk_attn(q, k_host, v_host, None, ts, want, 0.11)
+    rows = B * H_q
+    got = torch.full((B, H_q, 128), 7.0, dtype=dtype, device="cuda")
+    ops.gpu_topk_attn_rows(q.cuda(), k_dev, v_dev, ts.cuda(), got, 0.11, (5, rows - 2))
+    torch.cuda.synchronize()
+    gotc, wantc = got.cpu().view(rows, 128).float(), want.view(rows, 128).float()
+    assert bool((gotc[:5] == 7).all()) and bool((gotc[rows - 2:] == 7).all())
+    err = (gotc[5:rows - 2] - wantc[5:rows - 2]).abs()
+    lim = 1e-3 + 2.0 ** -7 * wantc[5:rows - 2].abs()
+    assert bool((err <= lim).all()), f"max err {float(err.max()):.3e}"
+    assert not gotc[2 * H_q + 9].any()                     # the row without a valid entry
+    # the split the end-to-end loop uses: the host takes the first rows, the GPU the rest
+    cut = 29
+    both_host = torch.full_like(q, 7.0).pin_memory()
+    both = torch.full((B, H_q, 128), 7.0, dtype=dtype, device="cuda")
+    call = ops.HostCorrectionCall(q, k_host, v_host, None, ts, both_host, 0.11, rows=(0, cut))
+    ticket = call.submit()
+    ops.gpu_topk_attn_rows(q.cuda(), k_dev, v_dev, ts.cuda(), both, 0.11, (cut, rows))
+    call.wait_ticket(ticket)
+    both.view(rows, 128)[:cut].copy_(both_host.view(rows, 128)[:cut])
+    torch.cuda.synchronize()
+    bc = both.cpu().view(rows, 128).float()
+    assert torch.equal(bc[:cut], wantc[:cut])
+    assert bool(((bc[cut:] - wantc[cut:]).abs() <= 1e-3 + 2.0 ** -7 * wantc[cut:].abs()).all())
+    ops.gpu_topk_attn_rows(q.cuda(), k_dev, v_dev, ts.cuda(), both, 0.11, (4, 4))      # an empty range is a no-op
+    with pytest.raises(RuntimeError):
+        ops.gpu_topk_attn_rows(q.cuda(), k_dev, v_dev, ts.cuda(), both, 0.11, (0, rows + 1))

@@ -178,3 +178,41 @@ def test_queued_jobs_complete_in_any_interleaving():
             ops.HostCorrectionCall.wait_ticket(t)
             assert torch.equal(out, want)
         assert _lib.lib.jf_pool_wait_timeout(0) == 0
+
+
+def test_host_correction_over_a_range_of_rows():
+    """The host correction restricted to a range of the (sequence, query head) rows -- the rest being
+    left to the GPU -- computes exactly those rows, bit for bit as in the full job, and touches no
+    other part of ``o_new``; the ranges of a partition add up to the full result."""
+    import torch
+    from jetfire_b200 import _lib, ops
+    g = torch.Generator().manual_seed(11)
+    B, H_q, H_kv, K, slots = 3, 8, 2, 24, 96
+    q = torch.randn(B, H_q, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(H_kv, slots, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(H_kv, slots, 128, generator=g).to(torch.bfloat16)
+    ops.set_cpu_attn_threads(3)
+    for dtype in (torch.int64, torch.int32):
+        ts = torch.randint(-2, slots + 2, (B, H_q, K), generator=g, dtype=dtype)      # some invalid entries
+        full = torch.empty_like(q)
+        ops.cpu_topk_attn(q, k, v, None, ts, full, 0.09)
+        part = torch.full_like(q, 7.0)
+        ops.HostCorrectionCall(q, k, v, None, ts, part, 0.09, rows=(5, 17)).run()
+        got, want = part.view(-1, 128), full.view(-1, 128)
+        assert torch.equal(got[5:17], want[5:17])
+        assert bool((got[:5] == 7).all()) and bool((got[17:] == 7).all())
+        pieces = torch.full_like(q, 7.0)
+        tickets = [ops.HostCorrectionCall(q, k, v, None, ts, pieces, 0.09, rows=r).submit() for r in ((0, 1), (1, 20), (20, 24))]
+        for t in tickets:
+            ops.HostCorrectionCall.wait_ticket(t)
+        assert torch.equal(pieces, full)
+    for bad in ((4, 4), (-1, 3), (3, 25), (9, 2)):
+        with pytest.raises(RuntimeError):
+            ops.HostCorrectionCall(q, k, v, None, ts, part, 0.09, rows=bad)
+    with pytest.raises(RuntimeError):
+        ops.HostCorrectionCall(q, k, v, None, ts, part, 0.09, rows=(0, 4)).stream_submit()
+    t = _lib.C.c_int64(0)
+    args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), None, ts.data_ptr(), 1, part.data_ptr(), 0, B, H_q, H_kv, slots, K, 0.09, None)
+    assert _lib.lib.jf_pool_submit_rows(*args, 4, 4, _lib.C.byref(t)) == _lib.JF_ERR_ARG
+    assert _lib.lib.jf_pool_submit_rows(*args, 0, B * H_q + 1, _lib.C.byref(t)) == _lib.JF_ERR_ARG
+    assert _lib.lib.jf_pool_submit_rows(*args, 0, 4, None) == _lib.JF_ERR_ARG
