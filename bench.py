@@ -1024,7 +1024,9 @@ def main():
         # selected mirror rows over the link (jf_gpu_topk_attn_rows), the workers the first ones.  The
         # share follows from the two rates, measured here on the first layers.
         n_rows = shard.b_count * shard.q_count
-        cut, share_info = n_rows, {"share": 0.0}
+        plan = {"cut": n_rows, "calls": None}      # workers only, until the shared plan has proved faster
+        share_info = {"share": 0.0}
+        gpu_full_us = None
         side_stream = torch.cuda.Stream()
         want_share = args.gpu_correction_share
         if want_share != "0":
@@ -1044,48 +1046,44 @@ def main():
                     L.call.fused()
                     L.slots_host.copy_(L.call.out["topk_slots_i32"])
                 torch.cuda.synchronize()
-                for L in probe[:1]:
-                    L.host_call.run()
-                t0 = time.perf_counter()
-                for L in probe:
-                    L.host_call.run()
-                host_us = (time.perf_counter() - t0) / len(probe) * 1e6
                 sample = max(1, n_rows // 8)
                 ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 gpu_us = []
-                for L in probe:
+                for L in probe:             # the GPU's rate over the link: the last eighth of the rows, alone
                     ev0.record()
                     ops.gpu_topk_attn_rows(L.q, L.k_mirror_dev, L.v_mirror_dev, L.call.out["topk_slots_i32"], L.o_new,
                                            128 ** -0.5, (n_rows - sample, n_rows))
                     ev1.record()
                     torch.cuda.synchronize()
                     gpu_us.append(ev0.elapsed_time(ev1) * 1e3 * n_rows / sample)
-                gpu_full_us = sorted(gpu_us)[len(gpu_us) // 2]
                 # the check of the GPU's rows against the workers' (rounding of the 16-bit result apart)
                 Lc = probe[-1]
+                Lc.host_call.run()
                 ref_rows = Lc.o_new_host.view(n_rows, 128)[n_rows - sample:].float()
                 got_rows = Lc.o_new.view(n_rows, 128)[n_rows - sample:].float().cpu()
                 agree = bool(((got_rows - ref_rows).abs() <= 1e-3 + 2.0 ** -7 * ref_rows.abs()).all())
-                if want_share == "auto":
-                    f = 0.9 * host_us / (host_us + gpu_full_us)     # a little less than the balance point: both sides slow each other
-                else:
-                    f = float(want_share)
-                f = min(max(f, 0.0), 0.5) if agree else 0.0
-                cut = n_rows - int(round(f * n_rows))
-                share_info.update({"share": (n_rows - cut) / n_rows, "rows_gpu": n_rows - cut, "rows_host": cut,
-                                   "host_us_per_layer_alone": host_us, "gpu_us_per_layer_alone": gpu_full_us,
-                                   "gpu_link_GBps": n_rows * w["top_k"] * 512 / gpu_full_us / 1e3,
-                                   "rows_agree_with_host": agree})
+                share_info["rows_agree_with_host"] = agree
+                if agree:
+                    gpu_full_us = sorted(gpu_us)[len(gpu_us) // 2]
+                    share_info["gpu_us_per_layer_alone"] = gpu_full_us
+                    share_info["gpu_link_GBps"] = n_rows * w["top_k"] * 512 / gpu_full_us / 1e3
             except Exception as exc:        # the mirrors could not be page-locked, or the probe failed: workers only
-                cut, share_info = n_rows, {"share": 0.0, "why": f"{type(exc).__name__}: {exc}"[:200]}
-        shared_calls = None                 # every rank decides for itself; rank 0 reports its own
-        if cut < n_rows:                    # the share is at most a half: the workers always have rows
-            shared_calls = [ops.HostCorrectionCall(L.q_host, L.k_shadow, L.v_shadow, None, L.slots_host, L.o_new_host,
-                                                   128 ** -0.5, rows=(0, cut)) for L in e2e_layers]
+                gpu_full_us, share_info = None, {"share": 0.0, "why": f"{type(exc).__name__}: {exc}"[:200]}
+
+        def shared_plan(host_us):
+            """Rows for the GPU from the two rates: the workers' per layer inside the pipelined loop and
+            the GPU's alone; a little less than the balance point, since the two slow each other."""
+            f = 0.9 * host_us / (host_us + gpu_full_us) if want_share == "auto" else float(want_share)
+            cut = n_rows - int(round(min(max(f, 0.0), 0.5) * n_rows))      # at most a half: the workers always have rows
+            if cut >= n_rows:
+                return None
             for L in e2e_layers:
                 L.gpu_event = torch.cuda.Event()
+            return {"cut": cut, "calls": [ops.HostCorrectionCall(L.q_host, L.k_shadow, L.v_shadow, None, L.slots_host,
+                                                                 L.o_new_host, 128 ** -0.5, rows=(0, cut)) for L in e2e_layers]}
 
         def merge_e2e(L):  # o_new host -> device, merge, result device -> host; on the copy stream
+            cut = plan["cut"]
             with torch.cuda.stream(copy_stream):
                 if cut < n_rows:            # the workers' rows come from the host, the GPU's are in place
                     copy_stream.wait_event(L.gpu_event)
@@ -1097,6 +1095,7 @@ def main():
 
         def e2e_step():
             main_s = torch.cuda.current_stream()
+            cut, shared_calls = plan["cut"], plan["calls"]
             for L in e2e_layers:
                 L.q.copy_(L.q_host, non_blocking=True)
                 L.call.fused()
@@ -1193,7 +1192,27 @@ def main():
             return float(tt.item())
 
         e2e_steps = max(3, min(args.steps, 10))
-        dt = timed(e2e_step, e2e_steps)
+        dt = timed(e2e_step, e2e_steps)            # the workers do every row
+        # The shared plan is kept only if it is faster, measured the same way.  Under several ranks every
+        # rank takes the second measurement if any rank has a plan (the timing is a collective).
+        mine = shared_plan(dt / len(e2e_layers) * 1e6) if gpu_full_us is not None else None
+        anyone = torch.tensor([1 if mine is not None else 0], dtype=torch.int32, device=device)
+        if world > 1:
+            dist.all_reduce(anyone, op=dist.ReduceOp.MAX)
+        if int(anyone.item()):
+            if mine is not None:
+                plan.update(mine)
+            dt_shared = timed(e2e_step, e2e_steps)
+            rate = lambda t: job_layer_bytes * len(e2e_layers) / t / 1e9
+            share_info.update({"workers_only_GBps": rate(dt), "shared_GBps": rate(dt_shared), "kept": dt_shared < dt})
+            if mine is not None:
+                share_info.update({"share": (n_rows - mine["cut"]) / n_rows, "rows_gpu": n_rows - mine["cut"],
+                                   "rows_host": mine["cut"]})
+            if dt_shared < dt:
+                dt = dt_shared
+            else:
+                plan.update({"cut": n_rows, "calls": None})
+                share_info["share"] = 0.0
         pipelined_out = e2e_layers[-1].out_host.clone()
         dt_serial_wait = timed(e2e_serial_step, max(2, e2e_steps // 2))
         check_out = e2e_layers[-1].out_host.clone()
@@ -1227,7 +1246,7 @@ def main():
                "d2h_bytes_per_step": d2h * world, "ms_per_step": dt_full * 1e3, "steps": e2e_steps,
                "layers_measured": n_e2e, "tokens_per_s": w["batch"] / dt_full, "host_threads_per_rank": cpu_threads,
                "us_per_layer": dt / n_e2e * 1e6, "host_correction_alone_us_per_layer": host_only_us,
-               "gpu_correction": dict(share_info, mirror_bytes_read_by_gpu_per_step=(n_rows - cut) * w["top_k"] * 512 * n_e2e * world,
+               "gpu_correction": dict(share_info, mirror_bytes_read_by_gpu_per_step=(n_rows - plan["cut"]) * w["top_k"] * 512 * n_e2e * world,
                                       what="rows of the correction the GPU computes from the host mirror over the host link "
                                            "(jf_gpu_topk_attn_rows) while the workers do the others; pipelined leg only"),
                "serial_layers": {"value": job_layer_bytes * n_e2e / dt_serial / 1e9, "unit": "GB/s",
