@@ -400,6 +400,8 @@ jf_status_t jf_pool_submit_rows(const void* q, const void* k_shadow, const void*
  *                             (start of the decode workspace, or NULL) and the stream continues
  * All three are capturable: a replayed graph raises the same trigger word again. */
 jf_status_t jf_submit_ctx_watch(int64_t handle, int64_t* trigger_host);
+/* The context's job covers rows [row_begin, row_end) only (see jf_pool_submit_rows); before use. */
+jf_status_t jf_submit_ctx_set_rows(int64_t handle, int64_t row_begin, int64_t row_end);
 jf_status_t jf_submit_ctx_unwatch(int64_t handle);
 jf_status_t jf_stream_signal_host(jf_stream_t stream, int64_t* done_dev, int64_t* trigger_dev);
 jf_status_t jf_stream_wait_host_flag(jf_stream_t stream, const int64_t* flag_dev, int32_t timeout_ms,

@@ -132,6 +132,7 @@ _SIGS = {
                                         C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_int64)]),
     "jf_submit_ctx_watch": (C.c_int32, [C.c_int64, C.c_void_p]),
     "jf_submit_ctx_unwatch": (C.c_int32, [C.c_int64]),
+    "jf_submit_ctx_set_rows": (C.c_int32, [C.c_int64, C.c_int64, C.c_int64]),
     "jf_stream_signal_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "jf_stream_wait_host_flag": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "jf_alloc_mapped": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),

@@ -4,7 +4,9 @@ Only the two paper modes are registered; one code path, no experiment knobs.  En
 variables kept from the reference: ``JETFIRE_MODE``, ``JETFIRE_TOPK``, ``JETFIRE_GROUP_SIZE``,
 ``JETFIRE_CPU_ATTN_THREADS``, ``JETFIRE_MAX_BATCH_SIZE``.  Own: ``JETFIRE_SLOTS_I32``,
 ``JETFIRE_STREAM_ORDERED`` (decode steps queued on the stream without a host wait),
-``JETFIRE_STREAM_SIGNAL`` (``flags`` | ``callbacks``: how such a step meets the host) and
+``JETFIRE_STREAM_SIGNAL`` (``flags`` | ``callbacks``: how such a step meets the host),
+``JETFIRE_GPU_CORRECTION_SHARE`` (0..0.5: rows of the correction the GPU computes itself from the
+mapped mirror over the host link, stream-ordered steps with flags only) and
 ``JETFIRE_NUMA_NODE`` (``auto`` | ``off`` | a node number: where the host mirrors and the
 correction workers of this rank are placed).
 """
@@ -51,6 +53,7 @@ class JetFireConfig:
     numa_node: int = NUMA_AUTO            # memory node of mirrors and workers: NUMA_AUTO, NUMA_OFF or a node
     stream_ordered: bool = True           # decode step queued on the stream without a host wait (capturable)
     stream_signal: str = "flags"          # how a stream-ordered step meets the host: "flags" or "callbacks"
+    gpu_correction_share: float = 0.0     # fraction of the correction's rows the GPU computes from the mapped mirror
 
     @property
     def scheme(self) -> QuantScheme:
@@ -115,10 +118,17 @@ def get_jetfire_config() -> JetFireConfig:
     signal = (os.environ.get("JETFIRE_STREAM_SIGNAL") or "flags").strip().lower()
     if signal not in ("flags", "callbacks"):
         raise ValueError(f"JETFIRE_STREAM_SIGNAL must be 'flags' or 'callbacks', got {signal!r}")
+    try:
+        share = float(os.environ.get("JETFIRE_GPU_CORRECTION_SHARE") or 0.0)
+    except ValueError as exc:
+        raise ValueError("JETFIRE_GPU_CORRECTION_SHARE must be a number between 0 and 0.5") from exc
+    if not 0.0 <= share <= 0.5:
+        raise ValueError("JETFIRE_GPU_CORRECTION_SHARE must be a number between 0 and 0.5")
     _CONFIG = JetFireConfig(mode=mode, top_k=top_k, group_size=group, cpu_attn_threads=threads,
                             max_batch_size=_int_env("JETFIRE_MAX_BATCH_SIZE", 32),
                             slots_i32=_int_env("JETFIRE_SLOTS_I32", 1) != 0, numa_node=_numa_env(),
-                            stream_ordered=_int_env("JETFIRE_STREAM_ORDERED", 1) != 0, stream_signal=signal)
+                            stream_ordered=_int_env("JETFIRE_STREAM_ORDERED", 1) != 0, stream_signal=signal,
+                            gpu_correction_share=share)
     return _CONFIG
 
 

@@ -130,6 +130,15 @@ class _StreamStep:
         self.slots_host = torch.zeros(B, H_q, top_k, dtype=slot_dtype).pin_memory()
         self.out = torch.zeros(B, H_q, 128, dtype=dtype, device=device)
         self.flags = cfg.stream_signal == "flags"
+        # rows [cut, B * H_q) of the correction are the GPU's (read from the mapped mirror over the host
+        # link while the workers do the others): only with flags, where the kernel that waits for the
+        # workers comes after it on the stream
+        rows = B * H_q
+        self.rows, self.cut = rows, rows
+        if self.flags and cfg.gpu_correction_share > 0.0 and store._k_shadow_dev is not None:
+            self.cut = max(1, rows - int(round(min(cfg.gpu_correction_share, 0.5) * rows)))
+        self.mirrors_dev = (store._k_shadow_dev, store._v_shadow_dev)
+        self.scale = scale
         if self.flags:
             # the correction is started and joined through two words in mapped memory (a line apart),
             # and its result is read by the merge kernel where the workers wrote it
@@ -138,7 +147,8 @@ class _StreamStep:
             self.o_new_host, self.o_new = ops.alloc_mapped_pinned_pair((B, H_q, 128), dtype)
             self.o_new_host.zero_()
             self.host = ops.HostCorrectionCall(self.q_host, store.k_shadow, store.v_shadow, None, self.slots_host,
-                                               self.o_new_host, scale, done_flag=self.words_host[8:9])
+                                               self.o_new_host, scale, done_flag=self.words_host[8:9],
+                                               rows=(0, self.cut) if self.cut < rows else None)
             self.host.watch(self.words_host[0:1])
         else:
             self.o_new_host = torch.zeros(B, H_q, 128, dtype=dtype).pin_memory()
@@ -172,6 +182,9 @@ class _StreamStep:
         self.slots_host.copy_(self.slots_dev, non_blocking=True)
         if self.flags:
             ops.stream_signal_host(self.words_dev[8:9], self.words_dev[0:1])
+            if self.cut < self.rows:        # the GPU's rows, while the workers do theirs
+                ops.gpu_topk_attn_rows(self.q, self.mirrors_dev[0], self.mirrors_dev[1], self.slots_dev, self.o_new,
+                                       self.scale, (self.cut, self.rows))
             ops.stream_wait_host_flag(self.words_dev[8:9], _HOST_WAIT_MS, self.call.status_record())
         else:
             self.host.stream_submit()
@@ -227,7 +240,7 @@ def decode_batched_stream_ordered(*, store: JetFireCacheStore, query: torch.Tens
     width = int(block_table.shape[1])
     need_S = min(width * store.block_size, ((int(max_seq_len) + 15) // 16) * 16)
     steps = store.__dict__.setdefault("_stream_steps", {})
-    key = (B, num_heads, top_k, query.dtype, cfg.slots_i32, cfg.stream_signal, float(scale))
+    key = (B, num_heads, top_k, query.dtype, cfg.slots_i32, cfg.stream_signal, float(scale), cfg.gpu_correction_share)
     step = steps.get(key)
     if step is None or step.max_S < need_S or step.max_blocks < min(width, (need_S + 15) // 16):
         max_S = min(width * store.block_size, -(-need_S // _MAX_S_STEP) * _MAX_S_STEP)

@@ -845,6 +845,17 @@ extern "C" jf_status_t jf_submit_ctx_watch(int64_t handle, int64_t* trigger_host
   return JF_OK;
 }
 
+// Restricts the context's job to the (sequence, query head) rows [row_begin, row_end) -- the others
+// being computed elsewhere (jf_gpu_topk_attn_rows); set before the context is used.
+extern "C" jf_status_t jf_submit_ctx_set_rows(int64_t handle, int64_t row_begin, int64_t row_end) {
+  if (!handle) return JF_ERR_ARG;
+  auto* c = reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle));
+  if (row_begin < 0 || row_end <= row_begin || row_end > static_cast<int64_t>(c->job.B) * c->job.H_q) return JF_ERR_ARG;
+  c->job.row_begin = row_begin;
+  c->job.row_count = row_end - row_begin;
+  return JF_OK;
+}
+
 extern "C" jf_status_t jf_submit_ctx_unwatch(int64_t handle) {
   if (!handle) return JF_ERR_ARG;
   dispatcher().unwatch(reinterpret_cast<SubmitCtx*>(static_cast<intptr_t>(handle)));

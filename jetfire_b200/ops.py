@@ -654,7 +654,7 @@ class HostCorrectionCall:
         self._keep = (q, k_shadow, v_shadow, head_map, ts_buf, o_new, done_flag)
         i32 = _i32(ts_buf)   # 32-bit slot list: the entry points of the same names with the _i32 suffix
         # rows=(begin, end): only that range of the B * H_q (sequence, query head) rows, the rest being
-        # someone else's (gpu_topk_attn_rows); submit() / run() only
+        # someone else's (gpu_topk_attn_rows)
         self._rows = None
         if rows is not None:
             r0, r1 = int(rows[0]), int(rows[1])
@@ -691,11 +691,12 @@ class HostCorrectionCall:
     # -- stream-ordered form (the reference's create_cpu_topk_submit_ctx /
     #    stream_submit_cpu_topk_attn / stream_wait_cpu_topk_attn, csrc/cpu_topk_attn.cpp:2147-2312) --
     def _handle(self) -> int:
-        _require(self._rows is None, "HostCorrectionCall: a row range is served by submit() / run() only")
         if getattr(self, "_ctx", None) is None:
             h = C.c_int64(0)
             check("create_cpu_topk_submit_ctx", self._fn_ctx(*self._args, 0, C.byref(h)))
             self._ctx = h.value
+            if self._rows is not None:
+                check("submit_ctx_set_rows", lib.jf_submit_ctx_set_rows(self._ctx, self._rows[-2], self._rows[-1]))
         return self._ctx
 
     def stream_submit(self, stream=None) -> None:

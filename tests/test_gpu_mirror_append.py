@@ -483,6 +483,34 @@ def test_stream_ordered_decode_entry_eager_and_captured(mode_name, mode, signal)
     del graph
 
 
+def test_stream_ordered_step_with_rows_of_the_correction_on_the_gpu():
+    """With a share of the correction's rows given to the GPU (read from the mapped mirror over the
+    host link while the workers do the others) the decode entry still gives the oracle's output."""
+    from jetfire_b200.adapter.cache_store import JetFireCacheStore
+    from jetfire_b200.adapter.config import JetFireConfig
+    from jetfire_b200.adapter import decode_path as dp
+    case = Case("k3v2", 2, 8, 2, 400, lens=[400, 263], seed=49)
+    cfg = JetFireConfig(mode="SymInt3K_SymInt2V", top_k=64, group_size=64, cpu_attn_threads=2, gpu_correction_share=0.3)
+    st = JetFireCacheStore(num_blocks=case.n_blocks, num_kv_heads=case.H_kv, head_dim=128, cfg=cfg, device="cuda",
+                           dtype=case.dtype, mirror_append="mapped")
+    st.write_slots(case.k_full.transpose(0, 1).contiguous().cuda(), case.v_full.transpose(0, 1).contiguous().cuda(),
+                   torch.arange(case.num_slots, dtype=torch.int64, device="cuda"))
+    impl = SimpleNamespace(scale=case.attn_scale, attn_type=SimpleNamespace(name="DECODER"))
+    layer = SimpleNamespace(num_heads=case.H_q, num_kv_heads=case.H_kv, head_size=128, layer_name="l0")
+    md = dp.make_decode_metadata(case.seq_lens.cuda(), case.block_table.cuda())
+    want = O.bf16_bits_to_f32(O.f32_to_bf16_bits(case.oracle_step(64)["out"]))
+    for _ in range(2):                      # the second run reuses the step's buffers
+        out = torch.zeros(case.B, case.H_q * 128, dtype=case.dtype, device="cuda")
+        assert dp.try_jetfire_decode(impl=impl, layer=layer, query=case.q.cuda(), attn_metadata=md, output=out,
+                                     store=st, cfg=cfg) is out
+        torch.cuda.synchronize()
+        step = dp.stream_steps(st)[0]
+        step.status()
+        assert (step.rows, step.cut) == (16, 11)            # 5 of the 16 rows on the GPU
+        err = np.abs(f32_values(out).reshape(case.B, case.H_q, 128) - want)
+        assert (err <= 2e-3 + (1e-3 + 2 ** -8) * np.abs(want)).all(), f"max err {err.max():.3e}"
+
+
 def test_stream_ordered_step_is_replaced_when_the_sequences_outgrow_it():
     """The stream-ordered step holds buffers for rows up to a multiple of 4096 positions; when a
     sequence grows past that the step is replaced (the old one released once the stream has

@@ -69,6 +69,23 @@ def test_several_contexts_are_watched_at_once():
         call.close()
 
 
+def test_a_watched_context_may_cover_a_range_of_rows():
+    ops.set_cpu_attn_threads(2)
+    q, k, v, ts = _buffers(31)
+    want = torch.empty_like(q)
+    ops.cpu_topk_attn(q, k, v, None, ts, want, 0.09)
+    words = torch.zeros(16, dtype=torch.int64)
+    got = torch.full_like(q, 7.0)
+    call = ops.HostCorrectionCall(q, k, v, None, ts, got, 0.09, done_flag=words[8:9], rows=(2, 13))
+    call.watch(words[0:1])
+    words[0] = 1
+    assert _wait(words[8:9], 1)
+    g, w = got.view(-1, 128), want.view(-1, 128)
+    assert torch.equal(g[2:13], w[2:13]) and bool((g[:2] == 7).all()) and bool((g[13:] == 7).all())
+    call.close()
+    assert _lib.lib.jf_submit_ctx_set_rows(0, 0, 1) == _lib.JF_ERR_ARG
+
+
 def test_watch_arguments():
     l = _lib.lib
     assert l.jf_submit_ctx_watch(0, None) == _lib.JF_ERR_ARG

@@ -209,8 +209,6 @@ def test_host_correction_over_a_range_of_rows():
     for bad in ((4, 4), (-1, 3), (3, 25), (9, 2)):
         with pytest.raises(RuntimeError):
             ops.HostCorrectionCall(q, k, v, None, ts, part, 0.09, rows=bad)
-    with pytest.raises(RuntimeError):
-        ops.HostCorrectionCall(q, k, v, None, ts, part, 0.09, rows=(0, 4)).stream_submit()
     t = _lib.C.c_int64(0)
     args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), None, ts.data_ptr(), 1, part.data_ptr(), 0, B, H_q, H_kv, slots, K, 0.09, None)
     assert _lib.lib.jf_pool_submit_rows(*args, 4, 4, _lib.C.byref(t)) == _lib.JF_ERR_ARG
