@@ -43,6 +43,34 @@ def test_split_rejects_inconsistent_input():
         mb.split_mixed_batch([0, 1, 2, 3], [1, 1])
 
 
+def test_split_partitions_the_rows_of_any_step():
+    """Seeded random steps: every query row belongs to exactly one part, the prefill offsets are the
+    running sum of the prefill lengths, and a step counts as ordered exactly when its decode
+    sequences come before its prefill sequences (empty sequences aside)."""
+    import random
+    rnd = random.Random(5)
+    for _ in range(300):
+        n = rnd.randint(1, 12)
+        qlens = [rnd.choice([0, 1, 1, 1, 2, 3, 7, 40]) for _ in range(n)]
+        seq_lens = [q + (rnd.choice([0, 0, 5, 100]) if q else 0) for q in qlens]
+        qsl = [0]
+        for q in qlens:
+            qsl.append(qsl[-1] + q)
+        sp = mb.split_mixed_batch(qsl, seq_lens)
+        assert sorted(sp.decode_rows + sp.prefill_rows) == list(range(qsl[-1]))
+        assert sp.decode_seqs == [i for i, q in enumerate(qlens) if q == 1]
+        assert sp.prefill_seqs == [i for i, q in enumerate(qlens) if q > 1]
+        assert sp.prefill_cu == [0] + [sum(qlens[i] for i in sp.prefill_seqs[:k + 1]) for k in range(len(sp.prefill_seqs))]
+        assert sp.max_prefill_len == max([qlens[i] for i in sp.prefill_seqs], default=0)
+        assert sp.prefill_with_context == [i for i in sp.prefill_seqs if seq_lens[i] != qlens[i]]
+        live = [q for q in qlens if q]
+        kinds = ["d" if q == 1 else "p" for q in live]
+        decode_first = "".join(kinds) == "d" * kinds.count("d") + "p" * kinds.count("p")
+        contiguous_decodes = (not sp.decode_seqs
+                              or sp.decode_seqs == list(range(sp.decode_seqs[0], sp.decode_seqs[0] + len(sp.decode_seqs))))
+        assert sp.ordered == (decode_first and contiguous_decodes), (qlens, sp)
+
+
 def test_counts_noted_on_the_metadata():
     md = mb.annotate_split_counts(SimpleNamespace(), torch.tensor([0, 1, 2, 7]), torch.tensor([9, 12, 5]))
     assert (md.num_decodes, md.num_prefills, md.num_decode_tokens, md.num_prefill_tokens) == (2, 1, 2, 5)
